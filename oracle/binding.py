@@ -1,0 +1,145 @@
+"""ctypes binding of the CPU oracle (libsz_oracle.so).  TEST INFRASTRUCTURE ONLY: the checker, never the product."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+F32, F16, Q8_0, IQ3_S, BF16, EXL3_BASE = 0, 1, 8, 21, 30, 1020
+
+
+def build():
+    """Compiles the oracle with the committed Makefile (gcc, -ffp-contract=off)."""
+    subprocess.run(["make", "-C", _HERE, "-s"], check=True)
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "libsz_oracle.so")
+        if not os.path.exists(path):
+            build()
+        L = C.CDLL(path)
+        L.szo_f16_to_f32.restype = C.c_float
+        L.szo_f16_to_f32.argtypes = [C.c_uint16]
+        L.szo_f32_to_f16.restype = C.c_uint16
+        L.szo_f32_to_f16.argtypes = [C.c_float]
+        L.szo_bf16_to_f32.restype = C.c_float
+        L.szo_bf16_to_f32.argtypes = [C.c_uint16]
+        L.szo_f32_to_bf16.restype = C.c_uint16
+        L.szo_f32_to_bf16.argtypes = [C.c_float]
+        L.szo_f64_to_f16_bits.restype = C.c_uint16
+        L.szo_f64_to_f16_bits.argtypes = [C.c_double]
+        L.szo_dequant.restype = C.c_int
+        L.szo_dequant.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t]
+        L.szo_exl3_cb.restype = C.c_float
+        L.szo_exl3_cb.argtypes = [C.c_int, C.c_uint32]
+        L.szo_exl3_state.restype = C.c_uint32
+        L.szo_exl3_blob_len.restype = C.c_size_t
+        L.szo_exl3_blob_len.argtypes = [C.c_size_t, C.c_size_t, C.c_int, C.c_int]
+        L.szo_exl3_reconstruct.argtypes = [C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        L.szo_exl3_matvec_blob.argtypes = [C.c_size_t, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_void_p,
+                                           C.c_void_p, C.c_int]
+        L.szo_matvec.restype = C.c_int
+        L.szo_matvec.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_int]
+        L.szo_route.restype = C.c_int
+        L.szo_route.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        L.szo_sigmoid.restype = C.c_float
+        L.szo_sigmoid.argtypes = [C.c_float]
+        L.szo_silu.restype = C.c_float
+        L.szo_silu.argtypes = [C.c_float]
+        L.szo_softplus.restype = C.c_float
+        L.szo_softplus.argtypes = [C.c_float]
+        L.szo_moe.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+        _LIB = L
+    return _LIB
+
+
+def _p(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def dequant(ty, data):
+    data = np.ascontiguousarray(data, dtype=np.uint8).reshape(-1)
+    be, bb = {F32: (1, 4), F16: (1, 2), BF16: (1, 2), Q8_0: (32, 34), IQ3_S: (256, 110)}[ty]
+    out = np.empty(data.size // bb * be, dtype=np.float32)
+    rc = lib().szo_dequant(ty, _p(data), data.size, _p(out), out.size)
+    if rc != 0:
+        raise ValueError("szo_dequant: %d" % rc)
+    return out
+
+
+def exl3_blob_len(n_in, n_out, bits, half=0):
+    return lib().szo_exl3_blob_len(n_in, n_out, bits, half)
+
+
+def exl3_reconstruct(n_in, n_out, bits, blob, cb=2, half=0):
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    assert blob.size == exl3_blob_len(n_in, n_out, bits, half)
+    w = np.empty((n_in, n_out), dtype=np.float32)
+    lib().szo_exl3_reconstruct(n_in, n_out, bits, half, cb, _p(blob), _p(w))
+    return w
+
+
+def exl3_decode_tile(tile, bits, cb=2, half=0, fast=False):
+    tile = np.ascontiguousarray(tile, dtype=np.uint16)
+    out = np.empty(256, dtype=np.float32)
+    fn = lib().szo_exl3_decode_tile_fast if fast else lib().szo_exl3_decode_tile
+    fn(_p(tile), C.c_int(bits), C.c_int(half), C.c_int(cb), _p(out))
+    return out
+
+
+def wht128(v):
+    v = np.array(v, dtype=np.float32).copy()
+    lib().szo_wht128(_p(v))
+    return v
+
+
+def matvec(ty, data, rows, cols, x, threads=1):
+    data = np.ascontiguousarray(data, dtype=np.uint8).reshape(-1)
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    assert x.size == cols
+    y = np.empty(rows, dtype=np.float32)
+    rc = lib().szo_matvec(ty, _p(data), rows, cols, _p(x), _p(y), threads)
+    if rc != 0:
+        raise ValueError("szo_matvec: %d" % rc)
+    return y
+
+
+def route(logits, k):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    idx = np.empty(k, dtype=np.int32)
+    w = np.empty(k, dtype=np.float64)
+    n = lib().szo_route(_p(logits), logits.size, k, _p(idx), _p(w))
+    return idx[:n], w[:n]
+
+
+class MoeLayerC(C.Structure):
+    _fields_ = [("hidden", C.c_int32), ("n_expert", C.c_int32), ("top_k", C.c_int32), ("expert_ff", C.c_int32),
+                ("shared_ff", C.c_int32), ("expert_type", C.c_int32), ("shared_type", C.c_int32),
+                ("router", C.c_void_p), ("shared_router", C.c_void_p),
+                ("gate", C.c_void_p), ("up", C.c_void_p), ("down", C.c_void_p),
+                ("gate_stride", C.c_uint64), ("up_stride", C.c_uint64), ("down_stride", C.c_uint64),
+                ("sh_gate", C.c_void_p), ("sh_up", C.c_void_p), ("sh_down", C.c_void_p)]
+
+
+def moe(layer, u, threads=1):
+    """`layer`: dict of numpy arrays and shapes (see shadow-engine_b200 `synth.make_moe_layer`).  One token.
+
+    Returns (y[hidden] f32, route_idx[k] i32, route_w[k] f64, logits[n_expert] f32)."""
+    Ls = MoeLayerC(layer["hidden"], layer["n_expert"], layer["top_k"], layer["expert_ff"], layer["shared_ff"],
+                   layer["expert_type"], layer["shared_type"],
+                   _p(layer["router"]), _p(layer["shared_router"]),
+                   _p(layer["gate"]), _p(layer["up"]), _p(layer["down"]),
+                   layer["gate"].strides[0], layer["up"].strides[0], layer["down"].strides[0],
+                   _p(layer["sh_gate"]), _p(layer["sh_up"]), _p(layer["sh_down"]))
+    u = np.ascontiguousarray(u, dtype=np.float32)
+    y = np.empty(layer["hidden"], dtype=np.float32)
+    idx = np.empty(layer["top_k"], dtype=np.int32)
+    w = np.empty(layer["top_k"], dtype=np.float64)
+    logits = np.empty(layer["n_expert"], dtype=np.float32)
+    lib().szo_moe(C.byref(Ls), _p(u), _p(y), _p(idx), _p(w), _p(logits), threads)
+    return y, idx, w, logits
