@@ -1,0 +1,102 @@
+// Shared device/host helpers for the shadowzero_b200 kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <stdarg.h>
+
+#include "../../include/shadowzero_b200.h"
+
+typedef uint8_t u8;
+typedef uint16_t u16;
+typedef uint32_t u32;
+typedef uint64_t u64;
+
+// ---- host side: errors ------------------------------------------------------------------------------------------------
+void sz_set_error(const char* fmt, ...);
+int sz_fail(int code, const char* fmt, ...);
+#define SZ_CUDA(expr)                                                                                   \
+    do {                                                                                                \
+        cudaError_t e_ = (expr);                                                                        \
+        if (e_ != cudaSuccess) return sz_fail(SZ_E_CUDA, "%s: %s", #expr, cudaGetErrorString(e_));      \
+    } while (0)
+
+static inline bool sz_aligned16(u64 p) { return (p & 15) == 0; }
+
+// Launch with the programmatic-dependent-launch attribute: the kernel may start while its predecessor on the stream drains;
+// every such kernel calls sz_pdl_wait() before it touches anything the predecessor wrote.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t sz_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
+                                    Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// ---- device side --------------------------------------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+// Wait for the kernels this one depends on (no-op when launched without the PDL attribute).
+__device__ __forceinline__ void sz_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Let the next kernel on the stream begin its prologue.
+__device__ __forceinline__ void sz_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+__device__ __forceinline__ float sz_f16_to_f32(u16 h) { return __half2float(__ushort_as_half(h)); }
+__device__ __forceinline__ float sz_bf16_to_f32(u16 b) { return __uint_as_float((u32)b << 16); }
+
+__device__ __forceinline__ float sz_warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ double sz_warp_sum(double v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// sigmoid as the CPU reference computes it: in f64, then narrowed (crates/shadowzero-model/src/forward.rs:262-264).
+__device__ __forceinline__ float sz_sigmoid(float x) { return (float)(1.0 / (1.0 + exp(-(double)x))); }
+__device__ __forceinline__ float sz_silu(float x) { return x * sz_sigmoid(x); }
+
+// ---- mbarrier + bulk async copy (TMA engine, untiled form) ---------------------------------------------------------------
+__device__ __forceinline__ u32 sz_smem_addr(const void* p) { return (u32)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void sz_mbar_init(u64* bar, u32 count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(sz_smem_addr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void sz_mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void sz_mbar_expect_tx(u64* bar, u32 bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(sz_smem_addr(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait on a phase: gives up after `limit` polls and returns false (the caller records an error and leaves).
+__device__ __forceinline__ bool sz_mbar_wait(u64* bar, u32 phase, u32 limit = 20000000u) {
+    u32 ok = 0;
+    for (u32 i = 0; i < limit; i++) {
+        asm volatile(
+            "{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+            : "=r"(ok)
+            : "r"(sz_smem_addr(bar)), "r"(phase)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// global -> shared bulk copy; src and dst 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void sz_bulk_g2s(void* dst, const void* src, u32 bytes, u64* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(sz_smem_addr(dst)),
+                 "l"(src), "r"(bytes), "r"(sz_smem_addr(bar))
+                 : "memory");
+}
+
+#endif  // __CUDACC__

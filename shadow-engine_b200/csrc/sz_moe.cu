@@ -1,0 +1,597 @@
+// The MoE sublayer of a verify pass for 1..8 rows: router + plan, grouped expert FFN, weighted combine.
+// Arithmetic follows Session::moe of the CPU reference (crates/shadowzero-model/src/forward.rs:1009-1034): router logits and
+// the softmax in f64, expert dot products accumulated in f32, the weighted sum over experts in f64 in rank order.
+#include "sz_moe.cuh"
+
+#include <float.h>
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// router: logits (a warp a router row, f64 accumulate), then the last block to finish does softmax, top-k and the plan
+
+#define SZ_ROUTE_WARPS 4
+
+__device__ __forceinline__ bool sz_better(float ad, int ai, float bd, int bi) { return ad > bd || (ad == bd && ai < bi); }
+
+__global__ void __launch_bounds__(SZ_ROUTE_WARPS * 32)
+sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restrict__ router, const float* __restrict__ shared_router,
+                int ne, int k, float* __restrict__ logits, int32_t* __restrict__ ridx, double* __restrict__ rw, SzPlan* __restrict__ plan,
+                SzPlan* __restrict__ plan_sh, u32* __restrict__ ctrl, int32_t* __restrict__ out_idx, double* __restrict__ out_w) {
+    __shared__ float dl[SZ_ROUTE_WARPS][SZ_MAX_EXPERTS];
+    __shared__ int cnt[SZ_MAX_EXPERTS];
+    __shared__ int slot_of[SZ_MAX_EXPERTS];
+    __shared__ int sel[SZ_MAX_VERIFY * SZ_MAX_TOPK];
+    __shared__ int s_last, s_groups;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ld = ne + 1;
+    sz_pdl_wait();
+    sz_pdl_trigger();
+
+    // ---- logits: row r of the router (row ne: the shared expert's gate) against every x row
+    const int r = blockIdx.x * SZ_ROUTE_WARPS + warp;
+    if (r < ne || (r == ne && shared_router != nullptr)) {
+        const float4* wrow = (const float4*)(r < ne ? router + (size_t)r * H : shared_router);
+        double acc[SZ_MAX_VERIFY];
+#pragma unroll
+        for (int j = 0; j < SZ_MAX_VERIFY; j++) acc[j] = 0.0;
+        for (int c = lane; c < H / 4; c += 32) {
+            const float4 w = __ldg(wrow + c);
+#pragma unroll
+            for (int j = 0; j < SZ_MAX_VERIFY; j++) {
+                if (j < m) {
+                    const float4 v = __ldg((const float4*)(x + (size_t)j * H) + c);
+                    acc[j] += (double)w.x * (double)v.x;
+                    acc[j] += (double)w.y * (double)v.y;
+                    acc[j] += (double)w.z * (double)v.z;
+                    acc[j] += (double)w.w * (double)v.w;
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < SZ_MAX_VERIFY; j++) {
+            if (j < m) {
+                const double s = sz_warp_sum(acc[j]);
+                if (lane == 0) logits[(size_t)j * ld + r] = (float)s;
+            }
+        }
+    }
+
+    // ---- the last block to arrive routes every row
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(&ctrl[0], 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+
+    for (int j = warp; j < m; j += SZ_ROUTE_WARPS) {
+        float* d = dl[warp];
+        float mx = -FLT_MAX;  // f32::MIN, forward.rs:1093
+        for (int i = lane; i < ne; i += 32) {
+            const float v = __ldcg(logits + (size_t)j * ld + i);
+            d[i] = v;
+            mx = fmaxf(mx, v);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        double z = 0.0;
+        for (int i = lane; i < ne; i += 32) {
+            const float dv = d[i] - mx;  // in f32, as the reference subtracts before widening
+            d[i] = dv;
+            z += exp((double)dv);
+        }
+        z = sz_warp_sum(z);
+        // top-k by (value descending, index ascending); exp is monotone, so the order of d is the order of ex
+        u32 taken = 0;
+        for (int t = 0; t < k; t++) {
+            float bd = -INFINITY;
+            int bi = 0x7fffffff;
+            for (int q = 0, i = lane; i < ne; q++, i += 32) {
+                if (!((taken >> q) & 1u) && sz_better(d[i], i, bd, bi)) { bd = d[i]; bi = i; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (sz_better(od, oi, bd, bi)) { bd = od; bi = oi; }
+            }
+            if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+            if (lane == 0) sel[j * SZ_MAX_TOPK + t] = bi;
+        }
+        __syncwarp();
+        double tz = 0.0;
+        for (int t = 0; t < k; t++) tz += exp((double)d[sel[j * SZ_MAX_TOPK + t]]) / z;
+        if (lane < k) {
+            const int e = sel[j * SZ_MAX_TOPK + lane];
+            const double wv = (exp((double)d[e]) / z) / tz;
+            ridx[j * k + lane] = e;
+            rw[j * k + lane] = wv;
+            if (out_idx) out_idx[j * k + lane] = e;
+            if (out_w) out_w[j * k + lane] = wv;
+        }
+        __syncwarp();
+    }
+    for (int i = threadIdx.x; i < ne; i += blockDim.x) cnt[i] = 0;
+    __syncthreads();
+
+    // ---- plan: groups in ascending expert order, rows ascending inside a group
+    const int pairs = m * k;
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[sel[(p / k) * SZ_MAX_TOPK + p % k]], 1);
+    __syncthreads();
+    if (warp == 0) {
+        int running = 0;
+        for (int base = 0; base < ne; base += 32) {
+            const int e = base + lane;
+            const int c = e < ne ? cnt[e] : 0;
+            const u32 mask = __ballot_sync(0xffffffffu, c > 0);
+            if (c > 0) {
+                const int slot = running + __popc(mask & ((1u << lane) - 1u));
+                slot_of[e] = slot;
+                plan->expert[slot] = e;
+                plan->count[slot] = c;
+            }
+            running += __popc(mask);
+        }
+        if (lane == 0) { s_groups = running; plan->n_groups = running; }
+    }
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int j = p / k;
+        const int e = sel[j * SZ_MAX_TOPK + p % k];
+        int pos = 0;
+        for (int jj = 0; jj < j; jj++)
+            for (int t = 0; t < k; t++) pos += (sel[jj * SZ_MAX_TOPK + t] == e);
+        const int g = slot_of[e];
+        plan->rows[g][pos] = j;
+        plan->pairs[g][pos] = p;
+    }
+    // the shared expert: one group holding every row; its per-pair buffers are indexed by row
+    if (threadIdx.x < SZ_MAX_VERIFY) {
+        plan_sh->rows[0][threadIdx.x] = threadIdx.x;
+        plan_sh->pairs[0][threadIdx.x] = threadIdx.x;
+    }
+    if (threadIdx.x == 0) {
+        plan_sh->n_groups = 1;
+        plan_sh->expert[0] = 0;
+        plan_sh->count[0] = m;
+        ctrl[0] = 0;  // ready for the next call
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// block formats (Q8_0, IQ3_S): a warp a matrix row, a lane four consecutive weights of every 128
+
+// Adds to acc[j] the lane's share of row . xs[j] for j < N.  `row`: the matrix row's bytes (2-byte aligned); xs: shared, [N][cols].
+template <int TYPE, int N>
+__device__ __forceinline__ void sz_row_dot(const u8* __restrict__ row, int cols, const float* xs, const u32* grid, int lane, float* acc) {
+    for (int e = 4 * lane; e < cols; e += 128) {
+        float w0, w1, w2, w3, scale;
+        if (TYPE == SZ_TYPE_Q8_0) {
+            const u8* blk = row + (e >> 5) * 34;
+            const int i = e & 31;
+            scale = sz_f16_to_f32(sz_ld16(blk));
+            const u32 q01 = sz_ld16(blk + 2 + i), q23 = sz_ld16(blk + 4 + i);
+            w0 = (float)(int8_t)(q01 & 0xff); w1 = (float)(int8_t)(q01 >> 8);
+            w2 = (float)(int8_t)(q23 & 0xff); w3 = (float)(int8_t)(q23 >> 8);
+        } else {
+            const u8* blk = row + (e >> 8) * 110;
+            const int jj = (e & 255) >> 2;  // group of four inside the superblock
+            const int idx = blk[2 + jj] | (((blk[66 + (jj >> 3)] >> (jj & 7)) & 1) << 8);
+            const int g = jj >> 3;
+            const int s = (blk[106 + (g >> 1)] >> (4 * (g & 1))) & 15;
+            scale = sz_f16_to_f32(sz_ld16(blk)) * (float)(1 + 2 * s);
+            const u32 mags = grid[idx];
+            const u32 sg = blk[74 + (jj >> 1)] >> (4 * (jj & 1));
+            w0 = (float)(mags & 0xff); w1 = (float)((mags >> 8) & 0xff); w2 = (float)((mags >> 16) & 0xff); w3 = (float)(mags >> 24);
+            w0 = (sg & 1) ? -w0 : w0; w1 = (sg & 2) ? -w1 : w1; w2 = (sg & 4) ? -w2 : w2; w3 = (sg & 8) ? -w3 : w3;
+        }
+#pragma unroll
+        for (int j = 0; j < N; j++) {
+            const float4 v = *(const float4*)(xs + (size_t)j * cols + e);
+            float p = w0 * v.x;
+            p = fmaf(w1, v.y, p);
+            p = fmaf(w2, v.z, p);
+            p = fmaf(w3, v.w, p);
+            acc[j] = fmaf(scale, p, acc[j]);
+        }
+    }
+}
+
+template <int TYPE>
+__device__ __forceinline__ int64_t sz_row_bytes(int cols) { return TYPE == SZ_TYPE_Q8_0 ? (int64_t)(cols / 32) * 34 : (int64_t)(cols / 256) * 110; }
+
+// gate and up rows of one group, SwiGLU fused: act[pair][r] = silu(gate_r . x) * (up_r . x)
+template <int TYPE, int N>
+__device__ __forceinline__ void sz_gateup_body(const u8* gate, const u8* up, int H, int FF, const float* xs, const u32* grid,
+                                               const int32_t* pairs, float* act, int r0, int r1) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t rb = sz_row_bytes<TYPE>(H);
+    for (int r = r0 + warp; r < r1; r += 8) {
+        float ag[N], au[N];
+#pragma unroll
+        for (int j = 0; j < N; j++) { ag[j] = 0.f; au[j] = 0.f; }
+        sz_row_dot<TYPE, N>(gate + r * rb, H, xs, grid, lane, ag);
+        sz_row_dot<TYPE, N>(up + r * rb, H, xs, grid, lane, au);
+#pragma unroll
+        for (int j = 0; j < N; j++) {
+            const float g = sz_warp_sum(ag[j]), u = sz_warp_sum(au[j]);
+            if (lane == 0) act[(size_t)pairs[j] * FF + r] = sz_silu(g) * u;
+        }
+    }
+}
+
+template <int TYPE, int N>
+__device__ __forceinline__ void sz_down_body(const u8* down, int FF, int H, const float* xs, const u32* grid, const int32_t* pairs,
+                                             float* eo, int r0, int r1) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t rb = sz_row_bytes<TYPE>(FF);
+    for (int r = r0 + warp; r < r1; r += 8) {
+        float a[N];
+#pragma unroll
+        for (int j = 0; j < N; j++) a[j] = 0.f;
+        sz_row_dot<TYPE, N>(down + r * rb, FF, xs, grid, lane, a);
+#pragma unroll
+        for (int j = 0; j < N; j++) {
+            const float v = sz_warp_sum(a[j]);
+            if (lane == 0) eo[(size_t)pairs[j] * H + r] = v;
+        }
+    }
+}
+
+#define SZ_ROWS_PER_CTA 32
+
+// grid: (ceil(out_rows / SZ_ROWS_PER_CTA), max groups).  DOWN = false: gate/up + SwiGLU from x rows; true: down from act rows.
+template <int TYPE, bool DOWN>
+__global__ void __launch_bounds__(256)
+sz_rows_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 stride0, const u8* __restrict__ w1, u64 stride1,
+               const float* __restrict__ in, int n_in, int n_out, float* __restrict__ out) {
+    extern __shared__ __align__(16) u8 smem[];
+    u32* grid = (u32*)smem;                // 512 words
+    float* xs = (float*)(smem + 2048);     // [n][n_in]
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int g = blockIdx.y;
+    if (g >= plan->n_groups) return;
+    const int n = plan->count[g];
+    const int64_t e = plan->expert[g];
+    const int32_t* src_rows = DOWN ? plan->pairs[g] : plan->rows[g];
+    for (int i = threadIdx.x; i < 512; i += 256) grid[i] = c_iq3s_grid[i];
+    for (int j = 0; j < n; j++) {
+        const float4* src = (const float4*)(in + (size_t)src_rows[j] * n_in);
+        float4* dst = (float4*)(xs + (size_t)j * n_in);
+        for (int i = threadIdx.x; i < n_in / 4; i += 256) dst[i] = __ldcg(src + i);
+    }
+    __syncthreads();
+    const int r0 = blockIdx.x * SZ_ROWS_PER_CTA;
+    const int r1 = min(r0 + SZ_ROWS_PER_CTA, n_out);
+    const u8* a = w0 + e * stride0;
+    const int32_t* pairs = plan->pairs[g];
+    if (!DOWN) {
+        const u8* b = w1 + e * stride1;
+        switch (n) {
+            case 1: sz_gateup_body<TYPE, 1>(a, b, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 2: sz_gateup_body<TYPE, 2>(a, b, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 3: sz_gateup_body<TYPE, 3>(a, b, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 4: sz_gateup_body<TYPE, 4>(a, b, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 5: sz_gateup_body<TYPE, 5>(a, b, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 6: sz_gateup_body<TYPE, 6>(a, b, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 7: sz_gateup_body<TYPE, 7>(a, b, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            default: sz_gateup_body<TYPE, 8>(a, b, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+        }
+    } else {
+        switch (n) {
+            case 1: sz_down_body<TYPE, 1>(a, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 2: sz_down_body<TYPE, 2>(a, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 3: sz_down_body<TYPE, 3>(a, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 4: sz_down_body<TYPE, 4>(a, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 5: sz_down_body<TYPE, 5>(a, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 6: sz_down_body<TYPE, 6>(a, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            case 7: sz_down_body<TYPE, 7>(a, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+            default: sz_down_body<TYPE, 8>(a, n_in, n_out, xs, grid, pairs, out, r0, r1); break;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// EXL3: a block a 128-output slice of one matrix for one group; warp w owns tile column w of the slice
+
+template <int K, int N>
+__device__ __forceinline__ void sz_exl3_body(const u8* __restrict__ blob, int n_in, int n_out, int ob, const float* xr, float* so,
+                                             const int32_t* pairs, float* out) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const u32* tr = (const u32*)(blob + 2 * (size_t)n_in + 2 * (size_t)n_out + 4);
+    const int nt = n_out / 16, kt = n_in / 16;
+    float acc[N][2];
+#pragma unroll
+    for (int j = 0; j < N; j++) { acc[j][0] = 0.f; acc[j][1] = 0.f; }
+    for (int k = 0; k < kt; k++) {
+        u32 st[8];
+        SzExl3Tile<K>::states(tr + ((size_t)k * nt + ob * 8 + warp) * (8 * K), lane, st);
+#pragma unroll
+        for (int jj = 0; jj < 8; jj++) {
+            const float v = sz_exl3_cb2(st[jj]);
+            const int row = k * 16 + sz_exl3_row(lane, jj);
+#pragma unroll
+            for (int j = 0; j < N; j++) acc[j][jj >> 2] = fmaf(xr[(size_t)j * n_in + row], v, acc[j][jj >> 2]);
+        }
+    }
+    // the four lanes that share lane >> 2 hold the four input-row classes of the same two output columns
+#pragma unroll
+    for (int j = 0; j < N; j++) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            float v = acc[j][h];
+            v += __shfl_xor_sync(0xffffffffu, v, 1);
+            v += __shfl_xor_sync(0xffffffffu, v, 2);
+            if ((lane & 3) == 0) so[j * 128 + warp * 16 + (lane >> 2) + 8 * h] = v;
+        }
+    }
+    __syncthreads();
+    // rotate the 128 outputs back and scale: y = H so * svh (exl3.rs:556-562); warp j takes row j
+    const u16* svh = (const u16*)(blob + 2 * (size_t)n_in);
+    for (int j = warp; j < N; j += 8) {
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[e] = so[j * 128 + lane + 32 * e];
+        sz_wht128_warp(v, lane);
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const int c = ob * 128 + lane + 32 * e;
+            out[(size_t)pairs[j] * n_out + c] = (v[e] * SZ_RSQRT128) * sz_f16_to_f32(svh[c]);
+        }
+    }
+}
+
+// grid: (blocks of 128 outputs x matrices, max groups).  in1 != null: the input row is silu(in0) * in1 (the SwiGLU product).
+template <int K>
+__global__ void __launch_bounds__(256)
+sz_exl3_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 stride0, const u8* __restrict__ w1, u64 stride1,
+               const float* __restrict__ in0, const float* __restrict__ in1, int in_by_pair, int n_in, int n_out,
+               float* __restrict__ out0, float* __restrict__ out1) {
+    extern __shared__ __align__(16) u8 smem[];
+    float* so = (float*)smem;              // [8][128]
+    float* xr = (float*)(smem + 4096);     // [n][n_in]
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int g = blockIdx.y;
+    if (g >= plan->n_groups) return;
+    const int n = plan->count[g];
+    const int64_t e = plan->expert[g];
+    const int nblk = n_out / 128;
+    const int mat = blockIdx.x / nblk, ob = blockIdx.x % nblk;
+    const u8* blob = mat == 0 ? w0 + e * stride0 : w1 + e * stride1;
+    float* out = mat == 0 ? out0 : out1;
+    const int32_t* src_rows = in_by_pair ? plan->pairs[g] : plan->rows[g];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the input in the trellis' basis: (x * suh) H on every 128-block (exl3.rs:414-421), a warp a (row, block) item
+    const u16* suh = (const u16*)blob;
+    const int nb = n_in / 128;
+    for (int item = warp; item < n * nb; item += 8) {
+        const int j = item / nb, b = item % nb;
+        const size_t src = (size_t)src_rows[j] * n_in + b * 128;
+        float v[4];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int i = lane + 32 * q;
+            float a = __ldcg(in0 + src + i);
+            if (in1) a = sz_silu(a) * __ldcg(in1 + src + i);
+            v[q] = a * sz_f16_to_f32(suh[b * 128 + i]);
+        }
+        sz_wht128_warp(v, lane);
+#pragma unroll
+        for (int q = 0; q < 4; q++) xr[(size_t)j * n_in + b * 128 + lane + 32 * q] = v[q] * SZ_RSQRT128;
+    }
+    __syncthreads();
+    const int32_t* pairs = plan->pairs[g];
+    switch (n) {
+        case 1: sz_exl3_body<K, 1>(blob, n_in, n_out, ob, xr, so, pairs, out); break;
+        case 2: sz_exl3_body<K, 2>(blob, n_in, n_out, ob, xr, so, pairs, out); break;
+        case 3: sz_exl3_body<K, 3>(blob, n_in, n_out, ob, xr, so, pairs, out); break;
+        case 4: sz_exl3_body<K, 4>(blob, n_in, n_out, ob, xr, so, pairs, out); break;
+        case 5: sz_exl3_body<K, 5>(blob, n_in, n_out, ob, xr, so, pairs, out); break;
+        case 6: sz_exl3_body<K, 6>(blob, n_in, n_out, ob, xr, so, pairs, out); break;
+        case 7: sz_exl3_body<K, 7>(blob, n_in, n_out, ob, xr, so, pairs, out); break;
+        default: sz_exl3_body<K, 8>(blob, n_in, n_out, ob, xr, so, pairs, out); break;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// y[j] = sum over ranks of w * eo (f64, rank order) + sigmoid(shared gate logit) * shared output (forward.rs:1020-1033)
+
+__global__ void __launch_bounds__(256)
+sz_combine_kernel(const float* __restrict__ eo, const double* __restrict__ rw, const float* __restrict__ so,
+                  const float* __restrict__ logits, int ne, int k, int H, int has_shared, float* __restrict__ y) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int j = blockIdx.y;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= H) return;
+    double acc = 0.0;
+    for (int t = 0; t < k; t++) acc += __ldcg(rw + j * k + t) * (double)__ldcg(eo + (size_t)(j * k + t) * H + i);
+    if (has_shared) {
+        const float sg = sz_sigmoid(__ldcg(logits + (size_t)j * (ne + 1) + ne));
+        acc += (double)(sg * __ldcg(so + (size_t)j * H + i));
+    }
+    y[(size_t)j * H + i] = (float)acc;
+}
+
+// ---------------------------------------------------------------------------------------------------------------------------------
+// host side
+
+static bool sz_is_exl3(int t) { return t > 1020 && t <= 1028; }
+static bool sz_is_block(int t) { return t == SZ_TYPE_Q8_0 || t == SZ_TYPE_IQ3_S; }
+
+static int sz_check_matrix(const char* what, int type, int n_in, int n_out) {
+    if (sz_is_exl3(type)) {
+        if (n_in % 128 || n_out % 128) return sz_fail(SZ_E_ARG, "%s: EXL3 needs whole 128-blocks, got %d -> %d", what, n_in, n_out);
+    } else if (type == SZ_TYPE_Q8_0) {
+        if (n_in % 128) return sz_fail(SZ_E_ARG, "%s: Q8_0 rows of %d weights are not a multiple of 128", what, n_in);
+    } else if (type == SZ_TYPE_IQ3_S) {
+        if (n_in % 256) return sz_fail(SZ_E_ARG, "%s: IQ3_S rows of %d weights are not whole superblocks", what, n_in);
+    } else {
+        return sz_fail(SZ_E_TYPE, "%s: no kernel for tensor type %d", what, type);
+    }
+    return SZ_OK;
+}
+
+// Block types start on a 16-byte boundary; an EXL3 blob is placed so that its trellis (after suh, svh and the marker) does.
+static int sz_check_align(const char* what, int type, u64 base, int n_in, int n_out) {
+    const u64 start = sz_is_exl3(type) ? base + 2 * (u64)n_in + 2 * (u64)n_out + 4 : base;
+    if (start & 15) return sz_fail(SZ_E_ARG, "%s: %s must start on a 16-byte boundary", what, sz_is_exl3(type) ? "the trellis of an EXL3 blob" : "the tensor");
+    return SZ_OK;
+}
+
+static int sz_moe_check(const sz_moe_layer* L, int m) {
+    if (!L) return sz_fail(SZ_E_ARG, "null layer");
+    if (m < 1 || m > SZ_MAX_VERIFY) return sz_fail(SZ_E_ARG, "a verify pass has 1..%d rows, got %d", SZ_MAX_VERIFY, m);
+    if (L->hidden <= 0 || L->hidden % 128) return sz_fail(SZ_E_ARG, "hidden = %d is not a positive multiple of 128", L->hidden);
+    if (L->n_expert < 1 || L->n_expert > SZ_MAX_EXPERTS) return sz_fail(SZ_E_ARG, "n_expert = %d (1..%d)", L->n_expert, SZ_MAX_EXPERTS);
+    if (L->top_k < 1 || L->top_k > SZ_MAX_TOPK || L->top_k > L->n_expert)
+        return sz_fail(SZ_E_ARG, "top_k = %d (1..%d, at most n_expert)", L->top_k, SZ_MAX_TOPK);
+    if (L->expert_ff <= 0 || L->shared_ff < 0) return sz_fail(SZ_E_ARG, "expert_ff = %d, shared_ff = %d", L->expert_ff, L->shared_ff);
+    int rc;
+    if ((rc = sz_check_matrix("expert gate/up", L->expert_type, L->hidden, L->expert_ff))) return rc;
+    if ((rc = sz_check_matrix("expert down", L->expert_type, L->expert_ff, L->hidden))) return rc;
+    if (!L->router || !L->gate || !L->up || !L->down) return sz_fail(SZ_E_ARG, "null router or expert tensor");
+    if (!sz_aligned16(L->router) || (L->gate_stride & 15) || (L->up_stride & 15) || (L->down_stride & 15))
+        return sz_fail(SZ_E_ARG, "the router must be 16-byte aligned and expert strides multiples of 16");
+    if ((rc = sz_check_align("expert gate", L->expert_type, L->gate, L->hidden, L->expert_ff))) return rc;
+    if ((rc = sz_check_align("expert up", L->expert_type, L->up, L->hidden, L->expert_ff))) return rc;
+    if ((rc = sz_check_align("expert down", L->expert_type, L->down, L->expert_ff, L->hidden))) return rc;
+    if (L->shared_ff > 0) {
+        if ((rc = sz_check_matrix("shared gate/up", L->shared_type, L->hidden, L->shared_ff))) return rc;
+        if ((rc = sz_check_matrix("shared down", L->shared_type, L->shared_ff, L->hidden))) return rc;
+        if (!L->shared_router || !L->sh_gate || !L->sh_up || !L->sh_down) return sz_fail(SZ_E_ARG, "null shared-expert tensor");
+        if (!sz_aligned16(L->shared_router)) return sz_fail(SZ_E_ARG, "the shared router row must be 16-byte aligned");
+        if ((rc = sz_check_align("shared gate", L->shared_type, L->sh_gate, L->hidden, L->shared_ff))) return rc;
+        if ((rc = sz_check_align("shared up", L->shared_type, L->sh_up, L->hidden, L->shared_ff))) return rc;
+        if ((rc = sz_check_align("shared down", L->shared_type, L->sh_down, L->shared_ff, L->hidden))) return rc;
+    }
+    return SZ_OK;
+}
+
+extern "C" int sz_moe_scratch_bytes(const sz_moe_layer* L, int m, int64_t* bytes) {
+    int rc = sz_moe_check(L, m);
+    if (rc) return rc;
+    if (!bytes) return sz_fail(SZ_E_ARG, "null result pointer");
+    *bytes = sz_moe_layout(L, m).total;
+    return SZ_OK;
+}
+
+extern "C" int sz_moe_scratch_init(uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
+    if (!scratch || scratch_bytes < 256 || (scratch & 255)) return sz_fail(SZ_E_ARG, "scratch must be 256-byte aligned and non-empty");
+    SZ_CUDA(cudaMemsetAsync((void*)scratch, 0, 256, (cudaStream_t)stream));
+    return SZ_OK;
+}
+
+extern "C" int sz_moe_launches(const sz_moe_layer* L) {
+    if (!L) return 0;
+    return L->shared_ff > 0 ? 6 : 4;
+}
+
+template <int TYPE>
+static int sz_launch_rows(cudaStream_t st, const SzPlan* plan, int groups, const u8* gate, u64 gs, const u8* up, u64 us, const u8* down,
+                          u64 ds, const float* x, int H, int FF, float* act, float* eo, bool down_pass) {
+    const size_t smem = 2048 + (size_t)SZ_MAX_VERIFY * (down_pass ? FF : H) * 4;
+    if (!down_pass) {
+        static bool set = false;
+        if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_rows_kernel<TYPE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        dim3 grid((FF + SZ_ROWS_PER_CTA - 1) / SZ_ROWS_PER_CTA, groups);
+        SZ_CUDA(sz_launch(sz_rows_kernel<TYPE, false>, grid, dim3(256), smem, st, true, plan, gate, gs, up, us, x, H, FF, act));
+    } else {
+        static bool set = false;
+        if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_rows_kernel<TYPE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        dim3 grid((H + SZ_ROWS_PER_CTA - 1) / SZ_ROWS_PER_CTA, groups);
+        SZ_CUDA(sz_launch(sz_rows_kernel<TYPE, true>, grid, dim3(256), smem, st, true, plan, down, ds, (const u8*)nullptr, (u64)0, act, FF, H, eo));
+    }
+    return SZ_OK;
+}
+
+template <int K>
+static int sz_launch_exl3(cudaStream_t st, const SzPlan* plan, int groups, const u8* w0, u64 s0, const u8* w1, u64 s1, const float* in0,
+                          const float* in1, int by_pair, int n_in, int n_out, float* out0, float* out1) {
+    static bool set = false;
+    if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_exl3_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+    const size_t smem = 4096 + (size_t)SZ_MAX_VERIFY * n_in * 4;
+    dim3 grid((n_out / 128) * (w1 ? 2 : 1), groups);
+    SZ_CUDA(sz_launch(sz_exl3_kernel<K>, grid, dim3(256), smem, st, true, plan, w0, s0, w1, s1, in0, in1, by_pair, n_in, n_out, out0, out1));
+    return SZ_OK;
+}
+
+// One expert FFN pass (gate/up then down) for the groups of `plan`.
+static int sz_ffn(cudaStream_t st, int type, const SzPlan* plan, int groups, u64 gate, u64 gs, u64 up, u64 us, u64 down, u64 ds,
+                  const float* x, int H, int FF, float* g, float* u, float* eo, bool down_pass) {
+    const u8 *pg = (const u8*)gate, *pu = (const u8*)up, *pd = (const u8*)down;
+    if (type == SZ_TYPE_Q8_0) return sz_launch_rows<SZ_TYPE_Q8_0>(st, plan, groups, pg, gs, pu, us, pd, ds, x, H, FF, g, eo, down_pass);
+    if (type == SZ_TYPE_IQ3_S) return sz_launch_rows<SZ_TYPE_IQ3_S>(st, plan, groups, pg, gs, pu, us, pd, ds, x, H, FF, g, eo, down_pass);
+#define SZ_EXL3_CASE(KK)                                                                                                        \
+    case KK:                                                                                                                    \
+        return down_pass ? sz_launch_exl3<KK>(st, plan, groups, pd, ds, nullptr, 0, g, u, 1, FF, H, eo, nullptr)               \
+                         : sz_launch_exl3<KK>(st, plan, groups, pg, gs, pu, us, x, nullptr, 0, H, FF, g, u);
+    switch (type - 1020) {
+        SZ_EXL3_CASE(1) SZ_EXL3_CASE(2) SZ_EXL3_CASE(3) SZ_EXL3_CASE(4) SZ_EXL3_CASE(5) SZ_EXL3_CASE(6) SZ_EXL3_CASE(7) SZ_EXL3_CASE(8)
+    }
+#undef SZ_EXL3_CASE
+    return sz_fail(SZ_E_TYPE, "no kernel for tensor type %d", type);
+}
+
+extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t y, uint64_t route_idx, uint64_t route_w,
+                             uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
+    int rc = sz_moe_check(L, m);
+    if (rc) return rc;
+    if (!x || !y || !sz_aligned16(x) || !sz_aligned16(y)) return sz_fail(SZ_E_ARG, "x and y must be non-null and 16-byte aligned");
+    if ((route_idx & 3) || (route_w & 7)) return sz_fail(SZ_E_ARG, "misaligned routing output");
+    const SzMoeScratch S = sz_moe_layout(L, m);
+    if (!scratch || (scratch & 255)) return sz_fail(SZ_E_ARG, "scratch must be 256-byte aligned");
+    if (scratch_bytes < S.total) return sz_fail(SZ_E_SCRATCH, "scratch of %lld bytes, %lld needed", (long long)scratch_bytes, (long long)S.total);
+    cudaStream_t st = (cudaStream_t)stream;
+    u8* base = (u8*)scratch;
+    u32* ctrl = (u32*)(base + S.ctrl);
+    float* logits = (float*)(base + S.logits);
+    int32_t* ridx = (int32_t*)(base + S.ridx);
+    double* rw = (double*)(base + S.rw);
+    SzPlan* plan = (SzPlan*)(base + S.plan);
+    SzPlan* plan_sh = (SzPlan*)(base + S.plan_sh);
+    float *g = (float*)(base + S.g), *u = (float*)(base + S.u), *sg = (float*)(base + S.sg), *su = (float*)(base + S.su);
+    float *eo = (float*)(base + S.eo), *so = (float*)(base + S.so);
+    const float* xp = (const float*)x;
+    const int H = L->hidden, FF = L->expert_ff, SF = L->shared_ff;
+    const bool shared = SF > 0;
+
+    const int route_rows = L->n_expert + (shared ? 1 : 0);
+    SZ_CUDA(sz_launch(sz_route_kernel, dim3((route_rows + SZ_ROUTE_WARPS - 1) / SZ_ROUTE_WARPS), dim3(SZ_ROUTE_WARPS * 32), 0, st, false, xp, m, H,
+                      (const float*)L->router, (const float*)(shared ? L->shared_router : 0), (int)L->n_expert, (int)L->top_k, logits, ridx,
+                      rw, plan, plan_sh, ctrl, (int32_t*)route_idx, (double*)route_w));
+    const int groups = m * L->top_k;
+    if ((rc = sz_ffn(st, L->expert_type, plan, groups, L->gate, L->gate_stride, L->up, L->up_stride, L->down, L->down_stride, xp, H, FF, g, u,
+                     eo, false)))
+        return rc;
+    if (shared && (rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, false))) return rc;
+    if ((rc = sz_ffn(st, L->expert_type, plan, groups, L->gate, L->gate_stride, L->up, L->up_stride, L->down, L->down_stride, xp, H, FF, g, u,
+                     eo, true)))
+        return rc;
+    if (shared && (rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true))) return rc;
+    SZ_CUDA(sz_launch(sz_combine_kernel, dim3((H + 255) / 256, m), dim3(256), 0, st, true, (const float*)eo, (const double*)rw, (const float*)so,
+                      (const float*)logits, (int)L->n_expert, (int)L->top_k, H, shared ? 1 : 0, (float*)y));
+    return SZ_OK;
+}
+
+extern "C" int sz_moe_verify_host(const sz_moe_layer* L, const float* x_host, int m, float* y_host, int32_t* route_idx_host,
+                                  double* route_w_host, uint64_t x_dev, uint64_t y_dev, uint64_t scratch, int64_t scratch_bytes,
+                                  uint64_t stream) {
+    int rc = sz_moe_check(L, m);
+    if (rc) return rc;
+    if (!x_host || !y_host || !x_dev || !y_dev) return sz_fail(SZ_E_ARG, "null host or device buffer");
+    cudaStream_t st = (cudaStream_t)stream;
+    const SzMoeScratch S = sz_moe_layout(L, m);
+    const size_t bytes = (size_t)m * L->hidden * sizeof(float);
+    SZ_CUDA(cudaMemcpyAsync((void*)x_dev, x_host, bytes, cudaMemcpyHostToDevice, st));
+    rc = sz_moe_verify(L, x_dev, m, y_dev, 0, 0, scratch, scratch_bytes, stream);
+    if (rc) return rc;
+    SZ_CUDA(cudaMemcpyAsync(y_host, (const void*)y_dev, bytes, cudaMemcpyDeviceToHost, st));
+    if (route_idx_host)
+        SZ_CUDA(cudaMemcpyAsync(route_idx_host, (const u8*)scratch + S.ridx, (size_t)m * L->top_k * 4, cudaMemcpyDeviceToHost, st));
+    if (route_w_host)
+        SZ_CUDA(cudaMemcpyAsync(route_w_host, (const u8*)scratch + S.rw, (size_t)m * L->top_k * 8, cudaMemcpyDeviceToHost, st));
+    SZ_CUDA(cudaStreamSynchronize(st));
+    return SZ_OK;
+}

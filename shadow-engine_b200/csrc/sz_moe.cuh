@@ -1,0 +1,56 @@
+// The MoE sublayer of a verify pass: shared definitions (plan tables, scratch layout).
+#pragma once
+
+#include "sz_formats.cuh"
+
+#define SZ_MAXG (SZ_MAX_VERIFY * SZ_MAX_TOPK)  // most groups (distinct experts) a pass of SZ_MAX_VERIFY rows can touch
+#define SZ_MAX_EXPERTS 1024
+
+// The routed work of one pass, grouped by expert so a matrix is streamed once for every row that chose it.  Groups are in
+// ascending expert order; inside a group the rows are in ascending row order.  (The reference's group record is
+// [count, in rows.., out rows..], crates/shadowzero-cuda/src/session.rs:2129-2146; pair = row * top_k + rank.)
+struct SzPlan {
+    int32_t n_groups;
+    int32_t pad[3];
+    int32_t expert[SZ_MAXG];
+    int32_t count[SZ_MAXG];
+    int32_t rows[SZ_MAXG][SZ_MAX_VERIFY];   // row j of x
+    int32_t pairs[SZ_MAXG][SZ_MAX_VERIFY];  // j * top_k + rank: row of the per-pair buffers
+};
+
+// Offsets (bytes) into the caller's scratch buffer.
+struct SzMoeScratch {
+    int64_t ctrl;      // u32[16]: [0] router ticket, [1] error flag
+    int64_t logits;    // f32 [m][n_expert + 1] (column n_expert: the shared expert's gate logit)
+    int64_t ridx;      // i32 [m][top_k]
+    int64_t rw;        // f64 [m][top_k]
+    int64_t plan;      // SzPlan: routed experts
+    int64_t plan_sh;   // SzPlan: the shared expert (one group of all m rows)
+    int64_t g, u;      // f32 [m * top_k][FF]: gate (or the SwiGLU product) and up outputs of the routed experts
+    int64_t sg, su;    // f32 [m][SF]: the same for the shared expert
+    int64_t eo;        // f32 [m * top_k][H]: down outputs per pair
+    int64_t so;        // f32 [m][H]: the shared expert's output
+    int64_t total;
+};
+
+static inline int64_t sz_up256(int64_t v) { return (v + 255) & ~(int64_t)255; }
+
+static inline SzMoeScratch sz_moe_layout(const sz_moe_layer* L, int m) {
+    SzMoeScratch s;
+    int64_t o = 0;
+    const int64_t pairs = (int64_t)m * L->top_k;
+    s.ctrl = o; o += 256;
+    s.logits = o; o = sz_up256(o + 4 * (int64_t)m * (L->n_expert + 1));
+    s.ridx = o; o = sz_up256(o + 4 * pairs);
+    s.rw = o; o = sz_up256(o + 8 * pairs);
+    s.plan = o; o = sz_up256(o + (int64_t)sizeof(SzPlan));
+    s.plan_sh = o; o = sz_up256(o + (int64_t)sizeof(SzPlan));
+    s.g = o; o = sz_up256(o + 4 * pairs * L->expert_ff);
+    s.u = o; o = sz_up256(o + 4 * pairs * L->expert_ff);
+    s.sg = o; o = sz_up256(o + 4 * (int64_t)m * L->shared_ff);
+    s.su = o; o = sz_up256(o + 4 * (int64_t)m * L->shared_ff);
+    s.eo = o; o = sz_up256(o + 4 * pairs * L->hidden);
+    s.so = o; o = sz_up256(o + 4 * (int64_t)m * L->hidden);
+    s.total = o;
+    return s;
+}

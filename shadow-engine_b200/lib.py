@@ -1,0 +1,73 @@
+"""ctypes binding of libshadowzero_b200.so: one declaration per entry point of include/shadowzero_b200.h."""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libshadowzero_b200.so")
+
+OK, E_ARG, E_TYPE, E_CUDA, E_SCRATCH, E_DEVICE = 0, 1, 2, 3, 4, 5
+TYPE_F32, TYPE_F16, TYPE_Q8_0, TYPE_IQ3_S, TYPE_BF16 = 0, 1, 8, 21, 30
+MAX_VERIFY, MAX_TOPK = 8, 16
+
+
+def TYPE_EXL3(k):
+    return 1020 + k
+
+
+class SzError(RuntimeError):
+    def __init__(self, code, text):
+        super().__init__("shadowzero_b200 error %d: %s" % (code, text))
+        self.code = code
+
+
+class MoeLayerC(C.Structure):
+    """struct sz_moe_layer"""
+    _fields_ = [("hidden", C.c_int32), ("n_expert", C.c_int32), ("top_k", C.c_int32), ("expert_ff", C.c_int32),
+                ("shared_ff", C.c_int32), ("expert_type", C.c_int32), ("shared_type", C.c_int32), ("reserved", C.c_int32),
+                ("router", C.c_uint64), ("shared_router", C.c_uint64),
+                ("gate", C.c_uint64), ("up", C.c_uint64), ("down", C.c_uint64),
+                ("gate_stride", C.c_uint64), ("up_stride", C.c_uint64), ("down_stride", C.c_uint64),
+                ("sh_gate", C.c_uint64), ("sh_up", C.c_uint64), ("sh_down", C.c_uint64)]
+
+
+# name -> (restype, argtypes); every symbol include/shadowzero_b200.h declares
+SYMBOLS = {
+    "sz_version": (C.c_char_p, []),
+    "sz_last_error": (C.c_char_p, []),
+    "sz_dequant": (C.c_int, [C.c_int, C.c_uint64, C.c_int64, C.c_uint64, C.c_int64, C.c_uint64]),
+    "sz_exl3_codebook": (C.c_int, [C.c_uint64, C.c_uint64]),
+    "sz_exl3_reconstruct_inner": (C.c_int, [C.c_int, C.c_uint64, C.c_int64, C.c_int64, C.c_uint64, C.c_uint64]),
+    "sz_moe_scratch_bytes": (C.c_int, [C.POINTER(MoeLayerC), C.c_int, C.POINTER(C.c_int64)]),
+    "sz_moe_scratch_init": (C.c_int, [C.c_uint64, C.c_int64, C.c_uint64]),
+    "sz_moe_verify": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64,
+                                C.c_int64, C.c_uint64]),
+    "sz_moe_verify_host": (C.c_int, [C.POINTER(MoeLayerC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                     C.c_uint64, C.c_uint64, C.c_uint64, C.c_int64, C.c_uint64]),
+    "sz_moe_launches": (C.c_int, [C.POINTER(MoeLayerC)]),
+}
+
+_lib = None
+
+
+def load():
+    """Loads the library; raises if it has not been built (no fallback of any kind)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("%s is missing: run `python -c 'import __graft_entry__ as g; g.build()'`" % LIB_PATH)
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            fn = getattr(L, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(rc):
+    if rc != OK:
+        raise SzError(rc, load().sz_last_error().decode("utf-8", "replace"))
+
+
+def version():
+    return load().sz_version().decode()
