@@ -42,6 +42,16 @@ extern "C" {
 const char* sz_version(void);
 const char* sz_last_error(void);
 
+/* ---- per-kernel timing ------------------------------------------------------------------------------------------
+ * The role of the reference's SHADOWZERO_KTIME switch (crates/shadowzero-cuda/src/kernels.rs:527-536,604).  Between
+ * sz_trace_begin and sz_trace_end every kernel this thread launches through the library is followed by a record of the next
+ * event of `events` (cudaEvent_t handles created by the caller, timing enabled) on the kernel's stream; events[0] is recorded
+ * by sz_trace_begin itself on `stream`.  sz_trace_end returns how many events were recorded; sz_trace_name(i) names the kernel
+ * that ended at events[i].  Events between kernels serialise them, so trace for attribution and time the untraced call. */
+int sz_trace_begin(uint64_t* events, int capacity, uint64_t stream);
+int sz_trace_end(void);
+const char* sz_trace_name(int i);
+
 /* ---- test kernels: the format decoders on their own --------------------------------------------------------------
  * Replace kernels/dequant.cu (dequant_*), kernels/convert.cu and the `exl3_codebook` entry of kernels/exl3.cu, which the
  * reference's GPU tests compare bit for bit with its Rust decoders (crates/shadowzero-cuda/tests/dequant.rs:40-70,

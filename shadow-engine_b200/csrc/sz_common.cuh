@@ -25,11 +25,14 @@ int sz_fail(int code, const char* fmt, ...);
 
 static inline bool sz_aligned16(u64 p) { return (p & 15) == 0; }
 
+// Per-kernel timing (sz_trace_begin): records the next caller-provided event on `stream` under `name`.  No-op when tracing is off.
+void sz_trace_mark(const char* name, cudaStream_t stream);
+
 // Launch with the programmatic-dependent-launch attribute: the kernel may start while its predecessor on the stream drains;
 // every such kernel calls sz_pdl_wait() before it touches anything the predecessor wrote.
 template <typename... KArgs, typename... Args>
-static inline cudaError_t sz_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool pdl,
-                                    Args... args) {
+static inline cudaError_t sz_launch(const char* name, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    bool pdl, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -40,7 +43,9 @@ static inline cudaError_t sz_launch(void (*kernel)(KArgs...), dim3 grid, dim3 bl
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    const cudaError_t rc = cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+    sz_trace_mark(name, stream);
+    return rc;
 }
 
 // ---- device side --------------------------------------------------------------------------------------------------------

@@ -20,7 +20,7 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
     __shared__ int cnt[SZ_MAX_EXPERTS];
     __shared__ int slot_of[SZ_MAX_EXPERTS];
     __shared__ int sel[SZ_MAX_VERIFY * SZ_MAX_TOPK];
-    __shared__ int s_last, s_groups;
+    __shared__ int s_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ld = ne + 1;
     sz_pdl_wait();
@@ -131,7 +131,7 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
             }
             running += __popc(mask);
         }
-        if (lane == 0) { s_groups = running; plan->n_groups = running; }
+        if (lane == 0) plan->n_groups = running;
     }
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
@@ -418,7 +418,6 @@ sz_combine_kernel(const float* __restrict__ eo, const double* __restrict__ rw, c
 // host side
 
 static bool sz_is_exl3(int t) { return t > 1020 && t <= 1028; }
-static bool sz_is_block(int t) { return t == SZ_TYPE_Q8_0 || t == SZ_TYPE_IQ3_S; }
 
 static int sz_check_matrix(const char* what, int type, int n_in, int n_out) {
     if (sz_is_exl3(type)) {
@@ -496,12 +495,12 @@ static int sz_launch_rows(cudaStream_t st, const SzPlan* plan, int groups, const
         static bool set = false;
         if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_rows_kernel<TYPE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
         dim3 grid((FF + SZ_ROWS_PER_CTA - 1) / SZ_ROWS_PER_CTA, groups);
-        SZ_CUDA(sz_launch(sz_rows_kernel<TYPE, false>, grid, dim3(256), smem, st, true, plan, gate, gs, up, us, x, H, FF, act));
+        SZ_CUDA(sz_launch("gateup_rows", sz_rows_kernel<TYPE, false>, grid, dim3(256), smem, st, true, plan, gate, gs, up, us, x, H, FF, act));
     } else {
         static bool set = false;
         if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_rows_kernel<TYPE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
         dim3 grid((H + SZ_ROWS_PER_CTA - 1) / SZ_ROWS_PER_CTA, groups);
-        SZ_CUDA(sz_launch(sz_rows_kernel<TYPE, true>, grid, dim3(256), smem, st, true, plan, down, ds, (const u8*)nullptr, (u64)0, act, FF, H, eo));
+        SZ_CUDA(sz_launch("down_rows", sz_rows_kernel<TYPE, true>, grid, dim3(256), smem, st, true, plan, down, ds, (const u8*)nullptr, (u64)0, act, FF, H, eo));
     }
     return SZ_OK;
 }
@@ -513,7 +512,7 @@ static int sz_launch_exl3(cudaStream_t st, const SzPlan* plan, int groups, const
     if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_exl3_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
     const size_t smem = 4096 + (size_t)SZ_MAX_VERIFY * n_in * 4;
     dim3 grid((n_out / 128) * (w1 ? 2 : 1), groups);
-    SZ_CUDA(sz_launch(sz_exl3_kernel<K>, grid, dim3(256), smem, st, true, plan, w0, s0, w1, s1, in0, in1, by_pair, n_in, n_out, out0, out1));
+    SZ_CUDA(sz_launch(w1 ? "gateup_exl3" : "down_exl3", sz_exl3_kernel<K>, grid, dim3(256), smem, st, true, plan, w0, s0, w1, s1, in0, in1, by_pair, n_in, n_out, out0, out1));
     return SZ_OK;
 }
 
@@ -558,7 +557,7 @@ extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t 
     const bool shared = SF > 0;
 
     const int route_rows = L->n_expert + (shared ? 1 : 0);
-    SZ_CUDA(sz_launch(sz_route_kernel, dim3((route_rows + SZ_ROUTE_WARPS - 1) / SZ_ROUTE_WARPS), dim3(SZ_ROUTE_WARPS * 32), 0, st, false, xp, m, H,
+    SZ_CUDA(sz_launch("route", sz_route_kernel, dim3((route_rows + SZ_ROUTE_WARPS - 1) / SZ_ROUTE_WARPS), dim3(SZ_ROUTE_WARPS * 32), 0, st, false, xp, m, H,
                       (const float*)L->router, (const float*)(shared ? L->shared_router : 0), (int)L->n_expert, (int)L->top_k, logits, ridx,
                       rw, plan, plan_sh, ctrl, (int32_t*)route_idx, (double*)route_w));
     const int groups = m * L->top_k;
@@ -570,7 +569,7 @@ extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t 
                      eo, true)))
         return rc;
     if (shared && (rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true))) return rc;
-    SZ_CUDA(sz_launch(sz_combine_kernel, dim3((H + 255) / 256, m), dim3(256), 0, st, true, (const float*)eo, (const double*)rw, (const float*)so,
+    SZ_CUDA(sz_launch("combine", sz_combine_kernel, dim3((H + 255) / 256, m), dim3(256), 0, st, true, (const float*)eo, (const double*)rw, (const float*)so,
                       (const float*)logits, (int)L->n_expert, (int)L->top_k, H, shared ? 1 : 0, (float*)y));
     return SZ_OK;
 }

@@ -34,6 +34,9 @@ class MoeLayerC(C.Structure):
 SYMBOLS = {
     "sz_version": (C.c_char_p, []),
     "sz_last_error": (C.c_char_p, []),
+    "sz_trace_begin": (C.c_int, [C.POINTER(C.c_uint64), C.c_int, C.c_uint64]),
+    "sz_trace_end": (C.c_int, []),
+    "sz_trace_name": (C.c_char_p, [C.c_int]),
     "sz_dequant": (C.c_int, [C.c_int, C.c_uint64, C.c_int64, C.c_uint64, C.c_int64, C.c_uint64]),
     "sz_exl3_codebook": (C.c_int, [C.c_uint64, C.c_uint64]),
     "sz_exl3_reconstruct_inner": (C.c_int, [C.c_int, C.c_uint64, C.c_int64, C.c_int64, C.c_uint64, C.c_uint64]),

@@ -58,7 +58,7 @@ def quantize_q8_0(w):
     return out.reshape(*shp[:-1], shp[-1] // 32 * 34)
 
 
-def quantize_iq3_s(w, chunk=1 << 16):
+def quantize_iq3_s(w, chunk=1 << 14):
     """w: float32 [..., cols] (cols % 256 == 0) -> uint8 [..., cols / 256 * 110].  Nearest-codebook encoder."""
     dev = w.device
     shp = w.shape
