@@ -2,8 +2,10 @@
 // Arithmetic follows Session::moe of the CPU reference (crates/shadowzero-model/src/forward.rs:1009-1034): router logits and
 // the softmax in f64, expert dot products accumulated in f32, the weighted sum over experts in f64 in rank order.
 #include "sz_moe.cuh"
+#include "sz_moe_exl3.cuh"
 
 #include <float.h>
+#include <stdlib.h>
 
 // ---------------------------------------------------------------------------------------------------------------------------------
 // router: logits (a warp a router row, f64 accumulate), then the last block to finish does softmax, top-k and the plan
@@ -15,7 +17,8 @@ __device__ __forceinline__ bool sz_better(float ad, int ai, float bd, int bi) { 
 __global__ void __launch_bounds__(SZ_ROUTE_WARPS * 32)
 sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restrict__ router, const float* __restrict__ shared_router,
                 int ne, int k, float* __restrict__ logits, int32_t* __restrict__ ridx, double* __restrict__ rw, SzPlan* __restrict__ plan,
-                SzPlan* __restrict__ plan_sh, u32* __restrict__ ctrl, int32_t* __restrict__ out_idx, double* __restrict__ out_w) {
+                SzPlan* __restrict__ plan_sh, u32* __restrict__ ctrl, int32_t* __restrict__ out_idx, double* __restrict__ out_w,
+                uint4* __restrict__ zero, int zero_n) {
     __shared__ float dl[SZ_ROUTE_WARPS][SZ_MAX_EXPERTS];
     __shared__ int cnt[SZ_MAX_EXPERTS];
     __shared__ int slot_of[SZ_MAX_EXPERTS];
@@ -25,6 +28,8 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
     const int ld = ne + 1;
     sz_pdl_wait();
     sz_pdl_trigger();
+    // the streaming kernels' fixed-point accumulators start every call at zero
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_n; i += gridDim.x * blockDim.x) zero[i] = make_uint4(0, 0, 0, 0);
 
     // ---- logits: row r of the router (row ne: the shared expert's gate) against every x row
     const int r = blockIdx.x * SZ_ROUTE_WARPS + warp;
@@ -244,7 +249,7 @@ template <int TYPE, bool DOWN>
 __global__ void __launch_bounds__(256)
 sz_rows_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 stride0, const u8* __restrict__ w1, u64 stride1,
                const float* __restrict__ in, int n_in, int n_out, float* __restrict__ out) {
-    extern __shared__ __align__(16) u8 smem[];
+    extern __shared__ __align__(128) u8 smem[];
     u32* grid = (u32*)smem;                // 512 words
     float* xs = (float*)(smem + 2048);     // [n][n_in]
     sz_pdl_wait();
@@ -347,7 +352,7 @@ __global__ void __launch_bounds__(256)
 sz_exl3_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 stride0, const u8* __restrict__ w1, u64 stride1,
                const float* __restrict__ in0, const float* __restrict__ in1, int in_by_pair, int n_in, int n_out,
                float* __restrict__ out0, float* __restrict__ out1) {
-    extern __shared__ __align__(16) u8 smem[];
+    extern __shared__ __align__(128) u8 smem[];
     float* so = (float*)smem;              // [8][128]
     float* xr = (float*)(smem + 4096);     // [n][n_in]
     sz_pdl_wait();
@@ -419,6 +424,24 @@ sz_combine_kernel(const float* __restrict__ eo, const double* __restrict__ rw, c
 
 static bool sz_is_exl3(int t) { return t > 1020 && t <= 1028; }
 
+// Which kernels a layer takes.  The streaming EXL3 kernels cover K = 2..4, expert widths 128 / 256 / 512 and hidden sizes that are
+// multiples of 512; everything else runs on the generic kernels above.
+struct SzFast { bool exl3; bool shared_fused; };
+
+static SzFast sz_fast_path(const sz_moe_layer* L) {
+    SzFast f = {false, false};
+    static const bool off = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;  // A/B switch: 1 = generic kernels only
+    if (off) return f;
+    const int K = L->expert_type - 1020;
+    const int FF = L->expert_ff;
+    if (sz_is_exl3(L->expert_type) && K >= 2 && K <= 4 && (FF == 128 || FF == 256 || FF == 512) && L->hidden % 512 == 0) {
+        f.exl3 = true;
+        f.shared_fused = L->shared_ff == FF && L->shared_type == L->expert_type;
+    }
+    return f;
+}
+
+
 static int sz_check_matrix(const char* what, int type, int n_in, int n_out) {
     if (sz_is_exl3(type)) {
         if (n_in % 128 || n_out % 128) return sz_fail(SZ_E_ARG, "%s: EXL3 needs whole 128-blocks, got %d -> %d", what, n_in, n_out);
@@ -484,6 +507,8 @@ extern "C" int sz_moe_scratch_init(uint64_t scratch, int64_t scratch_bytes, uint
 
 extern "C" int sz_moe_launches(const sz_moe_layer* L) {
     if (!L) return 0;
+    const SzFast f = sz_fast_path(L);
+    if (f.exl3) return 4 + (L->shared_ff > 0 && !f.shared_fused ? 2 : 0);
     return L->shared_ff > 0 ? 6 : 4;
 }
 
@@ -533,6 +558,44 @@ static int sz_ffn(cudaStream_t st, int type, const SzPlan* plan, int groups, u64
     return sz_fail(SZ_E_TYPE, "no kernel for tensor type %d", type);
 }
 
+static int sz_sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <int K, int NTC>
+static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const SzPlan* plan, const float* x, long long* acc_gu, long long* acc_d,
+                          u32* ctrl, bool sh) {
+    static bool set = false;
+    if (!set) {
+        SZ_CUDA(cudaFuncSetAttribute(sz_x3_gateup_kernel<K, NTC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzX3<K, NTC>::SMEM_BYTES));
+        SZ_CUDA(cudaFuncSetAttribute(sz_x3_down_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzX3<K, 4>::SMEM_BYTES));
+        set = true;
+    }
+    const dim3 grid(2 * sz_sm_count()), block(SZ_X3_THREADS);
+    SZ_CUDA(sz_launch("gateup_exl3s", sz_x3_gateup_kernel<K, NTC>, grid, block, SzX3<K, NTC>::SMEM_BYTES, st, true, plan, (const u8*)L->gate,
+                      (u64)L->gate_stride, (const u8*)L->up, (u64)L->up_stride, (const u8*)(sh ? L->sh_gate : 0), (const u8*)(sh ? L->sh_up : 0), x, m,
+                      (int)L->hidden, (int)L->top_k, acc_gu, ctrl));
+    SZ_CUDA(sz_launch("down_exl3s", sz_x3_down_kernel<K>, grid, block, SzX3<K, 4>::SMEM_BYTES, st, true, plan, (const u8*)L->gate, (u64)L->gate_stride,
+                      (const u8*)L->up, (u64)L->up_stride, (const u8*)L->down, (u64)L->down_stride, (const u8*)(sh ? L->sh_gate : 0),
+                      (const u8*)(sh ? L->sh_up : 0), (const u8*)(sh ? L->sh_down : 0), m, (int)L->hidden, (int)L->expert_ff, (int)L->top_k,
+                      (const long long*)acc_gu, acc_d, ctrl));
+    return SZ_OK;
+}
+
+static int sz_x3_launch(cudaStream_t st, const sz_moe_layer* L, int m, const SzPlan* plan, const float* x, long long* acc_gu, long long* acc_d,
+                        u32* ctrl, bool sh) {
+    const int K = L->expert_type - 1020, NTC = L->expert_ff / 128;
+#define SZ_X3_CASE(KK, NN) if (K == KK && NTC == NN) return sz_x3_launch_k<KK, NN>(st, L, m, plan, x, acc_gu, acc_d, ctrl, sh);
+    SZ_X3_CASE(2, 1) SZ_X3_CASE(2, 2) SZ_X3_CASE(2, 4) SZ_X3_CASE(3, 1) SZ_X3_CASE(3, 2) SZ_X3_CASE(3, 4) SZ_X3_CASE(4, 1) SZ_X3_CASE(4, 2) SZ_X3_CASE(4, 4)
+#undef SZ_X3_CASE
+    return sz_fail(SZ_E_TYPE, "no streaming EXL3 kernel for K = %d, FF = %d", K, L->expert_ff);
+}
+
 extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t y, uint64_t route_idx, uint64_t route_w,
                              uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
     int rc = sz_moe_check(L, m);
@@ -557,10 +620,27 @@ extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t 
     const bool shared = SF > 0;
 
     const int route_rows = L->n_expert + (shared ? 1 : 0);
+    const SzFast fast = sz_fast_path(L);
     SZ_CUDA(sz_launch("route", sz_route_kernel, dim3((route_rows + SZ_ROUTE_WARPS - 1) / SZ_ROUTE_WARPS), dim3(SZ_ROUTE_WARPS * 32), 0, st, false, xp, m, H,
                       (const float*)L->router, (const float*)(shared ? L->shared_router : 0), (int)L->n_expert, (int)L->top_k, logits, ridx,
-                      rw, plan, plan_sh, ctrl, (int32_t*)route_idx, (double*)route_w));
+                      rw, plan, plan_sh, ctrl, (int32_t*)route_idx, (double*)route_w, (uint4*)(base + S.acc_gu),
+                      fast.exl3 ? (int)(S.acc_bytes / 16) : 0));
     const int groups = m * L->top_k;
+    if (fast.exl3) {
+        // streaming EXL3 kernels for the routed experts (and the shared expert when it has the same type and width)
+        long long *acc_gu = (long long*)(base + S.acc_gu), *acc_d = (long long*)(base + S.acc_d);
+        const bool sh_fused = fast.shared_fused;
+        if (shared && !sh_fused) {
+            if ((rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, false))) return rc;
+            if ((rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true))) return rc;
+        }
+        if ((rc = sz_x3_launch(st, L, m, plan, xp, acc_gu, acc_d, ctrl, sh_fused))) return rc;
+        SZ_CUDA(sz_launch("combine_exl3", sz_x3_combine_kernel, dim3((m * (H / 128) + 3) / 4), dim3(128), 0, st, true, (const long long*)acc_d,
+                          (const int32_t*)ridx, (const double*)rw, (const u8*)L->down, (u64)L->down_stride,
+                          (const u8*)(sh_fused ? L->sh_down : 0), (const float*)(shared && !sh_fused ? so : nullptr), (const float*)logits,
+                          (int)L->n_expert, (int)L->top_k, m, H, FF, shared ? 1 : 0, (float*)y));
+        return SZ_OK;
+    }
     if ((rc = sz_ffn(st, L->expert_type, plan, groups, L->gate, L->gate_stride, L->up, L->up_stride, L->down, L->down_stride, xp, H, FF, g, u,
                      eo, false)))
         return rc;

@@ -30,6 +30,9 @@ struct SzMoeScratch {
     int64_t sg, su;    // f32 [m][SF]: the same for the shared expert
     int64_t eo;        // f32 [m * top_k][H]: down outputs per pair
     int64_t so;        // f32 [m][H]: the shared expert's output
+    int64_t acc_gu;    // i64 [m * top_k + m][2][FF]: fixed-point gate / up sums of the streaming kernels (pairs, then shared rows)
+    int64_t acc_d;     // i64 [m * top_k + m][H]: fixed-point down sums
+    int64_t acc_bytes; // acc_gu and acc_d are contiguous: this many bytes are zeroed at the start of a call
     int64_t total;
 };
 
@@ -51,6 +54,10 @@ static inline SzMoeScratch sz_moe_layout(const sz_moe_layer* L, int m) {
     s.su = o; o = sz_up256(o + 4 * (int64_t)m * L->shared_ff);
     s.eo = o; o = sz_up256(o + 4 * pairs * L->hidden);
     s.so = o; o = sz_up256(o + 4 * (int64_t)m * L->hidden);
+    const int64_t ffm = L->expert_ff > L->shared_ff ? L->expert_ff : L->shared_ff;
+    s.acc_gu = o; o = sz_up256(o + 8 * (pairs + m) * 2 * ffm);
+    s.acc_d = o; o = sz_up256(o + 8 * (pairs + m) * L->hidden);
+    s.acc_bytes = o - s.acc_gu;
     s.total = o;
     return s;
 }

@@ -1,0 +1,406 @@
+// EXL3 expert FFN for a verify pass, streaming form.
+//
+// Work is cut into units of one 128-input block (8 tile rows) by 8 * NTC tile columns of one matrix: 8 * (8 NTC) tiles, 24 KB at
+// K = 3, NTC = 4.  A block of 8 warps walks a contiguous range of units; the TMA engine (cp.async.bulk) keeps the next units'
+// trellis bytes arriving in a ring of shared-memory stages while the warps decode the current one.  Each lane decodes the 8
+// weights of a tile that the format assigns it (crates/shadowzero-model/src/exl3.rs:9-14) straight into the A fragment of
+// mma.sync.m16n8k16 - a tile IS one 16 (outputs) x 16 (inputs) A fragment - and the rows of the pass are the B operand, split into
+// an f16 high and low part (two MMAs into one f32 accumulator) so the activations keep f32 accuracy.  The multiply-adds thus cost
+// no issue slots; what is left on the ALUs is the trellis decode itself.
+//
+// A unit only covers part of the input, so its results are partial sums.  They are added into 64-bit fixed-point accumulators
+// (scale 2^34) with integer atomics: integer addition is associative, so the sum does not depend on which block finishes first and
+// the result is bit-for-bit reproducible, which float atomics would not give.
+#pragma once
+
+#include "sz_moe.cuh"
+
+#define SZ_X3_THREADS 256
+#define SZ_X3_STAGES 4
+#define SZ_FIX_SCALE 17179869184.0f           // 2^34
+#define SZ_FIX_INV (1.0 / 17179869184.0)
+
+template <int K, int NTC>
+struct SzX3 {
+    static constexpr int TILE_BYTES = 32 * K;
+    static constexpr int ROW_BYTES = 8 * NTC * TILE_BYTES;  // one tile row of the unit
+    static constexpr int STAGE_BYTES = 8 * ROW_BYTES;
+    static constexpr int FRAG_BYTES = 2 * 8 * 32 * 16;
+    static constexpr int SMEM_BYTES = SZ_X3_STAGES * STAGE_BYTES + FRAG_BYTES + SZ_X3_STAGES * 8 + 16;
+};
+
+__device__ __forceinline__ void sz_mma16816(float* c, const u32* a, u32 b0, u32 b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// The lane's 8 weights of a tile as the A fragment (outputs x inputs) of m16n8k16: a0 = (out g, in 2q..), a1 = (out g + 8, in 2q..),
+// a2 = (out g, in 2q + 8..), a3 = (out g + 8, in 2q + 8..) with g = lane / 4, q = lane % 4: tile positions j = {0,1}, {4,5}, {2,3}, {6,7}.
+template <int K>
+__device__ __forceinline__ void sz_exl3_afrag(const u32* tile, int lane, u32* a) {
+    u32 st[8];
+    SzExl3Tile<K>::states(tile, lane, st);
+    const __half2 kinv = __halves2half2(__ushort_as_half((u16)0x1eee), __ushort_as_half((u16)0x1eee));
+    const __half2 kbias = __halves2half2(__ushort_as_half((u16)0xc931), __ushort_as_half((u16)0xc931));
+    u32 p[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const u32 s0 = __dp4a(st[2 * i] * 0x83DCD12Du, 0x01010101u, 0x6400u);
+        const u32 s1 = __dp4a(st[2 * i + 1] * 0x83DCD12Du, 0x01010101u, 0x6400u);
+        const u32 packed = (s1 << 16) | s0;
+        const __half2 h = __hfma2(*(const __half2*)&packed, kinv, kbias);
+        p[i] = *(const u32*)&h;
+    }
+    a[0] = p[0]; a[1] = p[2]; a[2] = p[1]; a[3] = p[3];
+}
+
+// One unit's description.
+struct SzX3Unit {
+    const u8* src;        // first byte of the unit's first tile row
+    u64 row_stride;       // bytes between the unit's tile rows in global memory
+    const u16* suh;       // the 128 input signs/scales of the unit's input block
+    int n;                // rows in the group
+    const int32_t* rows;  // null: rows are 0..n-1 (the shared expert)
+    const int32_t* pairs; // null: pair = pair0 + t
+    int pair0;
+    int in_off;           // first input index of the block
+};
+
+// Writes the B fragments (the group's rows, rotated into the trellis' basis, f16 high and low parts) of one 128-input block.
+// v[e]: warp t's row t, element lane + 32 e, already multiplied by suh.  frag: [8 tile rows][32 lanes] of {hi b0, hi b1, lo b0, lo b1}.
+__device__ __forceinline__ void sz_x3_store_frag(uint4* frag, int t, int n, float* v, int lane) {
+    if (t < n) {
+        sz_wht128_warp(v, lane);
+        const int kk = lane & 15;
+        const int q = (kk & 7) >> 1, reg = kk >> 3, half = kk & 1;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            const float val = v[e] * SZ_RSQRT128;
+            const __half hi = __float2half_rn(val);
+            const __half lo = __float2half_rn(val - __half2float(hi));
+            const int kr = 2 * e + (lane >> 4);
+            u16* dst = (u16*)(frag + kr * 32 + 4 * t + q);
+            dst[reg * 2 + half] = __half_as_ushort(hi);
+            dst[4 + reg * 2 + half] = __half_as_ushort(lo);
+        }
+    } else {
+        frag[(lane >> 2) * 32 + 4 * t + (lane & 3)] = make_uint4(0, 0, 0, 0);
+    }
+}
+
+// Decodes and multiplies one staged unit: c[tc] accumulates outputs (warp * NTC + tc) * 16 + {g, g + 8} for rows 2q, 2q + 1.
+template <int K, int NTC>
+__device__ __forceinline__ void sz_x3_compute(const u8* stage, const uint4* frag, int warp, int lane, float (*c)[4]) {
+#pragma unroll
+    for (int tc = 0; tc < NTC; tc++) { c[tc][0] = 0.f; c[tc][1] = 0.f; c[tc][2] = 0.f; c[tc][3] = 0.f; }
+#pragma unroll 2
+    for (int kr = 0; kr < 8; kr++) {
+        const uint4 b = frag[kr * 32 + lane];
+#pragma unroll
+        for (int tc = 0; tc < NTC; tc++) {
+            const u32* tile = (const u32*)(stage + (size_t)(kr * 8 * NTC + warp * NTC + tc) * (32 * K));
+            u32 a[4];
+            sz_exl3_afrag<K>(tile, lane, a);
+            sz_mma16816(c[tc], a, b.x, b.y);
+            sz_mma16816(c[tc], a, b.z, b.w);
+        }
+    }
+}
+
+__device__ __forceinline__ void sz_fix_add(long long* dst, float v) {
+    atomicAdd((unsigned long long*)dst, (unsigned long long)__float2ll_rn(v * SZ_FIX_SCALE));
+}
+
+// ---- gate / up --------------------------------------------------------------------------------------------------------------------
+// Units: group x input block x {gate, up}; a unit is contiguous in memory (every tile column of 8 tile rows).
+// acc: i64 [pairs][2][FF]: pre-rotation sums of gate (0) and up (1) for every pair, zero on entry.
+template <int K, int NTC>
+__global__ void __launch_bounds__(SZ_X3_THREADS, 2)
+sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, u64 gstride, const u8* __restrict__ up, u64 ustride,
+                    const u8* __restrict__ sh_gate, const u8* __restrict__ sh_up, const float* __restrict__ x, int m, int H, int top_k,
+                    long long* __restrict__ acc, u32* __restrict__ ctrl) {
+    using X = SzX3<K, NTC>;
+    constexpr int FF = 128 * NTC;
+    extern __shared__ __align__(128) u8 smem[];
+    u8* stages = smem;
+    uint4* frags = (uint4*)(smem + SZ_X3_STAGES * X::STAGE_BYTES);
+    u64* bars = (u64*)(smem + SZ_X3_STAGES * X::STAGE_BYTES + X::FRAG_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < SZ_X3_STAGES; i++) sz_mbar_init(&bars[i], 1);
+        sz_mbar_fence_init();
+    }
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    __syncthreads();
+    const int D = plan ? plan->n_groups : 0;
+    const int NG = D + (sh_gate ? 1 : 0);
+    const int NS = H / 128;
+    const long long U = (long long)NG * NS * 2;
+    const int u0 = (int)(U * blockIdx.x / gridDim.x), u1 = (int)(U * (blockIdx.x + 1) / gridDim.x);
+    const int count = u1 - u0;
+    if (count <= 0) return;
+    const size_t hdr = 2 * (size_t)H + 2 * (size_t)FF + 4;
+
+    auto unit = [&](int u) {
+        SzX3Unit d;
+        const int g = u / (2 * NS), rem = u % (2 * NS), s = rem >> 1, mat = rem & 1;
+        const u8* blob;
+        if (g < D) {
+            const u64 e = (u64)plan->expert[g];
+            blob = mat ? up + e * ustride : gate + e * gstride;
+            d.n = plan->count[g]; d.rows = plan->rows[g]; d.pairs = plan->pairs[g]; d.pair0 = 0;
+        } else {
+            blob = mat ? sh_up : sh_gate;
+            d.n = m; d.rows = nullptr; d.pairs = nullptr; d.pair0 = m * top_k;
+        }
+        d.src = blob + hdr + (size_t)s * X::STAGE_BYTES;
+        d.row_stride = X::ROW_BYTES;
+        d.suh = (const u16*)blob + s * 128;
+        d.in_off = s * 128 + (mat << 30);  // bit 30 carries the matrix index
+        return d;
+    };
+    auto issue = [&](int i) {  // thread 0: start unit i's copy into stage i % STAGES
+        const SzX3Unit d = unit(u0 + i);
+        u64* bar = &bars[i % SZ_X3_STAGES];
+        sz_mbar_expect_tx(bar, X::STAGE_BYTES);
+        sz_bulk_g2s(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, d.src, X::STAGE_BYTES, bar);
+    };
+    auto prep_load = [&](const SzX3Unit& d, float* v) {  // warp t: row t of the group times suh, element lane + 32 e
+        if (warp < d.n) {
+            const int row = d.rows ? d.rows[warp] : warp;
+            const int off = d.in_off & 0x3fffffff;
+#pragma unroll
+            for (int e = 0; e < 4; e++)
+                v[e] = __ldg(x + (size_t)row * H + off + lane + 32 * e) * sz_f16_to_f32(__ldg(d.suh + lane + 32 * e));
+        }
+    };
+
+    if (threadIdx.x == 0)
+        for (int i = 0; i < SZ_X3_STAGES - 1 && i < count; i++) issue(i);
+    SzX3Unit cur = unit(u0);
+    {
+        float v[4];
+        prep_load(cur, v);
+        sz_x3_store_frag(frags, warp, cur.n, v, lane);
+    }
+    __syncthreads();
+    int failed = 0;
+    for (int i = 0; i < count; i++) {
+        if (threadIdx.x == 0 && i + SZ_X3_STAGES - 1 < count) issue(i + SZ_X3_STAGES - 1);
+        SzX3Unit nxt = cur;
+        float v[4];
+        if (i + 1 < count) { nxt = unit(u0 + i + 1); prep_load(nxt, v); }
+        if (!sz_mbar_wait(&bars[i % SZ_X3_STAGES], (i / SZ_X3_STAGES) & 1)) failed = 1;
+        float c[NTC][4];
+        if (!failed) {
+            sz_x3_compute<K, NTC>(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, frags + (i & 1) * 256, warp, lane, c);
+            const int mat = cur.in_off >> 30, q = lane & 3, g8 = lane >> 2;
+#pragma unroll
+            for (int tt = 0; tt < 2; tt++) {
+                const int t = 2 * q + tt;
+                if (t < cur.n) {
+                    const int pair = cur.pairs ? cur.pairs[t] : cur.pair0 + t;
+                    long long* dst = acc + ((size_t)pair * 2 + mat) * FF + (warp * NTC) * 16 + g8;
+#pragma unroll
+                    for (int tc = 0; tc < NTC; tc++) {
+                        sz_fix_add(dst + tc * 16, c[tc][tt]);
+                        sz_fix_add(dst + tc * 16 + 8, c[tc][2 + tt]);
+                    }
+                }
+            }
+        }
+        if (i + 1 < count) sz_x3_store_frag(frags + ((i + 1) & 1) * 256, warp, nxt.n, v, lane);
+        cur = nxt;
+        if (__syncthreads_or(failed)) { failed = 1; break; }
+    }
+    if (failed && threadIdx.x == 0) atomicExch(&ctrl[1], 1u);
+}
+
+// ---- down ---------------------------------------------------------------------------------------------------------------------------
+// Units: group x input block (128 of FF) x output chunk (512 outputs = 32 tile columns); 8 tile rows of 32 tiles each, strided.
+// The input of a unit is the SwiGLU product of its pairs, finished here from the gate/up accumulators: rotate back (H), scale by
+// svh, silu(g) * u, then into the down trellis' basis (suh, H).  out: i64 [pairs][H], zero on entry.
+template <int K>
+__global__ void __launch_bounds__(SZ_X3_THREADS, 2)
+sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, u64 gstride, const u8* __restrict__ up, u64 ustride,
+                  const u8* __restrict__ down, u64 dstride, const u8* __restrict__ sh_gate, const u8* __restrict__ sh_up,
+                  const u8* __restrict__ sh_down, int m, int H, int FF, int top_k, const long long* __restrict__ acc,
+                  long long* __restrict__ out, u32* __restrict__ ctrl) {
+    using X = SzX3<K, 4>;
+    extern __shared__ __align__(128) u8 smem[];
+    u8* stages = smem;
+    uint4* frags = (uint4*)(smem + SZ_X3_STAGES * X::STAGE_BYTES);
+    u64* bars = (u64*)(smem + SZ_X3_STAGES * X::STAGE_BYTES + X::FRAG_BYTES);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < SZ_X3_STAGES; i++) sz_mbar_init(&bars[i], 1);
+        sz_mbar_fence_init();
+    }
+    __syncthreads();
+    // the plan was finished two kernels ago; only the gate/up accumulators need the wait below
+    const int D = plan ? plan->n_groups : 0;
+    const int NG = D + (sh_down ? 1 : 0);
+    const int KB = FF / 128, NC = H / 512;
+    const long long U = (long long)NG * KB * NC;
+    const int u0 = (int)(U * blockIdx.x / gridDim.x), u1 = (int)(U * (blockIdx.x + 1) / gridDim.x);
+    const int count = u1 - u0;
+    const size_t hdr_d = 2 * (size_t)FF + 2 * (size_t)H + 4, hdr_g = 2 * (size_t)H + 2 * (size_t)FF + 4;
+    (void)hdr_g;
+    const u64 drow = (u64)(H / 16) * X::TILE_BYTES;  // bytes of one tile row of the down matrix
+
+    struct DUnit { const u8* src; const u16 *svg, *svu, *suh; int n; const int32_t* pairs; int pair0; int kb, c; };
+    auto unit = [&](int u) {
+        DUnit d;
+        const int g = u / (KB * NC), rem = u % (KB * NC);
+        d.kb = rem / NC; d.c = rem % NC;
+        const u8 *bg, *bu, *bd;
+        if (g < D) {
+            const u64 e = (u64)plan->expert[g];
+            bg = gate + e * gstride; bu = up + e * ustride; bd = down + e * dstride;
+            d.n = plan->count[g]; d.pairs = plan->pairs[g]; d.pair0 = 0;
+        } else {
+            bg = sh_gate; bu = sh_up; bd = sh_down;
+            d.n = m; d.pairs = nullptr; d.pair0 = m * top_k;
+        }
+        d.src = bd + hdr_d + (size_t)d.kb * 8 * drow + (size_t)d.c * X::ROW_BYTES;
+        d.svg = (const u16*)(bg + 2 * (size_t)H) + d.kb * 128;
+        d.svu = (const u16*)(bu + 2 * (size_t)H) + d.kb * 128;
+        d.suh = (const u16*)bd + d.kb * 128;
+        return d;
+    };
+    auto issue = [&](int i) {
+        const DUnit d = unit(u0 + i);
+        u64* bar = &bars[i % SZ_X3_STAGES];
+        u8* dst = stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES;
+        sz_mbar_expect_tx(bar, X::STAGE_BYTES);
+#pragma unroll
+        for (int kr = 0; kr < 8; kr++) sz_bulk_g2s(dst + kr * X::ROW_BYTES, d.src + kr * drow, X::ROW_BYTES, bar);
+    };
+    // warp t: gate and up sums of pair t (elements lane + 32 e of block kb) and the scales that finish them
+    auto prep_load = [&](const DUnit& d, long long* ag, long long* au, float* sc) {
+        if (warp < d.n) {
+            const int pair = d.pairs ? d.pairs[warp] : d.pair0 + warp;
+            const long long* a = acc + (size_t)pair * 2 * FF + d.kb * 128;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const int i = lane + 32 * e;
+                ag[e] = __ldcg(a + i);
+                au[e] = __ldcg(a + FF + i);
+                sc[e] = sz_f16_to_f32(__ldg(d.svg + i));
+                sc[4 + e] = sz_f16_to_f32(__ldg(d.svu + i));
+                sc[8 + e] = sz_f16_to_f32(__ldg(d.suh + i));
+            }
+        }
+    };
+    auto prep_store = [&](const DUnit& d, long long* ag, long long* au, float* sc, uint4* frag) {
+        float v[4];
+        if (warp < d.n) {
+            float g[4], u[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) { g[e] = (float)((double)ag[e] * SZ_FIX_INV); u[e] = (float)((double)au[e] * SZ_FIX_INV); }
+            sz_wht128_warp(g, lane);
+            sz_wht128_warp(u, lane);
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                const float gv = (g[e] * SZ_RSQRT128) * sc[e], uv = (u[e] * SZ_RSQRT128) * sc[4 + e];
+                v[e] = (sz_silu(gv) * uv) * sc[8 + e];
+            }
+        }
+        sz_x3_store_frag(frag, warp, d.n, v, lane);
+    };
+
+    if (count > 0 && threadIdx.x == 0)
+        for (int i = 0; i < SZ_X3_STAGES - 1 && i < count; i++) issue(i);
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    if (count <= 0) return;
+    DUnit cur = unit(u0);
+    {
+        long long ag[4], au[4];
+        float sc[12];
+        prep_load(cur, ag, au, sc);
+        prep_store(cur, ag, au, sc, frags);
+    }
+    __syncthreads();
+    int failed = 0;
+    for (int i = 0; i < count; i++) {
+        if (threadIdx.x == 0 && i + SZ_X3_STAGES - 1 < count) issue(i + SZ_X3_STAGES - 1);
+        DUnit nxt = cur;
+        long long ag[4], au[4];
+        float sc[12];
+        if (i + 1 < count) { nxt = unit(u0 + i + 1); prep_load(nxt, ag, au, sc); }
+        if (!sz_mbar_wait(&bars[i % SZ_X3_STAGES], (i / SZ_X3_STAGES) & 1)) failed = 1;
+        float c[4][4];
+        if (!failed) {
+            sz_x3_compute<K, 4>(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, frags + (i & 1) * 256, warp, lane, c);
+            const int q = lane & 3, g8 = lane >> 2;
+#pragma unroll
+            for (int tt = 0; tt < 2; tt++) {
+                const int t = 2 * q + tt;
+                if (t < cur.n) {
+                    const int pair = cur.pairs ? cur.pairs[t] : cur.pair0 + t;
+                    long long* dst = out + (size_t)pair * H + cur.c * 512 + (warp * 4) * 16 + g8;
+#pragma unroll
+                    for (int tc = 0; tc < 4; tc++) {
+                        sz_fix_add(dst + tc * 16, c[tc][tt]);
+                        sz_fix_add(dst + tc * 16 + 8, c[tc][2 + tt]);
+                    }
+                }
+            }
+        }
+        if (i + 1 < count) prep_store(nxt, ag, au, sc, frags + ((i + 1) & 1) * 256);
+        cur = nxt;
+        if (__syncthreads_or(failed)) { failed = 1; break; }
+    }
+    if (failed && threadIdx.x == 0) atomicExch(&ctrl[1], 1u);
+}
+
+// ---- combine ----------------------------------------------------------------------------------------------------------------------
+// y[j] = sum over ranks of w * (H eo * svh) + sigmoid(shared gate logit) * (H so * svh_shared): a warp a (row, 128-output block).
+// so_f32 != null: the shared expert's output comes finished (f32 [m][H]) from the generic kernels instead of the accumulators.
+__global__ void __launch_bounds__(128)
+sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restrict__ ridx, const double* __restrict__ rw,
+                     const u8* __restrict__ down, u64 dstride, const u8* __restrict__ sh_down, const float* __restrict__ so_f32,
+                     const float* __restrict__ logits, int ne, int top_k, int m, int H, int FF, int has_shared, float* __restrict__ y) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int item = blockIdx.x * 4 + warp;
+    const int nb = H / 128;
+    if (item >= m * nb) return;
+    const int j = item / nb, b = item % nb;
+    double a[4] = {0.0, 0.0, 0.0, 0.0};
+    for (int t = 0; t < top_k; t++) {
+        const int pair = j * top_k + t;
+        const u16* svh = (const u16*)(down + (u64)__ldcg(ridx + pair) * dstride + 2 * (size_t)FF) + b * 128;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; e++) v[e] = (float)((double)__ldcg(out + (size_t)pair * H + b * 128 + lane + 32 * e) * SZ_FIX_INV);
+        sz_wht128_warp(v, lane);
+        const double w = __ldcg(rw + pair);
+#pragma unroll
+        for (int e = 0; e < 4; e++) a[e] += w * (double)((v[e] * SZ_RSQRT128) * sz_f16_to_f32(svh[lane + 32 * e]));
+    }
+    if (has_shared) {
+        const float sg = sz_sigmoid(__ldcg(logits + (size_t)j * (ne + 1) + ne));
+        float v[4];
+        if (so_f32) {
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[e] = __ldcg(so_f32 + (size_t)j * H + b * 128 + lane + 32 * e);
+        } else {
+            const u16* svh = (const u16*)(sh_down + 2 * (size_t)FF) + b * 128;
+            const int pair = m * top_k + j;
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[e] = (float)((double)__ldcg(out + (size_t)pair * H + b * 128 + lane + 32 * e) * SZ_FIX_INV);
+            sz_wht128_warp(v, lane);
+#pragma unroll
+            for (int e = 0; e < 4; e++) v[e] = (v[e] * SZ_RSQRT128) * sz_f16_to_f32(svh[lane + 32 * e]);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; e++) a[e] += (double)(sg * v[e]);
+    }
+#pragma unroll
+    for (int e = 0; e < 4; e++) y[(size_t)j * H + b * 128 + lane + 32 * e] = (float)a[e];
+}

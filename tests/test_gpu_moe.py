@@ -52,6 +52,29 @@ def test_exl3_experts(bits, m):
     run_case(256, 32, 4, 128, 256, szlib.TYPE_EXL3(bits), szlib.TYPE_EXL3(bits), m, seed=3)
 
 
+@pytest.mark.parametrize("bits,ff,m", [(3, 512, 4), (3, 256, 1), (3, 128, 8), (2, 512, 3), (4, 512, 4), (4, 256, 5), (2, 128, 2)])
+def test_exl3_streaming_kernels(bits, ff, m):
+    # hidden a multiple of 512 and FF in {128, 256, 512} take the TMA-staged tensor-core kernels; the shared expert rides along
+    run_case(512, 32, 4, ff, ff, szlib.TYPE_EXL3(bits), szlib.TYPE_EXL3(bits), m, seed=20 + bits)
+
+
+def test_exl3_streaming_kernels_with_a_different_shared_expert():
+    run_case(1024, 32, 6, 256, 512, szlib.TYPE_EXL3(3), szlib.TYPE_EXL3(3), 4, seed=31)   # other width: generic kernels for it
+    run_case(512, 32, 6, 256, 256, szlib.TYPE_EXL3(3), szlib.TYPE_Q8_0, 4, seed=32)        # other type
+    run_case(512, 32, 6, 256, 0, szlib.TYPE_EXL3(3), szlib.TYPE_EXL3(3), 7, seed=33)       # none
+
+
+def test_exl3_streaming_kernels_all_rows_one_group():
+    L = synth.make_moe_layer(512, 16, 4, 256, 256, szlib.TYPE_EXL3(3), szlib.TYPE_EXL3(3), seed=34)
+    layer = moe.MoeLayer(L, "cuda:0")
+    x = torch.randn(1, 512, generator=torch.Generator().manual_seed(1)).repeat(8, 1).contiguous()
+    y = layer.moe_batch(x.cuda())
+    torch.cuda.synchronize()
+    want, _, _, _ = ob.moe(synth.to_numpy_layer(L), x[0].numpy())
+    assert all(torch.equal(y[0], y[j]) for j in range(8))
+    assert np.abs(y[0].cpu().numpy() - want).max() / np.abs(want).max() < REL_TOL
+
+
 def test_mixed_types_exl3_experts_q8_shared():
     run_case(256, 16, 4, 128, 256, szlib.TYPE_EXL3(3), szlib.TYPE_Q8_0, 4, seed=4)
 
@@ -94,10 +117,12 @@ def test_router_ties_go_to_the_lower_index():
         assert tied == sorted(tied)
 
 
-def test_repeated_calls_are_deterministic_and_scratch_is_reusable():
-    layer, x, y0 = run_case(512, 64, 6, 256, 256, szlib.TYPE_IQ3_S, szlib.TYPE_IQ3_S, 4, seed=9)
+@pytest.mark.parametrize("ety", [szlib.TYPE_IQ3_S, szlib.TYPE_EXL3(3)])
+def test_repeated_calls_are_deterministic_and_scratch_is_reusable(ety):
+    # bit-identical from call to call: the streaming kernels add partial sums with integer atomics, whose order does not matter
+    layer, x, y0 = run_case(512, 64, 6, 256, 256, ety, ety, 4, seed=9)
     xd = x.cuda()
-    for _ in range(3):
+    for _ in range(5):
         y = layer.moe_batch(xd)
         torch.cuda.synchronize()
         assert np.array_equal(y.cpu().numpy().view(np.uint32), y0.view(np.uint32))
