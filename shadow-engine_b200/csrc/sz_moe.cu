@@ -19,7 +19,6 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
                 int ne, int k, float* __restrict__ logits, int32_t* __restrict__ ridx, double* __restrict__ rw, SzPlan* __restrict__ plan,
                 SzPlan* __restrict__ plan_sh, u32* __restrict__ ctrl, int32_t* __restrict__ out_idx, double* __restrict__ out_w,
                 uint4* __restrict__ zero, int zero_n) {
-    __shared__ float dl[SZ_ROUTE_WARPS][SZ_MAX_EXPERTS];
     __shared__ int cnt[SZ_MAX_EXPERTS];
     __shared__ int slot_of[SZ_MAX_EXPERTS];
     __shared__ int sel[SZ_MAX_VERIFY * SZ_MAX_TOPK];
@@ -69,29 +68,29 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
     __threadfence();
 
     for (int j = warp; j < m; j += SZ_ROUTE_WARPS) {
-        float* d = dl[warp];
+        // the row's logits in registers: lane holds experts lane + 32 q
+        float d[SZ_MAX_EXPERTS / 32];
         float mx = -FLT_MAX;  // f32::MIN, forward.rs:1093
-        for (int i = lane; i < ne; i += 32) {
-            const float v = __ldcg(logits + (size_t)j * ld + i);
-            d[i] = v;
-            mx = fmaxf(mx, v);
+#pragma unroll
+        for (int q = 0; q < SZ_MAX_EXPERTS / 32; q++) {
+            const int i = lane + 32 * q;
+            d[q] = i < ne ? __ldcg(logits + (size_t)j * ld + i) : -INFINITY;
+            if (i < ne) mx = fmaxf(mx, d[q]);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-        double z = 0.0;
-        for (int i = lane; i < ne; i += 32) {
-            const float dv = d[i] - mx;  // in f32, as the reference subtracts before widening
-            d[i] = dv;
-            z += exp((double)dv);
-        }
-        z = sz_warp_sum(z);
-        // top-k by (value descending, index ascending); exp is monotone, so the order of d is the order of ex
+#pragma unroll
+        for (int q = 0; q < SZ_MAX_EXPERTS / 32; q++) d[q] = d[q] - mx;  // in f32, as the reference subtracts before widening
+        // top-k by (value descending, index ascending); exp is monotone, so the order of d is the order of exp(d)
         u32 taken = 0;
+        float mine = 0.f;  // lane t keeps the value of rank t
         for (int t = 0; t < k; t++) {
             float bd = -INFINITY;
             int bi = 0x7fffffff;
-            for (int q = 0, i = lane; i < ne; q++, i += 32) {
-                if (!((taken >> q) & 1u) && sz_better(d[i], i, bd, bi)) { bd = d[i]; bi = i; }
+#pragma unroll
+            for (int q = 0; q < SZ_MAX_EXPERTS / 32; q++) {
+                const int i = lane + 32 * q;
+                if (i < ne && !((taken >> q) & 1u) && sz_better(d[q], i, bd, bi)) { bd = d[q]; bi = i; }
             }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
@@ -100,14 +99,18 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
                 if (sz_better(od, oi, bd, bi)) { bd = od; bi = oi; }
             }
             if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+            if (lane == t) mine = bd;
             if (lane == 0) sel[j * SZ_MAX_TOPK + t] = bi;
         }
-        __syncwarp();
+        // weights: softmax over all experts, then the chosen ones renormalised - the full sum cancels, so only the k chosen
+        // exponentials are needed: w_t = exp(d_t) / sum over ranks (in rank order) of exp(d_t')
+        const double ex = lane < k ? exp((double)mine) : 0.0;
         double tz = 0.0;
-        for (int t = 0; t < k; t++) tz += exp((double)d[sel[j * SZ_MAX_TOPK + t]]) / z;
+        for (int t = 0; t < k; t++) tz += __shfl_sync(0xffffffffu, ex, t);
+        __syncwarp();
         if (lane < k) {
             const int e = sel[j * SZ_MAX_TOPK + lane];
-            const double wv = (exp((double)d[e]) / z) / tz;
+            const double wv = ex / tz;
             ridx[j * k + lane] = e;
             rw[j * k + lane] = wv;
             if (out_idx) out_idx[j * k + lane] = e;
@@ -635,7 +638,7 @@ extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t 
             if ((rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true))) return rc;
         }
         if ((rc = sz_x3_launch(st, L, m, plan, xp, acc_gu, acc_d, ctrl, sh_fused))) return rc;
-        SZ_CUDA(sz_launch("combine_exl3", sz_x3_combine_kernel, dim3((m * (H / 128) + 3) / 4), dim3(128), 0, st, true, (const long long*)acc_d,
+        SZ_CUDA(sz_launch("combine_exl3", sz_x3_combine_kernel, dim3(m * (H / 128)), dim3((L->top_k + 1) * 32), 0, st, true, (const long long*)acc_d,
                           (const int32_t*)ridx, (const double*)rw, (const u8*)L->down, (u64)L->down_stride,
                           (const u8*)(sh_fused ? L->sh_down : 0), (const float*)(shared && !sh_fused ? so : nullptr), (const float*)logits,
                           (int)L->n_expert, (int)L->top_k, m, H, FF, shared ? 1 : 0, (float*)y));

@@ -358,32 +358,29 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
 }
 
 // ---- combine ----------------------------------------------------------------------------------------------------------------------
-// y[j] = sum over ranks of w * (H eo * svh) + sigmoid(shared gate logit) * (H so * svh_shared): a warp a (row, 128-output block).
+// y[j] = sum over ranks of w * (H eo * svh) + sigmoid(shared gate logit) * (H so * svh_shared).  A block a (row, 128-output block);
+// warp t finishes rank t's contribution (warp top_k: the shared expert's), then warp 0 adds them in rank order in f64.
 // so_f32 != null: the shared expert's output comes finished (f32 [m][H]) from the generic kernels instead of the accumulators.
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__((SZ_MAX_TOPK + 1) * 32)
 sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restrict__ ridx, const double* __restrict__ rw,
                      const u8* __restrict__ down, u64 dstride, const u8* __restrict__ sh_down, const float* __restrict__ so_f32,
                      const float* __restrict__ logits, int ne, int top_k, int m, int H, int FF, int has_shared, float* __restrict__ y) {
+    __shared__ float part[SZ_MAX_TOPK + 1][128];
     sz_pdl_wait();
     sz_pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int item = blockIdx.x * 4 + warp;
     const int nb = H / 128;
-    if (item >= m * nb) return;
-    const int j = item / nb, b = item % nb;
-    double a[4] = {0.0, 0.0, 0.0, 0.0};
-    for (int t = 0; t < top_k; t++) {
-        const int pair = j * top_k + t;
+    const int j = blockIdx.x / nb, b = blockIdx.x % nb;
+    if (warp < top_k) {
+        const int pair = j * top_k + warp;
         const u16* svh = (const u16*)(down + (u64)__ldcg(ridx + pair) * dstride + 2 * (size_t)FF) + b * 128;
         float v[4];
 #pragma unroll
         for (int e = 0; e < 4; e++) v[e] = (float)((double)__ldcg(out + (size_t)pair * H + b * 128 + lane + 32 * e) * SZ_FIX_INV);
         sz_wht128_warp(v, lane);
-        const double w = __ldcg(rw + pair);
 #pragma unroll
-        for (int e = 0; e < 4; e++) a[e] += w * (double)((v[e] * SZ_RSQRT128) * sz_f16_to_f32(svh[lane + 32 * e]));
-    }
-    if (has_shared) {
+        for (int e = 0; e < 4; e++) part[warp][lane + 32 * e] = (v[e] * SZ_RSQRT128) * sz_f16_to_f32(svh[lane + 32 * e]);
+    } else if (warp == top_k && has_shared) {
         const float sg = sz_sigmoid(__ldcg(logits + (size_t)j * (ne + 1) + ne));
         float v[4];
         if (so_f32) {
@@ -399,8 +396,17 @@ sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restric
             for (int e = 0; e < 4; e++) v[e] = (v[e] * SZ_RSQRT128) * sz_f16_to_f32(svh[lane + 32 * e]);
         }
 #pragma unroll
-        for (int e = 0; e < 4; e++) a[e] += (double)(sg * v[e]);
+        for (int e = 0; e < 4; e++) part[top_k][lane + 32 * e] = sg * v[e];
     }
+    __syncthreads();
+    if (warp == 0) {
 #pragma unroll
-    for (int e = 0; e < 4; e++) y[(size_t)j * H + b * 128 + lane + 32 * e] = (float)a[e];
+        for (int e = 0; e < 4; e++) {
+            const int i = lane + 32 * e;
+            double a = 0.0;
+            for (int t = 0; t < top_k; t++) a += __ldcg(rw + j * top_k + t) * (double)part[t][i];
+            if (has_shared) a += (double)part[top_k][i];
+            y[(size_t)j * H + b * 128 + i] = (float)a;
+        }
+    }
 }
