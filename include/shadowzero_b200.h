@@ -110,6 +110,19 @@ int sz_moe_verify_host(const sz_moe_layer* layer, const float* x_host, int m, fl
 /* Number of kernel launches one sz_moe_verify call makes for this layer (for launch accounting). */
 int sz_moe_launches(const sz_moe_layer* layer);
 
+/* sz_moe_verify without a scratch argument.  (No counterpart in the reference: its session always owns a scratch buffer.)
+ * For hosts that cannot allocate device memory once they are running - an engine that gave all of it to its own arena at start-up,
+ * a plugin in a process that forbids the CUDA allocator after initialisation (a cudaMalloc would stall every stream of the GPU) -
+ * and so have no buffer to pass.  The scratch is a fixed array of sz_moe_static_scratch_max() bytes (4 MiB) that the library keeps
+ * in the memory of every GPU that loads it, until the process exits.  The call allocates nothing.
+ *   - A layer shape and row count whose sz_moe_scratch_bytes exceeds the array is refused with SZ_E_SCRATCH.
+ *   - The first call on a device looks the array up and clears its counters; make that call before any stream capture begins.
+ *   - All calls on a device share the one array, and it keeps what the last call left: two calls that can overlap on the GPU
+ *     (different streams without an ordering between them) race.  Calls on one stream, or ordered by events, are safe. */
+int sz_moe_static_scratch_max(int64_t* bytes);
+int sz_moe_verify_static(const sz_moe_layer* layer, uint64_t x, int m, uint64_t y, uint64_t route_idx, uint64_t route_w,
+                         uint64_t stream);
+
 #ifdef __cplusplus
 }
 #endif

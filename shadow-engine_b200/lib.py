@@ -47,6 +47,8 @@ SYMBOLS = {
     "sz_moe_verify_host": (C.c_int, [C.POINTER(MoeLayerC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_uint64, C.c_uint64, C.c_uint64, C.c_int64, C.c_uint64]),
     "sz_moe_launches": (C.c_int, [C.POINTER(MoeLayerC)]),
+    "sz_moe_static_scratch_max": (C.c_int, [C.POINTER(C.c_int64)]),
+    "sz_moe_verify_static": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
 }
 
 _lib = None
