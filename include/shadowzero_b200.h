@@ -110,6 +110,132 @@ int sz_moe_verify_host(const sz_moe_layer* layer, const float* x_host, int m, fl
 /* Number of kernel launches one sz_moe_verify call makes for this layer (for launch accounting). */
 int sz_moe_launches(const sz_moe_layer* layer);
 
+/* ---- the model: one description for the whole verify step ------------------------------------------------------------
+ * Shapes and tensors as Config::from_gguf and Model read them (crates/shadowzero-model/src/forward.rs:25-142, tensor names in
+ * crates/shadowzero-model/src/exl3_model.rs:223-243).  Every tensor is stored as the reference stores it: ggml [cols = in,
+ * rows = out] with whole rows contiguous, or one EXL3 blob.  `data` is a device address for the library (a host address for
+ * the CPU oracle, which reads the same structs).  The per-layer-embedding (PLE) branch and the sparse indexer are not part of
+ * this build: a model described here has neither (the indexer would only select below its budget anyway). */
+typedef struct sz_tensor {
+    int32_t type;      /* ggml type id; 0 rows = absent */
+    int32_t reserved;
+    uint64_t data;
+    int64_t rows;      /* outputs */
+    int64_t cols;      /* inputs */
+} sz_tensor;
+
+typedef struct sz_model_config {
+    int32_t n_layer, hidden, streams, hc_rank, vocab;
+    int32_t n_head, n_kv_head, head_dim, rope_dims;
+    int32_t n_expert, n_expert_used, expert_ff, shared_ff;
+    int32_t ssm_k_heads, ssm_v_heads, ssm_head_dim, conv_k;
+    int32_t attn_interval;      /* layer l is gated attention iff l % attn_interval == attn_interval - 1, else DeltaNet */
+    float eps;
+    float reserved;
+    double rope_theta;
+} sz_model_config;
+
+typedef struct sz_hc {          /* a hyper-connection read: forward.rs:797-817 */
+    sz_tensor norm;             /* F32 [streams * hidden] */
+    sz_tensor down;             /* [streams * hidden -> rank] */
+    sz_tensor up;               /* [rank -> streams * hidden] */
+    sz_tensor inject;           /* [streams * hidden -> streams]; absent for the output read */
+} sz_hc;
+
+typedef struct sz_layer {
+    sz_hc hc_attn, hc_ffn;
+    /* DeltaNet (forward.rs:819-896) */
+    sz_tensor attn_qkv, attn_gate, ssm_beta, ssm_alpha, ssm_conv1d, ssm_a, ssm_dt_bias, ssm_norm, ssm_out;
+    /* gated attention (forward.rs:898-1007) */
+    sz_tensor attn_q, attn_k, attn_v, attn_q_norm, attn_k_norm, attn_output;
+    sz_moe_layer moe;
+} sz_layer;
+
+typedef struct sz_model {
+    sz_model_config cfg;
+    sz_tensor token_embd;       /* [hidden -> vocab]: row t is token t's embedding */
+    sz_tensor output;           /* [hidden -> vocab] */
+    sz_hc output_hc;
+    const sz_layer* layers;     /* host array of n_layer entries */
+} sz_model;
+
+/* ---- the session: the verify surface ------------------------------------------------------------------------------------
+ * Replaces the verify subset of GpuSession (crates/shadowzero-cuda/src/session.rs): step_batch_verify_top (6061-6072), rollback
+ * (6217-6276), note_verify, capacity, tokens, and prefill by passes.  One engine thread owns a session (engine.rs:340-420).
+ * All device memory comes from the caller: sz_session_bytes sizes one block that holds the KV cache (ctx positions), the DeltaNet
+ * states (two copies: a pass never overwrites the state it started from, so a rejection needs no snapshot), and every scratch
+ * buffer.  flags: SZ_KV_Q8 keeps K and V as packed per-32 int8 + f16 scales (kernels/forward.cu:3652-3687); 0 keeps f32. */
+#define SZ_KV_Q8 1
+#define SZ_ACCEPT_NONE 0    /* the caller decides: read the top-64 of every row, then sz_session_commit(keep) */
+#define SZ_ACCEPT_GREEDY 1  /* on the device: keep row i + 1 while row i's best token is the drafted ids[i + 1] (engine.rs:2377-2408) */
+#define SZ_ACCEPT_ALL 2     /* prompt rows: all kept */
+typedef struct sz_session sz_session;
+int sz_session_bytes(const sz_model* model, int ctx, int flags, int64_t* bytes);
+int sz_session_create(const sz_model* model, int ctx, int flags, uint64_t mem, int64_t bytes, uint64_t stream, sz_session** out);
+void sz_session_destroy(sz_session* s);
+int sz_session_reset(sz_session* s, uint64_t stream);
+int sz_session_len(const sz_session* s);        /* committed positions: GpuSession::tokens().len() */
+int sz_session_capacity(const sz_session* s);   /* GpuSession::capacity() */
+/* Feeds a prompt in passes of up to SZ_MAX_VERIFY rows.  The last pass is left pending: read it with sz_session_result (its last
+ * row is the prompt's last token), then sz_session_commit(s, rows of that pass). */
+int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint64_t stream);
+/* One pass over ids[0..m): row i's output is what follows ids[..=i] (step_batch_verify).  want_head = 0 skips the output
+ * projection (prompt passes).  Asynchronous; the pass stays pending until sz_session_commit. */
+int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode, int eog_token, int want_head, uint64_t stream);
+/* Copies the pending pass's results to the host and synchronises: keep_next[2] = {rows kept by the device's acceptance, the
+ * token that follows them}; top = [m][128] u32, 64 logit bit patterns (largest first, ties to the lower id) then 64 token ids
+ * (session.rs:6034-6039); logits = [m][vocab] f32.  Any pointer may be null. */
+int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* top, float* logits, uint64_t stream);
+/* Keeps the first `keep` rows of the pending pass and drops the rest (rollback(&snap, &batch[..keep])). */
+int sz_session_commit(sz_session* s, int keep, uint64_t stream);
+/* Routing trace (the `layerL.route_idx` / `route_w` streams, forward.rs:1015-1018): switch it on, run a pass, read
+ * idx [n_layer][SZ_MAX_VERIFY][SZ_MAX_TOPK] and w (same shape, f64). */
+int sz_session_trace_routes(sz_session* s, int on);
+int sz_session_routes(sz_session* s, int32_t* idx, double* w, uint64_t stream);
+
+/* ---- the host side of speculation: drafting, the draft policy, sampling, the loop ------------------------------------------------
+ * Pure host code (no CUDA): C++ where the reference is Rust.  Token ids are uint32_t, as there. */
+/* Prompt lookup: the (up to) k tokens after the latest earlier occurrence of the history's last n tokens, n tried from `lens` in
+ * order (lookup_from, crates/shadowzero-serve/src/engine.rs:829-839).  Returns how many were written. */
+int sz_lookup(const uint32_t* hist, int n_hist, int k, const int* lens, int n_lens, uint32_t* out);
+/* SuffixDrafter (engine.rs:841-1011): trigram index of the history, longest then most recent match, propose_after chaining. */
+typedef struct sz_drafter sz_drafter;
+sz_drafter* sz_drafter_new(int min_match, int max_match, int capacity_tokens);
+void sz_drafter_free(sz_drafter* d);
+void sz_drafter_push(sz_drafter* d, uint32_t token);
+void sz_drafter_extend(sz_drafter* d, const uint32_t* tokens, int n);
+int sz_drafter_len(const sz_drafter* d);
+int sz_drafter_propose(const sz_drafter* d, int max_k, uint32_t* out, int* match_len);
+int sz_drafter_propose_with_min(const sz_drafter* d, int max_k, int min_match, uint32_t* out, int* match_len);
+int sz_drafter_propose_after(sz_drafter* d, const uint32_t* extra, int n_extra, int max_k, uint32_t* out, int* match_len);
+/* DraftPolicy (engine.rs:1013-1309): cost-per-millisecond choice between a neural window and a lookup window, chain length, and
+ * the adaptive neural depth.  It is consulted only when a neural drafter exists (engine.rs:2253-2264). */
+typedef struct sz_draft_policy sz_draft_policy;
+sz_draft_policy* sz_policy_new(int max_t, int base_spec, double margin);
+void sz_policy_free(sz_draft_policy* p);
+double sz_policy_accept_ema(const sz_draft_policy* p);
+int sz_policy_neural_k(const sz_draft_policy* p, int rem_tokens);
+int sz_policy_choose(const sz_draft_policy* p, int t_neural, int lookup_k, int match_len, int* lookup);
+int sz_policy_chain(const sz_draft_policy* p, int t_neural, double p_neural, int k_avail, int match_len);
+void sz_policy_observe(sz_draft_policy* p, int lookup, int t, int accepted, int match_len, double round_ms);
+void sz_policy_observe_chain(sz_draft_policy* p, int t_neural, int k_chain, int accepted, int match_len, double round_ms);
+/* Sampler (crates/shadowzero-serve/src/sampler.rs:83-210), the part that works from a row's top-64: a resolved sampler without
+ * penalties (Sampler::top_ok).  sz_uniform is the counter-based number of (seed, position). */
+typedef struct sz_sampler { float temperature; int32_t top_k; float top_p; float min_p; uint64_t seed; } sz_sampler;
+double sz_uniform(uint64_t seed, uint64_t pos);
+uint32_t sz_sample_top(const sz_sampler* sp, const uint32_t* top128, uint64_t pos);
+/* The draft / verify / accept / commit loop of engine.rs:2149-2454 for `--spec spec_k` with the suffix drafter (no neural
+ * drafter, draft policy not consulted): generates up to max_new tokens after the prompt into `out`; pass_log receives
+ * (drafted, accepted) per verify pass.  device_accept = 1 lets the device decide greedy acceptance (checked against the host). */
+typedef struct sz_gen_params { int32_t spec_k, max_new, lookup_min, greedy, eog_token, device_accept; sz_sampler sampler; } sz_gen_params;
+typedef struct sz_gen_stats {
+    int32_t n_tokens, passes, drafted, accepted, lookup_passes, reserved;
+    int32_t pos_tried[8], pos_right[8];
+    double draft_ms, verify_ms, commit_ms;
+} sz_gen_stats;
+int sz_generate(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint32_t* out, int32_t* pass_log, int pass_cap,
+                sz_gen_stats* stats, uint64_t stream);
+
 /* sz_moe_verify without a scratch argument.  (No counterpart in the reference: its session always owns a scratch buffer.)
  * For hosts that cannot allocate device memory once they are running - an engine that gave all of it to its own arena at start-up,
  * a plugin in a process that forbids the CUDA allocator after initialisation (a cudaMalloc would stall every stream of the GPU) -

@@ -54,6 +54,41 @@ def lib():
         L.szo_softplus.restype = C.c_float
         L.szo_softplus.argtypes = [C.c_float]
         L.szo_moe.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int]
+        L.szo_kv_q8_head_bytes.restype = C.c_size_t
+        L.szo_kv_q8_head_bytes.argtypes = [C.c_int]
+        L.szo_kv_quant_q8.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.szo_kv_dequant_q8.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.szo_top64.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p]
+        L.szo_session_new.restype = C.c_void_p
+        L.szo_session_new.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.szo_session_free.argtypes = [C.c_void_p]
+        L.szo_session_len.argtypes = [C.c_void_p]
+        L.szo_session_routes.restype = C.POINTER(C.c_int32)
+        L.szo_session_routes.argtypes = [C.c_void_p]
+        L.szo_session_route_weights.restype = C.POINTER(C.c_double)
+        L.szo_session_route_weights.argtypes = [C.c_void_p]
+        L.szo_session_assign.argtypes = [C.c_void_p, C.c_void_p]
+        L.szo_session_clone.restype = C.c_void_p
+        L.szo_session_clone.argtypes = [C.c_void_p]
+        L.szo_session_step.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.szo_lookup.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
+        L.szo_drafter_new.restype = C.c_void_p
+        L.szo_drafter_new.argtypes = [C.c_int, C.c_int, C.c_int]
+        L.szo_drafter_free.argtypes = [C.c_void_p]
+        L.szo_drafter_push.argtypes = [C.c_void_p, C.c_uint32]
+        L.szo_drafter_len.argtypes = [C.c_void_p]
+        L.szo_drafter_propose.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.POINTER(C.c_int)]
+        L.szo_drafter_propose_with_min.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_int)]
+        L.szo_drafter_propose_after.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_int)]
+        L.szo_splitmix64.restype = C.c_uint64
+        L.szo_splitmix64.argtypes = [C.c_uint64]
+        L.szo_uniform.restype = C.c_double
+        L.szo_uniform.argtypes = [C.c_uint64, C.c_uint64]
+        L.szo_sample.restype = C.c_uint32
+        L.szo_sample.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_uint64]
+        L.szo_sample_top.restype = C.c_uint32
+        L.szo_sample_top.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_uint64]
+        L.szo_generate.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
         _LIB = L
     return _LIB
 
@@ -143,3 +178,116 @@ def moe(layer, u, threads=1):
     logits = np.empty(layer["n_expert"], dtype=np.float32)
     lib().szo_moe(C.byref(Ls), _p(u), _p(y), _p(idx), _p(w), _p(logits), threads)
     return y, idx, w, logits
+
+
+# ---- part 2: sessions, cache formats, drafting, sampling, the speculation loop ------------------------------------------------
+
+class SamplerC(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("min_p", C.c_float), ("seed", C.c_uint64)]
+
+
+class GenParamsC(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("spec_k", "max_new", "lookup_min", "greedy", "eog_token", "reserved")] + [("sampler", SamplerC)]
+
+
+class GenStatsC(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_tokens", "passes", "drafted", "accepted", "lookup_passes")] + \
+               [("pos_tried", C.c_int32 * 8), ("pos_right", C.c_int32 * 8)]
+
+
+def kv_quant_q8(v):
+    v = np.ascontiguousarray(v, dtype=np.float32)
+    out = np.empty(lib().szo_kv_q8_head_bytes(v.size), dtype=np.uint8)
+    lib().szo_kv_quant_q8(_p(v), v.size, _p(out))
+    return out
+
+
+def kv_dequant_q8(b, hd):
+    out = np.empty(hd, dtype=np.float32)
+    lib().szo_kv_dequant_q8(_p(np.ascontiguousarray(b, dtype=np.uint8)), hd, _p(out))
+    return out
+
+
+def top64(logits):
+    logits = np.ascontiguousarray(logits, dtype=np.float32)
+    v = np.empty(64, dtype=np.float32)
+    i = np.empty(64, dtype=np.uint32)
+    lib().szo_top64(_p(logits), logits.size, _p(v), _p(i))
+    return v, i
+
+
+class Session:
+    """The CPU reference session over a host-resident struct sz_model (`model_struct`: a ctypes struct kept alive by the caller)."""
+
+    def __init__(self, host_model, kv_q8=False, threads=1):
+        self.hm = host_model
+        self.vocab = host_model.cfg["vocab"]
+        self.h = lib().szo_session_new(C.byref(host_model.model), 1 if kv_q8 else 0, threads)
+
+    def __del__(self):
+        if getattr(self, "h", None) and _LIB is not None:
+            _LIB.szo_session_free(self.h)
+            self.h = None
+
+    def __len__(self):
+        return lib().szo_session_len(self.h)
+
+    def step(self, token, want_logits=True, want_u=False):
+        lg = np.empty(self.vocab, dtype=np.float32) if want_logits else None
+        u = np.empty(self.hm.cfg["hidden"], dtype=np.float32) if want_u else None
+        lib().szo_session_step(self.h, int(token), _p(lg) if want_logits else None, _p(u) if want_u else None)
+        return (lg, u) if want_u else lg
+
+    def routes(self):
+        n, k = self.hm.cfg["n_layer"], self.hm.cfg["n_expert_used"]
+        idx = np.ctypeslib.as_array(lib().szo_session_routes(self.h), shape=(n, k)).copy()
+        w = np.ctypeslib.as_array(lib().szo_session_route_weights(self.h), shape=(n, k)).copy()
+        return idx, w
+
+    def generate(self, prompt, max_new, spec_k=3, greedy=True, sampler=None, lookup_min=4, eog=-1):
+        p = GenParamsC(spec_k, max_new, lookup_min, 1 if greedy else 0, eog, 0, sampler or SamplerC(1.0, 20, 0.95, 0.0, 1))
+        pr = np.array(prompt, dtype=np.uint32)
+        out = np.zeros(max_new, dtype=np.uint32)
+        log = np.zeros(2 * max_new, dtype=np.int32)
+        st = GenStatsC()
+        n = lib().szo_generate(self.h, _p(pr), len(prompt), C.byref(p), _p(out), _p(log), max_new, C.byref(st))
+        return [int(t) for t in out[:n]], [(int(log[2 * i]), int(log[2 * i + 1])) for i in range(st.passes)], st
+
+
+class Drafter:
+    def __init__(self, min_match=4, max_match=32, capacity=4096):
+        self.h = lib().szo_drafter_new(min_match, max_match, capacity)
+
+    def __del__(self):
+        if getattr(self, "h", None) and _LIB is not None:
+            _LIB.szo_drafter_free(self.h)
+            self.h = None
+
+    def extend(self, toks):
+        for t in toks:
+            lib().szo_drafter_push(self.h, int(t))
+
+    def __len__(self):
+        return lib().szo_drafter_len(self.h)
+
+    def propose(self, k, min_match=None):
+        out = np.zeros(max(k, 1), dtype=np.uint32)
+        ml = C.c_int()
+        n = lib().szo_drafter_propose(self.h, k, _p(out), C.byref(ml)) if min_match is None else \
+            lib().szo_drafter_propose_with_min(self.h, k, min_match, _p(out), C.byref(ml))
+        return [int(t) for t in out[:n]], ml.value
+
+    def propose_after(self, extra, k):
+        out = np.zeros(max(k, 1), dtype=np.uint32)
+        ex = np.array(extra, dtype=np.uint32)
+        ml = C.c_int()
+        n = lib().szo_drafter_propose_after(self.h, _p(ex), len(extra), k, _p(out), C.byref(ml))
+        return [int(t) for t in out[:n]], ml.value
+
+
+def lookup(hist, k, lens=(3, 2)):
+    h = np.array(hist, dtype=np.uint32)
+    ls = np.array(lens, dtype=np.int32)
+    out = np.zeros(max(k, 1), dtype=np.uint32)
+    n = lib().szo_lookup(_p(h), len(hist), k, _p(ls), len(lens), _p(out))
+    return [int(t) for t in out[:n]]

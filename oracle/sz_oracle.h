@@ -20,6 +20,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "../include/shadowzero_b200.h" /* the model description structs (sz_model, sz_layer, sz_tensor): data = host addresses here */
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -83,6 +85,44 @@ typedef struct {
  * optional outputs. */
 void szo_moe(const szo_moe_layer* L, const float* u, float* y, int32_t* route_idx, double* route_w, float* logits,
              int threads);
+
+/* ---- part 2 (sz_oracle_model.c): the forward step, the cache formats, drafting, sampling, the speculation loop ---------- */
+size_t szo_kv_q8_head_bytes(int hd);
+void szo_kv_quant_q8(const float* src, int hd, uint8_t* dst);     /* kernels/forward.cu:3664-3687 */
+void szo_kv_dequant_q8(const uint8_t* src, int hd, float* dst);
+void szo_top64(const float* logits, int vocab, float* vals64, uint32_t* ids64); /* kernels/forward.cu:3565-3625 */
+
+typedef struct szo_session szo_session;
+szo_session* szo_session_new(const sz_model* m, int kv_q8, int threads);
+void szo_session_free(szo_session* s);
+int szo_session_len(const szo_session* s);
+const int32_t* szo_session_routes(const szo_session* s);          /* [n_layer][top_k] of the last step */
+const double* szo_session_route_weights(const szo_session* s);
+void szo_session_assign(szo_session* dst, const szo_session* src); /* snapshot / restore */
+szo_session* szo_session_clone(const szo_session* src);
+void szo_session_step(szo_session* s, uint32_t token, float* logits, float* final_u); /* forward.rs:751-794 */
+
+int szo_lookup(const uint32_t* hist, int n_hist, int k, const int* lens, int n_lens, uint32_t* out); /* engine.rs:829-839 */
+typedef struct szo_drafter szo_drafter;
+szo_drafter* szo_drafter_new(int min_match, int max_match, int capacity_tokens);                     /* engine.rs:862-874 */
+void szo_drafter_free(szo_drafter* d);
+void szo_drafter_push(szo_drafter* d, uint32_t token);
+int szo_drafter_len(const szo_drafter* d);
+int szo_drafter_propose(const szo_drafter* d, int max_k, uint32_t* out, int* match_len);
+int szo_drafter_propose_with_min(const szo_drafter* d, int max_k, int min_match, uint32_t* out, int* match_len);
+int szo_drafter_propose_after(szo_drafter* d, const uint32_t* extra, int n_extra, int max_k, uint32_t* out, int* match_len);
+
+typedef struct { float temperature; int32_t top_k; float top_p; float min_p; uint64_t seed; } szo_sampler; /* a resolved Sampler */
+uint64_t szo_splitmix64(uint64_t x);
+double szo_uniform(uint64_t seed, uint64_t pos);                                                       /* sampler.rs:90-94 */
+uint32_t szo_sample(const szo_sampler* sp, const float* logits, int vocab, uint64_t pos);              /* sampler.rs:112-157 */
+uint32_t szo_sample_top(const szo_sampler* sp, const float* tv, const uint32_t* ti, int ntop, uint64_t pos);
+
+typedef struct { int32_t spec_k, max_new, lookup_min, greedy, eog_token, reserved; szo_sampler sampler; } szo_gen_params;
+typedef struct { int32_t n_tokens, passes, drafted, accepted, lookup_passes; int32_t pos_tried[8], pos_right[8]; } szo_gen_stats;
+/* Generates up to max_new tokens after the prompt with the engine's loop; pass_log gets (drafted, accepted) per verify pass. */
+int szo_generate(szo_session* s, const uint32_t* prompt, int n_prompt, const szo_gen_params* p, uint32_t* out, int32_t* pass_log,
+                 int pass_cap, szo_gen_stats* stats);
 
 #ifdef __cplusplus
 }

@@ -37,16 +37,25 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
         double acc[SZ_MAX_VERIFY];
 #pragma unroll
         for (int j = 0; j < SZ_MAX_VERIFY; j++) acc[j] = 0.0;
-        for (int c = lane; c < H / 4; c += 32) {
-            const float4 w = __ldg(wrow + c);
+        // four independent row loads in flight per lane (hidden is a multiple of 128 floats = 32 lanes x float4)
+        for (int c0 = 0; c0 < H / 4; c0 += 128) {
+            float4 w[4];
 #pragma unroll
-            for (int j = 0; j < SZ_MAX_VERIFY; j++) {
-                if (j < m) {
-                    const float4 v = __ldg((const float4*)(x + (size_t)j * H) + c);
-                    acc[j] += (double)w.x * (double)v.x;
-                    acc[j] += (double)w.y * (double)v.y;
-                    acc[j] += (double)w.z * (double)v.z;
-                    acc[j] += (double)w.w * (double)v.w;
+            for (int u = 0; u < 4; u++) w[u] = c0 + 32 * u + lane < H / 4 ? __ldg(wrow + c0 + 32 * u + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int c = c0 + 32 * u + lane;
+                if (c < H / 4) {
+#pragma unroll
+                    for (int j = 0; j < SZ_MAX_VERIFY; j++) {
+                        if (j < m) {
+                            const float4 v = __ldg((const float4*)(x + (size_t)j * H) + c);
+                            acc[j] += (double)w[u].x * (double)v.x;
+                            acc[j] += (double)w[u].y * (double)v.y;
+                            acc[j] += (double)w[u].z * (double)v.z;
+                            acc[j] += (double)w[u].w * (double)v.w;
+                        }
+                    }
                 }
             }
         }

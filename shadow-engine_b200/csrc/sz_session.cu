@@ -1,0 +1,520 @@
+// The verify surface of the GPU session: prefill, verify (1..8 rows in one pass), acceptance, commit / rollback.
+// Mirrors GpuSession::{step_batch_verify_top, rollback, note_verify, capacity, tokens} of the reference
+// (crates/shadowzero-cuda/src/session.rs:6061-6107, 6217-6276) for a model held entirely in HBM.
+//
+// State that a rejected draft must not touch is double-buffered instead of snapshotted: a pass reads the DeltaNet states and
+// conv rows of buffer `cur` and writes those after all m rows into buffer `cur ^ 1`; a commit of fewer rows re-runs the (cheap)
+// recurrences for the kept rows from the pass's saved inputs - the reference's replay (session.rs:6245-6268) - into `cur ^ 1`,
+// then the buffers swap.  The KV cache is append-only: rejected positions are overwritten by the next pass.
+#include "sz_session_kernels.cuh"
+
+#include <new>
+#include <string.h>
+#include <vector>
+
+struct SzLayerBuf {
+    int delta_index;   // index among DeltaNet layers, or -1
+    int attn_index;    // index among attention layers, or -1
+};
+
+struct sz_session {
+    sz_model model;
+    std::vector<sz_layer> layers;
+    std::vector<SzLayerBuf> lb;
+    int ctx, flags, n_delta, n_attn;
+    int len;          // committed positions
+    int cur;          // which state buffer is current
+    int last_m;       // rows of the last pass (0: none pending)
+    int want_routes;
+    // device memory (all inside the caller's block)
+    u8* base;
+    int64_t bytes;
+    float *r, *rn, *hdown, *mix, *u, *g, *y;
+    float *d_xin, *d_z, *d_b, *d_a, *d_xc, *d_beta, *d_decay, *d_og;   // per-layer saved: xin, xc, beta, decay [n_delta][8][...]
+    float *S[2], *conv[2];
+    float *a_qg, *a_k, *a_v, *a_q, *a_gate, *a_o, *a_part;
+    u8 *kc, *vc;
+    float* logits;
+    u64* tk_tmp;
+    u32* top;
+    int32_t *ids, *res, *routes;
+    double* route_w;
+    u8* moe_scratch;
+    int64_t moe_scratch_bytes;
+    int attn_splits;
+    // host staging
+    int32_t h_ids[SZ_MAX_VERIFY];
+};
+
+static int sz_is_attn(const sz_model_config& c, int l) { return l % c.attn_interval == c.attn_interval - 1; }
+
+struct SzSessLayout {
+    int64_t r, rn, hdown, mix, u, g, y, d_xin, d_z, d_b, d_a, d_xc, d_beta, d_decay, d_og, S0, S1, conv0, conv1, a_qg, a_k, a_v, a_q, a_gate,
+        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, routes, route_w, moe, total;
+    int64_t moe_bytes, S_bytes, conv_bytes, kv_bytes;
+    int splits;
+};
+
+static int64_t up256(int64_t v) { return (v + 255) & ~(int64_t)255; }
+
+static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L) {
+    const sz_model_config& c = m->cfg;
+    const int64_t M = SZ_MAX_VERIFY, H = c.hidden, C = c.streams, CH = C * H;
+    int n_delta = 0, n_attn = 0;
+    for (int l = 0; l < c.n_layer; l++) (sz_is_attn(c, l) ? n_attn : n_delta)++;
+    const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd, vh = c.ssm_v_heads;
+    const int64_t qd = (int64_t)c.n_head * c.head_dim, kvd = (int64_t)c.n_kv_head * c.head_dim;
+    int64_t o = 0;
+    auto take = [&](int64_t bytes) { int64_t at = o; o = up256(o + bytes); return at; };
+    L->r = take(4 * M * CH); L->rn = take(4 * M * CH); L->hdown = take(4 * M * c.hc_rank); L->mix = take(4 * M * CH);
+    L->u = take(4 * M * H); L->g = take(4 * M * C); L->y = take(4 * M * H);
+    const int64_t nd = n_delta > 0 ? n_delta : 1;
+    L->d_xin = take(4 * nd * M * ch); L->d_xc = take(4 * nd * M * ch); L->d_beta = take(4 * nd * M * vh); L->d_decay = take(4 * nd * M * vh);
+    L->d_z = take(4 * M * vd); L->d_b = take(4 * M * vh); L->d_a = take(4 * M * vh); L->d_og = take(4 * M * vd);
+    L->S_bytes = 4 * nd * vh * c.ssm_head_dim * c.ssm_head_dim;
+    L->conv_bytes = 4 * nd * (c.conv_k - 1) * ch;
+    L->S0 = take(L->S_bytes); L->S1 = take(L->S_bytes); L->conv0 = take(L->conv_bytes); L->conv1 = take(L->conv_bytes);
+    L->a_qg = take(4 * M * 2 * qd); L->a_k = take(4 * M * kvd); L->a_v = take(4 * M * kvd); L->a_q = take(4 * M * qd);
+    L->a_gate = take(4 * M * qd); L->a_o = take(4 * M * qd);
+    // enough (head, row, split) blocks to fill the GPU twice over, at least 256 positions a split
+    int splits = 1;
+    if (c.n_head > 0) {
+        splits = (int)((2 * 148 + c.n_head * 4 - 1) / (c.n_head * 4));
+        const int by_len = (ctx + 255) / 256;
+        if (splits > by_len) splits = by_len;
+        if (splits < 1) splits = 1;
+    }
+    L->splits = splits;
+    L->a_part = take(4 * M * c.n_head * splits * (c.head_dim + 2));
+    const int64_t hb = (flags & SZ_KV_Q8) ? (c.head_dim + (((c.head_dim >> 5) * 2 + 15) & ~15)) : 4 * (int64_t)c.head_dim;
+    L->kv_bytes = (int64_t)(n_attn > 0 ? n_attn : 1) * ctx * c.n_kv_head * hb;
+    L->kc = take(L->kv_bytes); L->vc = take(L->kv_bytes);
+    L->logits = take(4 * M * (int64_t)c.vocab);
+    const int64_t nb = ((int64_t)c.vocab + SZ_TK_N - 1) / SZ_TK_N;
+    L->tk_tmp = take(8 * M * nb * 64); L->top = take(4 * M * 128);
+    L->ids = take(4 * M); L->res = take(64);
+    L->routes = take(4 * (int64_t)c.n_layer * M * SZ_MAX_TOPK); L->route_w = take(8 * (int64_t)c.n_layer * M * SZ_MAX_TOPK);
+    int64_t moe_bytes = 0;
+    for (int l = 0; l < c.n_layer; l++) {
+        int64_t b = 0;
+        const int rc = sz_moe_scratch_bytes(&m->layers[l].moe, SZ_MAX_VERIFY, &b);
+        if (rc) return rc;
+        if (b > moe_bytes) moe_bytes = b;
+    }
+    L->moe_bytes = moe_bytes;
+    L->moe = take(moe_bytes);
+    L->total = o;
+    return SZ_OK;
+}
+
+int sz_dense_check(const sz_tensor* t, const char* what, int64_t rows, int64_t cols) {
+    if (!t->data || t->rows != rows || t->cols != cols)
+        return sz_fail(SZ_E_ARG, "%s: expected a [%lld -> %lld] tensor, got [%lld -> %lld]%s", what, (long long)cols, (long long)rows,
+                       (long long)t->cols, (long long)t->rows, t->data ? "" : " (null)");
+    switch (t->type) {
+        case SZ_TYPE_F32: case SZ_TYPE_F16: case SZ_TYPE_BF16: if (cols % 4) return sz_fail(SZ_E_ARG, "%s: %lld columns are not a multiple of 4", what, (long long)cols); break;
+        case SZ_TYPE_Q8_0: if (cols % 32) return sz_fail(SZ_E_ARG, "%s: Q8_0 rows of %lld weights", what, (long long)cols); break;
+        case SZ_TYPE_IQ3_S: if (cols % 256) return sz_fail(SZ_E_ARG, "%s: IQ3_S rows of %lld weights", what, (long long)cols); break;
+        default: return sz_fail(SZ_E_TYPE, "%s: no dense kernel for tensor type %d", what, t->type);
+    }
+    if (t->data & 15) return sz_fail(SZ_E_ARG, "%s: the tensor must start on a 16-byte boundary", what);
+    return SZ_OK;
+}
+
+static int sz_f32_check(const sz_tensor* t, const char* what, int64_t n) {
+    if (!t->data || t->type != SZ_TYPE_F32 || t->rows * t->cols != n || (t->data & 15))
+        return sz_fail(SZ_E_ARG, "%s: expected %lld F32 values, 16-byte aligned", what, (long long)n);
+    return SZ_OK;
+}
+
+static int sz_model_check(const sz_model* m) {
+    if (!m || !m->layers) return sz_fail(SZ_E_ARG, "null model");
+    const sz_model_config& c = m->cfg;
+    if (c.n_layer < 1 || c.hidden < 128 || c.hidden % 128 || c.streams < 1 || c.streams > 8 || c.hc_rank < 4 || c.hc_rank % 4 || c.vocab < 64)
+        return sz_fail(SZ_E_ARG, "bad model shape (layers %d, hidden %d, streams %d, rank %d, vocab %d)", c.n_layer, c.hidden, c.streams, c.hc_rank, c.vocab);
+    if (c.vocab > 64 * SZ_TK_N) return sz_fail(SZ_E_ARG, "vocab %d exceeds %d", c.vocab, 64 * SZ_TK_N);
+    if (c.attn_interval < 1) return sz_fail(SZ_E_ARG, "attn_interval %d", c.attn_interval);
+    if (!(c.head_dim == 64 || c.head_dim == 128 || c.head_dim == 256) || c.n_head < 1 || c.n_kv_head < 1 || c.n_head % c.n_kv_head || c.rope_dims % 2 ||
+        c.rope_dims > c.head_dim)
+        return sz_fail(SZ_E_ARG, "attention shape (heads %d / %d, head_dim %d, rope %d): head_dim must be 64, 128 or 256", c.n_head, c.n_kv_head, c.head_dim, c.rope_dims);
+    if (!(c.ssm_head_dim == 64 || c.ssm_head_dim == 128) || c.ssm_k_heads < 1 || c.ssm_v_heads % c.ssm_k_heads || c.conv_k < 2 || c.conv_k > 8)
+        return sz_fail(SZ_E_ARG, "DeltaNet shape (heads %d / %d, dim %d, conv %d): head dim must be 64 or 128", c.ssm_k_heads, c.ssm_v_heads, c.ssm_head_dim, c.conv_k);
+    const int64_t H = c.hidden, CH = (int64_t)c.streams * H;
+    const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd;
+    const int64_t qd = (int64_t)c.n_head * c.head_dim, kvd = (int64_t)c.n_kv_head * c.head_dim;
+    int rc;
+    auto hc = [&](const sz_hc& h, const char* what, bool inject) -> int {
+        int r2;
+        if ((r2 = sz_f32_check(&h.norm, what, CH))) return r2;
+        if ((r2 = sz_dense_check(&h.down, what, c.hc_rank, CH))) return r2;
+        if ((r2 = sz_dense_check(&h.up, what, CH, c.hc_rank))) return r2;
+        if (inject && (r2 = sz_dense_check(&h.inject, what, c.streams, CH))) return r2;
+        return SZ_OK;
+    };
+    if ((rc = sz_dense_check(&m->token_embd, "token_embd", c.vocab, H))) return rc;
+    if ((rc = sz_dense_check(&m->output, "output", c.vocab, H))) return rc;
+    if ((rc = hc(m->output_hc, "output_hc", false))) return rc;
+    for (int l = 0; l < c.n_layer; l++) {
+        const sz_layer& L = m->layers[l];
+        if ((rc = hc(L.hc_attn, "hc_attn", true))) return rc;
+        if ((rc = hc(L.hc_ffn, "hc_ffn", true))) return rc;
+        if (sz_is_attn(c, l)) {
+            if ((rc = sz_dense_check(&L.attn_q, "attn_q", 2 * qd, H))) return rc;
+            if ((rc = sz_dense_check(&L.attn_k, "attn_k", kvd, H))) return rc;
+            if ((rc = sz_dense_check(&L.attn_v, "attn_v", kvd, H))) return rc;
+            if ((rc = sz_dense_check(&L.attn_output, "attn_output", H, qd))) return rc;
+            if ((rc = sz_f32_check(&L.attn_q_norm, "attn_q_norm", c.head_dim))) return rc;
+            if ((rc = sz_f32_check(&L.attn_k_norm, "attn_k_norm", c.head_dim))) return rc;
+        } else {
+            if ((rc = sz_dense_check(&L.attn_qkv, "attn_qkv", ch, H))) return rc;
+            if ((rc = sz_dense_check(&L.attn_gate, "attn_gate", vd, H))) return rc;
+            if ((rc = sz_dense_check(&L.ssm_beta, "ssm_beta", c.ssm_v_heads, H))) return rc;
+            if ((rc = sz_dense_check(&L.ssm_alpha, "ssm_alpha", c.ssm_v_heads, H))) return rc;
+            if ((rc = sz_dense_check(&L.ssm_out, "ssm_out", H, vd))) return rc;
+            if ((rc = sz_f32_check(&L.ssm_conv1d, "ssm_conv1d", ch * c.conv_k))) return rc;
+            if ((rc = sz_f32_check(&L.ssm_a, "ssm_a", c.ssm_v_heads))) return rc;
+            if ((rc = sz_f32_check(&L.ssm_dt_bias, "ssm_dt.bias", c.ssm_v_heads))) return rc;
+            if ((rc = sz_f32_check(&L.ssm_norm, "ssm_norm", c.ssm_head_dim))) return rc;
+        }
+        if (L.moe.hidden != c.hidden || L.moe.n_expert != c.n_expert || L.moe.top_k != c.n_expert_used)
+            return sz_fail(SZ_E_ARG, "layer %d: the MoE description does not match the model shape", l);
+    }
+    return SZ_OK;
+}
+
+extern "C" int sz_session_bytes(const sz_model* m, int ctx, int flags, int64_t* bytes) {
+    int rc = sz_model_check(m);
+    if (rc) return rc;
+    if (ctx < 8 || !bytes) return sz_fail(SZ_E_ARG, "sz_session_bytes: ctx = %d", ctx);
+    SzSessLayout L;
+    if ((rc = sz_sess_layout(m, ctx, flags, &L))) return rc;
+    *bytes = L.total;
+    return SZ_OK;
+}
+
+extern "C" int sz_session_reset(sz_session* s, uint64_t stream) {
+    if (!s) return sz_fail(SZ_E_ARG, "null session");
+    SzSessLayout L;
+    int rc = sz_sess_layout(&s->model, s->ctx, s->flags, &L);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    SZ_CUDA(cudaMemsetAsync(s->S[0], 0, L.S_bytes, st));
+    SZ_CUDA(cudaMemsetAsync(s->S[1], 0, L.S_bytes, st));
+    SZ_CUDA(cudaMemsetAsync(s->conv[0], 0, L.conv_bytes, st));
+    SZ_CUDA(cudaMemsetAsync(s->conv[1], 0, L.conv_bytes, st));
+    if ((rc = sz_moe_scratch_init((uint64_t)s->moe_scratch, s->moe_scratch_bytes, stream))) return rc;
+    s->len = 0; s->cur = 0; s->last_m = 0;
+    return SZ_OK;
+}
+
+extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t mem, int64_t bytes, uint64_t stream, sz_session** out) {
+    int rc = sz_model_check(m);
+    if (rc) return rc;
+    if (!out || !mem || (mem & 255)) return sz_fail(SZ_E_ARG, "sz_session_create: memory must be 256-byte aligned");
+    SzSessLayout L;
+    if ((rc = sz_sess_layout(m, ctx, flags, &L))) return rc;
+    if (bytes < L.total) return sz_fail(SZ_E_SCRATCH, "sz_session_create: %lld bytes given, %lld needed", (long long)bytes, (long long)L.total);
+    sz_session* s = new (std::nothrow) sz_session();
+    if (!s) return sz_fail(SZ_E_ARG, "out of host memory");
+    s->model = *m;
+    s->layers.assign(m->layers, m->layers + m->cfg.n_layer);
+    s->model.layers = s->layers.data();
+    s->ctx = ctx; s->flags = flags; s->want_routes = 0;
+    s->lb.resize(m->cfg.n_layer);
+    s->n_delta = s->n_attn = 0;
+    for (int l = 0; l < m->cfg.n_layer; l++) {
+        const bool at = sz_is_attn(m->cfg, l);
+        s->lb[l].delta_index = at ? -1 : s->n_delta++;
+        s->lb[l].attn_index = at ? s->n_attn++ : -1;
+    }
+    u8* b = (u8*)mem;
+    s->base = b; s->bytes = bytes;
+    s->r = (float*)(b + L.r); s->rn = (float*)(b + L.rn); s->hdown = (float*)(b + L.hdown); s->mix = (float*)(b + L.mix);
+    s->u = (float*)(b + L.u); s->g = (float*)(b + L.g); s->y = (float*)(b + L.y);
+    s->d_xin = (float*)(b + L.d_xin); s->d_z = (float*)(b + L.d_z); s->d_b = (float*)(b + L.d_b); s->d_a = (float*)(b + L.d_a);
+    s->d_xc = (float*)(b + L.d_xc); s->d_beta = (float*)(b + L.d_beta); s->d_decay = (float*)(b + L.d_decay); s->d_og = (float*)(b + L.d_og);
+    s->S[0] = (float*)(b + L.S0); s->S[1] = (float*)(b + L.S1); s->conv[0] = (float*)(b + L.conv0); s->conv[1] = (float*)(b + L.conv1);
+    s->a_qg = (float*)(b + L.a_qg); s->a_k = (float*)(b + L.a_k); s->a_v = (float*)(b + L.a_v); s->a_q = (float*)(b + L.a_q);
+    s->a_gate = (float*)(b + L.a_gate); s->a_o = (float*)(b + L.a_o); s->a_part = (float*)(b + L.a_part);
+    s->kc = b + L.kc; s->vc = b + L.vc;
+    s->logits = (float*)(b + L.logits); s->tk_tmp = (u64*)(b + L.tk_tmp); s->top = (u32*)(b + L.top);
+    s->ids = (int32_t*)(b + L.ids); s->res = (int32_t*)(b + L.res); s->routes = (int32_t*)(b + L.routes); s->route_w = (double*)(b + L.route_w);
+    s->moe_scratch = b + L.moe; s->moe_scratch_bytes = L.moe_bytes;
+    s->attn_splits = L.splits;
+    if ((rc = sz_session_reset(s, stream))) { delete s; return rc; }
+    *out = s;
+    return SZ_OK;
+}
+
+extern "C" void sz_session_destroy(sz_session* s) { delete s; }
+extern "C" int sz_session_len(const sz_session* s) { return s ? s->len : -1; }
+extern "C" int sz_session_capacity(const sz_session* s) { return s ? s->ctx : -1; }
+extern "C" int sz_session_trace_routes(sz_session* s, int on) { if (!s) return sz_fail(SZ_E_ARG, "null session"); s->want_routes = on; return SZ_OK; }
+
+// ---- dense launcher -----------------------------------------------------------------------------------------------------------------
+int sz_dense_launch(SzDenseArgs& a, cudaStream_t st, const char* name) {
+    int total = 0;
+    for (int i = 0; i < a.n_jobs; i++) { a.job[i].row0 = total; total += a.job[i].rows; }
+    a.total_rows = total;
+    const size_t limit = 200 * 1024 - 2048;
+    int mt = a.m;
+    while (mt > 1 && (size_t)mt * a.cols * 4 > limit) mt = (mt + 1) / 2;
+    if ((size_t)mt * a.cols * 4 > limit) return sz_fail(SZ_E_ARG, "%s: %d input columns do not fit in shared memory", name, a.cols);
+    const size_t smem = 2048 + (size_t)mt * a.cols * 4;
+    int blocks = (total + 7) / 8;
+    const int cap = 148 * 8;
+    if (blocks > cap) blocks = cap;
+    static bool set[9] = {false};
+#define SZ_DENSE_CASE(MT)                                                                                                             \
+    case MT:                                                                                                                          \
+        if (!set[MT]) { SZ_CUDA(cudaFuncSetAttribute(sz_dense_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set[MT] = true; } \
+        SZ_CUDA(sz_launch(name, sz_dense_kernel<MT>, dim3(blocks), dim3(256), smem, st, true, a));                                   \
+        break;
+    switch (mt) {
+        SZ_DENSE_CASE(1) SZ_DENSE_CASE(2) SZ_DENSE_CASE(3) SZ_DENSE_CASE(4) SZ_DENSE_CASE(5) SZ_DENSE_CASE(6) SZ_DENSE_CASE(7) SZ_DENSE_CASE(8)
+    }
+#undef SZ_DENSE_CASE
+    return SZ_OK;
+}
+
+static SzDenseJob sz_job(const sz_tensor& t, float* out, int ostride, int epi = SZ_EPI_NONE, float div = 1.f) {
+    SzDenseJob j;
+    j.w = (const u8*)t.data; j.out = out; j.rows = (int)t.rows; j.type = t.type; j.ostride = ostride; j.epi = epi; j.div = div; j.row0 = 0;
+    return j;
+}
+
+// ---- one pass ---------------------------------------------------------------------------------------------------------------------------
+// hyper-connection read of `hc` for the m rows: applies the pending write (g_prev, y_prev) first; leaves u (and g when the read injects)
+static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bool pending, bool inject) {
+    const sz_model_config& c = s->model.cfg;
+    const int H = c.hidden, C = c.streams, CH = C * H;
+    SZ_CUDA(sz_launch("hc_norm", sz_hc_norm_kernel, dim3(C, m), dim3(256), 0, st, true, s->r, (const float*)(pending ? s->g : nullptr),
+                      (const float*)(pending ? s->y : nullptr), (const float*)hc.norm.data, H, C, c.eps, s->rn));
+    SzDenseArgs a = {};
+    a.x = s->rn; a.xstride = CH; a.cols = CH; a.m = m;
+    a.job[0] = sz_job(hc.down, s->hdown, c.hc_rank, SZ_EPI_SILU_DIV, (float)C);
+    a.n_jobs = 1;
+    if (inject) { a.job[1] = sz_job(hc.inject, s->g, C, SZ_EPI_SIGMOID2_DIV, (float)C); a.n_jobs = 2; }
+    int rc = sz_dense_launch(a, st, "hc_down");
+    if (rc) return rc;
+    SzDenseArgs b = {};
+    b.x = s->hdown; b.xstride = c.hc_rank; b.cols = c.hc_rank; b.m = m;
+    b.job[0] = sz_job(hc.up, s->mix, CH, SZ_EPI_SIGMOID);
+    b.n_jobs = 1;
+    if ((rc = sz_dense_launch(b, st, "hc_up"))) return rc;
+    SZ_CUDA(sz_launch("hc_mix", sz_hc_mix_kernel, dim3((H + 255) / 256, m), dim3(256), 0, st, true, (const float*)s->mix, (const float*)s->rn, H, C, s->u));
+    return SZ_OK;
+}
+
+template <int D, int PARTS>
+static int sz_scan_launch(cudaStream_t st, const char* name, const float* xc, const float* beta, const float* decay, const float* z,
+                          const float* norm_w, const float* Sin, float* Sout, int kh, int vh, int rows, float eps, float* og) {
+    SZ_CUDA(sz_launch(name, sz_delta_scan_kernel<D, PARTS>, dim3(vh), dim3(D * PARTS), 0, st, true, xc, beta, decay, z, norm_w, Sin, Sout, kh, vh,
+                      rows, eps, og));
+    return SZ_OK;
+}
+
+static int sz_scan(sz_session* s, cudaStream_t st, const char* name, int l, int rows, bool outputs) {
+    const sz_model_config& c = s->model.cfg;
+    const int di = s->lb[l].delta_index;
+    const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd;
+    const int64_t Sl = (int64_t)c.ssm_v_heads * c.ssm_head_dim * c.ssm_head_dim;
+    const float* xc = s->d_xc + (int64_t)di * SZ_MAX_VERIFY * ch;
+    const float* beta = s->d_beta + (int64_t)di * SZ_MAX_VERIFY * c.ssm_v_heads;
+    const float* decay = s->d_decay + (int64_t)di * SZ_MAX_VERIFY * c.ssm_v_heads;
+    const float* Sin = s->S[s->cur] + di * Sl;
+    float* Sout = s->S[s->cur ^ 1] + di * Sl;
+    const float* nw = (const float*)s->layers[l].ssm_norm.data;
+    float* og = outputs ? s->d_og : nullptr;
+    if (c.ssm_head_dim == 128)
+        return sz_scan_launch<128, 2>(st, name, xc, beta, decay, s->d_z, nw, Sin, Sout, c.ssm_k_heads, c.ssm_v_heads, rows, c.eps, og);
+    return sz_scan_launch<64, 1>(st, name, xc, beta, decay, s->d_z, nw, Sin, Sout, c.ssm_k_heads, c.ssm_v_heads, rows, c.eps, og);
+}
+
+static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
+    const sz_model_config& c = s->model.cfg;
+    const sz_layer& L = s->layers[l];
+    const int di = s->lb[l].delta_index;
+    const int H = c.hidden, vh = c.ssm_v_heads, kh = c.ssm_k_heads, d = c.ssm_head_dim;
+    const int64_t kd = (int64_t)kh * d, vd = (int64_t)vh * d, ch = 2 * kd + vd;
+    float* xin = s->d_xin + (int64_t)di * SZ_MAX_VERIFY * ch;
+    float* xc = s->d_xc + (int64_t)di * SZ_MAX_VERIFY * ch;
+    float* beta = s->d_beta + (int64_t)di * SZ_MAX_VERIFY * vh;
+    float* decay = s->d_decay + (int64_t)di * SZ_MAX_VERIFY * vh;
+    SzDenseArgs a = {};
+    a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 4;
+    a.job[0] = sz_job(L.attn_qkv, xin, (int)ch);
+    a.job[1] = sz_job(L.attn_gate, s->d_z, (int)vd);
+    a.job[2] = sz_job(L.ssm_beta, s->d_b, vh);
+    a.job[3] = sz_job(L.ssm_alpha, s->d_a, vh);
+    int rc = sz_dense_launch(a, st, "delta_proj");
+    if (rc) return rc;
+    const float* conv = s->conv[s->cur] + (int64_t)di * (c.conv_k - 1) * ch;
+    SZ_CUDA(sz_launch("delta_prep", sz_delta_prep_kernel, dim3(m), dim3(256), 0, st, true, (const float*)xin, conv, (const float*)L.ssm_conv1d.data,
+                      (const float*)s->d_b, (const float*)s->d_a, (const float*)L.ssm_a.data, (const float*)L.ssm_dt_bias.data, kh, vh, d,
+                      (int)c.conv_k, xc, beta, decay));
+    if ((rc = sz_scan(s, st, "delta_scan", l, m, true))) return rc;
+    SzDenseArgs b = {};
+    b.x = s->d_og; b.xstride = (int)vd; b.cols = (int)vd; b.m = m; b.n_jobs = 1;
+    b.job[0] = sz_job(L.ssm_out, s->y, H);
+    return sz_dense_launch(b, st, "ssm_out");
+}
+
+template <int EPL>
+static int sz_attn_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m) {
+    const sz_model_config& c = s->model.cfg;
+    SZ_CUDA(sz_launch("attention", sz_attn_kernel<EPL>, dim3(c.n_head, m, s->attn_splits), dim3(256), 0, st, true, (const float*)s->a_q, kc, vc,
+                      (int)c.n_head, (int)c.n_kv_head, s->len, (s->flags & SZ_KV_Q8) ? 1 : 0, s->attn_splits, s->a_part));
+    return SZ_OK;
+}
+
+static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
+    const sz_model_config& c = s->model.cfg;
+    const sz_layer& L = s->layers[l];
+    const int ai = s->lb[l].attn_index;
+    const int H = c.hidden, nh = c.n_head, nkv = c.n_kv_head, hd = c.head_dim;
+    const int q8 = (s->flags & SZ_KV_Q8) ? 1 : 0;
+    const int64_t hb = q8 ? (hd + (((hd >> 5) * 2 + 15) & ~15)) : 4 * (int64_t)hd;
+    const int64_t layer_bytes = (int64_t)s->ctx * nkv * hb;
+    u8 *kc = s->kc + ai * layer_bytes, *vc = s->vc + ai * layer_bytes;
+    SzDenseArgs a = {};
+    a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 3;
+    a.job[0] = sz_job(L.attn_q, s->a_qg, 2 * nh * hd);
+    a.job[1] = sz_job(L.attn_k, s->a_k, nkv * hd);
+    a.job[2] = sz_job(L.attn_v, s->a_v, nkv * hd);
+    int rc = sz_dense_launch(a, st, "attn_proj");
+    if (rc) return rc;
+    SZ_CUDA(sz_launch("attn_prep", sz_attn_prep_kernel, dim3(nh + 2 * nkv, m), dim3(128), 0, st, true, (const float*)s->a_qg, (const float*)s->a_k,
+                      (const float*)s->a_v, (const float*)L.attn_q_norm.data, (const float*)L.attn_k_norm.data, nh, nkv, hd, c.eps, s->len,
+                      (int)c.rope_dims, c.rope_theta, q8, kc, vc, s->a_q, s->a_gate));
+    if (hd == 64) rc = sz_attn_launch<2>(s, st, kc, vc, m);
+    else if (hd == 128) rc = sz_attn_launch<4>(s, st, kc, vc, m);
+    else rc = sz_attn_launch<8>(s, st, kc, vc, m);
+    if (rc) return rc;
+    SZ_CUDA(sz_launch("attn_merge", sz_attn_merge_kernel, dim3(nh, m), dim3(256), 0, st, true, (const float*)s->a_part, (const float*)s->a_gate, nh, hd,
+                      s->attn_splits, s->a_o));
+    SzDenseArgs b = {};
+    b.x = s->a_o; b.xstride = nh * hd; b.cols = nh * hd; b.m = m; b.n_jobs = 1;
+    b.job[0] = sz_job(L.attn_output, s->y, H);
+    return sz_dense_launch(b, st, "attn_output");
+}
+
+// Runs the m rows through every layer and, with `head`, through the output projection and the top-64.
+static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
+    const sz_model_config& c = s->model.cfg;
+    const int H = c.hidden, C = c.streams;
+    SZ_CUDA(sz_launch("embed", sz_embed_kernel, dim3(m), dim3(256), 0, st, false, (const int32_t*)s->ids, (const u8*)s->model.token_embd.data,
+                      (int)s->model.token_embd.type, H, C, (int)c.vocab, s->r));
+    int rc;
+    bool pending = false;
+    for (int l = 0; l < c.n_layer; l++) {
+        const sz_layer& L = s->layers[l];
+        if ((rc = sz_hc_read(s, st, L.hc_attn, m, pending, true))) return rc;
+        // g of this read is consumed by the write after the sublayer; the MoE read below overwrites s->g, so keep the order
+        rc = sz_is_attn(c, l) ? sz_attn_layer(s, st, l, m) : sz_delta_layer(s, st, l, m);
+        if (rc) return rc;
+        if ((rc = sz_hc_read(s, st, L.hc_ffn, m, true, true))) return rc;   // applies the mixer's write first
+        int32_t* ri = s->want_routes ? s->routes + (int64_t)l * SZ_MAX_VERIFY * SZ_MAX_TOPK : nullptr;
+        double* rw = s->want_routes ? s->route_w + (int64_t)l * SZ_MAX_VERIFY * SZ_MAX_TOPK : nullptr;
+        // the MoE writes its result to y, after the read has consumed the previous y
+        if ((rc = sz_moe_verify(&L.moe, (uint64_t)s->u, m, (uint64_t)s->y, (uint64_t)ri, (uint64_t)rw, (uint64_t)s->moe_scratch, s->moe_scratch_bytes,
+                                (uint64_t)st)))
+            return rc;
+        pending = true;
+    }
+    if (!head) {
+        // the last MoE write still has to reach r only if somebody reads r again; a later pass starts from the embedding, so it is dropped
+        return SZ_OK;
+    }
+    if ((rc = sz_hc_read(s, st, s->model.output_hc, m, pending, false))) return rc;
+    SzDenseArgs a = {};
+    a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 1;
+    a.job[0] = sz_job(s->model.output, s->logits, c.vocab);
+    if ((rc = sz_dense_launch(a, st, "lm_head"))) return rc;
+    const int nb = (c.vocab + SZ_TK_N - 1) / SZ_TK_N;
+    SZ_CUDA(sz_launch("topk_slices", sz_topk_slices_kernel, dim3(nb, m), dim3(256), 0, st, true, (const float*)s->logits, (int)c.vocab, (int)c.vocab, nb, s->tk_tmp));
+    SZ_CUDA(sz_launch("topk_merge", sz_topk_merge_kernel, dim3(m), dim3(256), 0, st, true, (const u64*)s->tk_tmp, nb, s->top));
+    return SZ_OK;
+}
+
+extern "C" int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode, int eog_token, int want_head, uint64_t stream) {
+    if (!s || !ids) return sz_fail(SZ_E_ARG, "null session or ids");
+    if (m < 1 || m > SZ_MAX_VERIFY) return sz_fail(SZ_E_ARG, "a pass has 1..%d rows, got %d", SZ_MAX_VERIFY, m);
+    if (s->last_m) return sz_fail(SZ_E_ARG, "the previous pass was not committed");
+    if (s->len + m > s->ctx) return sz_fail(SZ_E_ARG, "%d positions + %d rows exceed the session's capacity %d", s->len, m, s->ctx);
+    if (accept_mode == SZ_ACCEPT_GREEDY && !want_head) return sz_fail(SZ_E_ARG, "greedy acceptance needs the head");
+    cudaStream_t st = (cudaStream_t)stream;
+    memcpy(s->h_ids, ids, (size_t)m * 4);
+    SZ_CUDA(cudaMemcpyAsync(s->ids, s->h_ids, (size_t)m * 4, cudaMemcpyHostToDevice, st));
+    int rc = sz_forward(s, st, m, want_head != 0);
+    if (rc) return rc;
+    if (accept_mode != SZ_ACCEPT_NONE && want_head)
+        SZ_CUDA(sz_launch("accept", sz_accept_greedy_kernel, dim3(1), dim3(32), 0, st, true, (const u32*)s->top, (const int32_t*)s->ids, m, eog_token,
+                          accept_mode == SZ_ACCEPT_ALL ? 1 : 0, s->res));
+    s->last_m = m;
+    return SZ_OK;
+}
+
+extern "C" int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* top, float* logits, uint64_t stream) {
+    if (!s || !s->last_m) return sz_fail(SZ_E_ARG, "no pass to read");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (keep_next) SZ_CUDA(cudaMemcpyAsync(keep_next, s->res, 8, cudaMemcpyDeviceToHost, st));
+    if (top) SZ_CUDA(cudaMemcpyAsync(top, s->top, (size_t)s->last_m * 128 * 4, cudaMemcpyDeviceToHost, st));
+    if (logits) SZ_CUDA(cudaMemcpyAsync(logits, s->logits, (size_t)s->last_m * s->model.cfg.vocab * 4, cudaMemcpyDeviceToHost, st));
+    SZ_CUDA(cudaStreamSynchronize(st));
+    return SZ_OK;
+}
+
+extern "C" int sz_session_routes(sz_session* s, int32_t* idx, double* w, uint64_t stream) {
+    if (!s || !s->last_m || !s->want_routes) return sz_fail(SZ_E_ARG, "routes are recorded only after sz_session_trace_routes(1) and a pass");
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t n = (size_t)s->model.cfg.n_layer * SZ_MAX_VERIFY * SZ_MAX_TOPK;
+    if (idx) SZ_CUDA(cudaMemcpyAsync(idx, s->routes, n * 4, cudaMemcpyDeviceToHost, st));
+    if (w) SZ_CUDA(cudaMemcpyAsync(w, s->route_w, n * 8, cudaMemcpyDeviceToHost, st));
+    SZ_CUDA(cudaStreamSynchronize(st));
+    return SZ_OK;
+}
+
+// Keeps the first `keep` rows of the last pass: recurrent states of exactly those rows, conv rows, position count.
+extern "C" int sz_session_commit(sz_session* s, int keep, uint64_t stream) {
+    if (!s || !s->last_m) return sz_fail(SZ_E_ARG, "no pass to commit");
+    const int m = s->last_m;
+    if (keep < 0 || keep > m) return sz_fail(SZ_E_ARG, "keep = %d of a pass of %d rows", keep, m);
+    cudaStream_t st = (cudaStream_t)stream;
+    const sz_model_config& c = s->model.cfg;
+    s->last_m = 0;
+    if (keep == 0) return SZ_OK;  // nothing kept: the current buffers stand
+    const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd;
+    for (int l = 0; l < c.n_layer; l++) {
+        const int di = s->lb[l].delta_index;
+        if (di < 0) continue;
+        if (keep < m) {  // replay the recurrences of the kept rows from the saved inputs (the pass wrote the state after all m rows)
+            const int rc = sz_scan(s, st, "delta_replay", l, keep, false);
+            if (rc) return rc;
+        }
+        const float* xin = s->d_xin + (int64_t)di * SZ_MAX_VERIFY * ch;
+        const int64_t cl = (int64_t)(c.conv_k - 1) * ch;
+        SZ_CUDA(sz_launch("conv_commit", sz_conv_commit_kernel, dim3(c.conv_k - 1), dim3(256), 0, st, true, (const float*)(s->conv[s->cur] + di * cl), xin,
+                          (int)ch, (int)c.conv_k, keep, s->conv[s->cur ^ 1] + di * cl));
+    }
+    s->cur ^= 1;
+    s->len += keep;
+    return SZ_OK;
+}
+
+// Feeds a prompt: passes of up to 8 rows, every row kept; the head runs for the last pass only.  Afterwards sz_session_result gives the
+// top-64 (and logits) of the last pass's rows; the last row's are the prompt's.
+extern "C" int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint64_t stream) {
+    if (!s || !ids || n < 1) return sz_fail(SZ_E_ARG, "sz_session_prefill: nothing to feed");
+    int done = 0;
+    while (done < n) {
+        const int m = n - done < SZ_MAX_VERIFY ? n - done : SZ_MAX_VERIFY;
+        const bool last = done + m == n;
+        int rc = sz_session_verify(s, ids + done, m, SZ_ACCEPT_NONE, -1, last ? 1 : 0, stream);
+        if (rc) return rc;
+        if (last) { s->last_m = m; return SZ_OK; }  // left pending so the caller can read the result, then commit all m rows
+        if ((rc = sz_session_commit(s, m, stream))) return rc;
+        done += m;
+    }
+    return SZ_OK;
+}

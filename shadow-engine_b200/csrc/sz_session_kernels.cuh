@@ -1,0 +1,450 @@
+// Kernels of the verify pass other than the MoE sublayer and the dense projections: embedding rows, hyper-connection glue,
+// the DeltaNet front end and state scan, the attention front end (norm, RoPE, Q8_KV write) and the masked attention itself, the
+// top-64 of the logits and the greedy acceptance.  Arithmetic follows the CPU reference (crates/shadowzero-model/src/forward.rs);
+// sums the reference widens to f64 are f64 here too (FP64 is half rate on this part).
+#pragma once
+
+#include "sz_dense.cuh"
+
+#ifdef __CUDACC__
+
+__device__ __forceinline__ double sz_block_sum(double v, double* red) {
+    v = sz_warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    double t = 0.0;
+    for (int i = 0; i < nw; i++) t += red[i];
+    return t;
+}
+
+// ---- embedding: r[j][s][:] = row ids[j] of token_embd for every stream s (forward.rs:759-767) -----------------------------------
+__global__ void __launch_bounds__(256)
+sz_embed_kernel(const int32_t* __restrict__ ids, const u8* __restrict__ embd, int type, int H, int C, int vocab, float* __restrict__ r) {
+    __shared__ u32 grid[512];
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    for (int i = threadIdx.x; i < 512; i += 256) grid[i] = c_iq3s_grid[i];
+    __syncthreads();
+    const int j = blockIdx.x;
+    int tok = ids[j];
+    tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+    const u8* row = embd + (size_t)tok * sz_dense_row_bytes(type, H);
+    for (int e = 4 * threadIdx.x; e < H; e += 1024) {
+        float w[4], sc;
+        sz_dense_w4(type, row, e, grid, w, sc);
+        const float4 v = make_float4(sc * w[0], sc * w[1], sc * w[2], sc * w[3]);
+        for (int s = 0; s < C; s++) *(float4*)(r + ((size_t)j * C + s) * H + e) = v;
+    }
+}
+
+// ---- hyper-connection: (pending write) r[s] += g[s] * y, then rn[s] = rmsnorm(r[s]) * w[s] (forward.rs:801,1078-1084) ----------
+// grid (C, m)
+__global__ void __launch_bounds__(256)
+sz_hc_norm_kernel(float* __restrict__ r, const float* __restrict__ g, const float* __restrict__ y, const float* __restrict__ w, int H,
+                  int C, float eps, float* __restrict__ rn) {
+    __shared__ double red[8];
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int s = blockIdx.x, j = blockIdx.y;
+    float* rs = r + ((size_t)j * C + s) * H;
+    const float gs = g ? g[j * C + s] : 0.f;
+    double ss = 0.0;
+    for (int i = threadIdx.x; i < H; i += 256) {
+        float v = rs[i];
+        if (y) { v = v + gs * y[(size_t)j * H + i]; rs[i] = v; }
+        ss += (double)v * (double)v;
+    }
+    ss = sz_block_sum(ss, red);
+    const double rr = 1.0 / sqrt(ss / (double)H + (double)eps);
+    for (int i = threadIdx.x; i < H; i += 256) rn[((size_t)j * C + s) * H + i] = (float)((double)rs[i] * rr) * w[s * H + i];
+}
+
+// u[i] = (sum over streams of mix[s][i] * rn[s][i]) / C in f32, stream order (forward.rs:805-811).  grid (ceil(H / 256), m)
+__global__ void __launch_bounds__(256)
+sz_hc_mix_kernel(const float* __restrict__ mix, const float* __restrict__ rn, int H, int C, float* __restrict__ u) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int i = blockIdx.x * 256 + threadIdx.x, j = blockIdx.y;
+    if (i >= H) return;
+    float a = 0.f;
+    for (int s = 0; s < C; s++) a += mix[((size_t)j * C + s) * H + i] * rn[((size_t)j * C + s) * H + i];
+    u[(size_t)j * H + i] = a / (float)C;
+}
+
+// ---- DeltaNet front end (forward.rs:829-861): causal conv (k taps) + SiLU over the rows of the pass, L2 norm of q and k heads,
+// beta and decay.  grid (m), block 256.  conv: (k-1) x ch, oldest first: the state BEFORE the pass.  xin: [m][ch] raw projections.
+__global__ void __launch_bounds__(256)
+sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ conv, const float* __restrict__ cw, const float* __restrict__ b,
+                     const float* __restrict__ a, const float* __restrict__ a_log, const float* __restrict__ dt, int kh, int vh, int d, int k,
+                     float* __restrict__ xc, float* __restrict__ beta, float* __restrict__ decay) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int j = blockIdx.x;
+    const int kd = kh * d, ch = 2 * kd + vh * d;
+    for (int i = threadIdx.x; i < ch; i += 256) {
+        double acc = (double)cw[i * k + (k - 1)] * (double)xin[(size_t)j * ch + i];
+        for (int t = 0; t < k - 1; t++) {
+            const int tau = j - (k - 1) + t;  // row of this pass, or (negative) a row of the carried state
+            const float prev = tau >= 0 ? xin[(size_t)tau * ch + i] : conv[(size_t)((k - 1) + tau) * ch + i];
+            acc += (double)cw[i * k + t] * (double)prev;
+        }
+        xc[(size_t)j * ch + i] = sz_silu((float)acc);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int hq = warp; hq < 2 * kh; hq += 8) {  // heads 0..kh-1: q (also / sqrt(d)); kh..2kh-1: k
+        float* v = xc + (size_t)j * ch + (size_t)hq * d;
+        double ss = 0.0;
+        for (int i = lane; i < d; i += 32) ss += (double)v[i] * (double)v[i];
+        ss = sz_warp_sum(ss);
+        const double n = 1.0 / sqrt(ss + 1e-6);
+        const float sq = sqrtf((float)d);
+        for (int i = lane; i < d; i += 32) {
+            float t = (float)((double)v[i] * n);
+            if (hq < kh) t = t / sq;
+            v[i] = t;
+        }
+    }
+    for (int h = threadIdx.x; h < vh; h += 256) {
+        beta[j * vh + h] = sz_sigmoid(b[j * vh + h]);
+        const float sp_in = a[j * vh + h] + dt[h];
+        const float sp = sp_in > 20.0f ? sp_in : (float)log1p(exp((double)sp_in));
+        decay[j * vh + h] = (float)exp((double)a_log[h] * (double)sp);
+    }
+}
+
+// The carried conv rows after `keep` rows of the pass: the last k-1 of [state rows ; xin rows 0..keep-1].  grid (k-1), block 256
+__global__ void __launch_bounds__(256)
+sz_conv_commit_kernel(const float* __restrict__ conv, const float* __restrict__ xin, int ch, int k, int keep, float* __restrict__ conv_next) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int t = blockIdx.x;              // row of the new state, oldest first
+    const int tau = keep - (k - 1) + t;    // index into the pass rows, negative: into the old state
+    const float* src = tau >= 0 ? xin + (size_t)tau * ch : conv + (size_t)((k - 1) + tau) * ch;
+    for (int i = threadIdx.x; i < ch; i += 256) conv_next[(size_t)t * ch + i] = src[i];
+}
+
+// ---- DeltaNet state scan (forward.rs:859-894): per value head, the d x d state column-resident in registers.
+// Thread (col = tid % D, part = tid / D) holds S[i][col] for the i of its part.  grid (vh), block D * PARTS.
+// rows: how many rows of the pass to apply; S_in -> S_out; with `og` != null also writes the gated, normalised outputs.
+template <int D, int PARTS>
+__global__ void __launch_bounds__(D * PARTS)
+sz_delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ beta, const float* __restrict__ decay, const float* __restrict__ z,
+                     const float* __restrict__ norm_w, const float* __restrict__ S_in, float* __restrict__ S_out, int kh, int vh, int rows,
+                     float eps, float* __restrict__ og) {
+    constexpr int NI = D / PARTS;
+    __shared__ float sk[D], sq[D];
+    __shared__ double part[PARTS][D];
+    __shared__ double red[8];
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int hd = blockIdx.x;
+    const int col = threadIdx.x % D, pt = threadIdx.x / D;
+    const int kx = hd % kh;  // value heads are tiled over the key heads (forward.rs:862-864)
+    const int kd = kh * D, ch = 2 * kd + vh * D;
+    float S[NI];
+    const float* Sg = S_in + (size_t)hd * D * D;
+#pragma unroll
+    for (int i = 0; i < NI; i++) S[i] = Sg[(size_t)(pt * NI + i) * D + col];
+    for (int j = 0; j < rows; j++) {
+        const float* x = xc + (size_t)j * ch;
+        __syncthreads();
+        if (threadIdx.x < D) { sq[threadIdx.x] = x[kx * D + threadIdx.x]; sk[threadIdx.x] = x[kd + kx * D + threadIdx.x]; }
+        __syncthreads();
+        const float dc = decay[j * vh + hd], bt = beta[j * vh + hd];
+        double mem = 0.0;
+#pragma unroll
+        for (int i = 0; i < NI; i++) {
+            S[i] = S[i] * dc;
+            mem += (double)S[i] * (double)sk[pt * NI + i];
+        }
+        part[pt][col] = mem;
+        __syncthreads();
+        double tot = 0.0;
+#pragma unroll
+        for (int p = 0; p < PARTS; p++) tot += part[p][col];
+        const float dl = (float)(((double)x[2 * kd + hd * D + col] - tot) * (double)bt);
+        double o = 0.0;
+#pragma unroll
+        for (int i = 0; i < NI; i++) {
+            S[i] = __fadd_rn(S[i], __fmul_rn(sk[pt * NI + i], dl));  // unfused, as the reference
+            o += (double)S[i] * (double)sq[pt * NI + i];
+        }
+        if (og) {
+            __syncthreads();
+            part[pt][col] = o;
+            __syncthreads();
+            double ot = 0.0;
+#pragma unroll
+            for (int p = 0; p < PARTS; p++) ot += part[p][col];
+            const float of = (float)ot;
+            const double ss = sz_block_sum(pt == 0 ? (double)of * (double)of : 0.0, red);
+            if (pt == 0) {
+                const double rr = 1.0 / sqrt(ss / (double)D + (double)eps);
+                const float normed = (float)((double)of * rr) * norm_w[col];
+                og[(size_t)j * vh * D + hd * D + col] = normed * sz_sigmoid(z[(size_t)j * vh * D + hd * D + col]);
+            }
+        }
+    }
+    float* So = S_out + (size_t)hd * D * D;
+#pragma unroll
+    for (int i = 0; i < NI; i++) So[(size_t)(pt * NI + i) * D + col] = S[i];
+}
+
+// ---- attention front end (forward.rs:908-927): per head RMSNorm + NeoX RoPE of q and k, the gate halves, K and V into the cache.
+// grid (nh + 2 nkv, m), block 128.  Q8 cache rows: [pos][nkv][hd i8 | hd/32 f16 scales, zero-padded to 16 bytes] (the reference's
+// packed Q8_KV, kernels/forward.cu:3652-3687); f32 cache rows: [pos][nkv][hd].
+__device__ __forceinline__ int sz_kv_head_bytes(int hd) { return hd + (((hd >> 5) * 2 + 15) & ~15); }
+
+__device__ __forceinline__ void sz_kv_store(const float* src, int hd, int q8, u8* dst_q8, float* dst_f32) {
+    if (!q8) {
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) dst_f32[i] = src[i];
+        return;
+    }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5, ng = hd >> 5;
+    u16* sc = (u16*)(dst_q8 + hd);
+    for (int grp = warp; grp < ng; grp += nw) {
+        const float v0 = src[grp * 32 + lane];
+        float amax = fabsf(v0);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        const __half sh = __float2half_rn(amax > 0.0f ? amax * (1.0f / 127.0f) : 0.0f);
+        const float sr = __half2float(sh);
+        const float inv = sr > 0.0f ? (1.0f / sr) : 0.0f;
+        int q0 = __float2int_rn(v0 * inv);
+        q0 = q0 < -127 ? -127 : (q0 > 127 ? 127 : q0);
+        ((int8_t*)dst_q8)[grp * 32 + lane] = (int8_t)q0;
+        if (lane == 0) sc[grp] = __half_as_ushort(sh);
+    }
+    const int total = (sz_kv_head_bytes(hd) - hd) >> 1;
+    for (int u = ng + threadIdx.x; u < total; u += blockDim.x) sc[u] = 0;
+}
+
+__global__ void __launch_bounds__(128)
+sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, const float* __restrict__ vv, const float* __restrict__ wq,
+                    const float* __restrict__ wk, int nh, int nkv, int hd, float eps, int pos0, int rope_dims, double theta, int q8,
+                    u8* __restrict__ kc, u8* __restrict__ vc, float* __restrict__ q, float* __restrict__ gate) {
+    __shared__ float tmp[512];
+    __shared__ double red[8];
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int b = blockIdx.x, j = blockIdx.y;
+    const int pos = pos0 + j;
+    const size_t row_q8 = (size_t)nkv * sz_kv_head_bytes(hd), row_f = (size_t)nkv * hd * 4;
+    if (b >= nh + nkv) {  // V head: raw into the cache
+        const int h = b - nh - nkv;
+        u8* dst = vc + (size_t)pos * (q8 ? row_q8 : row_f) + (size_t)h * (q8 ? sz_kv_head_bytes(hd) : hd * 4);
+        sz_kv_store(vv + ((size_t)j * nkv + h) * hd, hd, q8, dst, (float*)dst);
+        return;
+    }
+    const bool isq = b < nh;
+    const float* x = isq ? qg + ((size_t)j * nh + b) * 2 * hd : kk + ((size_t)j * nkv + (b - nh)) * hd;
+    const float* w = isq ? wq : wk;
+    double ss = 0.0;
+    for (int i = threadIdx.x; i < hd; i += 128) ss += (double)x[i] * (double)x[i];
+    ss = sz_block_sum(ss, red);
+    const double rr = 1.0 / sqrt(ss / (double)hd + (double)eps);
+    for (int i = threadIdx.x; i < hd; i += 128) tmp[i] = (float)((double)x[i] * rr) * w[i];
+    __syncthreads();
+    const int half = rope_dims / 2;
+    for (int i = threadIdx.x; i < half; i += 128) {  // forward.rs:290-299
+        const double f = (double)pos / pow(theta, 2.0 * (double)i / (double)rope_dims);
+        const double cs = cos(f), sn = sin(f);
+        const double a0 = (double)tmp[i], b0 = (double)tmp[i + half];
+        tmp[i] = (float)(a0 * cs - b0 * sn);
+        tmp[i + half] = (float)(b0 * cs + a0 * sn);
+    }
+    __syncthreads();
+    if (isq) {
+        for (int i = threadIdx.x; i < hd; i += 128) {
+            q[((size_t)j * nh + b) * hd + i] = tmp[i];
+            gate[((size_t)j * nh + b) * hd + i] = x[hd + i];
+        }
+    } else {
+        const int h = b - nh;
+        u8* dst = kc + (size_t)pos * (q8 ? row_q8 : row_f) + (size_t)h * (q8 ? sz_kv_head_bytes(hd) : hd * 4);
+        sz_kv_store(tmp, hd, q8, dst, (float*)dst);
+    }
+}
+
+// ---- masked attention over the cache (forward.rs:978-997): row j of the pass attends to positions 0 .. pos0 + j.
+// grid (nh, m, splits), block 256: a warp a position at a time, lane owns hd / 32 consecutive dimensions; online softmax per warp,
+// merged per block; partial (max, sum, acc[hd]) per split.  part: [m][nh][splits][hd + 2].
+template <int EPL>  // elements per lane = hd / 32
+__global__ void __launch_bounds__(256)
+sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8* __restrict__ vc, int nh, int nkv, int pos0, int q8,
+               int splits, float* __restrict__ part) {
+    constexpr int HD = EPL * 32;
+    __shared__ float sm_m[8], sm_s[8];
+    __shared__ float sm_acc[8][HD];
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int h = blockIdx.x, j = blockIdx.y, sp = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = h / (nh / nkv);
+    const int n = pos0 + j + 1;
+    const int per = (n + splits - 1) / splits;
+    const int t0 = sp * per, t1 = min(n, t0 + per);
+    const int hb = sz_kv_head_bytes(HD);
+    const size_t rowb = (size_t)nkv * (q8 ? hb : HD * 4), headb = (size_t)g * (q8 ? hb : HD * 4);
+    float qv[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; e++) qv[e] = q[((size_t)j * nh + h) * HD + lane * EPL + e];
+    const float scale = rsqrtf((float)HD);
+    float mx = -INFINITY, sum = 0.f, acc[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; e++) acc[e] = 0.f;
+    for (int t = t0 + warp; t < t1; t += 8) {
+        const u8* kb = kc + (size_t)t * rowb + headb;
+        const u8* vb = vc + (size_t)t * rowb + headb;
+        float kvv[EPL], vvv[EPL];
+        if (q8) {
+            const float ks = sz_f16_to_f32(*(const u16*)(kb + HD + 2 * ((lane * EPL) >> 5)));
+            const float vs = sz_f16_to_f32(*(const u16*)(vb + HD + 2 * ((lane * EPL) >> 5)));
+#pragma unroll
+            for (int e = 0; e < EPL; e++) {
+                kvv[e] = (float)((const int8_t*)kb)[lane * EPL + e] * ks;
+                vvv[e] = (float)((const int8_t*)vb)[lane * EPL + e] * vs;
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < EPL; e++) { kvv[e] = ((const float*)kb)[lane * EPL + e]; vvv[e] = ((const float*)vb)[lane * EPL + e]; }
+        }
+        float s = 0.f;
+#pragma unroll
+        for (int e = 0; e < EPL; e++) s = fmaf(qv[e], kvv[e], s);
+        s = sz_warp_sum(s) * scale;
+        const float nm = fmaxf(mx, s);
+        const float c = __expf(mx - nm), p = __expf(s - nm);
+        sum = sum * c + p;
+#pragma unroll
+        for (int e = 0; e < EPL; e++) acc[e] = fmaf(p, vvv[e], acc[e] * c);
+        mx = nm;
+    }
+    if (lane == 0) { sm_m[warp] = mx; sm_s[warp] = sum; }
+#pragma unroll
+    for (int e = 0; e < EPL; e++) sm_acc[warp][lane * EPL + e] = acc[e];
+    __syncthreads();
+    float M = -INFINITY;
+    for (int w = 0; w < 8; w++) M = fmaxf(M, sm_m[w]);
+    float* out = part + (((size_t)j * nh + h) * splits + sp) * (HD + 2);
+    if (threadIdx.x < HD) {
+        float a = 0.f, ssum = 0.f;
+        for (int w = 0; w < 8; w++) {
+            const float c = sm_m[w] == -INFINITY ? 0.f : __expf(sm_m[w] - M);
+            a += sm_acc[w][threadIdx.x] * c;
+            ssum += sm_s[w] * c;
+        }
+        out[threadIdx.x] = a;
+        if (threadIdx.x == 0) { out[HD] = M; out[HD + 1] = ssum; }
+    }
+}
+
+// merge the splits and gate: o = (acc / z) * sigmoid(gate).  grid (nh, m), block 256
+__global__ void __launch_bounds__(256)
+sz_attn_merge_kernel(const float* __restrict__ part, const float* __restrict__ gate, int nh, int hd, int splits, float* __restrict__ o) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int h = blockIdx.x, j = blockIdx.y;
+    const float* p = part + ((size_t)j * nh + h) * splits * (hd + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; s++) M = fmaxf(M, p[(size_t)s * (hd + 2) + hd]);
+    for (int i = threadIdx.x; i < hd; i += 256) {
+        float a = 0.f, z = 0.f;
+        for (int s = 0; s < splits; s++) {
+            const float mm = p[(size_t)s * (hd + 2) + hd];
+            const float c = mm == -INFINITY ? 0.f : __expf(mm - M);
+            a += p[(size_t)s * (hd + 2) + i] * c;
+            z += p[(size_t)s * (hd + 2) + hd + 1] * c;
+        }
+        o[((size_t)j * nh + h) * hd + i] = (a / z) * sz_sigmoid(gate[((size_t)j * nh + h) * hd + i]);
+    }
+}
+
+// ---- top-64 of each row of logits: largest first, ties to the lower id, NaN as -inf (the order of kernels/forward.cu:3565-3625).
+// A key packs (orderable value bits, ~id) so that one 64-bit descending sort gives that order.
+#define SZ_TK_N 4096
+__device__ __forceinline__ u64 sz_tk_key(float v, u32 id) {
+    if (v != v) v = -INFINITY;
+    u32 b = __float_as_uint(v);
+    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((u64)b << 32) | (u64)(0xffffffffu - id);
+}
+__device__ __forceinline__ void sz_tk_unkey(u64 k, float& v, u32& id) {
+    u32 b = (u32)(k >> 32);
+    b = (b & 0x80000000u) ? (b & 0x7fffffffu) : ~b;
+    v = __uint_as_float(b);
+    id = 0xffffffffu - (u32)k;
+}
+__device__ __forceinline__ void sz_tk_sort(u64* sk) {  // bitonic, descending, SZ_TK_N keys, 256 threads
+    for (u32 k = 2; k <= SZ_TK_N; k <<= 1)
+        for (u32 jj = k >> 1; jj > 0; jj >>= 1) {
+            for (u32 t = threadIdx.x; t < SZ_TK_N; t += 256) {
+                const u32 l = t ^ jj;
+                if (l > t) {
+                    const bool up = (t & k) == 0;
+                    const u64 a = sk[t], b = sk[l];
+                    if (up ? (b > a) : (a > b)) { sk[t] = b; sk[l] = a; }
+                }
+            }
+            __syncthreads();
+        }
+}
+// grid (nb, m): slice blk of row j -> its 64 best keys at tmp[(j * nb + blk) * 64]
+__global__ void __launch_bounds__(256)
+sz_topk_slices_kernel(const float* __restrict__ logits, int vocab, int ls, int nb, u64* __restrict__ tmp) {
+    __shared__ u64 sk[SZ_TK_N];
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int blk = blockIdx.x, j = blockIdx.y;
+    const float* r = logits + (size_t)j * ls;
+    for (int t = threadIdx.x; t < SZ_TK_N; t += 256) {
+        const int i = blk * SZ_TK_N + t;
+        sk[t] = i < vocab ? sz_tk_key(r[i], (u32)i) : sz_tk_key(-INFINITY, 0xffffffffu);
+    }
+    __syncthreads();
+    sz_tk_sort(sk);
+    for (int t = threadIdx.x; t < 64; t += 256) tmp[((size_t)j * nb + blk) * 64 + t] = sk[t];
+}
+// grid (m): out row j = 64 value bit patterns then 64 ids (crates/shadowzero-cuda/src/session.rs:6034-6039)
+__global__ void __launch_bounds__(256)
+sz_topk_merge_kernel(const u64* __restrict__ tmp, int nb, u32* __restrict__ out) {
+    __shared__ u64 sk[SZ_TK_N];
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int j = blockIdx.x;
+    for (int t = threadIdx.x; t < SZ_TK_N; t += 256) sk[t] = t < nb * 64 ? tmp[(size_t)j * nb * 64 + t] : sz_tk_key(-INFINITY, 0xffffffffu);
+    __syncthreads();
+    sz_tk_sort(sk);
+    for (int t = threadIdx.x; t < 64; t += 256) {
+        float v; u32 id;
+        sz_tk_unkey(sk[t], v, id);
+        out[(size_t)j * 128 + t] = __float_as_uint(v);
+        out[(size_t)j * 128 + 64 + t] = id;
+    }
+}
+
+// ---- greedy acceptance on the device (the host loop of crates/shadowzero-serve/src/engine.rs:2377-2408 for the greedy case):
+// row i's best token must equal the next drafted token ids[i + 1]; a drafted end-of-generation token is never accepted.
+// res[0] = rows kept (1 .. m), res[1] = the token after the kept rows (best of row keep - 1).
+__global__ void sz_accept_greedy_kernel(const u32* __restrict__ top, const int32_t* __restrict__ ids, int m, int eog, int keep_all,
+                                        int32_t* __restrict__ res) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int keep = 1;
+    if (keep_all) keep = m;
+    else
+        for (int i = 0; i + 1 < m; i++) {
+            const int want = (int)top[(size_t)i * 128 + 64];
+            const int d = ids[i + 1];
+            if (want != d || d == eog) break;
+            keep++;
+        }
+    res[0] = keep;
+    res[1] = (int)top[(size_t)(keep - 1) * 128 + 64];
+}
+
+#endif  // __CUDACC__

@@ -47,6 +47,41 @@ SYMBOLS = {
     "sz_moe_verify_host": (C.c_int, [C.POINTER(MoeLayerC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_uint64, C.c_uint64, C.c_uint64, C.c_int64, C.c_uint64]),
     "sz_moe_launches": (C.c_int, [C.POINTER(MoeLayerC)]),
+    # the session (struct pointers are passed with ctypes.byref, so they are declared as void pointers here)
+    "sz_session_bytes": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int64)]),
+    "sz_session_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_uint64, C.c_int64, C.c_uint64, C.POINTER(C.c_void_p)]),
+    "sz_session_destroy": (None, [C.c_void_p]),
+    "sz_session_reset": (C.c_int, [C.c_void_p, C.c_uint64]),
+    "sz_session_len": (C.c_int, [C.c_void_p]),
+    "sz_session_capacity": (C.c_int, [C.c_void_p]),
+    "sz_session_prefill": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64]),
+    "sz_session_verify": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64]),
+    "sz_session_result": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_uint64]),
+    "sz_session_commit": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
+    "sz_session_trace_routes": (C.c_int, [C.c_void_p, C.c_int]),
+    "sz_session_routes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64]),
+    # host side of speculation
+    "sz_lookup": (C.c_int, [C.POINTER(C.c_uint32), C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_uint32)]),
+    "sz_drafter_new": (C.c_void_p, [C.c_int, C.c_int, C.c_int]),
+    "sz_drafter_free": (None, [C.c_void_p]),
+    "sz_drafter_push": (None, [C.c_void_p, C.c_uint32]),
+    "sz_drafter_extend": (None, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int]),
+    "sz_drafter_len": (C.c_int, [C.c_void_p]),
+    "sz_drafter_propose": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int)]),
+    "sz_drafter_propose_with_min": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int)]),
+    "sz_drafter_propose_after": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int)]),
+    "sz_policy_new": (C.c_void_p, [C.c_int, C.c_int, C.c_double]),
+    "sz_policy_free": (None, [C.c_void_p]),
+    "sz_policy_accept_ema": (C.c_double, [C.c_void_p]),
+    "sz_policy_neural_k": (C.c_int, [C.c_void_p, C.c_int]),
+    "sz_policy_choose": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int)]),
+    "sz_policy_chain": (C.c_int, [C.c_void_p, C.c_int, C.c_double, C.c_int, C.c_int]),
+    "sz_policy_observe": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double]),
+    "sz_policy_observe_chain": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double]),
+    "sz_uniform": (C.c_double, [C.c_uint64, C.c_uint64]),
+    "sz_sample_top": (C.c_uint32, [C.c_void_p, C.POINTER(C.c_uint32), C.c_uint64]),
+    "sz_generate": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.c_int,
+                              C.c_void_p, C.c_uint64]),
     "sz_moe_static_scratch_max": (C.c_int, [C.POINTER(C.c_int64)]),
     "sz_moe_verify_static": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
 }

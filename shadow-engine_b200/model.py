@@ -1,0 +1,337 @@
+"""The model description (struct sz_model) from Python: ctypes mirrors of the header's structs, seeded synthetic models with the
+reference's tensor names (crates/shadowzero-model/src/exl3_model.rs:223-243), and the two placements of one model - host memory
+for the CPU oracle, HBM for the library."""
+import ctypes as C
+
+import numpy as np
+import torch
+
+from . import lib as szlib
+from . import moe as szmoe
+from . import synth
+
+
+class Tensor(C.Structure):
+    _fields_ = [("type", C.c_int32), ("reserved", C.c_int32), ("data", C.c_uint64), ("rows", C.c_int64), ("cols", C.c_int64)]
+
+
+class ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_layer", "hidden", "streams", "hc_rank", "vocab", "n_head", "n_kv_head", "head_dim", "rope_dims",
+                                         "n_expert", "n_expert_used", "expert_ff", "shared_ff", "ssm_k_heads", "ssm_v_heads", "ssm_head_dim",
+                                         "conv_k", "attn_interval")] + [("eps", C.c_float), ("reserved", C.c_float), ("rope_theta", C.c_double)]
+
+
+class Hc(C.Structure):
+    _fields_ = [("norm", Tensor), ("down", Tensor), ("up", Tensor), ("inject", Tensor)]
+
+
+class Layer(C.Structure):
+    _fields_ = [("hc_attn", Hc), ("hc_ffn", Hc)] + \
+               [(n, Tensor) for n in ("attn_qkv", "attn_gate", "ssm_beta", "ssm_alpha", "ssm_conv1d", "ssm_a", "ssm_dt_bias", "ssm_norm", "ssm_out",
+                                      "attn_q", "attn_k", "attn_v", "attn_q_norm", "attn_k_norm", "attn_output")] + [("moe", szlib.MoeLayerC)]
+
+
+class Model(C.Structure):
+    _fields_ = [("cfg", ModelConfig), ("token_embd", Tensor), ("output", Tensor), ("output_hc", Hc), ("layers", C.POINTER(Layer))]
+
+
+class Sampler(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("top_k", C.c_int32), ("top_p", C.c_float), ("min_p", C.c_float), ("seed", C.c_uint64)]
+
+
+class GenParams(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("spec_k", "max_new", "lookup_min", "greedy", "eog_token", "device_accept")] + [("sampler", Sampler)]
+
+
+class GenStats(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_tokens", "passes", "drafted", "accepted", "lookup_passes", "reserved")] + \
+               [("pos_tried", C.c_int32 * 8), ("pos_right", C.c_int32 * 8), ("draft_ms", C.c_double), ("verify_ms", C.c_double), ("commit_ms", C.c_double)]
+
+
+# BASELINE config 1: the CPU-runnable tiny hybrid MoE (4 layers D D D A; hidden 512; 8 q / 2 kv heads of 64; DeltaNet 4 heads of 64;
+# 32 experts top-4 of FFN 256 + a shared expert of FFN 512; vocab 32000), with the reference's hyper-connections as block glue
+# (4 streams, rank = streams * hidden / 32 as in its checkpoints, docs/ARCH.md:79-80).
+TINY = dict(n_layer=4, hidden=512, streams=4, hc_rank=64, vocab=32000, n_head=8, n_kv_head=2, head_dim=64, rope_dims=32, n_expert=32,
+            n_expert_used=4, expert_ff=256, shared_ff=512, ssm_k_heads=4, ssm_v_heads=4, ssm_head_dim=64, conv_k=4, attn_interval=4,
+            eps=1e-6, rope_theta=1e7)
+
+
+def is_attention(cfg, l):
+    return l % cfg["attn_interval"] == cfg["attn_interval"] - 1
+
+
+def token_cycles(vocab, seed, cycle=16):
+    """A seeded permutation of the vocabulary made of cycles of `cycle` tokens: successor[t] is the token after t in its cycle."""
+    g = torch.Generator().manual_seed(seed * 7919 + 13)
+    order = torch.randperm(vocab, generator=g)
+    n = vocab // cycle * cycle
+    succ = torch.arange(vocab)
+    grp = order[:n].reshape(-1, cycle)
+    succ[grp.reshape(-1)] = torch.roll(grp, -1, dims=1).reshape(-1)
+    return succ, grp
+
+
+def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, shared_type=None, hc_type=szlib.TYPE_BF16, seed=1,
+               sigma=0.02, device="cpu", cycle=16, cycle_alpha=0.0):
+    """Seeded synthetic weights: name -> (ggml type, rows, cols, torch tensor of the stored bytes).  Matrices are N(0, sigma)
+    quantised to their type, norm weights are 1, ssm_a is negative, MoE layers come from synth.make_moe_layer.
+
+    A random-init model never repeats itself, so a suffix drafter would have nothing to draft.  With cycle_alpha > 0 the output
+    matrix is correlated with the embedding through a seeded permutation of the vocabulary made of `cycle`-token cycles
+    (row successor[t] of output.weight = alpha * embedding[t] + sqrt(1 - alpha^2) * noise: still N(0, sigma) entries): the model
+    leans towards continuing the cycle of its last token, while the layers' contribution makes it leave the cycle now and then -
+    repeated n-grams with occasional surprises, which is what speculation is measured on."""
+    shared_type = expert_type if shared_type is None else shared_type
+    H, Cs = cfg["hidden"], cfg["streams"]
+    CH = Cs * H
+    kd, vd = cfg["ssm_k_heads"] * cfg["ssm_head_dim"], cfg["ssm_v_heads"] * cfg["ssm_head_dim"]
+    ch = 2 * kd + vd
+    qd, kvd = cfg["n_head"] * cfg["head_dim"], cfg["n_kv_head"] * cfg["head_dim"]
+    T = {}
+
+    def mat(name, rows, cols, ty):
+        w = synth.normal((rows, cols), sigma, seed, name, device)
+        if ty == szlib.TYPE_F32:
+            b = w
+        elif ty == szlib.TYPE_BF16:
+            b = w.to(torch.bfloat16)
+        elif ty == szlib.TYPE_F16:
+            b = w.to(torch.float16)
+        elif ty == szlib.TYPE_Q8_0:
+            b = synth.quantize_q8_0(w)
+        elif ty == szlib.TYPE_IQ3_S:
+            b = synth.quantize_iq3_s(w)
+        else:
+            raise ValueError(ty)
+        T[name] = (ty, rows, cols, b.contiguous())
+
+    def vec(name, values):
+        T[name] = (szlib.TYPE_F32, 1, values.numel(), values.to(torch.float32).contiguous())
+
+    def hc(prefix, inject):
+        vec(prefix + "_norm.weight", torch.ones(CH, device=device))
+        mat(prefix + "_down.weight", cfg["hc_rank"], CH, hc_type)
+        mat(prefix + "_up.weight", CH, cfg["hc_rank"], hc_type)
+        if inject:
+            mat(prefix + "_inject.weight", Cs, CH, hc_type)
+
+    if cycle_alpha > 0.0:
+        # embedding rows 15x larger than the matrices' sigma, so that the token's identity is not drowned by the sublayers' outputs
+        emb = synth.normal((cfg["vocab"], H), 15.0 * sigma, seed, "token_embd.weight", device)
+        T["token_embd.weight"] = (dense_type, cfg["vocab"], H, (synth.quantize_q8_0(emb) if dense_type == szlib.TYPE_Q8_0 else emb).contiguous())
+        noise = synth.normal((cfg["vocab"], H), sigma, seed, "output.weight", device)
+        succ, _ = token_cycles(cfg["vocab"], seed, cycle)
+        w = torch.empty_like(emb)
+        w[succ.to(emb.device)] = cycle_alpha * (emb / 15.0) + (1.0 - cycle_alpha ** 2) ** 0.5 * noise
+        if dense_type == szlib.TYPE_Q8_0:
+            T["output.weight"] = (dense_type, cfg["vocab"], H, synth.quantize_q8_0(w).contiguous())
+        elif dense_type == szlib.TYPE_F32:
+            T["output.weight"] = (dense_type, cfg["vocab"], H, w.contiguous())
+        else:
+            raise ValueError("cycle_alpha needs a Q8_0 or F32 head")
+    else:
+        mat("token_embd.weight", cfg["vocab"], H, dense_type)
+        mat("output.weight", cfg["vocab"], H, dense_type)
+    hc("output_hc", False)
+    moe_layers = []
+    for l in range(cfg["n_layer"]):
+        p = "blk.%d." % l
+        hc(p + "hc_attn", True)
+        hc(p + "hc_ffn", True)
+        if is_attention(cfg, l):
+            mat(p + "attn_q.weight", 2 * qd, H, dense_type)
+            mat(p + "attn_k.weight", kvd, H, dense_type)
+            mat(p + "attn_v.weight", kvd, H, dense_type)
+            mat(p + "attn_output.weight", H, qd, dense_type)
+            vec(p + "attn_q_norm.weight", torch.ones(cfg["head_dim"], device=device))
+            vec(p + "attn_k_norm.weight", torch.ones(cfg["head_dim"], device=device))
+        else:
+            mat(p + "attn_qkv.weight", ch, H, dense_type)
+            mat(p + "attn_gate.weight", vd, H, dense_type)
+            mat(p + "ssm_beta.weight", cfg["ssm_v_heads"], H, dense_type)
+            mat(p + "ssm_alpha.weight", cfg["ssm_v_heads"], H, dense_type)
+            mat(p + "ssm_out.weight", H, vd, dense_type)
+            vec(p + "ssm_conv1d.weight", synth.normal((ch, cfg["conv_k"]), 0.3, seed, p + "ssm_conv1d", device).reshape(-1))
+            vec(p + "ssm_a", -(0.5 + torch.rand(cfg["ssm_v_heads"], generator=synth._gen(seed, p + "ssm_a", device), device=device)))
+            vec(p + "ssm_dt.bias", synth.normal((cfg["ssm_v_heads"],), 0.1, seed, p + "ssm_dt", device))
+            vec(p + "ssm_norm.weight", torch.ones(cfg["ssm_head_dim"], device=device))
+        moe_layers.append(synth.make_moe_layer(H, cfg["n_expert"], cfg["n_expert_used"], cfg["expert_ff"], cfg["shared_ff"], expert_type,
+                                               shared_type, seed=seed + 1000 * (l + 1), sigma=sigma, router_sigma=sigma, device=device,
+                                               name=p.rstrip(".")))
+    return dict(cfg=dict(cfg), tensors=T, moe=moe_layers)
+
+
+def _fill_config(c, cfg):
+    for k, v in cfg.items():
+        setattr(c, k, v)
+
+
+class _Placed:
+    """Common part of the two placements: builds struct sz_model from a `put(tensor) -> address` callback."""
+
+    def _build(self, M, put, put_moe):
+        cfg = M["cfg"]
+        self.cfg = cfg
+        self.model = Model()
+        _fill_config(self.model.cfg, cfg)
+        T = M["tensors"]
+
+        def tens(name):
+            ty, rows, cols, b = T[name]
+            t = Tensor()
+            t.type, t.rows, t.cols, t.data = ty, rows, cols, put(b)
+            return t
+
+        def hc(prefix, inject):
+            h = Hc()
+            h.norm, h.down, h.up = tens(prefix + "_norm.weight"), tens(prefix + "_down.weight"), tens(prefix + "_up.weight")
+            if inject:
+                h.inject = tens(prefix + "_inject.weight")
+            return h
+
+        self.model.token_embd, self.model.output, self.model.output_hc = tens("token_embd.weight"), tens("output.weight"), hc("output_hc", False)
+        self.layers = (Layer * cfg["n_layer"])()
+        for l in range(cfg["n_layer"]):
+            p = "blk.%d." % l
+            L = self.layers[l]
+            L.hc_attn, L.hc_ffn = hc(p + "hc_attn", True), hc(p + "hc_ffn", True)
+            if is_attention(cfg, l):
+                for n in ("attn_q", "attn_k", "attn_v", "attn_output", "attn_q_norm", "attn_k_norm"):
+                    setattr(L, n, tens(p + n + ".weight"))
+            else:
+                for n in ("attn_qkv", "attn_gate", "ssm_beta", "ssm_alpha", "ssm_out", "ssm_conv1d", "ssm_norm"):
+                    setattr(L, n, tens(p + n + ".weight"))
+                L.ssm_a, L.ssm_dt_bias = tens(p + "ssm_a"), tens(p + "ssm_dt.bias")
+            L.moe = put_moe(M["moe"][l])
+        self.model.layers = C.cast(self.layers, C.POINTER(Layer))
+
+
+class HostModel(_Placed):
+    """The model in host memory: what `oracle.binding` sessions take."""
+
+    def __init__(self, M):
+        self._keep = []
+
+        def put(b):
+            a = np.ascontiguousarray(b.detach().cpu().view(torch.uint8).numpy() if b.dtype == torch.bfloat16 else b.detach().cpu().numpy())
+            self._keep.append(a)
+            return a.ctypes.data
+
+        def put_moe(Ld):
+            Ln = synth.to_numpy_layer(Ld)
+            self._keep.append(Ln)
+            c = szlib.MoeLayerC()
+            for k in ("hidden", "n_expert", "top_k", "expert_ff", "shared_ff", "expert_type", "shared_type"):
+                setattr(c, k, Ln[k])
+            c.router, c.shared_router = Ln["router"].ctypes.data, Ln["shared_router"].ctypes.data
+            for k in ("gate", "up", "down"):
+                setattr(c, k, Ln[k].ctypes.data)
+                setattr(c, k + "_stride", Ln[k].strides[0])
+            for k in ("sh_gate", "sh_up", "sh_down"):
+                setattr(c, k, Ln[k].ctypes.data)
+            return c
+
+        self._build(M, put, put_moe)
+
+
+class DeviceModel(_Placed):
+    """The model resident in HBM: what `Session` takes."""
+
+    def __init__(self, M, device="cuda:0"):
+        self.device = torch.device(device)
+        self._keep = []
+
+        def put(b):
+            buf, addr, _ = szmoe.place(b.reshape(1, -1), self.device, 0)
+            self._keep.append(buf)
+            return addr
+
+        def put_moe(Ld):
+            ml = szmoe.MoeLayer(Ld, self.device)
+            self._keep.append(ml)
+            return ml.c
+
+        self._build(M, put, put_moe)
+
+
+class Session:
+    """A verify session on the GPU (struct sz_session): owns the one device block the library asks for."""
+
+    def __init__(self, dm, ctx, kv_q8=True, stream=None):
+        self.lib = szlib.load()
+        self.dm = dm
+        self.flags = 1 if kv_q8 else 0
+        n = C.c_int64()
+        szlib.check(self.lib.sz_session_bytes(C.byref(dm.model), ctx, self.flags, C.byref(n)))
+        self.mem = torch.empty(n.value + 256, dtype=torch.uint8, device=dm.device)
+        addr = self.mem.data_ptr() + (-self.mem.data_ptr()) % 256
+        self.stream = (stream or torch.cuda.current_stream(dm.device)).cuda_stream
+        self.h = C.c_void_p()
+        szlib.check(self.lib.sz_session_create(C.byref(dm.model), ctx, self.flags, addr, n.value, self.stream, C.byref(self.h)))
+        self.vocab = dm.cfg["vocab"]
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.sz_session_destroy(self.h)
+            self.h = None
+
+    def __len__(self):
+        return self.lib.sz_session_len(self.h)
+
+    def reset(self):
+        szlib.check(self.lib.sz_session_reset(self.h, self.stream))
+
+    def trace_routes(self, on=True):
+        szlib.check(self.lib.sz_session_trace_routes(self.h, 1 if on else 0))
+
+    def verify(self, ids, accept=0, eog=-1, head=True):
+        a = (C.c_int32 * len(ids))(*[int(t) for t in ids])
+        szlib.check(self.lib.sz_session_verify(self.h, a, len(ids), accept, eog, 1 if head else 0, self.stream))
+        self._m = len(ids)
+
+    def prefill(self, ids):
+        a = (C.c_int32 * len(ids))(*[int(t) for t in ids])
+        szlib.check(self.lib.sz_session_prefill(self.h, a, len(ids), self.stream))
+        self._m = (len(ids) - 1) % szlib.MAX_VERIFY + 1
+
+    def result(self, logits=False):
+        """(keep, next), top [m, 128] uint32, logits [m, vocab] float32 or None of the pending pass."""
+        m = self._m
+        kn = (C.c_int32 * 2)()
+        top = np.empty((m, 128), dtype=np.uint32)
+        lg = np.empty((m, self.vocab), dtype=np.float32) if logits else None
+        szlib.check(self.lib.sz_session_result(self.h, kn, top.ctypes.data_as(C.c_void_p), lg.ctypes.data_as(C.c_void_p) if logits else None, self.stream))
+        return (kn[0], kn[1]), top, lg
+
+    def routes(self):
+        n = self.dm.cfg["n_layer"]
+        idx = np.empty((n, szlib.MAX_VERIFY, szlib.MAX_TOPK), dtype=np.int32)
+        w = np.empty((n, szlib.MAX_VERIFY, szlib.MAX_TOPK), dtype=np.float64)
+        szlib.check(self.lib.sz_session_routes(self.h, idx.ctypes.data_as(C.c_void_p), w.ctypes.data_as(C.c_void_p), self.stream))
+        k = self.dm.cfg["n_expert_used"]
+        return idx.reshape(n, -1)[:, :self._m * k].reshape(n, self._m, k), w.reshape(n, -1)[:, :self._m * k].reshape(n, self._m, k)
+
+    def commit(self, keep):
+        szlib.check(self.lib.sz_session_commit(self.h, keep, self.stream))
+
+    def generate(self, prompt, max_new, spec_k=3, greedy=True, sampler=None, lookup_min=4, eog=-1, device_accept=True):
+        p = GenParams(spec_k, max_new, lookup_min, 1 if greedy else 0, eog, 1 if device_accept else 0,
+                      sampler or Sampler(1.0, 20, 0.95, 0.0, 1))
+        pr = (C.c_uint32 * len(prompt))(*[int(t) for t in prompt])
+        out = (C.c_uint32 * max_new)()
+        log = (C.c_int32 * (2 * max_new))()
+        st = GenStats()
+        szlib.check(self.lib.sz_generate(self.h, pr, len(prompt), C.byref(p), out, log, max_new, C.byref(st), self.stream))
+        n = st.n_tokens
+        return list(out[:n]), [(log[2 * i], log[2 * i + 1]) for i in range(st.passes)], st
+
+
+def make_prompt(n_tokens, vocab, seed=1, block=16, substitute=0.1, cycles=None):
+    """BASELINE config 1's prompt: a block of `block` tokens repeated, with a fraction of random substitutions, so a suffix drafter
+    finds repeats.  With `cycles` (token_cycles(...)[1]) the block is one of the model's own token cycles."""
+    rng = np.random.default_rng(seed)
+    base = rng.integers(0, vocab, block) if cycles is None else cycles[int(rng.integers(0, cycles.shape[0]))].numpy()[:block]
+    ids = np.tile(base, (n_tokens + block - 1) // block)[:n_tokens].copy()
+    sub = rng.random(n_tokens) < substitute
+    ids[sub] = rng.integers(0, vocab, int(sub.sum()))
+    return [int(t) for t in ids]

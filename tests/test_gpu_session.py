@@ -1,0 +1,144 @@
+"""The whole verify step on the GPU against the CPU oracle's Session::step (forward.rs:751-794) on seeded tiny models:
+routing indices identical, logits within 1e-2 relative (BASELINE's bound; the reference's own yardstick is rel < 5e-3 with
+identical routing, crates/shadowzero/tests/reference.rs:57-66), emitted greedy tokens and accepted counts identical, and the
+reference's structural tests: batched == one at a time, a rolled-back pass continues exactly (reference.rs:226-255, 291-319)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import binding as ob
+from tests.util import pkg
+
+pytestmark = pytest.mark.gpu
+szlib, md = pkg.lib, pkg.model
+
+LOGIT_REL = 1e-2   # BASELINE north star: logits within 1e-2 relative error
+SMALL = dict(md.TINY, vocab=4096, n_expert=16, expert_ff=128, shared_ff=128)
+
+
+def rel_err(a, b):
+    return float(np.abs(a - b).max() / max(np.abs(b).max(), 1e-9))
+
+
+@pytest.fixture(scope="module")
+def small():
+    M = md.make_model(SMALL, seed=3)
+    return M, md.HostModel(M), md.DeviceModel(M)
+
+
+def cpu_rows(hm, tokens, kv_q8):
+    s = ob.Session(hm, kv_q8=kv_q8, threads=4)
+    rows, routes = [], []
+    for t in tokens:
+        rows.append(s.step(t))
+        routes.append(s.routes()[0])
+    return np.stack(rows), np.stack(routes)
+
+
+@pytest.mark.parametrize("kv_q8", [False, True])
+def test_verify_rows_match_the_cpu_steps(small, kv_q8):
+    M, hm, dm = small
+    toks = [int(t) for t in np.random.default_rng(1).integers(0, SMALL["vocab"], 19)]
+    want, want_routes = cpu_rows(hm, toks, kv_q8)
+    sess = md.Session(dm, 64, kv_q8=kv_q8)
+    sess.trace_routes(True)
+    got, routes = [], []
+    for lo in range(0, len(toks), 8):   # passes of 8, 8 and 3 rows
+        chunk = toks[lo:lo + 8]
+        sess.verify(chunk)
+        _, top, lg = sess.result(logits=True)
+        idx, _ = sess.routes()
+        got.append(lg); routes.append(idx)
+        for j in range(len(chunk)):     # the device's top-64 is the oracle's order on the device's own logits
+            v, i = ob.top64(lg[j])
+            assert np.array_equal(top[j, 64:], i) and np.array_equal(top[j, :64], v.view(np.uint32))
+        sess.commit(len(chunk))
+    got = np.concatenate(got)
+    routes = np.concatenate(routes, axis=1)  # [layer, row, k]
+    assert len(sess) == len(toks)
+    for j in range(len(toks)):
+        assert np.array_equal(routes[:, j, :], want_routes[j]), "routing differs at row %d" % j
+        assert rel_err(got[j], want[j]) < LOGIT_REL, (j, rel_err(got[j], want[j]))
+        assert int(np.argmax(got[j])) == int(np.argmax(want[j]))
+    assert max(rel_err(got[j], want[j]) for j in range(len(toks))) < 1e-3  # where the f32 kernels actually land
+
+
+def test_batched_equals_one_at_a_time_and_rollback_continues_exactly(small):
+    M, hm, dm = small
+    toks = [int(t) for t in np.random.default_rng(2).integers(0, SMALL["vocab"], 12)]
+    a = md.Session(dm, 64, kv_q8=True)
+    single = []
+    for t in toks:
+        a.verify([t]); single.append(a.result(logits=True)[2][0]); a.commit(1)
+    b = md.Session(dm, 64, kv_q8=True)
+    b.verify(toks[:5]); first = b.result(logits=True)[2]; b.commit(5)
+    for j in range(5):
+        assert rel_err(first[j], single[j]) < 1e-5
+    # a pass of 5 rows of which only 2 are kept (3 rejected drafts), then the rest: as if the rejected rows never ran
+    wrong = [toks[5], toks[6], 7, 8, 9]
+    b.verify(wrong); b.result(); b.commit(2)
+    assert len(b) == 7
+    b.verify(toks[7:12]); rest = b.result(logits=True)[2]; b.commit(5)
+    for j in range(5):
+        assert rel_err(rest[j], single[7 + j]) < 1e-5, j
+    # and bit-identical to a session that never saw the rejected rows
+    c = md.Session(dm, 64, kv_q8=True)
+    c.verify(toks[:5]); c.result(); c.commit(5)
+    c.verify(toks[5:7]); c.result(); c.commit(2)
+    c.verify(toks[7:12]); rest_c = c.result(logits=True)[2]; c.commit(5)
+    assert np.array_equal(rest.view(np.uint32), rest_c.view(np.uint32))
+    # commit(0) keeps nothing
+    c.verify([1, 2, 3]); c.result(); c.commit(0)
+    assert len(c) == 12
+
+
+def test_session_refuses_misuse(small):
+    M, hm, dm = small
+    s = md.Session(dm, 16, kv_q8=True)
+    with pytest.raises(szlib.SzError):
+        s.verify(list(range(9)))
+    s.verify([1, 2])
+    with pytest.raises(szlib.SzError):
+        s.verify([3])          # previous pass not committed
+    with pytest.raises(szlib.SzError):
+        s.commit(3)            # more rows than the pass had
+    s.commit(2)
+    with pytest.raises(szlib.SzError):
+        s.commit(1)            # nothing pending
+    s.verify(list(range(8))); s.commit(8)
+    with pytest.raises(szlib.SzError):
+        s.verify(list(range(8)))   # 10 + 8 > 16
+
+
+@pytest.fixture(scope="module")
+def tiny_cycle():
+    M = md.make_model(md.TINY, seed=1, cycle_alpha=0.24)
+    _, cyc = md.token_cycles(md.TINY["vocab"], 1)
+    return M, md.HostModel(M), md.DeviceModel(M), md.make_prompt(256, md.TINY["vocab"], seed=1, cycles=cyc)
+
+
+def test_config1_greedy_spec3_tokens_and_accepted_counts(tiny_cycle):
+    # BASELINE config 1: 256-token prompt, 128 new tokens, greedy, --spec 3 with the suffix drafter; CPU scalar path vs GPU
+    M, hm, dm, prompt = tiny_cycle
+    want_toks, want_log, want_st = ob.Session(hm, kv_q8=True, threads=8).generate(prompt, 128, spec_k=3)
+    sess = md.Session(dm, 512, kv_q8=True)
+    toks, log, st = sess.generate(prompt, 128, spec_k=3, device_accept=True)
+    assert toks == want_toks
+    assert log == want_log
+    assert (st.passes, st.drafted, st.accepted, st.lookup_passes) == (want_st.passes, want_st.drafted, want_st.accepted, want_st.lookup_passes)
+    assert list(st.pos_tried) == list(want_st.pos_tried) and list(st.pos_right) == list(want_st.pos_right)
+    assert st.passes > 0 and st.accepted > 0
+    # speculation does not change what is generated
+    sess2 = md.Session(dm, 512, kv_q8=True)
+    plain, _, st2 = sess2.generate(prompt, 128, spec_k=0)
+    assert plain == toks and st2.passes == 0
+
+
+def test_config1_sampled_spec3(tiny_cycle):
+    # sampled acceptance: the token the target would have drawn at that position (sampler.rs:3-9); T = 0.7, top-p 0.9
+    M, hm, dm, prompt = tiny_cycle
+    want_toks, want_log, want_st = ob.Session(hm, kv_q8=True, threads=8).generate(prompt, 96, spec_k=3, greedy=False,
+                                                                                  sampler=ob.SamplerC(0.7, 20, 0.9, 0.0, 11))
+    sess = md.Session(dm, 512, kv_q8=True)
+    toks, log, st = sess.generate(prompt, 96, spec_k=3, greedy=False, sampler=md.Sampler(0.7, 20, 0.9, 0.0, 11))
+    assert toks == want_toks and log == want_log
