@@ -190,6 +190,9 @@ int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* top, float* l
 int sz_session_commit(sz_session* s, int keep, uint64_t stream);
 /* Routing trace (the `layerL.route_idx` / `route_w` streams, forward.rs:1015-1018): switch it on, run a pass, read
  * idx [n_layer][SZ_MAX_VERIFY][SZ_MAX_TOPK] and w (same shape, f64). */
+/* Benchmarks: pretend `len` tokens were fed - seeded pseudo-random keys and values in the first `len` cache positions of every
+ * attention layer, zero recurrent state - so a long context needs no long prefill.  Resets the session first. */
+int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, uint64_t stream);
 int sz_session_trace_routes(sz_session* s, int on);
 int sz_session_routes(sz_session* s, int32_t* idx, double* w, uint64_t stream);
 

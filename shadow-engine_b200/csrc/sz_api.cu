@@ -39,6 +39,8 @@ void sz_trace_mark(const char* name, cudaStream_t stream) {
     g_tr_n++;
 }
 
+bool sz_trace_active() { return g_tr_events != nullptr; }
+
 extern "C" int sz_trace_begin(uint64_t* events, int capacity, uint64_t stream) {
     if (!events || capacity < 2) return sz_fail(SZ_E_ARG, "sz_trace_begin: needs a list of at least two events");
     g_tr_events = (cudaEvent_t*)events;

@@ -27,6 +27,7 @@ static inline bool sz_aligned16(u64 p) { return (p & 15) == 0; }
 
 // Per-kernel timing (sz_trace_begin): records the next caller-provided event on `stream` under `name`.  No-op when tracing is off.
 void sz_trace_mark(const char* name, cudaStream_t stream);
+bool sz_trace_active();
 
 // Launch with the programmatic-dependent-launch attribute: the kernel may start while its predecessor on the stream drains;
 // every such kernel calls sz_pdl_wait() before it touches anything the predecessor wrote.

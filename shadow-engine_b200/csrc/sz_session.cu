@@ -8,7 +8,9 @@
 // then the buffers swap.  The KV cache is append-only: rejected positions are overwritten by the next pass.
 #include "sz_session_kernels.cuh"
 
+#include <map>
 #include <new>
+#include <stdlib.h>
 #include <string.h>
 #include <vector>
 
@@ -37,20 +39,28 @@ struct sz_session {
     float* logits;
     u64* tk_tmp;
     u32* top;
-    int32_t *ids, *res, *routes;
+    int32_t *ids, *res, *routes, *state;   // state: {committed positions, current state buffer} as the kernels see them
     double* route_w;
     u8* moe_scratch;
     int64_t moe_scratch_bytes;
     int attn_splits;
-    // host staging
-    int32_t h_ids[SZ_MAX_VERIFY];
+    // host staging (pinned, so that a captured graph re-reads it at every launch)
+    int32_t* h_pin;   // [0..8): ids of the pass, [8]: keep of a host-decided commit
+    int pending_committed;  // the pending pass was already committed on the device (acceptance modes GREEDY / ALL)
+    int inflight;           // a pass was launched and the stream not synchronised since: the id staging buffer may still be read
+    int use_graphs;
+    std::map<int, cudaGraphExec_t> graphs;
+    ~sz_session() {
+        for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
+        if (h_pin) cudaFreeHost(h_pin);
+    }
 };
 
 static int sz_is_attn(const sz_model_config& c, int l) { return l % c.attn_interval == c.attn_interval - 1; }
 
 struct SzSessLayout {
     int64_t r, rn, hdown, mix, u, g, y, d_xin, d_z, d_b, d_a, d_xc, d_beta, d_decay, d_og, S0, S1, conv0, conv1, a_qg, a_k, a_v, a_q, a_gate,
-        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, routes, route_w, moe, total;
+        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, total;
     int64_t moe_bytes, S_bytes, conv_bytes, kv_bytes;
     int splits;
 };
@@ -92,7 +102,7 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
     L->logits = take(4 * M * (int64_t)c.vocab);
     const int64_t nb = ((int64_t)c.vocab + SZ_TK_N - 1) / SZ_TK_N;
     L->tk_tmp = take(8 * M * nb * 64); L->top = take(4 * M * 128);
-    L->ids = take(4 * M); L->res = take(64);
+    L->ids = take(4 * M); L->res = take(64); L->state = take(64);
     L->routes = take(4 * (int64_t)c.n_layer * M * SZ_MAX_TOPK); L->route_w = take(8 * (int64_t)c.n_layer * M * SZ_MAX_TOPK);
     int64_t moe_bytes = 0;
     for (int l = 0; l < c.n_layer; l++) {
@@ -202,8 +212,10 @@ extern "C" int sz_session_reset(sz_session* s, uint64_t stream) {
     SZ_CUDA(cudaMemsetAsync(s->S[1], 0, L.S_bytes, st));
     SZ_CUDA(cudaMemsetAsync(s->conv[0], 0, L.conv_bytes, st));
     SZ_CUDA(cudaMemsetAsync(s->conv[1], 0, L.conv_bytes, st));
+    SZ_CUDA(cudaMemsetAsync(s->state, 0, 64, st));
+    SZ_CUDA(cudaMemsetAsync(s->res, 0, 64, st));
     if ((rc = sz_moe_scratch_init((uint64_t)s->moe_scratch, s->moe_scratch_bytes, stream))) return rc;
-    s->len = 0; s->cur = 0; s->last_m = 0;
+    s->len = 0; s->cur = 0; s->last_m = 0; s->pending_committed = 0; s->inflight = 0;
     return SZ_OK;
 }
 
@@ -220,6 +232,12 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->layers.assign(m->layers, m->layers + m->cfg.n_layer);
     s->model.layers = s->layers.data();
     s->ctx = ctx; s->flags = flags; s->want_routes = 0;
+    s->h_pin = nullptr;
+    if (cudaHostAlloc((void**)&s->h_pin, 64, cudaHostAllocDefault) != cudaSuccess) { delete s; return sz_fail(SZ_E_CUDA, "cudaHostAlloc of the id staging buffer failed"); }
+    {
+        const char* e = getenv("SZ_SESSION_GRAPHS");  // A/B switch: 0 = launch every kernel eagerly
+        s->use_graphs = !(e && atoi(e) == 0);
+    }
     s->lb.resize(m->cfg.n_layer);
     s->n_delta = s->n_attn = 0;
     for (int l = 0; l < m->cfg.n_layer; l++) {
@@ -238,7 +256,7 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->a_gate = (float*)(b + L.a_gate); s->a_o = (float*)(b + L.a_o); s->a_part = (float*)(b + L.a_part);
     s->kc = b + L.kc; s->vc = b + L.vc;
     s->logits = (float*)(b + L.logits); s->tk_tmp = (u64*)(b + L.tk_tmp); s->top = (u32*)(b + L.top);
-    s->ids = (int32_t*)(b + L.ids); s->res = (int32_t*)(b + L.res); s->routes = (int32_t*)(b + L.routes); s->route_w = (double*)(b + L.route_w);
+    s->ids = (int32_t*)(b + L.ids); s->res = (int32_t*)(b + L.res); s->state = (int32_t*)(b + L.state); s->routes = (int32_t*)(b + L.routes); s->route_w = (double*)(b + L.route_w);
     s->moe_scratch = b + L.moe; s->moe_scratch_bytes = L.moe_bytes;
     s->attn_splits = L.splits;
     if ((rc = sz_session_reset(s, stream))) { delete s; return rc; }
@@ -306,29 +324,28 @@ static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bo
     return SZ_OK;
 }
 
+// The DeltaNet scan: the pass of one layer (l >= 0: all m rows, with outputs) or the replay of a commit (l < 0: every layer in one
+// launch, the kept rows only, decided on the device).
 template <int D, int PARTS>
-static int sz_scan_launch(cudaStream_t st, const char* name, const float* xc, const float* beta, const float* decay, const float* z,
-                          const float* norm_w, const float* Sin, float* Sout, int kh, int vh, int rows, float eps, float* og) {
-    SZ_CUDA(sz_launch(name, sz_delta_scan_kernel<D, PARTS>, dim3(vh), dim3(D * PARTS), 0, st, true, xc, beta, decay, z, norm_w, Sin, Sout, kh, vh,
-                      rows, eps, og));
-    return SZ_OK;
-}
-
-static int sz_scan(sz_session* s, cudaStream_t st, const char* name, int l, int rows, bool outputs) {
+static int sz_scan_launch(sz_session* s, cudaStream_t st, int l, int m) {
     const sz_model_config& c = s->model.cfg;
-    const int di = s->lb[l].delta_index;
-    const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd;
-    const int64_t Sl = (int64_t)c.ssm_v_heads * c.ssm_head_dim * c.ssm_head_dim;
+    const int64_t kd = (int64_t)c.ssm_k_heads * D, vd = (int64_t)c.ssm_v_heads * D, ch = 2 * kd + vd;
+    const int64_t Sl = (int64_t)c.ssm_v_heads * D * D;
+    const int di = l >= 0 ? s->lb[l].delta_index : 0;
     const float* xc = s->d_xc + (int64_t)di * SZ_MAX_VERIFY * ch;
     const float* beta = s->d_beta + (int64_t)di * SZ_MAX_VERIFY * c.ssm_v_heads;
     const float* decay = s->d_decay + (int64_t)di * SZ_MAX_VERIFY * c.ssm_v_heads;
-    const float* Sin = s->S[s->cur] + di * Sl;
-    float* Sout = s->S[s->cur ^ 1] + di * Sl;
-    const float* nw = (const float*)s->layers[l].ssm_norm.data;
-    float* og = outputs ? s->d_og : nullptr;
-    if (c.ssm_head_dim == 128)
-        return sz_scan_launch<128, 2>(st, name, xc, beta, decay, s->d_z, nw, Sin, Sout, c.ssm_k_heads, c.ssm_v_heads, rows, c.eps, og);
-    return sz_scan_launch<64, 1>(st, name, xc, beta, decay, s->d_z, nw, Sin, Sout, c.ssm_k_heads, c.ssm_v_heads, rows, c.eps, og);
+    const float* nw = l >= 0 ? (const float*)s->layers[l].ssm_norm.data : nullptr;
+    SZ_CUDA(sz_launch(l >= 0 ? "delta_scan" : "delta_replay", sz_delta_scan_kernel<D, PARTS>, dim3(c.ssm_v_heads, l >= 0 ? 1 : s->n_delta),
+                      dim3(D * PARTS), 0, st, true, xc, beta, decay, (const float*)s->d_z, nw, (const float*)(s->S[0] + di * Sl),
+                      (const float*)(s->S[1] + di * Sl), s->S[0] + di * Sl, s->S[1] + di * Sl, (const int32_t*)s->state, (const int32_t*)s->res,
+                      (int)c.ssm_k_heads, (int)c.ssm_v_heads, m, c.eps, l >= 0 ? s->d_og : (float*)nullptr));
+    return SZ_OK;
+}
+
+static int sz_scan(sz_session* s, cudaStream_t st, int l, int m) {
+    if (s->model.cfg.ssm_head_dim == 128) return sz_scan_launch<128, 2>(s, st, l, m);
+    return sz_scan_launch<64, 1>(s, st, l, m);
 }
 
 static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
@@ -349,11 +366,11 @@ static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
     a.job[3] = sz_job(L.ssm_alpha, s->d_a, vh);
     int rc = sz_dense_launch(a, st, "delta_proj");
     if (rc) return rc;
-    const float* conv = s->conv[s->cur] + (int64_t)di * (c.conv_k - 1) * ch;
-    SZ_CUDA(sz_launch("delta_prep", sz_delta_prep_kernel, dim3(m), dim3(256), 0, st, true, (const float*)xin, conv, (const float*)L.ssm_conv1d.data,
-                      (const float*)s->d_b, (const float*)s->d_a, (const float*)L.ssm_a.data, (const float*)L.ssm_dt_bias.data, kh, vh, d,
-                      (int)c.conv_k, xc, beta, decay));
-    if ((rc = sz_scan(s, st, "delta_scan", l, m, true))) return rc;
+    const int64_t cl = (int64_t)(c.conv_k - 1) * ch;
+    SZ_CUDA(sz_launch("delta_prep", sz_delta_prep_kernel, dim3(m), dim3(256), 0, st, true, (const float*)xin, (const float*)(s->conv[0] + di * cl),
+                      (const float*)(s->conv[1] + di * cl), (const int32_t*)s->state, (const float*)L.ssm_conv1d.data, (const float*)s->d_b,
+                      (const float*)s->d_a, (const float*)L.ssm_a.data, (const float*)L.ssm_dt_bias.data, kh, vh, d, (int)c.conv_k, xc, beta, decay));
+    if ((rc = sz_scan(s, st, l, m))) return rc;
     SzDenseArgs b = {};
     b.x = s->d_og; b.xstride = (int)vd; b.cols = (int)vd; b.m = m; b.n_jobs = 1;
     b.job[0] = sz_job(L.ssm_out, s->y, H);
@@ -364,7 +381,7 @@ template <int EPL>
 static int sz_attn_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m) {
     const sz_model_config& c = s->model.cfg;
     SZ_CUDA(sz_launch("attention", sz_attn_kernel<EPL>, dim3(c.n_head, m, s->attn_splits), dim3(256), 0, st, true, (const float*)s->a_q, kc, vc,
-                      (int)c.n_head, (int)c.n_kv_head, s->len, (s->flags & SZ_KV_Q8) ? 1 : 0, s->attn_splits, s->a_part));
+                      (int)c.n_head, (int)c.n_kv_head, (const int32_t*)s->state, (s->flags & SZ_KV_Q8) ? 1 : 0, s->attn_splits, s->a_part));
     return SZ_OK;
 }
 
@@ -385,8 +402,8 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     int rc = sz_dense_launch(a, st, "attn_proj");
     if (rc) return rc;
     SZ_CUDA(sz_launch("attn_prep", sz_attn_prep_kernel, dim3(nh + 2 * nkv, m), dim3(128), 0, st, true, (const float*)s->a_qg, (const float*)s->a_k,
-                      (const float*)s->a_v, (const float*)L.attn_q_norm.data, (const float*)L.attn_k_norm.data, nh, nkv, hd, c.eps, s->len,
-                      (int)c.rope_dims, c.rope_theta, q8, kc, vc, s->a_q, s->a_gate));
+                      (const float*)s->a_v, (const float*)L.attn_q_norm.data, (const float*)L.attn_k_norm.data, nh, nkv, hd, c.eps,
+                      (const int32_t*)s->state, (int)c.rope_dims, c.rope_theta, q8, kc, vc, s->a_q, s->a_gate));
     if (hd == 64) rc = sz_attn_launch<2>(s, st, kc, vc, m);
     else if (hd == 128) rc = sz_attn_launch<4>(s, st, kc, vc, m);
     else rc = sz_attn_launch<8>(s, st, kc, vc, m);
@@ -410,22 +427,17 @@ static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
     for (int l = 0; l < c.n_layer; l++) {
         const sz_layer& L = s->layers[l];
         if ((rc = sz_hc_read(s, st, L.hc_attn, m, pending, true))) return rc;
-        // g of this read is consumed by the write after the sublayer; the MoE read below overwrites s->g, so keep the order
         rc = sz_is_attn(c, l) ? sz_attn_layer(s, st, l, m) : sz_delta_layer(s, st, l, m);
         if (rc) return rc;
         if ((rc = sz_hc_read(s, st, L.hc_ffn, m, true, true))) return rc;   // applies the mixer's write first
         int32_t* ri = s->want_routes ? s->routes + (int64_t)l * SZ_MAX_VERIFY * SZ_MAX_TOPK : nullptr;
         double* rw = s->want_routes ? s->route_w + (int64_t)l * SZ_MAX_VERIFY * SZ_MAX_TOPK : nullptr;
-        // the MoE writes its result to y, after the read has consumed the previous y
         if ((rc = sz_moe_verify(&L.moe, (uint64_t)s->u, m, (uint64_t)s->y, (uint64_t)ri, (uint64_t)rw, (uint64_t)s->moe_scratch, s->moe_scratch_bytes,
                                 (uint64_t)st)))
             return rc;
         pending = true;
     }
-    if (!head) {
-        // the last MoE write still has to reach r only if somebody reads r again; a later pass starts from the embedding, so it is dropped
-        return SZ_OK;
-    }
+    if (!head) return SZ_OK;  // the last write only matters to the output read; the next pass starts from the embedding
     if ((rc = sz_hc_read(s, st, s->model.output_hc, m, pending, false))) return rc;
     SzDenseArgs a = {};
     a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 1;
@@ -437,21 +449,80 @@ static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
     return SZ_OK;
 }
 
+// The commit as the device does it: replay of the kept rows where some were dropped, conv rows, position count and buffer swap.
+// All of it reads res[0] (rows kept) from device memory, so it can follow the acceptance kernel inside one graph.
+static int sz_commit_device(sz_session* s, cudaStream_t st, int m) {
+    const sz_model_config& c = s->model.cfg;
+    if (s->n_delta > 0) {
+        const int rc = sz_scan(s, st, -1, m);
+        if (rc) return rc;
+        const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd;
+        SZ_CUDA(sz_launch("conv_commit", sz_conv_commit_kernel, dim3(c.conv_k - 1, s->n_delta), dim3(256), 0, st, true, (const float*)s->conv[0],
+                          (const float*)s->conv[1], (const int32_t*)s->state, (const int32_t*)s->res, (const float*)s->d_xin, (int)ch, (int)c.conv_k,
+                          s->conv[0], s->conv[1]));
+    }
+    SZ_CUDA(sz_launch("state_update", sz_state_update_kernel, dim3(1), dim3(32), 0, st, true, s->state, (const int32_t*)s->res));
+    return SZ_OK;
+}
+
+// Everything a pass launches after the ids are on the device.
+static int sz_pass(sz_session* s, cudaStream_t st, int m, int accept_mode, int eog_token, bool head) {
+    int rc = sz_forward(s, st, m, head);
+    if (rc) return rc;
+    if (accept_mode != SZ_ACCEPT_NONE) {
+        SZ_CUDA(sz_launch("accept", sz_accept_greedy_kernel, dim3(1), dim3(32), 0, st, true, (const u32*)s->top, (const int32_t*)s->ids, m, eog_token,
+                          accept_mode == SZ_ACCEPT_ALL ? 1 : 0, head ? 1 : 0, s->res));
+        if ((rc = sz_commit_device(s, st, m))) return rc;
+    }
+    return SZ_OK;
+}
+
 extern "C" int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode, int eog_token, int want_head, uint64_t stream) {
     if (!s || !ids) return sz_fail(SZ_E_ARG, "null session or ids");
     if (m < 1 || m > SZ_MAX_VERIFY) return sz_fail(SZ_E_ARG, "a pass has 1..%d rows, got %d", SZ_MAX_VERIFY, m);
     if (s->last_m) return sz_fail(SZ_E_ARG, "the previous pass was not committed");
     if (s->len + m > s->ctx) return sz_fail(SZ_E_ARG, "%d positions + %d rows exceed the session's capacity %d", s->len, m, s->ctx);
     if (accept_mode == SZ_ACCEPT_GREEDY && !want_head) return sz_fail(SZ_E_ARG, "greedy acceptance needs the head");
+    if (accept_mode < SZ_ACCEPT_NONE || accept_mode > SZ_ACCEPT_ALL) return sz_fail(SZ_E_ARG, "accept_mode %d", accept_mode);
     cudaStream_t st = (cudaStream_t)stream;
-    memcpy(s->h_ids, ids, (size_t)m * 4);
-    SZ_CUDA(cudaMemcpyAsync(s->ids, s->h_ids, (size_t)m * 4, cudaMemcpyHostToDevice, st));
-    int rc = sz_forward(s, st, m, want_head != 0);
-    if (rc) return rc;
-    if (accept_mode != SZ_ACCEPT_NONE && want_head)
-        SZ_CUDA(sz_launch("accept", sz_accept_greedy_kernel, dim3(1), dim3(32), 0, st, true, (const u32*)s->top, (const int32_t*)s->ids, m, eog_token,
-                          accept_mode == SZ_ACCEPT_ALL ? 1 : 0, s->res));
+    if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
+    memcpy(s->h_pin, ids, (size_t)m * 4);
+    int rc = SZ_OK;
+    // one graph per (rows, head, acceptance, eog): every launch-time value a kernel needs lives in device memory
+    const int key = m | (want_head ? 16 : 0) | (accept_mode << 5) | ((eog_token & 0xfffff) << 8);
+    bool traced = sz_trace_active();
+    const bool capturable = st != (cudaStream_t)0 && st != cudaStreamLegacy && st != cudaStreamPerThread;  // the default stream cannot record
+    if (s->use_graphs && capturable && !traced && !s->want_routes) {
+        auto it = s->graphs.find(key);
+        if (it == s->graphs.end()) {
+            // first use: run the pass eagerly (this also does every one-time function-attribute set-up), then record it for the next time
+            SZ_CUDA(cudaMemcpyAsync(s->ids, s->h_pin, (size_t)m * 4, cudaMemcpyHostToDevice, st));
+            if ((rc = sz_pass(s, st, m, accept_mode, eog_token, want_head != 0))) return rc;
+            cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+            if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone && s->graphs.size() < 64) {
+                // record the same launches without running them
+                cudaGraph_t g = nullptr;
+                SZ_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+                cudaError_t e = cudaMemcpyAsync(s->ids, s->h_pin, (size_t)m * 4, cudaMemcpyHostToDevice, st);
+                int prc = e == cudaSuccess ? sz_pass(s, st, m, accept_mode, eog_token, want_head != 0) : SZ_E_CUDA;
+                cudaError_t e2 = cudaStreamEndCapture(st, &g);
+                if (prc == SZ_OK && e2 == cudaSuccess && g) {
+                    cudaGraphExec_t ge = nullptr;
+                    if (cudaGraphInstantiate(&ge, g, 0) == cudaSuccess) s->graphs[key] = ge;
+                }
+                if (g) cudaGraphDestroy(g);
+                (void)cudaGetLastError();
+            }
+        } else {
+            SZ_CUDA(cudaGraphLaunch(it->second, st));
+        }
+    } else {
+        SZ_CUDA(cudaMemcpyAsync(s->ids, s->h_pin, (size_t)m * 4, cudaMemcpyHostToDevice, st));
+        if ((rc = sz_pass(s, st, m, accept_mode, eog_token, want_head != 0))) return rc;
+    }
     s->last_m = m;
+    s->pending_committed = accept_mode != SZ_ACCEPT_NONE;
+    s->inflight = 1;
     return SZ_OK;
 }
 
@@ -462,6 +533,7 @@ extern "C" int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* to
     if (top) SZ_CUDA(cudaMemcpyAsync(top, s->top, (size_t)s->last_m * 128 * 4, cudaMemcpyDeviceToHost, st));
     if (logits) SZ_CUDA(cudaMemcpyAsync(logits, s->logits, (size_t)s->last_m * s->model.cfg.vocab * 4, cudaMemcpyDeviceToHost, st));
     SZ_CUDA(cudaStreamSynchronize(st));
+    s->inflight = 0;
     return SZ_OK;
 }
 
@@ -475,30 +547,23 @@ extern "C" int sz_session_routes(sz_session* s, int32_t* idx, double* w, uint64_
     return SZ_OK;
 }
 
-// Keeps the first `keep` rows of the last pass: recurrent states of exactly those rows, conv rows, position count.
+// Keeps the first `keep` rows of the pending pass: recurrent states of exactly those rows, conv rows, position count.  When the
+// device already decided (acceptance modes GREEDY / ALL) `keep` must be what it kept, as sz_session_result reported.
 extern "C" int sz_session_commit(sz_session* s, int keep, uint64_t stream) {
     if (!s || !s->last_m) return sz_fail(SZ_E_ARG, "no pass to commit");
     const int m = s->last_m;
     if (keep < 0 || keep > m) return sz_fail(SZ_E_ARG, "keep = %d of a pass of %d rows", keep, m);
     cudaStream_t st = (cudaStream_t)stream;
-    const sz_model_config& c = s->model.cfg;
-    s->last_m = 0;
-    if (keep == 0) return SZ_OK;  // nothing kept: the current buffers stand
-    const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd;
-    for (int l = 0; l < c.n_layer; l++) {
-        const int di = s->lb[l].delta_index;
-        if (di < 0) continue;
-        if (keep < m) {  // replay the recurrences of the kept rows from the saved inputs (the pass wrote the state after all m rows)
-            const int rc = sz_scan(s, st, "delta_replay", l, keep, false);
-            if (rc) return rc;
-        }
-        const float* xin = s->d_xin + (int64_t)di * SZ_MAX_VERIFY * ch;
-        const int64_t cl = (int64_t)(c.conv_k - 1) * ch;
-        SZ_CUDA(sz_launch("conv_commit", sz_conv_commit_kernel, dim3(c.conv_k - 1), dim3(256), 0, st, true, (const float*)(s->conv[s->cur] + di * cl), xin,
-                          (int)ch, (int)c.conv_k, keep, s->conv[s->cur ^ 1] + di * cl));
+    if (!s->pending_committed) {
+        if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
+        s->h_pin[8] = keep;
+        SZ_CUDA(cudaMemcpyAsync(s->res, s->h_pin + 8, 4, cudaMemcpyHostToDevice, st));
+        const int rc = sz_commit_device(s, st, m);
+        if (rc) return rc;
     }
-    s->cur ^= 1;
-    s->len += keep;
+    s->last_m = 0;
+    s->pending_committed = 0;
+    if (keep > 0) { s->cur ^= 1; s->len += keep; }
     return SZ_OK;
 }
 
@@ -510,11 +575,56 @@ extern "C" int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint
     while (done < n) {
         const int m = n - done < SZ_MAX_VERIFY ? n - done : SZ_MAX_VERIFY;
         const bool last = done + m == n;
-        int rc = sz_session_verify(s, ids + done, m, SZ_ACCEPT_NONE, -1, last ? 1 : 0, stream);
+        int rc = sz_session_verify(s, ids + done, m, last ? SZ_ACCEPT_NONE : SZ_ACCEPT_ALL, -1, last ? 1 : 0, stream);
         if (rc) return rc;
-        if (last) { s->last_m = m; return SZ_OK; }  // left pending so the caller can read the result, then commit all m rows
+        if (last) return SZ_OK;  // left pending so the caller can read the result, then commit all m rows
         if ((rc = sz_session_commit(s, m, stream))) return rc;
         done += m;
     }
+    return SZ_OK;
+}
+
+// ---- synthetic history (benchmarks) -------------------------------------------------------------------------------------------------
+// Fills the first `len` positions of every attention layer's cache with seeded pseudo-random keys and values (and small random
+// DeltaNet states), as if `len` tokens had been fed: a long context without running a long prefill.
+__global__ void sz_fill_kv_kernel(u8* __restrict__ kc, int64_t bytes_per_layer_used, int64_t layer_stride, int hd, int q8, u32 seed) {
+    const int layer = blockIdx.y;
+    u8* base = kc + layer * layer_stride;
+    const int hb = q8 ? sz_kv_head_bytes(hd) : hd * 4;
+    const int64_t heads = bytes_per_layer_used / hb;
+    for (int64_t h = blockIdx.x; h < heads; h += gridDim.x) {
+        u8* p = base + h * hb;
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+            u32 x = (u32)(h * 2654435761u) ^ (u32)(i * 40503u) ^ seed ^ (u32)(layer * 97u);
+            x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+            if (q8) p[i] = (u8)(int8_t)((int)(x % 255u) - 127);
+            else ((float*)p)[i] = ((float)(x % 2001u) - 1000.0f) * 1e-3f;
+        }
+        if (q8) {
+            u16* sc = (u16*)(p + hd);
+            for (int g = threadIdx.x; g < (hb - hd) / 2; g += blockDim.x) sc[g] = g < hd / 32 ? (u16)0x2000 : (u16)0;  // f16 2^-7
+        }
+    }
+}
+
+extern "C" int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, uint64_t stream) {
+    if (!s || s->last_m) return sz_fail(SZ_E_ARG, "sz_session_fill_synthetic: null session or a pass is pending");
+    if (len < 0 || len + SZ_MAX_VERIFY > s->ctx) return sz_fail(SZ_E_ARG, "sz_session_fill_synthetic: %d positions in a session of %d", len, s->ctx);
+    cudaStream_t st = (cudaStream_t)stream;
+    const sz_model_config& c = s->model.cfg;
+    int rc = sz_session_reset(s, stream);
+    if (rc) return rc;
+    if (s->n_attn > 0 && len > 0) {
+        const int q8 = (s->flags & SZ_KV_Q8) ? 1 : 0;
+        const int64_t hb = q8 ? (c.head_dim + (((c.head_dim >> 5) * 2 + 15) & ~15)) : 4 * (int64_t)c.head_dim;
+        const int64_t stride = (int64_t)s->ctx * c.n_kv_head * hb, used = (int64_t)len * c.n_kv_head * hb;
+        sz_fill_kv_kernel<<<dim3(1024, s->n_attn), 128, 0, st>>>(s->kc, used, stride, c.head_dim, q8, seed);
+        sz_fill_kv_kernel<<<dim3(1024, s->n_attn), 128, 0, st>>>(s->vc, used, stride, c.head_dim, q8, seed ^ 0x9e3779b9u);
+        SZ_CUDA(cudaGetLastError());
+    }
+    s->h_pin[8] = len;
+    SZ_CUDA(cudaMemcpyAsync(s->state, s->h_pin + 8, 4, cudaMemcpyHostToDevice, st));
+    SZ_CUDA(cudaStreamSynchronize(st));
+    s->len = len;
     return SZ_OK;
 }

@@ -76,13 +76,15 @@ sz_hc_mix_kernel(const float* __restrict__ mix, const float* __restrict__ rn, in
 // ---- DeltaNet front end (forward.rs:829-861): causal conv (k taps) + SiLU over the rows of the pass, L2 norm of q and k heads,
 // beta and decay.  grid (m), block 256.  conv: (k-1) x ch, oldest first: the state BEFORE the pass.  xin: [m][ch] raw projections.
 __global__ void __launch_bounds__(256)
-sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ conv, const float* __restrict__ cw, const float* __restrict__ b,
+sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ conv0, const float* __restrict__ conv1, const int32_t* __restrict__ state,
+                     const float* __restrict__ cw, const float* __restrict__ b,
                      const float* __restrict__ a, const float* __restrict__ a_log, const float* __restrict__ dt, int kh, int vh, int d, int k,
                      float* __restrict__ xc, float* __restrict__ beta, float* __restrict__ decay) {
     sz_pdl_wait();
     sz_pdl_trigger();
     const int j = blockIdx.x;
     const int kd = kh * d, ch = 2 * kd + vh * d;
+    const float* conv = state[1] ? conv1 : conv0;  // the carried rows of the current state buffer
     for (int i = threadIdx.x; i < ch; i += 256) {
         double acc = (double)cw[i * k + (k - 1)] * (double)xin[(size_t)j * ch + i];
         for (int t = 0; t < k - 1; t++) {
@@ -115,35 +117,71 @@ sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ co
     }
 }
 
-// The carried conv rows after `keep` rows of the pass: the last k-1 of [state rows ; xin rows 0..keep-1].  grid (k-1), block 256
+// The carried conv rows after the kept rows of the pass: the last k-1 of [state rows ; xin rows 0..keep-1], for every DeltaNet layer.
+// grid (k-1, n_delta), block 256.  res[0] = rows kept; nothing is written when it is 0.
 __global__ void __launch_bounds__(256)
-sz_conv_commit_kernel(const float* __restrict__ conv, const float* __restrict__ xin, int ch, int k, int keep, float* __restrict__ conv_next) {
+sz_conv_commit_kernel(const float* __restrict__ conv0, const float* __restrict__ conv1, const int32_t* __restrict__ state,
+                      const int32_t* __restrict__ res, const float* __restrict__ xin_all, int ch, int k, float* __restrict__ out0,
+                      float* __restrict__ out1) {
     sz_pdl_wait();
     sz_pdl_trigger();
-    const int t = blockIdx.x;              // row of the new state, oldest first
+    const int keep = res[0];
+    if (keep <= 0) return;
+    const int cur = state[1];
+    const int t = blockIdx.x, di = blockIdx.y;  // row of the new state, oldest first
+    const size_t cl = (size_t)(k - 1) * ch;
+    const float* conv = (cur ? conv1 : conv0) + di * cl;
+    float* dst = (cur ? out0 : out1) + di * cl;   // the other buffer
+    const float* xin = xin_all + (size_t)di * SZ_MAX_VERIFY * ch;
     const int tau = keep - (k - 1) + t;    // index into the pass rows, negative: into the old state
     const float* src = tau >= 0 ? xin + (size_t)tau * ch : conv + (size_t)((k - 1) + tau) * ch;
-    for (int i = threadIdx.x; i < ch; i += 256) conv_next[(size_t)t * ch + i] = src[i];
+    for (int i = threadIdx.x; i < ch; i += 256) dst[(size_t)t * ch + i] = src[i];
+}
+
+// After the commit kernels: positions += kept rows, and the state buffers swap.
+__global__ void sz_state_update_kernel(int32_t* __restrict__ state, const int32_t* __restrict__ res) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        const int keep = res[0];
+        if (keep > 0) { state[0] += keep; state[1] ^= 1; }
+    }
 }
 
 // ---- DeltaNet state scan (forward.rs:859-894): per value head, the d x d state column-resident in registers.
-// Thread (col = tid % D, part = tid / D) holds S[i][col] for the i of its part.  grid (vh), block D * PARTS.
-// rows: how many rows of the pass to apply; S_in -> S_out; with `og` != null also writes the gated, normalised outputs.
+// Thread (col = tid % D, part = tid / D) holds S[i][col] for the i of its part.  grid (vh, layers), block D * PARTS.
+// Reads the state of the current buffer (state[1]) and writes the other one.  With `og` != null it applies all m rows and writes
+// the gated, normalised outputs (the pass itself, one layer: blockIdx.y = 0 and the pointers are that layer's).  With og == null it
+// is the replay of a commit: layer blockIdx.y of every per-layer array, only the res[0] kept rows, and nothing at all when every
+// row was kept (the pass already wrote that state) or none was.
 template <int D, int PARTS>
 __global__ void __launch_bounds__(D * PARTS)
-sz_delta_scan_kernel(const float* __restrict__ xc, const float* __restrict__ beta, const float* __restrict__ decay, const float* __restrict__ z,
-                     const float* __restrict__ norm_w, const float* __restrict__ S_in, float* __restrict__ S_out, int kh, int vh, int rows,
-                     float eps, float* __restrict__ og) {
+sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__ beta_all, const float* __restrict__ decay_all,
+                     const float* __restrict__ z, const float* __restrict__ norm_w, const float* __restrict__ S0, const float* __restrict__ S1,
+                     float* __restrict__ O0, float* __restrict__ O1, const int32_t* __restrict__ state, const int32_t* __restrict__ res, int kh,
+                     int vh, int m, float eps, float* __restrict__ og) {
     constexpr int NI = D / PARTS;
     __shared__ float sk[D], sq[D];
     __shared__ double part[PARTS][D];
     __shared__ double red[8];
     sz_pdl_wait();
     sz_pdl_trigger();
-    const int hd = blockIdx.x;
+    const int hd = blockIdx.x, di = blockIdx.y;
     const int col = threadIdx.x % D, pt = threadIdx.x / D;
     const int kx = hd % kh;  // value heads are tiled over the key heads (forward.rs:862-864)
     const int kd = kh * D, ch = 2 * kd + vh * D;
+    int rows = m;
+    if (!og) {
+        rows = res[0];
+        if (rows <= 0 || rows >= m) return;
+    }
+    const int cur = state[1];
+    const size_t Sl = (size_t)vh * D * D;
+    const float* S_in = (cur ? S1 : S0) + di * Sl;
+    float* S_out = (cur ? O0 : O1) + di * Sl;
+    const float* xc = xc_all + (size_t)di * SZ_MAX_VERIFY * ch;
+    const float* beta = beta_all + (size_t)di * SZ_MAX_VERIFY * vh;
+    const float* decay = decay_all + (size_t)di * SZ_MAX_VERIFY * vh;
     float S[NI];
     const float* Sg = S_in + (size_t)hd * D * D;
 #pragma unroll
@@ -224,14 +262,14 @@ __device__ __forceinline__ void sz_kv_store(const float* src, int hd, int q8, u8
 
 __global__ void __launch_bounds__(128)
 sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, const float* __restrict__ vv, const float* __restrict__ wq,
-                    const float* __restrict__ wk, int nh, int nkv, int hd, float eps, int pos0, int rope_dims, double theta, int q8,
-                    u8* __restrict__ kc, u8* __restrict__ vc, float* __restrict__ q, float* __restrict__ gate) {
+                    const float* __restrict__ wk, int nh, int nkv, int hd, float eps, const int32_t* __restrict__ state, int rope_dims, double theta,
+                    int q8, u8* __restrict__ kc, u8* __restrict__ vc, float* __restrict__ q, float* __restrict__ gate) {
     __shared__ float tmp[512];
     __shared__ double red[8];
     sz_pdl_wait();
     sz_pdl_trigger();
     const int b = blockIdx.x, j = blockIdx.y;
-    const int pos = pos0 + j;
+    const int pos = state[0] + j;
     const size_t row_q8 = (size_t)nkv * sz_kv_head_bytes(hd), row_f = (size_t)nkv * hd * 4;
     if (b >= nh + nkv) {  // V head: raw into the cache
         const int h = b - nh - nkv;
@@ -274,8 +312,8 @@ sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, 
 // merged per block; partial (max, sum, acc[hd]) per split.  part: [m][nh][splits][hd + 2].
 template <int EPL>  // elements per lane = hd / 32
 __global__ void __launch_bounds__(256)
-sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8* __restrict__ vc, int nh, int nkv, int pos0, int q8,
-               int splits, float* __restrict__ part) {
+sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8* __restrict__ vc, int nh, int nkv,
+               const int32_t* __restrict__ state, int q8, int splits, float* __restrict__ part) {
     constexpr int HD = EPL * 32;
     __shared__ float sm_m[8], sm_s[8];
     __shared__ float sm_acc[8][HD];
@@ -284,7 +322,7 @@ sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8*
     const int h = blockIdx.x, j = blockIdx.y, sp = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = h / (nh / nkv);
-    const int n = pos0 + j + 1;
+    const int n = state[0] + j + 1;
     const int per = (n + splits - 1) / splits;
     const int t0 = sp * per, t1 = min(n, t0 + per);
     const int hb = sz_kv_head_bytes(HD);
@@ -430,7 +468,7 @@ sz_topk_merge_kernel(const u64* __restrict__ tmp, int nb, u32* __restrict__ out)
 // row i's best token must equal the next drafted token ids[i + 1]; a drafted end-of-generation token is never accepted.
 // res[0] = rows kept (1 .. m), res[1] = the token after the kept rows (best of row keep - 1).
 __global__ void sz_accept_greedy_kernel(const u32* __restrict__ top, const int32_t* __restrict__ ids, int m, int eog, int keep_all,
-                                        int32_t* __restrict__ res) {
+                                        int has_head, int32_t* __restrict__ res) {
     sz_pdl_wait();
     sz_pdl_trigger();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
@@ -444,7 +482,7 @@ __global__ void sz_accept_greedy_kernel(const u32* __restrict__ top, const int32
             keep++;
         }
     res[0] = keep;
-    res[1] = (int)top[(size_t)(keep - 1) * 128 + 64];
+    res[1] = has_head ? (int)top[(size_t)(keep - 1) * 128 + 64] : -1;
 }
 
 #endif  // __CUDACC__

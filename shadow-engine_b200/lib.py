@@ -58,6 +58,7 @@ SYMBOLS = {
     "sz_session_verify": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64]),
     "sz_session_result": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_uint64]),
     "sz_session_commit": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
+    "sz_session_fill_synthetic": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint64]),
     "sz_session_trace_routes": (C.c_int, [C.c_void_p, C.c_int]),
     "sz_session_routes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64]),
     # host side of speculation

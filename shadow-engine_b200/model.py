@@ -265,7 +265,10 @@ class Session:
         szlib.check(self.lib.sz_session_bytes(C.byref(dm.model), ctx, self.flags, C.byref(n)))
         self.mem = torch.empty(n.value + 256, dtype=torch.uint8, device=dm.device)
         addr = self.mem.data_ptr() + (-self.mem.data_ptr()) % 256
-        self.stream = (stream or torch.cuda.current_stream(dm.device)).cuda_stream
+        # a stream of its own: the default stream cannot record CUDA graphs, which the session uses for its passes
+        torch.cuda.synchronize(dm.device)
+        self._stream = stream or torch.cuda.Stream(dm.device)
+        self.stream = self._stream.cuda_stream
         self.h = C.c_void_p()
         szlib.check(self.lib.sz_session_create(C.byref(dm.model), ctx, self.flags, addr, n.value, self.stream, C.byref(self.h)))
         self.vocab = dm.cfg["vocab"]
@@ -280,6 +283,9 @@ class Session:
 
     def reset(self):
         szlib.check(self.lib.sz_session_reset(self.h, self.stream))
+
+    def fill_synthetic(self, length, seed=1):
+        szlib.check(self.lib.sz_session_fill_synthetic(self.h, length, seed, self.stream))
 
     def trace_routes(self, on=True):
         szlib.check(self.lib.sz_session_trace_routes(self.h, 1 if on else 0))

@@ -142,3 +142,36 @@ def test_config1_sampled_spec3(tiny_cycle):
     sess = md.Session(dm, 512, kv_q8=True)
     toks, log, st = sess.generate(prompt, 96, spec_k=3, greedy=False, sampler=md.Sampler(0.7, 20, 0.9, 0.0, 11))
     assert toks == want_toks and log == want_log
+
+
+def test_graph_replay_equals_eager_launches(small):
+    # the second pass with the same (rows, head, acceptance) replays a recorded CUDA graph: same bytes as the eager first pass
+    M, hm, dm = small
+    toks = [int(t) for t in np.random.default_rng(4).integers(0, SMALL["vocab"], 16)]
+    outs = []
+    for rounds in range(2):
+        s = md.Session(dm, 64, kv_q8=True)
+        got = []
+        for lo in (0, 4, 8, 12):           # four passes of 4 rows: the first is eager, the rest are graph launches
+            s.verify(toks[lo:lo + 4]); got.append(s.result(logits=True)[2]); s.commit(4)
+        outs.append(np.concatenate(got))
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    want, _ = cpu_rows(hm, toks, True)
+    assert max(rel_err(outs[0][j], want[j]) for j in range(16)) < 1e-3
+
+
+def test_synthetic_history_gives_a_long_context(small):
+    M, hm, dm = small
+    s = md.Session(dm, 4096, kv_q8=True)
+    s.fill_synthetic(3000, seed=7)
+    assert len(s) == 3000
+    s.verify([5, 6, 7, 8]); (_, _), top, lg = s.result(logits=True); s.commit(4)
+    assert len(s) == 3004 and np.isfinite(lg).all()
+    # deterministic: the same seed gives the same logits, another seed does not
+    t = md.Session(dm, 4096, kv_q8=True)
+    t.fill_synthetic(3000, seed=7)
+    t.verify([5, 6, 7, 8]); lg2 = t.result(logits=True)[2]; t.commit(4)
+    assert np.array_equal(lg.view(np.uint32), lg2.view(np.uint32))
+    t.fill_synthetic(3000, seed=8)
+    t.verify([5, 6, 7, 8]); lg3 = t.result(logits=True)[2]; t.commit(4)
+    assert not np.array_equal(lg, lg3)
