@@ -176,6 +176,7 @@ void sz_session_destroy(sz_session* s);
 int sz_session_reset(sz_session* s, uint64_t stream);
 int sz_session_len(const sz_session* s);        /* committed positions: GpuSession::tokens().len() */
 int sz_session_capacity(const sz_session* s);   /* GpuSession::capacity() */
+int sz_session_pending(const sz_session* s);    /* rows of the pass that awaits sz_session_commit (0: none) */
 /* Feeds a prompt in passes of up to SZ_MAX_VERIFY rows.  The last pass is left pending: read it with sz_session_result (its last
  * row is the prompt's last token), then sz_session_commit(s, rows of that pass). */
 int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint64_t stream);
@@ -230,14 +231,25 @@ uint32_t sz_sample_top(const sz_sampler* sp, const uint32_t* top128, uint64_t po
 /* The draft / verify / accept / commit loop of engine.rs:2149-2454 for `--spec spec_k` with the suffix drafter (no neural
  * drafter, draft policy not consulted): generates up to max_new tokens after the prompt into `out`; pass_log receives
  * (drafted, accepted) per verify pass.  device_accept = 1 lets the device decide greedy acceptance (checked against the host). */
-typedef struct sz_gen_params { int32_t spec_k, max_new, lookup_min, greedy, eog_token, device_accept; sz_sampler sampler; } sz_gen_params;
+typedef struct sz_gen_params {
+    int32_t spec_k, max_new, lookup_min, greedy, eog_token, device_accept;
+    sz_sampler sampler;
+    int32_t max_rounds;   /* sz_generate: stop after this many rounds of the loop (0: no limit); a round is one pass, drafted or not */
+    int32_t reserved;
+} sz_gen_params;
 typedef struct sz_gen_stats {
-    int32_t n_tokens, passes, drafted, accepted, lookup_passes, reserved;
+    int32_t n_tokens, passes, drafted, accepted, lookup_passes, rounds;
     int32_t pos_tried[8], pos_right[8];
     double draft_ms, verify_ms, commit_ms;
 } sz_gen_stats;
 int sz_generate(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint32_t* out, int32_t* pass_log, int pass_cap,
                 sz_gen_stats* stats, uint64_t stream);
+/* The same loop in pieces, so that a caller can run some rounds, look, and run more: sz_gen_begin feeds the prompt, sz_gen_run runs
+ * up to `rounds` rounds (0: to the end) appending to `out` and accumulating into `stats` (zero it before the first call). */
+typedef struct sz_gen sz_gen;
+int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint64_t stream, sz_gen** out);
+int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_log, int pass_cap, sz_gen_stats* stats, uint64_t stream);
+void sz_gen_free(sz_gen* g);
 
 /* sz_moe_verify without a scratch argument.  (No counterpart in the reference: its session always owns a scratch buffer.)
  * For hosts that cannot allocate device memory once they are running - an engine that gave all of it to its own arena at start-up,

@@ -44,24 +44,32 @@ __device__ __forceinline__ size_t sz_dense_row_bytes(int type, int cols) {
     }
 }
 
-// the lane's four weights at columns e .. e + 3 of `row`, and the scale they share
+template <typename T, bool GLOBAL>
+__device__ __forceinline__ T sz_ld(const void* p) {
+    if (GLOBAL) return __ldg((const T*)p);
+    return *(const T*)p;
+}
+
+// the lane's four weights at columns e .. e + 3 of `row`, and the scale they share.  GLOBAL: `row` is in global memory (read-only
+// path); otherwise any address space (a staged copy in shared memory)
+template <bool GLOBAL = true>
 __device__ __forceinline__ void sz_dense_w4(int type, const u8* __restrict__ row, int e, const u32* grid, float* w, float& scale) {
     if (type == SZ_TYPE_F32) {
-        const float4 v = __ldg((const float4*)(row + (size_t)e * 4));
+        const float4 v = sz_ld<float4, GLOBAL>(row + (size_t)e * 4);
         w[0] = v.x; w[1] = v.y; w[2] = v.z; w[3] = v.w; scale = 1.f;
     } else if (type == SZ_TYPE_BF16) {
-        const uint2 v = __ldg((const uint2*)(row + (size_t)e * 2));
+        const uint2 v = sz_ld<uint2, GLOBAL>(row + (size_t)e * 2);
         w[0] = __uint_as_float(v.x << 16); w[1] = __uint_as_float(v.x & 0xffff0000u);
         w[2] = __uint_as_float(v.y << 16); w[3] = __uint_as_float(v.y & 0xffff0000u); scale = 1.f;
     } else if (type == SZ_TYPE_F16) {
-        const uint2 v = __ldg((const uint2*)(row + (size_t)e * 2));
+        const uint2 v = sz_ld<uint2, GLOBAL>(row + (size_t)e * 2);
         w[0] = sz_f16_to_f32((u16)(v.x & 0xffff)); w[1] = sz_f16_to_f32((u16)(v.x >> 16));
         w[2] = sz_f16_to_f32((u16)(v.y & 0xffff)); w[3] = sz_f16_to_f32((u16)(v.y >> 16)); scale = 1.f;
     } else if (type == SZ_TYPE_Q8_0) {
         const u8* blk = row + (e >> 5) * 34;
         const int i = e & 31;
-        scale = sz_f16_to_f32(__ldg((const u16*)blk));
-        const u32 q01 = __ldg((const u16*)(blk + 2 + i)), q23 = __ldg((const u16*)(blk + 4 + i));
+        scale = sz_f16_to_f32(sz_ld<u16, GLOBAL>(blk));
+        const u32 q01 = sz_ld<u16, GLOBAL>(blk + 2 + i), q23 = sz_ld<u16, GLOBAL>(blk + 4 + i);
         w[0] = (float)(int8_t)(q01 & 0xff); w[1] = (float)(int8_t)(q01 >> 8);
         w[2] = (float)(int8_t)(q23 & 0xff); w[3] = (float)(int8_t)(q23 >> 8);
     } else {  // IQ3_S
@@ -120,7 +128,7 @@ __global__ void __launch_bounds__(256) sz_dense_kernel(const SzDenseArgs a) {
             for (int j = 0; j < MT; j++) acc[j] = 0.f;
             for (int e = 4 * lane; e < a.cols; e += 128) {
                 float w[4], scale;
-                sz_dense_w4(jb.type, row, e, grid, w, scale);
+                sz_dense_w4<true>(jb.type, row, e, grid, w, scale);
 #pragma unroll
                 for (int j = 0; j < MT; j++) {
                     if (j < mt) {
@@ -141,6 +149,261 @@ __global__ void __launch_bounds__(256) sz_dense_kernel(const SzDenseArgs a) {
                 }
             }
         }
+    }
+}
+
+// ---- streaming form -------------------------------------------------------------------------------------------------------------------
+// Units of R whole rows (about 32 KB) are copied into a ring of shared-memory stages by the TMA engine (cp.async.bulk) while the
+// warps work on the previous ones.  Warp w takes RW rows of the unit (row group w % NG) and one of KP column ranges (w / NG), so an
+// x value read from shared memory feeds RW rows: the kernel is bound by the weight stream, not by shared-memory reads of x.
+// Column-range partial sums meet in shared memory.  Needs row bytes that are a multiple of 16.
+struct SzDense2Cfg {
+    int R, RW, KP, NS;       // rows a unit, rows a warp, column parts, stages
+    int unit_bytes;          // R * row bytes (the same for every job: one input width, and the jobs of a launch share a type size class)
+    int units[SZ_DENSE_MAX_JOBS + 1];  // first unit of each job; units[n_jobs] = total
+};
+
+template <int MT, int RW>
+__global__ void __launch_bounds__(256) sz_dense2_kernel(const SzDenseArgs a, const SzDense2Cfg c) {
+    extern __shared__ __align__(128) u8 smem[];
+    u64* bars = (u64*)smem;                               // NS barriers (64 bytes reserved)
+    u32* grid = (u32*)(smem + 64);                        // IQ3_S codebook
+    float* red = (float*)(smem + 64 + 2048);              // [8 warps][RW][MT]
+    float* xs = (float*)(smem + 64 + 2048 + 8 * 4 * 8 * 4);
+    u8* stages = smem + 64 + 2048 + 1024 + (size_t)MT * a.cols * 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int NG = c.R / RW;
+    const int grp = warp % NG, kp = warp / NG;
+    const int part = a.cols / c.KP;
+    const int e0 = kp * part, e1 = e0 + part;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < c.NS; i++) sz_mbar_init(&bars[i], 1);
+        sz_mbar_fence_init();
+    }
+    for (int i = threadIdx.x; i < 512; i += 256) grid[i] = c_iq3s_grid[i];
+    __syncthreads();
+    const int total = c.units[a.n_jobs];
+    auto locate = [&](int u, int& ji, int& row0, int& nrows) {
+        ji = 0;
+#pragma unroll
+        for (int q = 1; q < SZ_DENSE_MAX_JOBS; q++)
+            if (q < a.n_jobs && u >= c.units[q]) ji = q;
+        row0 = (u - c.units[ji]) * c.R;
+        nrows = min(c.R, a.job[ji].rows - row0);
+    };
+    // weights do not depend on the previous kernel: start streaming before waiting for it
+    const int first = blockIdx.x, step = gridDim.x;
+    const int count = first < total ? (total - first + step - 1) / step : 0;
+    auto issue = [&](int local, int gi) {  // local: which of this block's units; gi: running copy index over all sweeps
+        int ji, row0, nrows;
+        locate(first + local * step, ji, row0, nrows);
+        const size_t rb = sz_dense_row_bytes(a.job[ji].type, a.cols);
+        u64* bar = &bars[gi % c.NS];
+        const u32 bytes = (u32)(nrows * rb);
+        sz_mbar_expect_tx(bar, bytes);
+        sz_bulk_g2s(stages + (size_t)(gi % c.NS) * c.unit_bytes, a.job[ji].w + (size_t)row0 * rb, bytes, bar);
+    };
+    for (int j0 = 0; j0 < a.m; j0 += MT) {
+        const int mt = min(MT, a.m - j0);
+        const int base = (j0 / MT) * count;  // units issued so far (each sweep streams every unit again)
+        if (threadIdx.x == 0)
+            for (int i = 0; i < c.NS - 1 && i < count; i++) issue(i, base + i);
+        if (j0 == 0) { sz_pdl_wait(); sz_pdl_trigger(); }
+        __syncthreads();
+        for (int j = 0; j < mt; j++) {
+            const float4* src = (const float4*)(a.x + (size_t)(j0 + j) * a.xstride);
+            float4* dst = (float4*)(xs + (size_t)j * a.cols);
+            for (int i = threadIdx.x; i < a.cols / 4; i += 256) dst[i] = __ldcg(src + i);
+        }
+        __syncthreads();
+        int failed = 0;
+        for (int i = 0; i < count; i++) {
+            const int gi = base + i;
+            if (threadIdx.x == 0 && i + c.NS - 1 < count) issue(i + c.NS - 1, gi + c.NS - 1);
+            int ji, row0, nrows;
+            locate(first + i * step, ji, row0, nrows);
+            const SzDenseJob& jb = a.job[ji];
+            const size_t rb = sz_dense_row_bytes(jb.type, a.cols);
+            if (!sz_mbar_wait(&bars[gi % c.NS], (gi / c.NS) & 1)) failed = 1;
+            const u8* st = stages + (size_t)(gi % c.NS) * c.unit_bytes;
+            float acc[RW][MT];
+#pragma unroll
+            for (int r = 0; r < RW; r++)
+#pragma unroll
+                for (int j = 0; j < MT; j++) acc[r][j] = 0.f;
+            if (!failed && kp < c.KP && grp * RW < nrows) {
+                for (int e = e0 + 4 * lane; e < e1; e += 128) {
+                    float4 xv[MT];
+#pragma unroll
+                    for (int j = 0; j < MT; j++) xv[j] = j < mt ? *(const float4*)(xs + (size_t)j * a.cols + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                    for (int r = 0; r < RW; r++) {
+                        const int rr = grp * RW + r;
+                        if (rr < nrows) {
+                            float w[4], scale;
+                            sz_dense_w4<false>(jb.type, st + (size_t)rr * rb, e, grid, w, scale);
+#pragma unroll
+                            for (int j = 0; j < MT; j++) {
+                                float p = w[0] * xv[j].x;
+                                p = fmaf(w[1], xv[j].y, p);
+                                p = fmaf(w[2], xv[j].z, p);
+                                p = fmaf(w[3], xv[j].w, p);
+                                acc[r][j] = fmaf(scale, p, acc[r][j]);
+                            }
+                        }
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < RW; r++)
+#pragma unroll
+                for (int j = 0; j < MT; j++) {
+                    const float v = sz_warp_sum(acc[r][j]);
+                    if (lane == 0) red[(warp * RW + r) * MT + j] = v;
+                }
+            if (__syncthreads_or(failed)) { failed = 1; break; }
+            // the column parts of a row meet here: thread t finishes (row rr, input row j)
+            for (int t = threadIdx.x; t < nrows * mt; t += 256) {
+                const int rr = t / mt, j = t % mt;
+                const int g2 = rr / RW, r2 = rr % RW;
+                float v = 0.f;
+                for (int q = 0; q < c.KP; q++) v += red[((q * NG + g2) * RW + r2) * MT + j];
+                jb.out[(size_t)(j0 + j) * jb.ostride + row0 + rr] = sz_epilogue(jb.epi, v, jb.div);
+            }
+            __syncthreads();
+        }
+        if (failed) break;
+    }
+}
+
+// ---- Q8_0 on the tensor pipe ----------------------------------------------------------------------------------------------------------
+// The same streaming skeleton for Q8_0 matrices, with the multiply-adds on mma.sync: a warp owns one eighth of the columns of a
+// 16-row unit; per 32-column block it turns each row's 32 int8 codes into f16 exactly (0x6400 | (q ^ 0x80) is the f16 1024 + q + 128),
+// multiplies them with the rows of the pass (the B operand, split into f16 high and low parts so the activations keep f32 accuracy)
+// into a fresh accumulator and adds that, times the block's scale, to the running sums.  Per weight this is ~2.6 issue slots
+// whatever the number of rows, against ~8 for the scalar form at 4 rows, which is what lets the kernel follow the HBM stream.
+// Lane (g, q) takes the block's bytes 8 q .. 8 q + 7 of rows g and g + 8; the k slots of the two MMAs are permuted accordingly and
+// the B fragments use the same permutation (x columns 8 q .. 8 q + 7 of row-of-the-pass g).
+__device__ __forceinline__ void sz_mma16816_z(float* c, const u32* a, u32 b0, u32 b1) {  // c += a * b
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// two int8 codes (the low 16 bits of p) as an f16 pair
+__device__ __forceinline__ u32 sz_q8_pair(u32 p) {
+    const u32 t = __byte_perm(p ^ 0x8080u, 0x64646464u, 0x4140);  // 0x64 b1' 0x64 b0' with b' = b ^ 0x80
+    const __half2 h = __hsub2(*(const __half2*)&t, __halves2half2(__ushort_as_half((u16)0x6480), __ushort_as_half((u16)0x6480)));  // - 1152
+    return *(const u32*)&h;
+}
+
+struct SzDenseQ8Cfg {
+    int NS, unit_bytes;
+    int units[SZ_DENSE_MAX_JOBS + 1];
+};
+
+// grid: any; block 256; dynamic shared memory: 64 (barriers) + 4096 (reduction) + m * cols * 4 (x as f16 hi | lo) + NS * unit_bytes
+__global__ void __launch_bounds__(256, 2) sz_dense_q8_kernel(const SzDenseArgs a, const SzDenseQ8Cfg c) {
+    extern __shared__ __align__(128) u8 smem[];
+    u64* bars = (u64*)smem;
+    float* red = (float*)(smem + 64);                       // [8 warps][16 rows][8 rows of the pass]
+    __half* xhi = (__half*)(smem + 64 + 4096);              // [m][cols]
+    __half* xlo = xhi + (size_t)a.m * a.cols;
+    u8* stages = smem + 64 + 4096 + (size_t)a.m * a.cols * 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, q = lane & 3;
+    const size_t rb = (size_t)(a.cols / 32) * 34;
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < c.NS; i++) sz_mbar_init(&bars[i], 1);
+        sz_mbar_fence_init();
+    }
+    __syncthreads();
+    const int total = c.units[a.n_jobs];
+    auto locate = [&](int u, int& ji, int& row0, int& nrows) {
+        ji = 0;
+#pragma unroll
+        for (int t = 1; t < SZ_DENSE_MAX_JOBS; t++)
+            if (t < a.n_jobs && u >= c.units[t]) ji = t;
+        row0 = (u - c.units[ji]) * 16;
+        nrows = min(16, a.job[ji].rows - row0);
+    };
+    const int first = blockIdx.x, step = gridDim.x;
+    const int count = first < total ? (total - first + step - 1) / step : 0;
+    auto issue = [&](int i) {
+        int ji, row0, nrows;
+        locate(first + i * step, ji, row0, nrows);
+        u64* bar = &bars[i % c.NS];
+        const u32 bytes = (u32)(nrows * rb);
+        sz_mbar_expect_tx(bar, bytes);
+        sz_bulk_g2s(stages + (size_t)(i % c.NS) * c.unit_bytes, a.job[ji].w + (size_t)row0 * rb, bytes, bar);
+    };
+    if (threadIdx.x == 0)
+        for (int i = 0; i < c.NS - 1 && i < count; i++) issue(i);
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    for (int j = 0; j < a.m; j++)
+        for (int i = threadIdx.x; i < a.cols; i += 256) {
+            const float v = __ldcg(a.x + (size_t)j * a.xstride + i);
+            const __half hi = __float2half_rn(v);
+            xhi[(size_t)j * a.cols + i] = hi;
+            xlo[(size_t)j * a.cols + i] = __float2half_rn(v - __half2float(hi));
+        }
+    __syncthreads();
+    const int part = a.cols / 8;          // columns of this warp: [warp * part, (warp + 1) * part), whole 32-column blocks
+    const int nblk = part / 32;
+    int failed = 0;
+    for (int i = 0; i < count; i++) {
+        if (threadIdx.x == 0 && i + c.NS - 1 < count) issue(i + c.NS - 1);
+        int ji, row0, nrows;
+        locate(first + i * step, ji, row0, nrows);
+        const SzDenseJob& jb = a.job[ji];
+        if (!sz_mbar_wait(&bars[i % c.NS], (i / c.NS) & 1)) failed = 1;
+        const u8* st = stages + (size_t)(i % c.NS) * c.unit_bytes;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};  // rows g, g + 8 x rows of the pass 2 q, 2 q + 1
+        if (!failed) {
+            const u8* r0 = st + (size_t)(g < nrows ? g : 0) * rb;
+            const u8* r1 = st + (size_t)(g + 8 < nrows ? g + 8 : 0) * rb;
+            for (int b = 0; b < nblk; b++) {
+                const int blk = warp * nblk + b;
+                const int col = blk * 32 + 8 * q;
+                uint4 bh = make_uint4(0, 0, 0, 0), bl = make_uint4(0, 0, 0, 0);
+                if (g < a.m) {
+                    bh = *(const uint4*)(xhi + (size_t)g * a.cols + col);
+                    bl = *(const uint4*)(xlo + (size_t)g * a.cols + col);
+                }
+                const u8* p0 = r0 + (size_t)blk * 34;
+                const u8* p1 = r1 + (size_t)blk * 34;
+                const float d0 = sz_f16_to_f32(*(const u16*)p0), d1 = sz_f16_to_f32(*(const u16*)p1);
+                const u16* c0 = (const u16*)(p0 + 2 + 8 * q);
+                const u16* c1 = (const u16*)(p1 + 2 + 8 * q);
+                u32 a1[4], a2[4];
+                a1[0] = sz_q8_pair(c0[0]); a1[2] = sz_q8_pair(c0[1]); a2[0] = sz_q8_pair(c0[2]); a2[2] = sz_q8_pair(c0[3]);
+                a1[1] = sz_q8_pair(c1[0]); a1[3] = sz_q8_pair(c1[1]); a2[1] = sz_q8_pair(c1[2]); a2[3] = sz_q8_pair(c1[3]);
+                float t[4] = {0.f, 0.f, 0.f, 0.f};
+                sz_mma16816_z(t, a1, bh.x, bh.y);
+                sz_mma16816_z(t, a2, bh.z, bh.w);
+                sz_mma16816_z(t, a1, bl.x, bl.y);
+                sz_mma16816_z(t, a2, bl.z, bl.w);
+                acc[0] = fmaf(d0, t[0], acc[0]); acc[1] = fmaf(d0, t[1], acc[1]);
+                acc[2] = fmaf(d1, t[2], acc[2]); acc[3] = fmaf(d1, t[3], acc[3]);
+            }
+        }
+        // the eight column parts of a row meet in shared memory
+        red[(warp * 16 + g) * 8 + 2 * q] = acc[0];
+        red[(warp * 16 + g) * 8 + 2 * q + 1] = acc[1];
+        red[(warp * 16 + g + 8) * 8 + 2 * q] = acc[2];
+        red[(warp * 16 + g + 8) * 8 + 2 * q + 1] = acc[3];
+        if (__syncthreads_or(failed)) { failed = 1; break; }
+        for (int t = threadIdx.x; t < 16 * 8; t += 256) {
+            const int rr = t >> 3, j = t & 7;
+            if (rr < nrows && j < a.m) {
+                float v = 0.f;
+#pragma unroll
+                for (int w = 0; w < 8; w++) v += red[(w * 16 + rr) * 8 + j];
+                jb.out[(size_t)j * jb.ostride + row0 + rr] = sz_epilogue(jb.epi, v, jb.div);
+            }
+        }
+        __syncthreads();
     }
 }
 

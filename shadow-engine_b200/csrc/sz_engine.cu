@@ -15,6 +15,7 @@ int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* top, float* l
 int sz_session_commit(sz_session* s, int keep, uint64_t stream);
 int sz_session_len(const sz_session* s);
 int sz_session_capacity(const sz_session* s);
+int sz_session_pending(const sz_session* s);
 }
 
 // ---- prompt lookup (engine.rs:821-839) --------------------------------------------------------------------------------------------
@@ -348,35 +349,55 @@ static double now_ms() {
     return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 
-extern "C" int sz_generate(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint32_t* out, int32_t* pass_log,
-                           int pass_cap, sz_gen_stats* stats, uint64_t stream) {
-    if (!s || !prompt || n_prompt < 1 || !p || !out || !stats) return sz_fail(SZ_E_ARG, "sz_generate: null argument or empty prompt");
-    if (p->spec_k < 0 || p->spec_k > SZ_MAX_VERIFY - 1) return sz_fail(SZ_E_ARG, "sz_generate: spec_k = %d (0..%d)", p->spec_k, SZ_MAX_VERIFY - 1);
-    if (sz_session_len(s) + n_prompt + p->max_new + SZ_MAX_VERIFY > sz_session_capacity(s))
-        return sz_fail(SZ_E_ARG, "sz_generate: prompt %d + %d new tokens do not fit the session", n_prompt, p->max_new);
-    std::memset(stats, 0, sizeof(*stats));
-    std::vector<uint32_t> top(SZ_MAX_VERIFY * 128), last(128);
-    int rc = sz_session_prefill(s, (const int32_t*)prompt, n_prompt, stream);
-    if (rc) return rc;
-    const int tail = (n_prompt - 1) % SZ_MAX_VERIFY + 1;  // rows of the last prompt pass
-    if ((rc = sz_session_result(s, nullptr, top.data(), nullptr, stream))) return rc;
-    if ((rc = sz_session_commit(s, tail, stream))) return rc;
-    std::memcpy(last.data(), top.data() + (size_t)(tail - 1) * 128, 128 * 4);
+struct sz_gen {
+    sz_session* s;
+    sz_gen_params p;
+    sz_drafter* sd = nullptr;
+    std::vector<uint32_t> hist, top, last;
+    int n = 0;            // tokens emitted so far
+    bool done = false;    // an end-of-generation token was drawn
+    ~sz_gen() { sz_drafter_free(sd); }
+};
 
-    const int lookup_min = p->lookup_min;
-    sz_drafter* sd = sz_drafter_new(lookup_min < 3 ? 3 : lookup_min, 32, n_prompt + p->max_new + 64);
-    std::vector<uint32_t> hist(prompt, prompt + n_prompt);
-    sz_drafter_extend(sd, prompt, n_prompt);
+extern "C" int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint64_t stream, sz_gen** out) {
+    if (!s || !prompt || n_prompt < 1 || !p || !out) return sz_fail(SZ_E_ARG, "sz_gen_begin: null argument or empty prompt");
+    if (p->spec_k < 0 || p->spec_k > SZ_MAX_VERIFY - 1) return sz_fail(SZ_E_ARG, "sz_gen_begin: spec_k = %d (0..%d)", p->spec_k, SZ_MAX_VERIFY - 1);
+    if (sz_session_len(s) + n_prompt + p->max_new + SZ_MAX_VERIFY > sz_session_capacity(s))
+        return sz_fail(SZ_E_ARG, "sz_gen_begin: prompt %d + %d new tokens do not fit the session", n_prompt, p->max_new);
+    sz_gen* g = new sz_gen();
+    g->s = s; g->p = *p;
+    g->top.resize(SZ_MAX_VERIFY * 128); g->last.resize(128);
+    int rc = sz_session_prefill(s, (const int32_t*)prompt, n_prompt, stream);
+    const int tail = (n_prompt - 1) % SZ_MAX_VERIFY + 1;  // rows of the last prompt pass
+    if (!rc) rc = sz_session_result(s, nullptr, g->top.data(), nullptr, stream);
+    if (!rc) rc = sz_session_commit(s, tail, stream);
+    if (rc) { delete g; return rc; }
+    std::memcpy(g->last.data(), g->top.data() + (size_t)(tail - 1) * 128, 128 * 4);
+    g->sd = sz_drafter_new(p->lookup_min < 3 ? 3 : p->lookup_min, 32, n_prompt + p->max_new + 64);
+    g->hist.assign(prompt, prompt + n_prompt);
+    sz_drafter_extend(g->sd, prompt, n_prompt);
+    *out = g;
+    return SZ_OK;
+}
+
+extern "C" void sz_gen_free(sz_gen* g) { delete g; }
+
+// Runs up to `rounds` rounds of the loop (0: until max_new tokens or an end-of-generation token).  A round emits one token plus the
+// drafts it accepts.  `out` receives every token emitted so far at its position; stats accumulate over calls that pass the same struct.
+extern "C" int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_log, int pass_cap, sz_gen_stats* stats, uint64_t stream) {
+    if (!g || !out || !stats) return sz_fail(SZ_E_ARG, "sz_gen_run: null argument");
+    sz_session* s = g->s;
+    const sz_gen_params* p = &g->p;
     auto pick = [&](const uint32_t* row, uint64_t pos) -> uint32_t { return p->greedy ? row[64] : sz_sample_top(&p->sampler, row, pos); };
     auto is_eog = [&](uint32_t t) { return p->eog_token >= 0 && t == (uint32_t)p->eog_token; };
-    int n = 0;
-    rc = SZ_OK;
-    while (n < p->max_new) {
-        const uint32_t next = pick(last.data(), (uint64_t)n);
-        if (is_eog(next)) break;
+    int& n = g->n;
+    int rc = SZ_OK, done_rounds = 0;
+    while (!g->done && n < p->max_new && (rounds <= 0 || done_rounds < rounds)) {
+        const uint32_t next = pick(g->last.data(), (uint64_t)n);
+        if (is_eog(next)) { g->done = true; break; }
         out[n++] = next;
-        hist.push_back(next);
-        sz_drafter_push(sd, next);
+        g->hist.push_back(next);
+        sz_drafter_push(g->sd, next);
         int32_t batch[SZ_MAX_VERIFY];
         batch[0] = (int32_t)next;
         uint32_t draft[SZ_MAX_VERIFY];
@@ -385,46 +406,59 @@ extern "C" int sz_generate(sz_session* s, const uint32_t* prompt, int n_prompt, 
         if (p->spec_k > 0) {
             const int rem = p->max_new - n;
             const int k = p->spec_k < rem ? p->spec_k : rem;
-            if (lookup_min > 0) nd = sz_drafter_propose(sd, k, draft, &match_len);
+            if (p->lookup_min > 0) nd = sz_drafter_propose(g->sd, k, draft, &match_len);
             if (nd >= 2) stats->lookup_passes++;
             else {
-                nd = sz_drafter_propose_with_min(sd, k, 3, draft, &match_len);
-                if (nd == 0) { const int lens[2] = {3, 2}; nd = sz_lookup(hist.data(), (int)hist.size(), k, lens, 2, draft); }
+                nd = sz_drafter_propose_with_min(g->sd, k, 3, draft, &match_len);
+                if (nd == 0) { const int lens[2] = {3, 2}; nd = sz_lookup(g->hist.data(), (int)g->hist.size(), k, lens, 2, draft); }
             }
         }
         const double t1 = now_ms();
         stats->draft_ms += t1 - t0;
         for (int i = 0; i < nd; i++) batch[1 + i] = (int32_t)draft[i];
         const int m = 1 + nd;
-        const bool dev_accept = p->greedy && p->device_accept && nd > 0;
+        const bool dev_accept = p->greedy && p->device_accept;
         if ((rc = sz_session_verify(s, batch, m, dev_accept ? SZ_ACCEPT_GREEDY : SZ_ACCEPT_NONE, p->eog_token, 1, stream))) break;
         int32_t kn[2] = {1, 0};
-        if ((rc = sz_session_result(s, dev_accept ? kn : nullptr, top.data(), nullptr, stream))) break;
+        if ((rc = sz_session_result(s, dev_accept ? kn : nullptr, g->top.data(), nullptr, stream))) break;
         const double t2 = now_ms();
         stats->verify_ms += t2 - t1;
         int keep = 1;
         for (int i = 0; i < nd; i++) {
             stats->pos_tried[i < 7 ? i : 7]++;
-            const uint32_t want = pick(top.data() + (size_t)i * 128, (uint64_t)n);
+            const uint32_t want = pick(g->top.data() + (size_t)i * 128, (uint64_t)n);
             if (want != draft[i] || is_eog(draft[i])) break;
             out[n++] = draft[i];
             keep++;
             stats->pos_right[i < 7 ? i : 7]++;
-            hist.push_back(draft[i]);
-            sz_drafter_push(sd, draft[i]);
+            g->hist.push_back(draft[i]);
+            sz_drafter_push(g->sd, draft[i]);
         }
         if (dev_accept && kn[0] != keep) { rc = sz_fail(SZ_E_DEVICE, "device acceptance kept %d rows, the host loop %d", kn[0], keep); break; }
         if ((rc = sz_session_commit(s, keep, stream))) break;
         stats->commit_ms += now_ms() - t2;
+        stats->rounds++;
+        done_rounds++;
         if (nd > 0) {
             stats->passes++;
             stats->drafted += nd;
             stats->accepted += keep - 1;
             if (pass_log && stats->passes <= pass_cap) { pass_log[2 * (stats->passes - 1)] = nd; pass_log[2 * (stats->passes - 1) + 1] = keep - 1; }
         }
-        std::memcpy(last.data(), top.data() + (size_t)(keep - 1) * 128, 128 * 4);
+        std::memcpy(g->last.data(), g->top.data() + (size_t)(keep - 1) * 128, 128 * 4);
     }
-    sz_drafter_free(sd);
     stats->n_tokens = n;
+    return rc;
+}
+
+extern "C" int sz_generate(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint32_t* out, int32_t* pass_log,
+                           int pass_cap, sz_gen_stats* stats, uint64_t stream) {
+    if (!stats || !out) return sz_fail(SZ_E_ARG, "sz_generate: null argument");
+    std::memset(stats, 0, sizeof(*stats));
+    sz_gen* g = nullptr;
+    int rc = sz_gen_begin(s, prompt, n_prompt, p, stream, &g);
+    if (rc) return rc;
+    rc = sz_gen_run(g, p->max_rounds, out, pass_log, pass_cap, stats, stream);
+    sz_gen_free(g);
     return rc;
 }

@@ -267,19 +267,26 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
 extern "C" void sz_session_destroy(sz_session* s) { delete s; }
 extern "C" int sz_session_len(const sz_session* s) { return s ? s->len : -1; }
 extern "C" int sz_session_capacity(const sz_session* s) { return s ? s->ctx : -1; }
+extern "C" int sz_session_pending(const sz_session* s) { return s ? s->last_m : -1; }
 extern "C" int sz_session_trace_routes(sz_session* s, int on) { if (!s) return sz_fail(SZ_E_ARG, "null session"); s->want_routes = on; return SZ_OK; }
 
 // ---- dense launcher -----------------------------------------------------------------------------------------------------------------
-int sz_dense_launch(SzDenseArgs& a, cudaStream_t st, const char* name) {
-    int total = 0;
-    for (int i = 0; i < a.n_jobs; i++) { a.job[i].row0 = total; total += a.job[i].rows; }
-    a.total_rows = total;
+static size_t sz_row_bytes_host(int type, int cols) {
+    switch (type) {
+        case SZ_TYPE_F32: return (size_t)cols * 4;
+        case SZ_TYPE_F16: case SZ_TYPE_BF16: return (size_t)cols * 2;
+        case SZ_TYPE_Q8_0: return (size_t)(cols / 32) * 34;
+        default: return (size_t)(cols / 256) * 110;
+    }
+}
+
+static int sz_dense_launch_generic(SzDenseArgs& a, cudaStream_t st, const char* name) {
     const size_t limit = 200 * 1024 - 2048;
     int mt = a.m;
     while (mt > 1 && (size_t)mt * a.cols * 4 > limit) mt = (mt + 1) / 2;
     if ((size_t)mt * a.cols * 4 > limit) return sz_fail(SZ_E_ARG, "%s: %d input columns do not fit in shared memory", name, a.cols);
     const size_t smem = 2048 + (size_t)mt * a.cols * 4;
-    int blocks = (total + 7) / 8;
+    int blocks = (a.total_rows + 7) / 8;
     const int cap = 148 * 8;
     if (blocks > cap) blocks = cap;
     static bool set[9] = {false};
@@ -292,6 +299,79 @@ int sz_dense_launch(SzDenseArgs& a, cudaStream_t st, const char* name) {
         SZ_DENSE_CASE(1) SZ_DENSE_CASE(2) SZ_DENSE_CASE(3) SZ_DENSE_CASE(4) SZ_DENSE_CASE(5) SZ_DENSE_CASE(6) SZ_DENSE_CASE(7) SZ_DENSE_CASE(8)
     }
 #undef SZ_DENSE_CASE
+    return SZ_OK;
+}
+
+template <int MT, int RW>
+static int sz_dense2_go(const SzDenseArgs& a, const SzDense2Cfg& c, int blocks, size_t smem, cudaStream_t st, const char* name) {
+    static bool set = false;
+    if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_dense2_kernel<MT, RW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); set = true; }
+    SZ_CUDA(sz_launch(name, sz_dense2_kernel<MT, RW>, dim3(blocks), dim3(256), smem, st, true, a, c));
+    return SZ_OK;
+}
+
+int sz_dense_launch(SzDenseArgs& a, cudaStream_t st, const char* name) {
+    int total = 0;
+    for (int i = 0; i < a.n_jobs; i++) { a.job[i].row0 = total; total += a.job[i].rows; }
+    a.total_rows = total;
+    static const bool generic_only = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;
+    // the streaming kernel wants one type for all jobs of the launch and rows that are whole 16-byte chunks
+    const int type = a.job[0].type;
+    const size_t rb = sz_row_bytes_host(type, a.cols);
+    bool ok = !generic_only && rb % 16 == 0 && rb <= 96 * 1024;
+    for (int i = 1; i < a.n_jobs; i++) ok = ok && a.job[i].type == type;
+    if (!ok) return sz_dense_launch_generic(a, st, name);
+    if (type == SZ_TYPE_Q8_0 && a.cols % 256 == 0) {
+        // tensor-pipe form: 16-row units, the columns split over the 8 warps
+        SzDenseQ8Cfg q = {};
+        q.unit_bytes = (int)(16 * rb);
+        const size_t fixed = 64 + 4096 + (size_t)a.m * a.cols * 4;
+        size_t budget = 110 * 1024;                        // two blocks a multiprocessor when that leaves at least two stages
+        if (fixed + 2 * (size_t)q.unit_bytes > budget) budget = 216 * 1024;
+        if (fixed + 2 * (size_t)q.unit_bytes <= budget) {
+            int NS = (int)((budget - fixed) / q.unit_bytes);
+            q.NS = NS > 4 ? 4 : NS;
+            int units = 0;
+            for (int i = 0; i < a.n_jobs; i++) { q.units[i] = units; units += (a.job[i].rows + 15) / 16; }
+            q.units[a.n_jobs] = units;
+            const size_t smem = fixed + (size_t)q.NS * q.unit_bytes;
+            int blocks = 148 * (smem <= 110 * 1024 ? 2 : 1);
+            if (blocks > units) blocks = units;
+            static bool set = false;
+            if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_dense_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); set = true; }
+            SZ_CUDA(sz_launch(name, sz_dense_q8_kernel, dim3(blocks), dim3(256), smem, st, true, a, q));
+            return SZ_OK;
+        }
+    }
+    SzDense2Cfg c = {};
+    int R = 32;
+    while (R > 2 && (size_t)R * rb > 36 * 1024) R >>= 1;
+    c.R = R;
+    c.RW = R < 4 ? R : 4;
+    const int NG = R / c.RW;
+    int KP = 8 / NG;
+    const int gran = type == SZ_TYPE_Q8_0 ? 32 : (type == SZ_TYPE_IQ3_S ? 256 : 4);
+    while (KP > 1 && (a.cols % (KP * gran) != 0)) KP >>= 1;
+    c.KP = KP;
+    c.unit_bytes = (int)((size_t)R * rb);
+    const size_t budget = 216 * 1024, fixed = 64 + 2048 + 1024;
+    int mt = a.m;
+    while (mt > 1 && fixed + (size_t)mt * a.cols * 4 + 2 * (size_t)c.unit_bytes > budget) mt = (mt + 1) / 2;
+    if (fixed + (size_t)mt * a.cols * 4 + 2 * (size_t)c.unit_bytes > budget) return sz_dense_launch_generic(a, st, name);
+    int NS = (int)((budget - fixed - (size_t)mt * a.cols * 4) / c.unit_bytes);
+    c.NS = NS > 4 ? 4 : NS;
+    int units = 0;
+    for (int i = 0; i < a.n_jobs; i++) { c.units[i] = units; units += (a.job[i].rows + R - 1) / R; }
+    c.units[a.n_jobs] = units;
+    const size_t smem = fixed + (size_t)mt * a.cols * 4 + (size_t)c.NS * c.unit_bytes;
+    const int per_sm = (int)((227 * 1024) / (smem + 1024));
+    int blocks = 148 * (per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm));
+    if (blocks > units) blocks = units;
+#define SZ_D2(MT)                                                                                   \
+    case MT:                                                                                        \
+        return c.RW == 4 ? sz_dense2_go<MT, 4>(a, c, blocks, smem, st, name) : sz_dense2_go<MT, 2>(a, c, blocks, smem, st, name);
+    switch (mt) { SZ_D2(1) SZ_D2(2) SZ_D2(3) SZ_D2(4) SZ_D2(5) SZ_D2(6) SZ_D2(7) SZ_D2(8) }
+#undef SZ_D2
     return SZ_OK;
 }
 

@@ -54,6 +54,7 @@ SYMBOLS = {
     "sz_session_reset": (C.c_int, [C.c_void_p, C.c_uint64]),
     "sz_session_len": (C.c_int, [C.c_void_p]),
     "sz_session_capacity": (C.c_int, [C.c_void_p]),
+    "sz_session_pending": (C.c_int, [C.c_void_p]),
     "sz_session_prefill": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64]),
     "sz_session_verify": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64]),
     "sz_session_result": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_uint64]),
@@ -83,6 +84,9 @@ SYMBOLS = {
     "sz_sample_top": (C.c_uint32, [C.c_void_p, C.POINTER(C.c_uint32), C.c_uint64]),
     "sz_generate": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.c_int,
                               C.c_void_p, C.c_uint64]),
+    "sz_gen_begin": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]),
+    "sz_gen_run": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.c_int, C.c_void_p, C.c_uint64]),
+    "sz_gen_free": (None, [C.c_void_p]),
     "sz_moe_static_scratch_max": (C.c_int, [C.POINTER(C.c_int64)]),
     "sz_moe_verify_static": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
 }

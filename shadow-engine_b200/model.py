@@ -40,11 +40,12 @@ class Sampler(C.Structure):
 
 
 class GenParams(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("spec_k", "max_new", "lookup_min", "greedy", "eog_token", "device_accept")] + [("sampler", Sampler)]
+    _fields_ = [(n, C.c_int32) for n in ("spec_k", "max_new", "lookup_min", "greedy", "eog_token", "device_accept")] + [("sampler", Sampler)] + \
+               [("max_rounds", C.c_int32), ("reserved", C.c_int32)]
 
 
 class GenStats(C.Structure):
-    _fields_ = [(n, C.c_int32) for n in ("n_tokens", "passes", "drafted", "accepted", "lookup_passes", "reserved")] + \
+    _fields_ = [(n, C.c_int32) for n in ("n_tokens", "passes", "drafted", "accepted", "lookup_passes", "rounds")] + \
                [("pos_tried", C.c_int32 * 8), ("pos_right", C.c_int32 * 8), ("draft_ms", C.c_double), ("verify_ms", C.c_double), ("commit_ms", C.c_double)]
 
 
@@ -320,9 +321,9 @@ class Session:
     def commit(self, keep):
         szlib.check(self.lib.sz_session_commit(self.h, keep, self.stream))
 
-    def generate(self, prompt, max_new, spec_k=3, greedy=True, sampler=None, lookup_min=4, eog=-1, device_accept=True):
+    def generate(self, prompt, max_new, spec_k=3, greedy=True, sampler=None, lookup_min=4, eog=-1, device_accept=True, max_rounds=0):
         p = GenParams(spec_k, max_new, lookup_min, 1 if greedy else 0, eog, 1 if device_accept else 0,
-                      sampler or Sampler(1.0, 20, 0.95, 0.0, 1))
+                      sampler or Sampler(1.0, 20, 0.95, 0.0, 1), max_rounds, 0)
         pr = (C.c_uint32 * len(prompt))(*[int(t) for t in prompt])
         out = (C.c_uint32 * max_new)()
         log = (C.c_int32 * (2 * max_new))()
@@ -330,6 +331,34 @@ class Session:
         szlib.check(self.lib.sz_generate(self.h, pr, len(prompt), C.byref(p), out, log, max_new, C.byref(st), self.stream))
         n = st.n_tokens
         return list(out[:n]), [(log[2 * i], log[2 * i + 1]) for i in range(st.passes)], st
+
+
+class Generator:
+    """The loop in pieces (sz_gen_begin / sz_gen_run): feed the prompt, then run rounds and look at the statistics in between."""
+
+    def __init__(self, sess, prompt, max_new, spec_k=3, greedy=True, sampler=None, lookup_min=4, eog=-1, device_accept=True):
+        self.sess, self.lib = sess, sess.lib
+        self.p = GenParams(spec_k, max_new, lookup_min, 1 if greedy else 0, eog, 1 if device_accept else 0,
+                           sampler or Sampler(1.0, 20, 0.95, 0.0, 1), 0, 0)
+        pr = (C.c_uint32 * len(prompt))(*[int(t) for t in prompt])
+        self.h = C.c_void_p()
+        szlib.check(self.lib.sz_gen_begin(sess.h, pr, len(prompt), C.byref(self.p), sess.stream, C.byref(self.h)))
+        self.out = (C.c_uint32 * max_new)()
+        self.log = (C.c_int32 * (2 * max_new))()
+        self.max_new = max_new
+        self.stats = GenStats()
+
+    def run(self, rounds=0):
+        szlib.check(self.lib.sz_gen_run(self.h, rounds, self.out, self.log, self.max_new, C.byref(self.stats), self.sess.stream))
+        return self.stats
+
+    def tokens(self):
+        return list(self.out[:self.stats.n_tokens])
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            self.lib.sz_gen_free(self.h)
+            self.h = None
 
 
 def make_prompt(n_tokens, vocab, seed=1, block=16, substitute=0.1, cycles=None):
