@@ -43,7 +43,7 @@ struct sz_session {
     double* route_w;
     u8* moe_scratch;
     int64_t moe_scratch_bytes;
-    int attn_splits;
+    int attn_splits, attn_splits2;
     // host staging (pinned, so that a captured graph re-reads it at every launch)
     int32_t* h_pin;   // [0..8): ids of the pass, [8]: keep of a host-decided commit
     int pending_committed;  // the pending pass was already committed on the device (acceptance modes GREEDY / ALL)
@@ -62,7 +62,7 @@ struct SzSessLayout {
     int64_t r, rn, hdown, mix, u, g, y, d_xin, d_z, d_b, d_a, d_xc, d_beta, d_decay, d_og, S0, S1, conv0, conv1, a_qg, a_k, a_v, a_q, a_gate,
         a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, total;
     int64_t moe_bytes, S_bytes, conv_bytes, kv_bytes;
-    int splits;
+    int splits, splits2;
 };
 
 static int64_t up256(int64_t v) { return (v + 255) & ~(int64_t)255; }
@@ -95,7 +95,12 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
         if (splits < 1) splits = 1;
     }
     L->splits = splits;
-    L->a_part = take(4 * M * c.n_head * splits * (c.head_dim + 2));
+    // the grouped kernel: one block per (kv head, split), about one block a multiprocessor
+    int splits2 = 148 / (c.n_kv_head > 0 ? c.n_kv_head : 1);
+    if (splits2 > (ctx + 255) / 256) splits2 = (ctx + 255) / 256;
+    if (splits2 < 1) splits2 = 1;
+    L->splits2 = splits2;
+    L->a_part = take(4 * M * c.n_head * (splits > splits2 ? splits : splits2) * (c.head_dim + 2));
     const int64_t hb = (flags & SZ_KV_Q8) ? (c.head_dim + (((c.head_dim >> 5) * 2 + 15) & ~15)) : 4 * (int64_t)c.head_dim;
     L->kv_bytes = (int64_t)(n_attn > 0 ? n_attn : 1) * ctx * c.n_kv_head * hb;
     L->kc = take(L->kv_bytes); L->vc = take(L->kv_bytes);
@@ -258,7 +263,7 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->logits = (float*)(b + L.logits); s->tk_tmp = (u64*)(b + L.tk_tmp); s->top = (u32*)(b + L.top);
     s->ids = (int32_t*)(b + L.ids); s->res = (int32_t*)(b + L.res); s->state = (int32_t*)(b + L.state); s->routes = (int32_t*)(b + L.routes); s->route_w = (double*)(b + L.route_w);
     s->moe_scratch = b + L.moe; s->moe_scratch_bytes = L.moe_bytes;
-    s->attn_splits = L.splits;
+    s->attn_splits = L.splits; s->attn_splits2 = L.splits2;
     if ((rc = sz_session_reset(s, stream))) { delete s; return rc; }
     *out = s;
     return SZ_OK;
@@ -461,8 +466,28 @@ template <int EPL>
 static int sz_attn_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m) {
     const sz_model_config& c = s->model.cfg;
     SZ_CUDA(sz_launch("attention", sz_attn_kernel<EPL>, dim3(c.n_head, m, s->attn_splits), dim3(256), 0, st, true, (const float*)s->a_q, kc, vc,
-                      (int)c.n_head, (int)c.n_kv_head, (const int32_t*)s->state, (s->flags & SZ_KV_Q8) ? 1 : 0, s->attn_splits, s->a_part));
+                      (int)c.n_head, (int)c.n_kv_head, s->ctx, (const int32_t*)s->state, (s->flags & SZ_KV_Q8) ? 1 : 0, s->attn_splits, s->a_part));
     return SZ_OK;
+}
+
+template <int HD, int NQT>
+static int sz_attn2_go(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m) {
+    const sz_model_config& c = s->model.cfg;
+    static bool set = false;
+    const size_t smem = (size_t)SzAttn2<HD>::smem_bytes(NQT);
+    if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_attn2_kernel<HD, NQT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
+    SZ_CUDA(sz_launch("attention_grouped", sz_attn2_kernel<HD, NQT>, dim3(c.n_kv_head, s->attn_splits2), dim3(256), smem, st, true, (const float*)s->a_q,
+                      kc, vc, (int)c.n_head, (int)c.n_kv_head, m, s->ctx, (const int32_t*)s->state, s->attn_splits2, s->a_part, (u32*)(s->state + 2)));
+    return SZ_OK;
+}
+
+template <int HD>
+static int sz_attn2_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m) {
+    const sz_model_config& c = s->model.cfg;
+    const int qv = c.n_head / c.n_kv_head * m;
+    if (qv <= 16) return sz_attn2_go<HD, 1>(s, st, kc, vc, m);
+    if (qv <= 32) return sz_attn2_go<HD, 2>(s, st, kc, vc, m);
+    return sz_attn2_go<HD, 4>(s, st, kc, vc, m);
 }
 
 static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
@@ -482,14 +507,24 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     int rc = sz_dense_launch(a, st, "attn_proj");
     if (rc) return rc;
     SZ_CUDA(sz_launch("attn_prep", sz_attn_prep_kernel, dim3(nh + 2 * nkv, m), dim3(128), 0, st, true, (const float*)s->a_qg, (const float*)s->a_k,
-                      (const float*)s->a_v, (const float*)L.attn_q_norm.data, (const float*)L.attn_k_norm.data, nh, nkv, hd, c.eps,
+                      (const float*)s->a_v, (const float*)L.attn_q_norm.data, (const float*)L.attn_k_norm.data, nh, nkv, hd, s->ctx, c.eps,
                       (const int32_t*)s->state, (int)c.rope_dims, c.rope_theta, q8, kc, vc, s->a_q, s->a_gate));
-    if (hd == 64) rc = sz_attn_launch<2>(s, st, kc, vc, m);
-    else if (hd == 128) rc = sz_attn_launch<4>(s, st, kc, vc, m);
-    else rc = sz_attn_launch<8>(s, st, kc, vc, m);
+    // the grouped tensor-core kernel serves the packed int8 cache with up to 64 queries a KV head; the simple kernel everything else
+    static const bool generic_only = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;
+    const bool grouped = q8 && !generic_only && (nh / nkv) * m <= 64;
+    int splits = grouped ? s->attn_splits2 : s->attn_splits;
+    if (grouped) {
+        if (hd == 64) rc = sz_attn2_launch<64>(s, st, kc, vc, m);
+        else if (hd == 128) rc = sz_attn2_launch<128>(s, st, kc, vc, m);
+        else rc = sz_attn2_launch<256>(s, st, kc, vc, m);
+    } else {
+        if (hd == 64) rc = sz_attn_launch<2>(s, st, kc, vc, m);
+        else if (hd == 128) rc = sz_attn_launch<4>(s, st, kc, vc, m);
+        else rc = sz_attn_launch<8>(s, st, kc, vc, m);
+    }
     if (rc) return rc;
     SZ_CUDA(sz_launch("attn_merge", sz_attn_merge_kernel, dim3(nh, m), dim3(256), 0, st, true, (const float*)s->a_part, (const float*)s->a_gate, nh, hd,
-                      s->attn_splits, s->a_o));
+                      splits, s->a_o));
     SzDenseArgs b = {};
     b.x = s->a_o; b.xstride = nh * hd; b.cols = nh * hd; b.m = m; b.n_jobs = 1;
     b.job[0] = sz_job(L.attn_output, s->y, H);
@@ -667,15 +702,16 @@ extern "C" int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint
 // ---- synthetic history (benchmarks) -------------------------------------------------------------------------------------------------
 // Fills the first `len` positions of every attention layer's cache with seeded pseudo-random keys and values (and small random
 // DeltaNet states), as if `len` tokens had been fed: a long context without running a long prefill.
-__global__ void sz_fill_kv_kernel(u8* __restrict__ kc, int64_t bytes_per_layer_used, int64_t layer_stride, int hd, int q8, u32 seed) {
+__global__ void sz_fill_kv_kernel(u8* __restrict__ kc, int len, int ctx, int nkv, int64_t layer_stride, int hd, int q8, u32 seed) {
     const int layer = blockIdx.y;
     u8* base = kc + layer * layer_stride;
     const int hb = q8 ? sz_kv_head_bytes(hd) : hd * 4;
-    const int64_t heads = bytes_per_layer_used / hb;
-    for (int64_t h = blockIdx.x; h < heads; h += gridDim.x) {
-        u8* p = base + h * hb;
+    const int64_t heads = (int64_t)nkv * len;
+    for (int64_t hp = blockIdx.x; hp < heads; hp += gridDim.x) {
+        const int64_t h = hp / len, pos = hp % len;
+        u8* p = base + (h * ctx + pos) * hb;
         for (int i = threadIdx.x; i < hd; i += blockDim.x) {
-            u32 x = (u32)(h * 2654435761u) ^ (u32)(i * 40503u) ^ seed ^ (u32)(layer * 97u);
+            u32 x = (u32)(hp * 2654435761u) ^ (u32)(i * 40503u) ^ seed ^ (u32)(layer * 97u);
             x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
             if (q8) p[i] = (u8)(int8_t)((int)(x % 255u) - 127);
             else ((float*)p)[i] = ((float)(x % 2001u) - 1000.0f) * 1e-3f;
@@ -697,9 +733,9 @@ extern "C" int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, 
     if (s->n_attn > 0 && len > 0) {
         const int q8 = (s->flags & SZ_KV_Q8) ? 1 : 0;
         const int64_t hb = q8 ? (c.head_dim + (((c.head_dim >> 5) * 2 + 15) & ~15)) : 4 * (int64_t)c.head_dim;
-        const int64_t stride = (int64_t)s->ctx * c.n_kv_head * hb, used = (int64_t)len * c.n_kv_head * hb;
-        sz_fill_kv_kernel<<<dim3(1024, s->n_attn), 128, 0, st>>>(s->kc, used, stride, c.head_dim, q8, seed);
-        sz_fill_kv_kernel<<<dim3(1024, s->n_attn), 128, 0, st>>>(s->vc, used, stride, c.head_dim, q8, seed ^ 0x9e3779b9u);
+        const int64_t stride = (int64_t)s->ctx * c.n_kv_head * hb;
+        sz_fill_kv_kernel<<<dim3(1024, s->n_attn), 128, 0, st>>>(s->kc, len, s->ctx, (int)c.n_kv_head, stride, (int)c.head_dim, q8, seed);
+        sz_fill_kv_kernel<<<dim3(1024, s->n_attn), 128, 0, st>>>(s->vc, len, s->ctx, (int)c.n_kv_head, stride, (int)c.head_dim, q8, seed ^ 0x9e3779b9u);
         SZ_CUDA(cudaGetLastError());
     }
     s->h_pin[8] = len;

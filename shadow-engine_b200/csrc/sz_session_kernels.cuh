@@ -232,8 +232,9 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
 }
 
 // ---- attention front end (forward.rs:908-927): per head RMSNorm + NeoX RoPE of q and k, the gate halves, K and V into the cache.
-// grid (nh + 2 nkv, m), block 128.  Q8 cache rows: [pos][nkv][hd i8 | hd/32 f16 scales, zero-padded to 16 bytes] (the reference's
-// packed Q8_KV, kernels/forward.cu:3652-3687); f32 cache rows: [pos][nkv][hd].
+// grid (nh + 2 nkv, m), block 128.  Q8 cache: [kv head][pos][hd i8 | hd/32 f16 scales, zero-padded to 16 bytes] - the reference's packed
+// Q8_KV head (kernels/forward.cu:3652-3687), stored per head so that a range of positions of one head is contiguous; f32 cache:
+// [kv head][pos][hd].
 __device__ __forceinline__ int sz_kv_head_bytes(int hd) { return hd + (((hd >> 5) * 2 + 15) & ~15); }
 
 __device__ __forceinline__ void sz_kv_store(const float* src, int hd, int q8, u8* dst_q8, float* dst_f32) {
@@ -262,18 +263,18 @@ __device__ __forceinline__ void sz_kv_store(const float* src, int hd, int q8, u8
 
 __global__ void __launch_bounds__(128)
 sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, const float* __restrict__ vv, const float* __restrict__ wq,
-                    const float* __restrict__ wk, int nh, int nkv, int hd, float eps, const int32_t* __restrict__ state, int rope_dims, double theta,
-                    int q8, u8* __restrict__ kc, u8* __restrict__ vc, float* __restrict__ q, float* __restrict__ gate) {
+                    const float* __restrict__ wk, int nh, int nkv, int hd, int ctx, float eps, const int32_t* __restrict__ state, int rope_dims,
+                    double theta, int q8, u8* __restrict__ kc, u8* __restrict__ vc, float* __restrict__ q, float* __restrict__ gate) {
     __shared__ float tmp[512];
     __shared__ double red[8];
     sz_pdl_wait();
     sz_pdl_trigger();
     const int b = blockIdx.x, j = blockIdx.y;
     const int pos = state[0] + j;
-    const size_t row_q8 = (size_t)nkv * sz_kv_head_bytes(hd), row_f = (size_t)nkv * hd * 4;
+    const size_t hbytes = q8 ? (size_t)sz_kv_head_bytes(hd) : (size_t)hd * 4;  // the cache is [kv head][position][head bytes]
     if (b >= nh + nkv) {  // V head: raw into the cache
         const int h = b - nh - nkv;
-        u8* dst = vc + (size_t)pos * (q8 ? row_q8 : row_f) + (size_t)h * (q8 ? sz_kv_head_bytes(hd) : hd * 4);
+        u8* dst = vc + ((size_t)h * ctx + pos) * hbytes;
         sz_kv_store(vv + ((size_t)j * nkv + h) * hd, hd, q8, dst, (float*)dst);
         return;
     }
@@ -302,7 +303,7 @@ sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, 
         }
     } else {
         const int h = b - nh;
-        u8* dst = kc + (size_t)pos * (q8 ? row_q8 : row_f) + (size_t)h * (q8 ? sz_kv_head_bytes(hd) : hd * 4);
+        u8* dst = kc + ((size_t)h * ctx + pos) * hbytes;
         sz_kv_store(tmp, hd, q8, dst, (float*)dst);
     }
 }
@@ -312,7 +313,7 @@ sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, 
 // merged per block; partial (max, sum, acc[hd]) per split.  part: [m][nh][splits][hd + 2].
 template <int EPL>  // elements per lane = hd / 32
 __global__ void __launch_bounds__(256)
-sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8* __restrict__ vc, int nh, int nkv,
+sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8* __restrict__ vc, int nh, int nkv, int ctx,
                const int32_t* __restrict__ state, int q8, int splits, float* __restrict__ part) {
     constexpr int HD = EPL * 32;
     __shared__ float sm_m[8], sm_s[8];
@@ -326,7 +327,7 @@ sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8*
     const int per = (n + splits - 1) / splits;
     const int t0 = sp * per, t1 = min(n, t0 + per);
     const int hb = sz_kv_head_bytes(HD);
-    const size_t rowb = (size_t)nkv * (q8 ? hb : HD * 4), headb = (size_t)g * (q8 ? hb : HD * 4);
+    const size_t rowb = (size_t)(q8 ? hb : HD * 4), headb = (size_t)g * ctx * rowb;
     float qv[EPL];
 #pragma unroll
     for (int e = 0; e < EPL; e++) qv[e] = q[((size_t)j * nh + h) * HD + lane * EPL + e];
@@ -377,6 +378,245 @@ sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8*
         }
         out[threadIdx.x] = a;
         if (threadIdx.x == 0) { out[HD] = M; out[HD + 1] = ssum; }
+    }
+}
+
+// ---- masked attention, grouped form --------------------------------------------------------------------------------------------------
+// A block takes one KV head and one range of positions and serves every query that shares the head: the G = nh / nkv heads of the
+// group times the m rows of the pass (up to 64 query vectors), so each key and value byte leaves HBM once per layer instead of once
+// per query.  Both contractions run on mma.sync: scores = Q K^T with the int8 keys turned into f16 exactly and the per-32 scales
+// applied to 32-dimension partial sums; out += P V with the value scales folded into P.  Chunks of 64 positions are staged by the
+// TMA engine (the cache is laid out per head, so a chunk is one contiguous copy), double-buffered.  Online softmax per query; the
+// partial (out, max, sum) of the block goes to the same merge kernel as the simple form.
+// Query vector qv = j * G + hh (row j of the pass, head hh of the group); row j attends to positions < pos0 + j + 1.
+#define SZ_AT_T 64
+template <int HD>
+struct SzAttn2 {
+    static constexpr int HB = HD + (((HD >> 5) * 2 + 15) & ~15);
+    static constexpr int KS = HD / 16;            // k-steps of the score contraction
+    static constexpr int DW = HD / 8;             // output dimensions of a warp
+    static constexpr int NT = DW / 8;             // its n-tiles
+    static constexpr int SST = SZ_AT_T + 2;       // row stride of the score / probability tile (floats)
+    static constexpr int STAGE = 2 * SZ_AT_T * HB;  // K chunk then V chunk
+    static int smem_bytes(int nqt) { return 64 + 2 * STAGE + nqt * KS * 32 * 16 * 2 + 64 * SST * 4 + 64 * 3 * 4; }
+};
+
+template <int HD, int NQT>
+__global__ void __launch_bounds__(256)
+sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const u8* __restrict__ vc, int nh, int nkv, int m, int ctx,
+                const int32_t* __restrict__ state, int splits, float* __restrict__ part, u32* __restrict__ err) {
+    using A = SzAttn2<HD>;
+    extern __shared__ __align__(128) u8 smem[];
+    u64* bars = (u64*)smem;
+    u8* stage = smem + 64;
+    uint4* qhi = (uint4*)(smem + 64 + 2 * A::STAGE);
+    uint4* qlo = qhi + NQT * A::KS * 32;
+    float* S = (float*)(qlo + NQT * A::KS * 32);          // [64][SST]
+    float* rmax = S + 64 * A::SST;                           // running max, sum, and this chunk's rescale factor per query
+    float* rsum = rmax + 64;
+    float* ralpha = rsum + 64;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, q4 = lane & 3;
+    const int kvh = blockIdx.x, sp = blockIdx.y;
+    const int G = nh / nkv, QV = G * m;
+    if (threadIdx.x == 0) {
+        sz_mbar_init(&bars[0], 1);
+        sz_mbar_init(&bars[1], 1);
+        sz_mbar_fence_init();
+    }
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int pos0 = state[0];
+    const int nmax = pos0 + m;
+    const int per = ((nmax + splits - 1) / splits + SZ_AT_T - 1) / SZ_AT_T * SZ_AT_T;
+    const int t0 = sp * per, t1 = min(nmax, t0 + per);
+    const int nchunk = t1 > t0 ? (t1 - t0 + SZ_AT_T - 1) / SZ_AT_T : 0;
+    const u8* kbase = kc + (size_t)kvh * ctx * A::HB;
+    const u8* vbase = vc + (size_t)kvh * ctx * A::HB;
+    // the queries as A fragments (f16 high and low parts), scaled by 1 / sqrt(HD)
+    const float scale = rsqrtf((float)HD);
+    for (int e = threadIdx.x; e < NQT * A::KS * 32; e += 256) {
+        const int ln = e & 31, ks = (e >> 5) % A::KS, qt = e / (32 * A::KS);
+        const int gg = ln >> 2, qq = ln & 3;
+        u32 hi[4], lo[4];
+#pragma unroll
+        for (int r = 0; r < 4; r++) {
+            const int qv = qt * 16 + gg + 8 * (r & 1);
+            const int dim = ks * 16 + 2 * qq + 8 * (r >> 1);
+            float v0 = 0.f, v1 = 0.f;
+            if (qv < QV) {
+                const int j = qv / G, h = kvh * G + qv % G;
+                const float* src = qin + ((size_t)j * nh + h) * HD + dim;
+                v0 = src[0] * scale; v1 = src[1] * scale;
+            }
+            const __half h0 = __float2half_rn(v0), h1 = __float2half_rn(v1);
+            const __half l0 = __float2half_rn(v0 - __half2float(h0)), l1 = __float2half_rn(v1 - __half2float(h1));
+            hi[r] = (u32)__half_as_ushort(h0) | ((u32)__half_as_ushort(h1) << 16);
+            lo[r] = (u32)__half_as_ushort(l0) | ((u32)__half_as_ushort(l1) << 16);
+        }
+        qhi[e] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        qlo[e] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+    }
+    if (threadIdx.x < 64) { rmax[threadIdx.x] = -INFINITY; rsum[threadIdx.x] = 0.f; }
+    auto issue = [&](int ci) {  // thread 0: chunk ci of this block into stage ci & 1
+        const int t = t0 + ci * SZ_AT_T;
+        const u32 bytes = (u32)(min(SZ_AT_T, t1 - t) * A::HB);
+        u64* bar = &bars[ci & 1];
+        u8* dst = stage + (size_t)(ci & 1) * A::STAGE;
+        sz_mbar_expect_tx(bar, 2 * bytes);
+        sz_bulk_g2s(dst, kbase + (size_t)t * A::HB, bytes, bar);
+        sz_bulk_g2s(dst + SZ_AT_T * A::HB, vbase + (size_t)t * A::HB, bytes, bar);
+    };
+    if (threadIdx.x == 0 && nchunk > 0) issue(0);
+    __syncthreads();
+    float o[NQT][A::NT][4];
+#pragma unroll
+    for (int a = 0; a < NQT; a++)
+#pragma unroll
+        for (int b = 0; b < A::NT; b++) { o[a][b][0] = 0.f; o[a][b][1] = 0.f; o[a][b][2] = 0.f; o[a][b][3] = 0.f; }
+    int failed = 0;
+    for (int ci = 0; ci < nchunk; ci++) {
+        if (threadIdx.x == 0 && ci + 1 < nchunk) issue(ci + 1);
+        if (!sz_mbar_wait(&bars[ci & 1], (ci >> 1) & 1)) failed = 1;
+        if (__syncthreads_or(failed)) { failed = 1; break; }
+        const u8* kch = stage + (size_t)(ci & 1) * A::STAGE;
+        const u8* vch = kch + SZ_AT_T * A::HB;
+        const int tbase = t0 + ci * SZ_AT_T;
+        // ---- scores of the chunk: warp w takes positions 8 w .. 8 w + 7
+        {
+            float sacc[NQT][4];
+#pragma unroll
+            for (int a = 0; a < NQT; a++) { sacc[a][0] = 0.f; sacc[a][1] = 0.f; sacc[a][2] = 0.f; sacc[a][3] = 0.f; }
+            const u8* krow = kch + (size_t)(8 * warp + g8) * A::HB;                 // the position this lane feeds as B
+            const u16* ksc0 = (const u16*)(kch + (size_t)(8 * warp + 2 * q4) * A::HB + HD);  // scales of the positions of its C columns
+            const u16* ksc1 = (const u16*)(kch + (size_t)(8 * warp + 2 * q4 + 1) * A::HB + HD);
+#pragma unroll 2
+            for (int grp = 0; grp < HD / 32; grp++) {
+                float t[NQT][4];
+#pragma unroll
+                for (int a = 0; a < NQT; a++) { t[a][0] = 0.f; t[a][1] = 0.f; t[a][2] = 0.f; t[a][3] = 0.f; }
+#pragma unroll
+                for (int kk = 0; kk < 2; kk++) {
+                    const int ks = grp * 2 + kk;
+                    const u32 b0 = sz_q8_pair(*(const u16*)(krow + ks * 16 + 2 * q4));
+                    const u32 b1 = sz_q8_pair(*(const u16*)(krow + ks * 16 + 8 + 2 * q4));
+#pragma unroll
+                    for (int a = 0; a < NQT; a++) {
+                        const uint4 ah = qhi[(a * A::KS + ks) * 32 + lane], al = qlo[(a * A::KS + ks) * 32 + lane];
+                        sz_mma16816_z(t[a], (const u32*)&ah, b0, b1);
+                        sz_mma16816_z(t[a], (const u32*)&al, b0, b1);
+                    }
+                }
+                const float s0 = sz_f16_to_f32(ksc0[grp]), s1 = sz_f16_to_f32(ksc1[grp]);
+#pragma unroll
+                for (int a = 0; a < NQT; a++) {
+                    sacc[a][0] = fmaf(s0, t[a][0], sacc[a][0]); sacc[a][1] = fmaf(s1, t[a][1], sacc[a][1]);
+                    sacc[a][2] = fmaf(s0, t[a][2], sacc[a][2]); sacc[a][3] = fmaf(s1, t[a][3], sacc[a][3]);
+                }
+            }
+#pragma unroll
+            for (int a = 0; a < NQT; a++) {
+                float* r0 = S + (size_t)(a * 16 + g8) * A::SST + 8 * warp + 2 * q4;
+                float* r1 = S + (size_t)(a * 16 + g8 + 8) * A::SST + 8 * warp + 2 * q4;
+                r0[0] = sacc[a][0]; r0[1] = sacc[a][1]; r1[0] = sacc[a][2]; r1[1] = sacc[a][3];
+            }
+        }
+        __syncthreads();
+        // ---- online softmax: four threads a query, 16 positions each
+        {
+            const int qv = threadIdx.x >> 2, sub = threadIdx.x & 3;
+            if (qv < NQT * 16) {
+                const int lim = qv < QV ? min(pos0 + qv / G + 1, t1) - tbase : 0;  // positions of the chunk this query may see
+                float* row = S + (size_t)qv * A::SST + sub * 16;
+                float mx = -INFINITY;
+#pragma unroll
+                for (int i = 0; i < 16; i++) if (sub * 16 + i < lim) mx = fmaxf(mx, row[i]);
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                const float mo = rmax[qv];
+                const float mn = fmaxf(mo, mx);
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    const float p = (sub * 16 + i < lim) ? __expf(row[i] - mn) : 0.f;
+                    row[i] = p;
+                    sum += p;
+                }
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                if (sub == 0) {
+                    const float al = mn == -INFINITY ? 1.f : __expf(mo - mn);
+                    ralpha[qv] = al;
+                    rsum[qv] = rsum[qv] * al + sum;
+                    rmax[qv] = mn;
+                }
+            }
+        }
+        __syncthreads();
+        // ---- out += P V: warp w takes dimensions w DW .. w DW + DW - 1, whose values share one scale group
+        {
+            const int d0 = warp * A::DW, vgrp = d0 >> 5;
+#pragma unroll
+            for (int a = 0; a < NQT; a++) {
+                const float al0 = ralpha[a * 16 + g8], al1 = ralpha[a * 16 + g8 + 8];
+#pragma unroll
+                for (int b = 0; b < A::NT; b++) { o[a][b][0] *= al0; o[a][b][1] *= al0; o[a][b][2] *= al1; o[a][b][3] *= al1; }
+            }
+#pragma unroll
+            for (int kk = 0; kk < SZ_AT_T / 16; kk++) {
+                const int p0 = kk * 16 + 2 * q4;  // positions p0, p0 + 1, p0 + 8, p0 + 9 are this lane's k slots
+                float vs[4];
+#pragma unroll
+                for (int r = 0; r < 4; r++) vs[r] = sz_f16_to_f32(*(const u16*)(vch + (size_t)(p0 + (r & 1) + 8 * (r >> 1)) * A::HB + HD + 2 * vgrp));
+                u32 bf[A::NT][2];
+#pragma unroll
+                for (int b = 0; b < A::NT; b++) {
+                    const int dim = d0 + 8 * b + g8;
+                    const u32 v00 = vch[(size_t)p0 * A::HB + dim], v01 = vch[(size_t)(p0 + 1) * A::HB + dim];
+                    const u32 v10 = vch[(size_t)(p0 + 8) * A::HB + dim], v11 = vch[(size_t)(p0 + 9) * A::HB + dim];
+                    bf[b][0] = sz_q8_pair(v00 | (v01 << 8));
+                    bf[b][1] = sz_q8_pair(v10 | (v11 << 8));
+                }
+#pragma unroll
+                for (int a = 0; a < NQT; a++) {
+                    u32 af[4];
+#pragma unroll
+                    for (int r = 0; r < 4; r++) {
+                        // a0: (query g, k p0..), a1: (query g + 8, k p0..), a2: (query g, k p0 + 8..), a3: (query g + 8, k p0 + 8..)
+                        const float* pr = S + (size_t)(a * 16 + g8 + 8 * (r & 1)) * A::SST + p0 + 8 * (r >> 1);
+                        const float pa = pr[0], pb = pr[1];
+                        const float wa = pa > 0.f ? pa * vs[2 * (r >> 1)] : 0.f, wb = pb > 0.f ? pb * vs[2 * (r >> 1) + 1] : 0.f;
+                        af[r] = (u32)__half_as_ushort(__float2half_rn(wa)) | ((u32)__half_as_ushort(__float2half_rn(wb)) << 16);
+                    }
+#pragma unroll
+                    for (int b = 0; b < A::NT; b++) sz_mma16816_z(o[a][b], af, bf[b][0], bf[b][1]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (failed) { if (threadIdx.x == 0) atomicExch(err, 2u); return; }
+    // ---- the block's partial result, in the merge kernel's layout: [row][head][split][HD + 2]
+#pragma unroll
+    for (int a = 0; a < NQT; a++)
+#pragma unroll
+        for (int r = 0; r < 2; r++) {
+            const int qv = a * 16 + g8 + 8 * r;
+            if (qv < QV) {
+                const int j = qv / G, h = kvh * G + qv % G;
+                float* out = part + (((size_t)j * nh + h) * splits + sp) * (HD + 2);
+#pragma unroll
+                for (int b = 0; b < A::NT; b++) {
+                    const int dim = warp * A::DW + 8 * b + 2 * q4;
+                    out[dim] = o[a][b][2 * r];
+                    out[dim + 1] = o[a][b][2 * r + 1];
+                }
+            }
+        }
+    if (threadIdx.x < QV) {
+        const int qv = threadIdx.x, j = qv / G, h = kvh * G + qv % G;
+        float* out = part + (((size_t)j * nh + h) * splits + sp) * (HD + 2);
+        out[HD] = rmax[qv];
+        out[HD + 1] = rsum[qv];
     }
 }
 
