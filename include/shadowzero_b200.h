@@ -86,6 +86,9 @@ typedef struct sz_moe_layer {
     uint64_t gate, up, down;                        /* expert e's matrix starts at base + e * stride bytes */
     uint64_t gate_stride, up_stride, down_stride;
     uint64_t sh_gate, sh_up, sh_down;
+    /* Expert parallelism: this GPU holds experts [ep_first, ep_first + ep_count) of the layer; gate / up / down then point at the
+     * first LOCAL expert.  ep_count = 0: all of them (no sharding).  ep_shared = 1 on the one rank that adds the shared expert. */
+    int32_t ep_first, ep_count, ep_shared, ep_reserved;
 } sz_moe_layer;
 /* Matrices are stored as the reference stores them: ggml [cols = in, rows = out], whole rows contiguous, for the block
  * types; one blob (f16 suh | f16 svh | 4-byte marker | trellis) for EXL3 (crates/shadowzero-model/src/exl3.rs:388-398).
@@ -250,6 +253,24 @@ typedef struct sz_gen sz_gen;
 int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint64_t stream, sz_gen** out);
 int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_log, int pass_cap, sz_gen_stats* stats, uint64_t stream);
 void sz_gen_free(sz_gen* g);
+
+/* ---- expert parallelism over NCCL ------------------------------------------------------------------------------------------
+ * No counterpart in the reference (its only multi-GPU mode is a two-stage layer split through host memory,
+ * crates/shadowzero-cuda/src/session.rs:6945-7015; expert parallelism was estimated and not built, docs/STATUS.md:1922).
+ * Experts are sharded by contiguous id range; router, attention, DeltaNet and the head are replicated, so every rank routes
+ * the same rows by itself and runs only the experts it holds: the dispatch exchange is empty.  The combine is one all-reduce
+ * per MoE layer of the weighted expert outputs as 64-bit fixed point (scale 2^40): integer addition is exact, so the result is
+ * the same bits for any number of ranks.  sz_ep_unique_id makes the NCCL id on one rank; the host carries it to the others
+ * (torch.distributed, MPI, a file); sz_ep_init joins.  One communicator per process; NCCL is loaded with dlopen at this point. */
+int sz_ep_unique_id(uint8_t id[128]);
+int sz_ep_init(int rank, int world, const uint8_t id[128]);
+int sz_ep_world(void);
+void sz_ep_destroy(void);
+/* The two halves of an expert-parallel MoE pass, for hosts that exchange the partial sums themselves (and for testing several
+ * ranks on one GPU): the partial (int64 [m][hidden], this rank's experts only), and the conversion of a summed buffer to f32. */
+int sz_moe_verify_partial(const sz_moe_layer* layer, uint64_t x, int m, uint64_t y_fix, uint64_t scratch, int64_t scratch_bytes,
+                          uint64_t stream);
+int sz_moe_finish(uint64_t y_fix, int m, int hidden, uint64_t y, uint64_t stream);
 
 /* sz_moe_verify without a scratch argument.  (No counterpart in the reference: its session always owns a scratch buffer.)
  * For hosts that cannot allocate device memory once they are running - an engine that gave all of it to its own arena at start-up,

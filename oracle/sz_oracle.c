@@ -474,14 +474,18 @@ void szo_moe(const szo_moe_layer* L, const float* u, float* y, int32_t* route_id
         szo_matvec(L->expert_type, L->down + e * L->down_stride, (size_t)H, (size_t)FF, g, out, threads);
         for (int i = 0; i < H; i++) acc[i] += rw[t] * (double)out[i];
     }
-    szo_matvec(L->shared_type, L->sh_gate, (size_t)SF, (size_t)H, u, g, threads);
-    szo_matvec(L->shared_type, L->sh_up, (size_t)SF, (size_t)H, u, up, threads);
-    for (int i = 0; i < SF; i++) g[i] = szo_silu(g[i]) * up[i];
-    szo_matvec(L->shared_type, L->sh_down, (size_t)H, (size_t)SF, g, out, threads);
-    float sgl;
-    szo_matvec(SZO_F32, (const uint8_t*)L->shared_router, 1, (size_t)H, u, &sgl, 1);
-    float sg = szo_sigmoid(sgl);
-    for (int i = 0; i < H; i++) y[i] = (float)(acc[i] + (double)(sg * out[i]));
+    if (SF > 0) {
+        szo_matvec(L->shared_type, L->sh_gate, (size_t)SF, (size_t)H, u, g, threads);
+        szo_matvec(L->shared_type, L->sh_up, (size_t)SF, (size_t)H, u, up, threads);
+        for (int i = 0; i < SF; i++) g[i] = szo_silu(g[i]) * up[i];
+        szo_matvec(L->shared_type, L->sh_down, (size_t)H, (size_t)SF, g, out, threads);
+        float sgl;
+        szo_matvec(SZO_F32, (const uint8_t*)L->shared_router, 1, (size_t)H, u, &sgl, 1);
+        float sg = szo_sigmoid(sgl);
+        for (int i = 0; i < H; i++) y[i] = (float)(acc[i] + (double)(sg * out[i]));
+    } else { /* a layer without a shared expert (not a shape the reference's model has) */
+        for (int i = 0; i < H; i++) y[i] = (float)acc[i];
+    }
     if (route_idx) for (int t = 0; t < k; t++) route_idx[t] = t < nk ? idx[t] : -1;
     if (route_w) for (int t = 0; t < k; t++) route_w[t] = t < nk ? rw[t] : 0.0;
     if (logits_out) memcpy(logits_out, logits, (size_t)L->n_expert * sizeof(float));

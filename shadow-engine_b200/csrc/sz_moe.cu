@@ -10,46 +10,122 @@
 // ---------------------------------------------------------------------------------------------------------------------------------
 // router: logits (a warp a router row, f64 accumulate), then the last block to finish does softmax, top-k and the plan
 
-#define SZ_ROUTE_WARPS 4
+#define SZ_ROUTE_WARPS 8
 
 __device__ __forceinline__ bool sz_better(float ad, int ai, float bd, int bi) { return ad > bd || (ad == bd && ai < bi); }
 
+// The row's best untaken logit among the NQ values a lane holds (experts lane + 32 q): four independent scans, then merged, so the
+// dependency chain is NQ / 4 long.
+template <int NQ>
+__device__ __forceinline__ void sz_lane_best(const float* d, u32 taken, int lane, int ne, float& bd, int& bi) {
+    float cd[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+    int ci[4] = {0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff};
+#pragma unroll
+    for (int q = 0; q < NQ; q++) {
+        const int i = lane + 32 * q;
+        if (i < ne && !((taken >> q) & 1u) && sz_better(d[q], i, cd[q & 3], ci[q & 3])) { cd[q & 3] = d[q]; ci[q & 3] = i; }
+    }
+    if (sz_better(cd[1], ci[1], cd[0], ci[0])) { cd[0] = cd[1]; ci[0] = ci[1]; }
+    if (sz_better(cd[3], ci[3], cd[2], ci[2])) { cd[2] = cd[3]; ci[2] = ci[3]; }
+    if (sz_better(cd[2], ci[2], cd[0], ci[0])) { cd[0] = cd[2]; ci[0] = ci[2]; }
+    bd = cd[0]; bi = ci[0];
+}
+
+// One row of the pass: max, top-k, weights.  A warp; the row's logits in registers.
+template <int NQ>
+__device__ __forceinline__ void sz_route_row(const float* __restrict__ logits_row, int ne, int k, int lane, int* sel_row, int32_t* ridx_row,
+                                             double* rw_row, int32_t* out_idx_row, double* out_w_row) {
+    float d[NQ];
+    float mx = -FLT_MAX;  // f32::MIN, forward.rs:1093
+#pragma unroll
+    for (int q = 0; q < NQ; q++) {
+        const int i = lane + 32 * q;
+        d[q] = i < ne ? __ldcg(logits_row + i) : -INFINITY;
+        if (i < ne) mx = fmaxf(mx, d[q]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+#pragma unroll
+    for (int q = 0; q < NQ; q++) d[q] = d[q] - mx;  // in f32, as the reference subtracts before widening
+    // top-k by (value descending, index ascending); exp is monotone, so the order of d is the order of exp(d)
+    u32 taken = 0;
+    float mine = 0.f;  // lane t keeps the value of rank t
+    int my_e = 0;
+    for (int t = 0; t < k; t++) {
+        float bd;
+        int bi;
+        sz_lane_best<NQ>(d, taken, lane, ne, bd, bi);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float od = __shfl_xor_sync(0xffffffffu, bd, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (sz_better(od, oi, bd, bi)) { bd = od; bi = oi; }
+        }
+        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
+        if (lane == t) { mine = bd; my_e = bi; }
+    }
+    // weights: softmax over all experts, then the chosen ones renormalised - the full sum cancels, so only the k chosen
+    // exponentials are needed: w_t = exp(d_t) / sum over ranks (in rank order) of exp(d_t')
+    const double ex = lane < k ? exp((double)mine) : 0.0;
+    double tz = 0.0;
+    for (int t = 0; t < k; t++) tz += __shfl_sync(0xffffffffu, ex, t);
+    if (lane < k) {
+        const double wv = ex / tz;
+        sel_row[lane] = my_e;
+        ridx_row[lane] = my_e;
+        rw_row[lane] = wv;
+        if (out_idx_row) out_idx_row[lane] = my_e;
+        if (out_w_row) out_w_row[lane] = wv;
+    }
+    __syncwarp();
+}
+
+// grid: ceil(rows / 8) blocks of 8 warps; dynamic shared memory m * H * 4 (the rows of the pass, staged once per block).
 __global__ void __launch_bounds__(SZ_ROUTE_WARPS * 32)
 sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restrict__ router, const float* __restrict__ shared_router,
                 int ne, int k, float* __restrict__ logits, int32_t* __restrict__ ridx, double* __restrict__ rw, SzPlan* __restrict__ plan,
                 SzPlan* __restrict__ plan_sh, u32* __restrict__ ctrl, int32_t* __restrict__ out_idx, double* __restrict__ out_w,
-                uint4* __restrict__ zero, int zero_n) {
+                uint4* __restrict__ zero, int zero_n, int ep_first, int ep_count) {
+    extern __shared__ __align__(16) float xs[];  // [m][H]
     __shared__ int cnt[SZ_MAX_EXPERTS];
     __shared__ int slot_of[SZ_MAX_EXPERTS];
     __shared__ int sel[SZ_MAX_VERIFY * SZ_MAX_TOPK];
     __shared__ int s_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ld = ne + 1;
+    // this block's router rows do not depend on the previous kernel: fetch them before waiting for it (16 float4 loads in flight a lane)
+    const int r = blockIdx.x * SZ_ROUTE_WARPS + warp;
+    const bool live = r < ne || (r == ne && shared_router != nullptr);
+    const float4* wrow = (const float4*)(r < ne ? router + (size_t)r * H : shared_router);
+    constexpr int WN = 16;  // float4 chunks of the row a lane keeps in flight: covers hidden <= 2048 in one sweep
+    float4 w[WN];
+#pragma unroll
+    for (int u = 0; u < WN; u++) w[u] = (live && 32 * u + lane < H / 4) ? __ldg(wrow + 32 * u + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
     sz_pdl_wait();
     sz_pdl_trigger();
     // the streaming kernels' fixed-point accumulators start every call at zero
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_n; i += gridDim.x * blockDim.x) zero[i] = make_uint4(0, 0, 0, 0);
+    for (int i = threadIdx.x; i < m * H / 4; i += blockDim.x) ((float4*)xs)[i] = __ldcg((const float4*)x + i);
+    __syncthreads();
 
-    // ---- logits: row r of the router (row ne: the shared expert's gate) against every x row
-    const int r = blockIdx.x * SZ_ROUTE_WARPS + warp;
-    if (r < ne || (r == ne && shared_router != nullptr)) {
-        const float4* wrow = (const float4*)(r < ne ? router + (size_t)r * H : shared_router);
+    // ---- logits: row r of the router (row ne: the shared expert's gate) against every x row, f64 accumulate
+    if (live) {
         double acc[SZ_MAX_VERIFY];
 #pragma unroll
         for (int j = 0; j < SZ_MAX_VERIFY; j++) acc[j] = 0.0;
-        // four independent row loads in flight per lane (hidden is a multiple of 128 floats = 32 lanes x float4)
-        for (int c0 = 0; c0 < H / 4; c0 += 128) {
-            float4 w[4];
+        for (int c0 = 0; c0 < H / 4; c0 += 32 * WN) {
+            if (c0 > 0) {
 #pragma unroll
-            for (int u = 0; u < 4; u++) w[u] = c0 + 32 * u + lane < H / 4 ? __ldg(wrow + c0 + 32 * u + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int u = 0; u < WN; u++) w[u] = c0 + 32 * u + lane < H / 4 ? __ldg(wrow + c0 + 32 * u + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
+            for (int u = 0; u < WN; u++) {
                 const int c = c0 + 32 * u + lane;
                 if (c < H / 4) {
 #pragma unroll
                     for (int j = 0; j < SZ_MAX_VERIFY; j++) {
                         if (j < m) {
-                            const float4 v = __ldg((const float4*)(x + (size_t)j * H) + c);
+                            const float4 v = ((const float4*)xs)[(size_t)j * (H / 4) + c];
                             acc[j] += (double)w[u].x * (double)v.x;
                             acc[j] += (double)w[u].y * (double)v.y;
                             acc[j] += (double)w[u].z * (double)v.z;
@@ -77,62 +153,23 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
     __threadfence();
 
     for (int j = warp; j < m; j += SZ_ROUTE_WARPS) {
-        // the row's logits in registers: lane holds experts lane + 32 q
-        float d[SZ_MAX_EXPERTS / 32];
-        float mx = -FLT_MAX;  // f32::MIN, forward.rs:1093
-#pragma unroll
-        for (int q = 0; q < SZ_MAX_EXPERTS / 32; q++) {
-            const int i = lane + 32 * q;
-            d[q] = i < ne ? __ldcg(logits + (size_t)j * ld + i) : -INFINITY;
-            if (i < ne) mx = fmaxf(mx, d[q]);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-#pragma unroll
-        for (int q = 0; q < SZ_MAX_EXPERTS / 32; q++) d[q] = d[q] - mx;  // in f32, as the reference subtracts before widening
-        // top-k by (value descending, index ascending); exp is monotone, so the order of d is the order of exp(d)
-        u32 taken = 0;
-        float mine = 0.f;  // lane t keeps the value of rank t
-        for (int t = 0; t < k; t++) {
-            float bd = -INFINITY;
-            int bi = 0x7fffffff;
-#pragma unroll
-            for (int q = 0; q < SZ_MAX_EXPERTS / 32; q++) {
-                const int i = lane + 32 * q;
-                if (i < ne && !((taken >> q) & 1u) && sz_better(d[q], i, bd, bi)) { bd = d[q]; bi = i; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float od = __shfl_xor_sync(0xffffffffu, bd, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-                if (sz_better(od, oi, bd, bi)) { bd = od; bi = oi; }
-            }
-            if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-            if (lane == t) mine = bd;
-            if (lane == 0) sel[j * SZ_MAX_TOPK + t] = bi;
-        }
-        // weights: softmax over all experts, then the chosen ones renormalised - the full sum cancels, so only the k chosen
-        // exponentials are needed: w_t = exp(d_t) / sum over ranks (in rank order) of exp(d_t')
-        const double ex = lane < k ? exp((double)mine) : 0.0;
-        double tz = 0.0;
-        for (int t = 0; t < k; t++) tz += __shfl_sync(0xffffffffu, ex, t);
-        __syncwarp();
-        if (lane < k) {
-            const int e = sel[j * SZ_MAX_TOPK + lane];
-            const double wv = ex / tz;
-            ridx[j * k + lane] = e;
-            rw[j * k + lane] = wv;
-            if (out_idx) out_idx[j * k + lane] = e;
-            if (out_w) out_w[j * k + lane] = wv;
-        }
-        __syncwarp();
+        int32_t* oi = out_idx ? out_idx + j * k : nullptr;
+        double* ow = out_w ? out_w + j * k : nullptr;
+        if (ne <= 256) sz_route_row<8>(logits + (size_t)j * ld, ne, k, lane, sel + j * SZ_MAX_TOPK, ridx + j * k, rw + j * k, oi, ow);
+        else if (ne <= 512) sz_route_row<16>(logits + (size_t)j * ld, ne, k, lane, sel + j * SZ_MAX_TOPK, ridx + j * k, rw + j * k, oi, ow);
+        else sz_route_row<32>(logits + (size_t)j * ld, ne, k, lane, sel + j * SZ_MAX_TOPK, ridx + j * k, rw + j * k, oi, ow);
     }
     for (int i = threadIdx.x; i < ne; i += blockDim.x) cnt[i] = 0;
     __syncthreads();
 
     // ---- plan: groups in ascending expert order, rows ascending inside a group
+    // with expert parallelism only the experts this rank holds enter the plan; routing itself is the same on every rank
     const int pairs = m * k;
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&cnt[sel[(p / k) * SZ_MAX_TOPK + p % k]], 1);
+    const int e_lo = ep_count > 0 ? ep_first : 0, e_hi = ep_count > 0 ? ep_first + ep_count : ne;
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = sel[(p / k) * SZ_MAX_TOPK + p % k];
+        if (e >= e_lo && e < e_hi) atomicAdd(&cnt[e], 1);
+    }
     __syncthreads();
     if (warp == 0) {
         int running = 0;
@@ -154,6 +191,7 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int j = p / k;
         const int e = sel[j * SZ_MAX_TOPK + p % k];
+        if (e < e_lo || e >= e_hi) continue;
         int pos = 0;
         for (int jj = 0; jj < j; jj++)
             for (int t = 0; t < k; t++) pos += (sel[jj * SZ_MAX_TOPK + t] == e);
@@ -414,21 +452,46 @@ sz_exl3_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 s
 // ---------------------------------------------------------------------------------------------------------------------------------
 // y[j] = sum over ranks of w * eo (f64, rank order) + sigmoid(shared gate logit) * shared output (forward.rs:1020-1033)
 
+// With expert parallelism (e_lo..e_hi the experts this rank holds, y_fix != null) only the local pairs count and every term is
+// added as 64-bit fixed point (scale 2^40), so that the all-reduce over ranks - integer addition - gives the same bits for any
+// number of ranks.
+#define SZ_YFIX_SCALE 1099511627776.0          // 2^40
+#define SZ_YFIX_INV (1.0 / 1099511627776.0)
+
 __global__ void __launch_bounds__(256)
-sz_combine_kernel(const float* __restrict__ eo, const double* __restrict__ rw, const float* __restrict__ so,
-                  const float* __restrict__ logits, int ne, int k, int H, int has_shared, float* __restrict__ y) {
+sz_combine_kernel(const float* __restrict__ eo, const int32_t* __restrict__ ridx, const double* __restrict__ rw, const float* __restrict__ so,
+                  const float* __restrict__ logits, int ne, int k, int H, int has_shared, float* __restrict__ y, long long* __restrict__ y_fix,
+                  int e_lo, int e_hi) {
     sz_pdl_wait();
     sz_pdl_trigger();
     const int j = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= H) return;
     double acc = 0.0;
-    for (int t = 0; t < k; t++) acc += __ldcg(rw + j * k + t) * (double)__ldcg(eo + (size_t)(j * k + t) * H + i);
+    long long fix = 0;
+    for (int t = 0; t < k; t++) {
+        if (y_fix) {
+            const int e = __ldcg(ridx + j * k + t);
+            if (e < e_lo || e >= e_hi) continue;
+            fix += __double2ll_rn(__ldcg(rw + j * k + t) * (double)__ldcg(eo + (size_t)(j * k + t) * H + i) * SZ_YFIX_SCALE);
+        } else {
+            acc += __ldcg(rw + j * k + t) * (double)__ldcg(eo + (size_t)(j * k + t) * H + i);
+        }
+    }
     if (has_shared) {
         const float sg = sz_sigmoid(__ldcg(logits + (size_t)j * (ne + 1) + ne));
-        acc += (double)(sg * __ldcg(so + (size_t)j * H + i));
+        const double sv = (double)(sg * __ldcg(so + (size_t)j * H + i));
+        if (y_fix) fix += __double2ll_rn(sv * SZ_YFIX_SCALE); else acc += sv;
     }
-    y[(size_t)j * H + i] = (float)acc;
+    if (y_fix) y_fix[(size_t)j * H + i] = fix; else y[(size_t)j * H + i] = (float)acc;
+}
+
+// the summed fixed-point output back to f32
+__global__ void __launch_bounds__(256) sz_yfix_finish_kernel(const long long* __restrict__ y_fix, int n, float* __restrict__ y) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) y[i] = (float)((double)__ldcg(y_fix + i) * SZ_YFIX_INV);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
@@ -482,6 +545,8 @@ static int sz_moe_check(const sz_moe_layer* L, int m) {
     if (L->top_k < 1 || L->top_k > SZ_MAX_TOPK || L->top_k > L->n_expert)
         return sz_fail(SZ_E_ARG, "top_k = %d (1..%d, at most n_expert)", L->top_k, SZ_MAX_TOPK);
     if (L->expert_ff <= 0 || L->shared_ff < 0) return sz_fail(SZ_E_ARG, "expert_ff = %d, shared_ff = %d", L->expert_ff, L->shared_ff);
+    if (L->ep_count < 0 || L->ep_first < 0 || (L->ep_count > 0 && L->ep_first + L->ep_count > L->n_expert))
+        return sz_fail(SZ_E_ARG, "expert shard [%d, %d) of %d experts", L->ep_first, L->ep_first + L->ep_count, L->n_expert);
     int rc;
     if ((rc = sz_check_matrix("expert gate/up", L->expert_type, L->hidden, L->expert_ff))) return rc;
     if ((rc = sz_check_matrix("expert down", L->expert_type, L->expert_ff, L->hidden))) return rc;
@@ -491,7 +556,7 @@ static int sz_moe_check(const sz_moe_layer* L, int m) {
     if ((rc = sz_check_align("expert gate", L->expert_type, L->gate, L->hidden, L->expert_ff))) return rc;
     if ((rc = sz_check_align("expert up", L->expert_type, L->up, L->hidden, L->expert_ff))) return rc;
     if ((rc = sz_check_align("expert down", L->expert_type, L->down, L->expert_ff, L->hidden))) return rc;
-    if (L->shared_ff > 0) {
+    if (L->shared_ff > 0 && (L->ep_count == 0 || L->ep_shared)) {  // a shard that does not add the shared term holds none of it
         if ((rc = sz_check_matrix("shared gate/up", L->shared_type, L->hidden, L->shared_ff))) return rc;
         if ((rc = sz_check_matrix("shared down", L->shared_type, L->shared_ff, L->hidden))) return rc;
         if (!L->shared_router || !L->sh_gate || !L->sh_up || !L->sh_down) return sz_fail(SZ_E_ARG, "null shared-expert tensor");
@@ -520,8 +585,9 @@ extern "C" int sz_moe_scratch_init(uint64_t scratch, int64_t scratch_bytes, uint
 extern "C" int sz_moe_launches(const sz_moe_layer* L) {
     if (!L) return 0;
     const SzFast f = sz_fast_path(L);
-    if (f.exl3) return 4 + (L->shared_ff > 0 && !f.shared_fused ? 2 : 0);
-    return L->shared_ff > 0 ? 6 : 4;
+    const int ep = L->ep_count > 0 ? 1 : 0;  // the fixed-point finish (the all-reduce is NCCL's kernel, not counted)
+    if (f.exl3) return 4 + (L->shared_ff > 0 && !f.shared_fused ? 2 : 0) + ep;
+    return (L->shared_ff > 0 ? 6 : 4) + ep;
 }
 
 template <int TYPE>
@@ -608,15 +674,29 @@ static int sz_x3_launch(cudaStream_t st, const sz_moe_layer* L, int m, const SzP
     return sz_fail(SZ_E_TYPE, "no streaming EXL3 kernel for K = %d, FF = %d", K, L->expert_ff);
 }
 
-extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t y, uint64_t route_idx, uint64_t route_w,
-                             uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
-    int rc = sz_moe_check(L, m);
+int sz_ep_allreduce_i64(long long* buf, size_t count, cudaStream_t st);  // sz_ep.cu
+extern "C" int sz_ep_world(void);
+
+// The pass itself.  y_fix == null: the whole layer into y (f32).  y_fix != null: expert-parallel share - only the experts this rank
+// holds (and the shared expert where ep_shared says so) - as 64-bit fixed point into y_fix; y is not touched.
+static int sz_moe_run(const sz_moe_layer* L0, uint64_t x, int m, float* y, long long* y_fix, uint64_t route_idx, uint64_t route_w, uint64_t scratch,
+                      int64_t scratch_bytes, uint64_t stream) {
+    int rc = sz_moe_check(L0, m);
     if (rc) return rc;
-    if (!x || !y || !sz_aligned16(x) || !sz_aligned16(y)) return sz_fail(SZ_E_ARG, "x and y must be non-null and 16-byte aligned");
+    if (!x || !sz_aligned16(x)) return sz_fail(SZ_E_ARG, "x must be non-null and 16-byte aligned");
     if ((route_idx & 3) || (route_w & 7)) return sz_fail(SZ_E_ARG, "misaligned routing output");
-    const SzMoeScratch S = sz_moe_layout(L, m);
+    const SzMoeScratch S = sz_moe_layout(L0, m);
     if (!scratch || (scratch & 255)) return sz_fail(SZ_E_ARG, "scratch must be 256-byte aligned");
     if (scratch_bytes < S.total) return sz_fail(SZ_E_SCRATCH, "scratch of %lld bytes, %lld needed", (long long)scratch_bytes, (long long)S.total);
+    // kernels index an expert's matrix as base + e * stride with the global expert id: shift the bases of a local shard accordingly
+    sz_moe_layer Lc = *L0;
+    const bool ep = y_fix != nullptr;
+    int e_lo = 0, e_hi = Lc.n_expert;
+    if (Lc.ep_count > 0) {
+        e_lo = Lc.ep_first; e_hi = Lc.ep_first + Lc.ep_count;
+        Lc.gate -= (u64)e_lo * Lc.gate_stride; Lc.up -= (u64)e_lo * Lc.up_stride; Lc.down -= (u64)e_lo * Lc.down_stride;
+    }
+    const sz_moe_layer* L = &Lc;
     cudaStream_t st = (cudaStream_t)stream;
     u8* base = (u8*)scratch;
     u32* ctrl = (u32*)(base + S.ctrl);
@@ -629,19 +709,23 @@ extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t 
     float *eo = (float*)(base + S.eo), *so = (float*)(base + S.so);
     const float* xp = (const float*)x;
     const int H = L->hidden, FF = L->expert_ff, SF = L->shared_ff;
-    const bool shared = SF > 0;
+    const bool shared = SF > 0 && (!ep || L->ep_count == 0 || L->ep_shared);
 
     const int route_rows = L->n_expert + (shared ? 1 : 0);
     const SzFast fast = sz_fast_path(L);
-    SZ_CUDA(sz_launch("route", sz_route_kernel, dim3((route_rows + SZ_ROUTE_WARPS - 1) / SZ_ROUTE_WARPS), dim3(SZ_ROUTE_WARPS * 32), 0, st, false, xp, m, H,
+    {
+        static bool set = false;
+        if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+    }
+    SZ_CUDA(sz_launch("route", sz_route_kernel, dim3((route_rows + SZ_ROUTE_WARPS - 1) / SZ_ROUTE_WARPS), dim3(SZ_ROUTE_WARPS * 32), (size_t)m * H * 4, st, false, xp, m, H,
                       (const float*)L->router, (const float*)(shared ? L->shared_router : 0), (int)L->n_expert, (int)L->top_k, logits, ridx,
                       rw, plan, plan_sh, ctrl, (int32_t*)route_idx, (double*)route_w, (uint4*)(base + S.acc_gu),
-                      fast.exl3 ? (int)(S.acc_bytes / 16) : 0));
+                      fast.exl3 ? (int)(S.acc_bytes / 16) : 0, (int)L->ep_first, (int)L->ep_count));
     const int groups = m * L->top_k;
     if (fast.exl3) {
         // streaming EXL3 kernels for the routed experts (and the shared expert when it has the same type and width)
         long long *acc_gu = (long long*)(base + S.acc_gu), *acc_d = (long long*)(base + S.acc_d);
-        const bool sh_fused = fast.shared_fused;
+        const bool sh_fused = fast.shared_fused && shared;
         if (shared && !sh_fused) {
             if ((rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, false))) return rc;
             if ((rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true))) return rc;
@@ -650,7 +734,7 @@ extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t 
         SZ_CUDA(sz_launch("combine_exl3", sz_x3_combine_kernel, dim3(m * (H / 128)), dim3((L->top_k + 1) * 32), 0, st, true, (const long long*)acc_d,
                           (const int32_t*)ridx, (const double*)rw, (const u8*)L->down, (u64)L->down_stride,
                           (const u8*)(sh_fused ? L->sh_down : 0), (const float*)(shared && !sh_fused ? so : nullptr), (const float*)logits,
-                          (int)L->n_expert, (int)L->top_k, m, H, FF, shared ? 1 : 0, (float*)y));
+                          (int)L->n_expert, (int)L->top_k, m, H, FF, shared ? 1 : 0, y, y_fix, e_lo, e_hi));
         return SZ_OK;
     }
     if ((rc = sz_ffn(st, L->expert_type, plan, groups, L->gate, L->gate_stride, L->up, L->up_stride, L->down, L->down_stride, xp, H, FF, g, u,
@@ -661,9 +745,37 @@ extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t 
                      eo, true)))
         return rc;
     if (shared && (rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true))) return rc;
-    SZ_CUDA(sz_launch("combine", sz_combine_kernel, dim3((H + 255) / 256, m), dim3(256), 0, st, true, (const float*)eo, (const double*)rw, (const float*)so,
-                      (const float*)logits, (int)L->n_expert, (int)L->top_k, H, shared ? 1 : 0, (float*)y));
+    SZ_CUDA(sz_launch("combine", sz_combine_kernel, dim3((H + 255) / 256, m), dim3(256), 0, st, true, (const float*)eo, (const int32_t*)ridx,
+                      (const double*)rw, (const float*)so, (const float*)logits, (int)L->n_expert, (int)L->top_k, H, shared ? 1 : 0, y, y_fix, e_lo, e_hi));
     return SZ_OK;
+}
+
+extern "C" int sz_moe_finish(uint64_t y_fix, int m, int hidden, uint64_t y, uint64_t stream) {
+    if (!y_fix || !y || m < 1 || m > SZ_MAX_VERIFY || hidden < 1 || (y_fix & 7) || (y & 3)) return sz_fail(SZ_E_ARG, "sz_moe_finish: bad argument");
+    const int n = m * hidden;
+    SZ_CUDA(sz_launch("moe_finish", sz_yfix_finish_kernel, dim3((n + 255) / 256), dim3(256), 0, (cudaStream_t)stream, true, (const long long*)y_fix, n, (float*)y));
+    return SZ_OK;
+}
+
+extern "C" int sz_moe_verify_partial(const sz_moe_layer* L, uint64_t x, int m, uint64_t y_fix, uint64_t scratch, int64_t scratch_bytes,
+                                     uint64_t stream) {
+    if (!y_fix || (y_fix & 15)) return sz_fail(SZ_E_ARG, "sz_moe_verify_partial: y_fix must be non-null and 16-byte aligned");
+    return sz_moe_run(L, x, m, nullptr, (long long*)y_fix, 0, 0, scratch, scratch_bytes, stream);
+}
+
+extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t y, uint64_t route_idx, uint64_t route_w,
+                             uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
+    if (!y || !sz_aligned16(y)) return sz_fail(SZ_E_ARG, "y must be non-null and 16-byte aligned");
+    if (!L || L->ep_count <= 0) return sz_moe_run(L, x, m, (float*)y, nullptr, route_idx, route_w, scratch, scratch_bytes, stream);
+    // expert-parallel layer: this rank's share in fixed point, summed over the ranks (exactly: integers), then back to f32
+    if (sz_ep_world() < 1) return sz_fail(SZ_E_ARG, "the layer is sharded (ep_count = %d) but sz_ep_init has not run", L->ep_count);
+    int rc = sz_moe_check(L, m);
+    if (rc) return rc;
+    const SzMoeScratch S = sz_moe_layout(L, m);
+    long long* y_fix = (long long*)((u8*)scratch + S.y_fix);
+    if ((rc = sz_moe_run(L, x, m, nullptr, y_fix, route_idx, route_w, scratch, scratch_bytes, stream))) return rc;
+    if (sz_ep_world() > 1 && (rc = sz_ep_allreduce_i64(y_fix, (size_t)m * L->hidden, (cudaStream_t)stream))) return rc;
+    return sz_moe_finish((uint64_t)y_fix, m, L->hidden, y, stream);
 }
 
 extern "C" int sz_moe_verify_host(const sz_moe_layer* L, const float* x_host, int m, float* y_host, int32_t* route_idx_host,

@@ -33,6 +33,7 @@ struct SzMoeScratch {
     int64_t acc_gu;    // i64 [m * top_k + m][2][FF]: fixed-point gate / up sums of the streaming kernels (pairs, then shared rows)
     int64_t acc_d;     // i64 [m * top_k + m][H]: fixed-point down sums
     int64_t acc_bytes; // acc_gu and acc_d are contiguous: this many bytes are zeroed at the start of a call
+    int64_t y_fix;     // i64 [m][H]: this rank's share of the output in fixed point (expert parallelism)
     int64_t total;
 };
 
@@ -58,6 +59,7 @@ static inline SzMoeScratch sz_moe_layout(const sz_moe_layer* L, int m) {
     s.acc_gu = o; o = sz_up256(o + 8 * (pairs + m) * 2 * ffm);
     s.acc_d = o; o = sz_up256(o + 8 * (pairs + m) * L->hidden);
     s.acc_bytes = o - s.acc_gu;
+    s.y_fix = o; o = sz_up256(o + 8 * (int64_t)m * L->hidden);
     s.total = o;
     return s;
 }

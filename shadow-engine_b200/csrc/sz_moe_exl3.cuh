@@ -364,8 +364,10 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
 __global__ void __launch_bounds__((SZ_MAX_TOPK + 1) * 32)
 sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restrict__ ridx, const double* __restrict__ rw,
                      const u8* __restrict__ down, u64 dstride, const u8* __restrict__ sh_down, const float* __restrict__ so_f32,
-                     const float* __restrict__ logits, int ne, int top_k, int m, int H, int FF, int has_shared, float* __restrict__ y) {
+                     const float* __restrict__ logits, int ne, int top_k, int m, int H, int FF, int has_shared, float* __restrict__ y,
+                     long long* __restrict__ y_fix, int e_lo, int e_hi) {
     __shared__ float part[SZ_MAX_TOPK + 1][128];
+    __shared__ int local[SZ_MAX_TOPK];
     sz_pdl_wait();
     sz_pdl_trigger();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -373,7 +375,10 @@ sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restric
     const int j = blockIdx.x / nb, b = blockIdx.x % nb;
     if (warp < top_k) {
         const int pair = j * top_k + warp;
-        const u16* svh = (const u16*)(down + (u64)__ldcg(ridx + pair) * dstride + 2 * (size_t)FF) + b * 128;
+        const int e = __ldcg(ridx + pair);
+        const bool mine = !y_fix || (e >= e_lo && e < e_hi);  // with expert parallelism only the experts held here count
+        if (lane == 0) local[warp] = mine;
+        const u16* svh = (const u16*)(down + (u64)(mine ? e : e_lo) * dstride + 2 * (size_t)FF) + b * 128;
         float v[4];
 #pragma unroll
         for (int e = 0; e < 4; e++) v[e] = (float)((double)__ldcg(out + (size_t)pair * H + b * 128 + lane + 32 * e) * SZ_FIX_INV);
@@ -403,10 +408,18 @@ sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restric
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int i = lane + 32 * e;
-            double a = 0.0;
-            for (int t = 0; t < top_k; t++) a += __ldcg(rw + j * top_k + t) * (double)part[t][i];
-            if (has_shared) a += (double)part[top_k][i];
-            y[(size_t)j * H + b * 128 + i] = (float)a;
+            if (y_fix) {  // every term in 64-bit fixed point: the sum over ranks is then exact
+                long long f = 0;
+                for (int t = 0; t < top_k; t++)
+                    if (local[t]) f += __double2ll_rn(__ldcg(rw + j * top_k + t) * (double)part[t][i] * 1099511627776.0);
+                if (has_shared) f += __double2ll_rn((double)part[top_k][i] * 1099511627776.0);
+                y_fix[(size_t)j * H + b * 128 + i] = f;
+            } else {
+                double a = 0.0;
+                for (int t = 0; t < top_k; t++) a += __ldcg(rw + j * top_k + t) * (double)part[t][i];
+                if (has_shared) a += (double)part[top_k][i];
+                y[(size_t)j * H + b * 128 + i] = (float)a;
+            }
         }
     }
 }

@@ -452,7 +452,7 @@ static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
     int rc = sz_dense_launch(a, st, "delta_proj");
     if (rc) return rc;
     const int64_t cl = (int64_t)(c.conv_k - 1) * ch;
-    SZ_CUDA(sz_launch("delta_prep", sz_delta_prep_kernel, dim3(m), dim3(256), 0, st, true, (const float*)xin, (const float*)(s->conv[0] + di * cl),
+    SZ_CUDA(sz_launch("delta_prep", sz_delta_prep_kernel, dim3((unsigned)((ch + 255) / 256), m), dim3(256), 0, st, true, (const float*)xin, (const float*)(s->conv[0] + di * cl),
                       (const float*)(s->conv[1] + di * cl), (const int32_t*)s->state, (const float*)L.ssm_conv1d.data, (const float*)s->d_b,
                       (const float*)s->d_a, (const float*)L.ssm_a.data, (const float*)L.ssm_dt_bias.data, kh, vh, d, (int)c.conv_k, xc, beta, decay));
     if ((rc = sz_scan(s, st, l, m))) return rc;

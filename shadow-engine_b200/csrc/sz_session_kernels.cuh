@@ -74,46 +74,51 @@ sz_hc_mix_kernel(const float* __restrict__ mix, const float* __restrict__ rn, in
 }
 
 // ---- DeltaNet front end (forward.rs:829-861): causal conv (k taps) + SiLU over the rows of the pass, L2 norm of q and k heads,
-// beta and decay.  grid (m), block 256.  conv: (k-1) x ch, oldest first: the state BEFORE the pass.  xin: [m][ch] raw projections.
+// beta and decay.  grid (ch / 256, m), block 256: a block takes 256 channels - whole heads, since the head width divides 256 - of
+// one row.  conv0 / conv1: (k-1) x ch, oldest first: the state BEFORE the pass (state[1] says which).  xin: [m][ch] raw projections.
 __global__ void __launch_bounds__(256)
 sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ conv0, const float* __restrict__ conv1, const int32_t* __restrict__ state,
                      const float* __restrict__ cw, const float* __restrict__ b,
                      const float* __restrict__ a, const float* __restrict__ a_log, const float* __restrict__ dt, int kh, int vh, int d, int k,
                      float* __restrict__ xc, float* __restrict__ beta, float* __restrict__ decay) {
+    __shared__ float sx[256];
     sz_pdl_wait();
     sz_pdl_trigger();
-    const int j = blockIdx.x;
+    const int j = blockIdx.y;
     const int kd = kh * d, ch = 2 * kd + vh * d;
     const float* conv = state[1] ? conv1 : conv0;  // the carried rows of the current state buffer
-    for (int i = threadIdx.x; i < ch; i += 256) {
+    const int i = blockIdx.x * 256 + threadIdx.x;
+    float v = 0.f;
+    if (i < ch) {
         double acc = (double)cw[i * k + (k - 1)] * (double)xin[(size_t)j * ch + i];
         for (int t = 0; t < k - 1; t++) {
             const int tau = j - (k - 1) + t;  // row of this pass, or (negative) a row of the carried state
             const float prev = tau >= 0 ? xin[(size_t)tau * ch + i] : conv[(size_t)((k - 1) + tau) * ch + i];
             acc += (double)cw[i * k + t] * (double)prev;
         }
-        xc[(size_t)j * ch + i] = sz_silu((float)acc);
+        v = sz_silu((float)acc);
     }
+    sx[threadIdx.x] = v;
     __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int hq = warp; hq < 2 * kh; hq += 8) {  // heads 0..kh-1: q (also / sqrt(d)); kh..2kh-1: k
-        float* v = xc + (size_t)j * ch + (size_t)hq * d;
-        double ss = 0.0;
-        for (int i = lane; i < d; i += 32) ss += (double)v[i] * (double)v[i];
-        ss = sz_warp_sum(ss);
-        const double n = 1.0 / sqrt(ss + 1e-6);
-        const float sq = sqrtf((float)d);
-        for (int i = lane; i < d; i += 32) {
-            float t = (float)((double)v[i] * n);
-            if (hq < kh) t = t / sq;
-            v[i] = t;
+    if (i < ch) {
+        if (i < 2 * kd) {  // a q or k channel: L2-normalise its head (q also / sqrt(d))
+            const int h0 = (threadIdx.x / d) * d;  // first channel of the head inside the block
+            double ss = 0.0;
+            for (int t = 0; t < d; t++) ss += (double)sx[h0 + t] * (double)sx[h0 + t];
+            const double n = 1.0 / sqrt(ss + 1e-6);
+            float t = (float)((double)v * n);
+            if (i < kd) t = t / sqrtf((float)d);
+            v = t;
         }
+        xc[(size_t)j * ch + i] = v;
     }
-    for (int h = threadIdx.x; h < vh; h += 256) {
-        beta[j * vh + h] = sz_sigmoid(b[j * vh + h]);
-        const float sp_in = a[j * vh + h] + dt[h];
-        const float sp = sp_in > 20.0f ? sp_in : (float)log1p(exp((double)sp_in));
-        decay[j * vh + h] = (float)exp((double)a_log[h] * (double)sp);
+    if (blockIdx.x == 0) {
+        for (int h = threadIdx.x; h < vh; h += 256) {
+            beta[j * vh + h] = sz_sigmoid(b[j * vh + h]);
+            const float sp_in = a[j * vh + h] + dt[h];
+            const float sp = sp_in > 20.0f ? sp_in : (float)log1p(exp((double)sp_in));
+            decay[j * vh + h] = (float)exp((double)a_log[h] * (double)sp);
+        }
     }
 }
 

@@ -1,0 +1,71 @@
+"""Expert parallelism, host side: which experts a rank holds, and bringing the library's NCCL communicator up from a
+torch.distributed process group (one process per GPU).
+
+The reference runs one GPU per session and splits a model over cards by LAYER range only (two sessions with a host hop,
+crates/shadowzero/tests/two_stage.rs:1-4); it has no expert-parallel path.  Here the experts of every MoE layer are sharded by
+contiguous id range; everything else (router, attention, DeltaNet state, cache, head) is replicated, so every rank computes the
+same routing and runs only the hits it holds.  The one exchange per layer is an all-reduce of the layer output in 64-bit fixed
+point: integer addition is associative, so the result is bit-identical for every group size and rank order."""
+import ctypes as C
+
+import numpy as np
+
+from . import lib as szlib
+
+FIX_SCALE = float(1 << 40)   # one unit of the fixed-point output = 2^-40
+
+
+def shard_range(rank, world, n_expert):
+    """Experts [first, first + count) held by `rank`: contiguous, sizes differ by at most one, earlier ranks take the remainder."""
+    if not (0 <= rank < world) or world > n_expert:
+        raise ValueError(f"rank {rank} of {world} over {n_expert} experts")
+    base, rem = divmod(n_expert, world)
+    first = rank * base + min(rank, rem)
+    return first, base + (1 if rank < rem else 0)
+
+
+def owner(expert, world, n_expert):
+    base, rem = divmod(n_expert, world)
+    edge = rem * (base + 1)
+    return expert // (base + 1) if expert < edge else rem + (expert - edge) // base
+
+
+def shard_spec(rank, world, n_expert):
+    """The `shard` argument of moe.MoeLayer / model.DeviceModel: rank 0 also carries the shared expert's term."""
+    first, count = shard_range(rank, world, n_expert)
+    return first, count, rank == 0
+
+
+def to_fixed(v):
+    """float64 array -> the int64 fixed-point terms the combine kernels add (round to nearest even, like cvt.rni.s64.f64)."""
+    return np.rint(np.asarray(v, dtype=np.float64) * FIX_SCALE).astype(np.int64)
+
+
+def from_fixed(f):
+    return (np.asarray(f, dtype=np.int64).astype(np.float64) / FIX_SCALE).astype(np.float32)
+
+
+def init_from_process_group(group=None, get_id=None, init=None):
+    """Creates the library's communicator over the ranks of a torch.distributed group: rank 0 draws the NCCL unique id, the
+    group broadcasts it (any backend), every rank joins.  `get_id` / `init` replace the library calls in host-only tests."""
+    import torch
+    import torch.distributed as dist
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    if get_id is None or init is None:
+        lib = szlib.load()
+
+        def get_id():
+            buf = (C.c_uint8 * 128)()
+            szlib.check(lib.sz_ep_unique_id(buf))
+            return bytes(buf)
+
+        def init(r, w, ident):
+            buf = (C.c_uint8 * 128).from_buffer_copy(ident)
+            szlib.check(lib.sz_ep_init(r, w, buf))
+    box = [get_id() if rank == 0 else None]
+    if world > 1:
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+    ident = box[0]
+    assert isinstance(ident, (bytes, bytearray)) and len(ident) == 128
+    init(rank, world, bytes(ident))
+    return rank, world

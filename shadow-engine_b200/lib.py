@@ -27,7 +27,8 @@ class MoeLayerC(C.Structure):
                 ("router", C.c_uint64), ("shared_router", C.c_uint64),
                 ("gate", C.c_uint64), ("up", C.c_uint64), ("down", C.c_uint64),
                 ("gate_stride", C.c_uint64), ("up_stride", C.c_uint64), ("down_stride", C.c_uint64),
-                ("sh_gate", C.c_uint64), ("sh_up", C.c_uint64), ("sh_down", C.c_uint64)]
+                ("sh_gate", C.c_uint64), ("sh_up", C.c_uint64), ("sh_down", C.c_uint64),
+                ("ep_first", C.c_int32), ("ep_count", C.c_int32), ("ep_shared", C.c_int32), ("ep_reserved", C.c_int32)]
 
 
 # name -> (restype, argtypes); every symbol include/shadowzero_b200.h declares
@@ -87,6 +88,12 @@ SYMBOLS = {
     "sz_gen_begin": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]),
     "sz_gen_run": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.c_int, C.c_void_p, C.c_uint64]),
     "sz_gen_free": (None, [C.c_void_p]),
+    "sz_ep_unique_id": (C.c_int, [C.c_void_p]),
+    "sz_ep_init": (C.c_int, [C.c_int, C.c_int, C.c_void_p]),
+    "sz_ep_world": (C.c_int, []),
+    "sz_ep_destroy": (None, []),
+    "sz_moe_verify_partial": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_int64, C.c_uint64]),
+    "sz_moe_finish": (C.c_int, [C.c_uint64, C.c_int, C.c_int, C.c_uint64, C.c_uint64]),
     "sz_moe_static_scratch_max": (C.c_int, [C.POINTER(C.c_int64)]),
     "sz_moe_verify_static": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
 }

@@ -7,6 +7,7 @@ import numpy as np
 import torch
 
 from . import lib as szlib
+from . import ep as szep
 from . import moe as szmoe
 from . import synth
 
@@ -238,9 +239,12 @@ class HostModel(_Placed):
 class DeviceModel(_Placed):
     """The model resident in HBM: what `Session` takes."""
 
-    def __init__(self, M, device="cuda:0"):
+    def __init__(self, M, device="cuda:0", ep=None):
+        """`ep` = (rank, world): hold only this rank's experts of every MoE layer (see `ep.shard_spec`); the library's
+        communicator must be up (`ep.init_from_process_group`) before a session of such a model runs a pass."""
         self.device = torch.device(device)
         self._keep = []
+        self.ep = ep
 
         def put(b):
             buf, addr, _ = szmoe.place(b.reshape(1, -1), self.device, 0)
@@ -248,7 +252,8 @@ class DeviceModel(_Placed):
             return addr
 
         def put_moe(Ld):
-            ml = szmoe.MoeLayer(Ld, self.device)
+            shard = szep.shard_spec(ep[0], ep[1], Ld["n_expert"]) if ep else None
+            ml = szmoe.MoeLayer(Ld, self.device, shard=shard)
             self._keep.append(ml)
             return ml.c
 

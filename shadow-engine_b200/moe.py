@@ -33,7 +33,9 @@ def place(t, device, lead=0):
 class MoeLayer:
     """One MoE layer resident on a GPU.  `L` is the description `synth.make_moe_layer` returns (torch tensors)."""
 
-    def __init__(self, L, device="cuda:0", max_rows=szlib.MAX_VERIFY):
+    def __init__(self, L, device="cuda:0", max_rows=szlib.MAX_VERIFY, shard=None):
+        """`shard` = (first, count, with_shared): hold only experts [first, first + count) of the layer (expert parallelism);
+        `with_shared` says whether this rank adds the shared expert's term (exactly one rank of a group does)."""
         self.lib = szlib.load()
         self.device = torch.device(device)
         self.shape = {k: L[k] for k in ("hidden", "n_expert", "top_k", "expert_ff", "shared_ff", "expert_type", "shared_type")}
@@ -51,11 +53,17 @@ class MoeLayer:
             self._keep.append(buf)
             return addr, stride
 
+        lo, hi = 0, L["n_expert"]
+        if shard is not None:
+            lo, hi = shard[0], shard[0] + shard[1]
+            assert 0 <= lo < hi <= L["n_expert"]
+            c.ep_first, c.ep_count, c.ep_shared = lo, hi - lo, int(bool(shard[2]))
+        self.shard = shard
         c.router, _ = put(L["router"].reshape(1, -1))
-        c.gate, c.gate_stride = put(L["gate"], lead(L["expert_type"], H, FF))
-        c.up, c.up_stride = put(L["up"], lead(L["expert_type"], H, FF))
-        c.down, c.down_stride = put(L["down"], lead(L["expert_type"], FF, H))
-        if SF > 0:
+        c.gate, c.gate_stride = put(L["gate"][lo:hi], lead(L["expert_type"], H, FF))
+        c.up, c.up_stride = put(L["up"][lo:hi], lead(L["expert_type"], H, FF))
+        c.down, c.down_stride = put(L["down"][lo:hi], lead(L["expert_type"], FF, H))
+        if SF > 0 and (shard is None or shard[2]):
             c.shared_router, _ = put(L["shared_router"].reshape(1, -1))
             c.sh_gate, _ = put(L["sh_gate"].reshape(1, -1), lead(L["shared_type"], H, SF))
             c.sh_up, _ = put(L["sh_up"].reshape(1, -1), lead(L["shared_type"], H, SF))
@@ -88,6 +96,26 @@ class MoeLayer:
         szlib.check(self.lib.sz_moe_verify(C.byref(self.c), x.data_ptr(), m, y.data_ptr(), a, b, self.scratch_addr,
                                            self.scratch_bytes, st))
         return (y, ridx, rw) if want_routing else y
+
+    def moe_partial(self, x, y_fix=None, stream=None):
+        """This rank's share of moe(x[j]) as 64-bit fixed point (int64 [m, hidden]); the shares of all ranks sum, as integers,
+        to the layer's output, which `finish` converts to float32."""
+        m = x.shape[0]
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == self.shape["hidden"]
+        if y_fix is None:
+            y_fix = torch.empty((m, self.shape["hidden"]), dtype=torch.int64, device=self.device)
+        st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        szlib.check(self.lib.sz_moe_verify_partial(C.byref(self.c), x.data_ptr(), m, y_fix.data_ptr(), self.scratch_addr,
+                                                   self.scratch_bytes, st))
+        return y_fix
+
+    def finish(self, y_fix, y=None, stream=None):
+        m, H = y_fix.shape
+        if y is None:
+            y = torch.empty((m, H), dtype=torch.float32, device=self.device)
+        st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        szlib.check(self.lib.sz_moe_finish(y_fix.data_ptr(), m, H, y.data_ptr(), st))
+        return y
 
     def moe_batch_host(self, x_host, y_host, x_dev, y_dev, stream=None):
         """The host-buffer entry point: x_host / y_host are (pinned) CPU float32 tensors [m, hidden]."""

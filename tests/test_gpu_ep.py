@@ -1,0 +1,130 @@
+"""Expert parallelism on the GPU.  One card emulates a group the way the reference tests its two-stage split on one card
+(crates/shadowzero/tests/two_stage.rs:1-4): G sharded copies of a layer, each producing its fixed-point share, summed as
+integers.  The sum must be bit-identical for every G; with two or more cards the same runs over NCCL."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import binding as ob
+from tests.util import pkg
+
+pytestmark = pytest.mark.gpu
+szlib, synth, moe, ep, model = pkg.lib, pkg.synth, pkg.moe, pkg.ep, pkg.model
+REL_TOL = 2e-4
+
+
+def emulate(L, x, G):
+    total = None
+    for r in range(G):
+        layer = moe.MoeLayer(L, "cuda:0", shard=ep.shard_spec(r, G, L["n_expert"]))
+        part = layer.moe_partial(x)
+        torch.cuda.synchronize()
+        total = part.clone() if total is None else total + part
+    return total, layer
+
+
+@pytest.mark.parametrize("ety,H,ne,k,FF,SF", [
+    ("q8", 512, 32, 4, 256, 512),      # generic kernels
+    ("iq3", 512, 64, 6, 256, 256),
+    ("x3", 512, 32, 4, 256, 256),      # streaming EXL3 kernels, shared expert fused
+    ("x3", 1024, 32, 6, 256, 512),     # shared expert on the generic kernels
+    ("x3", 512, 32, 6, 128, 0),        # no shared expert
+])
+def test_group_sizes_agree_bitwise(ety, H, ne, k, FF, SF):
+    ty = {"q8": szlib.TYPE_Q8_0, "iq3": szlib.TYPE_IQ3_S, "x3": szlib.TYPE_EXL3(3)}[ety]
+    L = synth.make_moe_layer(H, ne, k, FF, SF, ty, ty, seed=41)
+    m = 4
+    x = torch.randn(m, H, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).to(torch.float32).cuda()
+    ref, layer = emulate(L, x, 1)
+    for G in (2, 4, 8):
+        got, layer = emulate(L, x, G)
+        assert torch.equal(got, ref), G
+    y = layer.finish(ref).cpu().numpy()
+    whole = moe.MoeLayer(L, "cuda:0").moe_batch(x).cpu().numpy()
+    Ln = synth.to_numpy_layer(L)
+    for j in range(m):
+        want = ob.moe(Ln, x[j].cpu().numpy(), threads=4)[0]
+        scale = max(np.abs(want).max(), 1e-9)
+        assert np.abs(y[j] - want).max() / scale < REL_TOL
+        assert np.abs(y[j] - whole[j]).max() / scale < 1e-6     # the fixed-point path against the f64 accumulation
+
+
+def test_sharded_layer_needs_the_communicator():
+    L = synth.make_moe_layer(256, 16, 4, 128, 128, szlib.TYPE_Q8_0, szlib.TYPE_Q8_0, seed=42)
+    layer = moe.MoeLayer(L, "cuda:0", shard=(0, 8, True))
+    x = torch.randn(2, 256).cuda()
+    lib = szlib.load()
+    lib.sz_ep_destroy()
+    with pytest.raises(szlib.SzError):
+        layer.moe_batch(x)
+    # a group of one needs no NCCL: the whole layer as one shard gives the emulated bits
+    szlib.check(lib.sz_ep_init(0, 1, None))
+    try:
+        full = moe.MoeLayer(L, "cuda:0", shard=(0, 16, True))
+        y = full.moe_batch(x)
+        ref, _ = emulate(L, x, 2)
+        assert torch.equal(y, full.finish(ref))
+    finally:
+        lib.sz_ep_destroy()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ep.init_from_process_group()
+        dev = "cuda:%d" % rank
+        L = synth.make_moe_layer(512, 32, 4, 256, 256, szlib.TYPE_EXL3(3), szlib.TYPE_EXL3(3), seed=41)
+        x = torch.randn(4, 512, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).to(torch.float32).to(dev)
+        layer = moe.MoeLayer(L, dev, shard=ep.shard_spec(rank, world, 32))
+        y = layer.moe_batch(x)
+        torch.cuda.synchronize()
+        np.save(os.path.join(out_dir, "y%d.npy" % rank), y.cpu().numpy())
+        # a whole model: every rank must generate the same tokens
+        M = model.make_model(model.TINY, seed=1, cycle_alpha=0.24)
+        _, cyc = model.token_cycles(model.TINY["vocab"], 1)
+        dm = model.DeviceModel(M, dev, ep=(rank, world))
+        s = model.Session(dm, 512)
+        toks, _, st = s.generate(model.make_prompt(128, model.TINY["vocab"], seed=1, cycles=cyc), 48, spec_k=3)
+        assert st.accepted > 0
+        np.save(os.path.join(out_dir, "t%d.npy" % rank), np.asarray(toks, dtype=np.int64))
+        dist.barrier()
+        szlib.load().sz_ep_destroy()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_over_nccl(tmp_path):
+    import torch.multiprocessing as mp
+    world = 2
+    mp.spawn(_rank, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    y0, y1 = np.load(tmp_path / "y0.npy"), np.load(tmp_path / "y1.npy")
+    assert np.array_equal(y0, y1)
+    L = synth.make_moe_layer(512, 32, 4, 256, 256, szlib.TYPE_EXL3(3), szlib.TYPE_EXL3(3), seed=41)
+    x = torch.randn(4, 512, generator=torch.Generator().manual_seed(7)).to(torch.bfloat16).to(torch.float32).cuda()
+    ref, layer = emulate(L, x, 1)
+    assert np.array_equal(layer.finish(ref).cpu().numpy(), y0)          # two cards == one card, bit for bit
+    t0, t1 = np.load(tmp_path / "t0.npy"), np.load(tmp_path / "t1.npy")
+    assert np.array_equal(t0, t1)
+    lib = szlib.load()
+    szlib.check(lib.sz_ep_init(0, 1, None))
+    try:
+        M = model.make_model(model.TINY, seed=1, cycle_alpha=0.24)
+        _, cyc = model.token_cycles(model.TINY["vocab"], 1)
+        s = model.Session(model.DeviceModel(M, "cuda:0", ep=(0, 1)), 512)
+        toks, _, _ = s.generate(model.make_prompt(128, model.TINY["vocab"], seed=1, cycles=cyc), 48, spec_k=3)
+        assert np.array_equal(np.asarray(toks, dtype=np.int64), t0)
+    finally:
+        lib.sz_ep_destroy()
