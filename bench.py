@@ -1,14 +1,18 @@
-"""Benchmark of the verify-step hot path on B200.
+"""Benchmark of the speculative-decoding verify path on B200.
 
-Default workload ("c2-moe"): BASELINE config 2, the verify-step MoE microbench: hidden 2048, 512 experts top-10,
-expert FFN 512 + a shared expert of FFN 512, K+1 = 4 rows of N(0,1) activations rounded to bf16, expert weights EXL3 at
-3 bits a weight (--format exl3, the default) or IQ3_S / Q8_0.  One "step" is one MoE sublayer pass over the 4 rows.
-`--layers` distinct layers (default 8, ~5 GB) are cycled so each step streams expert weights that are not in the 126 MB L2.
+Default workload ("c3"): BASELINE config 3 - the full-size seeded hybrid MoE (48 layers 3:1 DeltaNet : gated attention, hidden
+2048, 512 experts top-10 of FFN 512 + a shared expert, EXL3 3-bit experts, Q8_0 dense matrices and head, vocab 151936, Q8_KV
+cache) decoding greedily at spec K=3, batch 1, at context 24576.  One "step" is one draft / verify / accept round: the suffix
+drafter proposes up to 3 tokens, one verify pass runs over the 1..4 rows, acceptance and rollback happen on the device.  The
+metric is accepted tokens per second (every emitted token: accepted drafts and the pass's own token).  With --gpus N (under
+torchrun) the experts of every layer are sharded over the N ranks (expert parallelism); one sequence, so scaling is "strong".
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--format exl3|iq3_s|q8_0] [--impl reference]
+`--workload c2-moe`: BASELINE config 2, the verify-step MoE microbench (one MoE sublayer pass over K+1 = 4 rows per step).
 
-Prints one JSON line (rank 0).  `--impl reference` times the CPU restatement of the reference's scalar path (the oracle)
-on the host cores for the same workload.
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c2-moe] [--impl reference]
+
+Prints one JSON line (rank 0).  `--impl reference` times the CPU restatement of the reference's scalar path (the oracle) on the
+host cores for the same workload.
 """
 import argparse
 import ctypes as C
@@ -25,6 +29,13 @@ if ROOT not in sys.path:
 
 C2 = dict(hidden=2048, n_expert=512, top_k=10, expert_ff=512, shared_ff=512, rows=4)
 METRIC = "verify-step us (MoE sublayer, K+1=4 rows, spec K=3)"
+
+# BASELINE config 3
+C3 = dict(n_layer=48, hidden=2048, streams=4, hc_rank=256, vocab=151936, n_head=16, n_kv_head=2, head_dim=256, rope_dims=64,
+          n_expert=512, n_expert_used=10, expert_ff=512, shared_ff=512, ssm_k_heads=16, ssm_v_heads=32, ssm_head_dim=128, conv_k=4,
+          attn_interval=4, eps=1e-6, rope_theta=1e7)
+C3_CTX = 24576
+C3_METRIC = "accepted tok/s at spec K=3"
 
 
 def peaks():
@@ -90,6 +101,250 @@ class ClockSampler:
         return {"sm_mhz": sm[len(sm) // 2], "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# ---- workload c3: accepted tok/s on the full-size model ---------------------------------------------------------------------------
+C3_ALPHA = 0.85
+
+
+def c3_bytes(cfg, ctx, distinct_per_layer, dense_bytes):
+    """Algorithmic bytes of one verify pass: every distinct routed expert and the shared expert once (EXL3 3-bit blobs), the
+    Q8_KV cache of the attention layers once, and - counted apart - `dense_bytes`: the projections, hyper-connection weights,
+    routers and the head, each read once."""
+    H, FF = cfg["hidden"], cfg["expert_ff"]
+    be = expert_bytes("exl3", H, FF)
+    n_attn = cfg["n_layer"] // cfg["attn_interval"]
+    hb = cfg["head_dim"] + ((cfg["head_dim"] // 32 * 2 + 15) & ~15)
+    experts = sum(distinct_per_layer) * be + cfg["n_layer"] * expert_bytes("exl3", H, cfg["shared_ff"])
+    kv = n_attn * ctx * cfg["n_kv_head"] * hb * 2
+    return {"experts": experts, "kv": kv, "experts_kv": experts + kv, "dense_and_head": dense_bytes, "all": experts + kv + dense_bytes}
+
+
+def run_c3(args):
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    torch.cuda.set_device(local)
+    device = "cuda:%d" % local
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    md, szlib, ep = pkg.model, pkg.lib, pkg.ep
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        dist.init_process_group("nccl")
+        ep.init_from_process_group()
+    hbm, peak_kind = peaks()
+    cfg = dict(C3, n_layer=args.n_layer)
+    M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha)
+    dm = md.DeviceModel(M, device, ep=(rank, world) if world > 1 else None)
+    # every tensor outside the experts is read once a pass, except the embedding table (m rows gathered)
+    dense_bytes = sum(t[3].numel() * t[3].element_size() for n, t in M["tensors"].items() if n != "token_embd.weight")
+    dense_bytes += sum(Ld["router"].numel() * 4 + Ld["shared_router"].numel() * 4 for Ld in M["moe"])
+    del M
+    torch.cuda.empty_cache()
+    ctx = args.ctx
+    K, W = args.steps, max(args.warmup, 3)
+    max_new = 4 * (3 * K + W + 64) + 64
+    sess = md.Session(dm, ctx + max_new + 64, kv_q8=True)
+    _, cyc = md.token_cycles(cfg["vocab"], 1)
+    n_prompt = 256
+    prompt = md.make_prompt(n_prompt, cfg["vocab"], seed=1, cycles=cyc)
+    # the long context: the cache up to ctx - 256 is filled in place with seeded values of the cache's own distribution, then
+    # the 256-token repeated-n-gram prompt is prefilled through the model
+    sess.fill_synthetic(ctx - n_prompt, seed=3)
+    if args.profile_passes > 0:
+        # for a profiler: N verify passes of 4 rows and nothing else (run with SZ_SESSION_GRAPHS=0 to see every launch by name)
+        for i in range(args.profile_passes):
+            sess.verify([int(t) for t in prompt[4 * i:4 * i + 4]], accept=1)
+            sess.result()
+            sess.commit(1)
+        torch.cuda.synchronize()
+        print(json.dumps({"profile_passes": args.profile_passes, "rows": 4, "context": ctx, "n_layer": cfg["n_layer"]}))
+        return
+    gen = md.Generator(sess, prompt, max_new, spec_k=3)
+    st = gen.run(W)
+    torch.cuda.synchronize()
+    stream = sess._stream
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def snap(s):
+        return dict(n=s.n_tokens, rounds=s.rounds, passes=s.passes, drafted=s.drafted, accepted=s.accepted)
+
+    # --- K rounds through the public loop (host drafter, ids host -> device, result device -> host every round), timed twice over:
+    # value = tokens / the device time of the K passes (events on the session's stream around each pass: graph of the pass with
+    # acceptance and commit, cache and weights resident); e2e = tokens / wall clock of the whole loop
+    barrier()
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    a = snap(st)
+    d0 = st.device_ms
+    t0 = time.perf_counter()
+    st = gen.run(K)
+    stream.synchronize()
+    wall_s = time.perf_counter() - t0
+    barrier()
+    b = c = snap(st)
+    dev_ms = st.device_ms - d0
+    clocks = sampler.stop()
+    if world > 1:
+        import torch.distributed as dist
+        t = torch.tensor([dev_ms, wall_s], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, wall_s = float(t[0]), float(t[1])
+    rounds = b["rounds"] - a["rounds"]
+    toks = b["n"] - a["n"]
+    gen_stats = dict(tokens=toks, rounds=rounds, drafted=b["drafted"] - a["drafted"], accepted=b["accepted"] - a["accepted"],
+                     tokens_per_round=toks / max(rounds, 1), draft_ms=st.draft_ms, verify_ms=st.verify_ms, commit_ms=st.commit_ms)
+    rows_avg = 1 + gen_stats["drafted"] / max(rounds, 1)   # rows of a pass: its own token and the drafts
+    gen_stats["accept_rate"] = gen_stats["accepted"] / max(gen_stats["drafted"], 1)
+    del gen
+
+    # --- the verify step alone: one pass of m rows, device time, for m = 1 and m = 4 (spec K=3), median of 15
+    def pass_us(m, n=15):
+        ids = [int(t) for t in prompt[:m]]
+        ts = []
+        for i in range(n + 3):
+            p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            p0.record(stream)
+            sess.verify(ids, accept=1)
+            p1.record(stream)
+            sess.result()
+            sess.commit(1)
+            if i >= 3:
+                ts.append(p0.elapsed_time(p1) * 1e3)
+        ts.sort()
+        return ts[len(ts) // 2]
+
+    step_us = {m: pass_us(m) for m in (1, 4)}
+    # --- routing of one 4-row pass: distinct experts per layer (the bytes the pass must read)
+    sess.trace_routes(True)
+    sess.verify([int(t) for t in prompt[:4]], accept=1)
+    sess.result()
+    ridx, _ = sess.routes()
+    sess.commit(1)
+    sess.trace_routes(False)
+    import numpy as np
+    distinct = [int(np.unique(ridx[l]).size) for l in range(cfg["n_layer"])]
+    # --- per-kernel attribution of one 4-row pass (eager, an event between launches: durations include the launch gap)
+    nev = 4096
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(nev)]
+    for e in evs:
+        e.record(stream)
+    stream.synchronize()
+    arr = (C.c_uint64 * nev)(*[e.cuda_event for e in evs])
+    L = szlib.load()
+    n_k = 0
+    for rep in range(2):
+        szlib.check(L.sz_trace_begin(arr, nev, sess.stream))
+        sess.verify([int(t) for t in prompt[:4]], accept=1)
+        n_k = L.sz_trace_end()
+        sess.result()
+        sess.commit(1)
+    per = {}
+    for i in range(1, n_k):
+        per.setdefault(L.sz_trace_name(i).decode(), []).append(evs[i - 1].elapsed_time(evs[i]) * 1e3)
+    kern = {nm: {"launches": len(v), "avg_us": sum(v) / len(v), "total_us": sum(v)} for nm, v in per.items()}
+    del sess
+    if world > 1:
+        szlib.check(L.sz_ep_destroy())
+    if rank != 0:
+        return
+
+    by = c3_bytes(cfg, ctx, distinct, dense_bytes)
+    be = expert_bytes("exl3", cfg["hidden"], cfg["expert_ff"])
+    roof = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "traffic": None, "kernel": "gateup_exl3s"}
+    ks = kern.get("gateup_exl3s")
+    if ks:
+        # gate + up of a layer's distinct routed experts and of the shared expert: 2/3 of their bytes, one launch a layer
+        per_launch = (sum(distinct) / len(distinct) / world + 1) * be * 2 / 3
+        roof.update(achieved=per_launch / (ks["avg_us"] * 1e-6) / 1e9, kernel_us=ks["avg_us"], bytes_per_launch=per_launch)
+        roof["frac"] = roof["achieved"] / hbm
+    roof.update(step_bytes=by["experts_kv"], step_bytes_all=by["all"], step_us=step_us[4],
+                step_achieved=by["experts_kv"] / (step_us[4] * 1e-6) / 1e9, step_achieved_all=by["all"] / (step_us[4] * 1e-6) / 1e9)
+    roof["step_frac"] = roof["step_achieved"] / hbm
+    roof["step_frac_all"] = roof["step_achieved_all"] / hbm
+    value = toks / (dev_ms * 1e-3)
+    cpu = None
+    if world == 1 and args.cpu_seconds > 0:
+        cpu = cpu_c3(pkg, args.cpu_seconds, os.cpu_count() or 1)
+    line = {
+        "metric": C3_METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
+        "ms_per_step": dev_ms / max(rounds, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32 activations, f16 EXL3 codebook weights, int8 Q8_0 / Q8_KV, f32 accumulate (router, norms, combine in f64)",
+        "data": "synthetic",
+        "config": {"workload": "c3", "n_layer": cfg["n_layer"], "hidden": cfg["hidden"], "n_expert": cfg["n_expert"], "top_k": cfg["n_expert_used"],
+                   "expert_ff": cfg["expert_ff"], "vocab": cfg["vocab"], "experts": "exl3-3bit", "dense": "q8_0", "kv": "q8_kv",
+                   "context": ctx, "spec_k": 3, "batch": 1, "greedy": True, "cycle_alpha": args.alpha,
+                   "parallelism": "ep%d" % world if world > 1 else "single",
+                   "l2": "inputs larger than L2: a pass streams ~%.1f GB of weights and cache" % (by["all"] / 1e9)},
+        "speculation": gen_stats, "verify_step_us": {"rows_1": step_us[1], "rows_4": step_us[4]},
+        "roofline": roof, "cpu_baseline": cpu,
+        "e2e": {"value": toks / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * rows_avg, "d2h_bytes_per_step": 8 + 512 * rows_avg,
+                "wall_ms_per_step": wall_s * 1e3 / max(rounds, 1)},
+        "gpu_launches": (n_k - 1) * rounds, "launches_per_pass": n_k - 1, "clocks": clocks,
+        "kernels": {k: v for k, v in sorted(kern.items(), key=lambda kv: -kv[1]["total_us"])},
+    }
+    print(json.dumps(line))
+
+
+def cpu_c3(pkg, budget_s, threads):
+    """Accepted tok/s of the CPU restatement of the reference's scalar path on the config-3 shapes.  The CPU path verifies one
+    token at a time (a batched pass is bitwise the one-at-a-time pass there), so its accepted tok/s is 1 / (seconds a token).
+    Sample: models of 4 and of 8 layers (one and two periods of the 3:1 pattern) with the full-size layers, vocabulary and head, a
+    few tokens each; a token of the 48-layer model costs t4 + 11 * (t8 - t4)."""
+    import torch  # noqa: F401
+    from oracle import binding as ob
+    md, szlib = pkg.model, pkg.lib
+    per = {}
+    ntok = 0
+    for nl in (4, 8):
+        cfg = dict(C3, n_layer=nl)
+        M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device="cpu", cycle_alpha=C3_ALPHA)
+        hm = md.HostModel(M)
+        s = ob.Session(hm, kv_q8=True, threads=threads)
+        s.step(1, want_logits=True)  # warm: page the weights in
+        t0, n = time.perf_counter(), 0
+        while True:
+            s.step(2 + n, want_logits=True)
+            n += 1
+            if time.perf_counter() - t0 > budget_s / 3 or n >= 16:
+                break
+        per[nl] = (time.perf_counter() - t0) / n
+        ntok += n
+        del s, hm, M
+    t_tok = per[4] + 11 * max(per[8] - per[4], 0.0)
+    return {"value": 1.0 / t_tok, "unit": "tok/s", "cores": threads, "kind": "port",
+            "sample": "%d tokens through 4- and 8-layer slices of the model (full-size layers, vocabulary, head), short context; "
+                      "seconds a token extrapolated to 48 layers: %.3f" % (ntok, t_tok),
+            "seconds_per_token": t_tok, "t4": per[4], "t8": per[8]}
+
+
+def run_reference_c3(args):
+    """The reference arm: the reference's own CPU implementation of the path - its scalar Session restated in C (the reference is
+    Rust and cannot be built here) - on all host cores, on a bounded sample of the config-3 workload."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    threads = os.cpu_count() or 1
+    cpu = cpu_c3(pkg, max(10.0, min(60.0, 2.0 * args.steps)), threads)
+    v = cpu["value"]
+    cpu_line = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    print(json.dumps({
+        "impl": "reference", "metric": C3_METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (f64 accumulate)",
+        "data": "synthetic", "config": {"workload": "c3", "context": "short (the sample does not fill 24576 positions)", "spec_k": 3, "batch": 1},
+        "cpu_baseline": cpu_line, "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+
+
+# ---- workload c2-moe: the MoE sublayer microbench ---------------------------------------------------------------------------------
 def build_layers(fmt, n_layers, device, seed=1):
     import __graft_entry__ as graft
     pkg = graft.load_package()
@@ -125,7 +380,7 @@ def cpu_step_seconds(host_layer, x, threads, budget_s):
             return el / reps, reps
 
 
-def run_reference(args):
+def run_reference_c2(args):
     """The reference arm: the reference's own CPU implementation of the path, i.e. its scalar f64-accumulating Session::moe
     restated in C (the reference itself is Rust and cannot be built here), on all host cores."""
     rank = int(os.environ.get("RANK", "0"))
@@ -259,6 +514,11 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe"])
+    ap.add_argument("--alpha", type=float, default=C3_ALPHA, help="c3: how strongly the synthetic model continues its token cycles")
+    ap.add_argument("--profile-passes", type=int, default=0, help="c3: only run this many 4-row verify passes (for ncu), no timing")
+    ap.add_argument("--ctx", type=int, default=C3_CTX, help="c3: context length the decode runs at")
+    ap.add_argument("--n-layer", type=int, default=C3["n_layer"], help="c3: layers (a smaller model for a quick check; not the benchmark)")
     ap.add_argument("--format", default="exl3", choices=["exl3", "iq3_s", "q8_0"])
     ap.add_argument("--also", default="iq3_s", help="comma list of further formats to time and report under 'also' ('' for none)")
     ap.add_argument("--layers", type=int, default=8)
@@ -266,8 +526,10 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph of the K steps")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     args = ap.parse_args()
+    if args.workload == "c3":
+        return run_reference_c3(args) if args.impl == "reference" else run_c3(args)
     if args.impl == "reference":
-        return run_reference(args)
+        return run_reference_c2(args)
 
     import torch
     rank = int(os.environ.get("RANK", "0"))

@@ -243,7 +243,8 @@ typedef struct sz_gen_params {
 typedef struct sz_gen_stats {
     int32_t n_tokens, passes, drafted, accepted, lookup_passes, rounds;
     int32_t pos_tried[8], pos_right[8];
-    double draft_ms, verify_ms, commit_ms;
+    double draft_ms, verify_ms, commit_ms;   /* host wall clock of the three parts of a round */
+    double device_ms;                          /* the passes alone, by events on their stream */
 } sz_gen_stats;
 int sz_generate(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint32_t* out, int32_t* pass_log, int pass_cap,
                 sz_gen_stats* stats, uint64_t stream);
@@ -265,7 +266,8 @@ void sz_gen_free(sz_gen* g);
 int sz_ep_unique_id(uint8_t id[128]);
 int sz_ep_init(int rank, int world, const uint8_t id[128]);
 int sz_ep_world(void);
-void sz_ep_destroy(void);
+/* Refused (SZ_E_ARG) while a session that recorded passes over the communicator is alive: destroy the sessions first. */
+int sz_ep_destroy(void);
 /* The two halves of an expert-parallel MoE pass, for hosts that exchange the partial sums themselves (and for testing several
  * ranks on one GPU): the partial (int64 [m][hidden], this rank's experts only), and the conversion of a summed buffer to f32. */
 int sz_moe_verify_partial(const sz_moe_layer* layer, uint64_t x, int m, uint64_t y_fix, uint64_t scratch, int64_t scratch_bytes,

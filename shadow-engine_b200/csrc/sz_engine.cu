@@ -356,7 +356,12 @@ struct sz_gen {
     std::vector<uint32_t> hist, top, last;
     int n = 0;            // tokens emitted so far
     bool done = false;    // an end-of-generation token was drawn
-    ~sz_gen() { sz_drafter_free(sd); }
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // bracket a pass on its stream: the device's share of a round
+    ~sz_gen() {
+        sz_drafter_free(sd);
+        if (ev0) cudaEventDestroy(ev0);
+        if (ev1) cudaEventDestroy(ev1);
+    }
 };
 
 extern "C" int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint64_t stream, sz_gen** out) {
@@ -367,6 +372,7 @@ extern "C" int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt,
     sz_gen* g = new sz_gen();
     g->s = s; g->p = *p;
     g->top.resize(SZ_MAX_VERIFY * 128); g->last.resize(128);
+    if (cudaEventCreate(&g->ev0) != cudaSuccess || cudaEventCreate(&g->ev1) != cudaSuccess) { delete g; return sz_fail(SZ_E_CUDA, "sz_gen_begin: no events"); }
     int rc = sz_session_prefill(s, (const int32_t*)prompt, n_prompt, stream);
     const int tail = (n_prompt - 1) % SZ_MAX_VERIFY + 1;  // rows of the last prompt pass
     if (!rc) rc = sz_session_result(s, nullptr, g->top.data(), nullptr, stream);
@@ -418,9 +424,13 @@ extern "C" int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_lo
         for (int i = 0; i < nd; i++) batch[1 + i] = (int32_t)draft[i];
         const int m = 1 + nd;
         const bool dev_accept = p->greedy && p->device_accept;
+        cudaEventRecord(g->ev0, (cudaStream_t)stream);
         if ((rc = sz_session_verify(s, batch, m, dev_accept ? SZ_ACCEPT_GREEDY : SZ_ACCEPT_NONE, p->eog_token, 1, stream))) break;
+        cudaEventRecord(g->ev1, (cudaStream_t)stream);
         int32_t kn[2] = {1, 0};
         if ((rc = sz_session_result(s, dev_accept ? kn : nullptr, g->top.data(), nullptr, stream))) break;
+        float dev = 0.f;
+        if (cudaEventElapsedTime(&dev, g->ev0, g->ev1) == cudaSuccess) stats->device_ms += dev;
         const double t2 = now_ms();
         stats->verify_ms += t2 - t1;
         int keep = 1;

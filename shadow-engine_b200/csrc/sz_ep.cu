@@ -25,6 +25,7 @@ struct Ep {
     fn_errstr errstr = nullptr;
     NcclComm comm = nullptr;
     int rank = 0, world = 0;
+    int graph_refs = 0;  // recorded passes (CUDA graphs) that contain a collective of this communicator
 } g_ep;
 
 int load_nccl() {
@@ -73,11 +74,19 @@ extern "C" int sz_ep_init(int rank, int world, const uint8_t id[128]) {
 
 extern "C" int sz_ep_world(void) { return g_ep.world; }
 
-extern "C" void sz_ep_destroy(void) {
+int sz_ep_graph_refs(int delta) { return g_ep.graph_refs += delta; }
+
+// NCCL waits inside ncclCommDestroy until every graph that recorded one of the communicator's collectives is gone, so a destroy
+// with such a session alive would never return: it is refused instead.
+extern "C" int sz_ep_destroy(void) {
+    if (g_ep.comm && g_ep.graph_refs > 0)
+        return sz_fail(SZ_E_ARG, "sz_ep_destroy: %d recorded pass(es) of live sessions still hold the communicator; destroy the sessions first",
+                       g_ep.graph_refs);
     if (g_ep.comm) g_ep.destroy(g_ep.comm);
     g_ep.comm = nullptr;
     g_ep.world = 0;
     g_ep.rank = 0;
+    return SZ_OK;
 }
 
 int sz_ep_allreduce_i64(long long* buf, size_t count, cudaStream_t st) {

@@ -750,11 +750,17 @@ static int sz_moe_run(const sz_moe_layer* L0, uint64_t x, int m, float* y, long 
     return SZ_OK;
 }
 
-extern "C" int sz_moe_finish(uint64_t y_fix, int m, int hidden, uint64_t y, uint64_t stream) {
+// pdl: whether the launch may overlap the tail of the kernel before it.  After a collective it may not: a library's kernel is no
+// party to the programmatic-dependency protocol, so the finish follows it in plain stream order.
+static int sz_moe_finish_launch(uint64_t y_fix, int m, int hidden, uint64_t y, uint64_t stream, bool pdl) {
     if (!y_fix || !y || m < 1 || m > SZ_MAX_VERIFY || hidden < 1 || (y_fix & 7) || (y & 3)) return sz_fail(SZ_E_ARG, "sz_moe_finish: bad argument");
     const int n = m * hidden;
-    SZ_CUDA(sz_launch("moe_finish", sz_yfix_finish_kernel, dim3((n + 255) / 256), dim3(256), 0, (cudaStream_t)stream, true, (const long long*)y_fix, n, (float*)y));
+    SZ_CUDA(sz_launch("moe_finish", sz_yfix_finish_kernel, dim3((n + 255) / 256), dim3(256), 0, (cudaStream_t)stream, pdl, (const long long*)y_fix, n, (float*)y));
     return SZ_OK;
+}
+
+extern "C" int sz_moe_finish(uint64_t y_fix, int m, int hidden, uint64_t y, uint64_t stream) {
+    return sz_moe_finish_launch(y_fix, m, hidden, y, stream, false);  // the caller's own exchange came before it
 }
 
 extern "C" int sz_moe_verify_partial(const sz_moe_layer* L, uint64_t x, int m, uint64_t y_fix, uint64_t scratch, int64_t scratch_bytes,
@@ -774,8 +780,9 @@ extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t 
     const SzMoeScratch S = sz_moe_layout(L, m);
     long long* y_fix = (long long*)((u8*)scratch + S.y_fix);
     if ((rc = sz_moe_run(L, x, m, nullptr, y_fix, route_idx, route_w, scratch, scratch_bytes, stream))) return rc;
-    if (sz_ep_world() > 1 && (rc = sz_ep_allreduce_i64(y_fix, (size_t)m * L->hidden, (cudaStream_t)stream))) return rc;
-    return sz_moe_finish((uint64_t)y_fix, m, L->hidden, y, stream);
+    const bool exchange = sz_ep_world() > 1;
+    if (exchange && (rc = sz_ep_allreduce_i64(y_fix, (size_t)m * L->hidden, (cudaStream_t)stream))) return rc;
+    return sz_moe_finish_launch((uint64_t)y_fix, m, L->hidden, y, stream, !exchange);
 }
 
 extern "C" int sz_moe_verify_host(const sz_moe_layer* L, const float* x_host, int m, float* y_host, int32_t* route_idx_host,

@@ -19,6 +19,9 @@ struct SzLayerBuf {
     int attn_index;    // index among attention layers, or -1
 };
 
+int sz_ep_graph_refs(int delta);  // sz_ep.cu: recorded passes that hold the communicator
+extern "C" int sz_ep_world(void);
+
 struct sz_session {
     sz_model model;
     std::vector<sz_layer> layers;
@@ -50,8 +53,10 @@ struct sz_session {
     int inflight;           // a pass was launched and the stream not synchronised since: the id staging buffer may still be read
     int use_graphs;
     std::map<int, cudaGraphExec_t> graphs;
+    int ep_graphs = 0;      // how many of them recorded a collective of the expert-parallel communicator
     ~sz_session() {
         for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
+        sz_ep_graph_refs(-ep_graphs);
         if (h_pin) cudaFreeHost(h_pin);
     }
 };
@@ -623,7 +628,10 @@ extern "C" int sz_session_verify(sz_session* s, const int32_t* ids, int m, int a
                 cudaError_t e2 = cudaStreamEndCapture(st, &g);
                 if (prc == SZ_OK && e2 == cudaSuccess && g) {
                     cudaGraphExec_t ge = nullptr;
-                    if (cudaGraphInstantiate(&ge, g, 0) == cudaSuccess) s->graphs[key] = ge;
+                    if (cudaGraphInstantiate(&ge, g, 0) == cudaSuccess) {
+                        s->graphs[key] = ge;
+                        if (sz_ep_world() > 1) { s->ep_graphs++; sz_ep_graph_refs(1); }
+                    }
                 }
                 if (g) cudaGraphDestroy(g);
                 (void)cudaGetLastError();

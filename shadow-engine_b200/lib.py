@@ -91,7 +91,7 @@ SYMBOLS = {
     "sz_ep_unique_id": (C.c_int, [C.c_void_p]),
     "sz_ep_init": (C.c_int, [C.c_int, C.c_int, C.c_void_p]),
     "sz_ep_world": (C.c_int, []),
-    "sz_ep_destroy": (None, []),
+    "sz_ep_destroy": (C.c_int, []),
     "sz_moe_verify_partial": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_int64, C.c_uint64]),
     "sz_moe_finish": (C.c_int, [C.c_uint64, C.c_int, C.c_int, C.c_uint64, C.c_uint64]),
     "sz_moe_static_scratch_max": (C.c_int, [C.POINTER(C.c_int64)]),

@@ -47,7 +47,8 @@ class GenParams(C.Structure):
 
 class GenStats(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("n_tokens", "passes", "drafted", "accepted", "lookup_passes", "rounds")] + \
-               [("pos_tried", C.c_int32 * 8), ("pos_right", C.c_int32 * 8), ("draft_ms", C.c_double), ("verify_ms", C.c_double), ("commit_ms", C.c_double)]
+               [("pos_tried", C.c_int32 * 8), ("pos_right", C.c_int32 * 8), ("draft_ms", C.c_double), ("verify_ms", C.c_double), ("commit_ms", C.c_double),
+                ("device_ms", C.c_double)]
 
 
 # BASELINE config 1: the CPU-runnable tiny hybrid MoE (4 layers D D D A; hidden 512; 8 q / 2 kv heads of 64; DeltaNet 4 heads of 64;
