@@ -35,6 +35,7 @@ C3 = dict(n_layer=48, hidden=2048, streams=4, hc_rank=256, vocab=151936, n_head=
           n_expert=512, n_expert_used=10, expert_ff=512, shared_ff=512, ssm_k_heads=16, ssm_v_heads=32, ssm_head_dim=128, conv_k=4,
           attn_interval=4, eps=1e-6, rope_theta=1e7)
 C3_CTX = 24576
+GATEUP_TRAFFIC = 33029376 + 7936   # bytes a launch of sz_x3_gateup_kernel<3,4> moved (read + write) under ncu, 39 routed + 1 shared expert
 C3_METRIC = "accepted tok/s at spec K=3"
 
 
@@ -133,6 +134,7 @@ def run_c3(args):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line
         dist.init_process_group("nccl")
         ep.init_from_process_group()
     hbm, peak_kind = peaks()
@@ -259,7 +261,9 @@ def run_c3(args):
 
     by = c3_bytes(cfg, ctx, distinct, dense_bytes)
     be = expert_bytes("exl3", cfg["hidden"], cfg["expert_ff"])
-    roof = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "traffic": None, "kernel": "gateup_exl3s"}
+    # traffic: dram__bytes_read + write of one launch of this kernel on these shapes (39 + 1 experts), from an ncu --set full capture
+    roof = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "traffic": GATEUP_TRAFFIC if world == 1 else None,
+            "traffic_source": "ncu capture of the same kernel and shapes on the c2-moe workload (40 experts a launch)", "kernel": "gateup_exl3s"}
     ks = kern.get("gateup_exl3s")
     if ks:
         # gate + up of a layer's distinct routed experts and of the shared expert: 2/3 of their bytes, one launch a layer
@@ -557,7 +561,8 @@ def main():
         # two launches carry that name (routed, shared): the routed one is the first of each pair; both are averaged here with
         # bytes of both, so the figure is the pair's
         bytes_pair = (r["distinct"] + 1) * r["expert_bytes"] * 2 / 3
-        out = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "traffic": None, "kernel": name}
+        out = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "traffic": GATEUP_TRAFFIC if name == "gateup_exl3" else None,
+               "kernel": name}
         if ks:
             dur_us = ks["avg_us"] * 2  # the pair
             out["achieved"] = bytes_pair / (dur_us * 1e-6) / 1e9

@@ -80,7 +80,9 @@ def _free_port():
 def _rank(rank, world, port, out_dir):
     import threading
     import torch.distributed as dist
-    threading.Timer(150, lambda: os._exit(3)).start()   # a rank that waits for a peer that died ends by itself
+    dog = threading.Timer(150, lambda: os._exit(3))     # a rank that waits for a peer that died ends by itself
+    dog.daemon = True
+    dog.start()
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("gloo", rank=rank, world_size=world)
