@@ -9,7 +9,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libshadowzero_b200.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC,-Wall",
-         "-fmad=true"]
+         "-fmad=true"] + os.environ.get("SZ_NVCC_FLAGS", "").split()   # e.g. SZ_NVCC_FLAGS=-DSZ_PHASES for in-kernel phase stamps
 
 
 def sources():

@@ -52,10 +52,31 @@ static inline cudaError_t sz_launch(const char* name, void (*kernel)(KArgs...), 
 // ---- device side --------------------------------------------------------------------------------------------------------
 #ifdef __CUDACC__
 
+// Phase stamps, debug builds only (-DSZ_PHASES): thread 0 of a block keeps clock64() readings in registers and one chosen block
+// writes them out at the end; sz_phase_read_<file> copies them to the host.  Compiled out otherwise.
+#ifdef SZ_PHASES
+static __device__ long long sz_phase_t[16][16];
+#define SZ_PH_DECL long long _ph[12]; int _phn = 0; (void)_ph; (void)_phn
+#define SZ_PH() do { if (threadIdx.x == 0 && _phn < 12) { _ph[_phn++] = clock64(); } } while (0)
+#define SZ_PH_FLUSH(kid, cond) do { if (threadIdx.x == 0 && (cond)) { for (int _i = 0; _i < 12; _i++) sz_phase_t[kid][_i] = _i < _phn ? _ph[_i] : 0; } } while (0)
+#else
+#define SZ_PH_DECL do {} while (0)
+#define SZ_PH() do {} while (0)
+#define SZ_PH_FLUSH(kid, cond) do {} while (0)
+#endif
+
 // Wait for the kernels this one depends on (no-op when launched without the PDL attribute).
 __device__ __forceinline__ void sz_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 // Let the next kernel on the stream begin its prologue.
 __device__ __forceinline__ void sz_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// A 16-byte read-only load the compiler must leave where it is written: a plain __ldg may be sunk to its first use, which for a
+// prefetch placed ahead of griddepcontrol.wait would put it after the wait.  Volatile asm statements keep their order.
+__device__ __forceinline__ uint4 sz_ldg16_here(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 
 __device__ __forceinline__ float sz_f16_to_f32(u16 h) { return __half2float(__ushort_as_half(h)); }
 __device__ __forceinline__ float sz_bf16_to_f32(u16 b) { return __uint_as_float((u32)b << 16); }
@@ -72,7 +93,10 @@ __device__ __forceinline__ double sz_warp_sum(double v) {
 }
 
 // sigmoid as the CPU reference computes it: in f64, then narrowed (crates/shadowzero-model/src/forward.rs:262-264).
-__device__ __forceinline__ float sz_sigmoid(float x) { return (float)(1.0 / (1.0 + exp(-(double)x))); }
+// The CPU reference takes the sigmoid in f64 and rounds (forward.rs:262-264).  A double-precision exp and divide cost about a
+// microsecond of dependent latency each on this part, which is the whole budget of a kernel here, so this is the f32 form: it
+// differs from the rounded f64 value by an ulp or two, the same size as the f32 accumulation noise of the dot products around it.
+__device__ __forceinline__ float sz_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
 __device__ __forceinline__ float sz_silu(float x) { return x * sz_sigmoid(x); }
 
 // ---- mbarrier + bulk async copy (TMA engine, untiled form) ---------------------------------------------------------------

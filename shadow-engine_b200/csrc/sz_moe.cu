@@ -93,6 +93,8 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
     __shared__ int s_last;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ld = ne + 1;
+    SZ_PH_DECL;
+    SZ_PH();  // 0 start
     // this block's router rows do not depend on the previous kernel: fetch them before waiting for it (16 float4 loads in flight a lane)
     const int r = blockIdx.x * SZ_ROUTE_WARPS + warp;
     const bool live = r < ne || (r == ne && shared_router != nullptr);
@@ -100,13 +102,21 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
     constexpr int WN = 16;  // float4 chunks of the row a lane keeps in flight: covers hidden <= 2048 in one sweep
     float4 w[WN];
 #pragma unroll
-    for (int u = 0; u < WN; u++) w[u] = (live && 32 * u + lane < H / 4) ? __ldg(wrow + 32 * u + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int u = 0; u < WN; u++) {
+        w[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (live && 32 * u + lane < H / 4) {
+            const uint4 q = sz_ldg16_here(wrow + 32 * u + lane);
+            w[u] = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
+        }
+    }
     sz_pdl_wait();
     sz_pdl_trigger();
+    SZ_PH();  // 1 after wait
     // the streaming kernels' fixed-point accumulators start every call at zero
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_n; i += gridDim.x * blockDim.x) zero[i] = make_uint4(0, 0, 0, 0);
     for (int i = threadIdx.x; i < m * H / 4; i += blockDim.x) ((float4*)xs)[i] = __ldcg((const float4*)x + i);
     __syncthreads();
+    SZ_PH();  // 2 x staged
 
     // ---- logits: row r of the router (row ne: the shared expert's gate) against every x row, f64 accumulate
     if (live) {
@@ -145,12 +155,14 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
     }
 
     // ---- the last block to arrive routes every row
+    SZ_PH();  // 3 logits done
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) s_last = (atomicAdd(&ctrl[0], 1u) == gridDim.x - 1);
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    SZ_PH();  // 4 ticket taken
 
     for (int j = warp; j < m; j += SZ_ROUTE_WARPS) {
         int32_t* oi = out_idx ? out_idx + j * k : nullptr;
@@ -161,6 +173,7 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
     }
     for (int i = threadIdx.x; i < ne; i += blockDim.x) cnt[i] = 0;
     __syncthreads();
+    SZ_PH();  // 5 rows routed
 
     // ---- plan: groups in ascending expert order, rows ascending inside a group
     // with expert parallelism only the experts this rank holds enter the plan; routing itself is the same on every rank
@@ -210,6 +223,8 @@ sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restri
         plan_sh->count[0] = m;
         ctrl[0] = 0;  // ready for the next call
     }
+    SZ_PH();  // 6 plan written
+    SZ_PH_FLUSH(0, true);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------------------
@@ -805,3 +820,7 @@ extern "C" int sz_moe_verify_host(const sz_moe_layer* L, const float* x_host, in
     SZ_CUDA(cudaStreamSynchronize(st));
     return SZ_OK;
 }
+
+#ifdef SZ_PHASES
+extern "C" int sz_phase_read_moe(long long* out) { return cudaMemcpyFromSymbol(out, sz_phase_t, sizeof(long long) * 16 * 16) == cudaSuccess ? 0 : 1; }
+#endif

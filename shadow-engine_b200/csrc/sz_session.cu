@@ -8,6 +8,7 @@
 // then the buffers swap.  The KV cache is append-only: rejected positions are overwritten by the next pass.
 #include "sz_session_kernels.cuh"
 
+#include <cmath>
 #include <map>
 #include <new>
 #include <stdlib.h>
@@ -35,6 +36,11 @@ struct sz_session {
     u8* base;
     int64_t bytes;
     float *r, *rn, *hdown, *mix, *u, *g, *y;
+    float* r2;            // the second residual buffer of the fused hyper-connection read (reads ping-pong between r and r2)
+    long long* hc_acc;    // [3][8][SZ_HC_ACC_ROWS] fixed-point accumulators of the fused read
+    double* rope_den;     // [rope_dims / 2]: theta^(2 i / rope_dims), computed on the host as the CPU reference computes it
+    int hc_fast;          // every hyper-connection of the model fits the fused kernels
+    int hc_n;             // reads launched so far in the pass being built (buffer parities are static per launch)
     float *d_xin, *d_z, *d_b, *d_a, *d_xc, *d_beta, *d_decay, *d_og;   // per-layer saved: xin, xc, beta, decay [n_delta][8][...]
     float *S[2], *conv[2];
     float *a_qg, *a_k, *a_v, *a_q, *a_gate, *a_o, *a_part;
@@ -64,7 +70,7 @@ struct sz_session {
 static int sz_is_attn(const sz_model_config& c, int l) { return l % c.attn_interval == c.attn_interval - 1; }
 
 struct SzSessLayout {
-    int64_t r, rn, hdown, mix, u, g, y, d_xin, d_z, d_b, d_a, d_xc, d_beta, d_decay, d_og, S0, S1, conv0, conv1, a_qg, a_k, a_v, a_q, a_gate,
+    int64_t r, r2, hc_acc, rope, rn, hdown, mix, u, g, y, d_xin, d_z, d_b, d_a, d_xc, d_beta, d_decay, d_og, S0, S1, conv0, conv1, a_qg, a_k, a_v, a_q, a_gate,
         a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, total;
     int64_t moe_bytes, S_bytes, conv_bytes, kv_bytes;
     int splits, splits2;
@@ -81,7 +87,7 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
     const int64_t qd = (int64_t)c.n_head * c.head_dim, kvd = (int64_t)c.n_kv_head * c.head_dim;
     int64_t o = 0;
     auto take = [&](int64_t bytes) { int64_t at = o; o = up256(o + bytes); return at; };
-    L->r = take(4 * M * CH); L->rn = take(4 * M * CH); L->hdown = take(4 * M * c.hc_rank); L->mix = take(4 * M * CH);
+    L->r = take(4 * M * CH); L->r2 = take(4 * M * CH); L->hc_acc = take(8 * 3 * M * SZ_HC_ACC_ROWS); L->rope = take(8 * (int64_t)(c.rope_dims > 0 ? c.rope_dims / 2 : 1)); L->rn = take(4 * M * CH); L->hdown = take(4 * M * c.hc_rank); L->mix = take(4 * M * CH);
     L->u = take(4 * M * H); L->g = take(4 * M * C); L->y = take(4 * M * H);
     const int64_t nd = n_delta > 0 ? n_delta : 1;
     L->d_xin = take(4 * nd * M * ch); L->d_xc = take(4 * nd * M * ch); L->d_beta = take(4 * nd * M * vh); L->d_decay = take(4 * nd * M * vh);
@@ -229,6 +235,8 @@ extern "C" int sz_session_reset(sz_session* s, uint64_t stream) {
     return SZ_OK;
 }
 
+static bool sz_hc_fits(const sz_model_config& c, const sz_hc& hc, bool inject);
+
 extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t mem, int64_t bytes, uint64_t stream, sz_session** out) {
     int rc = sz_model_check(m);
     if (rc) return rc;
@@ -248,6 +256,13 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
         const char* e = getenv("SZ_SESSION_GRAPHS");  // A/B switch: 0 = launch every kernel eagerly
         s->use_graphs = !(e && atoi(e) == 0);
     }
+    {
+        const char* e = getenv("SZ_GENERIC_KERNELS");
+        bool fast = !(e && atoi(e) != 0) && sz_hc_fits(m->cfg, m->output_hc, false);
+        for (int l = 0; l < m->cfg.n_layer && fast; l++) fast = sz_hc_fits(m->cfg, s->layers[l].hc_attn, true) && sz_hc_fits(m->cfg, s->layers[l].hc_ffn, true);
+        s->hc_fast = fast ? 1 : 0;
+        s->hc_n = 0;
+    }
     s->lb.resize(m->cfg.n_layer);
     s->n_delta = s->n_attn = 0;
     for (int l = 0; l < m->cfg.n_layer; l++) {
@@ -257,7 +272,7 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     }
     u8* b = (u8*)mem;
     s->base = b; s->bytes = bytes;
-    s->r = (float*)(b + L.r); s->rn = (float*)(b + L.rn); s->hdown = (float*)(b + L.hdown); s->mix = (float*)(b + L.mix);
+    s->r = (float*)(b + L.r); s->r2 = (float*)(b + L.r2); s->hc_acc = (long long*)(b + L.hc_acc); s->rope_den = (double*)(b + L.rope); s->rn = (float*)(b + L.rn); s->hdown = (float*)(b + L.hdown); s->mix = (float*)(b + L.mix);
     s->u = (float*)(b + L.u); s->g = (float*)(b + L.g); s->y = (float*)(b + L.y);
     s->d_xin = (float*)(b + L.d_xin); s->d_z = (float*)(b + L.d_z); s->d_b = (float*)(b + L.d_b); s->d_a = (float*)(b + L.d_a);
     s->d_xc = (float*)(b + L.d_xc); s->d_beta = (float*)(b + L.d_beta); s->d_decay = (float*)(b + L.d_decay); s->d_og = (float*)(b + L.d_og);
@@ -270,6 +285,11 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->moe_scratch = b + L.moe; s->moe_scratch_bytes = L.moe_bytes;
     s->attn_splits = L.splits; s->attn_splits2 = L.splits2;
     if ((rc = sz_session_reset(s, stream))) { delete s; return rc; }
+    if (m->cfg.rope_dims > 0) {  // forward.rs:290-299: angle = pos / theta^(2 i / rope_dims); the denominators never change
+        std::vector<double> den(m->cfg.rope_dims / 2);
+        for (size_t i = 0; i < den.size(); i++) den[i] = pow((double)m->cfg.rope_theta, 2.0 * (double)i / (double)m->cfg.rope_dims);
+        if (cudaMemcpy(s->rope_den, den.data(), den.size() * 8, cudaMemcpyHostToDevice) != cudaSuccess) { delete s; return sz_fail(SZ_E_CUDA, "rope table upload failed"); }
+    }
     *out = s;
     return SZ_OK;
 }
@@ -393,9 +413,47 @@ static SzDenseJob sz_job(const sz_tensor& t, float* out, int ostride, int epi = 
 
 // ---- one pass ---------------------------------------------------------------------------------------------------------------------------
 // hyper-connection read of `hc` for the m rows: applies the pending write (g_prev, y_prev) first; leaves u (and g when the read injects)
+static bool sz_hc_fits(const sz_model_config& c, const sz_hc& hc, bool inject) {
+    const int H = c.hidden, C = c.streams, rank = c.hc_rank, cpr = rank / 8;
+    if (hc.down.type != SZ_TYPE_BF16 || hc.up.type != SZ_TYPE_BF16 || hc.norm.type != SZ_TYPE_F32) return false;
+    if (inject && hc.inject.type != SZ_TYPE_BF16) return false;
+    if (H % 64 || H > 2048 || rank % 8 || rank > 256 || rank + C > 320 || rank + C > SZ_HC_ACC_ROWS) return false;
+    if (cpr < 1 || (32 % cpr) || (16 * C * cpr) % 32 || 16 * C * cpr > 2048 || 16 * C > 64) return false;
+    return true;
+}
+
 static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bool pending, bool inject) {
     const sz_model_config& c = s->model.cfg;
     const int H = c.hidden, C = c.streams, CH = C * H;
+    if (s->hc_fast) {
+        // read n: residual in buffer n & 1, out the other; accumulator n % 3, the previous read's holds the gates of the pending write
+        const int n = s->hc_n++;
+        float* rin = (n & 1) ? s->r2 : s->r;
+        float* rout = (n & 1) ? s->r : s->r2;
+        const int64_t as = (int64_t)SZ_MAX_VERIFY * SZ_HC_ACC_ROWS;
+        long long* acc = s->hc_acc + (n % 3) * as;
+        long long* acc_prev = s->hc_acc + ((n + 2) % 3) * as;
+        long long* acc_next = s->hc_acc + ((n + 1) % 3) * as;
+        int nt = ((int)c.hc_rank + C + 31) / 32 * 32;
+        if (nt < 256) nt = 256;
+        cudaError_t e1 = cudaErrorInvalidValue, e2 = cudaErrorInvalidValue;
+#define SZ_HC_CASE(MM)                                                                                                                   \
+    case MM:                                                                                                                             \
+        e1 = sz_launch("hc_down", sz_hc_down_kernel<MM>, dim3(CH / 64), dim3(nt), 0, st, true, (const float*)rin, rout,                  \
+                       (const long long*)(pending ? acc_prev : nullptr), (const float*)s->y, (const float*)hc.norm.data,                 \
+                       (const u8*)hc.down.data, (const u8*)(inject ? hc.inject.data : 0), H, C, (int)c.hc_rank, c.eps, s->rn, acc,       \
+                       acc_next);                                                                                                        \
+        e2 = sz_launch("hc_up", sz_hc_up_kernel<MM>, dim3(H / 16), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data, \
+                       (const float*)s->rn, H, C, (int)c.hc_rank, s->u);                                                                 \
+        break;
+        switch (m) {
+            SZ_HC_CASE(1) SZ_HC_CASE(2) SZ_HC_CASE(3) SZ_HC_CASE(4) SZ_HC_CASE(5) SZ_HC_CASE(6) SZ_HC_CASE(7) SZ_HC_CASE(8)
+        }
+#undef SZ_HC_CASE
+        SZ_CUDA(e1);
+        SZ_CUDA(e2);
+        return SZ_OK;
+    }
     SZ_CUDA(sz_launch("hc_norm", sz_hc_norm_kernel, dim3(C, m), dim3(256), 0, st, true, s->r, (const float*)(pending ? s->g : nullptr),
                       (const float*)(pending ? s->y : nullptr), (const float*)hc.norm.data, H, C, c.eps, s->rn));
     SzDenseArgs a = {};
@@ -513,7 +571,7 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     if (rc) return rc;
     SZ_CUDA(sz_launch("attn_prep", sz_attn_prep_kernel, dim3(nh + 2 * nkv, m), dim3(128), 0, st, true, (const float*)s->a_qg, (const float*)s->a_k,
                       (const float*)s->a_v, (const float*)L.attn_q_norm.data, (const float*)L.attn_k_norm.data, nh, nkv, hd, s->ctx, c.eps,
-                      (const int32_t*)s->state, (int)c.rope_dims, c.rope_theta, q8, kc, vc, s->a_q, s->a_gate));
+                      (const int32_t*)s->state, (int)c.rope_dims, (const double*)s->rope_den, q8, kc, vc, s->a_q, s->a_gate));
     // the grouped tensor-core kernel serves the packed int8 cache with up to 64 queries a KV head; the simple kernel everything else
     static const bool generic_only = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;
     const bool grouped = q8 && !generic_only && (nh / nkv) * m <= 64;
@@ -540,6 +598,8 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
 static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
     const sz_model_config& c = s->model.cfg;
     const int H = c.hidden, C = c.streams;
+    s->hc_n = 0;
+    if (s->hc_fast) SZ_CUDA(cudaMemsetAsync(s->hc_acc, 0, sizeof(long long) * SZ_MAX_VERIFY * SZ_HC_ACC_ROWS, st));  // read 0 adds into buffer 0
     SZ_CUDA(sz_launch("embed", sz_embed_kernel, dim3(m), dim3(256), 0, st, false, (const int32_t*)s->ids, (const u8*)s->model.token_embd.data,
                       (int)s->model.token_embd.type, H, C, (int)c.vocab, s->r));
     int rc;
@@ -752,3 +812,7 @@ extern "C" int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, 
     s->len = len;
     return SZ_OK;
 }
+
+#ifdef SZ_PHASES
+extern "C" int sz_phase_read_session(long long* out) { return cudaMemcpyFromSymbol(out, sz_phase_t, sizeof(long long) * 16 * 16) == cudaSuccess ? 0 : 1; }
+#endif

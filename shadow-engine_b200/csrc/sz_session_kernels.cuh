@@ -73,6 +73,241 @@ sz_hc_mix_kernel(const float* __restrict__ mix, const float* __restrict__ rn, in
     u[(size_t)j * H + i] = a / (float)C;
 }
 
+// ---- hyper-connection read, fused form ---------------------------------------------------------------------------------------------
+// Two launches a read instead of four.  The work is split so that every weight byte is requested at once and the activation rows a
+// block stages are small:
+//   down kernel: block b owns columns [64 b, 64 b + 64) of the C*H-wide input (all inside one stream s).  Each thread keeps one row
+//   slice of the down (or inject) matrix - 128 contiguous bytes - in registers, fetched before the dependency wait.  The block
+//   applies the pending residual write to stream s of every row, takes the stream's RMS (every block of a stream computes the same
+//   sum in the same order), writes its 64 columns of the new residual and of rn, and adds its partial dot products to a fixed-point
+//   accumulator (64-bit integer atomics: the total does not depend on the order the blocks arrive in).
+//   up kernel: block b owns 16 positions h of the hidden dimension and the C rows s*H + h of the up matrix for each (512-byte rows
+//   at rank 256, one 16-byte piece a lane, all in flight before the wait), turns the accumulator into silu(down / C), and finishes
+//   u[h] = mean over streams of sigmoid(up row) * rn in the same block.
+// Residual streams ping-pong between two buffers (a block reads the whole stream while its neighbours write their columns); the
+// accumulator rotates over three (this read's, the previous read's - it holds the inject gates the pending write needs - and the
+// next read's, which block 0 clears).
+#define SZ_HC_ACC_ROWS 272                    // rank + streams, padded
+#define SZ_HC_FIX 1099511627776.0             // 2^40
+#define SZ_HC_FIX_INV (1.0 / 1099511627776.0)
+
+// grid C*H / 64; block: a multiple of 32 threads, at least rank + C (one thread a matrix row) and at most 320
+template <int M>  // rows of the pass: a compile-time count keeps every per-row loop free of branches
+__global__ void __launch_bounds__(320)
+sz_hc_down_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, const long long* __restrict__ g_acc, const float* __restrict__ y,
+                  const float* __restrict__ normw, const u8* __restrict__ down, const u8* __restrict__ inject, int H, int C, int rank,
+                  float eps, float* __restrict__ rn, long long* __restrict__ acc, long long* __restrict__ acc_next) {
+    __shared__ double red[10][SZ_MAX_VERIFY];
+    __shared__ float rinv[SZ_MAX_VERIFY];
+    __shared__ float gs[SZ_MAX_VERIFY];
+    __shared__ __align__(16) float xs[SZ_MAX_VERIFY][64];
+    __shared__ float nws[64];
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31, nt = blockDim.x;
+    const int CH = C * H;
+    const int c0 = blockIdx.x * 64;
+    SZ_PH_DECL;
+    SZ_PH();  // 0
+    const int s = c0 / H;
+    // this thread's 64 weights: constant data, requested before the wait
+    const u8* wrow = nullptr;
+    if (t < rank) wrow = down + ((size_t)t * CH + c0) * 2;
+    else if (inject != nullptr && t < rank + C) wrow = inject + ((size_t)(t - rank) * CH + c0) * 2;
+    uint4 w[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) w[i] = wrow ? sz_ldg16_here((const uint4*)wrow + i) : make_uint4(0, 0, 0, 0);
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    SZ_PH();  // 1 after wait
+    // every load of the prologue is issued before anything waits on one: the gates, the stream's rows, the mixer output
+    if (t < 64) nws[t] = __ldg(normw + c0 + t);
+    long long graw = 0;
+    if (g_acc && t < M) graw = __ldcg(g_acc + t * SZ_HC_ACC_ROWS + rank + s);
+    constexpr int NV = 2;  // float4 pieces of a stream row a thread holds: covers H <= 8 * blockDim
+    float4 rv[M][NV], yv[M][NV];
+#pragma unroll
+    for (int j = 0; j < M; j++) {
+#pragma unroll
+        for (int q = 0; q < NV; q++) {
+            const int i = t + q * nt;
+            const bool on = i < H / 4;
+            rv[j][q] = on ? __ldcg((const float4*)(r_in + ((size_t)j * C + s) * H) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            yv[j][q] = on && g_acc ? __ldcg((const float4*)(y + (size_t)j * H) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    if (blockIdx.x == 0)
+        for (int i = t; i < SZ_MAX_VERIFY * SZ_HC_ACC_ROWS; i += nt) acc_next[i] = 0;
+    if (t < M) gs[t] = g_acc ? 2.0f * sz_sigmoid((float)((double)graw * SZ_HC_FIX_INV) / (float)C) : 0.f;
+    __syncthreads();
+    SZ_PH();  // 2 gates
+    // the pending write, the stream's sum of squares for every row, and this block's 64 columns of the new residual
+    const int lo4 = (c0 - s * H) / 4;  // first float4 of the block's columns inside the stream
+#pragma unroll
+    for (int j = 0; j < M; j++) {
+        double ss = 0.0;
+        if (j < M) {
+            const float g = gs[j];
+#pragma unroll
+            for (int q = 0; q < NV; q++) {
+                const int i = t + q * nt;
+                float4 v = rv[j][q];
+                const float4 w4 = yv[j][q];
+                v.x = v.x + g * w4.x; v.y = v.y + g * w4.y; v.z = v.z + g * w4.z; v.w = v.w + g * w4.w;
+                ss += (double)v.x * (double)v.x;
+                ss += (double)v.y * (double)v.y;
+                ss += (double)v.z * (double)v.z;
+                ss += (double)v.w * (double)v.w;
+                if (i >= lo4 && i < lo4 + 16) *(float4*)&xs[j][4 * (i - lo4)] = v;
+            }
+            ss = sz_warp_sum(ss);
+            if (lane == 0) red[warp][j] = ss;
+        }
+    }
+    __syncthreads();
+    SZ_PH();  // 3 sums
+    if (t < M) {
+        double v = 0.0;
+        for (int q = 0; q < (nt >> 5); q++) v += red[q][t];
+        rinv[t] = (float)(1.0 / sqrt(v / (double)H + (double)eps));
+    }
+    __syncthreads();
+    SZ_PH();  // 4 rinv
+    // this block's 64 columns: the new residual and rn (to memory for the up kernel, to shared memory for the dot products)
+    for (int idx = t; idx < M * 64; idx += nt) {
+        const int j = idx >> 6, c = idx & 63;
+        const size_t at = (size_t)j * CH + c0 + c;
+        const float v = xs[j][c];
+        r_out[at] = v;
+        const float x = (float)((double)v * (double)rinv[j]) * nws[c];
+        rn[at] = x;
+        xs[j][c] = x;
+    }
+    __syncthreads();
+    SZ_PH();  // 5 columns
+    if (wrow == nullptr) return;
+    float a[M];
+#pragma unroll
+    for (int j = 0; j < M; j++) a[j] = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const u32 ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const float w0 = __uint_as_float(ww[q] << 16), w1 = __uint_as_float(ww[q] & 0xffff0000u);
+#pragma unroll
+            for (int j = 0; j < M; j++) {
+                if (j < M) {
+                    const float2 xv = *(const float2*)&xs[j][8 * i + 2 * q];
+                    a[j] = fmaf(w0, xv.x, a[j]);
+                    a[j] = fmaf(w1, xv.y, a[j]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < M; j++)
+        if (j < M) atomicAdd((unsigned long long*)(acc + j * SZ_HC_ACC_ROWS + t), (unsigned long long)__double2ll_rn((double)a[j] * SZ_HC_FIX));
+    SZ_PH();  // 6 dots + atomics issued
+    SZ_PH_FLUSH(1, blockIdx.x == 5);
+}
+
+// grid H / 16, block 256.  CPR = rank / 8: 16-byte pieces a row of the up matrix.
+template <int M>
+__global__ void __launch_bounds__(256)
+sz_hc_up_kernel(const long long* __restrict__ acc, const u8* __restrict__ up, const float* __restrict__ rn, int H, int C, int rank,
+                float* __restrict__ u) {
+    __shared__ __align__(16) float hd[SZ_MAX_VERIFY][256];
+    __shared__ float mixs[64][SZ_MAX_VERIFY];
+    const int t = threadIdx.x;
+    const int cpr = rank >> 3;
+    const int h0 = blockIdx.x * 16;
+    const int chunks = 16 * C * cpr;  // <= 2048
+    SZ_PH_DECL;
+    SZ_PH();  // 0
+    uint4 w[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int ch = t + 256 * i;
+        w[i] = make_uint4(0, 0, 0, 0);
+        if (ch < chunks) {
+            const int lr = ch / cpr, c = ch - lr * cpr;       // local row s * 16 + hl
+            const int row = (lr >> 4) * H + h0 + (lr & 15);
+            w[i] = sz_ldg16_here((const uint4*)(up + (size_t)row * rank * 2) + c);
+        }
+    }
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    SZ_PH();  // 1
+#ifdef SZ_PHASES
+    { u32 touch = 0;
+      for (int i = 0; i < 8; i++) touch ^= w[i].x ^ w[i].w;
+      if (touch == 0x12345679u) mixs[0][0] = 1.f;
+      SZ_PH(); }  // 1b weights arrived
+#endif
+    for (int idx = t; idx < M * rank; idx += 256) {
+        const int j = idx / rank, q = idx - j * rank;
+        const float v = (float)((double)__ldcg(acc + j * SZ_HC_ACC_ROWS + q) * SZ_HC_FIX_INV);
+        hd[j][q] = sz_silu(v / (float)C);
+    }
+    __syncthreads();
+    SZ_PH();  // 2 hd
+    // all partial dot products first, then the butterflies over the cpr lanes of a row interleaved (independent chains).  A thread's
+    // pieces all sit at the same place c of their rows (256 is a multiple of cpr), so its 8 inputs per row are read once.
+    float p[8][M];
+    {
+        const int c = t % cpr;
+        float4 x0[M], x1[M];
+#pragma unroll
+        for (int j = 0; j < M; j++) { x0[j] = *(const float4*)&hd[j][8 * c]; x1[j] = *(const float4*)&hd[j][8 * c + 4]; }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const u32 ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+            float wf[8];
+#pragma unroll
+            for (int q = 0; q < 4; q++) { wf[2 * q] = __uint_as_float(ww[q] << 16); wf[2 * q + 1] = __uint_as_float(ww[q] & 0xffff0000u); }
+#pragma unroll
+            for (int j = 0; j < M; j++) {
+                float v = wf[0] * x0[j].x;
+                v = fmaf(wf[1], x0[j].y, v); v = fmaf(wf[2], x0[j].z, v); v = fmaf(wf[3], x0[j].w, v);
+                v = fmaf(wf[4], x1[j].x, v); v = fmaf(wf[5], x1[j].y, v); v = fmaf(wf[6], x1[j].z, v); v = fmaf(wf[7], x1[j].w, v);
+                p[i][j] = v;
+            }
+        }
+    }
+    for (int o = cpr >> 1; o > 0; o >>= 1) {
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int j = 0; j < M; j++)
+                if (j < M) p[i][j] += __shfl_xor_sync(0xffffffffu, p[i][j], o);
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int ch = t + 256 * i;
+        if (ch < chunks && ch % cpr == 0) {
+            const int lr = ch / cpr;
+#pragma unroll
+            for (int j = 0; j < M; j++)
+                if (j < M) mixs[lr][j] = p[i][j];
+        }
+    }
+    __syncthreads();
+    SZ_PH();  // 3 dots
+    // mix * rn for each (stream, position, row), one a thread; then the mean over the streams
+    for (int idx = t; idx < 16 * C * M; idx += 256) {
+        const int lr = idx / M, j = idx - lr * M;
+        mixs[lr][j] = sz_sigmoid(mixs[lr][j]) * __ldcg(rn + ((size_t)j * C + (lr >> 4)) * H + h0 + (lr & 15));
+    }
+    __syncthreads();
+    for (int idx = t; idx < M * 16; idx += 256) {
+        const int j = idx >> 4, hl = idx & 15;
+        float a = 0.f;
+        for (int s = 0; s < C; s++) a += mixs[s * 16 + hl][j];
+        u[(size_t)j * H + h0 + hl] = a / (float)C;
+    }
+    SZ_PH();  // 4 u
+    SZ_PH_FLUSH(2, blockIdx.x == 5);
+}
+
 // ---- DeltaNet front end (forward.rs:829-861): causal conv (k taps) + SiLU over the rows of the pass, L2 norm of q and k heads,
 // beta and decay.  grid (ch / 256, m), block 256: a block takes 256 channels - whole heads, since the head width divides 256 - of
 // one row.  conv0 / conv1: (k-1) x ch, oldest first: the state BEFORE the pass (state[1] says which).  xin: [m][ch] raw projections.
@@ -81,7 +316,7 @@ sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ co
                      const float* __restrict__ cw, const float* __restrict__ b,
                      const float* __restrict__ a, const float* __restrict__ a_log, const float* __restrict__ dt, int kh, int vh, int d, int k,
                      float* __restrict__ xc, float* __restrict__ beta, float* __restrict__ decay) {
-    __shared__ float sx[256];
+    __shared__ double sred[8];
     sz_pdl_wait();
     sz_pdl_trigger();
     const int j = blockIdx.y;
@@ -98,13 +333,22 @@ sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ co
         }
         v = sz_silu((float)acc);
     }
-    sx[threadIdx.x] = v;
+    // L2 norm of the q and k heads (q also / sqrt(d)): squares summed per warp, then over the warps of the head
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const double sq = sz_warp_sum((double)v * (double)v);
+    if (lane == 0) sred[warp] = sq;
     __syncthreads();
     if (i < ch) {
-        if (i < 2 * kd) {  // a q or k channel: L2-normalise its head (q also / sqrt(d))
-            const int h0 = (threadIdx.x / d) * d;  // first channel of the head inside the block
-            double ss = 0.0;
-            for (int t = 0; t < d; t++) ss += (double)sx[h0 + t] * (double)sx[h0 + t];
+        if (i < 2 * kd) {
+            double ss;
+            if (d >= 32) {
+                const int w0 = (threadIdx.x / d) * (d / 32);
+                ss = 0.0;
+                for (int t = 0; t < d / 32; t++) ss += sred[w0 + t];
+            } else {  // heads narrower than a warp: sum inside the warp's head segment
+                ss = (double)v * (double)v;
+                for (int o = d >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            }
             const double n = 1.0 / sqrt(ss + 1e-6);
             float t = (float)((double)v * n);
             if (i < kd) t = t / sqrtf((float)d);
@@ -116,8 +360,8 @@ sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ co
         for (int h = threadIdx.x; h < vh; h += 256) {
             beta[j * vh + h] = sz_sigmoid(b[j * vh + h]);
             const float sp_in = a[j * vh + h] + dt[h];
-            const float sp = sp_in > 20.0f ? sp_in : (float)log1p(exp((double)sp_in));
-            decay[j * vh + h] = (float)exp((double)a_log[h] * (double)sp);
+            const float sp = sp_in > 20.0f ? sp_in : log1pf(expf(sp_in));
+            decay[j * vh + h] = expf(a_log[h] * sp);
         }
     }
 }
@@ -269,7 +513,7 @@ __device__ __forceinline__ void sz_kv_store(const float* src, int hd, int q8, u8
 __global__ void __launch_bounds__(128)
 sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, const float* __restrict__ vv, const float* __restrict__ wq,
                     const float* __restrict__ wk, int nh, int nkv, int hd, int ctx, float eps, const int32_t* __restrict__ state, int rope_dims,
-                    double theta, int q8, u8* __restrict__ kc, u8* __restrict__ vc, float* __restrict__ q, float* __restrict__ gate) {
+                    const double* __restrict__ rope_den, int q8, u8* __restrict__ kc, u8* __restrict__ vc, float* __restrict__ q, float* __restrict__ gate) {
     __shared__ float tmp[512];
     __shared__ double red[8];
     sz_pdl_wait();
@@ -294,11 +538,17 @@ sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, 
     __syncthreads();
     const int half = rope_dims / 2;
     for (int i = threadIdx.x; i < half; i += 128) {  // forward.rs:290-299
-        const double f = (double)pos / pow(theta, 2.0 * (double)i / (double)rope_dims);
-        const double cs = cos(f), sn = sin(f);
-        const double a0 = (double)tmp[i], b0 = (double)tmp[i + half];
-        tmp[i] = (float)(a0 * cs - b0 * sn);
-        tmp[i + half] = (float)(b0 * cs + a0 * sn);
+        // angle = pos / theta^(2i / rope_dims) in f64 (the table holds the denominators), reduced to [-pi, pi] in f64; sine and cosine
+        // of the reduced angle in f32
+        const double f = (double)pos / __ldg(rope_den + i);
+        const double kq = rint(f * 0.15915494309189535);
+        double rd = fma(-kq, 6.283185307179586, f);
+        rd = fma(-kq, 2.4492935982947064e-16, rd);
+        float sn, cs;
+        sincosf((float)rd, &sn, &cs);
+        const float a0 = tmp[i], b0 = tmp[i + half];
+        tmp[i] = a0 * cs - b0 * sn;
+        tmp[i + half] = b0 * cs + a0 * sn;
     }
     __syncthreads();
     if (isq) {
@@ -625,24 +875,68 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
     }
 }
 
-// merge the splits and gate: o = (acc / z) * sigmoid(gate).  grid (nh, m), block 256
+// merge the splits and gate: o = (acc / z) * sigmoid(gate).  grid (nh, m), block 256.  The splits' (max, sum) pairs are read by one
+// thread each, the coefficients exp(max_s - max) go through shared memory, and the weighted sum over the splits runs in four
+// interleaved groups of threads so that many partial rows are in flight at once.
 __global__ void __launch_bounds__(256)
 sz_attn_merge_kernel(const float* __restrict__ part, const float* __restrict__ gate, int nh, int hd, int splits, float* __restrict__ o) {
+    __shared__ float coef[512];
+    __shared__ float red[8];
+    __shared__ float accs[4][256];
     sz_pdl_wait();
     sz_pdl_trigger();
-    const int h = blockIdx.x, j = blockIdx.y;
+    const int h = blockIdx.x, j = blockIdx.y, t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const float* p = part + ((size_t)j * nh + h) * splits * (hd + 2);
+    const float g = t < hd ? __ldcg(gate + ((size_t)j * nh + h) * hd + t) : 0.f;
+    float mm[2], zz[2];
     float M = -INFINITY;
-    for (int s = 0; s < splits; s++) M = fmaxf(M, p[(size_t)s * (hd + 2) + hd]);
-    for (int i = threadIdx.x; i < hd; i += 256) {
-        float a = 0.f, z = 0.f;
-        for (int s = 0; s < splits; s++) {
-            const float mm = p[(size_t)s * (hd + 2) + hd];
-            const float c = mm == -INFINITY ? 0.f : __expf(mm - M);
-            a += p[(size_t)s * (hd + 2) + i] * c;
-            z += p[(size_t)s * (hd + 2) + hd + 1] * c;
+#pragma unroll
+    for (int q = 0; q < 2; q++) {
+        const int s = t + 256 * q;
+        mm[q] = s < splits ? __ldcg(p + (size_t)s * (hd + 2) + hd) : -INFINITY;
+        zz[q] = s < splits ? __ldcg(p + (size_t)s * (hd + 2) + hd + 1) : 0.f;
+        M = fmaxf(M, mm[q]);
+    }
+#pragma unroll
+    for (int of = 16; of > 0; of >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, of));
+    if (lane == 0) red[warp] = M;
+    __syncthreads();
+    M = red[0];
+    for (int q = 1; q < 8; q++) M = fmaxf(M, red[q]);
+    __syncthreads();
+    float z = 0.f;
+#pragma unroll
+    for (int q = 0; q < 2; q++) {
+        const int s = t + 256 * q;
+        const float c = mm[q] == -INFINITY ? 0.f : __expf(mm[q] - M);
+        if (s < splits) coef[s] = c;
+        z += zz[q] * c;
+    }
+    z = sz_warp_sum(z);
+    if (lane == 0) red[warp] = z;
+    __syncthreads();
+    z = 0.f;
+    for (int q = 0; q < 8; q++) z += red[q];
+    // group gq of threads takes splits gq, gq + 4, ...; a thread four consecutive dimensions
+    const int per = hd / 4;              // threads a partial row needs (64 at hd = 256)
+    const int ngrp = 256 / per > 4 ? 4 : 256 / per;
+    const int gq = t / per, i4 = (t % per) * 4;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (gq < ngrp) {
+#pragma unroll 4
+        for (int s = gq; s < splits; s += ngrp) {
+            const float c = coef[s];
+            const float2* row = (const float2*)(p + (size_t)s * (hd + 2) + i4);  // rows are 8-byte aligned (hd + 2 is even)
+            const float2 v0 = __ldcg(row), v1 = __ldcg(row + 1);
+            a.x = fmaf(v0.x, c, a.x); a.y = fmaf(v0.y, c, a.y); a.z = fmaf(v1.x, c, a.z); a.w = fmaf(v1.y, c, a.w);
         }
-        o[((size_t)j * nh + h) * hd + i] = (a / z) * sz_sigmoid(gate[((size_t)j * nh + h) * hd + i]);
+        accs[gq][i4] = a.x; accs[gq][i4 + 1] = a.y; accs[gq][i4 + 2] = a.z; accs[gq][i4 + 3] = a.w;
+    }
+    __syncthreads();
+    if (t < hd) {
+        float v = 0.f;
+        for (int q = 0; q < ngrp; q++) v += accs[q][t];
+        o[((size_t)j * nh + h) * hd + t] = (v / z) * sz_sigmoid(g);
     }
 }
 
