@@ -299,17 +299,22 @@ __device__ __forceinline__ u32 sz_q8_pair(u32 p) {
 
 struct SzDenseQ8Cfg {
     int NS, unit_bytes;
+    int rbp;   // bytes between the rows of a staged unit: the row bytes padded so that rows 0..7 start in different banks
+    int xsp;   // halves between the staged rows of the pass, padded likewise
     int units[SZ_DENSE_MAX_JOBS + 1];
 };
 
-// grid: any; block 256; dynamic shared memory: 64 (barriers) + 4096 (reduction) + m * cols * 4 (x as f16 hi | lo) + NS * unit_bytes
+// Shared-memory layout matters more than anything else here: a matrix row is cols / 32 * 34 bytes, a multiple of 128 for the usual
+// widths, so eight lanes reading the same block of eight different rows would hit one bank eight times over.  Every row of a unit
+// is therefore its own bulk copy to a padded stride (rbp), and the rows of the pass are padded the same way (xsp).
+// grid: any; block 256; dynamic shared memory: 64 (barriers) + 4096 (reduction) + 2 * m * xsp * 2 (x as f16 hi | lo) + NS * unit_bytes
 __global__ void __launch_bounds__(256, 2) sz_dense_q8_kernel(const SzDenseArgs a, const SzDenseQ8Cfg c) {
     extern __shared__ __align__(128) u8 smem[];
     u64* bars = (u64*)smem;
     float* red = (float*)(smem + 64);                       // [8 warps][16 rows][8 rows of the pass]
-    __half* xhi = (__half*)(smem + 64 + 4096);              // [m][cols]
-    __half* xlo = xhi + (size_t)a.m * a.cols;
-    u8* stages = smem + 64 + 4096 + (size_t)a.m * a.cols * 4;
+    __half* xhi = (__half*)(smem + 64 + 4096);              // [m][xsp]
+    __half* xlo = xhi + (size_t)a.m * c.xsp;
+    u8* stages = smem + 64 + 4096 + (size_t)a.m * c.xsp * 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, q = lane & 3;
     const size_t rb = (size_t)(a.cols / 32) * 34;
@@ -333,21 +338,24 @@ __global__ void __launch_bounds__(256, 2) sz_dense_q8_kernel(const SzDenseArgs a
         int ji, row0, nrows;
         locate(first + i * step, ji, row0, nrows);
         u64* bar = &bars[i % c.NS];
-        const u32 bytes = (u32)(nrows * rb);
-        sz_mbar_expect_tx(bar, bytes);
-        sz_bulk_g2s(stages + (size_t)(i % c.NS) * c.unit_bytes, a.job[ji].w + (size_t)row0 * rb, bytes, bar);
+        sz_mbar_expect_tx(bar, (u32)(nrows * rb));
+        u8* dst = stages + (size_t)(i % c.NS) * c.unit_bytes;
+        const u8* src = a.job[ji].w + (size_t)row0 * rb;
+        for (int r = 0; r < nrows; r++) sz_bulk_g2s(dst + (size_t)r * c.rbp, src + (size_t)r * rb, (u32)rb, bar);
     };
     if (threadIdx.x == 0)
         for (int i = 0; i < c.NS - 1 && i < count; i++) issue(i);
     sz_pdl_wait();
     sz_pdl_trigger();
-    for (int j = 0; j < a.m; j++)
-        for (int i = threadIdx.x; i < a.cols; i += 256) {
-            const float v = __ldcg(a.x + (size_t)j * a.xstride + i);
-            const __half hi = __float2half_rn(v);
-            xhi[(size_t)j * a.cols + i] = hi;
-            xlo[(size_t)j * a.cols + i] = __float2half_rn(v - __half2float(hi));
-        }
+    for (int i = threadIdx.x; i < a.m * (a.cols / 4); i += 256) {
+        const int j = i / (a.cols / 4), c4 = i - j * (a.cols / 4);
+        const float4 v = __ldcg((const float4*)(a.x + (size_t)j * a.xstride) + c4);
+        const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+        const __half2 l0 = __floats2half2_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2half2_rn(v.z - f1.x, v.w - f1.y);
+        *(uint2*)(xhi + (size_t)j * c.xsp + 4 * c4) = make_uint2(*(const u32*)&h0, *(const u32*)&h1);
+        *(uint2*)(xlo + (size_t)j * c.xsp + 4 * c4) = make_uint2(*(const u32*)&l0, *(const u32*)&l1);
+    }
     __syncthreads();
     const int part = a.cols / 8;          // columns of this warp: [warp * part, (warp + 1) * part), whole 32-column blocks
     const int nblk = part / 32;
@@ -361,15 +369,15 @@ __global__ void __launch_bounds__(256, 2) sz_dense_q8_kernel(const SzDenseArgs a
         const u8* st = stages + (size_t)(i % c.NS) * c.unit_bytes;
         float acc[4] = {0.f, 0.f, 0.f, 0.f};  // rows g, g + 8 x rows of the pass 2 q, 2 q + 1
         if (!failed) {
-            const u8* r0 = st + (size_t)(g < nrows ? g : 0) * rb;
-            const u8* r1 = st + (size_t)(g + 8 < nrows ? g + 8 : 0) * rb;
+            const u8* r0 = st + (size_t)(g < nrows ? g : 0) * c.rbp;
+            const u8* r1 = st + (size_t)(g + 8 < nrows ? g + 8 : 0) * c.rbp;
             for (int b = 0; b < nblk; b++) {
                 const int blk = warp * nblk + b;
                 const int col = blk * 32 + 8 * q;
                 uint4 bh = make_uint4(0, 0, 0, 0), bl = make_uint4(0, 0, 0, 0);
                 if (g < a.m) {
-                    bh = *(const uint4*)(xhi + (size_t)g * a.cols + col);
-                    bl = *(const uint4*)(xlo + (size_t)g * a.cols + col);
+                    bh = *(const uint4*)(xhi + (size_t)g * c.xsp + col);
+                    bl = *(const uint4*)(xlo + (size_t)g * c.xsp + col);
                 }
                 const u8* p0 = r0 + (size_t)blk * 34;
                 const u8* p1 = r1 + (size_t)blk * 34;

@@ -354,8 +354,14 @@ int sz_dense_launch(SzDenseArgs& a, cudaStream_t st, const char* name) {
     if (type == SZ_TYPE_Q8_0 && a.cols % 256 == 0) {
         // tensor-pipe form: 16-row units, the columns split over the 8 warps
         SzDenseQ8Cfg q = {};
-        q.unit_bytes = (int)(16 * rb);
-        const size_t fixed = 64 + 4096 + (size_t)a.m * a.cols * 4;
+        // padded strides: consecutive rows 4 (mod 8) words apart in bank space, rows of the pass 16 words apart
+        int rbp = (int)rb;
+        while (((rbp / 4) % 32) % 8 != 4) rbp += 16;
+        int xsp = a.cols;
+        while (((xsp / 2) % 32) != 16) xsp += 8;
+        q.rbp = rbp; q.xsp = xsp;
+        q.unit_bytes = 16 * rbp;
+        const size_t fixed = 64 + 4096 + (size_t)a.m * xsp * 4;
         size_t budget = 110 * 1024;                        // two blocks a multiprocessor when that leaves at least two stages
         if (fixed + 2 * (size_t)q.unit_bytes > budget) budget = 216 * 1024;
         if (fixed + 2 * (size_t)q.unit_bytes <= budget) {
