@@ -78,6 +78,13 @@ __device__ __forceinline__ uint4 sz_ldg16_here(const void* p) {
     return v;
 }
 
+// The same for a 4-byte load of data that other kernels write (an ordinary global load, kept where it is written).
+__device__ __forceinline__ float sz_ld32_here(const float* p) {
+    float v;
+    asm volatile("ld.global.f32 %0, [%1];" : "=f"(v) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ float sz_f16_to_f32(u16 h) { return __half2float(__ushort_as_half(h)); }
 __device__ __forceinline__ float sz_bf16_to_f32(u16 b) { return __uint_as_float((u32)b << 16); }
 

@@ -10,28 +10,20 @@
 // ---------------------------------------------------------------------------------------------------------------------------------
 // router: logits (a warp a router row, f64 accumulate), then the last block to finish does softmax, top-k and the plan
 
-#define SZ_ROUTE_WARPS 8
+#define SZ_ROUTE_RB 4        // router rows a block
+#define SZ_ROUTE_THREADS 256
 
-__device__ __forceinline__ bool sz_better(float ad, int ai, float bd, int bi) { return ad > bd || (ad == bd && ai < bi); }
-
-// The row's best untaken logit among the NQ values a lane holds (experts lane + 32 q): four independent scans, then merged, so the
-// dependency chain is NQ / 4 long.
-template <int NQ>
-__device__ __forceinline__ void sz_lane_best(const float* d, u32 taken, int lane, int ne, float& bd, int& bi) {
-    float cd[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-    int ci[4] = {0x7fffffff, 0x7fffffff, 0x7fffffff, 0x7fffffff};
-#pragma unroll
-    for (int q = 0; q < NQ; q++) {
-        const int i = lane + 32 * q;
-        if (i < ne && !((taken >> q) & 1u) && sz_better(d[q], i, cd[q & 3], ci[q & 3])) { cd[q & 3] = d[q]; ci[q & 3] = i; }
-    }
-    if (sz_better(cd[1], ci[1], cd[0], ci[0])) { cd[0] = cd[1]; ci[0] = ci[1]; }
-    if (sz_better(cd[3], ci[3], cd[2], ci[2])) { cd[2] = cd[3]; ci[2] = ci[3]; }
-    if (sz_better(cd[2], ci[2], cd[0], ci[0])) { cd[0] = cd[2]; ci[0] = ci[2]; }
-    bd = cd[0]; bi = ci[0];
+// orderable 32-bit image of a float: a > b  <=>  key(a) > key(b) for every pair of non-NaN values (-0 sorts below +0, which cannot
+// matter here: the values are logit - max, and a tie in value is decided by the index)
+__device__ __forceinline__ u32 sz_fkey(float v) {
+    const u32 u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
+__device__ __forceinline__ float sz_fkey_inv(u32 k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
 
-// One row of the pass: max, top-k, weights.  A warp; the row's logits in registers.
+// One row of the pass: max, top-k by (value descending, index ascending), weights.  A warp; the row's logits in registers, lane l
+// holds experts l + 32 q.  Each round takes the warp-wide best with two redux instructions (best key, then lowest index among
+// the lanes that hold it); only the winner's lane rescans its values.
 template <int NQ>
 __device__ __forceinline__ void sz_route_row(const float* __restrict__ logits_row, int ne, int k, int lane, int* sel_row, int32_t* ridx_row,
                                              double* rw_row, int32_t* out_idx_row, double* out_w_row) {
@@ -45,28 +37,40 @@ __device__ __forceinline__ void sz_route_row(const float* __restrict__ logits_ro
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    u32 key[NQ];
 #pragma unroll
-    for (int q = 0; q < NQ; q++) d[q] = d[q] - mx;  // in f32, as the reference subtracts before widening
-    // top-k by (value descending, index ascending); exp is monotone, so the order of d is the order of exp(d)
-    u32 taken = 0;
-    float mine = 0.f;  // lane t keeps the value of rank t
+    for (int q = 0; q < NQ; q++) key[q] = lane + 32 * q < ne ? sz_fkey(d[q] - mx) : 0u;  // in f32, as the reference subtracts before widening; 0 = absent
+    auto local_best = [&](u32& bk, int& bq) {  // best remaining key of the lane and its slot (lowest slot on ties)
+        u32 ck[4] = {0u, 0u, 0u, 0u};
+        int cq[4] = {NQ, NQ, NQ, NQ};
+#pragma unroll
+        for (int q = 0; q < NQ; q++)
+            if (key[q] > ck[q & 3]) { ck[q & 3] = key[q]; cq[q & 3] = q; }
+#pragma unroll
+        for (int c = 1; c < 4; c++)
+            if (ck[c] > ck[0] || (ck[c] == ck[0] && cq[c] < cq[0])) { ck[0] = ck[c]; cq[0] = cq[c]; }
+        bk = ck[0]; bq = cq[0];
+    };
+    u32 bk;
+    int bq;
+    local_best(bk, bq);
+    u32 mine = 0;
     int my_e = 0;
     for (int t = 0; t < k; t++) {
-        float bd;
-        int bi;
-        sz_lane_best<NQ>(d, taken, lane, ne, bd, bi);
+        const u32 wk = __reduce_max_sync(0xffffffffu, bk);
+        const u32 cand = (bk == wk && bq < NQ) ? (u32)(lane + 32 * bq) : 0x7fffffffu;
+        const u32 wi = __reduce_min_sync(0xffffffffu, cand);
+        if (lane == t) { mine = wk; my_e = (int)wi; }
+        if ((int)(wi & 31u) == lane) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float od = __shfl_xor_sync(0xffffffffu, bd, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (sz_better(od, oi, bd, bi)) { bd = od; bi = oi; }
+            for (int q = 0; q < NQ; q++)
+                if (q == (int)(wi >> 5)) key[q] = 0u;
+            local_best(bk, bq);
         }
-        if ((bi & 31) == lane) taken |= 1u << (bi >> 5);
-        if (lane == t) { mine = bd; my_e = bi; }
     }
     // weights: softmax over all experts, then the chosen ones renormalised - the full sum cancels, so only the k chosen
     // exponentials are needed: w_t = exp(d_t) / sum over ranks (in rank order) of exp(d_t')
-    const double ex = lane < k ? exp((double)mine) : 0.0;
+    const double ex = lane < k ? exp((double)sz_fkey_inv(mine)) : 0.0;
     double tz = 0.0;
     for (int t = 0; t < k; t++) tz += __shfl_sync(0xffffffffu, ex, t);
     if (lane < k) {
@@ -80,147 +84,177 @@ __device__ __forceinline__ void sz_route_row(const float* __restrict__ logits_ro
     __syncwarp();
 }
 
-// grid: ceil(rows / 8) blocks of 8 warps; dynamic shared memory m * H * 4 (the rows of the pass, staged once per block).
-__global__ void __launch_bounds__(SZ_ROUTE_WARPS * 32)
-sz_route_kernel(const float* __restrict__ x, int m, int H, const float* __restrict__ router, const float* __restrict__ shared_router,
+// Sums N = 2^h values a lane over the 32 lanes of a warp.  While more than one value is left, a step at offset o halves them: the
+// lanes with bit o set keep the upper half and send the lower, the others the reverse, so N + N/2 + .. shuffles do the work of
+// 5 N.  Afterwards every lane holds the total of value number lane >> (5 - h) in v[0].
+template <int N>
+__device__ __forceinline__ void sz_warp_sum_many(double* v, int lane) {
+    int n = N;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        if (n > 1) {
+            const int half = n >> 1;
+            const bool up = (lane & o) != 0;
+#pragma unroll
+            for (int i = 0; i < N / 2; i++) {
+                if (i < half) {
+                    const double send = up ? v[i] : v[i + half];
+                    const double keep = up ? v[i + half] : v[i];
+                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                }
+            }
+            n = half;
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+        }
+    }
+}
+
+// grid: ceil(rows / 4) blocks of 256 threads.  A block takes 4 router rows (row ne: the shared expert's gate); its threads split the
+// hidden dimension: thread t holds the float4 pieces t, t + 256, .. of every one of the 4 rows (fetched before the dependency
+// wait) and of the M rows of the pass, so nothing is staged in shared memory and every product is formed and added in f64 with one
+// conversion a weight.  The 4 x M partial sums a thread ends with are summed over the warp (sz_warp_sum_many), then over the 8 warps
+// in warp order.  M: rows of the pass; MP: M rounded up to a power of two; NCH: float4 pieces a thread holds per row.
+template <int M, int MP, int NCH>
+__global__ void __launch_bounds__(SZ_ROUTE_THREADS)
+sz_route_kernel(const float* __restrict__ x, int H, const float* __restrict__ router, const float* __restrict__ shared_router,
                 int ne, int k, float* __restrict__ logits, int32_t* __restrict__ ridx, double* __restrict__ rw, SzPlan* __restrict__ plan,
                 SzPlan* __restrict__ plan_sh, u32* __restrict__ ctrl, int32_t* __restrict__ out_idx, double* __restrict__ out_w,
                 uint4* __restrict__ zero, int zero_n, int ep_first, int ep_count) {
-    extern __shared__ __align__(16) float xs[];  // [m][H]
-    __shared__ int cnt[SZ_MAX_EXPERTS];
-    __shared__ int slot_of[SZ_MAX_EXPERTS];
+    constexpr int RB = SZ_ROUTE_RB, N = RB * MP;
+    __shared__ double part[SZ_ROUTE_THREADS / 32][N];
+    __shared__ u32 rowmask[SZ_MAX_EXPERTS];     // which rows of the pass chose expert e
+    __shared__ u32 bitmap[SZ_MAX_EXPERTS / 32]; // experts chosen at all (and held here)
     __shared__ int sel[SZ_MAX_VERIFY * SZ_MAX_TOPK];
     __shared__ int s_last;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int ld = ne + 1;
+    const int nrows = ne + (shared_router != nullptr ? 1 : 0);
+    const int row0 = blockIdx.x * RB;
     SZ_PH_DECL;
     SZ_PH();  // 0 start
-    // this block's router rows do not depend on the previous kernel: fetch them before waiting for it (16 float4 loads in flight a lane)
-    const int r = blockIdx.x * SZ_ROUTE_WARPS + warp;
-    const bool live = r < ne || (r == ne && shared_router != nullptr);
-    const float4* wrow = (const float4*)(r < ne ? router + (size_t)r * H : shared_router);
-    constexpr int WN = 16;  // float4 chunks of the row a lane keeps in flight: covers hidden <= 2048 in one sweep
-    float4 w[WN];
+    // the router rows do not depend on the previous kernel: fetched before waiting for it
+    float4 w[RB][NCH];
 #pragma unroll
-    for (int u = 0; u < WN; u++) {
-        w[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (live && 32 * u + lane < H / 4) {
-            const uint4 q = sz_ldg16_here(wrow + 32 * u + lane);
-            w[u] = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
+    for (int r = 0; r < RB; r++) {
+        const int row = row0 + r;
+        const float4* wrow = (const float4*)(row < ne ? router + (size_t)row * H : shared_router);
+#pragma unroll
+        for (int u = 0; u < NCH; u++) {
+            w[r][u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row < nrows && t + 256 * u < H / 4) {
+                const uint4 q = sz_ldg16_here(wrow + t + 256 * u);
+                w[r][u] = make_float4(__uint_as_float(q.x), __uint_as_float(q.y), __uint_as_float(q.z), __uint_as_float(q.w));
+            }
         }
     }
+    for (int i = t; i < SZ_MAX_EXPERTS; i += SZ_ROUTE_THREADS) rowmask[i] = 0u;
+    if (t < SZ_MAX_EXPERTS / 32) bitmap[t] = 0u;
     sz_pdl_wait();
     sz_pdl_trigger();
     SZ_PH();  // 1 after wait
+    float4 xv[M][NCH];
+#pragma unroll
+    for (int j = 0; j < M; j++)
+#pragma unroll
+        for (int u = 0; u < NCH; u++)
+            xv[j][u] = t + 256 * u < H / 4 ? __ldcg((const float4*)(x + (size_t)j * H) + t + 256 * u) : make_float4(0.f, 0.f, 0.f, 0.f);
     // the streaming kernels' fixed-point accumulators start every call at zero
-    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < zero_n; i += gridDim.x * blockDim.x) zero[i] = make_uint4(0, 0, 0, 0);
-    for (int i = threadIdx.x; i < m * H / 4; i += blockDim.x) ((float4*)xs)[i] = __ldcg((const float4*)x + i);
-    __syncthreads();
-    SZ_PH();  // 2 x staged
+    for (int i = blockIdx.x * blockDim.x + t; i < zero_n; i += gridDim.x * blockDim.x) zero[i] = make_uint4(0, 0, 0, 0);
 
-    // ---- logits: row r of the router (row ne: the shared expert's gate) against every x row, f64 accumulate
-    if (live) {
-        double acc[SZ_MAX_VERIFY];
+    // ---- logits: f64 products, f64 sums
+    double acc[N];
 #pragma unroll
-        for (int j = 0; j < SZ_MAX_VERIFY; j++) acc[j] = 0.0;
-        for (int c0 = 0; c0 < H / 4; c0 += 32 * WN) {
-            if (c0 > 0) {
+    for (int i = 0; i < N; i++) acc[i] = 0.0;
 #pragma unroll
-                for (int u = 0; u < WN; u++) w[u] = c0 + 32 * u + lane < H / 4 ? __ldg(wrow + c0 + 32 * u + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
+    for (int u = 0; u < NCH; u++) {
+        double xd[M][4];
 #pragma unroll
-            for (int u = 0; u < WN; u++) {
-                const int c = c0 + 32 * u + lane;
-                if (c < H / 4) {
+        for (int j = 0; j < M; j++) { xd[j][0] = (double)xv[j][u].x; xd[j][1] = (double)xv[j][u].y; xd[j][2] = (double)xv[j][u].z; xd[j][3] = (double)xv[j][u].w; }
 #pragma unroll
-                    for (int j = 0; j < SZ_MAX_VERIFY; j++) {
-                        if (j < m) {
-                            const float4 v = ((const float4*)xs)[(size_t)j * (H / 4) + c];
-                            acc[j] += (double)w[u].x * (double)v.x;
-                            acc[j] += (double)w[u].y * (double)v.y;
-                            acc[j] += (double)w[u].z * (double)v.z;
-                            acc[j] += (double)w[u].w * (double)v.w;
-                        }
-                    }
-                }
+        for (int r = 0; r < RB; r++) {
+            const double w0 = (double)w[r][u].x, w1 = (double)w[r][u].y, w2 = (double)w[r][u].z, w3 = (double)w[r][u].w;
+#pragma unroll
+            for (int j = 0; j < M; j++) {
+                double a = acc[r * MP + j];
+                a = fma(w0, xd[j][0], a);
+                a = fma(w1, xd[j][1], a);
+                a = fma(w2, xd[j][2], a);
+                a = fma(w3, xd[j][3], a);
+                acc[r * MP + j] = a;
             }
         }
+    }
+    SZ_PH();  // 2 products
+    constexpr int HB = N == 1 ? 0 : (N == 2 ? 1 : (N == 4 ? 2 : (N == 8 ? 3 : (N == 16 ? 4 : 5))));  // log2(N), N <= 32
+    sz_warp_sum_many<N>(acc, lane);
+    if ((lane & ((32 >> HB) - 1)) == 0) part[warp][lane >> (5 - HB)] = acc[0];
+    __syncthreads();
+    if (t < N) {
+        double s = 0.0;
 #pragma unroll
-        for (int j = 0; j < SZ_MAX_VERIFY; j++) {
-            if (j < m) {
-                const double s = sz_warp_sum(acc[j]);
-                if (lane == 0) logits[(size_t)j * ld + r] = (float)s;
-            }
-        }
+        for (int q = 0; q < SZ_ROUTE_THREADS / 32; q++) s += part[q][t];
+        const int r = t / MP, j = t % MP;
+        if (j < M && row0 + r < nrows) logits[(size_t)j * ld + row0 + r] = (float)s;
     }
 
     // ---- the last block to arrive routes every row
     SZ_PH();  // 3 logits done
     __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(&ctrl[0], 1u) == gridDim.x - 1);
+    if (t == 0) s_last = (atomicAdd(&ctrl[0], 1u) == gridDim.x - 1);
     __syncthreads();
     if (!s_last) return;
     __threadfence();
     SZ_PH();  // 4 ticket taken
 
-    for (int j = warp; j < m; j += SZ_ROUTE_WARPS) {
+    for (int j = warp; j < M; j += SZ_ROUTE_THREADS / 32) {
         int32_t* oi = out_idx ? out_idx + j * k : nullptr;
         double* ow = out_w ? out_w + j * k : nullptr;
         if (ne <= 256) sz_route_row<8>(logits + (size_t)j * ld, ne, k, lane, sel + j * SZ_MAX_TOPK, ridx + j * k, rw + j * k, oi, ow);
         else if (ne <= 512) sz_route_row<16>(logits + (size_t)j * ld, ne, k, lane, sel + j * SZ_MAX_TOPK, ridx + j * k, rw + j * k, oi, ow);
         else sz_route_row<32>(logits + (size_t)j * ld, ne, k, lane, sel + j * SZ_MAX_TOPK, ridx + j * k, rw + j * k, oi, ow);
     }
-    for (int i = threadIdx.x; i < ne; i += blockDim.x) cnt[i] = 0;
     __syncthreads();
     SZ_PH();  // 5 rows routed
 
-    // ---- plan: groups in ascending expert order, rows ascending inside a group
-    // with expert parallelism only the experts this rank holds enter the plan; routing itself is the same on every rank
-    const int pairs = m * k;
+    // ---- plan: groups in ascending expert order, rows ascending inside a group.  Each (row, rank) pair marks its expert in a bitmap
+    // and its row in the expert's row mask; a group's index is then the number of marked experts below it and a pair's place in the
+    // group the number of lower rows in the mask.  With expert parallelism only the experts this rank holds enter the plan; routing
+    // itself is the same on every rank.
+    const int pairs = M * k;
     const int e_lo = ep_count > 0 ? ep_first : 0, e_hi = ep_count > 0 ? ep_first + ep_count : ne;
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int e = sel[(p / k) * SZ_MAX_TOPK + p % k];
-        if (e >= e_lo && e < e_hi) atomicAdd(&cnt[e], 1);
+    int e = -1, j = 0;
+    if (t < pairs) {
+        j = t / k;
+        e = sel[j * SZ_MAX_TOPK + t % k];
+        if (e < e_lo || e >= e_hi) e = -1;
+        if (e >= 0) { atomicOr(&rowmask[e], 1u << j); atomicOr(&bitmap[e >> 5], 1u << (e & 31)); }
     }
     __syncthreads();
-    if (warp == 0) {
-        int running = 0;
-        for (int base = 0; base < ne; base += 32) {
-            const int e = base + lane;
-            const int c = e < ne ? cnt[e] : 0;
-            const u32 mask = __ballot_sync(0xffffffffu, c > 0);
-            if (c > 0) {
-                const int slot = running + __popc(mask & ((1u << lane) - 1u));
-                slot_of[e] = slot;
-                plan->expert[slot] = e;
-                plan->count[slot] = c;
-            }
-            running += __popc(mask);
-        }
-        if (lane == 0) plan->n_groups = running;
-    }
-    __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int j = p / k;
-        const int e = sel[j * SZ_MAX_TOPK + p % k];
-        if (e < e_lo || e >= e_hi) continue;
-        int pos = 0;
-        for (int jj = 0; jj < j; jj++)
-            for (int t = 0; t < k; t++) pos += (sel[jj * SZ_MAX_TOPK + t] == e);
-        const int g = slot_of[e];
+    if (e >= 0) {
+        int g = __popc(bitmap[e >> 5] & ((1u << (e & 31)) - 1u));
+        for (int q = 0; q < (e >> 5); q++) g += __popc(bitmap[q]);
+        const u32 rm = rowmask[e];
+        const int pos = __popc(rm & ((1u << j) - 1u));
         plan->rows[g][pos] = j;
-        plan->pairs[g][pos] = p;
+        plan->pairs[g][pos] = t;
+        if (pos == 0) { plan->expert[g] = e; plan->count[g] = __popc(rm); }
+    }
+    if (t == 0) {
+        int n = 0;
+        for (int q = 0; q < SZ_MAX_EXPERTS / 32; q++) n += __popc(bitmap[q]);
+        plan->n_groups = n;
     }
     // the shared expert: one group holding every row; its per-pair buffers are indexed by row
-    if (threadIdx.x < SZ_MAX_VERIFY) {
-        plan_sh->rows[0][threadIdx.x] = threadIdx.x;
-        plan_sh->pairs[0][threadIdx.x] = threadIdx.x;
+    if (t < SZ_MAX_VERIFY) {
+        plan_sh->rows[0][t] = t;
+        plan_sh->pairs[0][t] = t;
     }
-    if (threadIdx.x == 0) {
+    if (t == 0) {
         plan_sh->n_groups = 1;
         plan_sh->expert[0] = 0;
-        plan_sh->count[0] = m;
+        plan_sh->count[0] = M;
         ctrl[0] = 0;  // ready for the next call
     }
     SZ_PH();  // 6 plan written
@@ -555,7 +589,7 @@ static int sz_check_align(const char* what, int type, u64 base, int n_in, int n_
 static int sz_moe_check(const sz_moe_layer* L, int m) {
     if (!L) return sz_fail(SZ_E_ARG, "null layer");
     if (m < 1 || m > SZ_MAX_VERIFY) return sz_fail(SZ_E_ARG, "a verify pass has 1..%d rows, got %d", SZ_MAX_VERIFY, m);
-    if (L->hidden <= 0 || L->hidden % 128) return sz_fail(SZ_E_ARG, "hidden = %d is not a positive multiple of 128", L->hidden);
+    if (L->hidden <= 0 || L->hidden % 128 || L->hidden > 4096) return sz_fail(SZ_E_ARG, "hidden = %d is not a multiple of 128 in 128..4096", L->hidden);
     if (L->n_expert < 1 || L->n_expert > SZ_MAX_EXPERTS) return sz_fail(SZ_E_ARG, "n_expert = %d (1..%d)", L->n_expert, SZ_MAX_EXPERTS);
     if (L->top_k < 1 || L->top_k > SZ_MAX_TOPK || L->top_k > L->n_expert)
         return sz_fail(SZ_E_ARG, "top_k = %d (1..%d, at most n_expert)", L->top_k, SZ_MAX_TOPK);
@@ -729,13 +763,25 @@ static int sz_moe_run(const sz_moe_layer* L0, uint64_t x, int m, float* y, long 
     const int route_rows = L->n_expert + (shared ? 1 : 0);
     const SzFast fast = sz_fast_path(L);
     {
-        static bool set = false;
-        if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); set = true; }
+        const dim3 grid((route_rows + SZ_ROUTE_RB - 1) / SZ_ROUTE_RB), block(SZ_ROUTE_THREADS);
+        const int nch = (H / 4 + SZ_ROUTE_THREADS - 1) / SZ_ROUTE_THREADS;
+        cudaError_t e = cudaErrorInvalidValue;
+#define SZ_ROUTE_GO(MM, MPP, NC)                                                                                                         \
+    e = sz_launch("route", sz_route_kernel<MM, MPP, NC>, grid, block, 0, st, true, xp, H, (const float*)L->router,                       \
+                  (const float*)(shared ? L->shared_router : 0), (int)L->n_expert, (int)L->top_k, logits, ridx, rw, plan, plan_sh, ctrl, \
+                  (int32_t*)route_idx, (double*)route_w, (uint4*)(base + S.acc_gu), fast.exl3 ? (int)(S.acc_bytes / 16) : 0,             \
+                  (int)L->ep_first, (int)L->ep_count)
+#define SZ_ROUTE_M(MM, MPP)                                                                    \
+    case MM:                                                                                   \
+        if (nch <= 1) SZ_ROUTE_GO(MM, MPP, 1); else if (nch == 2) SZ_ROUTE_GO(MM, MPP, 2); else SZ_ROUTE_GO(MM, MPP, 4); \
+        break;
+        switch (m) {
+            SZ_ROUTE_M(1, 1) SZ_ROUTE_M(2, 2) SZ_ROUTE_M(3, 4) SZ_ROUTE_M(4, 4) SZ_ROUTE_M(5, 8) SZ_ROUTE_M(6, 8) SZ_ROUTE_M(7, 8) SZ_ROUTE_M(8, 8)
+        }
+#undef SZ_ROUTE_M
+#undef SZ_ROUTE_GO
+        SZ_CUDA(e);
     }
-    SZ_CUDA(sz_launch("route", sz_route_kernel, dim3((route_rows + SZ_ROUTE_WARPS - 1) / SZ_ROUTE_WARPS), dim3(SZ_ROUTE_WARPS * 32), (size_t)m * H * 4, st, false, xp, m, H,
-                      (const float*)L->router, (const float*)(shared ? L->shared_router : 0), (int)L->n_expert, (int)L->top_k, logits, ridx,
-                      rw, plan, plan_sh, ctrl, (int32_t*)route_idx, (double*)route_w, (uint4*)(base + S.acc_gu),
-                      fast.exl3 ? (int)(S.acc_bytes / 16) : 0, (int)L->ep_first, (int)L->ep_count));
     const int groups = m * L->top_k;
     if (fast.exl3) {
         // streaming EXL3 kernels for the routed experts (and the shared expert when it has the same type and width)

@@ -410,69 +410,107 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
                      float* __restrict__ O0, float* __restrict__ O1, const int32_t* __restrict__ state, const int32_t* __restrict__ res, int kh,
                      int vh, int m, float eps, float* __restrict__ og) {
     constexpr int NI = D / PARTS;
+    constexpr int RUN = NI < 16 ? NI : 16;  // sums run in f32 over 16 terms and the runs are added in f64, as the reference's exact
+                                            // GPU scan does (kernels/forward.cu:991-1013): a conversion to f64 per term would
+                                            // keep the conversion unit busy for longer than the state takes to arrive
     __shared__ float sk[D], sq[D];
     __shared__ double part[PARTS][D];
-    __shared__ double red[8];
-    sz_pdl_wait();
-    sz_pdl_trigger();
+    __shared__ float ofs[SZ_MAX_VERIFY][D];
+    __shared__ double rrs[SZ_MAX_VERIFY];
     const int hd = blockIdx.x, di = blockIdx.y;
     const int col = threadIdx.x % D, pt = threadIdx.x / D;
     const int kx = hd % kh;  // value heads are tiled over the key heads (forward.rs:862-864)
     const int kd = kh * D, ch = 2 * kd + vh * D;
+    const size_t Sl = (size_t)vh * D * D;
+    float S[NI];
+    // the state belongs to the previous pass (and the buffer index with it): in the pass itself it is fetched ahead of the wait
+    if (og) {
+        const int cur0 = state[1];
+        const float* Sg = (cur0 ? S1 : S0) + di * Sl + (size_t)hd * D * D;
+#pragma unroll
+        for (int i = 0; i < NI; i++) S[i] = sz_ld32_here(Sg + (size_t)(pt * NI + i) * D + col);
+    }
+    sz_pdl_wait();
+    sz_pdl_trigger();
     int rows = m;
     if (!og) {
         rows = res[0];
         if (rows <= 0 || rows >= m) return;
     }
     const int cur = state[1];
-    const size_t Sl = (size_t)vh * D * D;
     const float* S_in = (cur ? S1 : S0) + di * Sl;
     float* S_out = (cur ? O0 : O1) + di * Sl;
     const float* xc = xc_all + (size_t)di * SZ_MAX_VERIFY * ch;
     const float* beta = beta_all + (size_t)di * SZ_MAX_VERIFY * vh;
     const float* decay = decay_all + (size_t)di * SZ_MAX_VERIFY * vh;
-    float S[NI];
-    const float* Sg = S_in + (size_t)hd * D * D;
+    if (!og) {
+        const float* Sg = S_in + (size_t)hd * D * D;
 #pragma unroll
-    for (int i = 0; i < NI; i++) S[i] = Sg[(size_t)(pt * NI + i) * D + col];
+        for (int i = 0; i < NI; i++) S[i] = Sg[(size_t)(pt * NI + i) * D + col];
+    }
     for (int j = 0; j < rows; j++) {
         const float* x = xc + (size_t)j * ch;
         __syncthreads();
         if (threadIdx.x < D) { sq[threadIdx.x] = x[kx * D + threadIdx.x]; sk[threadIdx.x] = x[kd + kx * D + threadIdx.x]; }
-        __syncthreads();
+        const float vj = x[2 * kd + hd * D + col];
         const float dc = decay[j * vh + hd], bt = beta[j * vh + hd];
+        __syncthreads();
         double mem = 0.0;
 #pragma unroll
-        for (int i = 0; i < NI; i++) {
-            S[i] = S[i] * dc;
-            mem += (double)S[i] * (double)sk[pt * NI + i];
+        for (int i0 = 0; i0 < NI; i0 += RUN) {
+            float run = 0.f;
+#pragma unroll
+            for (int i = i0; i < i0 + RUN; i++) {
+                S[i] = S[i] * dc;
+                run = fmaf(S[i], sk[pt * NI + i], run);
+            }
+            mem += (double)run;
         }
         part[pt][col] = mem;
         __syncthreads();
         double tot = 0.0;
 #pragma unroll
         for (int p = 0; p < PARTS; p++) tot += part[p][col];
-        const float dl = (float)(((double)x[2 * kd + hd * D + col] - tot) * (double)bt);
+        const float dl = (float)(((double)vj - tot) * (double)bt);
         double o = 0.0;
 #pragma unroll
-        for (int i = 0; i < NI; i++) {
-            S[i] = __fadd_rn(S[i], __fmul_rn(sk[pt * NI + i], dl));  // unfused, as the reference
-            o += (double)S[i] * (double)sq[pt * NI + i];
+        for (int i0 = 0; i0 < NI; i0 += RUN) {
+            float run = 0.f;
+#pragma unroll
+            for (int i = i0; i < i0 + RUN; i++) {
+                S[i] = __fadd_rn(S[i], __fmul_rn(sk[pt * NI + i], dl));  // unfused, as the CPU reference
+                run = fmaf(S[i], sq[pt * NI + i], run);
+            }
+            o += (double)run;
         }
         if (og) {
             __syncthreads();
             part[pt][col] = o;
             __syncthreads();
-            double ot = 0.0;
-#pragma unroll
-            for (int p = 0; p < PARTS; p++) ot += part[p][col];
-            const float of = (float)ot;
-            const double ss = sz_block_sum(pt == 0 ? (double)of * (double)of : 0.0, red);
             if (pt == 0) {
-                const double rr = 1.0 / sqrt(ss / (double)D + (double)eps);
-                const float normed = (float)((double)of * rr) * norm_w[col];
-                og[(size_t)j * vh * D + hd * D + col] = normed * sz_sigmoid(z[(size_t)j * vh * D + hd * D + col]);
+                double ot = 0.0;
+#pragma unroll
+                for (int p = 0; p < PARTS; p++) ot += part[p][col];
+                ofs[j][col] = (float)ot;
             }
+        }
+    }
+    if (og) {
+        // gated RMS norm of every row's output at once: warp w sums the squares of row w, one thread a row takes the root, then
+        // every thread scales its share
+        __syncthreads();
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int j = warp; j < rows; j += (D * PARTS) / 32) {
+            double ss = 0.0;
+            for (int i = lane; i < D; i += 32) ss += (double)ofs[j][i] * (double)ofs[j][i];
+            ss = sz_warp_sum(ss);
+            if (lane == 0) rrs[j] = 1.0 / sqrt(ss / (double)D + (double)eps);
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < rows * D; idx += D * PARTS) {
+            const int j = idx / D, c = idx - j * D;
+            const float normed = (float)((double)ofs[j][c] * rrs[j]) * norm_w[c];
+            og[(size_t)j * vh * D + hd * D + c] = normed * sz_sigmoid(z[(size_t)j * vh * D + hd * D + c]);
         }
     }
     float* So = S_out + (size_t)hd * D * D;
