@@ -29,6 +29,10 @@ __device__ __forceinline__ void sz_route_row(const float* __restrict__ logits_ro
                                              double* rw_row, int32_t* out_idx_row, double* out_w_row) {
     float d[NQ];
     float mx = -FLT_MAX;  // f32::MIN, forward.rs:1093
+#ifdef SZ_PHASES
+    const bool dbg = lane == 0 && (threadIdx.x >> 5) == 0;
+    if (dbg) sz_phase_t[3][0] = clock64();
+#endif
 #pragma unroll
     for (int q = 0; q < NQ; q++) {
         const int i = lane + 32 * q;
@@ -54,6 +58,9 @@ __device__ __forceinline__ void sz_route_row(const float* __restrict__ logits_ro
     u32 bk;
     int bq;
     local_best(bk, bq);
+#ifdef SZ_PHASES
+    if (dbg) sz_phase_t[3][1] = clock64();
+#endif
     u32 mine = 0;
     int my_e = 0;
     for (int t = 0; t < k; t++) {
@@ -70,7 +77,13 @@ __device__ __forceinline__ void sz_route_row(const float* __restrict__ logits_ro
     }
     // weights: softmax over all experts, then the chosen ones renormalised - the full sum cancels, so only the k chosen
     // exponentials are needed: w_t = exp(d_t) / sum over ranks (in rank order) of exp(d_t')
+#ifdef SZ_PHASES
+    if (dbg) sz_phase_t[3][2] = clock64();
+#endif
     const double ex = lane < k ? exp((double)sz_fkey_inv(mine)) : 0.0;
+#ifdef SZ_PHASES
+    if (dbg) sz_phase_t[3][3] = clock64() + (long long)(ex == 12345.0);
+#endif
     double tz = 0.0;
     for (int t = 0; t < k; t++) tz += __shfl_sync(0xffffffffu, ex, t);
     if (lane < k) {
@@ -82,6 +95,9 @@ __device__ __forceinline__ void sz_route_row(const float* __restrict__ logits_ro
         if (out_w_row) out_w_row[lane] = wv;
     }
     __syncwarp();
+#ifdef SZ_PHASES
+    if (dbg) sz_phase_t[3][4] = clock64();
+#endif
 }
 
 // Sums N = 2^h values a lane over the 32 lanes of a warp.  While more than one value is left, a step at offset o halves them: the

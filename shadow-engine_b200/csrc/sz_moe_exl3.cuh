@@ -127,6 +127,8 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     uint4* frags = (uint4*)(smem + SZ_X3_STAGES * X::STAGE_BYTES);
     u64* bars = (u64*)(smem + SZ_X3_STAGES * X::STAGE_BYTES + X::FRAG_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    SZ_PH_DECL;
+    SZ_PH();  // 0
     if (threadIdx.x == 0) {
         for (int i = 0; i < SZ_X3_STAGES; i++) sz_mbar_init(&bars[i], 1);
         sz_mbar_fence_init();
@@ -134,6 +136,7 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     sz_pdl_wait();
     sz_pdl_trigger();
     __syncthreads();
+    SZ_PH();  // 1 after wait
     const int D = plan ? plan->n_groups : 0;
     const int NG = D + (sh_gate ? 1 : 0);
     const int NS = H / 128;
@@ -186,6 +189,7 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
         sz_x3_store_frag(frags, warp, cur.n, v, lane);
     }
     __syncthreads();
+    SZ_PH();  // 2 first fragments
     int failed = 0;
     for (int i = 0; i < count; i++) {
         if (threadIdx.x == 0 && i + SZ_X3_STAGES - 1 < count) issue(i + SZ_X3_STAGES - 1);
@@ -214,8 +218,10 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
         if (i + 1 < count) sz_x3_store_frag(frags + ((i + 1) & 1) * 256, warp, nxt.n, v, lane);
         cur = nxt;
         if (__syncthreads_or(failed)) { failed = 1; break; }
+        SZ_PH();  // 3.. a unit
     }
     if (failed && threadIdx.x == 0) atomicExch(&ctrl[1], 1u);
+    SZ_PH_FLUSH(4, blockIdx.x == 7);
 }
 
 // ---- down ---------------------------------------------------------------------------------------------------------------------------
