@@ -322,7 +322,7 @@ __device__ __forceinline__ int64_t sz_row_bytes(int cols) { return TYPE == SZ_TY
 // gate and up rows of one group, SwiGLU fused: act[pair][r] = silu(gate_r . x) * (up_r . x)
 template <int TYPE, int N>
 __device__ __forceinline__ void sz_gateup_body(const u8* gate, const u8* up, int H, int FF, const float* xs, const u32* grid,
-                                               const int32_t* pairs, float* act, int r0, int r1) {
+                                               const u8* pairs, float* act, int r0, int r1) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t rb = sz_row_bytes<TYPE>(H);
     for (int r = r0 + warp; r < r1; r += 8) {
@@ -340,7 +340,7 @@ __device__ __forceinline__ void sz_gateup_body(const u8* gate, const u8* up, int
 }
 
 template <int TYPE, int N>
-__device__ __forceinline__ void sz_down_body(const u8* down, int FF, int H, const float* xs, const u32* grid, const int32_t* pairs,
+__device__ __forceinline__ void sz_down_body(const u8* down, int FF, int H, const float* xs, const u32* grid, const u8* pairs,
                                              float* eo, int r0, int r1) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int64_t rb = sz_row_bytes<TYPE>(FF);
@@ -373,7 +373,7 @@ sz_rows_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 s
     if (g >= plan->n_groups) return;
     const int n = plan->count[g];
     const int64_t e = plan->expert[g];
-    const int32_t* src_rows = DOWN ? plan->pairs[g] : plan->rows[g];
+    const u8* src_rows = DOWN ? plan->pairs[g] : plan->rows[g];
     for (int i = threadIdx.x; i < 512; i += 256) grid[i] = c_iq3s_grid[i];
     for (int j = 0; j < n; j++) {
         const float4* src = (const float4*)(in + (size_t)src_rows[j] * n_in);
@@ -384,7 +384,7 @@ sz_rows_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 s
     const int r0 = blockIdx.x * SZ_ROWS_PER_CTA;
     const int r1 = min(r0 + SZ_ROWS_PER_CTA, n_out);
     const u8* a = w0 + e * stride0;
-    const int32_t* pairs = plan->pairs[g];
+    const u8* pairs = plan->pairs[g];
     if (!DOWN) {
         const u8* b = w1 + e * stride1;
         switch (n) {
@@ -416,7 +416,7 @@ sz_rows_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 s
 
 template <int K, int N>
 __device__ __forceinline__ void sz_exl3_body(const u8* __restrict__ blob, int n_in, int n_out, int ob, const float* xr, float* so,
-                                             const int32_t* pairs, float* out) {
+                                             const u8* pairs, float* out) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const u32* tr = (const u32*)(blob + 2 * (size_t)n_in + 2 * (size_t)n_out + 4);
     const int nt = n_out / 16, kt = n_in / 16;
@@ -480,7 +480,7 @@ sz_exl3_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 s
     const int mat = blockIdx.x / nblk, ob = blockIdx.x % nblk;
     const u8* blob = mat == 0 ? w0 + e * stride0 : w1 + e * stride1;
     float* out = mat == 0 ? out0 : out1;
-    const int32_t* src_rows = in_by_pair ? plan->pairs[g] : plan->rows[g];
+    const u8* src_rows = in_by_pair ? plan->pairs[g] : plan->rows[g];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // the input in the trellis' basis: (x * suh) H on every 128-block (exl3.rs:414-421), a warp a (row, block) item
     const u16* suh = (const u16*)blob;
@@ -501,7 +501,7 @@ sz_exl3_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 s
         for (int q = 0; q < 4; q++) xr[(size_t)j * n_in + b * 128 + lane + 32 * q] = v[q] * SZ_RSQRT128;
     }
     __syncthreads();
-    const int32_t* pairs = plan->pairs[g];
+    const u8* pairs = plan->pairs[g];
     switch (n) {
         case 1: sz_exl3_body<K, 1>(blob, n_in, n_out, ob, xr, so, pairs, out); break;
         case 2: sz_exl3_body<K, 2>(blob, n_in, n_out, ob, xr, so, pairs, out); break;

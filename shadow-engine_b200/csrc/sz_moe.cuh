@@ -12,11 +12,14 @@
 struct SzPlan {
     int32_t n_groups;
     int32_t pad[3];
-    int32_t expert[SZ_MAXG];
-    int32_t count[SZ_MAXG];
-    int32_t rows[SZ_MAXG][SZ_MAX_VERIFY];   // row j of x
-    int32_t pairs[SZ_MAXG][SZ_MAX_VERIFY];  // j * top_k + rank: row of the per-pair buffers
+    // compact types (experts < 32768, at most 8 rows, at most 128 pairs): the whole plan is 2.4 KB, small enough for a consumer
+    // kernel to copy into shared memory in one sweep
+    int16_t expert[SZ_MAXG];
+    uint8_t count[SZ_MAXG];
+    uint8_t rows[SZ_MAXG][SZ_MAX_VERIFY];   // row j of x
+    uint8_t pairs[SZ_MAXG][SZ_MAX_VERIFY];  // j * top_k + rank: row of the per-pair buffers
 };
+static_assert(SZ_MAX_VERIFY * SZ_MAX_TOPK <= 256, "pair indices are bytes");
 
 // Offsets (bytes) into the caller's scratch buffer.
 struct SzMoeScratch {

@@ -61,8 +61,8 @@ struct SzX3Unit {
     u64 row_stride;       // bytes between the unit's tile rows in global memory
     const u16* suh;       // the 128 input signs/scales of the unit's input block
     int n;                // rows in the group
-    const int32_t* rows;  // null: rows are 0..n-1 (the shared expert)
-    const int32_t* pairs; // null: pair = pair0 + t
+    const u8* rows;   // null: rows are 0..n-1 (the shared expert)
+    const u8* pairs; // null: pair = pair0 + t
     int pair0;
     int in_off;           // first input index of the block
 };
@@ -108,6 +108,17 @@ __device__ __forceinline__ void sz_x3_compute(const u8* stage, const uint4* frag
     }
 }
 
+// The routed plan into shared memory in one cooperative sweep: its fields are then a shared-memory read away instead of a chain of
+// dependent loads from L2 (group count -> expert -> rows -> activations).
+__device__ __forceinline__ const SzPlan* sz_plan_stage(const SzPlan* __restrict__ plan, SzPlan* sp) {
+    if (!plan) return nullptr;
+    static_assert(sizeof(SzPlan) % 16 == 0, "SzPlan is copied in 16-byte pieces");
+    const uint4* src = (const uint4*)plan;
+    uint4* dst = (uint4*)sp;
+    for (int i = threadIdx.x; i < (int)(sizeof(SzPlan) / 16); i += blockDim.x) dst[i] = __ldcg(src + i);
+    return sp;
+}
+
 __device__ __forceinline__ void sz_fix_add(long long* dst, float v) {
     atomicAdd((unsigned long long*)dst, (unsigned long long)__float2ll_rn(v * SZ_FIX_SCALE));
 }
@@ -135,6 +146,8 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     }
     sz_pdl_wait();
     sz_pdl_trigger();
+    __shared__ __align__(16) SzPlan splan;
+    plan = sz_plan_stage(plan, &splan);
     __syncthreads();
     SZ_PH();  // 1 after wait
     const int D = plan ? plan->n_groups : 0;
@@ -244,8 +257,10 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
         for (int i = 0; i < SZ_X3_STAGES; i++) sz_mbar_init(&bars[i], 1);
         sz_mbar_fence_init();
     }
-    __syncthreads();
     // the plan was finished two kernels ago; only the gate/up accumulators need the wait below
+    __shared__ __align__(16) SzPlan splan;
+    plan = sz_plan_stage(plan, &splan);
+    __syncthreads();
     const int D = plan ? plan->n_groups : 0;
     const int NG = D + (sh_down ? 1 : 0);
     const int KB = FF / 128, NC = H / 512;
@@ -256,7 +271,7 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
     (void)hdr_g;
     const u64 drow = (u64)(H / 16) * X::TILE_BYTES;  // bytes of one tile row of the down matrix
 
-    struct DUnit { const u8* src; const u16 *svg, *svu, *suh; int n; const int32_t* pairs; int pair0; int kb, c; };
+    struct DUnit { const u8* src; const u16 *svg, *svu, *suh; int n; const u8* pairs; int pair0; int kb, c; };
     auto unit = [&](int u) {
         DUnit d;
         const int g = u / (KB * NC), rem = u % (KB * NC);
