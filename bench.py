@@ -39,6 +39,20 @@ GATEUP_TRAFFIC = 33029376 + 7936   # bytes a launch of sz_x3_gateup_kernel<3,4> 
 C3_METRIC = "accepted tok/s at spec K=3"
 
 
+class QuietStdout:
+    """Everything libraries write to file descriptor 1 while this is active goes to stderr (NCCL prints its version line there when
+    NCCL_DEBUG is set in the environment); `emit` writes the one JSON line to the real stdout."""
+
+    def __init__(self):
+        sys.stdout.flush()
+        self.real = os.dup(1)
+        os.dup2(2, 1)
+
+    def emit(self, line):
+        sys.stdout.flush()
+        os.write(self.real, (line + "\n").encode())
+
+
 def peaks():
     try:
         p = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -120,6 +134,7 @@ def c3_bytes(cfg, ctx, distinct_per_layer, dense_bytes):
 
 
 def run_c3(args):
+    out = QuietStdout()
     import torch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -136,7 +151,10 @@ def run_c3(args):
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line
         dist.init_process_group("nccl")
-        ep.init_from_process_group()
+        if args.exchange == "nccl":
+            ep.init_from_process_group()
+        else:
+            peer = ep.PeerExchange(C3["hidden"])
     hbm, peak_kind = peaks()
     cfg = dict(C3, n_layer=args.n_layer)
     M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha)
@@ -163,7 +181,7 @@ def run_c3(args):
             sess.result()
             sess.commit(1)
         torch.cuda.synchronize()
-        print(json.dumps({"profile_passes": args.profile_passes, "rows": 4, "context": ctx, "n_layer": cfg["n_layer"]}))
+        out.emit(json.dumps({"profile_passes": args.profile_passes, "rows": 4, "context": ctx, "n_layer": cfg["n_layer"]}))
         return
     gen = md.Generator(sess, prompt, max_new, spec_k=3)
     st = gen.run(W)
@@ -255,7 +273,13 @@ def run_c3(args):
     kern = {nm: {"launches": len(v), "avg_us": sum(v) / len(v), "total_us": sum(v)} for nm, v in per.items()}
     del sess
     if world > 1:
-        szlib.check(L.sz_ep_destroy())
+        import torch.distributed as dist
+        dist.barrier()
+        if args.exchange == "nccl":
+            szlib.check(L.sz_ep_destroy())
+        else:
+            assert peer.status() == 0, "a wait of the peer exchange ran out"
+            peer.close()
     if rank != 0:
         return
 
@@ -286,7 +310,7 @@ def run_c3(args):
         "config": {"workload": "c3", "n_layer": cfg["n_layer"], "hidden": cfg["hidden"], "n_expert": cfg["n_expert"], "top_k": cfg["n_expert_used"],
                    "expert_ff": cfg["expert_ff"], "vocab": cfg["vocab"], "experts": "exl3-3bit", "dense": "q8_0", "kv": "q8_kv",
                    "context": ctx, "spec_k": 3, "batch": 1, "greedy": True, "cycle_alpha": args.alpha,
-                   "parallelism": "ep%d" % world if world > 1 else "single",
+                   "parallelism": "ep%d" % world if world > 1 else "single", "exchange": args.exchange if world > 1 else None,
                    "l2": "inputs larger than L2: a pass streams ~%.1f GB of weights and cache" % (by["all"] / 1e9)},
         "speculation": gen_stats, "verify_step_us": {"rows_1": step_us[1], "rows_4": step_us[4]},
         "roofline": roof, "cpu_baseline": cpu,
@@ -295,7 +319,7 @@ def run_c3(args):
         "gpu_launches": (n_k - 1) * rounds, "launches_per_pass": n_k - 1, "clocks": clocks,
         "kernels": {k: v for k, v in sorted(kern.items(), key=lambda kv: -kv[1]["total_us"])},
     }
-    print(json.dumps(line))
+    out.emit(json.dumps(line))
 
 
 def cpu_c3(pkg, budget_s, threads):
@@ -520,6 +544,8 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe"])
     ap.add_argument("--alpha", type=float, default=C3_ALPHA, help="c3: how strongly the synthetic model continues its token cycles")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="c3, N > 1: the expert-parallel exchange - stores into the peers' memory from the combine kernel (default) or an NCCL all-reduce")
     ap.add_argument("--profile-passes", type=int, default=0, help="c3: only run this many 4-row verify passes (for ncu), no timing")
     ap.add_argument("--ctx", type=int, default=C3_CTX, help="c3: context length the decode runs at")
     ap.add_argument("--n-layer", type=int, default=C3["n_layer"], help="c3: layers (a smaller model for a quick check; not the benchmark)")
@@ -535,6 +561,7 @@ def main():
     if args.impl == "reference":
         return run_reference_c2(args)
 
+    out = QuietStdout()
     import torch
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -602,7 +629,7 @@ def main():
         "also": [{"format": r["fmt"], "value": r["ms_per_step"] * 1e3, "unit": "us", "e2e_us": r["e2e_us"],
                   "roofline": roofline(r), "kernels": r["kernels"]} for r in also],
     }
-    print(json.dumps(line))
+    out.emit(json.dumps(line))
 
 
 if __name__ == "__main__":

@@ -274,6 +274,30 @@ int sz_moe_verify_partial(const sz_moe_layer* layer, uint64_t x, int m, uint64_t
                           uint64_t stream);
 int sz_moe_finish(uint64_t y_fix, int m, int hidden, uint64_t y, uint64_t stream);
 
+/* The same exchange without a collective library on the data path: every rank owns an exchange buffer that its peers map (CUDA
+ * IPC over NVLink).  The combine kernel of a layer stores the rank's fixed-point share straight into every rank's buffer and bumps
+ * an arrival counter there; the finish kernel waits - a bounded number of polls - for all sources and adds the shares.  When an
+ * exchange is attached, expert-parallel layers use it instead of NCCL (sz_ep_init is then not needed).
+ *   sz_ep_p2p_bytes / _alloc / _free: the buffer (an allocation of its own, zeroed: IPC exports whole allocations);
+ *   sz_ep_ipc_export / _import / _close: the 64-byte handle the host carries to the peers, and the mapping on their side;
+ *   sz_ep_p2p_attach(rank, world, hidden, bufs): bufs[r] = rank r's buffer as this process addresses it; _detach;
+ *   sz_ep_p2p_status: 1 in *error once a wait of this rank ran out (a peer died or fell behind by more than the poll budget):
+ *   the pass still ends, its output is wrong, and every later wait of this rank returns at once.
+ * All ranks must attach zeroed buffers and then run the same sequence of passes.
+ * sz_moe_verify_partial with y_fix = 0 pushes the share; sz_moe_finish_exchange adds up (the two halves, for tests that run several
+ * ranks on one GPU one after the other). */
+int sz_ep_p2p_bytes(int world, int hidden, int64_t* bytes);
+int sz_ep_p2p_alloc(int64_t bytes, uint64_t* ptr);
+int sz_ep_p2p_free(uint64_t ptr);
+int sz_ep_ipc_export(uint64_t ptr, uint8_t handle[64]);
+int sz_ep_ipc_import(const uint8_t handle[64], uint64_t* ptr);
+int sz_ep_ipc_close(uint64_t ptr);
+int sz_ep_p2p_attach(int rank, int world, int hidden, const uint64_t* bufs);
+void sz_ep_p2p_detach(void);
+int sz_ep_p2p_world(void);
+int sz_ep_p2p_status(int* error);
+int sz_moe_finish_exchange(const sz_moe_layer* layer, int m, uint64_t y, uint64_t stream);
+
 /* sz_moe_verify without a scratch argument.  (No counterpart in the reference: its session always owns a scratch buffer.)
  * For hosts that cannot allocate device memory once they are running - an engine that gave all of it to its own arena at start-up,
  * a plugin in a process that forbids the CUDA allocator after initialisation (a cudaMalloc would stall every stream of the GPU) -

@@ -96,3 +96,151 @@ int sz_ep_allreduce_i64(long long* buf, size_t count, cudaStream_t st) {
     sz_trace_mark("ep_allreduce", st);
     return SZ_OK;
 }
+
+// ---- exchange over peer memory ------------------------------------------------------------------------------------------------------
+#include "sz_moe.cuh"
+
+namespace {
+struct P2p {
+    int rank = 0, world = 0;
+    int hidden = 0;
+    u8* buf[SZ_EP_MAX_RANKS] = {};
+} g_p2p;
+}  // namespace
+
+// Sums the ranks' rows of the current slot into y.  grid: any; block 256.  Thread 0 of every block waits for the sources (a bounded
+// number of polls; on running out it raises the header's error word and the block goes on with what is there, so the kernel always
+// ends).  The last block to finish closes the exchange: epoch + 1, target + blocks of the combine kernel.
+__global__ void __launch_bounds__(256)
+sz_ep_finish_kernel(u8* __restrict__ mine, int world, long long row_elems, unsigned long long nb, int n, float* __restrict__ y) {
+    __shared__ int s_last;
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    SzEpHeader* hdr = (SzEpHeader*)mine;
+    const unsigned long long want = hdr->target + nb;
+    const int slot = (int)(hdr->epoch & 1ull);
+    if (threadIdx.x < world) {
+        volatile unsigned long long* c = sz_ep_arrive(mine, threadIdx.x);
+        int polls = 0;
+        bool ok = false;
+        while (polls < SZ_EP_SPIN_LIMIT && *(volatile unsigned int*)&hdr->error == 0) {
+            unsigned long long v;
+            asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(c));
+            if (v >= want) { ok = true; break; }
+            polls++;
+            __nanosleep(64);
+        }
+        if (!ok) atomicExch(&hdr->error, 1u);
+    }
+    __syncthreads();
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        long long f = 0;
+        for (int r = 0; r < world; r++) f += __ldcg(sz_ep_slot(mine, world, row_elems, slot, r) + i);
+        y[i] = (float)((double)f * (1.0 / 1099511627776.0));
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) s_last = (atomicAdd(&hdr->ticket, 1u) == gridDim.x - 1);
+    __syncthreads();
+    if (s_last && threadIdx.x == 0) {
+        hdr->ticket = 0;
+        hdr->target = want;
+        hdr->epoch = hdr->epoch + 1;
+    }
+}
+
+extern "C" int sz_ep_p2p_bytes(int world, int hidden, int64_t* bytes) {
+    if (!bytes || world < 1 || world > SZ_EP_MAX_RANKS || hidden < 1) return sz_fail(SZ_E_ARG, "sz_ep_p2p_bytes: %d ranks, hidden %d", world, hidden);
+    *bytes = SZ_EP_HDR_BYTES + (int64_t)2 * world * SZ_MAX_VERIFY * hidden * 8;
+    return SZ_OK;
+}
+
+// The exchange buffer has to be an allocation of its own (CUDA IPC exports whole allocations), made once at start-up.
+extern "C" int sz_ep_p2p_alloc(int64_t bytes, uint64_t* ptr) {
+    if (!ptr || bytes <= 0) return sz_fail(SZ_E_ARG, "sz_ep_p2p_alloc: bad argument");
+    void* p = nullptr;
+    SZ_CUDA(cudaMalloc(&p, (size_t)bytes));
+    SZ_CUDA(cudaMemset(p, 0, (size_t)bytes));
+    SZ_CUDA(cudaDeviceSynchronize());
+    *ptr = (uint64_t)p;
+    return SZ_OK;
+}
+extern "C" int sz_ep_p2p_free(uint64_t ptr) {
+    if (ptr) SZ_CUDA(cudaFree((void*)ptr));
+    return SZ_OK;
+}
+extern "C" int sz_ep_ipc_export(uint64_t ptr, uint8_t handle[64]) {
+    if (!ptr || !handle) return sz_fail(SZ_E_ARG, "sz_ep_ipc_export: null argument");
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(h) == 64, "CUDA IPC handles are 64 bytes");
+    SZ_CUDA(cudaIpcGetMemHandle(&h, (void*)ptr));
+    memcpy(handle, &h, 64);
+    return SZ_OK;
+}
+extern "C" int sz_ep_ipc_import(const uint8_t handle[64], uint64_t* ptr) {
+    if (!ptr || !handle) return sz_fail(SZ_E_ARG, "sz_ep_ipc_import: null argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void* p = nullptr;
+    SZ_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    *ptr = (uint64_t)p;
+    return SZ_OK;
+}
+extern "C" int sz_ep_ipc_close(uint64_t ptr) {
+    if (ptr) SZ_CUDA(cudaIpcCloseMemHandle((void*)ptr));
+    return SZ_OK;
+}
+
+// bufs[r]: rank r's exchange buffer as this process addresses it (its own allocation for r == rank, an imported mapping otherwise;
+// on one GPU, for tests, simply other local allocations).  Expert-parallel layers then exchange over these buffers instead of NCCL.
+extern "C" int sz_ep_p2p_attach(int rank, int world, int hidden, const uint64_t* bufs) {
+    if (!bufs || world < 1 || world > SZ_EP_MAX_RANKS || rank < 0 || rank >= world || hidden < 1)
+        return sz_fail(SZ_E_ARG, "sz_ep_p2p_attach: rank %d of %d, hidden %d", rank, world, hidden);
+    for (int r = 0; r < world; r++)
+        if (!bufs[r] || (bufs[r] & 255)) return sz_fail(SZ_E_ARG, "sz_ep_p2p_attach: buffer %d is null or not 256-byte aligned", r);
+    g_p2p.rank = rank; g_p2p.world = world; g_p2p.hidden = hidden;
+    for (int r = 0; r < SZ_EP_MAX_RANKS; r++) g_p2p.buf[r] = r < world ? (u8*)bufs[r] : nullptr;
+    return SZ_OK;
+}
+extern "C" void sz_ep_p2p_detach(void) { g_p2p = P2p(); }
+extern "C" int sz_ep_p2p_world(void) { return g_p2p.world; }
+
+// 0: no wait of this rank's exchanges ever ran out.  Synchronises the device.
+extern "C" int sz_ep_p2p_status(int* error) {
+    if (!error) return sz_fail(SZ_E_ARG, "null argument");
+    *error = 0;
+    if (!g_p2p.world) return SZ_OK;
+    SzEpHeader h;
+    SZ_CUDA(cudaMemcpy(&h, g_p2p.buf[g_p2p.rank], sizeof(h), cudaMemcpyDeviceToHost));
+    *error = (int)h.error;
+    return SZ_OK;
+}
+
+// for sz_moe.cu: the push descriptor of the attached exchange (world 0: none), and the finish launch
+int sz_ep_p2p_push(int hidden, SzEpPush* p) {
+    memset(p, 0, sizeof(*p));
+    if (!g_p2p.world) return SZ_OK;
+    if (hidden != g_p2p.hidden) return sz_fail(SZ_E_ARG, "the exchange buffers were sized for hidden %d, the layer has %d", g_p2p.hidden, hidden);
+    for (int r = 0; r < g_p2p.world; r++) p->buf[r] = g_p2p.buf[r];
+    p->world = g_p2p.world; p->me = g_p2p.rank;
+    p->row_elems = (long long)SZ_MAX_VERIFY * hidden;
+    return SZ_OK;
+}
+int sz_ep_p2p_finish(int m, int hidden, unsigned long long combine_blocks, float* y, cudaStream_t st);
+int sz_moe_combine_blocks(const sz_moe_layer* L, int m);  // sz_moe.cu
+
+// The finish half on its own, for hosts (and tests) that run the two halves of an exchange apart: sz_moe_verify_partial pushes,
+// this adds up.  The layer says how many blocks the combine kernel of the push had.
+extern "C" int sz_moe_finish_exchange(const sz_moe_layer* L, int m, uint64_t y, uint64_t stream) {
+    if (!L || !y || m < 1 || m > SZ_MAX_VERIFY) return sz_fail(SZ_E_ARG, "sz_moe_finish_exchange: bad argument");
+    if (!g_p2p.world) return sz_fail(SZ_E_ARG, "sz_moe_finish_exchange: no exchange attached");
+    if (L->hidden != g_p2p.hidden) return sz_fail(SZ_E_ARG, "the exchange buffers were sized for hidden %d, the layer has %d", g_p2p.hidden, L->hidden);
+    return sz_ep_p2p_finish(m, L->hidden, (unsigned long long)sz_moe_combine_blocks(L, m), (float*)y, (cudaStream_t)stream);
+}
+
+int sz_ep_p2p_finish(int m, int hidden, unsigned long long combine_blocks, float* y, cudaStream_t st) {
+    const int n = m * hidden;
+    SZ_CUDA(sz_launch("ep_finish", sz_ep_finish_kernel, dim3((n + 1023) / 1024), dim3(256), 0, st, true, g_p2p.buf[g_p2p.rank], g_p2p.world,
+                      (long long)SZ_MAX_VERIFY * hidden, combine_blocks, n, y));
+    return SZ_OK;
+}

@@ -526,15 +526,15 @@ sz_exl3_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 s
 __global__ void __launch_bounds__(256)
 sz_combine_kernel(const float* __restrict__ eo, const int32_t* __restrict__ ridx, const double* __restrict__ rw, const float* __restrict__ so,
                   const float* __restrict__ logits, int ne, int k, int H, int has_shared, float* __restrict__ y, long long* __restrict__ y_fix,
-                  int e_lo, int e_hi) {
+                  int e_lo, int e_hi, const SzEpPush push) {
     sz_pdl_wait();
     sz_pdl_trigger();
     const int j = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= H) return;
+    const bool on = i < H;
     double acc = 0.0;
     long long fix = 0;
-    for (int t = 0; t < k; t++) {
+    for (int t = 0; t < (on ? k : 0); t++) {
         if (y_fix) {
             const int e = __ldcg(ridx + j * k + t);
             if (e < e_lo || e >= e_hi) continue;
@@ -543,12 +543,20 @@ sz_combine_kernel(const float* __restrict__ eo, const int32_t* __restrict__ ridx
             acc += __ldcg(rw + j * k + t) * (double)__ldcg(eo + (size_t)(j * k + t) * H + i);
         }
     }
-    if (has_shared) {
+    if (has_shared && on) {
         const float sg = sz_sigmoid(__ldcg(logits + (size_t)j * (ne + 1) + ne));
         const double sv = (double)(sg * __ldcg(so + (size_t)j * H + i));
         if (y_fix) fix += __double2ll_rn(sv * SZ_YFIX_SCALE); else acc += sv;
     }
-    if (y_fix) y_fix[(size_t)j * H + i] = fix; else y[(size_t)j * H + i] = (float)acc;
+    if (!y_fix) { if (on) y[(size_t)j * H + i] = (float)acc; return; }
+    if (push.world == 0) { if (on) y_fix[(size_t)j * H + i] = fix; return; }
+    if (on) {
+        const int slot = (int)(((const SzEpHeader*)push.buf[push.me])->epoch & 1ull);
+        for (int r = 0; r < push.world; r++) sz_ep_slot(push.buf[r], push.world, push.row_elems, slot, push.me)[(size_t)j * H + i] = fix;
+    }
+    __threadfence_system();
+    __syncthreads();   // every thread of the block reaches this: the returns above depend on kernel arguments only
+    if (threadIdx.x < push.world) atomicAdd_system(sz_ep_arrive(push.buf[threadIdx.x], push.me), 1ull);
 }
 
 // the summed fixed-point output back to f32
@@ -740,12 +748,15 @@ static int sz_x3_launch(cudaStream_t st, const sz_moe_layer* L, int m, const SzP
 }
 
 int sz_ep_allreduce_i64(long long* buf, size_t count, cudaStream_t st);  // sz_ep.cu
+int sz_ep_p2p_push(int hidden, SzEpPush* p);
+int sz_ep_p2p_finish(int m, int hidden, unsigned long long combine_blocks, float* y, cudaStream_t st);
+extern "C" int sz_ep_p2p_world(void);
 extern "C" int sz_ep_world(void);
 
 // The pass itself.  y_fix == null: the whole layer into y (f32).  y_fix != null: expert-parallel share - only the experts this rank
 // holds (and the shared expert where ep_shared says so) - as 64-bit fixed point into y_fix; y is not touched.
 static int sz_moe_run(const sz_moe_layer* L0, uint64_t x, int m, float* y, long long* y_fix, uint64_t route_idx, uint64_t route_w, uint64_t scratch,
-                      int64_t scratch_bytes, uint64_t stream) {
+                      int64_t scratch_bytes, uint64_t stream, const SzEpPush& push, unsigned long long* combine_blocks) {
     int rc = sz_moe_check(L0, m);
     if (rc) return rc;
     if (!x || !sz_aligned16(x)) return sz_fail(SZ_E_ARG, "x must be non-null and 16-byte aligned");
@@ -811,7 +822,8 @@ static int sz_moe_run(const sz_moe_layer* L0, uint64_t x, int m, float* y, long 
         SZ_CUDA(sz_launch("combine_exl3", sz_x3_combine_kernel, dim3(m * (H / 128)), dim3((L->top_k + 1) * 32), 0, st, true, (const long long*)acc_d,
                           (const int32_t*)ridx, (const double*)rw, (const u8*)L->down, (u64)L->down_stride,
                           (const u8*)(sh_fused ? L->sh_down : 0), (const float*)(shared && !sh_fused ? so : nullptr), (const float*)logits,
-                          (int)L->n_expert, (int)L->top_k, m, H, FF, shared ? 1 : 0, y, y_fix, e_lo, e_hi));
+                          (int)L->n_expert, (int)L->top_k, m, H, FF, shared ? 1 : 0, y, y_fix, e_lo, e_hi, push));
+        if (combine_blocks) *combine_blocks = (unsigned long long)m * (H / 128);
         return SZ_OK;
     }
     if ((rc = sz_ffn(st, L->expert_type, plan, groups, L->gate, L->gate_stride, L->up, L->up_stride, L->down, L->down_stride, xp, H, FF, g, u,
@@ -823,7 +835,8 @@ static int sz_moe_run(const sz_moe_layer* L0, uint64_t x, int m, float* y, long 
         return rc;
     if (shared && (rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true))) return rc;
     SZ_CUDA(sz_launch("combine", sz_combine_kernel, dim3((H + 255) / 256, m), dim3(256), 0, st, true, (const float*)eo, (const int32_t*)ridx,
-                      (const double*)rw, (const float*)so, (const float*)logits, (int)L->n_expert, (int)L->top_k, H, shared ? 1 : 0, y, y_fix, e_lo, e_hi));
+                      (const double*)rw, (const float*)so, (const float*)logits, (int)L->n_expert, (int)L->top_k, H, shared ? 1 : 0, y, y_fix, e_lo, e_hi, push));
+    if (combine_blocks) *combine_blocks = (unsigned long long)((H + 255) / 256) * m;
     return SZ_OK;
 }
 
@@ -836,27 +849,51 @@ static int sz_moe_finish_launch(uint64_t y_fix, int m, int hidden, uint64_t y, u
     return SZ_OK;
 }
 
+// blocks of the combine kernel a pass of m rows launches for this layer (what one exchange adds to the arrival counters)
+int sz_moe_combine_blocks(const sz_moe_layer* L, int m) {
+    return sz_fast_path(L).exl3 ? m * (L->hidden / 128) : ((L->hidden + 255) / 256) * m;
+}
+
 extern "C" int sz_moe_finish(uint64_t y_fix, int m, int hidden, uint64_t y, uint64_t stream) {
     return sz_moe_finish_launch(y_fix, m, hidden, y, stream, false);  // the caller's own exchange came before it
 }
 
 extern "C" int sz_moe_verify_partial(const sz_moe_layer* L, uint64_t x, int m, uint64_t y_fix, uint64_t scratch, int64_t scratch_bytes,
                                      uint64_t stream) {
+    if (sz_ep_p2p_world() > 0 && !y_fix) {  // exchange attached and no local destination: the partial goes to every rank's buffer
+        int rc = sz_moe_check(L, m);
+        if (rc) return rc;
+        SzEpPush push;
+        if ((rc = sz_ep_p2p_push(L->hidden, &push))) return rc;
+        const SzMoeScratch S0 = sz_moe_layout(L, m);
+        return sz_moe_run(L, x, m, nullptr, (long long*)((u8*)scratch + S0.y_fix), 0, 0, scratch, scratch_bytes, stream, push, nullptr);
+    }
     if (!y_fix || (y_fix & 15)) return sz_fail(SZ_E_ARG, "sz_moe_verify_partial: y_fix must be non-null and 16-byte aligned");
-    return sz_moe_run(L, x, m, nullptr, (long long*)y_fix, 0, 0, scratch, scratch_bytes, stream);
+    SzEpPush none = {};
+    return sz_moe_run(L, x, m, nullptr, (long long*)y_fix, 0, 0, scratch, scratch_bytes, stream, none, nullptr);
 }
 
 extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t y, uint64_t route_idx, uint64_t route_w,
                              uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
     if (!y || !sz_aligned16(y)) return sz_fail(SZ_E_ARG, "y must be non-null and 16-byte aligned");
-    if (!L || L->ep_count <= 0) return sz_moe_run(L, x, m, (float*)y, nullptr, route_idx, route_w, scratch, scratch_bytes, stream);
+    SzEpPush none = {};
+    if (!L || L->ep_count <= 0) return sz_moe_run(L, x, m, (float*)y, nullptr, route_idx, route_w, scratch, scratch_bytes, stream, none, nullptr);
     // expert-parallel layer: this rank's share in fixed point, summed over the ranks (exactly: integers), then back to f32
-    if (sz_ep_world() < 1) return sz_fail(SZ_E_ARG, "the layer is sharded (ep_count = %d) but sz_ep_init has not run", L->ep_count);
     int rc = sz_moe_check(L, m);
     if (rc) return rc;
+    if (sz_ep_p2p_world() > 0) {
+        // over peer memory: the combine kernel stores its share into every rank's exchange buffer and the finish kernel adds the shares
+        SzEpPush push;
+        if ((rc = sz_ep_p2p_push(L->hidden, &push))) return rc;
+        const SzMoeScratch S0 = sz_moe_layout(L, m);
+        unsigned long long nb = 0;
+        if ((rc = sz_moe_run(L, x, m, nullptr, (long long*)((u8*)scratch + S0.y_fix), route_idx, route_w, scratch, scratch_bytes, stream, push, &nb))) return rc;
+        return sz_ep_p2p_finish(m, L->hidden, nb, (float*)y, (cudaStream_t)stream);
+    }
+    if (sz_ep_world() < 1) return sz_fail(SZ_E_ARG, "the layer is sharded (ep_count = %d) but neither sz_ep_init nor sz_ep_p2p_attach has run", L->ep_count);
     const SzMoeScratch S = sz_moe_layout(L, m);
     long long* y_fix = (long long*)((u8*)scratch + S.y_fix);
-    if ((rc = sz_moe_run(L, x, m, nullptr, y_fix, route_idx, route_w, scratch, scratch_bytes, stream))) return rc;
+    if ((rc = sz_moe_run(L, x, m, nullptr, y_fix, route_idx, route_w, scratch, scratch_bytes, stream, none, nullptr))) return rc;
     const bool exchange = sz_ep_world() > 1;
     if (exchange && (rc = sz_ep_allreduce_i64(y_fix, (size_t)m * L->hidden, (cudaStream_t)stream))) return rc;
     return sz_moe_finish_launch((uint64_t)y_fix, m, L->hidden, y, stream, !exchange);

@@ -9,6 +9,35 @@
 // The routed work of one pass, grouped by expert so a matrix is streamed once for every row that chose it.  Groups are in
 // ascending expert order; inside a group the rows are in ascending row order.  (The reference's group record is
 // [count, in rows.., out rows..], crates/shadowzero-cuda/src/session.rs:2129-2146; pair = row * top_k + rank.)
+// Expert-parallel exchange over peer memory (no collective library on the data path).  Every rank owns one exchange buffer that
+// its peers map (CUDA IPC): a header, one arrival counter a source rank, and two slots of [ranks][8 * hidden] 64-bit fixed-point
+// partial outputs.  The combine kernel of rank `me` stores its partial output into slot (epoch & 1), row `me`, of EVERY rank's
+// buffer (plain stores over NVLink), fences, and bumps the arrival counter `me` of every rank; the finish kernel of a rank waits
+// (bounded) until every source's counter reached the round's target, adds the rows - integers, so any order gives the same bits -
+// and converts.  Two slots are enough: a rank can only start round e + 2 after every peer has sent round e + 1, which a peer does
+// only after it has finished reading round e.
+#define SZ_EP_MAX_RANKS 8
+#define SZ_EP_HDR_BYTES 2048           // header (128) + 8 counters on lines of their own, padded
+#define SZ_EP_SPIN_LIMIT 400000        // polls of a counter before a waiting block gives up and raises the error word
+
+struct SzEpHeader {
+    unsigned long long epoch;    // exchanges completed by this rank
+    unsigned long long target;   // arrivals a source has made once the current exchange is complete, minus this exchange's
+    unsigned int ticket;         // finish blocks done in the current exchange
+    unsigned int error;          // a wait ran out
+};
+
+struct SzEpPush {
+    u8* buf[SZ_EP_MAX_RANKS];    // every rank's exchange buffer as this process sees it (own or mapped)
+    int world, me;
+    long long row_elems;         // 8 * hidden: elements between two ranks' rows of a slot
+};
+
+__device__ __forceinline__ long long* sz_ep_slot(u8* buf, int world, long long row_elems, int slot, int src) {
+    return (long long*)(buf + SZ_EP_HDR_BYTES) + ((long long)slot * world + src) * row_elems;
+}
+__device__ __forceinline__ unsigned long long* sz_ep_arrive(u8* buf, int src) { return (unsigned long long*)(buf + 128 + 128 * src); }
+
 struct SzPlan {
     int32_t n_groups;
     int32_t pad[3];

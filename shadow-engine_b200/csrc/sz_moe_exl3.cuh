@@ -386,7 +386,7 @@ __global__ void __launch_bounds__((SZ_MAX_TOPK + 1) * 32)
 sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restrict__ ridx, const double* __restrict__ rw,
                      const u8* __restrict__ down, u64 dstride, const u8* __restrict__ sh_down, const float* __restrict__ so_f32,
                      const float* __restrict__ logits, int ne, int top_k, int m, int H, int FF, int has_shared, float* __restrict__ y,
-                     long long* __restrict__ y_fix, int e_lo, int e_hi) {
+                     long long* __restrict__ y_fix, int e_lo, int e_hi, const SzEpPush push) {
     __shared__ float part[SZ_MAX_TOPK + 1][128];
     __shared__ int local[SZ_MAX_TOPK];
     sz_pdl_wait();
@@ -434,13 +434,24 @@ sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restric
                 for (int t = 0; t < top_k; t++)
                     if (local[t]) f += __double2ll_rn(__ldcg(rw + j * top_k + t) * (double)part[t][i] * 1099511627776.0);
                 if (has_shared) f += __double2ll_rn((double)part[top_k][i] * 1099511627776.0);
-                y_fix[(size_t)j * H + b * 128 + i] = f;
+                if (push.world > 0) {
+                    const int slot = (int)(((const SzEpHeader*)push.buf[push.me])->epoch & 1ull);
+                    for (int r = 0; r < push.world; r++)
+                        sz_ep_slot(push.buf[r], push.world, push.row_elems, slot, push.me)[(size_t)j * H + b * 128 + i] = f;
+                } else {
+                    y_fix[(size_t)j * H + b * 128 + i] = f;
+                }
             } else {
                 double a = 0.0;
                 for (int t = 0; t < top_k; t++) a += __ldcg(rw + j * top_k + t) * (double)part[t][i];
                 if (has_shared) a += (double)part[top_k][i];
                 y[(size_t)j * H + b * 128 + i] = (float)a;
             }
+        }
+        if (y_fix && push.world > 0) {  // the block's stores are out: make them visible system-wide, then announce them to every rank
+            __threadfence_system();
+            __syncwarp();
+            if (lane < push.world) atomicAdd_system(sz_ep_arrive(push.buf[lane], push.me), 1ull);
         }
     }
 }

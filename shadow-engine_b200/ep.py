@@ -69,3 +69,67 @@ def init_from_process_group(group=None, get_id=None, init=None):
     assert isinstance(ident, (bytes, bytearray)) and len(ident) == 128
     init(rank, world, bytes(ident))
     return rank, world
+
+
+class PeerExchange:
+    """The exchange over peer memory: this rank's buffer, the peers' buffers mapped through CUDA IPC, attached to the library.
+    `group`: a torch.distributed process group (one process per GPU, the current CUDA device already set).  With `group=None`
+    and `local_world` set, all the ranks' buffers are allocated in this process (several ranks emulated on one GPU, for tests):
+    `use(rank)` then switches the rank the library acts as."""
+
+    def __init__(self, hidden, group=None, local_world=None):
+        import torch.distributed as dist
+        self.lib = szlib.load()
+        self.hidden = hidden
+        self.mapped = []
+        n = C.c_int64()
+        if local_world is not None:
+            self.rank, self.world = 0, local_world
+            szlib.check(self.lib.sz_ep_p2p_bytes(self.world, hidden, C.byref(n)))
+            self.bufs = []
+            for _ in range(self.world):
+                p = C.c_uint64()
+                szlib.check(self.lib.sz_ep_p2p_alloc(n.value, C.byref(p)))
+                self.bufs.append(p.value)
+            self.own = list(self.bufs)
+            self.use(0)
+            return
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        szlib.check(self.lib.sz_ep_p2p_bytes(self.world, hidden, C.byref(n)))
+        p = C.c_uint64()
+        szlib.check(self.lib.sz_ep_p2p_alloc(n.value, C.byref(p)))
+        self.own = [p.value]
+        h = (C.c_uint8 * 64)()
+        szlib.check(self.lib.sz_ep_ipc_export(p.value, h))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(h), group=group)
+        self.bufs = []
+        for r in range(self.world):
+            if r == self.rank:
+                self.bufs.append(p.value)
+                continue
+            q = C.c_uint64()
+            hb = (C.c_uint8 * 64).from_buffer_copy(handles[r])
+            szlib.check(self.lib.sz_ep_ipc_import(hb, C.byref(q)))
+            self.mapped.append(q.value)
+            self.bufs.append(q.value)
+        self.use(self.rank)
+        dist.barrier(group=group)   # nobody pushes before every rank has mapped and zeroed
+
+    def use(self, rank):
+        self.rank = rank
+        arr = (C.c_uint64 * self.world)(*self.bufs)
+        szlib.check(self.lib.sz_ep_p2p_attach(rank, self.world, self.hidden, arr))
+
+    def status(self):
+        e = C.c_int()
+        szlib.check(self.lib.sz_ep_p2p_status(C.byref(e)))
+        return e.value
+
+    def close(self):
+        self.lib.sz_ep_p2p_detach()
+        for q in self.mapped:
+            self.lib.sz_ep_ipc_close(q)
+        for p in self.own:
+            self.lib.sz_ep_p2p_free(p)
+        self.mapped, self.own = [], []

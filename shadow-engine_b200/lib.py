@@ -94,6 +94,17 @@ SYMBOLS = {
     "sz_ep_destroy": (C.c_int, []),
     "sz_moe_verify_partial": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_int64, C.c_uint64]),
     "sz_moe_finish": (C.c_int, [C.c_uint64, C.c_int, C.c_int, C.c_uint64, C.c_uint64]),
+    "sz_ep_p2p_bytes": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int64)]),
+    "sz_ep_p2p_alloc": (C.c_int, [C.c_int64, C.POINTER(C.c_uint64)]),
+    "sz_ep_p2p_free": (C.c_int, [C.c_uint64]),
+    "sz_ep_ipc_export": (C.c_int, [C.c_uint64, C.c_void_p]),
+    "sz_ep_ipc_import": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
+    "sz_ep_ipc_close": (C.c_int, [C.c_uint64]),
+    "sz_ep_p2p_attach": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_uint64)]),
+    "sz_ep_p2p_detach": (None, []),
+    "sz_ep_p2p_world": (C.c_int, []),
+    "sz_ep_p2p_status": (C.c_int, [C.POINTER(C.c_int)]),
+    "sz_moe_finish_exchange": (C.c_int, [C.POINTER(MoeLayerC), C.c_int, C.c_uint64, C.c_uint64]),
     "sz_moe_static_scratch_max": (C.c_int, [C.POINTER(C.c_int64)]),
     "sz_moe_verify_static": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
 }

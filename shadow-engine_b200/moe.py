@@ -109,6 +109,19 @@ class MoeLayer:
                                                    self.scratch_bytes, st))
         return y_fix
 
+    def push_partial(self, x, stream=None):
+        """With a peer exchange attached: this rank's share goes into every rank's exchange buffer."""
+        m = x.shape[0]
+        st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        szlib.check(self.lib.sz_moe_verify_partial(C.byref(self.c), x.data_ptr(), m, 0, self.scratch_addr, self.scratch_bytes, st))
+
+    def finish_exchange(self, m, y=None, stream=None):
+        if y is None:
+            y = torch.empty((m, self.shape["hidden"]), dtype=torch.float32, device=self.device)
+        st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        szlib.check(self.lib.sz_moe_finish_exchange(C.byref(self.c), m, y.data_ptr(), st))
+        return y
+
     def finish(self, y_fix, y=None, stream=None):
         m, H = y_fix.shape
         if y is None:

@@ -71,6 +71,56 @@ def test_sharded_layer_needs_the_communicator():
         lib.sz_ep_destroy()
 
 
+@pytest.mark.parametrize("ety,H,FF,SF", [("q8", 512, 256, 512), ("x3", 512, 256, 256)])
+def test_peer_exchange_emulated_on_one_gpu(ety, H, FF, SF):
+    """The exchange over peer memory with every rank's buffer on this GPU: all ranks push, then all ranks add up.  Every rank must
+    end with the bits of the integer sum of the shares."""
+    ty = {"q8": szlib.TYPE_Q8_0, "x3": szlib.TYPE_EXL3(3)}[ety]
+    L = synth.make_moe_layer(H, 32, 4, FF, SF, ty, ty, seed=43)
+    x = torch.randn(3, H, generator=torch.Generator().manual_seed(8)).to(torch.bfloat16).to(torch.float32).cuda()
+    ref, any_layer = emulate(L, x, 1)
+    want = any_layer.finish(ref)
+    for G in (2, 4):
+        ex = ep.PeerExchange(H, local_world=G)
+        try:
+            layers = [moe.MoeLayer(L, "cuda:0", shard=ep.shard_spec(r, G, 32)) for r in range(G)]
+            for rounds in range(3):                      # several exchanges: the slots alternate, the counters accumulate
+                for r in range(G):
+                    ex.use(r)
+                    layers[r].push_partial(x)
+                ys = []
+                for r in range(G):
+                    ex.use(r)
+                    ys.append(layers[r].finish_exchange(3))
+                torch.cuda.synchronize()
+                for r in range(G):
+                    assert torch.equal(ys[r], want), (G, rounds, r)
+            for r in range(G):
+                ex.use(r)
+                assert ex.status() == 0
+        finally:
+            ex.close()
+
+
+def test_peer_exchange_wait_runs_out_without_hanging():
+    """A peer that never sends: the finish kernel gives up after its poll budget, raises the error word, and the context stays
+    usable.  (The failure is a flag that nothing sets - no fault, no trap.)"""
+    L = synth.make_moe_layer(256, 16, 4, 128, 128, szlib.TYPE_Q8_0, szlib.TYPE_Q8_0, seed=44)
+    x = torch.randn(2, 256).cuda()
+    ex = ep.PeerExchange(256, local_world=2)
+    try:
+        layer = moe.MoeLayer(L, "cuda:0", shard=ep.shard_spec(0, 2, 16))
+        ex.use(0)
+        layer.moe_batch(x)                               # rank 1 never pushes
+        torch.cuda.synchronize()
+        assert ex.status() == 1
+        layer.moe_batch(x)                               # later waits return at once
+        torch.cuda.synchronize()
+        assert torch.isfinite(torch.ones(4, device="cuda").sum()).item()
+    finally:
+        ex.close()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -95,6 +145,25 @@ def _rank(rank, world, port, out_dir):
         y = layer.moe_batch(x)
         torch.cuda.synchronize()
         np.save(os.path.join(out_dir, "y%d.npy" % rank), y.cpu().numpy())
+        # the same layer over peer memory instead of NCCL, several exchanges in a row
+        ex = ep.PeerExchange(512)
+        try:
+            for it in range(4):
+                yp = layer.moe_batch(x)
+                torch.cuda.synchronize()
+                assert torch.equal(yp, y), it
+            assert ex.status() == 0
+            M2 = model.make_model(model.TINY, seed=1, cycle_alpha=0.24)
+            _, cyc2 = model.token_cycles(model.TINY["vocab"], 1)
+            dm2 = model.DeviceModel(M2, dev, ep=(rank, world))
+            s2 = model.Session(dm2, 512)
+            toks2, _, _ = s2.generate(model.make_prompt(128, model.TINY["vocab"], seed=1, cycles=cyc2), 48, spec_k=3)
+            np.save(os.path.join(out_dir, "p%d.npy" % rank), np.asarray(toks2, dtype=np.int64))
+            assert ex.status() == 0
+            del s2
+            dist.barrier()
+        finally:
+            ex.close()
         # a whole model: every rank must generate the same tokens
         M = model.make_model(model.TINY, seed=1, cycle_alpha=0.24)
         _, cyc = model.token_cycles(model.TINY["vocab"], 1)
@@ -125,6 +194,7 @@ def test_two_gpus_over_nccl(tmp_path):
     assert np.array_equal(layer.finish(ref).cpu().numpy(), y0)          # two cards == one card, bit for bit
     t0, t1 = np.load(tmp_path / "t0.npy"), np.load(tmp_path / "t1.npy")
     assert np.array_equal(t0, t1)
+    assert np.array_equal(np.load(tmp_path / "p0.npy"), t0) and np.array_equal(np.load(tmp_path / "p1.npy"), t0)
     lib = szlib.load()
     szlib.check(lib.sz_ep_init(0, 1, None))
     try:
