@@ -532,6 +532,7 @@ sz_combine_kernel(const float* __restrict__ eo, const int32_t* __restrict__ ridx
     const int j = blockIdx.y;
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     const bool on = i < H;
+    const int slot = y_fix && push.world > 0 ? (int)(__ldcg(&((const SzEpHeader*)push.buf[push.me])->epoch) & 1ull) : 0;
     double acc = 0.0;
     long long fix = 0;
     for (int t = 0; t < (on ? k : 0); t++) {
@@ -551,7 +552,6 @@ sz_combine_kernel(const float* __restrict__ eo, const int32_t* __restrict__ ridx
     if (!y_fix) { if (on) y[(size_t)j * H + i] = (float)acc; return; }
     if (push.world == 0) { if (on) y_fix[(size_t)j * H + i] = fix; return; }
     if (on) {
-        const int slot = (int)(((const SzEpHeader*)push.buf[push.me])->epoch & 1ull);
         for (int r = 0; r < push.world; r++) sz_ep_slot(push.buf[r], push.world, push.row_elems, slot, push.me)[(size_t)j * H + i] = fix;
     }
     __threadfence_system();

@@ -394,6 +394,8 @@ sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restric
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = H / 128;
     const int j = blockIdx.x / nb, b = blockIdx.x % nb;
+    // which of the two slots of the exchange buffers this round writes (read once, early: it is a load from L2)
+    const int slot = y_fix && push.world > 0 ? (int)(__ldcg(&((const SzEpHeader*)push.buf[push.me])->epoch) & 1ull) : 0;
     if (warp < top_k) {
         const int pair = j * top_k + warp;
         const int e = __ldcg(ridx + pair);
@@ -435,7 +437,6 @@ sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restric
                     if (local[t]) f += __double2ll_rn(__ldcg(rw + j * top_k + t) * (double)part[t][i] * 1099511627776.0);
                 if (has_shared) f += __double2ll_rn((double)part[top_k][i] * 1099511627776.0);
                 if (push.world > 0) {
-                    const int slot = (int)(((const SzEpHeader*)push.buf[push.me])->epoch & 1ull);
                     for (int r = 0; r < push.world; r++)
                         sz_ep_slot(push.buf[r], push.world, push.row_elems, slot, push.me)[(size_t)j * H + b * 128 + i] = f;
                 } else {
