@@ -66,7 +66,33 @@ static __device__ long long sz_phase_t[16][16];
 #endif
 
 // Wait for the kernels this one depends on (no-op when launched without the PDL attribute).
+#ifdef SZ_PHASES
+// debug builds: block 0 of every kernel logs (source line of the wait, time before it, time after it) - a device-side timeline of a
+// pass, valid inside CUDA graphs too.  One log per translation unit; sz_timeline_read_<file> copies it out.
+static __device__ unsigned long long sz_tl[3 * 4096];
+static __device__ unsigned int sz_tl_n;
+__device__ __forceinline__ unsigned long long sz_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ void sz_pdl_wait_at(int line) {
+    const bool log = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && threadIdx.x == 0;
+    const unsigned long long t0 = log ? sz_gtime() : 0;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (log) {
+        const unsigned int i = atomicAdd(&sz_tl_n, 1u);
+        if (i < 4096) { sz_tl[3 * i] = (unsigned long long)line; sz_tl[3 * i + 1] = t0; sz_tl[3 * i + 2] = sz_gtime(); }
+    }
+}
+#define sz_pdl_wait() sz_pdl_wait_at(__LINE__)
+#define SZ_TIMELINE_READER(name)                                                                                                  \
+    extern "C" int sz_timeline_read_##name(unsigned long long* out, unsigned int* n, int reset) {                                 \
+        if (cudaMemcpyFromSymbol(n, sz_tl_n, 4) != cudaSuccess) return 1;                                                         \
+        if (cudaMemcpyFromSymbol(out, sz_tl, sizeof(unsigned long long) * 3 * 4096) != cudaSuccess) return 1;                     \
+        if (reset) { const unsigned int z = 0; if (cudaMemcpyToSymbol(sz_tl_n, &z, 4) != cudaSuccess) return 1; }                 \
+        return 0;                                                                                                                 \
+    }
+#else
 __device__ __forceinline__ void sz_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#define SZ_TIMELINE_READER(name)
+#endif
 // Let the next kernel on the stream begin its prologue.
 __device__ __forceinline__ void sz_pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -244,3 +244,5 @@ int sz_ep_p2p_finish(int m, int hidden, unsigned long long combine_blocks, float
                       (long long)SZ_MAX_VERIFY * hidden, combine_blocks, n, y));
     return SZ_OK;
 }
+
+SZ_TIMELINE_READER(ep)

@@ -21,85 +21,6 @@ __device__ __forceinline__ u32 sz_fkey(float v) {
 }
 __device__ __forceinline__ float sz_fkey_inv(u32 k) { return __uint_as_float((k & 0x80000000u) ? (k & 0x7fffffffu) : ~k); }
 
-// One row of the pass: max, top-k by (value descending, index ascending), weights.  A warp; the row's logits in registers, lane l
-// holds experts l + 32 q.  Each round takes the warp-wide best with two redux instructions (best key, then lowest index among
-// the lanes that hold it); only the winner's lane rescans its values.
-template <int NQ>
-__device__ __forceinline__ void sz_route_row(const float* __restrict__ logits_row, int ne, int k, int lane, int* sel_row, int32_t* ridx_row,
-                                             double* rw_row, int32_t* out_idx_row, double* out_w_row) {
-    float d[NQ];
-    float mx = -FLT_MAX;  // f32::MIN, forward.rs:1093
-#ifdef SZ_PHASES
-    const bool dbg = lane == 0 && (threadIdx.x >> 5) == 0;
-    if (dbg) sz_phase_t[3][0] = clock64();
-#endif
-#pragma unroll
-    for (int q = 0; q < NQ; q++) {
-        const int i = lane + 32 * q;
-        d[q] = i < ne ? __ldcg(logits_row + i) : -INFINITY;
-        if (i < ne) mx = fmaxf(mx, d[q]);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    u32 key[NQ];
-#pragma unroll
-    for (int q = 0; q < NQ; q++) key[q] = lane + 32 * q < ne ? sz_fkey(d[q] - mx) : 0u;  // in f32, as the reference subtracts before widening; 0 = absent
-    auto local_best = [&](u32& bk, int& bq) {  // best remaining key of the lane and its slot (lowest slot on ties)
-        u32 ck[4] = {0u, 0u, 0u, 0u};
-        int cq[4] = {NQ, NQ, NQ, NQ};
-#pragma unroll
-        for (int q = 0; q < NQ; q++)
-            if (key[q] > ck[q & 3]) { ck[q & 3] = key[q]; cq[q & 3] = q; }
-#pragma unroll
-        for (int c = 1; c < 4; c++)
-            if (ck[c] > ck[0] || (ck[c] == ck[0] && cq[c] < cq[0])) { ck[0] = ck[c]; cq[0] = cq[c]; }
-        bk = ck[0]; bq = cq[0];
-    };
-    u32 bk;
-    int bq;
-    local_best(bk, bq);
-#ifdef SZ_PHASES
-    if (dbg) sz_phase_t[3][1] = clock64();
-#endif
-    u32 mine = 0;
-    int my_e = 0;
-    for (int t = 0; t < k; t++) {
-        const u32 wk = __reduce_max_sync(0xffffffffu, bk);
-        const u32 cand = (bk == wk && bq < NQ) ? (u32)(lane + 32 * bq) : 0x7fffffffu;
-        const u32 wi = __reduce_min_sync(0xffffffffu, cand);
-        if (lane == t) { mine = wk; my_e = (int)wi; }
-        if ((int)(wi & 31u) == lane) {
-#pragma unroll
-            for (int q = 0; q < NQ; q++)
-                if (q == (int)(wi >> 5)) key[q] = 0u;
-            local_best(bk, bq);
-        }
-    }
-    // weights: softmax over all experts, then the chosen ones renormalised - the full sum cancels, so only the k chosen
-    // exponentials are needed: w_t = exp(d_t) / sum over ranks (in rank order) of exp(d_t')
-#ifdef SZ_PHASES
-    if (dbg) sz_phase_t[3][2] = clock64();
-#endif
-    const double ex = lane < k ? exp((double)sz_fkey_inv(mine)) : 0.0;
-#ifdef SZ_PHASES
-    if (dbg) sz_phase_t[3][3] = clock64() + (long long)(ex == 12345.0);
-#endif
-    double tz = 0.0;
-    for (int t = 0; t < k; t++) tz += __shfl_sync(0xffffffffu, ex, t);
-    if (lane < k) {
-        const double wv = ex / tz;
-        sel_row[lane] = my_e;
-        ridx_row[lane] = my_e;
-        rw_row[lane] = wv;
-        if (out_idx_row) out_idx_row[lane] = my_e;
-        if (out_w_row) out_w_row[lane] = wv;
-    }
-    __syncwarp();
-#ifdef SZ_PHASES
-    if (dbg) sz_phase_t[3][4] = clock64();
-#endif
-}
-
 // Sums N = 2^h values a lane over the 32 lanes of a warp.  While more than one value is left, a step at offset o halves them: the
 // lanes with bit o set keep the upper half and send the lower, the others the reverse, so N + N/2 + .. shuffles do the work of
 // 5 N.  Afterwards every lane holds the total of value number lane >> (5 - h) in v[0].
@@ -143,6 +64,12 @@ sz_route_kernel(const float* __restrict__ x, int H, const float* __restrict__ ro
     __shared__ u32 bitmap[SZ_MAX_EXPERTS / 32]; // experts chosen at all (and held here)
     __shared__ int sel[SZ_MAX_VERIFY * SZ_MAX_TOPK];
     __shared__ int s_last;
+    __shared__ float tk_red[SZ_ROUTE_THREADS / 32];
+    __shared__ u64 tk_max[SZ_ROUTE_THREADS];
+    __shared__ u64 tk_floor[SZ_MAX_VERIFY];
+    __shared__ int tk_cnt[SZ_MAX_VERIFY];
+    __shared__ u64 tk_cand[MP][SZ_MAX_TOPK * (SZ_MAX_EXPERTS / (SZ_ROUTE_THREADS / MP))];
+    __shared__ double tk_ex[SZ_MAX_VERIFY][SZ_MAX_TOPK];
     const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     const int ld = ne + 1;
     const int nrows = ne + (shared_router != nullptr ? 1 : 0);
@@ -224,12 +151,75 @@ sz_route_kernel(const float* __restrict__ x, int H, const float* __restrict__ ro
     __threadfence();
     SZ_PH();  // 4 ticket taken
 
-    for (int j = warp; j < M; j += SZ_ROUTE_THREADS / 32) {
-        int32_t* oi = out_idx ? out_idx + j * k : nullptr;
-        double* ow = out_w ? out_w + j * k : nullptr;
-        if (ne <= 256) sz_route_row<8>(logits + (size_t)j * ld, ne, k, lane, sel + j * SZ_MAX_TOPK, ridx + j * k, rw + j * k, oi, ow);
-        else if (ne <= 512) sz_route_row<16>(logits + (size_t)j * ld, ne, k, lane, sel + j * SZ_MAX_TOPK, ridx + j * k, rw + j * k, oi, ow);
-        else sz_route_row<32>(logits + (size_t)j * ld, ne, k, lane, sel + j * SZ_MAX_TOPK, ridx + j * k, rw + j * k, oi, ow);
+    // ---- top-k of every row, all rows at once: G = 256 / MP threads a row, a thread owns the experts g, g + G, ..  The k-th best of
+    // the G per-thread maxima is a floor under the k-th best logit, so only values at or above it (at most k threads' worth, typically
+    // a dozen) can be chosen; those are ranked by counting.  Keys are (orderable f32 image of logit - max, ~index): one unsigned
+    // comparison orders by value descending, then index ascending.  Every loop is a short rolled loop.
+    {
+        constexpr int G = SZ_ROUTE_THREADS / MP;          // threads a row
+        constexpr int NK = SZ_MAX_EXPERTS / G;            // most keys a thread owns
+        const int j = t / G, g = t % G;
+        const bool live_row = j < M;
+        float lv[NK];
+        float mxv = -FLT_MAX;  // f32::MIN, forward.rs:1093
+#pragma unroll
+        for (int q = 0; q < NK; q++) {
+            const int e = g + G * q;
+            lv[q] = (live_row && e < ne) ? __ldcg(logits + (size_t)j * ld + e) : -INFINITY;
+            if (live_row && e < ne) mxv = fmaxf(mxv, lv[q]);
+        }
+        // the row's maximum: over the thread's values, the warp, then the warps of the row
+        for (int o = 16; o > 0; o >>= 1) mxv = fmaxf(mxv, __shfl_xor_sync(0xffffffffu, mxv, o));
+        if (lane == 0) tk_red[warp] = mxv;
+        __syncthreads();
+        constexpr int WPR = G / 32 > 0 ? G / 32 : 1;      // warps a row
+        mxv = tk_red[(t / 32 / WPR) * WPR];
+        for (int q = 1; q < WPR; q++) mxv = fmaxf(mxv, tk_red[(t / 32 / WPR) * WPR + q]);
+        u64 key[NK];
+        u64 best = 0ull;
+#pragma unroll
+        for (int q = 0; q < NK; q++) {
+            const int e = g + G * q;
+            key[q] = (live_row && e < ne) ? (((u64)sz_fkey(lv[q] - mxv) << 32) | (u64)(0xffffffffu - (u32)e)) : 0ull;  // in f32, as the reference
+            best = key[q] > best ? key[q] : best;
+        }
+        tk_max[t] = best;
+        if (g == 0) tk_cnt[j] = 0;
+        __syncthreads();
+        int rank = 0;
+#pragma unroll 4
+        for (int i = 0; i < G; i++) rank += tk_max[j * G + i] > best;
+        if (live_row && rank == k - 1) tk_floor[j] = best;   // keys are distinct, so exactly one thread has this rank
+        __syncthreads();
+        const u64 fl = live_row ? tk_floor[j] : ~0ull;
+#pragma unroll
+        for (int q = 0; q < NK; q++)
+            if (key[q] >= fl && key[q] != 0ull) tk_cand[j][atomicAdd(&tk_cnt[j], 1)] = key[q];
+        __syncthreads();
+        const int C = live_row ? tk_cnt[j] : 0;              // k <= C <= k * NK
+        for (int i = g; i < C; i += G) {
+            const u64 mine = tk_cand[j][i];
+            int r = 0;
+#pragma unroll 4
+            for (int q = 0; q < C; q++) r += tk_cand[j][q] > mine;
+            if (r < k) {
+                const int e = (int)(0xffffffffu - (u32)mine);
+                sel[j * SZ_MAX_TOPK + r] = e;
+                ridx[j * k + r] = e;
+                if (out_idx) out_idx[j * k + r] = e;
+                tk_ex[j][r] = exp((double)sz_fkey_inv((u32)(mine >> 32)));
+            }
+        }
+        __syncthreads();
+        // weights: softmax over all experts, then the chosen ones renormalised - the full sum cancels, so only the k chosen
+        // exponentials are needed: w_r = exp(d_r) / sum over ranks (in rank order) of exp(d_r')
+        if (live_row && g < k) {
+            double tz = 0.0;
+            for (int r = 0; r < k; r++) tz += tk_ex[j][r];
+            const double wv = tk_ex[j][g] / tz;
+            rw[j * k + g] = wv;
+            if (out_w) out_w[j * k + g] = wv;
+        }
     }
     __syncthreads();
     SZ_PH();  // 5 rows routed
@@ -923,3 +913,5 @@ extern "C" int sz_moe_verify_host(const sz_moe_layer* L, const float* x_host, in
 #ifdef SZ_PHASES
 extern "C" int sz_phase_read_moe(long long* out) { return cudaMemcpyFromSymbol(out, sz_phase_t, sizeof(long long) * 16 * 16) == cudaSuccess ? 0 : 1; }
 #endif
+
+SZ_TIMELINE_READER(moe)

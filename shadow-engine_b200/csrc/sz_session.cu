@@ -822,3 +822,5 @@ extern "C" int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, 
 #ifdef SZ_PHASES
 extern "C" int sz_phase_read_session(long long* out) { return cudaMemcpyFromSymbol(out, sz_phase_t, sizeof(long long) * 16 * 16) == cudaSuccess ? 0 : 1; }
 #endif
+
+SZ_TIMELINE_READER(session)
