@@ -54,6 +54,38 @@ struct SzExl3Tile {
     static constexpr int NA = (SPAN + 31) / 32 + 1;  // words of the span once it starts at bit 0, plus one to peek
     static constexpr int NW = NA + 1;                // words loaded: the span at any bit offset
 
+    // What depends on the lane only: the (wrapped) word offsets of its span and the bit offset inside the first word.  A kernel that
+    // decodes many tiles computes this once.
+    struct Lane { int wi[NW]; int off; };
+    __device__ __forceinline__ static Lane lane_setup(int lane) {
+        Lane L;
+        const int sb = ((8 * lane + 1) * K - 16 + RING) % RING;
+        const int w0 = sb >> 5;
+        L.off = sb & 31;
+#pragma unroll
+        for (int i = 0; i < NW; i++) {
+            int wi = w0 + i;
+            wi = wi >= WORDS ? wi - WORDS : wi;
+            wi = wi >= WORDS ? wi - WORDS : wi;
+            L.wi[i] = wi;
+        }
+        return L;
+    }
+    __device__ __forceinline__ static void states_pre(const u32* tile, const Lane& L, u32* st) {
+        u32 w[NW];
+#pragma unroll
+        for (int i = 0; i < NW; i++) w[i] = tile[L.wi[i]];
+        u32 a[NA];
+#pragma unroll
+        for (int i = 0; i < NA; i++) a[i] = __funnelshift_l(w[i + 1], w[i], L.off);
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int pos = j * K;
+            const int wi = pos >> 5, sh = pos & 31;
+            st[j] = (sh <= 16 ? (a[wi] >> (16 - sh)) : __funnelshift_l(a[wi + 1], a[wi], sh) >> 16) & 0xffffu;
+        }
+    }
+
     // the 8 states of lane `lane`; `tile` points at the tile's words (4-byte aligned, any address space)
     __device__ __forceinline__ static void states(const u32* tile, int lane, u32* st) {
         const int sb = ((8 * lane + 1) * K - 16 + RING) % RING;  // first bit of window 0

@@ -37,18 +37,40 @@ __device__ __forceinline__ void sz_mma16816(float* c, const u32* a, u32 b0, u32 
 
 // The lane's 8 weights of a tile as the A fragment (outputs x inputs) of m16n8k16: a0 = (out g, in 2q..), a1 = (out g + 8, in 2q..),
 // a2 = (out g, in 2q + 8..), a3 = (out g + 8, in 2q + 8..) with g = lane / 4, q = lane % 4: tile positions j = {0,1}, {4,5}, {2,3}, {6,7}.
+// The codebook's byte sum (exl3.rs:66-86: the four bytes of state * 0x83DCD12D, plus 0x6400) for four states at once on the integer
+// tensor pipe: the products are the A operand of mma.m16n8k32.u8 as they stand (a register = one product = four k slots), the B
+// operand is a constant 0/1 matrix that routes each register's four bytes to an output column of the same lane, and the
+// accumulator starts at 0x6400.  c[i] = 0x6400 + bytes of x[i].  Two of these replace eight dp4a in the issue stream.
+__device__ __forceinline__ void sz_bytesum4(const u32* x, u32 sel0, u32 sel1, u32* c) {
+    c[0] = 0x6400u; c[1] = 0x6400u; c[2] = 0x6400u; c[3] = 0x6400u;
+    // A registers: a0 = (row g, k 4q..), a1 = (row g + 8, k 4q..), a2 = (row g, k 16 + 4q..), a3 = (row g + 8, k 16 + 4q..)
+    // C registers: c0 = (row g, col 2q), c1 = (row g, col 2q + 1), c2 = (row g + 8, col 2q), c3 = (row g + 8, col 2q + 1)
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(x[0]), "r"(x[2]), "r"(x[1]), "r"(x[3]), "r"(sel0), "r"(sel1));
+}
+
 template <int K>
-__device__ __forceinline__ void sz_exl3_afrag(const u32* tile, int lane, u32* a) {
+__device__ __forceinline__ void sz_exl3_afrag(const u32* tile, int lane, const typename SzExl3Tile<K>::Lane& LS, u32* a) {
     u32 st[8];
-    SzExl3Tile<K>::states(tile, lane, st);
+    SzExl3Tile<K>::states_pre(tile, LS, st);
     const __half2 kinv = __halves2half2(__ushort_as_half((u16)0x1eee), __ushort_as_half((u16)0x1eee));
     const __half2 kbias = __halves2half2(__ushort_as_half((u16)0xc931), __ushort_as_half((u16)0xc931));
+    // B operand (k x n, column n = lane / 4 of this lane, k rows 4q.. in the first register, 16 + 4q.. in the second): column 2q'
+    // takes the bytes k = 4q'.. (register a0 / a1 of lane q'), column 2q' + 1 the bytes k = 16 + 4q'.. (a2 / a3)
+    const int n = lane >> 2, q = lane & 3;
+    const u32 sel0 = ((n & 1) == 0 && (n >> 1) == q) ? 0x01010101u : 0u;
+    const u32 sel1 = ((n & 1) == 1 && (n >> 1) == q) ? 0x01010101u : 0u;
+    u32 x[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) x[i] = st[i] * 0x83DCD12Du;
+    u32 c[8];
+    sz_bytesum4(x, sel0, sel1, c);          // c0 = sum(x0), c1 = sum(x1), c2 = sum(x2), c3 = sum(x3)
+    sz_bytesum4(x + 4, sel0, sel1, c + 4);
     u32 p[4];
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        const u32 s0 = __dp4a(st[2 * i] * 0x83DCD12Du, 0x01010101u, 0x6400u);
-        const u32 s1 = __dp4a(st[2 * i + 1] * 0x83DCD12Du, 0x01010101u, 0x6400u);
-        const u32 packed = (s1 << 16) | s0;
+        const u32 packed = __byte_perm(c[2 * i], c[2 * i + 1], 0x5410);
         const __half2 h = __hfma2(*(const __half2*)&packed, kinv, kbias);
         p[i] = *(const u32*)&h;
     }
@@ -94,14 +116,17 @@ template <int K, int NTC>
 __device__ __forceinline__ void sz_x3_compute(const u8* stage, const uint4* frag, int warp, int lane, float (*c)[4]) {
 #pragma unroll
     for (int tc = 0; tc < NTC; tc++) { c[tc][0] = 0.f; c[tc][1] = 0.f; c[tc][2] = 0.f; c[tc][3] = 0.f; }
-#pragma unroll 2
+    const typename SzExl3Tile<K>::Lane LS = SzExl3Tile<K>::lane_setup(lane);
+    const u8* wbase = stage + (size_t)(warp * NTC) * (32 * K);
+    const uint4* fl = frag + lane;
+#pragma unroll
     for (int kr = 0; kr < 8; kr++) {
-        const uint4 b = frag[kr * 32 + lane];
+        const uint4 b = fl[kr * 32];
 #pragma unroll
         for (int tc = 0; tc < NTC; tc++) {
-            const u32* tile = (const u32*)(stage + (size_t)(kr * 8 * NTC + warp * NTC + tc) * (32 * K));
+            const u32* tile = (const u32*)(wbase + (size_t)(kr * 8 * NTC + tc) * (32 * K));
             u32 a[4];
-            sz_exl3_afrag<K>(tile, lane, a);
+            sz_exl3_afrag<K>(tile, lane, LS, a);
             sz_mma16816(c[tc], a, b.x, b.y);
             sz_mma16816(c[tc], a, b.z, b.w);
         }
@@ -209,10 +234,13 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
         SzX3Unit nxt = cur;
         float v[4];
         if (i + 1 < count) { nxt = unit(u0 + i + 1); prep_load(nxt, v); }
+        if (i == 1) SZ_PH();  // unit 1: start
         if (!sz_mbar_wait(&bars[i % SZ_X3_STAGES], (i / SZ_X3_STAGES) & 1)) failed = 1;
+        if (i == 1) SZ_PH();  // unit 1: data arrived
         float c[NTC][4];
         if (!failed) {
             sz_x3_compute<K, NTC>(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, frags + (i & 1) * 256, warp, lane, c);
+            if (i == 1) SZ_PH();  // unit 1: decoded and multiplied
             const int mat = cur.in_off >> 30, q = lane & 3, g8 = lane >> 2;
 #pragma unroll
             for (int tt = 0; tt < 2; tt++) {
@@ -228,7 +256,9 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
                 }
             }
         }
+        if (i == 1) SZ_PH();  // unit 1: atomics issued
         if (i + 1 < count) sz_x3_store_frag(frags + ((i + 1) & 1) * 256, warp, nxt.n, v, lane);
+        if (i == 1) SZ_PH();  // unit 1: next fragments stored
         cur = nxt;
         if (__syncthreads_or(failed)) { failed = 1; break; }
         SZ_PH();  // 3.. a unit
