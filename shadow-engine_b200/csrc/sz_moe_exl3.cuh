@@ -175,6 +175,9 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     plan = sz_plan_stage(plan, &splan);
     __syncthreads();
     SZ_PH();  // 1 after wait
+#ifdef SZ_PHASES
+    if (threadIdx.x == 0 && blockIdx.x == 0) { sz_phase_t[5][4] = (long long)sz_gtime(); sz_phase_t[5][0] = 0; sz_phase_t[5][1] = 0x7fffffffffffffffll; sz_phase_t[5][2] = 0; }
+#endif
     const int D = plan ? plan->n_groups : 0;
     const int NG = D + (sh_gate ? 1 : 0);
     const int NS = H / 128;
@@ -265,6 +268,15 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     }
     if (failed && threadIdx.x == 0) atomicExch(&ctrl[1], 1u);
     SZ_PH_FLUSH(4, blockIdx.x == 7);
+#ifdef SZ_PHASES
+    if (threadIdx.x == 0) {  // spread of the blocks' end times, and of their unit counts
+        const unsigned long long te = sz_gtime();
+        atomicMax((unsigned long long*)&sz_phase_t[5][0], te);
+        atomicMin((unsigned long long*)&sz_phase_t[5][1], te);
+        atomicMax((unsigned long long*)&sz_phase_t[5][2], (unsigned long long)count);
+        if (blockIdx.x == 0) sz_phase_t[5][3] = (long long)te;
+    }
+#endif
 }
 
 // ---- down ---------------------------------------------------------------------------------------------------------------------------
