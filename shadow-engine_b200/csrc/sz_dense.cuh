@@ -308,7 +308,7 @@ struct SzDenseQ8Cfg {
 // widths, so eight lanes reading the same block of eight different rows would hit one bank eight times over.  Every row of a unit
 // is therefore its own bulk copy to a padded stride (rbp), and the rows of the pass are padded the same way (xsp).
 // grid: any; block 256; dynamic shared memory: 64 (barriers) + 4096 (reduction) + 2 * m * xsp * 2 (x as f16 hi | lo) + NS * unit_bytes
-__global__ void __launch_bounds__(256, 2) sz_dense_q8_kernel(const SzDenseArgs a, const SzDenseQ8Cfg c) {
+static __global__ void __launch_bounds__(256, 2) sz_dense_q8_kernel(const SzDenseArgs a, const SzDenseQ8Cfg c) {
     extern __shared__ __align__(128) u8 smem[];
     u64* bars = (u64*)smem;
     float* red = (float*)(smem + 64);                       // [8 warps][16 rows][8 rows of the pass]

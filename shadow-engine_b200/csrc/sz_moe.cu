@@ -3,6 +3,7 @@
 // the softmax in f64, expert dot products accumulated in f32, the weighted sum over experts in f64 in rank order.
 #include "sz_moe.cuh"
 #include "sz_moe_exl3.cuh"
+#include "sz_moe_blk.cuh"
 
 #include <float.h>
 #include <stdlib.h>
@@ -653,9 +654,58 @@ extern "C" int sz_moe_launches(const sz_moe_layer* L) {
     return (L->shared_ff > 0 ? 6 : 4) + ep;
 }
 
+static int sz_sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+// The streaming block-format kernels.  Returns SZ_E_TYPE (without setting an error text) when the shape is not one they take.
+template <int TYPE, bool DOWN>
+static int sz_launch_blk(cudaStream_t st, const SzPlan* plan, int groups, const u8* w0, u64 s0, const u8* w1, u64 s1, const float* in, int n_in,
+                         int n_out, float* out, u32* ctrl) {
+    constexpr int RT = DOWN ? 4 : 1;
+    if (n_in % 256 || n_out % (16 * RT) || groups < 1) return SZ_E_TYPE;
+    const size_t rb = TYPE == SZ_TYPE_Q8_0 ? (size_t)(n_in / 32) * 34 : (size_t)(n_in / 256) * 110;
+    SzBlkCfg c = {};
+    c.by_row = rb % 16 == 0;
+    int rbp = (int)rb;
+    if (c.by_row) while (((rbp / 4) % 32) % 8 != 4) rbp += 16;   // consecutive rows 4 (mod 8) words apart in bank space
+    c.rbp = rbp;
+    c.unit_bytes = (DOWN ? 1 : 2) * 16 * RT * rbp;
+    int xsp = n_in;
+    while (((xsp / 2) % 32) != 16) xsp += 8;
+    c.xsp = xsp;
+    c.slices = n_out / (16 * RT);
+    const size_t fixed = 64 + 2048 + 4096 + 16384 + (size_t)2 * SZ_MAX_VERIFY * xsp * 2;
+    const size_t budget = 220 * 1024;
+    if (fixed + 2 * (size_t)c.unit_bytes > budget) return SZ_E_TYPE;
+    int NS = (int)((budget - fixed) / c.unit_bytes);
+    c.NS = NS > 4 ? 4 : NS;
+    const size_t smem = fixed + (size_t)c.NS * c.unit_bytes;
+    static bool set = false;
+    if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_blk_ffn_kernel<TYPE, DOWN, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024)); set = true; }
+    const int per_sm = smem + 4096 <= 110 * 1024 ? 2 : 1;
+    int blocks = sz_sm_count() * per_sm;
+    const long long units = (long long)groups * c.slices;
+    if (blocks > units) blocks = (int)units;
+    SZ_CUDA(sz_launch(DOWN ? "down_blk" : "gateup_blk", sz_blk_ffn_kernel<TYPE, DOWN, RT>, dim3(blocks), dim3(256), smem, st, true, plan, w0, s0, w1, s1,
+                      in, n_in, n_out, out, c, ctrl));
+    return SZ_OK;
+}
+
 template <int TYPE>
 static int sz_launch_rows(cudaStream_t st, const SzPlan* plan, int groups, const u8* gate, u64 gs, const u8* up, u64 us, const u8* down,
-                          u64 ds, const float* x, int H, int FF, float* act, float* eo, bool down_pass) {
+                          u64 ds, const float* x, int H, int FF, float* act, float* eo, bool down_pass, u32* ctrl) {
+    static const bool generic_only = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;
+    if (!generic_only) {  // the streaming tensor-pipe kernels, where the shapes fit them
+        int rc = down_pass ? sz_launch_blk<TYPE, true>(st, plan, groups, down, ds, nullptr, 0, act, FF, H, eo, ctrl)
+                           : sz_launch_blk<TYPE, false>(st, plan, groups, gate, gs, up, us, x, H, FF, act, ctrl);
+        if (rc != SZ_E_TYPE) return rc;  // SZ_E_TYPE: not a shape for them
+    }
     const size_t smem = 2048 + (size_t)SZ_MAX_VERIFY * (down_pass ? FF : H) * 4;
     if (!down_pass) {
         static bool set = false;
@@ -684,10 +734,10 @@ static int sz_launch_exl3(cudaStream_t st, const SzPlan* plan, int groups, const
 
 // One expert FFN pass (gate/up then down) for the groups of `plan`.
 static int sz_ffn(cudaStream_t st, int type, const SzPlan* plan, int groups, u64 gate, u64 gs, u64 up, u64 us, u64 down, u64 ds,
-                  const float* x, int H, int FF, float* g, float* u, float* eo, bool down_pass) {
+                  const float* x, int H, int FF, float* g, float* u, float* eo, bool down_pass, u32* ctrl) {
     const u8 *pg = (const u8*)gate, *pu = (const u8*)up, *pd = (const u8*)down;
-    if (type == SZ_TYPE_Q8_0) return sz_launch_rows<SZ_TYPE_Q8_0>(st, plan, groups, pg, gs, pu, us, pd, ds, x, H, FF, g, eo, down_pass);
-    if (type == SZ_TYPE_IQ3_S) return sz_launch_rows<SZ_TYPE_IQ3_S>(st, plan, groups, pg, gs, pu, us, pd, ds, x, H, FF, g, eo, down_pass);
+    if (type == SZ_TYPE_Q8_0) return sz_launch_rows<SZ_TYPE_Q8_0>(st, plan, groups, pg, gs, pu, us, pd, ds, x, H, FF, g, eo, down_pass, ctrl);
+    if (type == SZ_TYPE_IQ3_S) return sz_launch_rows<SZ_TYPE_IQ3_S>(st, plan, groups, pg, gs, pu, us, pd, ds, x, H, FF, g, eo, down_pass, ctrl);
 #define SZ_EXL3_CASE(KK)                                                                                                        \
     case KK:                                                                                                                    \
         return down_pass ? sz_launch_exl3<KK>(st, plan, groups, pd, ds, nullptr, 0, g, u, 1, FF, H, eo, nullptr)               \
@@ -699,14 +749,6 @@ static int sz_ffn(cudaStream_t st, int type, const SzPlan* plan, int groups, u64
     return sz_fail(SZ_E_TYPE, "no kernel for tensor type %d", type);
 }
 
-static int sz_sm_count() {
-    static int n = 0;
-    if (!n) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    }
-    return n;
-}
 
 template <int K, int NTC>
 static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const SzPlan* plan, const float* x, long long* acc_gu, long long* acc_d,
@@ -805,8 +847,8 @@ static int sz_moe_run(const sz_moe_layer* L0, uint64_t x, int m, float* y, long 
         long long *acc_gu = (long long*)(base + S.acc_gu), *acc_d = (long long*)(base + S.acc_d);
         const bool sh_fused = fast.shared_fused && shared;
         if (shared && !sh_fused) {
-            if ((rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, false))) return rc;
-            if ((rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true))) return rc;
+            if ((rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, false, ctrl))) return rc;
+            if ((rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true, ctrl))) return rc;
         }
         if ((rc = sz_x3_launch(st, L, m, plan, xp, acc_gu, acc_d, ctrl, sh_fused))) return rc;
         SZ_CUDA(sz_launch("combine_exl3", sz_x3_combine_kernel, dim3(m * (H / 128)), dim3((L->top_k + 1) * 32), 0, st, true, (const long long*)acc_d,
@@ -817,13 +859,13 @@ static int sz_moe_run(const sz_moe_layer* L0, uint64_t x, int m, float* y, long 
         return SZ_OK;
     }
     if ((rc = sz_ffn(st, L->expert_type, plan, groups, L->gate, L->gate_stride, L->up, L->up_stride, L->down, L->down_stride, xp, H, FF, g, u,
-                     eo, false)))
+                     eo, false, ctrl)))
         return rc;
-    if (shared && (rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, false))) return rc;
+    if (shared && (rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, false, ctrl))) return rc;
     if ((rc = sz_ffn(st, L->expert_type, plan, groups, L->gate, L->gate_stride, L->up, L->up_stride, L->down, L->down_stride, xp, H, FF, g, u,
-                     eo, true)))
+                     eo, true, ctrl)))
         return rc;
-    if (shared && (rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true))) return rc;
+    if (shared && (rc = sz_ffn(st, L->shared_type, plan_sh, 1, L->sh_gate, 0, L->sh_up, 0, L->sh_down, 0, xp, H, SF, sg, su, so, true, ctrl))) return rc;
     SZ_CUDA(sz_launch("combine", sz_combine_kernel, dim3((H + 255) / 256, m), dim3(256), 0, st, true, (const float*)eo, (const int32_t*)ridx,
                       (const double*)rw, (const float*)so, (const float*)logits, (int)L->n_expert, (int)L->top_k, H, shared ? 1 : 0, y, y_fix, e_lo, e_hi, push));
     if (combine_blocks) *combine_blocks = (unsigned long long)((H + 255) / 256) * m;
