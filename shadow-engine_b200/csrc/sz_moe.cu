@@ -680,14 +680,14 @@ static int sz_launch_blk(cudaStream_t st, const SzPlan* plan, int groups, const 
     while (((xsp / 2) % 32) != 16) xsp += 8;
     c.xsp = xsp;
     c.slices = n_out / (16 * RT);
-    const size_t fixed = 64 + 2048 + 4096 + 16384 + (size_t)2 * SZ_MAX_VERIFY * xsp * 2;
-    const size_t budget = 220 * 1024;
+    const size_t fixed = 64 + 2048 + 4096 + (size_t)(DOWN ? 1 : 2) * RT * 4096 + (size_t)2 * SZ_MAX_VERIFY * xsp * 2;
+    const size_t budget = 224 * 1024;
     if (fixed + 2 * (size_t)c.unit_bytes > budget) return SZ_E_TYPE;
     int NS = (int)((budget - fixed) / c.unit_bytes);
     c.NS = NS > 4 ? 4 : NS;
     const size_t smem = fixed + (size_t)c.NS * c.unit_bytes;
     static bool set = false;
-    if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_blk_ffn_kernel<TYPE, DOWN, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024)); set = true; }
+    if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_blk_ffn_kernel<TYPE, DOWN, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024)); set = true; }
     const int per_sm = smem + 4096 <= 110 * 1024 ? 2 : 1;
     int blocks = sz_sm_count() * per_sm;
     const long long units = (long long)groups * c.slices;

@@ -62,7 +62,7 @@ __device__ __forceinline__ void sz_blk_frag(const u8* r0, const u8* r1, int blk,
 // grid: any; block 256.  DOWN = false: out[pair][r] = silu(gate_r . x_row) * (up_r . x_row) with x = in[rows of the group]; true:
 // out[pair][r] = down_r . in[pair].  n_in: columns (a multiple of 256); n_out: rows of the matrices (a multiple of 16).
 // RT: 16-row tiles of a unit (the down matrices have short rows - FF columns - so a unit takes several tiles to be worth its barriers).
-// dynamic shared memory: 64 (barriers) | 2048 (IQ3_S grid) | 4096 (sign masks) | 16384 (reduction) | 2 * 8 * xsp * 2 (B operand) | NS * unit_bytes
+// dynamic shared memory: 64 (barriers) | 2048 (IQ3_S grid) | 4096 (sign masks) | NM * RT * 4096 (reduction) | 2 * 8 * xsp * 2 (B operand) | NS * unit_bytes
 template <int TYPE, bool DOWN, int RT>
 __global__ void __launch_bounds__(256)
 sz_blk_ffn_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u64 stride0, const u8* __restrict__ w1, u64 stride1,
@@ -75,7 +75,7 @@ sz_blk_ffn_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ w0, u6
     u32* grid = (u32*)(smem + 64);
     uint4* slut = (uint4*)(smem + 64 + 2048);
     float* red = (float*)(smem + 64 + 2048 + 4096);           // [NM * RT][8 warps][16 rows][8 group rows]
-    __half* xhi = (__half*)(smem + 64 + 2048 + 4096 + 16384); // [8][xsp]
+    __half* xhi = (__half*)(smem + 64 + 2048 + 4096 + NM * RT * 4096); // [8][xsp]
     __half* xlo = xhi + (size_t)SZ_MAX_VERIFY * c.xsp;
     u8* stages = (u8*)(xlo + (size_t)SZ_MAX_VERIFY * c.xsp);
     __shared__ __align__(16) SzPlan splan;

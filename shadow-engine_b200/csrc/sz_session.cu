@@ -481,7 +481,7 @@ static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bo
 // The DeltaNet scan: the pass of one layer (l >= 0: all m rows, with outputs) or the replay of a commit (l < 0: every layer in one
 // launch, the kept rows only, decided on the device).
 template <int D, int PARTS>
-static int sz_scan_launch(sz_session* s, cudaStream_t st, int l, int m) {
+static int sz_scan_launch(sz_session* s, cudaStream_t st, int l, int m, const SzDeltaPrep& pp) {
     const sz_model_config& c = s->model.cfg;
     const int64_t kd = (int64_t)c.ssm_k_heads * D, vd = (int64_t)c.ssm_v_heads * D, ch = 2 * kd + vd;
     const int64_t Sl = (int64_t)c.ssm_v_heads * D * D;
@@ -493,13 +493,13 @@ static int sz_scan_launch(sz_session* s, cudaStream_t st, int l, int m) {
     SZ_CUDA(sz_launch(l >= 0 ? "delta_scan" : "delta_replay", sz_delta_scan_kernel<D, PARTS>, dim3(c.ssm_v_heads, l >= 0 ? 1 : s->n_delta),
                       dim3(D * PARTS), 0, st, true, xc, beta, decay, (const float*)s->d_z, nw, (const float*)(s->S[0] + di * Sl),
                       (const float*)(s->S[1] + di * Sl), s->S[0] + di * Sl, s->S[1] + di * Sl, (const int32_t*)s->state, (const int32_t*)s->res,
-                      (int)c.ssm_k_heads, (int)c.ssm_v_heads, m, c.eps, l >= 0 ? s->d_og : (float*)nullptr));
+                      (int)c.ssm_k_heads, (int)c.ssm_v_heads, m, c.eps, l >= 0 ? s->d_og : (float*)nullptr, pp));
     return SZ_OK;
 }
 
-static int sz_scan(sz_session* s, cudaStream_t st, int l, int m) {
-    if (s->model.cfg.ssm_head_dim == 128) return sz_scan_launch<128, 2>(s, st, l, m);
-    return sz_scan_launch<64, 1>(s, st, l, m);
+static int sz_scan(sz_session* s, cudaStream_t st, int l, int m, const SzDeltaPrep& pp) {
+    if (s->model.cfg.ssm_head_dim == 128) return sz_scan_launch<128, 2>(s, st, l, m, pp);
+    return sz_scan_launch<64, 1>(s, st, l, m, pp);
 }
 
 static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
@@ -521,10 +521,18 @@ static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
     int rc = sz_dense_launch(a, st, "delta_proj");
     if (rc) return rc;
     const int64_t cl = (int64_t)(c.conv_k - 1) * ch;
-    SZ_CUDA(sz_launch("delta_prep", sz_delta_prep_kernel, dim3((unsigned)((ch + 255) / 256), m), dim3(256), 0, st, true, (const float*)xin, (const float*)(s->conv[0] + di * cl),
-                      (const float*)(s->conv[1] + di * cl), (const int32_t*)s->state, (const float*)L.ssm_conv1d.data, (const float*)s->d_b,
-                      (const float*)s->d_a, (const float*)L.ssm_a.data, (const float*)L.ssm_dt_bias.data, kh, vh, d, (int)c.conv_k, xc, beta, decay));
-    if ((rc = sz_scan(s, st, l, m))) return rc;
+    static const bool split_prep = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;
+    SzDeltaPrep pp = {};
+    if (split_prep) {  // the front end as a kernel of its own (the second implementation the fused one is checked against)
+        SZ_CUDA(sz_launch("delta_prep", sz_delta_prep_kernel, dim3((unsigned)((ch + 255) / 256), m), dim3(256), 0, st, true, (const float*)xin, (const float*)(s->conv[0] + di * cl),
+                          (const float*)(s->conv[1] + di * cl), (const int32_t*)s->state, (const float*)L.ssm_conv1d.data, (const float*)s->d_b,
+                          (const float*)s->d_a, (const float*)L.ssm_a.data, (const float*)L.ssm_dt_bias.data, kh, vh, d, (int)c.conv_k, xc, beta, decay));
+    } else {
+        pp.xin = xin; pp.conv0 = s->conv[0] + di * cl; pp.conv1 = s->conv[1] + di * cl; pp.cw = (const float*)L.ssm_conv1d.data;
+        pp.b = s->d_b; pp.a = s->d_a; pp.a_log = (const float*)L.ssm_a.data; pp.dt = (const float*)L.ssm_dt_bias.data;
+        pp.xc = xc; pp.beta = beta; pp.decay = decay; pp.k = (int)c.conv_k;
+    }
+    if ((rc = sz_scan(s, st, l, m, pp))) return rc;
     SzDenseArgs b = {};
     b.x = s->d_og; b.xstride = (int)vd; b.cols = (int)vd; b.m = m; b.n_jobs = 1;
     b.job[0] = sz_job(L.ssm_out, s->y, H);
@@ -640,7 +648,7 @@ static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
 static int sz_commit_device(sz_session* s, cudaStream_t st, int m) {
     const sz_model_config& c = s->model.cfg;
     if (s->n_delta > 0) {
-        const int rc = sz_scan(s, st, -1, m);
+        const int rc = sz_scan(s, st, -1, m, SzDeltaPrep());
         if (rc) return rc;
         const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd;
         SZ_CUDA(sz_launch("conv_commit", sz_conv_commit_kernel, dim3(c.conv_k - 1, s->n_delta), dim3(256), 0, st, true, (const float*)s->conv[0],

@@ -403,12 +403,30 @@ __global__ void sz_state_update_kernel(int32_t* __restrict__ state, const int32_
 // the gated, normalised outputs (the pass itself, one layer: blockIdx.y = 0 and the pointers are that layer's).  With og == null it
 // is the replay of a commit: layer blockIdx.y of every per-layer array, only the res[0] kept rows, and nothing at all when every
 // row was kept (the pass already wrote that state) or none was.
+// In the pass itself (og != null) the block also does the front end for the channels it needs - q and k of its key head, v of its
+// own head: causal conv + SiLU, L2 norms, beta and decay (what sz_delta_prep_kernel does for a whole row) - so the layer needs no
+// launch between the projections and the scan.  It leaves the conv outputs, beta and decay where the replay of a commit reads them.
+struct SzDeltaPrep {
+    const float* xin;     // [m][ch] raw projections of this layer (null: the front end already ran as a kernel of its own)
+    const float* conv0;   // (k - 1) x ch carried rows, two buffers
+    const float* conv1;
+    const float* cw;      // [ch][k] conv taps
+    const float* b;       // [m][vh]
+    const float* a;       // [m][vh]
+    const float* a_log;   // [vh]
+    const float* dt;      // [vh]
+    float* xc;            // [m][ch] out
+    float* beta;          // [m][vh] out
+    float* decay;         // [m][vh] out
+    int k;
+};
+
 template <int D, int PARTS>
 __global__ void __launch_bounds__(D * PARTS)
 sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__ beta_all, const float* __restrict__ decay_all,
                      const float* __restrict__ z, const float* __restrict__ norm_w, const float* __restrict__ S0, const float* __restrict__ S1,
                      float* __restrict__ O0, float* __restrict__ O1, const int32_t* __restrict__ state, const int32_t* __restrict__ res, int kh,
-                     int vh, int m, float eps, float* __restrict__ og) {
+                     int vh, int m, float eps, float* __restrict__ og, const SzDeltaPrep pp) {
     constexpr int NI = D / PARTS;
     constexpr int RUN = NI < 16 ? NI : 16;  // sums run in f32 over 16 terms and the runs are added in f64, as the reference's exact
                                             // GPU scan does (kernels/forward.cu:991-1013): a conversion to f64 per term would
@@ -417,6 +435,8 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
     __shared__ double part[PARTS][D];
     __shared__ float ofs[SZ_MAX_VERIFY][D];
     __shared__ double rrs[SZ_MAX_VERIFY];
+    __shared__ float pbuf[SZ_MAX_VERIFY][3][D];   // the rows' q, k, v after the front end
+    __shared__ float sbeta[SZ_MAX_VERIFY], sdecay[SZ_MAX_VERIFY];
     const int hd = blockIdx.x, di = blockIdx.y;
     const int col = threadIdx.x % D, pt = threadIdx.x / D;
     const int kx = hd % kh;  // value heads are tiled over the key heads (forward.rs:862-864)
@@ -448,12 +468,68 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
 #pragma unroll
         for (int i = 0; i < NI; i++) S[i] = Sg[(size_t)(pt * NI + i) * D + col];
     }
+    const bool fused = og != nullptr && pp.xin != nullptr;
+    if (fused) {
+        // ---- front end for this block's channels (forward.rs:829-861)
+        const float* conv = cur ? pp.conv1 : pp.conv0;
+        const int k = pp.k;
+        for (int idx = threadIdx.x; idx < rows * 3 * D; idx += D * PARTS) {
+            const int j = idx / (3 * D), c = idx - j * 3 * D, part3 = c / D, i = c - part3 * D;
+            const int chn = part3 == 0 ? kx * D + i : (part3 == 1 ? kd + kx * D + i : 2 * kd + hd * D + i);
+            double acc = (double)pp.cw[chn * k + (k - 1)] * (double)pp.xin[(size_t)j * ch + chn];
+            for (int t = 0; t < k - 1; t++) {
+                const int tau = j - (k - 1) + t;  // row of this pass, or (negative) a row of the carried state
+                const float prev = tau >= 0 ? pp.xin[(size_t)tau * ch + chn] : conv[(size_t)((k - 1) + tau) * ch + chn];
+                acc += (double)pp.cw[chn * k + t] * (double)prev;
+            }
+            pbuf[j][part3][i] = sz_silu((float)acc);
+        }
+        if (threadIdx.x < rows) {
+            const int j = threadIdx.x;
+            const float bt = sz_sigmoid(pp.b[j * vh + hd]);
+            const float sp_in = pp.a[j * vh + hd] + pp.dt[hd];
+            const float sp = sp_in > 20.0f ? sp_in : log1pf(expf(sp_in));
+            const float dc = expf(pp.a_log[hd] * sp);
+            sbeta[j] = bt; sdecay[j] = dc;
+            pp.beta[j * vh + hd] = bt; pp.decay[j * vh + hd] = dc;
+        }
+        __syncthreads();
+        // L2 norm of q and k (q also / sqrt(d)): a warp an item (row, q or k)
+        {
+            const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+            for (int it = warp; it < rows * 2; it += (D * PARTS) / 32) {
+                const int j = it >> 1, part3 = it & 1;
+                double ss = 0.0;
+                for (int i = lane; i < D; i += 32) ss += (double)pbuf[j][part3][i] * (double)pbuf[j][part3][i];
+                ss = sz_warp_sum(ss);
+                const double nn = 1.0 / sqrt(ss + 1e-6);
+                for (int i = lane; i < D; i += 32) {
+                    float t = (float)((double)pbuf[j][part3][i] * nn);
+                    if (part3 == 0) t = t / sqrtf((float)D);
+                    pbuf[j][part3][i] = t;
+                }
+            }
+        }
+        __syncthreads();
+        // what the replay of a commit reads: q and k once a key head (its first value head writes them), v by every head
+        for (int idx = threadIdx.x; idx < rows * 3 * D; idx += D * PARTS) {
+            const int j = idx / (3 * D), c = idx - j * 3 * D, part3 = c / D, i = c - part3 * D;
+            if (part3 == 2) pp.xc[(size_t)j * ch + 2 * kd + hd * D + i] = pbuf[j][2][i];
+            else if (hd < kh) pp.xc[(size_t)j * ch + part3 * kd + kx * D + i] = pbuf[j][part3][i];
+        }
+    }
     for (int j = 0; j < rows; j++) {
         const float* x = xc + (size_t)j * ch;
         __syncthreads();
-        if (threadIdx.x < D) { sq[threadIdx.x] = x[kx * D + threadIdx.x]; sk[threadIdx.x] = x[kd + kx * D + threadIdx.x]; }
-        const float vj = x[2 * kd + hd * D + col];
-        const float dc = decay[j * vh + hd], bt = beta[j * vh + hd];
+        float vj, dc, bt;
+        if (fused) {
+            if (threadIdx.x < D) { sq[threadIdx.x] = pbuf[j][0][threadIdx.x]; sk[threadIdx.x] = pbuf[j][1][threadIdx.x]; }
+            vj = pbuf[j][2][col]; dc = sdecay[j]; bt = sbeta[j];
+        } else {
+            if (threadIdx.x < D) { sq[threadIdx.x] = x[kx * D + threadIdx.x]; sk[threadIdx.x] = x[kd + kx * D + threadIdx.x]; }
+            vj = x[2 * kd + hd * D + col];
+            dc = decay[j * vh + hd]; bt = beta[j * vh + hd];
+        }
         __syncthreads();
         double mem = 0.0;
 #pragma unroll
