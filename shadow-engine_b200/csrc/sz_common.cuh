@@ -104,6 +104,23 @@ __device__ __forceinline__ uint4 sz_ldg16_here(const void* p) {
     return v;
 }
 
+// 2- and 4-byte forms of the same (read-only data: weights, or what a kernel two or more launches back wrote).
+__device__ __forceinline__ u32 sz_ldg32_here(const void* p) {
+    u32 v;
+    asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ u16 sz_ldg16b_here(const void* p) {
+    u16 v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ double sz_ldg64f_here(const double* p) {
+    double v;
+    asm volatile("ld.global.nc.f64 %0, [%1];" : "=d"(v) : "l"(p));
+    return v;
+}
+
 // The same for a 4-byte load of data that other kernels write (an ordinary global load, kept where it is written).
 __device__ __forceinline__ float sz_ld32_here(const float* p) {
     float v;

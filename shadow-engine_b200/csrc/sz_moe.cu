@@ -671,7 +671,7 @@ static int sz_launch_blk(cudaStream_t st, const SzPlan* plan, int groups, const 
     if (n_in % 256 || n_out % (16 * RT) || groups < 1) return SZ_E_TYPE;
     const size_t rb = TYPE == SZ_TYPE_Q8_0 ? (size_t)(n_in / 32) * 34 : (size_t)(n_in / 256) * 110;
     SzBlkCfg c = {};
-    c.by_row = rb % 16 == 0;
+    c.by_row = rb % 16 == 0 && rb >= 1024;   // short rows go in one copy a unit: a copy a row would cost more to issue than the bank conflicts it avoids
     int rbp = (int)rb;
     if (c.by_row) while (((rbp / 4) % 32) % 8 != 4) rbp += 16;   // consecutive rows 4 (mod 8) words apart in bank space
     c.rbp = rbp;
@@ -681,13 +681,13 @@ static int sz_launch_blk(cudaStream_t st, const SzPlan* plan, int groups, const 
     c.xsp = xsp;
     c.slices = n_out / (16 * RT);
     const size_t fixed = 64 + 2048 + 4096 + (size_t)(DOWN ? 1 : 2) * RT * 4096 + (size_t)2 * SZ_MAX_VERIFY * xsp * 2;
-    const size_t budget = 224 * 1024;
+    const size_t budget = 222 * 1024;   // dynamic + the kernel's static shared memory stay under the 227 KB a block may have
     if (fixed + 2 * (size_t)c.unit_bytes > budget) return SZ_E_TYPE;
     int NS = (int)((budget - fixed) / c.unit_bytes);
     c.NS = NS > 4 ? 4 : NS;
     const size_t smem = fixed + (size_t)c.NS * c.unit_bytes;
     static bool set = false;
-    if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_blk_ffn_kernel<TYPE, DOWN, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024)); set = true; }
+    if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_blk_ffn_kernel<TYPE, DOWN, RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024)); set = true; }
     const int per_sm = smem + 4096 <= 110 * 1024 ? 2 : 1;
     int blocks = sz_sm_count() * per_sm;
     const long long units = (long long)groups * c.slices;

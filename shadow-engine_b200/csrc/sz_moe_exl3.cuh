@@ -431,42 +431,59 @@ sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restric
                      long long* __restrict__ y_fix, int e_lo, int e_hi, const SzEpPush push) {
     __shared__ float part[SZ_MAX_TOPK + 1][128];
     __shared__ int local[SZ_MAX_TOPK];
-    sz_pdl_wait();
-    sz_pdl_trigger();
+    __shared__ double rws[SZ_MAX_TOPK];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nb = H / 128;
     const int j = blockIdx.x / nb, b = blockIdx.x % nb;
+    // Routing and scales do not come from the kernel before this one (the router ran three launches back, the scales are weights):
+    // they are fetched ahead of the dependency wait, so that only the expert sums themselves are read after it.
+    int e = 0;
+    bool mine = false;
+    float sv[4] = {0.f, 0.f, 0.f, 0.f};
+    float sg = 0.f;
+    if (warp < top_k) {
+        const int pair = j * top_k + warp;
+        e = (int)sz_ldg32_here(ridx + pair);
+        mine = !y_fix || (e >= e_lo && e < e_hi);  // with expert parallelism only the experts held here count
+        const u16* svh = (const u16*)(down + (u64)(mine ? e : e_lo) * dstride + 2 * (size_t)FF) + b * 128;
+#pragma unroll
+        for (int q = 0; q < 4; q++) sv[q] = sz_f16_to_f32(sz_ldg16b_here(svh + lane + 32 * q));
+        if (lane == 0) { local[warp] = mine; rws[warp] = sz_ldg64f_here(rw + pair); }
+    } else if (warp == top_k && has_shared) {
+        sg = sz_sigmoid(__uint_as_float(sz_ldg32_here(logits + (size_t)j * (ne + 1) + ne)));
+        if (!so_f32) {
+            const u16* svh = (const u16*)(sh_down + 2 * (size_t)FF) + b * 128;
+#pragma unroll
+            for (int q = 0; q < 4; q++) sv[q] = sz_f16_to_f32(sz_ldg16b_here(svh + lane + 32 * q));
+        }
+    }
+    sz_pdl_wait();
+    sz_pdl_trigger();
     // which of the two slots of the exchange buffers this round writes (read once, early: it is a load from L2)
     const int slot = y_fix && push.world > 0 ? (int)(__ldcg(&((const SzEpHeader*)push.buf[push.me])->epoch) & 1ull) : 0;
     if (warp < top_k) {
         const int pair = j * top_k + warp;
-        const int e = __ldcg(ridx + pair);
-        const bool mine = !y_fix || (e >= e_lo && e < e_hi);  // with expert parallelism only the experts held here count
-        if (lane == 0) local[warp] = mine;
-        const u16* svh = (const u16*)(down + (u64)(mine ? e : e_lo) * dstride + 2 * (size_t)FF) + b * 128;
         float v[4];
 #pragma unroll
-        for (int e = 0; e < 4; e++) v[e] = (float)((double)__ldcg(out + (size_t)pair * H + b * 128 + lane + 32 * e) * SZ_FIX_INV);
+        for (int q = 0; q < 4; q++) v[q] = (float)((double)__ldcg(out + (size_t)pair * H + b * 128 + lane + 32 * q) * SZ_FIX_INV);
         sz_wht128_warp(v, lane);
 #pragma unroll
-        for (int e = 0; e < 4; e++) part[warp][lane + 32 * e] = (v[e] * SZ_RSQRT128) * sz_f16_to_f32(svh[lane + 32 * e]);
+        for (int q = 0; q < 4; q++) part[warp][lane + 32 * q] = (v[q] * SZ_RSQRT128) * sv[q];
     } else if (warp == top_k && has_shared) {
-        const float sg = sz_sigmoid(__ldcg(logits + (size_t)j * (ne + 1) + ne));
         float v[4];
         if (so_f32) {
 #pragma unroll
-            for (int e = 0; e < 4; e++) v[e] = __ldcg(so_f32 + (size_t)j * H + b * 128 + lane + 32 * e);
+            for (int q = 0; q < 4; q++) v[q] = __ldcg(so_f32 + (size_t)j * H + b * 128 + lane + 32 * q);
         } else {
-            const u16* svh = (const u16*)(sh_down + 2 * (size_t)FF) + b * 128;
             const int pair = m * top_k + j;
 #pragma unroll
-            for (int e = 0; e < 4; e++) v[e] = (float)((double)__ldcg(out + (size_t)pair * H + b * 128 + lane + 32 * e) * SZ_FIX_INV);
+            for (int q = 0; q < 4; q++) v[q] = (float)((double)__ldcg(out + (size_t)pair * H + b * 128 + lane + 32 * q) * SZ_FIX_INV);
             sz_wht128_warp(v, lane);
 #pragma unroll
-            for (int e = 0; e < 4; e++) v[e] = (v[e] * SZ_RSQRT128) * sz_f16_to_f32(svh[lane + 32 * e]);
+            for (int q = 0; q < 4; q++) v[q] = (v[q] * SZ_RSQRT128) * sv[q];
         }
 #pragma unroll
-        for (int e = 0; e < 4; e++) part[top_k][lane + 32 * e] = sg * v[e];
+        for (int q = 0; q < 4; q++) part[top_k][lane + 32 * q] = sg * v[q];
     }
     __syncthreads();
     if (warp == 0) {
@@ -476,7 +493,7 @@ sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restric
             if (y_fix) {  // every term in 64-bit fixed point: the sum over ranks is then exact
                 long long f = 0;
                 for (int t = 0; t < top_k; t++)
-                    if (local[t]) f += __double2ll_rn(__ldcg(rw + j * top_k + t) * (double)part[t][i] * 1099511627776.0);
+                    if (local[t]) f += __double2ll_rn(rws[t] * (double)part[t][i] * 1099511627776.0);
                 if (has_shared) f += __double2ll_rn((double)part[top_k][i] * 1099511627776.0);
                 if (push.world > 0) {
                     for (int r = 0; r < push.world; r++)
@@ -486,7 +503,7 @@ sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restric
                 }
             } else {
                 double a = 0.0;
-                for (int t = 0; t < top_k; t++) a += __ldcg(rw + j * top_k + t) * (double)part[t][i];
+                for (int t = 0; t < top_k; t++) a += rws[t] * (double)part[t][i];
                 if (has_shared) a += (double)part[top_k][i];
                 y[(size_t)j * H + b * 128 + i] = (float)a;
             }
