@@ -111,7 +111,9 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
     if (splits2 > (ctx + 255) / 256) splits2 = (ctx + 255) / 256;
     if (splits2 < 1) splits2 = 1;
     L->splits2 = splits2;
-    L->a_part = take(4 * M * c.n_head * (splits > splits2 ? splits : splits2) * (c.head_dim + 2));
+    // (with few queries a head the grouped kernel runs two blocks a multiprocessor and takes twice the splits)
+    const int smax = splits > 2 * splits2 ? splits : 2 * splits2;
+    L->a_part = take(4 * M * c.n_head * smax * (c.head_dim + 2));
     const int64_t hb = (flags & SZ_KV_Q8) ? (c.head_dim + (((c.head_dim >> 5) * 2 + 15) & ~15)) : 4 * (int64_t)c.head_dim;
     L->kv_bytes = (int64_t)(n_attn > 0 ? n_attn : 1) * ctx * c.n_kv_head * hb;
     L->kc = take(L->kv_bytes); L->vc = take(L->kv_bytes);
@@ -548,23 +550,28 @@ static int sz_attn_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8
 }
 
 template <int HD, int NQT>
-static int sz_attn2_go(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m) {
+static int sz_attn2_go(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m, int* splits_used) {
     const sz_model_config& c = s->model.cfg;
     static bool set = false;
     const size_t smem = (size_t)SzAttn2<HD>::smem_bytes(NQT);
     if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_attn2_kernel<HD, NQT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); set = true; }
-    SZ_CUDA(sz_launch("attention_grouped", sz_attn2_kernel<HD, NQT>, dim3(c.n_kv_head, s->attn_splits2), dim3(256), smem, st, true, (const float*)s->a_q,
-                      kc, vc, (int)c.n_head, (int)c.n_kv_head, m, s->ctx, (const int32_t*)s->state, s->attn_splits2, s->a_part, (u32*)(s->state + 2)));
+    // two blocks fit a multiprocessor when the query fragments are small: twice the splits then, so that each block's chain of
+    // chunks is half as long and the two blocks hide each other's barriers
+    int splits = s->attn_splits2;
+    if (smem + 2048 <= 113 * 1024 && 2 * splits <= (s->ctx + 255) / 256) splits *= 2;
+    *splits_used = splits;
+    SZ_CUDA(sz_launch("attention_grouped", sz_attn2_kernel<HD, NQT>, dim3(c.n_kv_head, splits), dim3(256), smem, st, true, (const float*)s->a_q,
+                      kc, vc, (int)c.n_head, (int)c.n_kv_head, m, s->ctx, (const int32_t*)s->state, splits, s->a_part, (u32*)(s->state + 2)));
     return SZ_OK;
 }
 
 template <int HD>
-static int sz_attn2_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m) {
+static int sz_attn2_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m, int* splits_used) {
     const sz_model_config& c = s->model.cfg;
     const int qv = c.n_head / c.n_kv_head * m;
-    if (qv <= 16) return sz_attn2_go<HD, 1>(s, st, kc, vc, m);
-    if (qv <= 32) return sz_attn2_go<HD, 2>(s, st, kc, vc, m);
-    return sz_attn2_go<HD, 4>(s, st, kc, vc, m);
+    if (qv <= 16) return sz_attn2_go<HD, 1>(s, st, kc, vc, m, splits_used);
+    if (qv <= 32) return sz_attn2_go<HD, 2>(s, st, kc, vc, m, splits_used);
+    return sz_attn2_go<HD, 4>(s, st, kc, vc, m, splits_used);
 }
 
 static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
@@ -591,9 +598,9 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     const bool grouped = q8 && !generic_only && (nh / nkv) * m <= 64;
     int splits = grouped ? s->attn_splits2 : s->attn_splits;
     if (grouped) {
-        if (hd == 64) rc = sz_attn2_launch<64>(s, st, kc, vc, m);
-        else if (hd == 128) rc = sz_attn2_launch<128>(s, st, kc, vc, m);
-        else rc = sz_attn2_launch<256>(s, st, kc, vc, m);
+        if (hd == 64) rc = sz_attn2_launch<64>(s, st, kc, vc, m, &splits);
+        else if (hd == 128) rc = sz_attn2_launch<128>(s, st, kc, vc, m, &splits);
+        else rc = sz_attn2_launch<256>(s, st, kc, vc, m, &splits);
     } else {
         if (hd == 64) rc = sz_attn_launch<2>(s, st, kc, vc, m);
         else if (hd == 128) rc = sz_attn_launch<4>(s, st, kc, vc, m);

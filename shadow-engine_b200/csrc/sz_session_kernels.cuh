@@ -787,20 +787,30 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, q4 = lane & 3;
     const int kvh = blockIdx.x, sp = blockIdx.y;
     const int G = nh / nkv, QV = G * m;
-    if (threadIdx.x == 0) {
-        sz_mbar_init(&bars[0], 1);
-        sz_mbar_init(&bars[1], 1);
-        sz_mbar_fence_init();
-    }
-    sz_pdl_wait();
-    sz_pdl_trigger();
-    const int pos0 = state[0];
+    // The committed length belongs to the previous pass, and so does every cache position below it: the block's first chunk is
+    // requested ahead of the dependency wait when it lies wholly there (the rows of this pass are written by the kernel before).
+    int pos0;
+    asm volatile("ld.global.s32 %0, [%1];" : "=r"(pos0) : "l"(state));
     const int nmax = pos0 + m;
     const int per = ((nmax + splits - 1) / splits + SZ_AT_T - 1) / SZ_AT_T * SZ_AT_T;
     const int t0 = sp * per, t1 = min(nmax, t0 + per);
     const int nchunk = t1 > t0 ? (t1 - t0 + SZ_AT_T - 1) / SZ_AT_T : 0;
     const u8* kbase = kc + (size_t)kvh * ctx * A::HB;
     const u8* vbase = vc + (size_t)kvh * ctx * A::HB;
+    const bool early = nchunk > 0 && t0 + SZ_AT_T <= pos0;
+    if (threadIdx.x == 0) {
+        sz_mbar_init(&bars[0], 1);
+        sz_mbar_init(&bars[1], 1);
+        sz_mbar_fence_init();
+        if (early) {
+            const u32 bytes = (u32)(SZ_AT_T * A::HB);
+            sz_mbar_expect_tx(&bars[0], 2 * bytes);
+            sz_bulk_g2s(stage, kbase + (size_t)t0 * A::HB, bytes, &bars[0]);
+            sz_bulk_g2s(stage + SZ_AT_T * A::HB, vbase + (size_t)t0 * A::HB, bytes, &bars[0]);
+        }
+    }
+    sz_pdl_wait();
+    sz_pdl_trigger();
     // the queries as A fragments (f16 high and low parts), scaled by 1 / sqrt(HD)
     const float scale = rsqrtf((float)HD);
     for (int e = threadIdx.x; e < NQT * A::KS * 32; e += 256) {
@@ -835,7 +845,7 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
         sz_bulk_g2s(dst, kbase + (size_t)t * A::HB, bytes, bar);
         sz_bulk_g2s(dst + SZ_AT_T * A::HB, vbase + (size_t)t * A::HB, bytes, bar);
     };
-    if (threadIdx.x == 0 && nchunk > 0) issue(0);
+    if (threadIdx.x == 0 && nchunk > 0 && !early) issue(0);
     __syncthreads();
     float o[NQT][A::NT][4];
 #pragma unroll
