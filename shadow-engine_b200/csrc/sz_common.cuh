@@ -147,6 +147,13 @@ __device__ __forceinline__ double sz_warp_sum(double v) {
 // microsecond of dependent latency each on this part, which is the whole budget of a kernel here, so this is the f32 form: it
 // differs from the rounded f64 value by an ulp or two, the same size as the f32 accumulation noise of the dot products around it.
 __device__ __forceinline__ float sz_sigmoid(float x) { return 1.0f / (1.0f + expf(-x)); }
+// 1 / sqrt(v) to about 1e-14 relative: the f32 estimate refined by one Newton step in f64.  A correctly rounded f64 square root
+// and divide cost several hundred cycles of dependent latency; this is four multiply-adds.
+__device__ __forceinline__ double sz_rsqrt64(double v) {
+    const double r = (double)rsqrtf((float)v);
+    return r * fma(-0.5 * v, r * r, 1.5);
+}
+
 __device__ __forceinline__ float sz_silu(float x) { return x * sz_sigmoid(x); }
 
 // ---- mbarrier + bulk async copy (TMA engine, untiled form) ---------------------------------------------------------------

@@ -31,6 +31,7 @@ struct SzDenseArgs {
     int xstride;
     int cols;
     int m;
+    u32* err;        // set to 1 when a bounded wait on a copy ran out (null: not reported)
 };
 
 #ifdef __CUDACC__
@@ -203,6 +204,7 @@ __global__ void __launch_bounds__(256) sz_dense2_kernel(const SzDenseArgs a, con
         sz_mbar_expect_tx(bar, bytes);
         sz_bulk_g2s(stages + (size_t)(gi % c.NS) * c.unit_bytes, a.job[ji].w + (size_t)row0 * rb, bytes, bar);
     };
+    int failed = 0;
     for (int j0 = 0; j0 < a.m; j0 += MT) {
         const int mt = min(MT, a.m - j0);
         const int base = (j0 / MT) * count;  // units issued so far (each sweep streams every unit again)
@@ -216,7 +218,6 @@ __global__ void __launch_bounds__(256) sz_dense2_kernel(const SzDenseArgs a, con
             for (int i = threadIdx.x; i < a.cols / 4; i += 256) dst[i] = __ldcg(src + i);
         }
         __syncthreads();
-        int failed = 0;
         for (int i = 0; i < count; i++) {
             const int gi = base + i;
             if (threadIdx.x == 0 && i + c.NS - 1 < count) issue(i + c.NS - 1, gi + c.NS - 1);
@@ -274,6 +275,7 @@ __global__ void __launch_bounds__(256) sz_dense2_kernel(const SzDenseArgs a, con
         }
         if (failed) break;
     }
+    if (failed && threadIdx.x == 0 && a.err) atomicExch(a.err, 1u);
 }
 
 // ---- Q8_0 on the tensor pipe ----------------------------------------------------------------------------------------------------------
@@ -413,6 +415,7 @@ static __global__ void __launch_bounds__(256, 2) sz_dense_q8_kernel(const SzDens
         }
         __syncthreads();
     }
+    if (failed && threadIdx.x == 0 && a.err) atomicExch(a.err, 1u);
 }
 
 #endif  // __CUDACC__

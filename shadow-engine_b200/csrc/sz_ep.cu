@@ -4,6 +4,7 @@
 #include "sz_common.cuh"
 
 #include <dlfcn.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace {
@@ -104,6 +105,7 @@ namespace {
 struct P2p {
     int rank = 0, world = 0;
     int hidden = 0;
+    int polls = SZ_EP_SPIN_LIMIT;   // how often a finish block polls a counter before it gives up
     u8* buf[SZ_EP_MAX_RANKS] = {};
 } g_p2p;
 }  // namespace
@@ -112,7 +114,7 @@ struct P2p {
 // number of polls; on running out it raises the header's error word and the block goes on with what is there, so the kernel always
 // ends).  The last block to finish closes the exchange: epoch + 1, target + blocks of the combine kernel.
 __global__ void __launch_bounds__(256)
-sz_ep_finish_kernel(u8* __restrict__ mine, int world, long long row_elems, unsigned long long nb, int n, float* __restrict__ y) {
+sz_ep_finish_kernel(u8* __restrict__ mine, int world, long long row_elems, unsigned long long nb, int n, float* __restrict__ y, int poll_limit) {
     __shared__ int s_last;
     sz_pdl_wait();
     sz_pdl_trigger();
@@ -123,12 +125,12 @@ sz_ep_finish_kernel(u8* __restrict__ mine, int world, long long row_elems, unsig
         volatile unsigned long long* c = sz_ep_arrive(mine, threadIdx.x);
         int polls = 0;
         bool ok = false;
-        while (polls < SZ_EP_SPIN_LIMIT && *(volatile unsigned int*)&hdr->error == 0) {
+        while (polls < poll_limit && *(volatile unsigned int*)&hdr->error == 0) {
             unsigned long long v;
             asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(c));
             if (v >= want) { ok = true; break; }
             polls++;
-            __nanosleep(64);
+            __nanosleep(polls < 4096 ? 32 : 1000);   // quick at first, then about a microsecond a poll
         }
         if (!ok) atomicExch(&hdr->error, 1u);
     }
@@ -199,6 +201,13 @@ extern "C" int sz_ep_p2p_attach(int rank, int world, int hidden, const uint64_t*
     for (int r = 0; r < world; r++)
         if (!bufs[r] || (bufs[r] & 255)) return sz_fail(SZ_E_ARG, "sz_ep_p2p_attach: buffer %d is null or not 256-byte aligned", r);
     g_p2p.rank = rank; g_p2p.world = world; g_p2p.hidden = hidden;
+    {
+        // the poll budget of a wait: about two seconds by default (a peer may be busy recording a graph or loading a module);
+        // SZ_EP_WAIT_POLLS overrides it (the test of a wait that runs out uses a small one)
+        const char* e = getenv("SZ_EP_WAIT_POLLS");
+        const long v = e ? atol(e) : 0;
+        g_p2p.polls = v > 0 && v < 2000000000L ? (int)v : SZ_EP_SPIN_LIMIT;
+    }
     for (int r = 0; r < SZ_EP_MAX_RANKS; r++) g_p2p.buf[r] = r < world ? (u8*)bufs[r] : nullptr;
     return SZ_OK;
 }
@@ -241,7 +250,7 @@ extern "C" int sz_moe_finish_exchange(const sz_moe_layer* L, int m, uint64_t y, 
 int sz_ep_p2p_finish(int m, int hidden, unsigned long long combine_blocks, float* y, cudaStream_t st) {
     const int n = m * hidden;
     SZ_CUDA(sz_launch("ep_finish", sz_ep_finish_kernel, dim3((n + 1023) / 1024), dim3(256), 0, st, true, g_p2p.buf[g_p2p.rank], g_p2p.world,
-                      (long long)SZ_MAX_VERIFY * hidden, combine_blocks, n, y));
+                      (long long)SZ_MAX_VERIFY * hidden, combine_blocks, n, y, g_p2p.polls));
     return SZ_OK;
 }
 

@@ -948,7 +948,10 @@ extern "C" int sz_moe_verify_host(const sz_moe_layer* L, const float* x_host, in
         SZ_CUDA(cudaMemcpyAsync(route_idx_host, (const u8*)scratch + S.ridx, (size_t)m * L->top_k * 4, cudaMemcpyDeviceToHost, st));
     if (route_w_host)
         SZ_CUDA(cudaMemcpyAsync(route_w_host, (const u8*)scratch + S.rw, (size_t)m * L->top_k * 8, cudaMemcpyDeviceToHost, st));
+    u32 err = 0;  // (pageable: this copy is the call's last and the call synchronises anyway)
+    SZ_CUDA(cudaMemcpyAsync(&err, (const u8*)scratch + S.ctrl + 4, 4, cudaMemcpyDeviceToHost, st));
     SZ_CUDA(cudaStreamSynchronize(st));
+    if (err) return sz_fail(SZ_E_DEVICE, "a bounded wait on an asynchronous copy ran out in a MoE kernel: the results of this call are not valid");
     return SZ_OK;
 }
 

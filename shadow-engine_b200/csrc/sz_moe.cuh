@@ -18,7 +18,7 @@
 // only after it has finished reading round e.
 #define SZ_EP_MAX_RANKS 8
 #define SZ_EP_HDR_BYTES 2048           // header (128) + 8 counters on lines of their own, padded
-#define SZ_EP_SPIN_LIMIT 400000        // polls of a counter before a waiting block gives up and raises the error word
+#define SZ_EP_SPIN_LIMIT 1000000       // polls of a counter (about a microsecond each) before a waiting block gives up and raises the error word
 
 struct SzEpHeader {
     unsigned long long epoch;    // exchanges completed by this rank

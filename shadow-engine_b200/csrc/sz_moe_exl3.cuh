@@ -205,11 +205,13 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
         d.in_off = s * 128 + (mat << 30);  // bit 30 carries the matrix index
         return d;
     };
+    constexpr int UD0 = 12;
+    __shared__ const u8* usrc[UD0];  // (filled with the descriptors below)
     auto issue = [&](int i) {  // thread 0: start unit i's copy into stage i % STAGES
-        const SzX3Unit d = unit(u0 + i);
+        const u8* src = i < UD0 ? usrc[i] : unit(u0 + i).src;
         u64* bar = &bars[i % SZ_X3_STAGES];
         sz_mbar_expect_tx(bar, X::STAGE_BYTES);
-        sz_bulk_g2s(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, d.src, X::STAGE_BYTES, bar);
+        sz_bulk_g2s(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, src, X::STAGE_BYTES, bar);
     };
     auto prep_load = [&](const SzX3Unit& d, float* v) {  // warp t: row t of the group times suh, element lane + 32 e
         if (warp < d.n) {
@@ -221,9 +223,15 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
         }
     };
 
+    // the block's unit descriptors, worked out once and in parallel (divisions, plan look-ups, 64-bit address arithmetic)
+    constexpr int UD = 12;
+    __shared__ SzX3Unit ud[UD];
+    if (threadIdx.x < UD && threadIdx.x < count) { ud[threadIdx.x] = unit(u0 + threadIdx.x); usrc[threadIdx.x] = ud[threadIdx.x].src; }
+    __syncthreads();
+    auto unit_at = [&](int i) { return i < UD ? ud[i] : unit(u0 + i); };
     if (threadIdx.x == 0)
         for (int i = 0; i < SZ_X3_STAGES - 1 && i < count; i++) issue(i);
-    SzX3Unit cur = unit(u0);
+    SzX3Unit cur = unit_at(0);
     {
         float v[4];
         prep_load(cur, v);
@@ -236,7 +244,7 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
         if (threadIdx.x == 0 && i + SZ_X3_STAGES - 1 < count) issue(i + SZ_X3_STAGES - 1);
         SzX3Unit nxt = cur;
         float v[4];
-        if (i + 1 < count) { nxt = unit(u0 + i + 1); prep_load(nxt, v); }
+        if (i + 1 < count) { nxt = unit_at(i + 1); prep_load(nxt, v); }
         if (i == 1) SZ_PH();  // unit 1: start
         if (!sz_mbar_wait(&bars[i % SZ_X3_STAGES], (i / SZ_X3_STAGES) & 1)) failed = 1;
         if (i == 1) SZ_PH();  // unit 1: data arrived
@@ -333,8 +341,11 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
         d.suh = (const u16*)bd + d.kb * 128;
         return d;
     };
+    constexpr int UD = 12;
+    __shared__ DUnit ud[UD];
+    auto unit_at = [&](int i) { return i < UD ? ud[i] : unit(u0 + i); };
     auto issue = [&](int i) {
-        const DUnit d = unit(u0 + i);
+        const DUnit d = unit_at(i);
         u64* bar = &bars[i % SZ_X3_STAGES];
         u8* dst = stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES;
         sz_mbar_expect_tx(bar, X::STAGE_BYTES);
@@ -374,12 +385,14 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
         sz_x3_store_frag(frag, warp, d.n, v, lane);
     };
 
+    if (threadIdx.x < UD && threadIdx.x < count) ud[threadIdx.x] = unit(u0 + threadIdx.x);
+    __syncthreads();
     if (count > 0 && threadIdx.x == 0)
         for (int i = 0; i < SZ_X3_STAGES - 1 && i < count; i++) issue(i);
     sz_pdl_wait();
     sz_pdl_trigger();
     if (count <= 0) return;
-    DUnit cur = unit(u0);
+    DUnit cur = unit_at(0);
     {
         long long ag[4], au[4];
         float sc[12];
@@ -393,7 +406,7 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
         DUnit nxt = cur;
         long long ag[4], au[4];
         float sc[12];
-        if (i + 1 < count) { nxt = unit(u0 + i + 1); prep_load(nxt, ag, au, sc); }
+        if (i + 1 < count) { nxt = unit_at(i + 1); prep_load(nxt, ag, au, sc); }
         if (!sz_mbar_wait(&bars[i % SZ_X3_STAGES], (i / SZ_X3_STAGES) & 1)) failed = 1;
         float c[4][4];
         if (!failed) {

@@ -465,6 +465,7 @@ static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bo
     SZ_CUDA(sz_launch("hc_norm", sz_hc_norm_kernel, dim3(C, m), dim3(256), 0, st, true, s->r, (const float*)(pending ? s->g : nullptr),
                       (const float*)(pending ? s->y : nullptr), (const float*)hc.norm.data, H, C, c.eps, s->rn));
     SzDenseArgs a = {};
+    a.err = (u32*)(s->state + 2);
     a.x = s->rn; a.xstride = CH; a.cols = CH; a.m = m;
     a.job[0] = sz_job(hc.down, s->hdown, c.hc_rank, SZ_EPI_SILU_DIV, (float)C);
     a.n_jobs = 1;
@@ -472,6 +473,7 @@ static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bo
     int rc = sz_dense_launch(a, st, "hc_down");
     if (rc) return rc;
     SzDenseArgs b = {};
+    b.err = (u32*)(s->state + 2);
     b.x = s->hdown; b.xstride = c.hc_rank; b.cols = c.hc_rank; b.m = m;
     b.job[0] = sz_job(hc.up, s->mix, CH, SZ_EPI_SIGMOID);
     b.n_jobs = 1;
@@ -515,6 +517,7 @@ static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
     float* beta = s->d_beta + (int64_t)di * SZ_MAX_VERIFY * vh;
     float* decay = s->d_decay + (int64_t)di * SZ_MAX_VERIFY * vh;
     SzDenseArgs a = {};
+    a.err = (u32*)(s->state + 2);
     a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 4;
     a.job[0] = sz_job(L.attn_qkv, xin, (int)ch);
     a.job[1] = sz_job(L.attn_gate, s->d_z, (int)vd);
@@ -536,6 +539,7 @@ static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
     }
     if ((rc = sz_scan(s, st, l, m, pp))) return rc;
     SzDenseArgs b = {};
+    b.err = (u32*)(s->state + 2);
     b.x = s->d_og; b.xstride = (int)vd; b.cols = (int)vd; b.m = m; b.n_jobs = 1;
     b.job[0] = sz_job(L.ssm_out, s->y, H);
     return sz_dense_launch(b, st, "ssm_out");
@@ -584,6 +588,7 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     const int64_t layer_bytes = (int64_t)s->ctx * nkv * hb;
     u8 *kc = s->kc + ai * layer_bytes, *vc = s->vc + ai * layer_bytes;
     SzDenseArgs a = {};
+    a.err = (u32*)(s->state + 2);
     a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 3;
     a.job[0] = sz_job(L.attn_q, s->a_qg, 2 * nh * hd);
     a.job[1] = sz_job(L.attn_k, s->a_k, nkv * hd);
@@ -610,6 +615,7 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     SZ_CUDA(sz_launch("attn_merge", sz_attn_merge_kernel, dim3(nh, m), dim3(256), 0, st, true, (const float*)s->a_part, (const float*)s->a_gate, nh, hd,
                       splits, s->a_o));
     SzDenseArgs b = {};
+    b.err = (u32*)(s->state + 2);
     b.x = s->a_o; b.xstride = nh * hd; b.cols = nh * hd; b.m = m; b.n_jobs = 1;
     b.job[0] = sz_job(L.attn_output, s->y, H);
     return sz_dense_launch(b, st, "attn_output");
@@ -641,6 +647,7 @@ static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
     if (!head) return SZ_OK;  // the last write only matters to the output read; the next pass starts from the embedding
     if ((rc = sz_hc_read(s, st, s->model.output_hc, m, pending, false))) return rc;
     SzDenseArgs a = {};
+    a.err = (u32*)(s->state + 2);
     a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 1;
     a.job[0] = sz_job(s->model.output, s->logits, c.vocab);
     if ((rc = sz_dense_launch(a, st, "lm_head"))) return rc;
@@ -736,8 +743,14 @@ extern "C" int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* to
     if (keep_next) SZ_CUDA(cudaMemcpyAsync(keep_next, s->res, 8, cudaMemcpyDeviceToHost, st));
     if (top) SZ_CUDA(cudaMemcpyAsync(top, s->top, (size_t)s->last_m * 128 * 4, cudaMemcpyDeviceToHost, st));
     if (logits) SZ_CUDA(cudaMemcpyAsync(logits, s->logits, (size_t)s->last_m * s->model.cfg.vocab * 4, cudaMemcpyDeviceToHost, st));
+    // the error words the kernels raise when one of their bounded waits runs out: [10] the session's kernels, [11] the MoE kernels
+    SZ_CUDA(cudaMemcpyAsync(s->h_pin + 10, s->state + 2, 4, cudaMemcpyDeviceToHost, st));
+    SZ_CUDA(cudaMemcpyAsync(s->h_pin + 11, s->moe_scratch + 4, 4, cudaMemcpyDeviceToHost, st));
     SZ_CUDA(cudaStreamSynchronize(st));
     s->inflight = 0;
+    if (s->h_pin[10] || s->h_pin[11])
+        return sz_fail(SZ_E_DEVICE, "a bounded wait on an asynchronous copy ran out (session word %d, MoE word %d): the results of this pass are not valid",
+                       s->h_pin[10], s->h_pin[11]);
     return SZ_OK;
 }
 

@@ -57,7 +57,7 @@ sz_hc_norm_kernel(float* __restrict__ r, const float* __restrict__ g, const floa
         ss += (double)v * (double)v;
     }
     ss = sz_block_sum(ss, red);
-    const double rr = 1.0 / sqrt(ss / (double)H + (double)eps);
+    const double rr = sz_rsqrt64(ss / (double)H + (double)eps);
     for (int i = threadIdx.x; i < H; i += 256) rn[((size_t)j * C + s) * H + i] = (float)((double)rs[i] * rr) * w[s * H + i];
 }
 
@@ -167,7 +167,7 @@ sz_hc_down_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, con
     if (t < M) {
         double v = 0.0;
         for (int q = 0; q < (nt >> 5); q++) v += red[q][t];
-        rinv[t] = (float)(1.0 / sqrt(v / (double)H + (double)eps));
+        rinv[t] = (float)sz_rsqrt64(v / (double)H + (double)eps);
     }
     __syncthreads();
     SZ_PH();  // 4 rinv
@@ -349,7 +349,7 @@ sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ co
                 ss = (double)v * (double)v;
                 for (int o = d >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
             }
-            const double n = 1.0 / sqrt(ss + 1e-6);
+            const double n = sz_rsqrt64(ss + 1e-6);
             float t = (float)((double)v * n);
             if (i < kd) t = t / sqrtf((float)d);
             v = t;
@@ -502,7 +502,7 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
                 double ss = 0.0;
                 for (int i = lane; i < D; i += 32) ss += (double)pbuf[j][part3][i] * (double)pbuf[j][part3][i];
                 ss = sz_warp_sum(ss);
-                const double nn = 1.0 / sqrt(ss + 1e-6);
+                const double nn = sz_rsqrt64(ss + 1e-6);
                 for (int i = lane; i < D; i += 32) {
                     float t = (float)((double)pbuf[j][part3][i] * nn);
                     if (part3 == 0) t = t / sqrtf((float)D);
@@ -580,7 +580,7 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
             double ss = 0.0;
             for (int i = lane; i < D; i += 32) ss += (double)ofs[j][i] * (double)ofs[j][i];
             ss = sz_warp_sum(ss);
-            if (lane == 0) rrs[j] = 1.0 / sqrt(ss / (double)D + (double)eps);
+            if (lane == 0) rrs[j] = sz_rsqrt64(ss / (double)D + (double)eps);
         }
         __syncthreads();
         for (int idx = threadIdx.x; idx < rows * D; idx += D * PARTS) {
@@ -647,7 +647,7 @@ sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, 
     double ss = 0.0;
     for (int i = threadIdx.x; i < hd; i += 128) ss += (double)x[i] * (double)x[i];
     ss = sz_block_sum(ss, red);
-    const double rr = 1.0 / sqrt(ss / (double)hd + (double)eps);
+    const double rr = sz_rsqrt64(ss / (double)hd + (double)eps);
     for (int i = threadIdx.x; i < hd; i += 128) tmp[i] = (float)((double)x[i] * rr) * w[i];
     __syncthreads();
     const int half = rope_dims / 2;

@@ -107,7 +107,11 @@ def test_peer_exchange_wait_runs_out_without_hanging():
     usable.  (The failure is a flag that nothing sets - no fault, no trap.)"""
     L = synth.make_moe_layer(256, 16, 4, 128, 128, szlib.TYPE_Q8_0, szlib.TYPE_Q8_0, seed=44)
     x = torch.randn(2, 256).cuda()
-    ex = ep.PeerExchange(256, local_world=2)
+    os.environ["SZ_EP_WAIT_POLLS"] = "50000"          # a short budget: this wait is meant to run out
+    try:
+        ex = ep.PeerExchange(256, local_world=2)
+    finally:
+        del os.environ["SZ_EP_WAIT_POLLS"]
     try:
         layer = moe.MoeLayer(L, "cuda:0", shard=ep.shard_spec(0, 2, 16))
         ex.use(0)
