@@ -311,6 +311,46 @@ int sz_moe_static_scratch_max(int64_t* bytes);
 int sz_moe_verify_static(const sz_moe_layer* layer, uint64_t x, int m, uint64_t y, uint64_t route_idx, uint64_t route_w,
                          uint64_t stream);
 
+/* ---- lm_head over an EXL3 output.weight, dense or screened by the 2-bit proxy ("Q2_P") -------------------------------------------
+ * Replaces HeadProxy (crates/shadowzero-cuda/src/session.rs:428-452, built at 2631-2674 by exl3_build_q2_proxy_*,
+ * kernels/exl3.cu:915-996), mv_head_proxy_sparse (session.rs:5950-5995: exl3_rotate_rows_f32 kernels/exl3.cu:609-625,
+ * proxy_q2_quant_x / proxy_q2_dp4a_bmax_* / proxy_pick_rows / proxy_compact_seen kernels/forward.cu:4367-4632,
+ * matvec_cols_exl3_pre_sparse_* kernels/exl3.cu:349-480) and head_top_at (session.rs:5997-6022: topk_slices_blks, topk_merge_blks,
+ * kernels/forward.cu:4635-4680).
+ * rows = vocabulary, cols = hidden, both multiples of 128 (cols <= 4096, rows <= 262144); bits = 2..6 or 8; the blob sits at an
+ * address = 12 mod 16.  k_blk = 0: every 128-output block is evaluated (the exact head) and w_q2 / w_sc may be 0.  k_blk > 0
+ * (clamped to 16 .. rows / 128; the reference's default is 128): each row of the pass keeps its k_use best blocks by proxy score,
+ * k_use = k_blk, or max(64, 3 k_blk / 4) when need_k <= 16 (session.rs:5964); only the union of those blocks is evaluated, so a
+ * token outside them cannot appear in the top-64 (the reference uses this form for serving, never for its exact path). */
+typedef struct sz_head {
+    int32_t rows, cols, bits, k_blk;
+    uint64_t weight;             /* the EXL3 blob of output.weight */
+    uint64_t w_q2, w_sc;         /* the proxy: sz_head_proxy_bytes sizes them, sz_head_proxy_build fills them */
+    uint64_t work;               /* sz_head_work_bytes bytes, 256-byte aligned, cleared once by sz_head_work_init */
+    int64_t work_bytes;
+} sz_head;
+int sz_head_proxy_bytes(int rows, int cols, int64_t* q2_bytes, int64_t* sc_bytes);
+int sz_head_work_bytes(int rows, int cols, int k_blk, int64_t* bytes);
+int sz_head_work_init(const sz_head* h, uint64_t stream);
+int sz_head_proxy_build(const sz_head* h, uint64_t stream);
+/* What a pass of m rows will do: blocks kept a row, the length of the block list, and the row stride of its logits (elements):
+ * max_sel * 128 packed logits with the proxy, `rows` without. */
+int sz_head_plan(const sz_head* h, int m, int need_k, int32_t* k_use, int32_t* max_sel, int64_t* logits_stride);
+/* x: f32 [m][xstride] device rows.  logits: f32 [m][logits_stride] (with the proxy: block list entry s at elements 128 s ..).
+ * top: u32 [m][128], the layout of sz_session_result.  Asynchronous on `stream`, capturable, no allocation. */
+int sz_head_top(const sz_head* h, uint64_t x, int xstride, int m, int need_k, uint64_t logits, uint64_t top, uint64_t stream);
+/* Where the intermediate buffers of the last sz_head_top live inside `work` (tests, traces): rotated rows f32 [8][cols]; their
+ * int8 codes [8][cols]; block scales and bias terms f32 [8][cols / 128]; block maxima f32 [8][rows / 128]; the block list u32
+ * {count, blocks ascending}; the error word (nonzero: a bounded wait ran out). */
+#define SZ_HEAD_XR 0
+#define SZ_HEAD_XQ 1
+#define SZ_HEAD_XSC 2
+#define SZ_HEAD_XCORR 3
+#define SZ_HEAD_BMAX 4
+#define SZ_HEAD_SEL 5
+#define SZ_HEAD_ERR 6
+int sz_head_stage(const sz_head* h, int what, uint64_t* addr, int64_t* bytes);
+
 #ifdef __cplusplus
 }
 #endif

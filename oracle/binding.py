@@ -89,6 +89,12 @@ def lib():
         L.szo_sample_top.restype = C.c_uint32
         L.szo_sample_top.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_uint64]
         L.szo_generate.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+        L.szo_head_rotate.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
+        L.szo_head_proxy_build.argtypes = [C.c_size_t, C.c_size_t, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.szo_proxy_quant_x.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.szo_proxy_bmax.argtypes = [C.c_size_t, C.c_size_t, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+        L.szo_head_k_use.argtypes = [C.c_int, C.c_int]
+        L.szo_proxy_pick.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
         _LIB = L
     return _LIB
 
@@ -291,3 +297,57 @@ def lookup(hist, k, lens=(3, 2)):
     out = np.zeros(max(k, 1), dtype=np.uint32)
     n = lib().szo_lookup(_p(h), len(hist), k, _p(ls), len(lens), _p(out))
     return [int(t) for t in out[:n]]
+
+
+# ---- part 3: the lm_head's 2-bit screening proxy --------------------------------------------------------------------------------
+
+def head_proxy_build(rows, cols, bits, blob):
+    """(w_q2 uint8 [rows * cols / 4], w_sc uint16 [rows * cols / 128]) of an EXL3 output.weight blob."""
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    assert blob.size == exl3_blob_len(cols, rows, bits)
+    q2 = np.empty(rows * cols // 4, dtype=np.uint8)
+    sc = np.empty(rows * cols // 128, dtype=np.uint16)
+    lib().szo_head_proxy_build(rows, cols, bits, _p(blob), _p(q2), _p(sc))
+    return q2, sc
+
+
+def head_rotate(blob, x):
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    blob = np.ascontiguousarray(blob, dtype=np.uint8)
+    xr = np.empty_like(x)
+    for j in range(x.shape[0]):
+        lib().szo_head_rotate(_p(blob), _p(x[j]), x.shape[1], _p(xr[j]))
+    return xr
+
+
+def proxy_quant_x(xr):
+    """xr: [m, cols] -> (xq int8 [m, cols], x_sc f32 [m, cols / 128], x_corr f32 [m, cols / 128])."""
+    xr = np.ascontiguousarray(xr, dtype=np.float32)
+    m, cols = xr.shape
+    xq = np.empty((m, cols), dtype=np.int8)
+    sc = np.empty((m, cols // 128), dtype=np.float32)
+    corr = np.empty((m, cols // 128), dtype=np.float32)
+    for j in range(m):
+        lib().szo_proxy_quant_x(_p(xr[j]), cols, _p(xq[j]), _p(sc[j]), _p(corr[j]))
+    return xq, sc, corr
+
+
+def proxy_bmax(rows, cols, q2, sc, xq, x_sc, x_corr):
+    m = xq.shape[0]
+    out = np.empty((m, rows // 128), dtype=np.float32)
+    for j in range(m):
+        lib().szo_proxy_bmax(rows, cols, _p(q2), _p(sc), _p(np.ascontiguousarray(xq[j])), _p(np.ascontiguousarray(x_sc[j])),
+                             _p(np.ascontiguousarray(x_corr[j])), _p(out[j]))
+    return out
+
+
+def head_k_use(k_blk, need_k):
+    return lib().szo_head_k_use(k_blk, need_k)
+
+
+def proxy_pick(bmax, k_use, max_sel):
+    bmax = np.ascontiguousarray(bmax, dtype=np.float32)
+    m, n_ob = bmax.shape
+    sel = np.empty(max(max_sel, 1), dtype=np.uint32)
+    n = lib().szo_proxy_pick(_p(bmax), m, n_ob, k_use, max_sel, _p(sel))
+    return sel[:n].copy()

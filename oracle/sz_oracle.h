@@ -124,6 +124,15 @@ typedef struct { int32_t n_tokens, passes, drafted, accepted, lookup_passes; int
 int szo_generate(szo_session* s, const uint32_t* prompt, int n_prompt, const szo_gen_params* p, uint32_t* out, int32_t* pass_log,
                  int pass_cap, szo_gen_stats* stats);
 
+/* ---- part 3 (sz_oracle_head.c): the lm_head's 2-bit screening proxy and block selection (GPU-only in the reference) ---- */
+void szo_head_rotate(const uint8_t* blob, const float* x, size_t cols, float* xr);                       /* kernels/exl3.cu:609-625 */
+void szo_head_proxy_build(size_t rows, size_t cols, int bits, const uint8_t* blob, uint8_t* w_q2, uint16_t* w_sc); /* exl3.cu:915-987 */
+void szo_proxy_quant_x(const float* xr, size_t cols, int8_t* xq, float* x_sc, float* x_corr);            /* kernels/forward.cu:4369-4420 */
+void szo_proxy_bmax(size_t rows, size_t cols, const uint8_t* w_q2, const uint16_t* w_sc, const int8_t* xq, const float* x_sc,
+                    const float* x_corr, float* bmax);                                                   /* kernels/forward.cu:4428-4495 */
+int szo_head_k_use(int k_blk, int need_k);                                                               /* session.rs:5964 */
+int szo_proxy_pick(const float* bmax, int m, int n_ob, int k_use, int max_sel, uint32_t* sel);           /* kernels/forward.cu:4536-4632 */
+
 #ifdef __cplusplus
 }
 #endif

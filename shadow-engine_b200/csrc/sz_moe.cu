@@ -263,6 +263,8 @@ sz_route_kernel(const float* __restrict__ x, int H, const float* __restrict__ ro
         plan_sh->expert[0] = 0;
         plan_sh->count[0] = M;
         ctrl[0] = 0;  // ready for the next call
+        ctrl[2] = 0;  // the unit counters of the streaming expert kernels
+        ctrl[3] = 0;
     }
     SZ_PH();  // 6 plan written
     SZ_PH_FLUSH(0, true);

@@ -17,6 +17,7 @@
 
 #define SZ_X3_THREADS 256
 #define SZ_X3_STAGES 4
+#define SZ_X3_TICKET 2   // ctrl[2]: the unit counter of the gate / up kernel, ctrl[3]: of the down kernel (the router kernel clears both)
 #define SZ_FIX_SCALE 17179869184.0f           // 2^34
 #define SZ_FIX_INV (1.0 / 17179869184.0)
 
@@ -182,9 +183,13 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     const int NG = D + (sh_gate ? 1 : 0);
     const int NS = H / 128;
     const long long U = (long long)NG * NS * 2;
-    const int u0 = (int)(U * blockIdx.x / gridDim.x), u1 = (int)(U * (blockIdx.x + 1) / gridDim.x);
-    const int count = u1 - u0;
-    if (count <= 0) return;
+    // Which units a block takes.  Few units (a pass of one or two rows): a fixed contiguous share, so that nobody ends up with three
+    // where others have one.  Many: the first unit is the block's number, the rest are drawn from a counter as the block goes, so
+    // that blocks which got heavier units (more rows a group) or a slower start take fewer and all blocks end together.
+    const bool dyn = U >= 3LL * gridDim.x;
+    const int u0 = dyn ? (int)blockIdx.x : (int)(U * blockIdx.x / gridDim.x);
+    const int u1 = dyn ? (int)U : (int)(U * (blockIdx.x + 1) / gridDim.x);
+    if (u0 >= u1) return;
     const size_t hdr = 2 * (size_t)H + 2 * (size_t)FF + 4;
 
     auto unit = [&](int u) {
@@ -205,13 +210,14 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
         d.in_off = s * 128 + (mat << 30);  // bit 30 carries the matrix index
         return d;
     };
-    constexpr int UD0 = 12;
-    __shared__ const u8* usrc[UD0];  // (filled with the descriptors below)
-    auto issue = [&](int i) {  // thread 0: start unit i's copy into stage i % STAGES
-        const u8* src = i < UD0 ? usrc[i] : unit(u0 + i).src;
+    // the block's i-th unit lives in slot i % RING: its number (-1: the block has no i-th unit) and its description
+    constexpr int RING = 16, LA = SZ_X3_STAGES - 1;
+    __shared__ SzX3Unit ud[RING];
+    __shared__ int uid[RING];
+    auto issue = [&](int i) {  // thread 0: start the copy of the block's i-th unit into stage i % STAGES
         u64* bar = &bars[i % SZ_X3_STAGES];
         sz_mbar_expect_tx(bar, X::STAGE_BYTES);
-        sz_bulk_g2s(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, src, X::STAGE_BYTES, bar);
+        sz_bulk_g2s(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, ud[i % RING].src, X::STAGE_BYTES, bar);
     };
     auto prep_load = [&](const SzX3Unit& d, float* v) {  // warp t: row t of the group times suh, element lane + 32 e
         if (warp < d.n) {
@@ -222,16 +228,32 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
                 v[e] = __ldg(x + (size_t)row * H + off + lane + 32 * e) * sz_f16_to_f32(__ldg(d.suh + lane + 32 * e));
         }
     };
-
-    // the block's unit descriptors, worked out once and in parallel (divisions, plan look-ups, 64-bit address arithmetic)
-    constexpr int UD = 12;
-    __shared__ SzX3Unit ud[UD];
-    if (threadIdx.x < UD && threadIdx.x < count) { ud[threadIdx.x] = unit(u0 + threadIdx.x); usrc[threadIdx.x] = ud[threadIdx.x].src; }
-    __syncthreads();
-    auto unit_at = [&](int i) { return i < UD ? ud[i] : unit(u0 + i); };
-    if (threadIdx.x == 0)
-        for (int i = 0; i < SZ_X3_STAGES - 1 && i < count; i++) issue(i);
-    SzX3Unit cur = unit_at(0);
+    u32 pending = 0xffffffffu;  // thread 0, dynamic mode: the ticket asked for one round ago (for slot i + LA of round i)
+    if (!dyn) {  // every slot now, in parallel (the static share is at most RING - 2 units long)
+        if (threadIdx.x < RING) {
+            const int u = u0 + threadIdx.x;
+            uid[threadIdx.x] = u < u1 ? u : -1;
+            if (u < u1) ud[threadIdx.x] = unit(u);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0)
+            for (int i = 0; i < LA && uid[i] >= 0; i++) issue(i);
+    } else {
+        if (threadIdx.x == 0) {
+            u32 t[LA];
+            for (int i = 1; i < LA; i++) t[i] = atomicAdd(&ctrl[SZ_X3_TICKET], 1u) + gridDim.x;
+            pending = atomicAdd(&ctrl[SZ_X3_TICKET], 1u) + gridDim.x;
+            uid[0] = u0; ud[0] = unit(u0);
+            issue(0);
+            for (int i = 1; i < LA; i++) {
+                const bool ok = t[i] < (u32)U;
+                uid[i] = ok ? (int)t[i] : -1;
+                if (ok) { ud[i] = unit((int)t[i]); issue(i); }
+            }
+        }
+        __syncthreads();
+    }
+    SzX3Unit cur = ud[0];
     {
         float v[4];
         prep_load(cur, v);
@@ -239,12 +261,27 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     }
     __syncthreads();
     SZ_PH();  // 2 first fragments
-    int failed = 0;
-    for (int i = 0; i < count; i++) {
-        if (threadIdx.x == 0 && i + SZ_X3_STAGES - 1 < count) issue(i + SZ_X3_STAGES - 1);
+    int failed = 0, count = 0;
+    for (int i = 0; uid[i % RING] >= 0; i++) {
+        count++;
+        if (threadIdx.x == 0) {  // slot i + LA: read by everybody from round i + LA - 1 on, two barriers from here
+            const int sl = (i + LA) % RING;
+            if (dyn) {
+                const bool ok = pending < (u32)U;
+                uid[sl] = ok ? (int)pending : -1;
+                if (ok) {
+                    ud[sl] = unit((int)pending);
+                    issue(i + LA);
+                    pending = atomicAdd(&ctrl[SZ_X3_TICKET], 1u) + gridDim.x;  // (its value is not looked at before the next round)
+                }
+            } else if (i + LA < RING ? uid[sl] >= 0 : false) {
+                issue(i + LA);
+            }
+        }
+        const bool more = uid[(i + 1) % RING] >= 0;
         SzX3Unit nxt = cur;
         float v[4];
-        if (i + 1 < count) { nxt = unit_at(i + 1); prep_load(nxt, v); }
+        if (more) { nxt = ud[(i + 1) % RING]; prep_load(nxt, v); }
         if (i == 1) SZ_PH();  // unit 1: start
         if (!sz_mbar_wait(&bars[i % SZ_X3_STAGES], (i / SZ_X3_STAGES) & 1)) failed = 1;
         if (i == 1) SZ_PH();  // unit 1: data arrived
@@ -268,7 +305,7 @@ sz_x3_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
             }
         }
         if (i == 1) SZ_PH();  // unit 1: atomics issued
-        if (i + 1 < count) sz_x3_store_frag(frags + ((i + 1) & 1) * 256, warp, nxt.n, v, lane);
+        if (more) sz_x3_store_frag(frags + ((i + 1) & 1) * 256, warp, nxt.n, v, lane);
         if (i == 1) SZ_PH();  // unit 1: next fragments stored
         cur = nxt;
         if (__syncthreads_or(failed)) { failed = 1; break; }
@@ -401,16 +438,23 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
     }
     __syncthreads();
     int failed = 0;
+    int fb = 0;  // which of the two fragment buffers holds the current unit's input
     for (int i = 0; i < count; i++) {
         if (threadIdx.x == 0 && i + SZ_X3_STAGES - 1 < count) issue(i + SZ_X3_STAGES - 1);
         DUnit nxt = cur;
         long long ag[4], au[4];
         float sc[12];
-        if (i + 1 < count) { nxt = unit_at(i + 1); prep_load(nxt, ag, au, sc); }
+        // the output chunks of one (group, input block) follow one another and share their input: it is prepared once
+        bool fresh = false;
+        if (i + 1 < count) {
+            nxt = unit_at(i + 1);
+            fresh = nxt.kb != cur.kb || nxt.suh != cur.suh;
+            if (fresh) prep_load(nxt, ag, au, sc);
+        }
         if (!sz_mbar_wait(&bars[i % SZ_X3_STAGES], (i / SZ_X3_STAGES) & 1)) failed = 1;
         float c[4][4];
         if (!failed) {
-            sz_x3_compute<K, 4>(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, frags + (i & 1) * 256, warp, lane, c);
+            sz_x3_compute<K, 4>(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, frags + fb * 256, warp, lane, c);
             const int q = lane & 3, g8 = lane >> 2;
 #pragma unroll
             for (int tt = 0; tt < 2; tt++) {
@@ -426,7 +470,7 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
                 }
             }
         }
-        if (i + 1 < count) prep_store(nxt, ag, au, sc, frags + ((i + 1) & 1) * 256);
+        if (fresh) { prep_store(nxt, ag, au, sc, frags + (fb ^ 1) * 256); fb ^= 1; }
         cur = nxt;
         if (__syncthreads_or(failed)) { failed = 1; break; }
     }
@@ -437,7 +481,7 @@ sz_x3_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
 // y[j] = sum over ranks of w * (H eo * svh) + sigmoid(shared gate logit) * (H so * svh_shared).  A block a (row, 128-output block);
 // warp t finishes rank t's contribution (warp top_k: the shared expert's), then warp 0 adds them in rank order in f64.
 // so_f32 != null: the shared expert's output comes finished (f32 [m][H]) from the generic kernels instead of the accumulators.
-__global__ void __launch_bounds__((SZ_MAX_TOPK + 1) * 32)
+static __global__ void __launch_bounds__((SZ_MAX_TOPK + 1) * 32)
 sz_x3_combine_kernel(const long long* __restrict__ out, const int32_t* __restrict__ ridx, const double* __restrict__ rw,
                      const u8* __restrict__ down, u64 dstride, const u8* __restrict__ sh_down, const float* __restrict__ so_f32,
                      const float* __restrict__ logits, int ne, int top_k, int m, int H, int FF, int has_shared, float* __restrict__ y,

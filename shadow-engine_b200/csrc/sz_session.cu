@@ -652,7 +652,7 @@ static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
     a.job[0] = sz_job(s->model.output, s->logits, c.vocab);
     if ((rc = sz_dense_launch(a, st, "lm_head"))) return rc;
     const int nb = (c.vocab + SZ_TK_N - 1) / SZ_TK_N;
-    SZ_CUDA(sz_launch("topk_slices", sz_topk_slices_kernel, dim3(nb, m), dim3(256), 0, st, true, (const float*)s->logits, (int)c.vocab, (int)c.vocab, nb, s->tk_tmp));
+    SZ_CUDA(sz_launch("topk_slices", sz_topk_slices_kernel, dim3(nb, m), dim3(256), 0, st, true, (const float*)s->logits, (int)c.vocab, (int)c.vocab, nb, s->tk_tmp, (const u32*)nullptr));
     SZ_CUDA(sz_launch("topk_merge", sz_topk_merge_kernel, dim3(m), dim3(256), 0, st, true, (const u64*)s->tk_tmp, nb, s->top));
     return SZ_OK;
 }

@@ -5,6 +5,7 @@
 #pragma once
 
 #include "sz_dense.cuh"
+#include "sz_topk.cuh"
 
 #ifdef __CUDACC__
 
@@ -1061,111 +1062,6 @@ sz_attn_merge_kernel(const float* __restrict__ part, const float* __restrict__ g
         float v = 0.f;
         for (int q = 0; q < ngrp; q++) v += accs[q][t];
         o[((size_t)j * nh + h) * hd + t] = (v / z) * sz_sigmoid(g);
-    }
-}
-
-// ---- top-64 of each row of logits: largest first, ties to the lower id, NaN as -inf (the order of kernels/forward.cu:3565-3625).
-// A key packs (orderable value bits, ~id) so that one 64-bit descending sort gives that order.
-#define SZ_TK_N 4096
-__device__ __forceinline__ u64 sz_tk_key(float v, u32 id) {
-    if (v != v) v = -INFINITY;
-    u32 b = __float_as_uint(v);
-    b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-    return ((u64)b << 32) | (u64)(0xffffffffu - id);
-}
-__device__ __forceinline__ void sz_tk_unkey(u64 k, float& v, u32& id) {
-    u32 b = (u32)(k >> 32);
-    b = (b & 0x80000000u) ? (b & 0x7fffffffu) : ~b;
-    v = __uint_as_float(b);
-    id = 0xffffffffu - (u32)k;
-}
-// The 64 best of up to 16 * 256 keys held 16 a thread, written sorted (descending) to dst[0..64).  Instead of sorting everything:
-// the 64th best of the 256 per-thread maxima is a floor under the 64th best key (64 keys are at least that large), so only keys at
-// or above it can be among the winners - at most 64 threads x 16 keys, typically ~70 - and only those are sorted.
-// sm: 256 keys (the maxima); cand: 1024 keys; cnt: one counter.  All 256 threads call it.
-__device__ __forceinline__ void sz_tk_select(const u64* key, u64* sm, u64* cand, int* cnt, u64* dst) {
-    const int t = threadIdx.x;
-    u64 mx = key[0];
-#pragma unroll
-    for (int i = 1; i < 16; i++) mx = key[i] > mx ? key[i] : mx;
-    sm[t] = mx;
-    if (t == 0) *cnt = 0;
-    __syncthreads();
-    // rank of this thread's maximum among the 256 (ties - only padding keys can tie - by thread number)
-    int rank = 0;
-    for (int i = 0; i < 256; i += 2) {
-        const ulonglong2 o = *(const ulonglong2*)(sm + i);
-        rank += (o.x > mx || (o.x == mx && i < t)) + (o.y > mx || (o.y == mx && i + 1 < t));
-    }
-    __syncthreads();
-    if (rank == 63) sm[0] = mx;
-    __syncthreads();
-    const u64 floor64 = sm[0];
-#pragma unroll
-    for (int i = 0; i < 16; i++)
-        if (key[i] >= floor64) cand[atomicAdd(cnt, 1)] = key[i];
-    __syncthreads();
-    const int c = *cnt;  // 64 <= c <= 1024
-    int p = 64;
-    while (p < c) p <<= 1;
-    for (int i = c + t; i < p; i += 256) cand[i] = 0ull;  // below every real key
-    __syncthreads();
-    for (int k = 2; k <= p; k <<= 1)
-        for (int jj = k >> 1; jj > 0; jj >>= 1) {
-            for (int i = t; i < p; i += 256) {
-                const int l = i ^ jj;
-                if (l > i) {
-                    const bool up = (i & k) == 0;
-                    const u64 a = cand[i], b = cand[l];
-                    if (up ? (b > a) : (a > b)) { cand[i] = b; cand[l] = a; }
-                }
-            }
-            __syncthreads();
-        }
-    if (t < 64) dst[t] = cand[t];
-}
-
-// grid (nb, m): slice blk of row j -> its 64 best keys, sorted, at tmp[(j * nb + blk) * 64]
-__global__ void __launch_bounds__(256)
-sz_topk_slices_kernel(const float* __restrict__ logits, int vocab, int ls, int nb, u64* __restrict__ tmp) {
-    __shared__ __align__(16) u64 sm[256];
-    __shared__ u64 cand[1024];
-    __shared__ int cnt;
-    sz_pdl_wait();
-    sz_pdl_trigger();
-    const int blk = blockIdx.x, j = blockIdx.y;
-    const float* r = logits + (size_t)j * ls;
-    u64 key[16];
-#pragma unroll
-    for (int q = 0; q < 16; q++) {
-        const int i = blk * SZ_TK_N + threadIdx.x + 256 * q;
-        key[q] = i < vocab ? sz_tk_key(__ldcg(r + i), (u32)i) : sz_tk_key(-INFINITY, 0xffffffffu);
-    }
-    sz_tk_select(key, sm, cand, &cnt, tmp + ((size_t)j * nb + blk) * 64);
-}
-// grid (m): out row j = 64 value bit patterns then 64 ids (crates/shadowzero-cuda/src/session.rs:6034-6039); nb * 64 <= 4096
-__global__ void __launch_bounds__(256)
-sz_topk_merge_kernel(const u64* __restrict__ tmp, int nb, u32* __restrict__ out) {
-    __shared__ __align__(16) u64 sm[256];
-    __shared__ u64 cand[1024];
-    __shared__ u64 best[64];
-    __shared__ int cnt;
-    sz_pdl_wait();
-    sz_pdl_trigger();
-    const int j = blockIdx.x;
-    u64 key[16];
-#pragma unroll
-    for (int q = 0; q < 16; q++) {
-        const int i = threadIdx.x + 256 * q;
-        key[q] = i < nb * 64 ? __ldcg(tmp + (size_t)j * nb * 64 + i) : sz_tk_key(-INFINITY, 0xffffffffu);
-    }
-    sz_tk_select(key, sm, cand, &cnt, best);
-    __syncthreads();
-    if (threadIdx.x < 64) {
-        float v; u32 id;
-        sz_tk_unkey(best[threadIdx.x], v, id);
-        out[(size_t)j * 128 + threadIdx.x] = __float_as_uint(v);
-        out[(size_t)j * 128 + 64 + threadIdx.x] = id;
     }
 }
 

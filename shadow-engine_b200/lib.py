@@ -31,6 +31,14 @@ class MoeLayerC(C.Structure):
                 ("ep_first", C.c_int32), ("ep_count", C.c_int32), ("ep_shared", C.c_int32), ("ep_reserved", C.c_int32)]
 
 
+class HeadC(C.Structure):
+    """struct sz_head"""
+    _fields_ = [("rows", C.c_int32), ("cols", C.c_int32), ("bits", C.c_int32), ("k_blk", C.c_int32),
+                ("weight", C.c_uint64), ("w_q2", C.c_uint64), ("w_sc", C.c_uint64), ("work", C.c_uint64), ("work_bytes", C.c_int64)]
+
+
+HEAD_XR, HEAD_XQ, HEAD_XSC, HEAD_XCORR, HEAD_BMAX, HEAD_SEL, HEAD_ERR = range(7)
+
 # name -> (restype, argtypes); every symbol include/shadowzero_b200.h declares
 SYMBOLS = {
     "sz_version": (C.c_char_p, []),
@@ -106,6 +114,13 @@ SYMBOLS = {
     "sz_ep_p2p_status": (C.c_int, [C.POINTER(C.c_int)]),
     "sz_moe_finish_exchange": (C.c_int, [C.POINTER(MoeLayerC), C.c_int, C.c_uint64, C.c_uint64]),
     "sz_moe_static_scratch_max": (C.c_int, [C.POINTER(C.c_int64)]),
+    "sz_head_proxy_bytes": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "sz_head_work_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64)]),
+    "sz_head_work_init": (C.c_int, [C.POINTER(HeadC), C.c_uint64]),
+    "sz_head_proxy_build": (C.c_int, [C.POINTER(HeadC), C.c_uint64]),
+    "sz_head_plan": (C.c_int, [C.POINTER(HeadC), C.c_int, C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.POINTER(C.c_int64)]),
+    "sz_head_top": (C.c_int, [C.POINTER(HeadC), C.c_uint64, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64]),
+    "sz_head_stage": (C.c_int, [C.POINTER(HeadC), C.c_int, C.POINTER(C.c_uint64), C.POINTER(C.c_int64)]),
     "sz_moe_verify_static": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64]),
 }
 
