@@ -157,7 +157,9 @@ def run_c3(args):
             peer = ep.PeerExchange(C3["hidden"])
     hbm, peak_kind = peaks()
     cfg = dict(C3, n_layer=args.n_layer)
-    M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha)
+    head_type = szlib.TYPE_Q8_0 if args.head == "q8" else szlib.TYPE_EXL3(4)
+    M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha,
+                      head_type=head_type)
     dm = md.DeviceModel(M, device, ep=(rank, world) if world > 1 else None)
     # every tensor outside the experts is read once a pass, except the embedding table (m rows gathered)
     dense_bytes = sum(t[3].numel() * t[3].element_size() for n, t in M["tensors"].items() if n != "token_embd.weight")
@@ -167,7 +169,7 @@ def run_c3(args):
     ctx = args.ctx
     K, W = args.steps, max(args.warmup, 3)
     max_new = 4 * (3 * K + W + 64) + 64
-    sess = md.Session(dm, ctx + max_new + 64, kv_q8=True)
+    sess = md.Session(dm, ctx + max_new + 64, kv_q8=True, head_proxy=args.head == "proxy")
     _, cyc = md.token_cycles(cfg["vocab"], 1)
     n_prompt = 256
     prompt = md.make_prompt(n_prompt, cfg["vocab"], seed=1, cycles=cyc)
@@ -309,6 +311,7 @@ def run_c3(args):
         "data": "synthetic",
         "config": {"workload": "c3", "n_layer": cfg["n_layer"], "hidden": cfg["hidden"], "n_expert": cfg["n_expert"], "top_k": cfg["n_expert_used"],
                    "expert_ff": cfg["expert_ff"], "vocab": cfg["vocab"], "experts": "exl3-3bit", "dense": "q8_0", "kv": "q8_kv",
+                   "head": {"q8": "q8_0, read in full", "exl3": "exl3-4bit, read in full", "proxy": "exl3-4bit screened by its 2-bit proxy (128 blocks a row)"}[args.head],
                    "context": ctx, "spec_k": 3, "batch": 1, "greedy": True, "cycle_alpha": args.alpha,
                    "parallelism": "ep%d" % world if world > 1 else "single", "exchange": args.exchange if world > 1 else None,
                    "l2": "inputs larger than L2: a pass streams ~%.1f GB of weights and cache" % (by["all"] / 1e9)},
@@ -547,6 +550,8 @@ def main():
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="c3, N > 1: the expert-parallel exchange - stores into the peers' memory from the combine kernel (default) or an NCCL all-reduce")
     ap.add_argument("--profile-passes", type=int, default=0, help="c3: only run this many 4-row verify passes (for ncu), no timing")
+    ap.add_argument("--head", default="q8", choices=["q8", "exl3", "proxy"],
+                    help="c3: output.weight as Q8_0 read in full, as 4-bit EXL3 read in full, or EXL3 screened by its 2-bit proxy (Q2_P)")
     ap.add_argument("--ctx", type=int, default=C3_CTX, help="c3: context length the decode runs at")
     ap.add_argument("--n-layer", type=int, default=C3["n_layer"], help="c3: layers (a smaller model for a quick check; not the benchmark)")
     ap.add_argument("--format", default="exl3", choices=["exl3", "iq3_s", "q8_0"])

@@ -169,6 +169,8 @@ typedef struct sz_model {
  * states (two copies: a pass never overwrites the state it started from, so a rejection needs no snapshot), and every scratch
  * buffer.  flags: SZ_KV_Q8 keeps K and V as packed per-32 int8 + f16 scales (kernels/forward.cu:3652-3687); 0 keeps f32. */
 #define SZ_KV_Q8 1
+#define SZ_HEAD_PROXY 2     /* output.weight is an EXL3 blob and the head is screened by its 2-bit proxy (see sz_head below); without the
+                             * flag an EXL3 output.weight is evaluated in full.  Blocks kept a row: 128, or the environment's SZ_HEAD_KBLK */
 #define SZ_ACCEPT_NONE 0    /* the caller decides: read the top-64 of every row, then sz_session_commit(keep) */
 #define SZ_ACCEPT_GREEDY 1  /* on the device: keep row i + 1 while row i's best token is the drafted ids[i + 1] (engine.rs:2377-2408) */
 #define SZ_ACCEPT_ALL 2     /* prompt rows: all kept */

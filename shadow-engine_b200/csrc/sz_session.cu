@@ -60,6 +60,7 @@ struct sz_session {
     int use_graphs;
     std::map<int, cudaGraphExec_t> graphs;
     int ep_graphs = 0;      // how many of them recorded a collective of the expert-parallel communicator
+    sz_head head = {};      // rows > 0: output.weight is an EXL3 blob and the head runs through sz_head_top
     ~sz_session() {
         for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
         sz_ep_graph_refs(-ep_graphs);
@@ -71,10 +72,27 @@ static int sz_is_attn(const sz_model_config& c, int l) { return l % c.attn_inter
 
 struct SzSessLayout {
     int64_t r, r2, hc_acc, rope, rn, hdown, mix, u, g, y, d_xin, d_z, d_b, d_a, d_xc, d_beta, d_decay, d_og, S0, S1, conv0, conv1, a_qg, a_k, a_v, a_q, a_gate,
-        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, total;
-    int64_t moe_bytes, S_bytes, conv_bytes, kv_bytes;
+        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, head_q2, head_sc, head_work, total;
+    int64_t moe_bytes, S_bytes, conv_bytes, kv_bytes, head_work_bytes;
     int splits, splits2;
 };
+
+// output.weight as an EXL3 blob: the head is sz_head_top's (dense, or screened by the 2-bit proxy with SZ_HEAD_PROXY).
+static bool sz_head_is_exl3(const sz_model* m) { return m->output.type > 1020 && m->output.type <= 1028; }
+static int sz_head_describe(const sz_model* m, int flags, sz_head* h) {
+    *h = sz_head();
+    if (!sz_head_is_exl3(m)) {
+        if (flags & SZ_HEAD_PROXY) return sz_fail(SZ_E_ARG, "SZ_HEAD_PROXY needs an EXL3 output.weight (type %d given)", m->output.type);
+        return SZ_OK;
+    }
+    h->rows = m->cfg.vocab; h->cols = m->cfg.hidden; h->bits = m->output.type - 1020;
+    h->weight = m->output.data;
+    if (flags & SZ_HEAD_PROXY) {
+        const char* e = getenv("SZ_HEAD_KBLK");  // blocks kept a row (the reference's SHADOWZERO_HEAD_KBLK, session.rs:2655)
+        h->k_blk = e && atoi(e) > 0 ? atoi(e) : 128;
+    }
+    return SZ_OK;
+}
 
 static int64_t up256(int64_t v) { return (v + 255) & ~(int64_t)255; }
 
@@ -131,6 +149,21 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
     }
     L->moe_bytes = moe_bytes;
     L->moe = take(moe_bytes);
+    L->head_q2 = L->head_sc = L->head_work = 0;
+    L->head_work_bytes = 0;
+    sz_head hd;
+    int hrc = sz_head_describe(m, flags, &hd);
+    if (hrc) return hrc;
+    if (hd.rows > 0) {
+        if ((hrc = sz_head_work_bytes(hd.rows, hd.cols, hd.k_blk, &L->head_work_bytes))) return hrc;
+        L->head_work = take(L->head_work_bytes);
+        if (hd.k_blk > 0) {
+            int64_t q2 = 0, sc = 0;
+            if ((hrc = sz_head_proxy_bytes(hd.rows, hd.cols, &q2, &sc))) return hrc;
+            L->head_q2 = take(q2);
+            L->head_sc = take(sc);
+        }
+    }
     L->total = o;
     return SZ_OK;
 }
@@ -180,7 +213,9 @@ static int sz_model_check(const sz_model* m) {
         return SZ_OK;
     };
     if ((rc = sz_dense_check(&m->token_embd, "token_embd", c.vocab, H))) return rc;
-    if ((rc = sz_dense_check(&m->output, "output", c.vocab, H))) return rc;
+    if (sz_head_is_exl3(m)) {
+        if (!m->output.data || m->output.rows != c.vocab || m->output.cols != H) return sz_fail(SZ_E_ARG, "output: expected a [%d -> %d] tensor", H, (int)c.vocab);
+    } else if ((rc = sz_dense_check(&m->output, "output", c.vocab, H))) return rc;
     if ((rc = hc(m->output_hc, "output_hc", false))) return rc;
     for (int l = 0; l < c.n_layer; l++) {
         const sz_layer& L = m->layers[l];
@@ -286,6 +321,12 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->ids = (int32_t*)(b + L.ids); s->res = (int32_t*)(b + L.res); s->state = (int32_t*)(b + L.state); s->routes = (int32_t*)(b + L.routes); s->route_w = (double*)(b + L.route_w);
     s->moe_scratch = b + L.moe; s->moe_scratch_bytes = L.moe_bytes;
     s->attn_splits = L.splits; s->attn_splits2 = L.splits2;
+    if ((rc = sz_head_describe(m, flags, &s->head))) { delete s; return rc; }
+    if (s->head.rows > 0) {
+        s->head.work = (uint64_t)(b + L.head_work); s->head.work_bytes = L.head_work_bytes;
+        if (s->head.k_blk > 0) { s->head.w_q2 = (uint64_t)(b + L.head_q2); s->head.w_sc = (uint64_t)(b + L.head_sc); }
+        if ((rc = sz_head_work_init(&s->head, stream)) || (s->head.k_blk > 0 && (rc = sz_head_proxy_build(&s->head, stream)))) { delete s; return rc; }
+    }
     if ((rc = sz_session_reset(s, stream))) { delete s; return rc; }
     if (m->cfg.rope_dims > 0) {  // forward.rs:290-299: angle = pos / theta^(2 i / rope_dims); the denominators never change
         std::vector<double> den(m->cfg.rope_dims / 2);
@@ -646,6 +687,7 @@ static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
     }
     if (!head) return SZ_OK;  // the last write only matters to the output read; the next pass starts from the embedding
     if ((rc = sz_hc_read(s, st, s->model.output_hc, m, pending, false))) return rc;
+    if (s->head.rows > 0) return sz_head_top(&s->head, (uint64_t)s->u, H, m, 64, (uint64_t)s->logits, (uint64_t)s->top, (uint64_t)st);
     SzDenseArgs a = {};
     a.err = (u32*)(s->state + 2);
     a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 1;
@@ -742,15 +784,25 @@ extern "C" int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* to
     cudaStream_t st = (cudaStream_t)stream;
     if (keep_next) SZ_CUDA(cudaMemcpyAsync(keep_next, s->res, 8, cudaMemcpyDeviceToHost, st));
     if (top) SZ_CUDA(cudaMemcpyAsync(top, s->top, (size_t)s->last_m * 128 * 4, cudaMemcpyDeviceToHost, st));
+    if (logits && s->head.k_blk > 0)
+        return sz_fail(SZ_E_ARG, "sz_session_result: with the screened head (SZ_HEAD_PROXY) only the kept blocks have logits; ask for the top-64");
     if (logits) SZ_CUDA(cudaMemcpyAsync(logits, s->logits, (size_t)s->last_m * s->model.cfg.vocab * 4, cudaMemcpyDeviceToHost, st));
+    s->h_pin[12] = 0;
+    if (s->head.rows > 0) {
+        uint64_t at = 0;
+        int64_t nb = 0;
+        const int hrc = sz_head_stage(&s->head, SZ_HEAD_ERR, &at, &nb);
+        if (hrc) return hrc;
+        SZ_CUDA(cudaMemcpyAsync(s->h_pin + 12, (const void*)at, 4, cudaMemcpyDeviceToHost, st));
+    }
     // the error words the kernels raise when one of their bounded waits runs out: [10] the session's kernels, [11] the MoE kernels
     SZ_CUDA(cudaMemcpyAsync(s->h_pin + 10, s->state + 2, 4, cudaMemcpyDeviceToHost, st));
     SZ_CUDA(cudaMemcpyAsync(s->h_pin + 11, s->moe_scratch + 4, 4, cudaMemcpyDeviceToHost, st));
     SZ_CUDA(cudaStreamSynchronize(st));
     s->inflight = 0;
-    if (s->h_pin[10] || s->h_pin[11])
-        return sz_fail(SZ_E_DEVICE, "a bounded wait on an asynchronous copy ran out (session word %d, MoE word %d): the results of this pass are not valid",
-                       s->h_pin[10], s->h_pin[11]);
+    if (s->h_pin[10] || s->h_pin[11] || s->h_pin[12])
+        return sz_fail(SZ_E_DEVICE, "a bounded wait on an asynchronous copy ran out (session word %d, MoE word %d, head word %d): the results of this pass are not valid",
+                       s->h_pin[10], s->h_pin[11], s->h_pin[12]);
     return SZ_OK;
 }
 

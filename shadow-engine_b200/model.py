@@ -75,7 +75,7 @@ def token_cycles(vocab, seed, cycle=16):
 
 
 def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, shared_type=None, hc_type=szlib.TYPE_BF16, seed=1,
-               sigma=0.02, device="cpu", cycle=16, cycle_alpha=0.0):
+               sigma=0.02, device="cpu", cycle=16, cycle_alpha=0.0, head_type=None):
     """Seeded synthetic weights: name -> (ggml type, rows, cols, torch tensor of the stored bytes).  Matrices are N(0, sigma)
     quantised to their type, norm weights are 1, ssm_a is negative, MoE layers come from synth.make_moe_layer.
 
@@ -83,8 +83,14 @@ def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, sha
     matrix is correlated with the embedding through a seeded permutation of the vocabulary made of `cycle`-token cycles
     (row successor[t] of output.weight = alpha * embedding[t] + sqrt(1 - alpha^2) * noise: still N(0, sigma) entries): the model
     leans towards continuing the cycle of its last token, while the layers' contribution makes it leave the cycle now and then -
-    repeated n-grams with occasional surprises, which is what speculation is measured on."""
+    repeated n-grams with occasional surprises, which is what speculation is measured on.
+
+    head_type = TYPE_EXL3(k) stores output.weight as an EXL3 blob (random trellis words: no trellis quantiser is available, so
+    the head cannot be made from a wanted matrix).  The correlation then runs the other way: the embedding of token t is made
+    from the decoded row successor[t] of the head (CUDA device only: the decode is the library's)."""
     shared_type = expert_type if shared_type is None else shared_type
+    head_type = dense_type if head_type is None else head_type
+    head_exl3 = 1020 < head_type <= 1028
     H, Cs = cfg["hidden"], cfg["streams"]
     CH = Cs * H
     kd, vd = cfg["ssm_k_heads"] * cfg["ssm_head_dim"], cfg["ssm_v_heads"] * cfg["ssm_head_dim"]
@@ -118,7 +124,21 @@ def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, sha
         if inject:
             mat(prefix + "_inject.weight", Cs, CH, hc_type)
 
-    if cycle_alpha > 0.0:
+    if head_exl3:
+        bits = head_type - 1020
+        blob = synth.random_exl3_blobs(1, H, cfg["vocab"], bits, sigma, seed, "output.weight", device)[0]
+        T["output.weight"] = (head_type, cfg["vocab"], H, blob.contiguous())
+        if cycle_alpha > 0.0:
+            rows = synth.exl3_reconstruct(blob, H, cfg["vocab"], bits).t()          # [vocab, H]: row v = the head's weights of token v
+            rows = rows * (sigma / rows.std(dim=1, keepdim=True).clamp_min(1e-12))
+            succ, _ = token_cycles(cfg["vocab"], seed, cycle)
+            noise = synth.normal((cfg["vocab"], H), sigma, seed, "token_embd.weight", device)
+            emb = 15.0 * (cycle_alpha * rows[succ.to(rows.device)] + (1.0 - cycle_alpha ** 2) ** 0.5 * noise)
+            del rows, noise
+            T["token_embd.weight"] = (dense_type, cfg["vocab"], H, (synth.quantize_q8_0(emb) if dense_type == szlib.TYPE_Q8_0 else emb).contiguous())
+        else:
+            mat("token_embd.weight", cfg["vocab"], H, dense_type)
+    elif cycle_alpha > 0.0:
         # embedding rows 15x larger than the matrices' sigma, so that the token's identity is not drowned by the sublayers' outputs
         emb = synth.normal((cfg["vocab"], H), 15.0 * sigma, seed, "token_embd.weight", device)
         T["token_embd.weight"] = (dense_type, cfg["vocab"], H, (synth.quantize_q8_0(emb) if dense_type == szlib.TYPE_Q8_0 else emb).contiguous())
@@ -182,7 +202,7 @@ class _Placed:
         def tens(name):
             ty, rows, cols, b = T[name]
             t = Tensor()
-            t.type, t.rows, t.cols, t.data = ty, rows, cols, put(b)
+            t.type, t.rows, t.cols, t.data = ty, rows, cols, put(b, 12 if 1020 < ty <= 1028 else 0)  # an EXL3 blob: trellis on a 16-byte boundary
             return t
 
         def hc(prefix, inject):
@@ -215,7 +235,7 @@ class HostModel(_Placed):
     def __init__(self, M):
         self._keep = []
 
-        def put(b):
+        def put(b, lead=0):
             a = np.ascontiguousarray(b.detach().cpu().view(torch.uint8).numpy() if b.dtype == torch.bfloat16 else b.detach().cpu().numpy())
             self._keep.append(a)
             return a.ctypes.data
@@ -247,8 +267,8 @@ class DeviceModel(_Placed):
         self._keep = []
         self.ep = ep
 
-        def put(b):
-            buf, addr, _ = szmoe.place(b.reshape(1, -1), self.device, 0)
+        def put(b, lead=0):
+            buf, addr, _ = szmoe.place(b.reshape(1, -1), self.device, lead)
             self._keep.append(buf)
             return addr
 
@@ -264,10 +284,11 @@ class DeviceModel(_Placed):
 class Session:
     """A verify session on the GPU (struct sz_session): owns the one device block the library asks for."""
 
-    def __init__(self, dm, ctx, kv_q8=True, stream=None):
+    def __init__(self, dm, ctx, kv_q8=True, stream=None, head_proxy=False):
+        """head_proxy: screen an EXL3 output.weight with its 2-bit proxy (SZ_HEAD_PROXY); the proxy is built here."""
         self.lib = szlib.load()
         self.dm = dm
-        self.flags = 1 if kv_q8 else 0
+        self.flags = (1 if kv_q8 else 0) | (2 if head_proxy else 0)
         n = C.c_int64()
         szlib.check(self.lib.sz_session_bytes(C.byref(dm.model), ctx, self.flags, C.byref(n)))
         self.mem = torch.empty(n.value + 256, dtype=torch.uint8, device=dm.device)

@@ -118,6 +118,27 @@ def random_exl3_blobs(count, n_in, n_out, bits, sigma, seed, name, device="cpu")
     return out
 
 
+def exl3_reconstruct(blob, n_in, n_out, bits):
+    """W [n_in, n_out] float32 = diag(suh) H W_hat H diag(svh) of one EXL3 blob (a uint8 CUDA tensor), H = Hadamard(128) / sqrt(128)
+    on every 128-block of both axes (crates/shadowzero-model/src/exl3.rs:246-286).  The trellis is decoded by the library
+    (sz_exl3_reconstruct_inner); the rotations are two matrix products here.  For building synthetic models, not for parity."""
+    if blob.device.type != "cuda":
+        raise ValueError("exl3_reconstruct needs the blob on a CUDA device")
+    L = szlib.load()
+    blob = blob.contiguous()
+    w = torch.empty((n_in, n_out), dtype=torch.float32, device=blob.device)
+    szlib.check(L.sz_exl3_reconstruct_inner(bits, blob.data_ptr(), n_in, n_out, w.data_ptr(), torch.cuda.current_stream(blob.device).cuda_stream))
+    h = torch.ones((1, 1), dtype=torch.float32, device=blob.device)
+    while h.shape[0] < 128:
+        h = torch.cat([torch.cat([h, h], dim=1), torch.cat([h, -h], dim=1)], dim=0)
+    h = h / 128 ** 0.5
+    suh = blob[:2 * n_in].view(torch.float16).to(torch.float32)
+    svh = blob[2 * n_in:2 * n_in + 2 * n_out].view(torch.float16).to(torch.float32)
+    w = (w.reshape(n_in, n_out // 128, 128) @ h).reshape(n_in, n_out)                 # output side
+    w = (h @ w.reshape(n_in // 128, 128, n_out)).reshape(n_in, n_out)                 # input side (H is symmetric)
+    return w * suh[:, None] * svh[None, :]
+
+
 def matrix_bytes(ty, n_in, n_out):
     if ty == szlib.TYPE_Q8_0:
         return n_out * (n_in // 32) * 34

@@ -66,3 +66,35 @@ def test_compute_calls_refuse_bad_arguments_without_launching():
     assert L.sz_moe_verify(C.byref(_layer()), 4096, 4, 4096, 0, 0, 4096, 16, 0) == szlib.E_SCRATCH
     with pytest.raises(szlib.SzError):
         szlib.check(L.sz_moe_verify(C.byref(_layer()), 4096, 4, 4096, 0, 0, 4097, 1 << 20, 0))
+
+
+def test_head_calls_check_their_arguments_without_launching():
+    L = szlib.load()
+    n = C.c_int64()
+    assert L.sz_head_work_bytes(4096, 512, 16, C.byref(n)) == szlib.OK and n.value > 0
+    assert L.sz_head_work_bytes(4000, 512, 16, C.byref(n)) == szlib.E_ARG
+    assert L.sz_head_work_bytes(4096, 8192, 16, C.byref(n)) == szlib.E_ARG
+    h = szlib.HeadC(rows=4096, cols=512, bits=7, k_blk=0, weight=4096 + 12, work=4096, work_bytes=1 << 30)
+    assert L.sz_head_top(C.byref(h), 4096, 512, 4, 64, 4096, 4096, 0) == szlib.E_TYPE
+    h.bits = 4
+    h.weight = 4096
+    assert L.sz_head_top(C.byref(h), 4096, 512, 4, 64, 4096, 4096, 0) == szlib.E_ARG
+    h.weight = 4096 + 12
+    assert L.sz_head_top(C.byref(h), 4096, 512, 9, 64, 4096, 4096, 0) == szlib.E_ARG
+    h.work_bytes = 16
+    assert L.sz_head_top(C.byref(h), 4096, 512, 4, 64, 4096, 4096, 0) == szlib.E_SCRATCH
+    h.work_bytes = 1 << 30
+    ku, ms, ls = C.c_int32(), C.c_int32(), C.c_int64()
+    h.k_blk = 128                                                   # clamped to the 32 blocks there are
+    h.w_q2, h.w_sc = 4096, 4096
+    assert L.sz_head_plan(C.byref(h), 4, 64, C.byref(ku), C.byref(ms), C.byref(ls)) == szlib.OK
+    assert (ku.value, ms.value, ls.value) == (32, 32, 4096)
+    h.rows, h.k_blk = 151936, 128
+    assert L.sz_head_plan(C.byref(h), 4, 64, C.byref(ku), C.byref(ms), C.byref(ls)) == szlib.OK
+    assert (ku.value, ms.value, ls.value) == (128, 512, 65536)
+    assert L.sz_head_plan(C.byref(h), 1, 16, C.byref(ku), C.byref(ms), C.byref(ls)) == szlib.OK and ku.value == 96   # session.rs:5964
+    h.k_blk = 0
+    assert L.sz_head_plan(C.byref(h), 8, 64, C.byref(ku), C.byref(ms), C.byref(ls)) == szlib.OK and ls.value == 151936
+    q2, sc = C.c_int64(), C.c_int64()
+    assert L.sz_head_proxy_bytes(151936, 2048, C.byref(q2), C.byref(sc)) == szlib.OK
+    assert q2.value + sc.value == 82_653_184                        # the 82.7 MB of the reference's proxy at this shape
