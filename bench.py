@@ -303,7 +303,7 @@ def run_c3(args):
     value = toks / (dev_ms * 1e-3)
     cpu = None
     if world == 1 and args.cpu_seconds > 0:
-        cpu = cpu_c3(pkg, args.cpu_seconds, os.cpu_count() or 1)
+        cpu = cpu_c3(pkg, args.cpu_seconds, os.cpu_count() or 1, args.head)
     line = {
         "metric": C3_METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
         "ms_per_step": dev_ms / max(rounds, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
@@ -325,7 +325,7 @@ def run_c3(args):
     out.emit(json.dumps(line))
 
 
-def cpu_c3(pkg, budget_s, threads):
+def cpu_c3(pkg, budget_s, threads, head="q8"):
     """Accepted tok/s of the CPU restatement of the reference's scalar path on the config-3 shapes.  The CPU path verifies one
     token at a time (a batched pass is bitwise the one-at-a-time pass there), so its accepted tok/s is 1 / (seconds a token).
     Sample: models of 4 and of 8 layers (one and two periods of the 3:1 pattern) with the full-size layers, vocabulary and head, a
@@ -337,7 +337,10 @@ def cpu_c3(pkg, budget_s, threads):
     ntok = 0
     for nl in (4, 8):
         cfg = dict(C3, n_layer=nl)
-        M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device="cpu", cycle_alpha=C3_ALPHA)
+        # (the time of a token does not depend on which tokens come out: with an EXL3 head, whose token cycles need a GPU to build,
+        # the sample's model has none; the CPU path always evaluates the head in full, as the reference's --exact does)
+        M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device="cpu",
+                          cycle_alpha=C3_ALPHA if head == "q8" else 0.0, head_type=szlib.TYPE_Q8_0 if head == "q8" else szlib.TYPE_EXL3(4))
         hm = md.HostModel(M)
         s = ob.Session(hm, kv_q8=True, threads=threads)
         s.step(1, want_logits=True)  # warm: page the weights in
@@ -365,7 +368,7 @@ def run_reference_c3(args):
     import __graft_entry__ as graft
     pkg = graft.load_package()
     threads = os.cpu_count() or 1
-    cpu = cpu_c3(pkg, max(10.0, min(60.0, 2.0 * args.steps)), threads)
+    cpu = cpu_c3(pkg, max(10.0, min(60.0, 2.0 * args.steps)), threads, args.head)
     v = cpu["value"]
     cpu_line = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps({

@@ -174,6 +174,8 @@ typedef struct sz_model {
 #define SZ_ACCEPT_NONE 0    /* the caller decides: read the top-64 of every row, then sz_session_commit(keep) */
 #define SZ_ACCEPT_GREEDY 1  /* on the device: keep row i + 1 while row i's best token is the drafted ids[i + 1] (engine.rs:2377-2408) */
 #define SZ_ACCEPT_ALL 2     /* prompt rows: all kept */
+#define SZ_ACCEPT_SAMPLED 3 /* on the device, through sz_session_verify_sampled: row i's token is the sampler's draw at output position
+                             * pos + i from the row's top-64 (sampler.rs:159-210); row i + 1 is kept while that draw is the drafted ids[i + 1] */
 typedef struct sz_session sz_session;
 int sz_session_bytes(const sz_model* model, int ctx, int flags, int64_t* bytes);
 int sz_session_create(const sz_model* model, int ctx, int flags, uint64_t mem, int64_t bytes, uint64_t stream, sz_session** out);
@@ -188,6 +190,14 @@ int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint64_t stream
 /* One pass over ids[0..m): row i's output is what follows ids[..=i] (step_batch_verify).  want_head = 0 skips the output
  * projection (prompt passes).  Asynchronous; the pass stays pending until sz_session_commit. */
 int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode, int eog_token, int want_head, uint64_t stream);
+/* Sampled acceptance on the device.  The sampler (a resolved one without penalties, `struct sz_sampler` below) is set once; a pass
+ * then names the output position of its first row: row i draws with the counter-based uniform number of (seed, pos + i), exactly
+ * as the host loop does (engine.rs:2377-2408 with Sampler::sample_top).  keep_next of sz_session_result = {rows kept, the draw of
+ * the last kept row}.  The draw matches sz_sample_top except where the uniform number falls within an ulp of a boundary of the
+ * cumulative distribution (the device's double-precision exp is not the host library's). */
+struct sz_sampler;
+int sz_session_set_sampler(sz_session* s, const struct sz_sampler* sp);
+int sz_session_verify_sampled(sz_session* s, const int32_t* ids, int m, uint64_t pos, int eog_token, uint64_t stream);
 /* Copies the pending pass's results to the host and synchronises: keep_next[2] = {rows kept by the device's acceptance, the
  * token that follows them}; top = [m][128] u32, 64 logit bit patterns (largest first, ties to the lower id) then 64 token ids
  * (session.rs:6034-6039); logits = [m][vocab] f32.  Any pointer may be null. */
@@ -235,7 +245,7 @@ double sz_uniform(uint64_t seed, uint64_t pos);
 uint32_t sz_sample_top(const sz_sampler* sp, const uint32_t* top128, uint64_t pos);
 /* The draft / verify / accept / commit loop of engine.rs:2149-2454 for `--spec spec_k` with the suffix drafter (no neural
  * drafter, draft policy not consulted): generates up to max_new tokens after the prompt into `out`; pass_log receives
- * (drafted, accepted) per verify pass.  device_accept = 1 lets the device decide greedy acceptance (checked against the host). */
+ * (drafted, accepted) per verify pass.  device_accept = 1 lets the device decide acceptance, greedy or sampled (checked against the host's own decision). */
 typedef struct sz_gen_params {
     int32_t spec_k, max_new, lookup_min, greedy, eog_token, device_accept;
     sz_sampler sampler;

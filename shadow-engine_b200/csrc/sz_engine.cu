@@ -373,7 +373,8 @@ extern "C" int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt,
     g->s = s; g->p = *p;
     g->top.resize(SZ_MAX_VERIFY * 128); g->last.resize(128);
     if (cudaEventCreate(&g->ev0) != cudaSuccess || cudaEventCreate(&g->ev1) != cudaSuccess) { delete g; return sz_fail(SZ_E_CUDA, "sz_gen_begin: no events"); }
-    int rc = sz_session_prefill(s, (const int32_t*)prompt, n_prompt, stream);
+    int rc = !p->greedy && p->device_accept ? sz_session_set_sampler(s, &p->sampler) : SZ_OK;
+    if (!rc) rc = sz_session_prefill(s, (const int32_t*)prompt, n_prompt, stream);
     const int tail = (n_prompt - 1) % SZ_MAX_VERIFY + 1;  // rows of the last prompt pass
     if (!rc) rc = sz_session_result(s, nullptr, g->top.data(), nullptr, stream);
     if (!rc) rc = sz_session_commit(s, tail, stream);
@@ -423,9 +424,12 @@ extern "C" int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_lo
         stats->draft_ms += t1 - t0;
         for (int i = 0; i < nd; i++) batch[1 + i] = (int32_t)draft[i];
         const int m = 1 + nd;
-        const bool dev_accept = p->greedy && p->device_accept;
+        const bool dev_accept = p->device_accept != 0;
         cudaEventRecord(g->ev0, (cudaStream_t)stream);
-        if ((rc = sz_session_verify(s, batch, m, dev_accept ? SZ_ACCEPT_GREEDY : SZ_ACCEPT_NONE, p->eog_token, 1, stream))) break;
+        // sampled: row i is the draw at output position n + i (n already counts this round's first token)
+        rc = dev_accept && !p->greedy ? sz_session_verify_sampled(s, batch, m, (uint64_t)n, p->eog_token, stream)
+                                      : sz_session_verify(s, batch, m, dev_accept ? SZ_ACCEPT_GREEDY : SZ_ACCEPT_NONE, p->eog_token, 1, stream);
+        if (rc) break;
         cudaEventRecord(g->ev1, (cudaStream_t)stream);
         int32_t kn[2] = {1, 0};
         if ((rc = sz_session_result(s, dev_accept ? kn : nullptr, g->top.data(), nullptr, stream))) break;

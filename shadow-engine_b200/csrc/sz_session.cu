@@ -54,7 +54,9 @@ struct sz_session {
     int64_t moe_scratch_bytes;
     int attn_splits, attn_splits2;
     // host staging (pinned, so that a captured graph re-reads it at every launch)
-    int32_t* h_pin;   // [0..8): ids of the pass, [8]: keep of a host-decided commit
+    int32_t* h_pin;   // [0..8): ids of the pass, [8]: keep of a host-decided commit, [10..12]: error words read back, [16..24): SzSampleArgs
+    sz_sampler samp = {};   // sz_session_set_sampler
+    int has_samp = 0;
     int pending_committed;  // the pending pass was already committed on the device (acceptance modes GREEDY / ALL)
     int inflight;           // a pass was launched and the stream not synchronised since: the id staging buffer may still be read
     int use_graphs;
@@ -138,7 +140,7 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
     L->logits = take(4 * M * (int64_t)c.vocab);
     const int64_t nb = ((int64_t)c.vocab + SZ_TK_N - 1) / SZ_TK_N;
     L->tk_tmp = take(8 * M * nb * 64); L->top = take(4 * M * 128);
-    L->ids = take(4 * M); L->res = take(64); L->state = take(64);
+    L->ids = take(128); L->res = take(64);   // ids: the rows' tokens, then (word 16) the sampler block of a sampled pass L->state = take(64);
     L->routes = take(4 * (int64_t)c.n_layer * M * SZ_MAX_TOPK); L->route_w = take(8 * (int64_t)c.n_layer * M * SZ_MAX_TOPK);
     int64_t moe_bytes = 0;
     for (int l = 0; l < c.n_layer; l++) {
@@ -288,7 +290,7 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->model.layers = s->layers.data();
     s->ctx = ctx; s->flags = flags; s->want_routes = 0;
     s->h_pin = nullptr;
-    if (cudaHostAlloc((void**)&s->h_pin, 64, cudaHostAllocDefault) != cudaSuccess) { delete s; return sz_fail(SZ_E_CUDA, "cudaHostAlloc of the id staging buffer failed"); }
+    if (cudaHostAlloc((void**)&s->h_pin, 128, cudaHostAllocDefault) != cudaSuccess) { delete s; return sz_fail(SZ_E_CUDA, "cudaHostAlloc of the id staging buffer failed"); }
     {
         const char* e = getenv("SZ_SESSION_GRAPHS");  // A/B switch: 0 = launch every kernel eagerly
         s->use_graphs = !(e && atoi(e) == 0);
@@ -719,7 +721,11 @@ static int sz_commit_device(sz_session* s, cudaStream_t st, int m) {
 static int sz_pass(sz_session* s, cudaStream_t st, int m, int accept_mode, int eog_token, bool head) {
     int rc = sz_forward(s, st, m, head);
     if (rc) return rc;
-    if (accept_mode != SZ_ACCEPT_NONE) {
+    if (accept_mode == SZ_ACCEPT_SAMPLED) {
+        SZ_CUDA(sz_launch("accept_sampled", sz_accept_sampled_kernel, dim3(1), dim3(32 * SZ_MAX_VERIFY), 0, st, true, (const u32*)s->top,
+                          (const int32_t*)s->ids, m, eog_token, (const SzSampleArgs*)(s->ids + 16), s->res));
+        if ((rc = sz_commit_device(s, st, m))) return rc;
+    } else if (accept_mode != SZ_ACCEPT_NONE) {
         SZ_CUDA(sz_launch("accept", sz_accept_greedy_kernel, dim3(1), dim3(32), 0, st, true, (const u32*)s->top, (const int32_t*)s->ids, m, eog_token,
                           accept_mode == SZ_ACCEPT_ALL ? 1 : 0, head ? 1 : 0, s->res));
         if ((rc = sz_commit_device(s, st, m))) return rc;
@@ -727,16 +733,41 @@ static int sz_pass(sz_session* s, cudaStream_t st, int m, int accept_mode, int e
     return SZ_OK;
 }
 
+static int sz_verify_impl(sz_session* s, const int32_t* ids, int m, int accept_mode, int eog_token, int want_head, uint64_t stream);
+
 extern "C" int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode, int eog_token, int want_head, uint64_t stream) {
+    if (accept_mode < SZ_ACCEPT_NONE || accept_mode > SZ_ACCEPT_ALL) return sz_fail(SZ_E_ARG, "accept_mode %d (sampled acceptance: sz_session_verify_sampled)", accept_mode);
+    return sz_verify_impl(s, ids, m, accept_mode, eog_token, want_head, stream);
+}
+
+extern "C" int sz_session_set_sampler(sz_session* s, const sz_sampler* sp) {
+    if (!s || !sp) return sz_fail(SZ_E_ARG, "sz_session_set_sampler: null argument");
+    if (!(sp->temperature > 0.0f)) return sz_fail(SZ_E_ARG, "sz_session_set_sampler: temperature %g (greedy decoding is SZ_ACCEPT_GREEDY)", (double)sp->temperature);
+    s->samp = *sp;
+    s->has_samp = 1;
+    return SZ_OK;
+}
+
+extern "C" int sz_session_verify_sampled(sz_session* s, const int32_t* ids, int m, uint64_t pos, int eog_token, uint64_t stream) {
+    if (!s) return sz_fail(SZ_E_ARG, "null session or ids");
+    if (!s->has_samp) return sz_fail(SZ_E_ARG, "sz_session_verify_sampled: no sampler set (sz_session_set_sampler)");
+    if (s->inflight) { SZ_CUDA(cudaStreamSynchronize((cudaStream_t)stream)); s->inflight = 0; }  // the staging block is free again
+    SzSampleArgs a = {s->samp.temperature, s->samp.top_k, s->samp.top_p, s->samp.min_p, s->samp.seed, pos};
+    static_assert(sizeof(SzSampleArgs) == 32, "the sampler block is eight words of the staging buffer");
+    memcpy(s->h_pin + 16, &a, sizeof(a));
+    return sz_verify_impl(s, ids, m, SZ_ACCEPT_SAMPLED, eog_token, 1, stream);
+}
+
+static int sz_verify_impl(sz_session* s, const int32_t* ids, int m, int accept_mode, int eog_token, int want_head, uint64_t stream) {
     if (!s || !ids) return sz_fail(SZ_E_ARG, "null session or ids");
     if (m < 1 || m > SZ_MAX_VERIFY) return sz_fail(SZ_E_ARG, "a pass has 1..%d rows, got %d", SZ_MAX_VERIFY, m);
     if (s->last_m) return sz_fail(SZ_E_ARG, "the previous pass was not committed");
     if (s->len + m > s->ctx) return sz_fail(SZ_E_ARG, "%d positions + %d rows exceed the session's capacity %d", s->len, m, s->ctx);
     if (accept_mode == SZ_ACCEPT_GREEDY && !want_head) return sz_fail(SZ_E_ARG, "greedy acceptance needs the head");
-    if (accept_mode < SZ_ACCEPT_NONE || accept_mode > SZ_ACCEPT_ALL) return sz_fail(SZ_E_ARG, "accept_mode %d", accept_mode);
     cudaStream_t st = (cudaStream_t)stream;
     if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
     memcpy(s->h_pin, ids, (size_t)m * 4);
+    const size_t staged = accept_mode == SZ_ACCEPT_SAMPLED ? 96 : (size_t)m * 4;  // a sampled pass carries its sampler block along
     int rc = SZ_OK;
     // one graph per (rows, head, acceptance, eog): every launch-time value a kernel needs lives in device memory
     const int key = m | (want_head ? 16 : 0) | (accept_mode << 5) | ((eog_token & 0xfffff) << 8);
@@ -746,14 +777,14 @@ extern "C" int sz_session_verify(sz_session* s, const int32_t* ids, int m, int a
         auto it = s->graphs.find(key);
         if (it == s->graphs.end()) {
             // first use: run the pass eagerly (this also does every one-time function-attribute set-up), then record it for the next time
-            SZ_CUDA(cudaMemcpyAsync(s->ids, s->h_pin, (size_t)m * 4, cudaMemcpyHostToDevice, st));
+            SZ_CUDA(cudaMemcpyAsync(s->ids, s->h_pin, staged, cudaMemcpyHostToDevice, st));
             if ((rc = sz_pass(s, st, m, accept_mode, eog_token, want_head != 0))) return rc;
             cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
             if (cudaStreamIsCapturing(st, &cs) == cudaSuccess && cs == cudaStreamCaptureStatusNone && s->graphs.size() < 64) {
                 // record the same launches without running them
                 cudaGraph_t g = nullptr;
                 SZ_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-                cudaError_t e = cudaMemcpyAsync(s->ids, s->h_pin, (size_t)m * 4, cudaMemcpyHostToDevice, st);
+                cudaError_t e = cudaMemcpyAsync(s->ids, s->h_pin, staged, cudaMemcpyHostToDevice, st);
                 int prc = e == cudaSuccess ? sz_pass(s, st, m, accept_mode, eog_token, want_head != 0) : SZ_E_CUDA;
                 cudaError_t e2 = cudaStreamEndCapture(st, &g);
                 if (prc == SZ_OK && e2 == cudaSuccess && g) {
@@ -770,7 +801,7 @@ extern "C" int sz_session_verify(sz_session* s, const int32_t* ids, int m, int a
             SZ_CUDA(cudaGraphLaunch(it->second, st));
         }
     } else {
-        SZ_CUDA(cudaMemcpyAsync(s->ids, s->h_pin, (size_t)m * 4, cudaMemcpyHostToDevice, st));
+        SZ_CUDA(cudaMemcpyAsync(s->ids, s->h_pin, staged, cudaMemcpyHostToDevice, st));
         if ((rc = sz_pass(s, st, m, accept_mode, eog_token, want_head != 0))) return rc;
     }
     s->last_m = m;

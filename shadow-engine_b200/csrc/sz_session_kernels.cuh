@@ -1086,4 +1086,80 @@ __global__ void sz_accept_greedy_kernel(const u32* __restrict__ top, const int32
     res[1] = has_head ? (int)top[(size_t)(keep - 1) * 128 + 64] : -1;
 }
 
+// ---- sampled acceptance on the device: Sampler::sample_top (crates/shadowzero-serve/src/sampler.rs:159-210) for every row of the
+// pass, then the host loop's rule (engine.rs:2377-2408).  A warp a row: the exponentials in parallel, everything whose order of
+// operations decides a rounding (the f64 sums, the walk along the cumulative distribution) sequentially in lane 0, as the host does.
+struct SzSampleArgs { float temperature; int top_k; float top_p; float min_p; unsigned long long seed; unsigned long long pos; };
+__device__ __forceinline__ unsigned long long sz_splitmix64_dev(unsigned long long x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+__global__ void __launch_bounds__(32 * SZ_MAX_VERIFY)
+sz_accept_sampled_kernel(const u32* __restrict__ top, const int32_t* __restrict__ ids, int m, int eog, const SzSampleArgs* __restrict__ sa,
+                         int32_t* __restrict__ res) {
+    __shared__ double probs[SZ_MAX_VERIFY][64];
+    __shared__ u32 picks[SZ_MAX_VERIFY];
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int j = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (j < m) {
+        const SzSampleArgs a = *sa;
+        const u32* row = top + (size_t)j * 128;
+        const float v0 = __uint_as_float(row[lane]), v1 = __uint_as_float(row[lane + 32]);
+        const float mx = __shfl_sync(0xffffffffu, v0, 0);
+        u32 pick = row[64];
+        if (isfinite(mx)) {   // (uniform over the warp)
+            const float cut = __fsub_rn(mx, __fmul_rn(18.0f, a.temperature));
+            // the values are sorted: the candidates are a prefix
+            const u32 b0 = __ballot_sync(0xffffffffu, v0 >= cut), b1 = __ballot_sync(0xffffffffu, v1 >= cut);
+            int n = b0 == 0xffffffffu ? 32 + (b1 == 0xffffffffu ? 32 : __ffs(~b1) - 1) : __ffs(~b0) - 1;
+            const int tk = a.top_k < 1 ? 1 : a.top_k;
+            if (n > tk) n = tk;
+            const float inv_t = __fdiv_rn(1.0f, a.temperature);
+            if (lane < n) probs[j][lane] = exp((double)__fmul_rn(__fsub_rn(v0, mx), inv_t));
+            if (lane + 32 < n) probs[j][lane + 32] = exp((double)__fmul_rn(__fsub_rn(v1, mx), inv_t));
+            __syncwarp();
+            if (lane == 0) {
+                double total = 0.0;
+                for (int i = 0; i < n; i++) total += probs[j][i];
+                for (int i = 0; i < n; i++) probs[j][i] = probs[j][i] / total;
+                const double floor_p = (double)a.min_p * probs[j][0];
+                int keep = 0;
+                while (keep < n && probs[j][keep] >= floor_p) keep++;
+                if (keep < 1) keep = 1;
+                if (a.top_p < 1.0f) {
+                    double acc = 0.0;
+                    int cnt = 0;
+                    for (int i = 0; i < keep; i++) { acc += probs[j][i]; cnt++; if (acc >= (double)a.top_p) break; }
+                    keep = cnt < 1 ? 1 : cnt;
+                }
+                double mass = 0.0;
+                for (int i = 0; i < keep; i++) mass += probs[j][i];
+                const unsigned long long bits = sz_splitmix64_dev(sz_splitmix64_dev(a.seed) ^ ((a.pos + (unsigned long long)j) * 0xD6E8FEB86659FD93ull));
+                double u = ((double)(bits >> 11) / 9007199254740992.0) * mass;
+                int at = keep - 1;
+                for (int i = 0; i < keep; i++) {
+                    if (u < probs[j][i]) { at = i; break; }
+                    u -= probs[j][i];
+                }
+                pick = row[64 + at];
+            }
+        }
+        if (lane == 0) picks[j] = pick;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int keep = 1;
+        for (int i = 0; i + 1 < m; i++) {
+            const int d = ids[i + 1];
+            if ((int)picks[i] != d || d == eog) break;
+            keep++;
+        }
+        res[0] = keep;
+        res[1] = (int)picks[keep - 1];
+    }
+}
+
 #endif  // __CUDACC__

@@ -66,6 +66,8 @@ SYMBOLS = {
     "sz_session_pending": (C.c_int, [C.c_void_p]),
     "sz_session_prefill": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64]),
     "sz_session_verify": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64]),
+    "sz_session_set_sampler": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "sz_session_verify_sampled": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64, C.c_int, C.c_uint64]),
     "sz_session_result": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_uint64]),
     "sz_session_commit": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
     "sz_session_fill_synthetic": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint64]),

@@ -323,6 +323,15 @@ class Session:
         szlib.check(self.lib.sz_session_verify(self.h, a, len(ids), accept, eog, 1 if head else 0, self.stream))
         self._m = len(ids)
 
+    def set_sampler(self, sampler):
+        szlib.check(self.lib.sz_session_set_sampler(self.h, C.byref(sampler)))
+
+    def verify_sampled(self, ids, pos, eog=-1):
+        """A pass whose acceptance is sampled on the device: row i's token is the sampler's draw at output position pos + i."""
+        a = (C.c_int32 * len(ids))(*[int(t) for t in ids])
+        szlib.check(self.lib.sz_session_verify_sampled(self.h, a, len(ids), pos, eog, self.stream))
+        self._m = len(ids)
+
     def prefill(self, ids):
         a = (C.c_int32 * len(ids))(*[int(t) for t in ids])
         szlib.check(self.lib.sz_session_prefill(self.h, a, len(ids), self.stream))

@@ -2,6 +2,8 @@
 routing indices identical, logits within 1e-2 relative (BASELINE's bound; the reference's own yardstick is rel < 5e-3 with
 identical routing, crates/shadowzero/tests/reference.rs:57-66), emitted greedy tokens and accepted counts identical, and the
 reference's structural tests: batched == one at a time, a rolled-back pass continues exactly (reference.rs:226-255, 291-319)."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
@@ -140,8 +142,48 @@ def test_config1_sampled_spec3(tiny_cycle):
     want_toks, want_log, want_st = ob.Session(hm, kv_q8=True, threads=8).generate(prompt, 96, spec_k=3, greedy=False,
                                                                                   sampler=ob.SamplerC(0.7, 20, 0.9, 0.0, 11))
     sess = md.Session(dm, 512, kv_q8=True)
-    toks, log, st = sess.generate(prompt, 96, spec_k=3, greedy=False, sampler=md.Sampler(0.7, 20, 0.9, 0.0, 11))
+    toks, log, st = sess.generate(prompt, 96, spec_k=3, greedy=False, sampler=md.Sampler(0.7, 20, 0.9, 0.0, 11))   # acceptance on the device
     assert toks == want_toks and log == want_log
+    host = md.Session(dm, 512, kv_q8=True)
+    toks_h, log_h, _ = host.generate(prompt, 96, spec_k=3, greedy=False, sampler=md.Sampler(0.7, 20, 0.9, 0.0, 11), device_accept=False)
+    assert toks_h == want_toks and log_h == want_log
+
+
+def test_sampled_acceptance_on_the_device_is_the_host_draw(small):
+    # every row's draw on the device against sz_sample_top on the same top-64 table, over several samplers and positions
+    M, hm, dm = small
+    L = szlib.load()
+    toks = [int(t) for t in np.random.default_rng(9).integers(0, SMALL["vocab"], 8)]
+    fresh = md.Session(dm, 64, kv_q8=True)
+    with pytest.raises(szlib.SzError):
+        fresh.verify_sampled(toks, 0)            # no sampler yet
+    for sp in (md.Sampler(0.7, 20, 0.9, 0.0, 11), md.Sampler(1.3, 64, 1.0, 0.05, 5), md.Sampler(0.2, 1, 0.5, 0.0, 3), md.Sampler(2.0, 40, 0.95, 0.1, 77)):
+        sess = md.Session(dm, 64, kv_q8=True)
+        sess.set_sampler(sp)
+
+        def host_picks(top, pos, n):
+            return [int(L.sz_sample_top(C.byref(sp), top[j].ctypes.data_as(C.POINTER(C.c_uint32)), pos + j)) for j in range(n)]
+
+        for pos in (0, 1000003):
+            sess.verify_sampled(toks, pos)
+            (keep, nxt), top, _ = sess.result()
+            picks = host_picks(top, pos, len(toks))
+            want_keep = 1
+            while want_keep < len(toks) and picks[want_keep - 1] == toks[want_keep]:
+                want_keep += 1
+            assert keep == want_keep and nxt == picks[keep - 1], (sp.temperature, pos)
+            sess.commit(keep)
+            assert len(sess) == keep
+            sess.reset()
+        # drafts that ARE the sampler's draws are all kept: draw row 0, draft it, draw again, ...
+        chain = [toks[0]]
+        for step in range(3):
+            sess.verify_sampled(chain, 40)
+            (keep, nxt), top, _ = sess.result()
+            assert keep == len(chain) and nxt == host_picks(top, 40, len(chain))[-1]
+            sess.commit(keep)
+            sess.reset()
+            chain.append(nxt)
 
 
 def test_graph_replay_equals_eager_launches(small):
