@@ -72,18 +72,22 @@ int launch_build(const sz_head* h, cudaStream_t st) {
     return SZ_OK;
 }
 
-template <int K>
-int launch_exl3(const sz_head* h, const HeadWork& w, int m, int grid, const u32* sel, float* logits, int ls, cudaStream_t st) {
-    const size_t smem = SzHeadX<K>::smem_bytes(w.n_b);
+template <int K, int MC>
+int launch_exl3_mc(const sz_head* h, const HeadWork& w, int m, int grid, const u32* sel, float* logits, int ls, cudaStream_t st) {
+    const size_t smem = SzHeadX<K, MC>::smem_bytes(w.n_b);
     static bool set = false;  // one attribute a kernel instance
     if (!set) {
-        SZ_CUDA(cudaFuncSetAttribute(sz_head_exl3_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        SZ_CUDA(cudaFuncSetAttribute(sz_head_exl3_kernel<K, MC>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
         set = true;
     }
     if (smem > 200 * 1024) return sz_fail(SZ_E_ARG, "sz_head_top: %d inputs at %d bits need %zu bytes of shared memory", (int)h->cols, K, smem);
-    SZ_CUDA(sz_launch("head_exl3", sz_head_exl3_kernel<K>, dim3(grid), dim3(SZ_X3_THREADS), smem, st, true, (const u8*)h->weight, (int)h->rows,
+    SZ_CUDA(sz_launch("head_exl3", sz_head_exl3_kernel<K, MC>, dim3(grid), dim3(SZ_X3_THREADS), smem, st, true, (const u8*)h->weight, (int)h->rows,
                       (int)h->cols, (const float*)w.xr, m, sel, logits, ls, w.ctrl + 1));
     return SZ_OK;
+}
+template <int K>
+int launch_exl3(const sz_head* h, const HeadWork& w, int m, int grid, const u32* sel, float* logits, int ls, cudaStream_t st) {
+    return m <= 4 ? launch_exl3_mc<K, 4>(h, w, m, grid, sel, logits, ls, st) : launch_exl3_mc<K, 8>(h, w, m, grid, sel, logits, ls, st);
 }
 
 #define SZ_HEAD_BITS(CALL)                  \

@@ -285,24 +285,29 @@ sz_head_pick_kernel(const float* __restrict__ bmax, int n_ob, int k_use, int max
 // previous ones are decoded (a tile is the A fragment of mma.m16n8k16, the rows of the pass are the B operand in f16 high and low
 // parts, as for the experts).  The whole input range belongs to one block, so the sums stay in registers; the output rotation, the
 // 1/sqrt(128) and svh follow, and row j's 128 logits go to logits[j * ls + slot * 128 ..].
-template <int K>
+// MC = how many rows of the pass have B-fragment columns in shared memory (4 or 8): a pass of at most four rows keeps half the
+// fragments, which lets a third block share the multiprocessor.
+template <int K, int MC>
 struct SzHeadX {
     using X = SzX3<K, 1>;
     static constexpr int OUT_BYTES = 8 * 128 * 4;
-    static size_t smem_bytes(int n_b) { return (size_t)SZ_X3_STAGES * X::STAGE_BYTES + (size_t)n_b * 4096 + OUT_BYTES + SZ_X3_STAGES * 8 + 16; }
+    static constexpr int FRAG_UNIT = 8 * 4 * MC;  // uint4 entries of one input block: 8 tile rows x (4 lanes a row of the pass)
+    static size_t smem_bytes(int n_b) { return (size_t)SZ_X3_STAGES * X::STAGE_BYTES + (size_t)n_b * FRAG_UNIT * 16 + OUT_BYTES + SZ_X3_STAGES * 8 + 16; }
 };
 
-template <int K>
+template <int K, int MC>
 static __global__ void __launch_bounds__(SZ_X3_THREADS)
 sz_head_exl3_kernel(const u8* __restrict__ blob, int rows, int cols, const float* __restrict__ xr, int m, const u32* __restrict__ sel,
                     float* __restrict__ logits, int ls, u32* __restrict__ err) {
     using X = SzX3<K, 1>;
+    using HX = SzHeadX<K, MC>;
+    static_assert(SZ_X3_STAGES == 4, "the loop below takes the ring two stages at a time");
     extern __shared__ __align__(128) u8 smem[];
     const int n_b = cols >> 7, nt = rows >> 4;
     u8* stages = smem;
-    uint4* frags = (uint4*)(smem + SZ_X3_STAGES * X::STAGE_BYTES);                   // [n_b][8 tile rows][32 lanes]
-    float* outs = (float*)(smem + SZ_X3_STAGES * X::STAGE_BYTES + (size_t)n_b * 4096);  // [8 rows][128]
-    u64* bars = (u64*)((u8*)outs + SzHeadX<K>::OUT_BYTES);
+    uint4* frags = (uint4*)(smem + SZ_X3_STAGES * X::STAGE_BYTES);                                  // [n_b][8 tile rows][4 MC]
+    float* outs = (float*)(smem + SZ_X3_STAGES * X::STAGE_BYTES + (size_t)n_b * HX::FRAG_UNIT * 16);   // [8 rows][128]
+    u64* bars = (u64*)((u8*)outs + HX::OUT_BYTES);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (threadIdx.x == 0) {
         for (int i = 0; i < SZ_X3_STAGES; i++) sz_mbar_init(&bars[i], 1);
@@ -325,38 +330,69 @@ sz_head_exl3_kernel(const u8* __restrict__ blob, int rows, int cols, const float
         for (int kr = 0; kr < 8; kr++) sz_bulk_g2s(dst + kr * X::ROW_BYTES, src + kr * drow, X::ROW_BYTES, bar);
     };
     if (threadIdx.x == 0)
-        for (int i = 0; i < SZ_X3_STAGES - 1 && i < n_b; i++) issue(i);
+        for (int i = 0; i < 2 && i < n_b; i++) issue(i);
     // warp t: row t of the pass, already rotated, as B fragments of every input block (rows beyond the pass are zero columns)
-    for (int b = 0; b < n_b; b++) {
-        uint4* frag = frags + (size_t)b * 256;
-        if (warp < m) {
-            const int kk = lane & 15;
-            const int q = (kk & 7) >> 1, reg = kk >> 3, half = kk & 1;
+    if (warp < MC) {
+        for (int b = 0; b < n_b; b++) {
+            uint4* frag = frags + (size_t)b * HX::FRAG_UNIT;
+            if (warp < m) {
+                const int kk = lane & 15;
+                const int q = (kk & 7) >> 1, reg = kk >> 3, half = kk & 1;
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const float val = __ldcg(xr + (size_t)warp * cols + b * 128 + lane + 32 * e) * SZ_RSQRT128;
-                const __half hi = __float2half_rn(val);
-                const __half lo = __float2half_rn(val - __half2float(hi));
-                const int kr = 2 * e + (lane >> 4);
-                u16* dst = (u16*)(frag + kr * 32 + 4 * warp + q);
-                dst[reg * 2 + half] = __half_as_ushort(hi);
-                dst[4 + reg * 2 + half] = __half_as_ushort(lo);
+                for (int e = 0; e < 4; e++) {
+                    const float val = __ldcg(xr + (size_t)warp * cols + b * 128 + lane + 32 * e) * SZ_RSQRT128;
+                    const __half hi = __float2half_rn(val);
+                    const __half lo = __float2half_rn(val - __half2float(hi));
+                    const int kr = 2 * e + (lane >> 4);
+                    u16* dst = (u16*)(frag + kr * (4 * MC) + 4 * warp + q);
+                    dst[reg * 2 + half] = __half_as_ushort(hi);
+                    dst[4 + reg * 2 + half] = __half_as_ushort(lo);
+                }
+            } else {
+                frag[(lane >> 2) * (4 * MC) + 4 * warp + (lane & 3)] = make_uint4(0, 0, 0, 0);
             }
-        } else {
-            frag[(lane >> 2) * 32 + 4 * warp + (lane & 3)] = make_uint4(0, 0, 0, 0);
         }
     }
     __syncthreads();
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const typename SzExl3Tile<K>::Lane LS = SzExl3Tile<K>::lane_setup(lane);
+    const bool has_b = lane < 4 * MC;   // lanes whose column of the B operand belongs to a row held in shared memory
+    auto bfrag = [&](int unit, int kr) { return has_b ? frags[(size_t)unit * HX::FRAG_UNIT + kr * (4 * MC) + lane] : make_uint4(0, 0, 0, 0); };
+    float accA[4] = {0.f, 0.f, 0.f, 0.f}, accB[4] = {0.f, 0.f, 0.f, 0.f};
     int failed = 0;
-    for (int i = 0; i < n_b; i++) {
-        if (threadIdx.x == 0 && i + SZ_X3_STAGES - 1 < n_b) issue(i + SZ_X3_STAGES - 1);  // into the stage round i - 1 left
+    // two input blocks a round, decoded side by side into accumulators of their own: twice the independent work in flight a warp
+    for (int i = 0; i < n_b; i += 2) {
+        const bool two = i + 1 < n_b;
+        if (threadIdx.x == 0) {  // the stages the previous round left
+            if (i + 2 < n_b) issue(i + 2);
+            if (i + 3 < n_b) issue(i + 3);
+        }
         if (!sz_mbar_wait(&bars[i % SZ_X3_STAGES], (i / SZ_X3_STAGES) & 1)) failed = 1;
+        if (two && !sz_mbar_wait(&bars[(i + 1) % SZ_X3_STAGES], ((i + 1) / SZ_X3_STAGES) & 1)) failed = 1;
         if (!failed) {
-            float c[1][4];
-            sz_x3_compute<K, 1>(stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES, frags + (size_t)i * 256, warp, lane, c);
+            const u8* sA = stages + (size_t)(i % SZ_X3_STAGES) * X::STAGE_BYTES + (size_t)warp * X::TILE_BYTES;
+            const u8* sB = stages + (size_t)((i + 1) % SZ_X3_STAGES) * X::STAGE_BYTES + (size_t)warp * X::TILE_BYTES;
+            if (two) {
 #pragma unroll
-            for (int r = 0; r < 4; r++) acc[r] += c[0][r];
+                for (int kr = 0; kr < 8; kr++) {
+                    const uint4 bA = bfrag(i, kr), bB = bfrag(i + 1, kr);
+                    u32 aA[4], aB[4];
+                    sz_exl3_afrag<K>((const u32*)(sA + (size_t)kr * X::ROW_BYTES), lane, LS, aA);
+                    sz_exl3_afrag<K>((const u32*)(sB + (size_t)kr * X::ROW_BYTES), lane, LS, aB);
+                    sz_mma16816(accA, aA, bA.x, bA.y);
+                    sz_mma16816(accB, aB, bB.x, bB.y);
+                    sz_mma16816(accA, aA, bA.z, bA.w);
+                    sz_mma16816(accB, aB, bB.z, bB.w);
+                }
+            } else {
+#pragma unroll
+                for (int kr = 0; kr < 8; kr++) {
+                    const uint4 bA = bfrag(i, kr);
+                    u32 aA[4];
+                    sz_exl3_afrag<K>((const u32*)(sA + (size_t)kr * X::ROW_BYTES), lane, LS, aA);
+                    sz_mma16816(accA, aA, bA.x, bA.y);
+                    sz_mma16816(accA, aA, bA.z, bA.w);
+                }
+            }
         }
         if (__syncthreads_or(failed)) { failed = 1; break; }
     }
@@ -366,10 +402,10 @@ sz_head_exl3_kernel(const u8* __restrict__ blob, int rows, int cols, const float
     }
     {   // c0 = (output g, row 2q), c1 = (output g, row 2q + 1), c2 = (output g + 8, row 2q), c3 = (output g + 8, row 2q + 1)
         const int g = lane >> 2, q = lane & 3;
-        outs[(2 * q) * 128 + warp * 16 + g] = acc[0];
-        outs[(2 * q + 1) * 128 + warp * 16 + g] = acc[1];
-        outs[(2 * q) * 128 + warp * 16 + g + 8] = acc[2];
-        outs[(2 * q + 1) * 128 + warp * 16 + g + 8] = acc[3];
+        outs[(2 * q) * 128 + warp * 16 + g] = accA[0] + accB[0];
+        outs[(2 * q + 1) * 128 + warp * 16 + g] = accA[1] + accB[1];
+        outs[(2 * q) * 128 + warp * 16 + g + 8] = accA[2] + accB[2];
+        outs[(2 * q + 1) * 128 + warp * 16 + g + 8] = accA[3] + accB[3];
     }
     __syncthreads();
     if (warp < m) {

@@ -140,7 +140,8 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
     L->logits = take(4 * M * (int64_t)c.vocab);
     const int64_t nb = ((int64_t)c.vocab + SZ_TK_N - 1) / SZ_TK_N;
     L->tk_tmp = take(8 * M * nb * 64); L->top = take(4 * M * 128);
-    L->ids = take(128); L->res = take(64);   // ids: the rows' tokens, then (word 16) the sampler block of a sampled pass L->state = take(64);
+    L->ids = take(128);  // the rows' tokens, then (word 16) the sampler block of a sampled pass
+    L->res = take(64); L->state = take(64);
     L->routes = take(4 * (int64_t)c.n_layer * M * SZ_MAX_TOPK); L->route_w = take(8 * (int64_t)c.n_layer * M * SZ_MAX_TOPK);
     int64_t moe_bytes = 0;
     for (int l = 0; l < c.n_layer; l++) {

@@ -20,6 +20,10 @@ __device__ __forceinline__ void sz_tk_unkey(u64 k, float& v, u32& id) {
     v = __uint_as_float(b);
     id = 0xffffffffu - (u32)k;
 }
+// A key for a slot that holds no logit (past the end of a row): below every real key (whose high word is at least 0x007fffff) and
+// different for every slot, so that keys never tie - the selection below counts on that.  Decoded as (-inf, id 0xffffffff).
+__device__ __forceinline__ u64 sz_tk_pad(int slot) { return (u64)(0xfffu - ((u32)slot & 0xfffu)); }
+__device__ __forceinline__ bool sz_tk_is_pad(u64 k) { return (k >> 32) == 0; }
 // The 64 best of up to 16 * 256 keys held 16 a thread, written sorted (descending) to dst[0..64).  Instead of sorting everything:
 // the 64th best of the 256 per-thread maxima is a floor under the 64th best key (64 keys are at least that large), so only keys at
 // or above it can be among the winners - at most 64 threads x 16 keys, typically ~70 - and only those are sorted.
@@ -32,7 +36,7 @@ __device__ __forceinline__ void sz_tk_select(const u64* key, u64* sm, u64* cand,
     sm[t] = mx;
     if (t == 0) *cnt = 0;
     __syncthreads();
-    // rank of this thread's maximum among the 256 (ties - only padding keys can tie - by thread number)
+    // rank of this thread's maximum among the 256 (keys are distinct; the thread number would break a tie)
     int rank = 0;
     for (int i = 0; i < 256; i += 2) {
         const ulonglong2 o = *(const ulonglong2*)(sm + i);
@@ -44,9 +48,12 @@ __device__ __forceinline__ void sz_tk_select(const u64* key, u64* sm, u64* cand,
     const u64 floor64 = sm[0];
 #pragma unroll
     for (int i = 0; i < 16; i++)
-        if (key[i] >= floor64) cand[atomicAdd(cnt, 1)] = key[i];
+        if (key[i] >= floor64) {
+            const int at = atomicAdd(cnt, 1);
+            if (at < 1024) cand[at] = key[i];  // (distinct keys: at most 64 threads x 16 keys reach the floor)
+        }
     __syncthreads();
-    const int c = *cnt;  // 64 <= c <= 1024
+    const int c = *cnt < 1024 ? *cnt : 1024;  // 64 <= c <= 1024
     int p = 64;
     while (p < c) p <<= 1;
     for (int i = c + t; i < p; i += 256) cand[i] = 0ull;  // below every real key
@@ -84,7 +91,7 @@ sz_topk_slices_kernel(const float* __restrict__ logits, int vocab, int ls, int n
     for (int q = 0; q < 16; q++) {
         const int i = blk * SZ_TK_N + threadIdx.x + 256 * q;
         const u32 id = sel ? (i < n ? __ldcg(sel + 1 + (i >> 7)) * 128u + (u32)(i & 127) : 0u) : (u32)i;
-        key[q] = i < n ? sz_tk_key(__ldcg(r + i), id) : sz_tk_key(-INFINITY, 0xffffffffu);
+        key[q] = i < n ? sz_tk_key(__ldcg(r + i), id) : sz_tk_pad(threadIdx.x + 256 * q);
     }
     sz_tk_select(key, sm, cand, &cnt, tmp + ((size_t)j * nb + blk) * 64);
 }
@@ -102,13 +109,15 @@ sz_topk_merge_kernel(const u64* __restrict__ tmp, int nb, u32* __restrict__ out)
 #pragma unroll
     for (int q = 0; q < 16; q++) {
         const int i = threadIdx.x + 256 * q;
-        key[q] = i < nb * 64 ? __ldcg(tmp + (size_t)j * nb * 64 + i) : sz_tk_key(-INFINITY, 0xffffffffu);
+        key[q] = i < nb * 64 ? __ldcg(tmp + (size_t)j * nb * 64 + i) : sz_tk_pad(i);
+        if (sz_tk_is_pad(key[q])) key[q] = sz_tk_pad(i);  // a slice's empty slots: distinct again among all slices
     }
     sz_tk_select(key, sm, cand, &cnt, best);
     __syncthreads();
     if (threadIdx.x < 64) {
         float v; u32 id;
         sz_tk_unkey(best[threadIdx.x], v, id);
+        if (sz_tk_is_pad(best[threadIdx.x])) { v = -INFINITY; id = 0xffffffffu; }  // fewer than 64 logits in the row
         out[(size_t)j * 128 + threadIdx.x] = __float_as_uint(v);
         out[(size_t)j * 128 + 64 + threadIdx.x] = id;
     }
