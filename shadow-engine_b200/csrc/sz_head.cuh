@@ -285,6 +285,48 @@ sz_head_pick_kernel(const float* __restrict__ bmax, int n_ob, int k_use, int max
 // previous ones are decoded (a tile is the A fragment of mma.m16n8k16, the rows of the pass are the B operand in f16 high and low
 // parts, as for the experts).  The whole input range belongs to one block, so the sums stay in registers; the output rotation, the
 // 1/sqrt(128) and svh follow, and row j's 128 logits go to logits[j * ls + slot * 128 ..].
+// The decode of two tiles in lockstep (the steps of sz_exl3_afrag, written alternately): a warp issues in order, so the second tile's
+// step fills the wait for the first's result.  The asm statements are not volatile: pure functions of their inputs, free to move.
+__device__ __forceinline__ void sz_mma16816_free(float* c, const u32* a, u32 b0, u32 b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void sz_bytesum4_free(const u32* x, u32 sel0, u32 sel1, u32* c) {
+    c[0] = 0x6400u; c[1] = 0x6400u; c[2] = 0x6400u; c[3] = 0x6400u;
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+        : "r"(x[0]), "r"(x[2]), "r"(x[1]), "r"(x[3]), "r"(sel0), "r"(sel1));
+}
+template <int K>
+__device__ __forceinline__ void sz_exl3_afrag2(const u32* tileA, const u32* tileB, int lane, const typename SzExl3Tile<K>::Lane& LS, u32* aA, u32* aB) {
+    u32 sA[8], sB[8];
+    SzExl3Tile<K>::states_pre(tileA, LS, sA);
+    SzExl3Tile<K>::states_pre(tileB, LS, sB);
+    const __half2 kinv = __halves2half2(__ushort_as_half((u16)0x1eee), __ushort_as_half((u16)0x1eee));
+    const __half2 kbias = __halves2half2(__ushort_as_half((u16)0xc931), __ushort_as_half((u16)0xc931));
+    const int n = lane >> 2, q = lane & 3;
+    const u32 sel0 = ((n & 1) == 0 && (n >> 1) == q) ? 0x01010101u : 0u;
+    const u32 sel1 = ((n & 1) == 1 && (n >> 1) == q) ? 0x01010101u : 0u;
+#pragma unroll
+    for (int i = 0; i < 8; i++) { sA[i] *= 0x83DCD12Du; sB[i] *= 0x83DCD12Du; }
+    u32 cA[8], cB[8];
+    sz_bytesum4_free(sA, sel0, sel1, cA);
+    sz_bytesum4_free(sB, sel0, sel1, cB);
+    sz_bytesum4_free(sA + 4, sel0, sel1, cA + 4);
+    sz_bytesum4_free(sB + 4, sel0, sel1, cB + 4);
+    u32 pA[4], pB[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const u32 ka = __byte_perm(cA[2 * i], cA[2 * i + 1], 0x5410), kb = __byte_perm(cB[2 * i], cB[2 * i + 1], 0x5410);
+        const __half2 ha = __hfma2(*(const __half2*)&ka, kinv, kbias), hb = __hfma2(*(const __half2*)&kb, kinv, kbias);
+        pA[i] = *(const u32*)&ha;
+        pB[i] = *(const u32*)&hb;
+    }
+    aA[0] = pA[0]; aA[1] = pA[2]; aA[2] = pA[1]; aA[3] = pA[3];
+    aB[0] = pB[0]; aB[1] = pB[2]; aB[2] = pB[1]; aB[3] = pB[3];
+}
+
 // MC = how many rows of the pass have B-fragment columns in shared memory (4 or 8): a pass of at most four rows keeps half the
 // fragments, which lets a third block share the multiprocessor.
 template <int K, int MC>
@@ -376,12 +418,11 @@ sz_head_exl3_kernel(const u8* __restrict__ blob, int rows, int cols, const float
                 for (int kr = 0; kr < 8; kr++) {
                     const uint4 bA = bfrag(i, kr), bB = bfrag(i + 1, kr);
                     u32 aA[4], aB[4];
-                    sz_exl3_afrag<K>((const u32*)(sA + (size_t)kr * X::ROW_BYTES), lane, LS, aA);
-                    sz_exl3_afrag<K>((const u32*)(sB + (size_t)kr * X::ROW_BYTES), lane, LS, aB);
-                    sz_mma16816(accA, aA, bA.x, bA.y);
-                    sz_mma16816(accB, aB, bB.x, bB.y);
-                    sz_mma16816(accA, aA, bA.z, bA.w);
-                    sz_mma16816(accB, aB, bB.z, bB.w);
+                    sz_exl3_afrag2<K>((const u32*)(sA + (size_t)kr * X::ROW_BYTES), (const u32*)(sB + (size_t)kr * X::ROW_BYTES), lane, LS, aA, aB);
+                    sz_mma16816_free(accA, aA, bA.x, bA.y);
+                    sz_mma16816_free(accB, aB, bB.x, bB.y);
+                    sz_mma16816_free(accA, aA, bA.z, bA.w);
+                    sz_mma16816_free(accB, aB, bB.z, bB.w);
                 }
             } else {
 #pragma unroll

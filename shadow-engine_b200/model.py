@@ -126,7 +126,8 @@ def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, sha
 
     if head_exl3:
         bits = head_type - 1020
-        blob = synth.random_exl3_blobs(1, H, cfg["vocab"], bits, sigma, seed, "output.weight", device)[0]
+        # (every token's row equally strong, as in a Gaussian head: a few loud rows would win every argmax)
+        blob = synth.random_exl3_blobs(1, H, cfg["vocab"], bits, sigma, seed, "output.weight", device, even=True)[0]
         T["output.weight"] = (head_type, cfg["vocab"], H, blob.contiguous())
         if cycle_alpha > 0.0:
             rows = synth.exl3_reconstruct(blob, H, cfg["vocab"], bits).t()          # [vocab, H]: row v = the head's weights of token v

@@ -98,13 +98,16 @@ def exl3_blob_len(n_in, n_out, bits):
     return 2 * n_in + 2 * n_out + 4 + n_in * n_out * bits // 8
 
 
-def random_exl3_blobs(count, n_in, n_out, bits, sigma, seed, name, device="cpu"):
-    """`count` EXL3 blobs (reference layout: f16 suh | f16 svh | marker | trellis) as uint8 [count, blob_len]."""
+def random_exl3_blobs(count, n_in, n_out, bits, sigma, seed, name, device="cpu", even=False):
+    """`count` EXL3 blobs (reference layout: f16 suh | f16 svh | marker | trellis) as uint8 [count, blob_len].
+    even: every output scale has the magnitude sigma (all rows of the matrix equally strong) instead of sigma * (0.5 .. 1.5)."""
     g = _gen(seed, name, device)
     n = exl3_blob_len(n_in, n_out, bits)
     out = torch.empty((count, n), dtype=torch.uint8, device=device)
     suh = (torch.randint(0, 2, (count, n_in), generator=g, device=device).to(torch.float32) * 2 - 1).to(torch.float16)
     mag = sigma * (0.5 + torch.rand((count, n_out), generator=g, device=device))
+    if even:
+        mag = torch.full_like(mag, sigma)
     sgn = torch.randint(0, 2, (count, n_out), generator=g, device=device).to(torch.float32) * 2 - 1
     svh = (mag * sgn).to(torch.float16)
     out[:, :2 * n_in] = suh.view(torch.uint8).reshape(count, -1)
