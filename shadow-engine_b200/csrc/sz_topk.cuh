@@ -10,6 +10,7 @@
 #define SZ_TK_N 4096
 __device__ __forceinline__ u64 sz_tk_key(float v, u32 id) {
     if (v != v) v = -INFINITY;
+    if (v == 0.0f) v = 0.0f;  // -0 ties with +0 in the reference's comparison (va == vb): one key for both (decoded as +0)
     u32 b = __float_as_uint(v);
     b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
     return ((u64)b << 32) | (u64)(0xffffffffu - id);
