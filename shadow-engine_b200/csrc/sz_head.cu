@@ -178,7 +178,7 @@ extern "C" int sz_head_top(const sz_head* h, uint64_t x, int xstride, int m, int
         else
             SZ_CUDA(sz_launch("head_proxy", sz_head_proxy_kernel<8>, dim3(w.n_ob), dim3(128), smem, st, true, (const u8*)h->w_q2, (const u16*)h->w_sc,
                               (const u32*)w.xq, (const float*)w.x_sc, (const float*)w.x_corr, w.bmax, w.n_ob, (int)h->cols, m));
-        SZ_CUDA(sz_launch("head_pick", sz_head_pick_kernel, dim3(m), dim3(32), 0, st, true, (const float*)w.bmax, w.n_ob, ku, ms, w.seen, w.ctrl, w.sel));
+        SZ_CUDA(sz_launch("head_pick", sz_head_pick_kernel, dim3(m), dim3(256), 0, st, true, (const float*)w.bmax, w.n_ob, ku, ms, w.seen, w.ctrl, w.sel));
         grid = ms;
         ls = ms * 128;
         sel = w.sel;

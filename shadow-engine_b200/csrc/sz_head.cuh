@@ -14,7 +14,7 @@
 
 #ifdef __CUDACC__
 
-#define SZ_HEAD_PICK_KEYS 8  // the pick kernel ranks at most 256 * 8 = 2048 blocks = 262144 outputs
+#define SZ_HEAD_PICK_KEYS 8  // keys a thread of the pick kernel holds: 256 * 8 = 2048 blocks = 262144 outputs at most
 
 // ---- the proxy, once: 128 x 128 blocks of W_rot = H_out(W_hat) * svh / 128 as 2-bit codes {-3, -1, 1, 3} * scale ------------------------
 // grid (n_ob, n_b), 256 threads; warp w decodes tile column w of the block, one tile row at a time.
@@ -203,97 +203,77 @@ sz_head_proxy_kernel(const u8* __restrict__ w_q2, const u16* __restrict__ w_sc, 
 }
 
 // ---- the block list: the k best blocks of every row (value descending, index ascending, NaN below everything), their union ascending --------
-// grid m, one warp a row: a lane holds every 32nd block's key in registers.  A row's k-th best key is found bit by bit (the largest
-// threshold that k keys still reach: one warp-wide count a bit, no barrier): first the 32 bits of the value, where a key reaches the
-// candidate exactly when its value word does (the index word of a real key is never below the candidate's), then the 12 index bits
-// among equal values.  Every key at or above the result sets its block's bit in `seen`.  The last warp to finish (a ticket in
-// ctrl[0]) turns the bits into sel[1 ..], sel[0] = how many (at most max_sel), and clears bits and ticket for the next pass.
-#define SZ_HEAD_PICK_LANE_KEYS (SZ_HEAD_PICK_KEYS * 8)  // 64 keys a lane: 2048 blocks
-static __global__ void __launch_bounds__(32)
+// grid m, 256 threads.  A row's k-th best key is found bit by bit (the largest threshold that k keys still reach: a count a bit);
+// every key at or above it sets its block's bit in `seen`.  The last block to finish (a ticket in ctrl[0]) turns the bits into
+// sel[1 ..], sel[0] = how many (at most max_sel), and clears bits and ticket for the next pass.
+static __global__ void __launch_bounds__(256)
 sz_head_pick_kernel(const float* __restrict__ bmax, int n_ob, int k_use, int max_sel, u32* __restrict__ seen, u32* __restrict__ ctrl,
                     u32* __restrict__ sel) {
-    const int lane = threadIdx.x;
+    __shared__ int cnts[2][8];
+    __shared__ int offs[64];
+    __shared__ int s_last;
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31;
     sz_pdl_wait();
     sz_pdl_trigger();
     const float* r = bmax + (size_t)blockIdx.x * n_ob;
-    const int nk = (n_ob + 31) >> 5;
-    u32 hi[SZ_HEAD_PICK_LANE_KEYS];   // the value word of block lane + 32 q; 0 (below every real key's) past the end
+    u64 key[SZ_HEAD_PICK_KEYS];
 #pragma unroll
-    for (int q = 0; q < SZ_HEAD_PICK_LANE_KEYS; q++) {
-        hi[q] = 0u;
-        if (q < nk) {
-            const int i = lane + 32 * q;
-            float v = i < n_ob ? __ldcg(r + i) : 0.0f;
-            if (v != v) v = -3.0e38f;
-            hi[q] = i < n_ob ? (u32)(sz_tk_key(v, (u32)i) >> 32) : 0u;
-        }
+    for (int q = 0; q < SZ_HEAD_PICK_KEYS; q++) {
+        const int i = t + 256 * q;
+        float v = i < n_ob ? __ldcg(r + i) : 0.0f;
+        if (v != v) v = -3.0e38f;
+        key[q] = i < n_ob ? sz_tk_key(v, (u32)i) : 0ull;  // 0 is below every real key
     }
     const int k = k_use < n_ob ? k_use : n_ob;
-    u32 thi = 0u;
-    for (int bit = 31; bit >= 0; bit--) {
-        const u32 cand = thi | (1u << bit);
+    // every real key has bits 31..12 set (block numbers are below 4096): the threshold keeps them set and the search covers the rest
+    u64 T = 0x00000000fffff000ull;
+    int it = 0;
+    for (int bit = 63; bit >= 0; bit--) {
+        if (bit < 32 && bit >= 12) continue;
+        const u64 cand = T | (1ull << bit);
         int c = 0;
 #pragma unroll
-        for (int q = 0; q < SZ_HEAD_PICK_LANE_KEYS; q++)
-            if (q < nk) c += hi[q] >= cand;
-        if (__reduce_add_sync(0xffffffffu, c) >= k) thi = cand;
-    }
-    // thi = the value word of the k-th best key; `above` keys beat it outright, the rest of the k come from the keys that equal it,
-    // lowest block numbers first: the (k - above)-th smallest index among them, again bit by bit (index word = ~index: larger is better)
-    int above = 0;
+        for (int q = 0; q < SZ_HEAD_PICK_KEYS; q++) c += key[q] >= cand;
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (lane == 0) cnts[it & 1][warp] = c;
+        __syncthreads();
+        int tot = 0;
 #pragma unroll
-    for (int q = 0; q < SZ_HEAD_PICK_LANE_KEYS; q++)
-        if (q < nk) above += hi[q] > thi;
-    above = __reduce_add_sync(0xffffffffu, above);
-    const int need = k - above;   // >= 1
-    u32 tlo = 0xfffff000u;
-    for (int bit = 11; bit >= 0; bit--) {
-        const u32 cand = tlo | (1u << bit);
-        int c = 0;
-#pragma unroll
-        for (int q = 0; q < SZ_HEAD_PICK_LANE_KEYS; q++)
-            if (q < nk) c += hi[q] == thi && (0xffffffffu - (u32)(lane + 32 * q)) >= cand;
-        if (__reduce_add_sync(0xffffffffu, c) >= need) tlo = cand;
+        for (int w = 0; w < 8; w++) tot += cnts[it & 1][w];
+        if (tot >= k) T = cand;
+        it++;
     }
 #pragma unroll
-    for (int q = 0; q < SZ_HEAD_PICK_LANE_KEYS; q++)
-        if (q < nk) {
-            const u32 i = (u32)(lane + 32 * q);
-            if (hi[q] != 0u && (hi[q] > thi || (hi[q] == thi && (0xffffffffu - i) >= tlo))) atomicOr(&seen[i >> 5], 1u << (i & 31));
+    for (int q = 0; q < SZ_HEAD_PICK_KEYS; q++)
+        if (key[q] >= T && key[q] != 0ull) {
+            const u32 i = (u32)(t + 256 * q);
+            atomicOr(&seen[i >> 5], 1u << (i & 31));
         }
     __threadfence();
-    __syncwarp();
-    int last = 0;
-    if (lane == 0) last = atomicAdd(&ctrl[0], 1u) == gridDim.x - 1;
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (!last) return;
+    __syncthreads();
+    if (t == 0) s_last = atomicAdd(&ctrl[0], 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!s_last) return;
     __threadfence();
-    const int n_words = (n_ob + 31) >> 5;  // at most 64: two words a lane, lane L owns words 2L and 2L + 1 (ascending order over lanes)
-    u32 m0 = 0, m1 = 0;
-    if (2 * lane < n_words) m0 = atomicExch(&seen[2 * lane], 0u);
-    if (2 * lane + 1 < n_words) m1 = atomicExch(&seen[2 * lane + 1], 0u);
-    const int mine = __popc(m0) + __popc(m1);
-    int pre = mine;   // inclusive prefix over the lanes
-#pragma unroll
-    for (int off = 1; off < 32; off <<= 1) {
-        const int v = __shfl_up_sync(0xffffffffu, pre, off);
-        if (lane >= off) pre += v;
+    const int n_words = (n_ob + 31) >> 5;  // at most 64
+    u32 mask = 0;
+    if (t < n_words) mask = atomicExch(&seen[t], 0u);
+    if (t < 64) offs[t] = __popc(mask);
+    __syncthreads();
+    int pos = 0, total = 0;
+    for (int w = 0; w < 64; w++) {
+        const int c = offs[w];
+        pos += w < t ? c : 0;
+        total += c;
     }
-    const int total = __shfl_sync(0xffffffffu, pre, 31);
-    int pos = pre - mine;
-    while (m0) {
-        const int bit = __ffs((int)m0) - 1;
-        m0 &= m0 - 1;
-        if (pos < max_sel) sel[1 + pos] = (u32)(2 * lane * 32 + bit);
-        pos++;
-    }
-    while (m1) {
-        const int bit = __ffs((int)m1) - 1;
-        m1 &= m1 - 1;
-        if (pos < max_sel) sel[1 + pos] = (u32)((2 * lane + 1) * 32 + bit);
-        pos++;
-    }
-    if (lane == 0) {
+    if (t < n_words)
+        while (mask) {
+            const int bit = __ffs((int)mask) - 1;
+            mask &= mask - 1;
+            if (pos < max_sel) sel[1 + pos] = (u32)(t * 32 + bit);
+            pos++;
+        }
+    if (t == 0) {
         sel[0] = (u32)(total < max_sel ? total : max_sel);
         ctrl[0] = 0;
     }
