@@ -602,15 +602,17 @@ def main():
 
     def roofline(r):
         # the dominant kernel: gate+up of the routed experts (2/3 of an expert's bytes per distinct expert)
-        name = "gateup_exl3" if r["fmt"] == "exl3" else "gateup_rows"
+        # (the trace name of whichever gate/up kernel ran: the streaming EXL3 kernel takes routed and shared experts in one launch,
+        # the block-format kernels and the generic ones in one launch each; all launches of a step are added up with the bytes of both)
+        names = ["gateup_exl3s", "gateup_exl3"] if r["fmt"] == "exl3" else ["gateup_blk", "gateup_rows"]
+        name = next((n for n in names if n in r["kernels"]), names[0])
         ks = r["kernels"].get(name)
-        # two launches carry that name (routed, shared): the routed one is the first of each pair; both are averaged here with
-        # bytes of both, so the figure is the pair's
         bytes_pair = (r["distinct"] + 1) * r["expert_bytes"] * 2 / 3
-        out = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "traffic": GATEUP_TRAFFIC if name == "gateup_exl3" else None,
+        out = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "traffic": GATEUP_TRAFFIC if name == "gateup_exl3s" else None,
                "kernel": name}
         if ks:
-            dur_us = ks["avg_us"] * 2  # the pair
+            per_step = max(1, round(ks["launches"] / max(args.steps, 1)))
+            dur_us = ks["avg_us"] * per_step
             out["achieved"] = bytes_pair / (dur_us * 1e-6) / 1e9
             out["frac"] = out["achieved"] / hbm
             out["kernel_us"] = dur_us
