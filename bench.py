@@ -1,13 +1,13 @@
 """Benchmark of the speculative-decoding verify path on B200.
 
-Default workload ("c3"): BASELINE config 3 - the full-size seeded hybrid MoE (48 layers 3:1 DeltaNet : gated attention, hidden
+Default workload ("c3"): benchmark config 3 - the full-size seeded hybrid MoE (48 layers 3:1 DeltaNet : gated attention, hidden
 2048, 512 experts top-10 of FFN 512 + a shared expert, EXL3 3-bit experts, Q8_0 dense matrices, a 4-bit EXL3 head screened by
 its 2-bit proxy (`--head q8` / `exl3`: a Q8_0 or an EXL3 head read in full), vocab 151936, Q8_KV cache) decoding greedily at spec K=3, batch 1, at context 24576.  One "step" is one draft / verify / accept round: the suffix
 drafter proposes up to 3 tokens, one verify pass runs over the 1..4 rows, acceptance and rollback happen on the device.  The
 metric is accepted tokens per second (every emitted token: accepted drafts and the pass's own token).  With --gpus N (under
 torchrun) the experts of every layer are sharded over the N ranks (expert parallelism); one sequence, so scaling is "strong".
 
-`--workload c2-moe`: BASELINE config 2, the verify-step MoE microbench (one MoE sublayer pass over K+1 = 4 rows per step).
+`--workload c2-moe`: benchmark config 2, the verify-step MoE microbench (one MoE sublayer pass over K+1 = 4 rows per step).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c2-moe] [--impl reference]
 
@@ -30,7 +30,7 @@ if ROOT not in sys.path:
 C2 = dict(hidden=2048, n_expert=512, top_k=10, expert_ff=512, shared_ff=512, rows=4)
 METRIC = "verify-step us (MoE sublayer, K+1=4 rows, spec K=3)"
 
-# BASELINE config 3
+# benchmark config 3
 C3 = dict(n_layer=48, hidden=2048, streams=4, hc_rank=256, vocab=151936, n_head=16, n_kv_head=2, head_dim=256, rope_dims=64,
           n_expert=512, n_expert_used=10, expert_ff=512, shared_ff=512, ssm_k_heads=16, ssm_v_heads=32, ssm_head_dim=128, conv_k=4,
           attn_interval=4, eps=1e-6, rope_theta=1e7)

@@ -51,7 +51,7 @@ class GenStats(C.Structure):
                 ("device_ms", C.c_double)]
 
 
-# BASELINE config 1: the CPU-runnable tiny hybrid MoE (4 layers D D D A; hidden 512; 8 q / 2 kv heads of 64; DeltaNet 4 heads of 64;
+# benchmark config 1: the CPU-runnable tiny hybrid MoE (4 layers D D D A; hidden 512; 8 q / 2 kv heads of 64; DeltaNet 4 heads of 64;
 # 32 experts top-4 of FFN 256 + a shared expert of FFN 512; vocab 32000), with the reference's hyper-connections as block glue
 # (4 streams, rank = streams * hidden / 32 as in its checkpoints, docs/ARCH.md:79-80).
 TINY = dict(n_layer=4, hidden=512, streams=4, hc_rank=64, vocab=32000, n_head=8, n_kv_head=2, head_dim=64, rope_dims=32, n_expert=32,
@@ -399,7 +399,7 @@ class Generator:
 
 
 def make_prompt(n_tokens, vocab, seed=1, block=16, substitute=0.1, cycles=None):
-    """BASELINE config 1's prompt: a block of `block` tokens repeated, with a fraction of random substitutions, so a suffix drafter
+    """benchmark config 1's prompt: a block of `block` tokens repeated, with a fraction of random substitutions, so a suffix drafter
     finds repeats.  With `cycles` (token_cycles(...)[1]) the block is one of the model's own token cycles."""
     rng = np.random.default_rng(seed)
     base = rng.integers(0, vocab, block) if cycles is None else cycles[int(rng.integers(0, cycles.shape[0]))].numpy()[:block]

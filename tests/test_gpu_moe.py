@@ -38,7 +38,7 @@ def run_case(H, ne, k, FF, SF, ety, sty, m, seed=1, x_scale=1.0, router_sigma=No
 
 @pytest.mark.parametrize("m", [1, 2, 4, 8])
 def test_q8_0_tiny_model_shapes(m):
-    # BASELINE config 1's MoE: hidden 512, 32 experts top-4, FF 256, shared FF 512, Q8_0
+    # benchmark config 1's MoE: hidden 512, 32 experts top-4, FF 256, shared FF 512, Q8_0
     run_case(512, 32, 4, 256, 512, szlib.TYPE_Q8_0, szlib.TYPE_Q8_0, m)
 
 
@@ -138,7 +138,7 @@ def test_host_buffer_entry_point_matches_the_device_one():
 
 
 def test_microbench_shapes_iq3_s_and_exl3():
-    # BASELINE config 2 shapes (hidden 2048, 512 experts top-10, FF 512 + shared 512) with a reduced expert pool so the
+    # benchmark config 2 shapes (hidden 2048, 512 experts top-10, FF 512 + shared 512) with a reduced expert pool so the
     # CPU oracle finishes in seconds: the router only sees the first 64 experts' rows.
     for ety in (szlib.TYPE_IQ3_S, szlib.TYPE_EXL3(3)):
         run_case(2048, 64, 10, 512, 512, ety, ety, 4, seed=12)

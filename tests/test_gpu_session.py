@@ -1,5 +1,5 @@
 """The whole verify step on the GPU against the CPU oracle's Session::step (forward.rs:751-794) on seeded tiny models:
-routing indices identical, logits within 1e-2 relative (BASELINE's bound; the reference's own yardstick is rel < 5e-3 with
+routing indices identical, logits within 1e-2 relative (the benchmark's bound; the reference's own yardstick is rel < 5e-3 with
 identical routing, crates/shadowzero/tests/reference.rs:57-66), emitted greedy tokens and accepted counts identical, and the
 reference's structural tests: batched == one at a time, a rolled-back pass continues exactly (reference.rs:226-255, 291-319)."""
 import ctypes as C
@@ -14,7 +14,7 @@ from tests.util import pkg
 pytestmark = pytest.mark.gpu
 szlib, md = pkg.lib, pkg.model
 
-LOGIT_REL = 1e-2   # BASELINE north star: logits within 1e-2 relative error
+LOGIT_REL = 1e-2   # the benchmark's target: logits within 1e-2 relative error
 SMALL = dict(md.TINY, vocab=4096, n_expert=16, expert_ff=128, shared_ff=128)
 
 
@@ -120,7 +120,7 @@ def tiny_cycle():
 
 
 def test_config1_greedy_spec3_tokens_and_accepted_counts(tiny_cycle):
-    # BASELINE config 1: 256-token prompt, 128 new tokens, greedy, --spec 3 with the suffix drafter; CPU scalar path vs GPU
+    # benchmark config 1: 256-token prompt, 128 new tokens, greedy, --spec 3 with the suffix drafter; CPU scalar path vs GPU
     M, hm, dm, prompt = tiny_cycle
     want_toks, want_log, want_st = ob.Session(hm, kv_q8=True, threads=8).generate(prompt, 128, spec_k=3)
     sess = md.Session(dm, 512, kv_q8=True)
