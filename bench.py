@@ -35,7 +35,19 @@ C3 = dict(n_layer=48, hidden=2048, streams=4, hc_rank=256, vocab=151936, n_head=
           n_expert=512, n_expert_used=10, expert_ff=512, shared_ff=512, ssm_k_heads=16, ssm_v_heads=32, ssm_head_dim=128, conv_k=4,
           attn_interval=4, eps=1e-6, rope_theta=1e7)
 C3_CTX = 24576
-GATEUP_TRAFFIC = 33029376 + 7936   # bytes a launch of sz_x3_gateup_kernel<3,4> moved (read + write) under ncu, 39 routed + 1 shared expert
+GATEUP_PROFILE = os.path.join(ROOT, "profiles", "c2_moe_gateup_exl3_full.md")
+
+
+def gateup_traffic(experts_per_launch):
+    """DRAM bytes (read + written) a launch of the EXL3 gate/up kernel moves, from the committed ncu capture of that kernel on
+    these expert shapes: the capture's `traffic:` line gives the bytes of one launch and how many experts it covered; traffic grows
+    in proportion to the experts a launch streams, so it is scaled to `experts_per_launch`.  None when the profile has no such line."""
+    import re
+    try:
+        m = re.search(r"^traffic:\s*(\d+)\s*bytes a launch over\s*(\d+)\s*experts", open(GATEUP_PROFILE).read(), re.M)
+        return int(m.group(1)) / int(m.group(2)) * experts_per_launch
+    except Exception:
+        return None
 C3_METRIC = "accepted tok/s at spec K=3"
 
 
@@ -122,6 +134,21 @@ class ClockSampler:
 # about as many tokens a round as the reference reports for its suffix drafter (2.8): 3.1 and 2.9.
 C3_ALPHA = 0.85
 C3_ALPHA_BY_HEAD = {"q8": 0.85, "exl3": 0.95, "proxy": 0.95}
+C3_BETA_BY_HEAD = {"q8": 0.0, "exl3": 0.0, "proxy": 0.0}
+
+
+def c3_config(args, cfg, ctx, bytes_all=None):
+    """The `config` object of a c3 line: both arms (the library and the CPU reference) print the same one."""
+    world = args.gpus
+    return {"workload": "c3", "n_layer": cfg["n_layer"], "hidden": cfg["hidden"], "n_expert": cfg["n_expert"], "top_k": cfg["n_expert_used"],
+            "expert_ff": cfg["expert_ff"], "vocab": cfg["vocab"], "experts": "exl3-3bit", "dense": "q8_0", "kv": "q8_kv",
+            "head": {"q8": "q8_0, read in full", "exl3": "exl3-4bit, read in full", "proxy": "exl3-4bit screened by its 2-bit proxy (128 blocks a row)"}[args.head],
+            "context": ctx, "spec_k": 3, "batch": 1, "greedy": True,
+            "requests": "256-token prompts (a token cycle of the model repeated, 10%% random substitutions), %d tokens decoded each; "
+                        "prompt passes and the cache fill are outside the timed region" % args.request_tokens,
+            "acceptance_knobs": {"cycle_alpha": args.alpha, "cycle_beta": args.beta, "prompt_substitution": 0.1},
+            "parallelism": "ep%d" % world if world > 1 else "single", "exchange": args.exchange if world > 1 else None,
+            "l2": "inputs larger than L2: a pass streams about 5 GB of weights and cache"}
 
 
 def c3_bytes(cfg, ctx, distinct_per_layer, dense_bytes):
@@ -163,7 +190,7 @@ def run_c3(args):
     cfg = dict(C3, n_layer=args.n_layer)
     head_type = szlib.TYPE_Q8_0 if args.head == "q8" else szlib.TYPE_EXL3(4)
     M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha,
-                      head_type=head_type)
+                      cycle_beta=args.beta, head_type=head_type)
     dm = md.DeviceModel(M, device, ep=(rank, world) if world > 1 else None)
     # every tensor outside the experts is read once a pass, except the embedding table (m rows gathered)
     dense_bytes = sum(t[3].numel() * t[3].element_size() for n, t in M["tensors"].items() if n != "token_embd.weight")
@@ -176,27 +203,29 @@ def run_c3(args):
     torch.cuda.empty_cache()
     ctx = args.ctx
     K, W = args.steps, max(args.warmup, 3)
-    max_new = 4 * (3 * K + W + 64) + 64
-    sess = md.Session(dm, ctx + max_new + 64, kv_q8=True, head_proxy=args.head == "proxy")
+    n_prompt, n_new = 256, args.request_tokens
+    sess = md.Session(dm, ctx + n_new + 64, kv_q8=True, head_proxy=args.head == "proxy")
     _, cyc = md.token_cycles(cfg["vocab"], 1)
-    n_prompt = 256
-    prompt = md.make_prompt(n_prompt, cfg["vocab"], seed=1, cycles=cyc)
-    # the long context: the cache up to ctx - 256 is filled in place with seeded values of the cache's own distribution, then
-    # the 256-token repeated-n-gram prompt is prefilled through the model
-    sess.fill_synthetic(ctx - n_prompt, seed=3)
+    stream = sess._stream
+
+    def request(i):
+        """Request i of the workload: the cache up to ctx - 256 filled in place with seeded values of the cache's own distribution
+        (the long context), then a 256-token prompt of its own - one of the model's token cycles repeated, 10% of the tokens
+        substituted at random - fed through the model.  Returns the generator, positioned after the prompt."""
+        sess.fill_synthetic(ctx - n_prompt, seed=3)
+        return md.Generator(sess, md.make_prompt(n_prompt, cfg["vocab"], seed=1 + i, cycles=cyc), n_new, spec_k=3)
+
     if args.profile_passes > 0:
         # for a profiler: N verify passes of 4 rows and nothing else (run with SZ_SESSION_GRAPHS=0 to see every launch by name)
+        sess.fill_synthetic(ctx - n_prompt, seed=3)
+        prompt = md.make_prompt(n_prompt, cfg["vocab"], seed=1, cycles=cyc)
         for i in range(args.profile_passes):
             sess.verify([int(t) for t in prompt[4 * i:4 * i + 4]], accept=1)
-            sess.result()
-            sess.commit(1)
+            (keep, _), _, _ = sess.result()
+            sess.commit(keep)
         torch.cuda.synchronize()
         out.emit(json.dumps({"profile_passes": args.profile_passes, "rows": 4, "context": ctx, "n_layer": cfg["n_layer"]}))
         return
-    gen = md.Generator(sess, prompt, max_new, spec_k=3)
-    st = gen.run(W)
-    torch.cuda.synchronize()
-    stream = sess._stream
 
     def barrier():
         if world > 1:
@@ -204,49 +233,85 @@ def run_c3(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def snap(s):
-        return dict(n=s.n_tokens, rounds=s.rounds, passes=s.passes, drafted=s.drafted, accepted=s.accepted)
+    def agree_max(v):
+        if world == 1:
+            return v
+        import torch.distributed as dist
+        t = torch.tensor([v], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
 
-    # --- K rounds through the public loop (host drafter, ids host -> device, result device -> host every round), timed twice over:
-    # value = tokens / the device time of the K passes (events on the session's stream around each pass: graph of the pass with
-    # acceptance and commit, cache and weights resident); e2e = tokens / wall clock of the whole loop
+    # --- the workload: a stream of requests.  Every request decodes n_new tokens after its prompt through the public loop (host
+    # drafter, ids host -> device, result device -> host every round).  Only decode rounds are timed - the prompt passes and the
+    # cache fill between requests are not - and the rounds of whole requests are added up:
+    #   value = tokens / the device time of the passes (events on the session's stream around each pass: the graph of the pass
+    #           with acceptance and commit; cache and weights resident);  e2e = tokens / wall clock of the loop.
+    # Warm-up: whole requests, untimed, until at least W rounds ran (the first request also records the CUDA graphs).  Timed: whole
+    # requests until at least K rounds and a second of device time; every rank runs the same requests (the tokens are the same
+    # bits on every rank), and the decision to go on is taken on the slowest rank's clock.
+    tot = dict(n=0, rounds=0, passes=0, drafted=0, accepted=0, dev_ms=0.0, wall_s=0.0, draft_ms=0.0, verify_ms=0.0, commit_ms=0.0,
+               tried=[0] * 8, right=[0] * 8, requests=0)
+
+    def run_request(i, acc):
+        gen = request(i)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        st = gen.run(0)
+        stream.synchronize()
+        wall = time.perf_counter() - t0
+        if acc is not None:
+            acc["n"] += st.n_tokens; acc["rounds"] += st.rounds; acc["passes"] += st.passes; acc["drafted"] += st.drafted
+            acc["accepted"] += st.accepted; acc["dev_ms"] += st.device_ms; acc["wall_s"] += wall
+            acc["draft_ms"] += st.draft_ms; acc["verify_ms"] += st.verify_ms; acc["commit_ms"] += st.commit_ms
+            for j in range(8):
+                acc["tried"][j] += st.pos_tried[j]; acc["right"][j] += st.pos_right[j]
+            acc["requests"] += 1
+        rounds = st.rounds
+        del gen
+        return rounds
+
+    req, warm_rounds = 0, 0
+    while warm_rounds < W or req == 0:
+        warm_rounds += run_request(req, None)
+        req += 1
     barrier()
     sampler = ClockSampler(torch.cuda.current_device())
     sampler.start()
-    a = snap(st)
-    d0 = st.device_ms
-    t0 = time.perf_counter()
-    st = gen.run(K)
-    stream.synchronize()
-    wall_s = time.perf_counter() - t0
+    while True:
+        run_request(req, tot)
+        req += 1
+        if tot["rounds"] >= K and agree_max(tot["dev_ms"]) >= 1000.0:
+            break
+        if tot["requests"] >= 400:
+            break
     barrier()
-    b = c = snap(st)
-    dev_ms = st.device_ms - d0
     clocks = sampler.stop()
-    if world > 1:
-        import torch.distributed as dist
-        t = torch.tensor([dev_ms, wall_s], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        dev_ms, wall_s = float(t[0]), float(t[1])
-    rounds = b["rounds"] - a["rounds"]
-    toks = b["n"] - a["n"]
-    gen_stats = dict(tokens=toks, rounds=rounds, drafted=b["drafted"] - a["drafted"], accepted=b["accepted"] - a["accepted"],
-                     tokens_per_round=toks / max(rounds, 1), draft_ms=st.draft_ms, verify_ms=st.verify_ms, commit_ms=st.commit_ms)
+    dev_ms, wall_s = agree_max(tot["dev_ms"]), agree_max(tot["wall_s"])
+    rounds, toks = tot["rounds"], tot["n"]
+    gen_stats = dict(tokens=toks, rounds=rounds, requests=tot["requests"], warmup_rounds=warm_rounds, drafting_rounds=tot["passes"],
+                     drafted=tot["drafted"], accepted=tot["accepted"], tokens_per_round=toks / max(rounds, 1),
+                     right_by_position=tot["right"][:3], tried_by_position=tot["tried"][:3],
+                     accept_rate_by_position=[tot["right"][j] / max(tot["tried"][j], 1) for j in range(3)],
+                     draft_ms=tot["draft_ms"], verify_ms=tot["verify_ms"], commit_ms=tot["commit_ms"])
     rows_avg = 1 + gen_stats["drafted"] / max(rounds, 1)   # rows of a pass: its own token and the drafts
     gen_stats["accept_rate"] = gen_stats["accepted"] / max(gen_stats["drafted"], 1)
-    del gen
+    sess.fill_synthetic(ctx - n_prompt, seed=3)
+    prompt = md.make_prompt(n_prompt, cfg["vocab"], seed=1, cycles=cyc)
+    sess.prefill(prompt)
+    sess.result()
+    sess.commit((n_prompt - 1) % 8 + 1)
 
     # --- the verify step alone: one pass of m rows, device time, for m = 1 and m = 4 (spec K=3), median of 15
     def pass_us(m, n=15):
-        ids = [int(t) for t in prompt[:m]]
+        ids = [int(prompt[0])] * m   # drafts that repeat the token: rejected, so the pass carries acceptance, replay and commit, and keeps 1 row
         ts = []
         for i in range(n + 3):
             p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             p0.record(stream)
             sess.verify(ids, accept=1)
             p1.record(stream)
-            sess.result()
-            sess.commit(1)
+            (kept, _), _, _ = sess.result()
+            sess.commit(kept)
             if i >= 3:
                 ts.append(p0.elapsed_time(p1) * 1e3)
         ts.sort()
@@ -255,7 +320,7 @@ def run_c3(args):
     step_us = {m: pass_us(m) for m in (1, 4)}
     # --- routing of one 4-row pass: distinct experts per layer (the bytes the pass must read)
     sess.trace_routes(True)
-    sess.verify([int(t) for t in prompt[:4]], accept=1)
+    sess.verify([int(t) for t in prompt[:4]], accept=0)
     sess.result()
     ridx, _ = sess.routes()
     sess.commit(1)
@@ -275,8 +340,8 @@ def run_c3(args):
         szlib.check(L.sz_trace_begin(arr, nev, sess.stream))
         sess.verify([int(t) for t in prompt[:4]], accept=1)
         n_k = L.sz_trace_end()
-        sess.result()
-        sess.commit(1)
+        (kept, _), _, _ = sess.result()
+        sess.commit(kept)
     per = {}
     for i in range(1, n_k):
         per.setdefault(L.sz_trace_name(i).decode(), []).append(evs[i - 1].elapsed_time(evs[i]) * 1e3)
@@ -296,8 +361,10 @@ def run_c3(args):
     by = c3_bytes(cfg, ctx, distinct, dense_bytes)
     be = expert_bytes("exl3", cfg["hidden"], cfg["expert_ff"])
     # traffic: dram__bytes_read + write of one launch of this kernel on these shapes (39 + 1 experts), from an ncu --set full capture
-    roof = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "traffic": GATEUP_TRAFFIC if world == 1 else None,
-            "traffic_source": "ncu capture of the same kernel and shapes on the c2-moe workload (40 experts a launch)", "kernel": "gateup_exl3s"}
+    roof = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind,
+            "traffic": gateup_traffic(sum(distinct) / len(distinct) / world + 1),
+            "traffic_source": "profiles/c2_moe_gateup_exl3_full.md: ncu capture of the same kernel and expert shapes on the c2-moe workload, "
+                              "scaled by the experts a launch streams", "kernel": "gateup_exl3s"}
     ks = kern.get("gateup_exl3s")
     if ks:
         # gate + up of a layer's distinct routed experts and of the shared expert: 2/3 of their bytes, one launch a layer
@@ -311,18 +378,13 @@ def run_c3(args):
     value = toks / (dev_ms * 1e-3)
     cpu = None
     if world == 1 and args.cpu_seconds > 0:
-        cpu = cpu_c3(pkg, args.cpu_seconds, os.cpu_count() or 1, args.head)
+        cpu = cpu_c3(pkg, args.cpu_seconds, os.cpu_count() or 1, args.head, ctx)
     line = {
-        "metric": C3_METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": W,
+        "metric": C3_METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": W, "rounds_timed": rounds,
         "ms_per_step": dev_ms / max(rounds, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32 activations, f16 EXL3 codebook weights, int8 Q8_0 / Q8_KV, f32 accumulate (router, norms, combine in f64)",
         "data": "synthetic",
-        "config": {"workload": "c3", "n_layer": cfg["n_layer"], "hidden": cfg["hidden"], "n_expert": cfg["n_expert"], "top_k": cfg["n_expert_used"],
-                   "expert_ff": cfg["expert_ff"], "vocab": cfg["vocab"], "experts": "exl3-3bit", "dense": "q8_0", "kv": "q8_kv",
-                   "head": {"q8": "q8_0, read in full", "exl3": "exl3-4bit, read in full", "proxy": "exl3-4bit screened by its 2-bit proxy (128 blocks a row)"}[args.head],
-                   "context": ctx, "spec_k": 3, "batch": 1, "greedy": True, "cycle_alpha": args.alpha,
-                   "parallelism": "ep%d" % world if world > 1 else "single", "exchange": args.exchange if world > 1 else None,
-                   "l2": "inputs larger than L2: a pass streams ~%.1f GB of weights and cache" % (by["all"] / 1e9)},
+        "config": c3_config(args, cfg, ctx, by["all"]),
         "speculation": gen_stats, "verify_step_us": {"rows_1": step_us[1], "rows_4": step_us[4]},
         "roofline": roof, "cpu_baseline": cpu,
         "e2e": {"value": toks / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * rows_avg, "d2h_bytes_per_step": 8 + 512 * rows_avg,
@@ -333,11 +395,12 @@ def run_c3(args):
     out.emit(json.dumps(line))
 
 
-def cpu_c3(pkg, budget_s, threads, head="q8"):
-    """Accepted tok/s of the CPU restatement of the reference's scalar path on the config-3 shapes.  The CPU path verifies one
-    token at a time (a batched pass is bitwise the one-at-a-time pass there), so its accepted tok/s is 1 / (seconds a token).
-    Sample: models of 4 and of 8 layers (one and two periods of the 3:1 pattern) with the full-size layers, vocabulary and head, a
-    few tokens each; a token of the 48-layer model costs t4 + 11 * (t8 - t4)."""
+def cpu_c3(pkg, budget_s, threads, head="q8", ctx=C3_CTX):
+    """Accepted tok/s of the CPU restatement of the reference's scalar path on the config-3 shapes, at the benchmark's context.
+    The CPU path verifies one token at a time (a batched pass is bitwise the one-at-a-time pass there), so its accepted tok/s is
+    1 / (seconds a token).  Sample: models of 4 and of 8 layers (one and two periods of the 3:1 pattern) with the full-size layers,
+    vocabulary and head; the attention layers' caches are filled to the benchmark's context with the same seeded history the GPU
+    arm uses, then a few tokens are stepped; a token of the 48-layer model costs t4 + 11 * (t8 - t4)."""
     import torch  # noqa: F401
     from oracle import binding as ob
     md, szlib = pkg.model, pkg.lib
@@ -351,6 +414,7 @@ def cpu_c3(pkg, budget_s, threads, head="q8"):
                           cycle_alpha=C3_ALPHA if head == "q8" else 0.0, head_type=szlib.TYPE_Q8_0 if head == "q8" else szlib.TYPE_EXL3(4))
         hm = md.HostModel(M)
         s = ob.Session(hm, kv_q8=True, threads=threads)
+        s.fill_synthetic(max(ctx - 32, 0), seed=3)
         s.step(1, want_logits=True)  # warm: page the weights in
         t0, n = time.perf_counter(), 0
         while True:
@@ -363,26 +427,26 @@ def cpu_c3(pkg, budget_s, threads, head="q8"):
         del s, hm, M
     t_tok = per[4] + 11 * max(per[8] - per[4], 0.0)
     return {"value": 1.0 / t_tok, "unit": "tok/s", "cores": threads, "kind": "port",
-            "sample": "%d tokens through 4- and 8-layer slices of the model (full-size layers, vocabulary, head), short context; "
-                      "seconds a token extrapolated to 48 layers: %.3f" % (ntok, t_tok),
+            "sample": "%d tokens through 4- and 8-layer slices of the model (full-size layers, vocabulary, head) at context %d; "
+                      "seconds a token extrapolated to 48 layers: %.3f" % (ntok, ctx, t_tok),
             "seconds_per_token": t_tok, "t4": per[4], "t8": per[8]}
 
 
 def run_reference_c3(args):
     """The reference arm: the reference's own CPU implementation of the path - its scalar Session restated in C (the reference is
-    Rust and cannot be built here) - on all host cores, on a bounded sample of the config-3 workload."""
+    Rust and cannot be built here) - on all host cores, on a bounded sample of the config-3 workload at the same context."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     import __graft_entry__ as graft
     pkg = graft.load_package()
     threads = os.cpu_count() or 1
-    cpu = cpu_c3(pkg, max(10.0, min(60.0, 2.0 * args.steps)), threads, args.head)
+    cpu = cpu_c3(pkg, max(10.0, min(60.0, 2.0 * args.steps)), threads, args.head, args.ctx)
     v = cpu["value"]
     cpu_line = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps({
         "impl": "reference", "metric": C3_METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (f64 accumulate)",
-        "data": "synthetic", "config": {"workload": "c3", "context": "short (the sample does not fill 24576 positions)", "spec_k": 3, "batch": 1},
+        "data": "synthetic", "config": c3_config(args, dict(C3, n_layer=args.n_layer), args.ctx),
         "cpu_baseline": cpu_line, "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
@@ -565,6 +629,8 @@ def main():
     ap.add_argument("--head", default="proxy", choices=["q8", "exl3", "proxy"],
                     help="c3: output.weight as Q8_0 read in full, as 4-bit EXL3 read in full, or EXL3 screened by its 2-bit proxy (Q2_P)")
     ap.add_argument("--ctx", type=int, default=C3_CTX, help="c3: context length the decode runs at")
+    ap.add_argument("--request-tokens", type=int, default=96, help="c3: tokens decoded after each request's 256-token prompt")
+    ap.add_argument("--beta", type=float, default=None, help="c3: how strongly the synthetic model leans towards skipping a token of its cycle")
     ap.add_argument("--n-layer", type=int, default=C3["n_layer"], help="c3: layers (a smaller model for a quick check; not the benchmark)")
     ap.add_argument("--format", default="exl3", choices=["exl3", "iq3_s", "q8_0"])
     ap.add_argument("--also", default="iq3_s", help="comma list of further formats to time and report under 'also' ('' for none)")
@@ -575,6 +641,8 @@ def main():
     args = ap.parse_args()
     if args.alpha is None:
         args.alpha = C3_ALPHA_BY_HEAD[args.head]
+    if args.beta is None:
+        args.beta = C3_BETA_BY_HEAD[args.head]
     if args.workload == "c3":
         return run_reference_c3(args) if args.impl == "reference" else run_c3(args)
     if args.impl == "reference":
@@ -608,8 +676,8 @@ def main():
         name = next((n for n in names if n in r["kernels"]), names[0])
         ks = r["kernels"].get(name)
         bytes_pair = (r["distinct"] + 1) * r["expert_bytes"] * 2 / 3
-        out = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "traffic": GATEUP_TRAFFIC if name == "gateup_exl3s" else None,
-               "kernel": name}
+        out = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind,
+               "traffic": gateup_traffic(r["distinct"] + 1) if name == "gateup_exl3s" else None, "kernel": name}
         if ks:
             per_step = max(1, round(ks["launches"] / max(args.steps, 1)))
             dur_us = ks["avg_us"] * per_step

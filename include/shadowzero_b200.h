@@ -209,6 +209,16 @@ int sz_session_commit(sz_session* s, int keep, uint64_t stream);
 /* Benchmarks: pretend `len` tokens were fed - seeded pseudo-random keys and values in the first `len` cache positions of every
  * attention layer, zero recurrent state - so a long context needs no long prefill.  Resets the session first. */
 int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, uint64_t stream);
+/* Copies one piece of the committed state to host memory and synchronises - what GpuSession::snapshot (session.rs:3407-3459) saves,
+ * for tests and checkpoints.  DELTA_S: f32 [v heads][d][d] (key index, then value index) and DELTA_CONV: f32 [conv_k - 1][channels],
+ * oldest row first, of DeltaNet layer `layer`; KV_K / KV_V: the first sz_session_len positions of attention layer `layer` in the
+ * reference's order [position][kv head][head bytes] (head bytes: 4 head_dim, or the packed Q8_KV head).  `bytes` must be the exact
+ * size of the piece; no pass may be pending. */
+#define SZ_STATE_DELTA_S 0
+#define SZ_STATE_DELTA_CONV 1
+#define SZ_STATE_KV_K 2
+#define SZ_STATE_KV_V 3
+int sz_session_export(sz_session* s, int what, int layer, void* dst, int64_t bytes, uint64_t stream);
 int sz_session_trace_routes(sz_session* s, int on);
 int sz_session_routes(sz_session* s, int32_t* idx, double* w, uint64_t stream);
 
@@ -296,6 +306,9 @@ int sz_moe_finish(uint64_t y_fix, int m, int hidden, uint64_t y, uint64_t stream
  *   sz_ep_p2p_status: 1 in *error once a wait of this rank ran out (a peer died or fell behind by more than the poll budget):
  *   the pass still ends, its output is wrong, and every later wait of this rank returns at once.
  * All ranks must attach zeroed buffers and then run the same sequence of passes.
+ * A session's recorded passes (CUDA graphs) carry the attached addresses: while such a session is alive sz_ep_p2p_attach and
+ * sz_ep_p2p_detach return SZ_E_ARG, and sz_ep_p2p_free / sz_ep_ipc_close refuse a buffer that is attached.  Destroy the sessions,
+ * detach, then close and free.  Passes recorded before an attach (or an sz_ep_init) are dropped and recorded again.
  * sz_moe_verify_partial with y_fix = 0 pushes the share; sz_moe_finish_exchange adds up (the two halves, for tests that run several
  * ranks on one GPU one after the other). */
 int sz_ep_p2p_bytes(int world, int hidden, int64_t* bytes);
@@ -305,7 +318,7 @@ int sz_ep_ipc_export(uint64_t ptr, uint8_t handle[64]);
 int sz_ep_ipc_import(const uint8_t handle[64], uint64_t* ptr);
 int sz_ep_ipc_close(uint64_t ptr);
 int sz_ep_p2p_attach(int rank, int world, int hidden, const uint64_t* bufs);
-void sz_ep_p2p_detach(void);
+int sz_ep_p2p_detach(void);
 int sz_ep_p2p_world(void);
 int sz_ep_p2p_status(int* error);
 int sz_moe_finish_exchange(const sz_moe_layer* layer, int m, uint64_t y, uint64_t stream);
@@ -316,10 +329,17 @@ int sz_moe_finish_exchange(const sz_moe_layer* layer, int m, uint64_t y, uint64_
  * and so have no buffer to pass.  The scratch is a fixed array of sz_moe_static_scratch_max() bytes (4 MiB) that the library keeps
  * in the memory of every GPU that loads it, until the process exits.  The call allocates nothing.
  *   - A layer shape and row count whose sz_moe_scratch_bytes exceeds the array is refused with SZ_E_SCRATCH.
- *   - The first call on a device looks the array up and clears its counters; make that call before any stream capture begins.
+ *   - The first call on a device looks the array up and clears its counters (a synchronous clear: it is ordered before work on
+ *     every stream); make that call before any stream capture begins.
+ *   - The array's address is private, so the error word that a kernel raises when one of its bounded waits runs out is read with
+ *     sz_moe_static_status (it synchronises the stream); nonzero means the y of that call is not valid.  sz_moe_static_reset clears
+ *     the control words again - the static twin of sz_moe_scratch_init - and looks the array up anew: call it after a failed call,
+ *     and after a cudaDeviceReset (the address the library remembered is stale then).
  *   - All calls on a device share the one array, and it keeps what the last call left: two calls that can overlap on the GPU
  *     (different streams without an ordering between them) race.  Calls on one stream, or ordered by events, are safe. */
 int sz_moe_static_scratch_max(int64_t* bytes);
+int sz_moe_static_status(int* error, uint64_t stream);
+int sz_moe_static_reset(void);
 int sz_moe_verify_static(const sz_moe_layer* layer, uint64_t x, int m, uint64_t y, uint64_t route_idx, uint64_t route_w,
                          uint64_t stream);
 

@@ -71,6 +71,9 @@ def lib():
         L.szo_session_clone.restype = C.c_void_p
         L.szo_session_clone.argtypes = [C.c_void_p]
         L.szo_session_step.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+        L.szo_session_fill_synthetic.argtypes = [C.c_void_p, C.c_int, C.c_uint32]
+        L.szo_session_state.restype = C.c_void_p
+        L.szo_session_state.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
         L.szo_lookup.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
         L.szo_drafter_new.restype = C.c_void_p
         L.szo_drafter_new.argtypes = [C.c_int, C.c_int, C.c_int]
@@ -243,6 +246,16 @@ class Session:
         u = np.empty(self.hm.cfg["hidden"], dtype=np.float32) if want_u else None
         lib().szo_session_step(self.h, int(token), _p(lg) if want_logits else None, _p(u) if want_u else None)
         return (lg, u) if want_u else lg
+
+    def fill_synthetic(self, length, seed=1):
+        lib().szo_session_fill_synthetic(self.h, length, seed)
+
+    def state(self, what, layer):
+        """A copy of one piece of the state: 0 recurrent state, 1 carried conv rows (float32), 2 / 3 the K / V cache (bytes)."""
+        n = C.c_size_t()
+        p = lib().szo_session_state(self.h, what, layer, C.byref(n))
+        raw = np.frombuffer(C.string_at(p, n.value), dtype=np.uint8).copy()
+        return raw.view(np.float32) if what < 2 else raw
 
     def routes(self):
         n, k = self.hm.cfg["n_layer"], self.hm.cfg["n_expert_used"]

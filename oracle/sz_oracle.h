@@ -101,6 +101,10 @@ const double* szo_session_route_weights(const szo_session* s);
 void szo_session_assign(szo_session* dst, const szo_session* src); /* snapshot / restore */
 szo_session* szo_session_clone(const szo_session* src);
 void szo_session_step(szo_session* s, uint32_t token, float* logits, float* final_u); /* forward.rs:751-794 */
+/* the library's synthetic history (sz_session_fill_synthetic), value for value: no counterpart in the reference */
+void szo_session_fill_synthetic(szo_session* s, int len, uint32_t seed);
+/* one piece of the state: 0 recurrent state [v heads][d][d], 1 carried conv rows, 2 / 3 K / V cache [position][kv head][head] */
+const void* szo_session_state(const szo_session* s, int what, int l, size_t* bytes);
 
 int szo_lookup(const uint32_t* hist, int n_hist, int k, const int* lens, int n_lens, uint32_t* out); /* engine.rs:829-839 */
 typedef struct szo_drafter szo_drafter;

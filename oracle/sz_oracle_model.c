@@ -189,6 +189,63 @@ szo_session* szo_session_clone(const szo_session* src) {
     return d;
 }
 
+/* The synthetic history of the library's sz_session_fill_synthetic, value for value: `len` positions of every attention layer's
+ * cache from an integer hash of (kv head, position, element, layer, seed), zero recurrent state.  Not part of the reference: a long
+ * context for tests and benchmarks without a long prefill.  Packed heads get codes in [-127, 127] and the scale 2^-7 (f16 0x2000). */
+static uint32_t fill_hash(uint64_t hp, uint32_t i, uint32_t seed, uint32_t layer) {
+    uint32_t x = (uint32_t)(hp * 2654435761u) ^ (uint32_t)(i * 40503u) ^ seed ^ (uint32_t)(layer * 97u);
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+    return x;
+}
+
+void szo_session_fill_synthetic(szo_session* s, int len, uint32_t seed) {
+    const sz_model_config* c = &s->m->cfg;
+    size_t nkv = (size_t)c->n_kv_head, hd = (size_t)c->head_dim, hb = szo_kv_q8_head_bytes((int)hd);
+    uint32_t ai = 0;
+    for (int l = 0; l < c->n_layer; l++) {
+        layer_state* L = &s->st[l];
+        if (!is_attention(c, l)) {
+            memset(L->s, 0, delta_s_floats(c) * sizeof(float));
+            memset(L->conv, 0, (size_t)(c->conv_k - 1) * delta_channels(c) * sizeof(float));
+            continue;
+        }
+        kv_reserve(s, L, (size_t)len);
+        for (int which = 0; which < 2; which++) {
+            uint32_t sd = which ? seed ^ 0x9e3779b9u : seed;
+            for (size_t h = 0; h < nkv; h++)
+                for (size_t pos = 0; pos < (size_t)len; pos++) {
+                    uint64_t hp = (uint64_t)h * (uint64_t)len + pos;
+                    if (s->kv_q8) {
+                        uint8_t* p = (which ? L->vq : L->kq) + (pos * nkv + h) * hb;
+                        for (size_t i = 0; i < hd; i++) p[i] = (uint8_t)(int8_t)((int)(fill_hash(hp, (uint32_t)i, sd, ai) % 255u) - 127);
+                        uint16_t* sc = (uint16_t*)(p + hd);
+                        for (size_t g = 0; g < (hb - hd) / 2; g++) sc[g] = g < hd / 32 ? (uint16_t)0x2000 : (uint16_t)0;
+                    } else {
+                        float* p = (which ? L->v : L->k) + (pos * nkv + h) * hd;
+                        for (size_t i = 0; i < hd; i++) p[i] = ((float)(fill_hash(hp, (uint32_t)i, sd, ai) % 2001u) - 1000.0f) * 1e-3f;
+                    }
+                }
+        }
+        ai++;
+    }
+    s->len = (size_t)len;
+}
+
+/* Where one piece of the session's state lives (what: 0 recurrent state, 1 carried conv rows, 2 K cache, 3 V cache) and its size. */
+const void* szo_session_state(const szo_session* s, int what, int l, size_t* bytes) {
+    const sz_model_config* c = &s->m->cfg;
+    const layer_state* L = &s->st[l];
+    size_t kvb = s->len * (size_t)c->n_kv_head * (s->kv_q8 ? szo_kv_q8_head_bytes(c->head_dim) : (size_t)c->head_dim * sizeof(float));
+    switch (what) {
+        case 0: *bytes = delta_s_floats(c) * sizeof(float); return L->s;
+        case 1: *bytes = (size_t)(c->conv_k - 1) * delta_channels(c) * sizeof(float); return L->conv;
+        case 2: *bytes = kvb; return s->kv_q8 ? (const void*)L->kq : (const void*)L->k;
+        case 3: *bytes = kvb; return s->kv_q8 ? (const void*)L->vq : (const void*)L->v;
+    }
+    *bytes = 0;
+    return NULL;
+}
+
 /* forward.rs:797-817 */
 static void hc_read(const szo_session* s, const float* r, const sz_hc* hc, int inject, float* u, float* g) {
     const sz_model_config* c = &s->m->cfg;

@@ -28,6 +28,7 @@ struct Ep {
     int rank = 0, world = 0;
     int graph_refs = 0;  // recorded passes (CUDA graphs) that contain a collective of this communicator
 } g_ep;
+int g_ep_generation = 0;  // bumped whenever the exchange set-up changes (communicator up / down, buffers attached / detached)
 
 int load_nccl() {
     if (g_ep.lib) return SZ_OK;
@@ -61,7 +62,7 @@ extern "C" int sz_ep_unique_id(uint8_t id[128]) {
 extern "C" int sz_ep_init(int rank, int world, const uint8_t id[128]) {
     if (world < 1 || rank < 0 || rank >= world) return sz_fail(SZ_E_ARG, "rank %d of %d", rank, world);
     if (g_ep.world) return sz_fail(SZ_E_ARG, "sz_ep_init: already initialised (%d ranks)", g_ep.world);
-    if (world == 1) { g_ep.rank = 0; g_ep.world = 1; return SZ_OK; }  // one rank: nothing to exchange, NCCL is not needed
+    if (world == 1) { g_ep.rank = 0; g_ep.world = 1; g_ep_generation++; return SZ_OK; }  // one rank: nothing to exchange, NCCL is not needed
     if (!id) return sz_fail(SZ_E_ARG, "null id");
     int rc = load_nccl();
     if (rc) return rc;
@@ -70,10 +71,13 @@ extern "C" int sz_ep_init(int rank, int world, const uint8_t id[128]) {
     const int e = g_ep.init(&g_ep.comm, world, u, rank);
     if (e) return sz_fail(SZ_E_CUDA, "ncclCommInitRank: %s", g_ep.errstr(e));
     g_ep.rank = rank; g_ep.world = world;
+    g_ep_generation++;
     return SZ_OK;
 }
 
 extern "C" int sz_ep_world(void) { return g_ep.world; }
+// Sessions compare this with the value they recorded their passes under: a pass recorded under another exchange set-up is dropped.
+int sz_ep_generation(void) { return g_ep_generation; }
 
 int sz_ep_graph_refs(int delta) { return g_ep.graph_refs += delta; }
 
@@ -87,6 +91,7 @@ extern "C" int sz_ep_destroy(void) {
     g_ep.comm = nullptr;
     g_ep.world = 0;
     g_ep.rank = 0;
+    g_ep_generation++;
     return SZ_OK;
 }
 
@@ -107,8 +112,19 @@ struct P2p {
     int hidden = 0;
     int polls = SZ_EP_SPIN_LIMIT;   // how often a finish block polls a counter before it gives up
     u8* buf[SZ_EP_MAX_RANKS] = {};
+    int graph_refs = 0;             // recorded passes of live sessions whose kernels hold these buffer addresses
 } g_p2p;
+
+bool p2p_attached(uint64_t ptr) {
+    for (int r = 0; r < g_p2p.world; r++)
+        if ((uint64_t)g_p2p.buf[r] == ptr) return true;
+    return false;
+}
 }  // namespace
+
+// A recorded pass bakes the buffer addresses, the rank and the poll budget into its kernels' arguments: while one is alive the
+// attachment must not change and the buffers must stay mapped (a replay would store into freed or unmapped peer memory).
+int sz_ep_p2p_graph_refs(int delta) { return g_p2p.graph_refs += delta; }
 
 // Sums the ranks' rows of the current slot into y.  grid: any; block 256.  Thread 0 of every block waits for the sources (a bounded
 // number of polls; on running out it raises the header's error word and the block goes on with what is there, so the kernel always
@@ -168,6 +184,7 @@ extern "C" int sz_ep_p2p_alloc(int64_t bytes, uint64_t* ptr) {
     return SZ_OK;
 }
 extern "C" int sz_ep_p2p_free(uint64_t ptr) {
+    if (ptr && p2p_attached(ptr)) return sz_fail(SZ_E_ARG, "sz_ep_p2p_free: the buffer is attached to the exchange; sz_ep_p2p_detach first");
     if (ptr) SZ_CUDA(cudaFree((void*)ptr));
     return SZ_OK;
 }
@@ -189,6 +206,7 @@ extern "C" int sz_ep_ipc_import(const uint8_t handle[64], uint64_t* ptr) {
     return SZ_OK;
 }
 extern "C" int sz_ep_ipc_close(uint64_t ptr) {
+    if (ptr && p2p_attached(ptr)) return sz_fail(SZ_E_ARG, "sz_ep_ipc_close: the mapping is attached to the exchange; sz_ep_p2p_detach first");
     if (ptr) SZ_CUDA(cudaIpcCloseMemHandle((void*)ptr));
     return SZ_OK;
 }
@@ -200,6 +218,9 @@ extern "C" int sz_ep_p2p_attach(int rank, int world, int hidden, const uint64_t*
         return sz_fail(SZ_E_ARG, "sz_ep_p2p_attach: rank %d of %d, hidden %d", rank, world, hidden);
     for (int r = 0; r < world; r++)
         if (!bufs[r] || (bufs[r] & 255)) return sz_fail(SZ_E_ARG, "sz_ep_p2p_attach: buffer %d is null or not 256-byte aligned", r);
+    if (g_p2p.graph_refs > 0)
+        return sz_fail(SZ_E_ARG, "sz_ep_p2p_attach: %d recorded pass(es) of live sessions hold the current attachment; destroy the sessions first", g_p2p.graph_refs);
+    g_ep_generation++;
     g_p2p.rank = rank; g_p2p.world = world; g_p2p.hidden = hidden;
     {
         // the poll budget of a wait: about two seconds by default (a peer may be busy recording a graph or loading a module);
@@ -211,7 +232,13 @@ extern "C" int sz_ep_p2p_attach(int rank, int world, int hidden, const uint64_t*
     for (int r = 0; r < SZ_EP_MAX_RANKS; r++) g_p2p.buf[r] = r < world ? (u8*)bufs[r] : nullptr;
     return SZ_OK;
 }
-extern "C" void sz_ep_p2p_detach(void) { g_p2p = P2p(); }
+extern "C" int sz_ep_p2p_detach(void) {
+    if (g_p2p.graph_refs > 0)
+        return sz_fail(SZ_E_ARG, "sz_ep_p2p_detach: %d recorded pass(es) of live sessions hold the attachment; destroy the sessions first", g_p2p.graph_refs);
+    g_p2p = P2p();
+    g_ep_generation++;
+    return SZ_OK;
+}
 extern "C" int sz_ep_p2p_world(void) { return g_p2p.world; }
 
 // 0: no wait of this rank's exchanges ever ran out.  Synchronises the device.

@@ -20,8 +20,11 @@ struct SzLayerBuf {
     int attn_index;    // index among attention layers, or -1
 };
 
-int sz_ep_graph_refs(int delta);  // sz_ep.cu: recorded passes that hold the communicator
+int sz_ep_graph_refs(int delta);      // sz_ep.cu: recorded passes that hold the communicator
+int sz_ep_p2p_graph_refs(int delta);  // ... that hold the addresses of the attached peer-memory exchange
+int sz_ep_generation(void);           // changes whenever the exchange set-up does
 extern "C" int sz_ep_world(void);
+extern "C" int sz_ep_p2p_world(void);
 
 struct sz_session {
     sz_model model;
@@ -54,18 +57,27 @@ struct sz_session {
     int64_t moe_scratch_bytes;
     int attn_splits, attn_splits2;
     // host staging (pinned, so that a captured graph re-reads it at every launch)
-    int32_t* h_pin;   // [0..8): ids of the pass, [8]: keep of a host-decided commit, [10..12]: error words read back, [16..24): SzSampleArgs
+    int32_t* h_pin;   // [0..8): ids of the pass, [8]: keep of a host-decided commit, [10..12]: error words read back, [13..14]: {kept, next}, [16..24): SzSampleArgs
     sz_sampler samp = {};   // sz_session_set_sampler
     int has_samp = 0;
-    int pending_committed;  // the pending pass was already committed on the device (acceptance modes GREEDY / ALL)
+    int pending_committed;  // the pending pass was already committed on the device (acceptance modes GREEDY / ALL / SAMPLED)
+    int device_keep;        // rows the device kept in that pass: known at launch for ALL, read by sz_session_result otherwise (-1: not read yet)
     int inflight;           // a pass was launched and the stream not synchronised since: the id staging buffer may still be read
     int use_graphs;
     std::map<int, cudaGraphExec_t> graphs;
     int ep_graphs = 0;      // how many of them recorded a collective of the expert-parallel communicator
+    int p2p_graphs = 0;     // how many of them recorded kernels that address the attached peer-memory exchange
+    int graph_gen = 0;      // the exchange set-up (sz_ep_generation) the graphs were recorded under
     sz_head head = {};      // rows > 0: output.weight is an EXL3 blob and the head runs through sz_head_top
-    ~sz_session() {
+    void drop_graphs() {
         for (auto& kv : graphs) cudaGraphExecDestroy(kv.second);
+        graphs.clear();
         sz_ep_graph_refs(-ep_graphs);
+        sz_ep_p2p_graph_refs(-p2p_graphs);
+        ep_graphs = p2p_graphs = 0;
+    }
+    ~sz_session() {
+        drop_graphs();
         if (h_pin) cudaFreeHost(h_pin);
     }
 };
@@ -775,6 +787,11 @@ static int sz_verify_impl(sz_session* s, const int32_t* ids, int m, int accept_m
     bool traced = sz_trace_active();
     const bool capturable = st != (cudaStream_t)0 && st != cudaStreamLegacy && st != cudaStreamPerThread;  // the default stream cannot record
     if (s->use_graphs && capturable && !traced && !s->want_routes) {
+        if (s->graph_gen != sz_ep_generation()) {  // recorded under another exchange set-up (or none): those launches no longer apply
+            if (!s->graphs.empty()) SZ_CUDA(cudaStreamSynchronize(st));
+            s->drop_graphs();
+            s->graph_gen = sz_ep_generation();
+        }
         auto it = s->graphs.find(key);
         if (it == s->graphs.end()) {
             // first use: run the pass eagerly (this also does every one-time function-attribute set-up), then record it for the next time
@@ -792,7 +809,8 @@ static int sz_verify_impl(sz_session* s, const int32_t* ids, int m, int accept_m
                     cudaGraphExec_t ge = nullptr;
                     if (cudaGraphInstantiate(&ge, g, 0) == cudaSuccess) {
                         s->graphs[key] = ge;
-                        if (sz_ep_world() > 1) { s->ep_graphs++; sz_ep_graph_refs(1); }
+                        if (sz_ep_p2p_world() > 0) { s->p2p_graphs++; sz_ep_p2p_graph_refs(1); }
+                        else if (sz_ep_world() > 1) { s->ep_graphs++; sz_ep_graph_refs(1); }
                     }
                 }
                 if (g) cudaGraphDestroy(g);
@@ -807,6 +825,7 @@ static int sz_verify_impl(sz_session* s, const int32_t* ids, int m, int accept_m
     }
     s->last_m = m;
     s->pending_committed = accept_mode != SZ_ACCEPT_NONE;
+    s->device_keep = accept_mode == SZ_ACCEPT_ALL ? m : -1;
     s->inflight = 1;
     return SZ_OK;
 }
@@ -814,7 +833,7 @@ static int sz_verify_impl(sz_session* s, const int32_t* ids, int m, int accept_m
 extern "C" int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* top, float* logits, uint64_t stream) {
     if (!s || !s->last_m) return sz_fail(SZ_E_ARG, "no pass to read");
     cudaStream_t st = (cudaStream_t)stream;
-    if (keep_next) SZ_CUDA(cudaMemcpyAsync(keep_next, s->res, 8, cudaMemcpyDeviceToHost, st));
+    SZ_CUDA(cudaMemcpyAsync(s->h_pin + 13, s->res, 8, cudaMemcpyDeviceToHost, st));
     if (top) SZ_CUDA(cudaMemcpyAsync(top, s->top, (size_t)s->last_m * 128 * 4, cudaMemcpyDeviceToHost, st));
     if (logits && s->head.k_blk > 0)
         return sz_fail(SZ_E_ARG, "sz_session_result: with the screened head (SZ_HEAD_PROXY) only the kept blocks have logits; ask for the top-64");
@@ -832,6 +851,8 @@ extern "C" int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* to
     SZ_CUDA(cudaMemcpyAsync(s->h_pin + 11, s->moe_scratch + 4, 4, cudaMemcpyDeviceToHost, st));
     SZ_CUDA(cudaStreamSynchronize(st));
     s->inflight = 0;
+    if (keep_next) { keep_next[0] = s->h_pin[13]; keep_next[1] = s->h_pin[14]; }
+    if (s->pending_committed) s->device_keep = s->h_pin[13];
     if (s->h_pin[10] || s->h_pin[11] || s->h_pin[12])
         return sz_fail(SZ_E_DEVICE, "a bounded wait on an asynchronous copy ran out (session word %d, MoE word %d, head word %d): the results of this pass are not valid",
                        s->h_pin[10], s->h_pin[11], s->h_pin[12]);
@@ -855,7 +876,11 @@ extern "C" int sz_session_commit(sz_session* s, int keep, uint64_t stream) {
     const int m = s->last_m;
     if (keep < 0 || keep > m) return sz_fail(SZ_E_ARG, "keep = %d of a pass of %d rows", keep, m);
     cudaStream_t st = (cudaStream_t)stream;
-    if (!s->pending_committed) {
+    if (s->pending_committed) {
+        // the device already advanced its state by the rows IT kept: the host's bookkeeping must follow that number, not the caller's
+        if (s->device_keep < 0) return sz_fail(SZ_E_ARG, "the device decided this pass: read sz_session_result before sz_session_commit");
+        if (keep != s->device_keep) return sz_fail(SZ_E_ARG, "keep = %d, but the device kept %d rows of this pass", keep, s->device_keep);
+    } else {
         if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
         s->h_pin[8] = keep;
         SZ_CUDA(cudaMemcpyAsync(s->res, s->h_pin + 8, 4, cudaMemcpyHostToDevice, st));
@@ -928,6 +953,43 @@ extern "C" int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, 
     SZ_CUDA(cudaMemcpyAsync(s->state, s->h_pin + 8, 4, cudaMemcpyHostToDevice, st));
     SZ_CUDA(cudaStreamSynchronize(st));
     s->len = len;
+    return SZ_OK;
+}
+
+// ---- committed state to the host ------------------------------------------------------------------------------------------------------
+// What GpuSession::snapshot (crates/shadowzero-cuda/src/session.rs:3407-3459) copies, one piece at a time: the recurrent state and the
+// carried conv rows of a DeltaNet layer (the current buffer), or the cache rows of an attention layer in the reference's order
+// [position][kv head][head bytes] (the library keeps them per KV head).  No pass may be pending.
+extern "C" int sz_session_export(sz_session* s, int what, int layer, void* dst, int64_t bytes, uint64_t stream) {
+    if (!s || !dst) return sz_fail(SZ_E_ARG, "sz_session_export: null argument");
+    if (s->last_m) return sz_fail(SZ_E_ARG, "sz_session_export: a pass is pending; commit it first");
+    const sz_model_config& c = s->model.cfg;
+    if (layer < 0 || layer >= c.n_layer) return sz_fail(SZ_E_ARG, "sz_session_export: layer %d of %d", layer, c.n_layer);
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool attn = sz_is_attn(c, layer);
+    if (what == SZ_STATE_DELTA_S || what == SZ_STATE_DELTA_CONV) {
+        if (attn) return sz_fail(SZ_E_ARG, "sz_session_export: layer %d is an attention layer", layer);
+        const int di = s->lb[layer].delta_index;
+        const int64_t d = c.ssm_head_dim, ch = (2 * (int64_t)c.ssm_k_heads + c.ssm_v_heads) * d;
+        const int64_t n = what == SZ_STATE_DELTA_S ? 4 * (int64_t)c.ssm_v_heads * d * d : 4 * (int64_t)(c.conv_k - 1) * ch;
+        if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_export: %lld bytes given, the piece has %lld", (long long)bytes, (long long)n);
+        const u8* src = what == SZ_STATE_DELTA_S ? (const u8*)s->S[s->cur] : (const u8*)s->conv[s->cur];
+        SZ_CUDA(cudaMemcpyAsync(dst, src + (int64_t)di * n, (size_t)n, cudaMemcpyDeviceToHost, st));
+    } else if (what == SZ_STATE_KV_K || what == SZ_STATE_KV_V) {
+        if (!attn) return sz_fail(SZ_E_ARG, "sz_session_export: layer %d is a DeltaNet layer", layer);
+        const int ai = s->lb[layer].attn_index;
+        const int64_t hb = (s->flags & SZ_KV_Q8) ? (c.head_dim + (((c.head_dim >> 5) * 2 + 15) & ~15)) : 4 * (int64_t)c.head_dim;
+        const int64_t n = (int64_t)s->len * c.n_kv_head * hb;
+        if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_export: %lld bytes given, %d positions take %lld", (long long)bytes, s->len, (long long)n);
+        const u8* base = (what == SZ_STATE_KV_K ? s->kc : s->vc) + (int64_t)ai * s->ctx * c.n_kv_head * hb;
+        for (int h = 0; h < c.n_kv_head && s->len > 0; h++)
+            SZ_CUDA(cudaMemcpy2DAsync((u8*)dst + h * hb, (size_t)(c.n_kv_head * hb), base + (int64_t)h * s->ctx * hb, (size_t)hb, (size_t)hb, (size_t)s->len,
+                                      cudaMemcpyDeviceToHost, st));
+    } else {
+        return sz_fail(SZ_E_ARG, "sz_session_export: unknown piece %d", what);
+    }
+    SZ_CUDA(cudaStreamSynchronize(st));
+    s->inflight = 0;
     return SZ_OK;
 }
 

@@ -127,9 +127,11 @@ class PeerExchange:
         return e.value
 
     def close(self):
-        self.lib.sz_ep_p2p_detach()
+        """Detaches, unmaps and frees.  Raises while a session that recorded passes over this exchange is alive (its CUDA graphs hold
+        the buffer addresses): destroy the sessions first."""
+        szlib.check(self.lib.sz_ep_p2p_detach())
         for q in self.mapped:
-            self.lib.sz_ep_ipc_close(q)
+            szlib.check(self.lib.sz_ep_ipc_close(q))
         for p in self.own:
-            self.lib.sz_ep_p2p_free(p)
+            szlib.check(self.lib.sz_ep_p2p_free(p))
         self.mapped, self.own = [], []

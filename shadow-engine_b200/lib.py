@@ -37,6 +37,7 @@ class HeadC(C.Structure):
                 ("weight", C.c_uint64), ("w_q2", C.c_uint64), ("w_sc", C.c_uint64), ("work", C.c_uint64), ("work_bytes", C.c_int64)]
 
 
+STATE_DELTA_S, STATE_DELTA_CONV, STATE_KV_K, STATE_KV_V = range(4)
 HEAD_XR, HEAD_XQ, HEAD_XSC, HEAD_XCORR, HEAD_BMAX, HEAD_SEL, HEAD_ERR = range(7)
 
 # name -> (restype, argtypes); every symbol include/shadowzero_b200.h declares
@@ -71,6 +72,7 @@ SYMBOLS = {
     "sz_session_result": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_uint64]),
     "sz_session_commit": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
     "sz_session_fill_synthetic": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint64]),
+    "sz_session_export": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_uint64]),
     "sz_session_trace_routes": (C.c_int, [C.c_void_p, C.c_int]),
     "sz_session_routes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64]),
     # host side of speculation
@@ -111,11 +113,13 @@ SYMBOLS = {
     "sz_ep_ipc_import": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint64)]),
     "sz_ep_ipc_close": (C.c_int, [C.c_uint64]),
     "sz_ep_p2p_attach": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_uint64)]),
-    "sz_ep_p2p_detach": (None, []),
+    "sz_ep_p2p_detach": (C.c_int, []),
     "sz_ep_p2p_world": (C.c_int, []),
     "sz_ep_p2p_status": (C.c_int, [C.POINTER(C.c_int)]),
     "sz_moe_finish_exchange": (C.c_int, [C.POINTER(MoeLayerC), C.c_int, C.c_uint64, C.c_uint64]),
     "sz_moe_static_scratch_max": (C.c_int, [C.POINTER(C.c_int64)]),
+    "sz_moe_static_status": (C.c_int, [C.POINTER(C.c_int), C.c_uint64]),
+    "sz_moe_static_reset": (C.c_int, []),
     "sz_head_proxy_bytes": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "sz_head_work_bytes": (C.c_int, [C.c_int, C.c_int, C.c_int, C.POINTER(C.c_int64)]),
     "sz_head_work_init": (C.c_int, [C.POINTER(HeadC), C.c_uint64]),

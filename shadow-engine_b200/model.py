@@ -75,7 +75,7 @@ def token_cycles(vocab, seed, cycle=16):
 
 
 def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, shared_type=None, hc_type=szlib.TYPE_BF16, seed=1,
-               sigma=0.02, device="cpu", cycle=16, cycle_alpha=0.0, head_type=None):
+               sigma=0.02, device="cpu", cycle=16, cycle_alpha=0.0, head_type=None, cycle_beta=0.0):
     """Seeded synthetic weights: name -> (ggml type, rows, cols, torch tensor of the stored bytes).  Matrices are N(0, sigma)
     quantised to their type, norm weights are 1, ssm_a is negative, MoE layers come from synth.make_moe_layer.
 
@@ -84,6 +84,11 @@ def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, sha
     (row successor[t] of output.weight = alpha * embedding[t] + sqrt(1 - alpha^2) * noise: still N(0, sigma) entries): the model
     leans towards continuing the cycle of its last token, while the layers' contribution makes it leave the cycle now and then -
     repeated n-grams with occasional surprises, which is what speculation is measured on.
+
+    With cycle_beta > 0 a token also leans, less strongly, towards the token TWO places on in its cycle: when the layers'
+    contribution tips the balance the model skips a token but stays inside its cycle, so a drafter that looks the context up in the
+    history keeps finding it and is right at a position only some of the time - partial acceptance, position by position, as on
+    real text (the reference reports 75 / 75 / 83 % at draft positions 1 / 2 / 3, docs/SPECULATION.md:95-98).
 
     head_type = TYPE_EXL3(k) stores output.weight as an EXL3 blob (random trellis words: no trellis quantiser is available, so
     the head cannot be made from a wanted matrix).  The correlation then runs the other way: the embedding of token t is made
@@ -134,7 +139,11 @@ def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, sha
             rows = rows * (sigma / rows.std(dim=1, keepdim=True).clamp_min(1e-12))
             succ, _ = token_cycles(cfg["vocab"], seed, cycle)
             noise = synth.normal((cfg["vocab"], H), sigma, seed, "token_embd.weight", device)
-            emb = 15.0 * (cycle_alpha * rows[succ.to(rows.device)] + (1.0 - cycle_alpha ** 2) ** 0.5 * noise)
+            succ = succ.to(rows.device)
+            emb = cycle_alpha * rows[succ] + (1.0 - cycle_alpha ** 2) ** 0.5 * noise
+            if cycle_beta > 0.0:
+                emb += cycle_beta * rows[succ[succ]]
+            emb *= 15.0
             del rows, noise
             T["token_embd.weight"] = (dense_type, cfg["vocab"], H, (synth.quantize_q8_0(emb) if dense_type == szlib.TYPE_Q8_0 else emb).contiguous())
         else:
@@ -146,7 +155,10 @@ def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, sha
         noise = synth.normal((cfg["vocab"], H), sigma, seed, "output.weight", device)
         succ, _ = token_cycles(cfg["vocab"], seed, cycle)
         w = torch.empty_like(emb)
-        w[succ.to(emb.device)] = cycle_alpha * (emb / 15.0) + (1.0 - cycle_alpha ** 2) ** 0.5 * noise
+        succ = succ.to(emb.device)
+        w[succ] = cycle_alpha * (emb / 15.0) + (1.0 - cycle_alpha ** 2) ** 0.5 * noise
+        if cycle_beta > 0.0:
+            w[succ[succ]] += cycle_beta * (emb / 15.0)
         if dense_type == szlib.TYPE_Q8_0:
             T["output.weight"] = (dense_type, cfg["vocab"], H, synth.quantize_q8_0(w).contiguous())
         elif dense_type == szlib.TYPE_F32:
@@ -357,6 +369,21 @@ class Session:
 
     def commit(self, keep):
         szlib.check(self.lib.sz_session_commit(self.h, keep, self.stream))
+
+    def export(self, what, layer):
+        """One piece of the committed state (sz_session_export): the recurrent state [v heads, d, d] or the carried conv rows
+        [conv_k - 1, channels] of a DeltaNet layer as float32, or the K / V cache of an attention layer as bytes
+        [positions, kv heads, head bytes]."""
+        c = self.dm.cfg
+        if what == szlib.STATE_DELTA_S:
+            a = np.empty((c["ssm_v_heads"], c["ssm_head_dim"], c["ssm_head_dim"]), dtype=np.float32)
+        elif what == szlib.STATE_DELTA_CONV:
+            a = np.empty((c["conv_k"] - 1, (2 * c["ssm_k_heads"] + c["ssm_v_heads"]) * c["ssm_head_dim"]), dtype=np.float32)
+        else:
+            hb = c["head_dim"] + ((c["head_dim"] // 32 * 2 + 15) & ~15) if self.flags & 1 else 4 * c["head_dim"]
+            a = np.empty((len(self), c["n_kv_head"], hb), dtype=np.uint8)
+        szlib.check(self.lib.sz_session_export(self.h, what, layer, a.ctypes.data_as(C.c_void_p), a.nbytes, self.stream))
+        return a
 
     def generate(self, prompt, max_new, spec_k=3, greedy=True, sampler=None, lookup_min=4, eog=-1, device_accept=True, max_rounds=0):
         p = GenParams(spec_k, max_new, lookup_min, 1 if greedy else 0, eog, 1 if device_accept else 0,

@@ -32,6 +32,7 @@ def emulate(L, x, G):
     ("x3", 512, 32, 4, 256, 256),      # streaming EXL3 kernels, shared expert fused
     ("x3", 1024, 32, 6, 256, 512),     # shared expert on the generic kernels
     ("x3", 512, 32, 6, 128, 0),        # no shared expert
+    ("x3", 2048, 512, 10, 512, 512),   # the benchmark's layer shape (configs 2 and 3)
 ])
 def test_group_sizes_agree_bitwise(ety, H, ne, k, FF, SF):
     ty = {"q8": szlib.TYPE_Q8_0, "iq3": szlib.TYPE_IQ3_S, "x3": szlib.TYPE_EXL3(3)}[ety]
@@ -125,6 +126,40 @@ def test_peer_exchange_wait_runs_out_without_hanging():
         ex.close()
 
 
+def test_exchange_cannot_be_taken_apart_under_a_session_that_recorded_passes():
+    """A recorded pass (CUDA graph) carries the exchange buffers' addresses in its kernel arguments: detaching, re-attaching, unmapping
+    or freeing them while the session lives is refused with an error code (a replay would otherwise write into freed memory).  A
+    group of one rank on this GPU; the stale graph is never replayed."""
+    lib = szlib.load()
+    M = model.make_model(dict(model.TINY, vocab=2048, n_layer=2, attn_interval=2), seed=6)
+    ex = ep.PeerExchange(model.TINY["hidden"], local_world=1)
+    closed = False
+    try:
+        dm = model.DeviceModel(M, "cuda:0", ep=(0, 1))
+        s = model.Session(dm, 64)
+        outs = []
+        for i in range(3):                       # the first pass runs eagerly and is recorded, the others replay it
+            s.verify([5, 6, 7]); outs.append(s.result(logits=True)[2]); s.commit(0)
+        assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
+        assert ex.status() == 0
+        assert lib.sz_ep_p2p_detach() == szlib.E_ARG
+        assert lib.sz_ep_p2p_free(ex.own[0]) == szlib.E_ARG
+        with pytest.raises(szlib.SzError):
+            ex.use(0)                            # a re-attach is a change of the attachment too
+        with pytest.raises(szlib.SzError):
+            ex.close()
+        del s
+        ex.close()
+        closed = True
+        # a session made while nothing is attached records its passes afresh
+        s = model.Session(model.DeviceModel(M, "cuda:0"), 64)
+        s.verify([5, 6, 7]); again = s.result(logits=True)[2]; s.commit(0)
+        assert np.abs(again - outs[0]).max() <= 1e-5 * np.abs(outs[0]).max()
+    finally:
+        if not closed:
+            ex.close()
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -164,6 +199,7 @@ def _rank(rank, world, port, out_dir):
             toks2, _, _ = s2.generate(model.make_prompt(128, model.TINY["vocab"], seed=1, cycles=cyc2), 48, spec_k=3)
             np.save(os.path.join(out_dir, "p%d.npy" % rank), np.asarray(toks2, dtype=np.int64))
             assert ex.status() == 0
+            assert szlib.load().sz_ep_p2p_detach() != 0     # s2's recorded passes hold the mapped addresses: refused
             del s2
             dist.barrier()
         finally:

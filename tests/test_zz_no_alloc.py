@@ -8,6 +8,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import binding as ob
 from tests.util import pkg
 
 szlib, synth, moe = pkg.lib, pkg.synth, pkg.moe
@@ -48,3 +49,18 @@ def test_static_scratch_gives_the_same_bytes_twice_in_a_row(ety, H, FF):
         torch.cuda.synchronize()
         assert torch.equal(ridx, widx) and torch.equal(rw, ww)
         assert np.array_equal(y.cpu().numpy().view(np.uint32), want.cpu().numpy().view(np.uint32))
+        err = C.c_int(-1)
+        szlib.check(L.sz_moe_static_status(C.byref(err), st))
+        assert err.value == 0                      # no bounded wait ran out in the shared array's kernels
+    # and against the CPU oracle directly, not only against the sibling entry point
+    Ln = synth.to_numpy_layer(Ld)
+    for j in range(4):
+        ref, idx, _, _ = ob.moe(Ln, x[j].cpu().numpy(), threads=2)
+        assert np.array_equal(idx, ridx[j].cpu().numpy())
+        assert np.abs(y[j].cpu().numpy() - ref).max() / max(np.abs(ref).max(), 1e-9) < 2e-4
+    # the reset (after a failed call or a device reset) leaves the entry point usable with the same result
+    szlib.check(L.sz_moe_static_reset())
+    y2 = torch.full_like(x, float("nan"))
+    szlib.check(L.sz_moe_verify_static(C.byref(layer.c), x.data_ptr(), 4, y2.data_ptr(), 0, 0, st))
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y)
