@@ -2,7 +2,7 @@
 // Arithmetic follows Session::moe of the CPU reference (crates/shadowzero-model/src/forward.rs:1009-1034): router logits and
 // the softmax in f64, expert dot products accumulated in f32, the weighted sum over experts in f64 in rank order.
 #include "sz_moe.cuh"
-#include "sz_moe_exl3.cuh"
+#include "sz_moe_exl3w.cuh"
 #include "sz_moe_blk.cuh"
 
 #include <float.h>
@@ -759,9 +759,27 @@ static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const S
     if (!set) {
         SZ_CUDA(cudaFuncSetAttribute(sz_x3_gateup_kernel<K, NTC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzX3<K, NTC>::SMEM_BYTES));
         SZ_CUDA(cudaFuncSetAttribute(sz_x3_down_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzX3<K, 4>::SMEM_BYTES));
+        SZ_CUDA(cudaFuncSetAttribute(sz_xw_gateup_kernel<K, NTC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzXW<K, NTC>::SMEM_BYTES));
+        SZ_CUDA(cudaFuncSetAttribute(sz_xw_down_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzXW<K, 4>::SMEM_BYTES));
         set = true;
     }
-    const dim3 grid(2 * sz_sm_count()), block(SZ_X3_THREADS);
+    // SZ_X3_CLASSIC=1: the block-synchronous kernels of sz_moe_exl3.cuh (the second implementation; same bits) instead of the
+    // warp-specialised ones
+    const char* cl = getenv("SZ_X3_CLASSIC");   // (read at every call: a test switches it inside one process)
+    const bool classic = cl && atoi(cl) != 0;
+    const dim3 grid(2 * sz_sm_count());
+    if (!classic) {
+        const dim3 block(SZ_XW_THREADS);
+        SZ_CUDA(sz_launch("gateup_exl3s", sz_xw_gateup_kernel<K, NTC>, grid, block, SzXW<K, NTC>::SMEM_BYTES, st, true, plan, (const u8*)L->gate,
+                          (u64)L->gate_stride, (const u8*)L->up, (u64)L->up_stride, (const u8*)(sh ? L->sh_gate : 0), (const u8*)(sh ? L->sh_up : 0), x, m,
+                          (int)L->hidden, (int)L->top_k, acc_gu, ctrl));
+        SZ_CUDA(sz_launch("down_exl3s", sz_xw_down_kernel<K>, grid, block, SzXW<K, 4>::SMEM_BYTES, st, true, plan, (const u8*)L->gate, (u64)L->gate_stride,
+                          (const u8*)L->up, (u64)L->up_stride, (const u8*)L->down, (u64)L->down_stride, (const u8*)(sh ? L->sh_gate : 0),
+                          (const u8*)(sh ? L->sh_up : 0), (const u8*)(sh ? L->sh_down : 0), m, (int)L->hidden, (int)L->expert_ff, (int)L->top_k,
+                          (const long long*)acc_gu, acc_d, ctrl));
+        return SZ_OK;
+    }
+    const dim3 block(SZ_X3_THREADS);
     SZ_CUDA(sz_launch("gateup_exl3s", sz_x3_gateup_kernel<K, NTC>, grid, block, SzX3<K, NTC>::SMEM_BYTES, st, true, plan, (const u8*)L->gate,
                       (u64)L->gate_stride, (const u8*)L->up, (u64)L->up_stride, (const u8*)(sh ? L->sh_gate : 0), (const u8*)(sh ? L->sh_up : 0), x, m,
                       (int)L->hidden, (int)L->top_k, acc_gu, ctrl));

@@ -289,6 +289,15 @@ extern "C" int sz_session_reset(sz_session* s, uint64_t stream) {
 
 static bool sz_hc_fits(const sz_model_config& c, const sz_hc& hc, bool inject);
 
+static int sz_sm_count_session() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+    }
+    return n;
+}
+
 extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t mem, int64_t bytes, uint64_t stream, sz_session** out) {
     int rc = sz_model_check(m);
     if (rc) return rc;
@@ -419,9 +428,23 @@ int sz_dense_launch(SzDenseArgs& a, cudaStream_t st, const char* name) {
         while (((xsp / 2) % 32) != 16) xsp += 8;
         q.rbp = rbp; q.xsp = xsp;
         q.unit_bytes = 16 * rbp;
-        const size_t fixed = 64 + 4096 + (size_t)a.m * xsp * 4;
+        size_t fixed = 64 + 4096 + (size_t)a.m * xsp * 4;
         size_t budget = 110 * 1024;                        // two blocks a multiprocessor when that leaves at least two stages
         if (fixed + 2 * (size_t)q.unit_bytes > budget) budget = 216 * 1024;
+        if (fixed + 2 * (size_t)q.unit_bytes > budget && a.m > 1 && 64 + 4096 + (size_t)((a.m + 1) / 2) * xsp * 4 + 2 * (size_t)q.unit_bytes <= budget) {
+            // wide inputs with many rows do not fit next to two stages: two launches over half the rows each (the matrix is read
+            // twice, from L2 the second time where it fits).  A row's result must not depend on how many rows share its pass
+            // (batched == one at a time, bit for bit: crates/shadowzero/tests/reference.rs:226-255), so every row count has to
+            // go through this one kernel's arithmetic rather than fall through to the f32 kernel below.
+            const int m0 = (a.m + 1) / 2;
+            SzDenseArgs lo = a, hi = a;
+            lo.m = m0;
+            hi.m = a.m - m0;
+            hi.x = a.x + (size_t)m0 * a.xstride;
+            for (int i = 0; i < a.n_jobs; i++) hi.job[i].out = a.job[i].out + (size_t)m0 * a.job[i].ostride;
+            const int rc = sz_dense_launch(lo, st, name);
+            return rc ? rc : sz_dense_launch(hi, st, name);
+        }
         if (fixed + 2 * (size_t)q.unit_bytes <= budget) {
             int NS = (int)((budget - fixed) / q.unit_bytes);
             q.NS = NS > 4 ? 4 : NS;
@@ -500,7 +523,27 @@ static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bo
         long long* acc_next = s->hc_acc + ((n + 1) % 3) * as;
         int nt = ((int)c.hc_rank + C + 31) / 32 * 32;
         if (nt < 256) nt = 256;
-        cudaError_t e1 = cudaErrorInvalidValue, e2 = cudaErrorInvalidValue;
+        cudaError_t e1 = cudaErrorInvalidValue, e2 = cudaSuccess;
+        // one launch (down half, grid-wide barrier, up half) when all its blocks fit the GPU at once - the barrier needs every block
+        // resident; SZ_HC_SPLIT=1 keeps the two halves as launches of their own (the second implementation of the same arithmetic)
+        static const bool split = getenv("SZ_HC_SPLIT") && atoi(getenv("SZ_HC_SPLIT")) != 0;
+        const int blocks = CH / 64 > H / 16 ? CH / 64 : H / 16;
+        if (!split && blocks <= sz_sm_count_session()) {
+#define SZ_HC_CASE(MM)                                                                                                                   \
+    case MM:                                                                                                                             \
+        e1 = sz_launch("hc_read", sz_hc_read_kernel<MM>, dim3(blocks), dim3(nt), 0, st, true, (const float*)rin, rout,                   \
+                       (const long long*)(pending ? acc_prev : nullptr), (const float*)s->y, (const float*)hc.norm.data,                 \
+                       (const u8*)hc.down.data, (const u8*)(inject ? hc.inject.data : 0), (const u8*)hc.up.data, H, C, (int)c.hc_rank,   \
+                       c.eps, s->rn, acc, acc_next, s->u, (u32*)(s->state + 4), (u32*)(s->state + 2));                                   \
+        break;
+            switch (m) {
+                SZ_HC_CASE(1) SZ_HC_CASE(2) SZ_HC_CASE(3) SZ_HC_CASE(4) SZ_HC_CASE(5) SZ_HC_CASE(6) SZ_HC_CASE(7) SZ_HC_CASE(8)
+            }
+#undef SZ_HC_CASE
+            SZ_CUDA(e1);
+            return SZ_OK;
+        }
+        e2 = cudaErrorInvalidValue;
 #define SZ_HC_CASE(MM)                                                                                                                   \
     case MM:                                                                                                                             \
         e1 = sz_launch("hc_down", sz_hc_down_kernel<MM>, dim3(CH / 64), dim3(nt), 0, st, true, (const float*)rin, rout,                  \

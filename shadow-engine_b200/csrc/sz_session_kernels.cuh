@@ -93,11 +93,25 @@ sz_hc_mix_kernel(const float* __restrict__ mix, const float* __restrict__ rn, in
 #define SZ_HC_FIX_INV (1.0 / 1099511627776.0)
 
 // grid C*H / 64; block: a multiple of 32 threads, at least rank + C (one thread a matrix row) and at most 320
+// this thread's 64 weights of the down (or inject) matrix: constant data, requested before the dependency wait
+__device__ __forceinline__ const u8* sz_hc_down_fetch(const u8* __restrict__ down, const u8* __restrict__ inject, int H, int C, int rank, uint4* w) {
+    const int t = threadIdx.x, CH = C * H, c0 = blockIdx.x * 64;
+    const u8* wrow = nullptr;
+    if (c0 < CH) {
+        if (t < rank) wrow = down + ((size_t)t * CH + c0) * 2;
+        else if (inject != nullptr && t < rank + C) wrow = inject + ((size_t)(t - rank) * CH + c0) * 2;
+    }
+#pragma unroll
+    for (int i = 0; i < 8; i++) w[i] = wrow ? sz_ldg16_here((const uint4*)wrow + i) : make_uint4(0, 0, 0, 0);
+    return wrow;
+}
+
+// everything after the wait; every thread of the block returns from it together (no early exits: a grid-wide barrier may follow)
 template <int M>  // rows of the pass: a compile-time count keeps every per-row loop free of branches
-__global__ void __launch_bounds__(320)
-sz_hc_down_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, const long long* __restrict__ g_acc, const float* __restrict__ y,
-                  const float* __restrict__ normw, const u8* __restrict__ down, const u8* __restrict__ inject, int H, int C, int rank,
-                  float eps, float* __restrict__ rn, long long* __restrict__ acc, long long* __restrict__ acc_next) {
+__device__ __forceinline__ void
+sz_hc_down_body(const float* __restrict__ r_in, float* __restrict__ r_out, const long long* __restrict__ g_acc, const float* __restrict__ y,
+                const float* __restrict__ normw, int H, int C, int rank, float eps, float* __restrict__ rn, long long* __restrict__ acc,
+                long long* __restrict__ acc_next, const u8* wrow, const uint4* w) {
     __shared__ double red[10][SZ_MAX_VERIFY];
     __shared__ float rinv[SZ_MAX_VERIFY];
     __shared__ float gs[SZ_MAX_VERIFY];
@@ -107,17 +121,7 @@ sz_hc_down_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, con
     const int CH = C * H;
     const int c0 = blockIdx.x * 64;
     SZ_PH_DECL;
-    SZ_PH();  // 0
     const int s = c0 / H;
-    // this thread's 64 weights: constant data, requested before the wait
-    const u8* wrow = nullptr;
-    if (t < rank) wrow = down + ((size_t)t * CH + c0) * 2;
-    else if (inject != nullptr && t < rank + C) wrow = inject + ((size_t)(t - rank) * CH + c0) * 2;
-    uint4 w[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) w[i] = wrow ? sz_ldg16_here((const uint4*)wrow + i) : make_uint4(0, 0, 0, 0);
-    sz_pdl_wait();
-    sz_pdl_trigger();
     SZ_PH();  // 1 after wait
     // every load of the prologue is issued before anything waits on one: the gates, the stream's rows, the mixer output
     if (t < 64) nws[t] = __ldg(normw + c0 + t);
@@ -184,38 +188,67 @@ sz_hc_down_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, con
     }
     __syncthreads();
     SZ_PH();  // 5 columns
-    if (wrow == nullptr) return;
-    float a[M];
+    if (wrow != nullptr) {
+        float a[M];
 #pragma unroll
-    for (int j = 0; j < M; j++) a[j] = 0.f;
+        for (int j = 0; j < M; j++) a[j] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const u32 ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+        for (int i = 0; i < 8; i++) {
+            const u32 ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const float w0 = __uint_as_float(ww[q] << 16), w1 = __uint_as_float(ww[q] & 0xffff0000u);
+            for (int q = 0; q < 4; q++) {
+                const float w0 = __uint_as_float(ww[q] << 16), w1 = __uint_as_float(ww[q] & 0xffff0000u);
 #pragma unroll
-            for (int j = 0; j < M; j++) {
-                if (j < M) {
-                    const float2 xv = *(const float2*)&xs[j][8 * i + 2 * q];
-                    a[j] = fmaf(w0, xv.x, a[j]);
-                    a[j] = fmaf(w1, xv.y, a[j]);
+                for (int j = 0; j < M; j++) {
+                    if (j < M) {
+                        const float2 xv = *(const float2*)&xs[j][8 * i + 2 * q];
+                        a[j] = fmaf(w0, xv.x, a[j]);
+                        a[j] = fmaf(w1, xv.y, a[j]);
+                    }
                 }
             }
         }
-    }
 #pragma unroll
-    for (int j = 0; j < M; j++)
-        if (j < M) atomicAdd((unsigned long long*)(acc + j * SZ_HC_ACC_ROWS + t), (unsigned long long)__double2ll_rn((double)a[j] * SZ_HC_FIX));
+        for (int j = 0; j < M; j++)
+            if (j < M) atomicAdd((unsigned long long*)(acc + j * SZ_HC_ACC_ROWS + t), (unsigned long long)__double2ll_rn((double)a[j] * SZ_HC_FIX));
+    }
     SZ_PH();  // 6 dots + atomics issued
     SZ_PH_FLUSH(1, blockIdx.x == 5);
 }
 
-// grid H / 16, block 256.  CPR = rank / 8: 16-byte pieces a row of the up matrix.
 template <int M>
-__global__ void __launch_bounds__(256)
-sz_hc_up_kernel(const long long* __restrict__ acc, const u8* __restrict__ up, const float* __restrict__ rn, int H, int C, int rank,
-                float* __restrict__ u) {
+__global__ void __launch_bounds__(320)
+sz_hc_down_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, const long long* __restrict__ g_acc, const float* __restrict__ y,
+                  const float* __restrict__ normw, const u8* __restrict__ down, const u8* __restrict__ inject, int H, int C, int rank,
+                  float eps, float* __restrict__ rn, long long* __restrict__ acc, long long* __restrict__ acc_next) {
+    uint4 w[8];
+    const u8* wrow = sz_hc_down_fetch(down, inject, H, C, rank, w);
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    sz_hc_down_body<M>(r_in, r_out, g_acc, y, normw, H, C, rank, eps, rn, acc, acc_next, wrow, w);
+}
+
+// grid H / 16, block 256.  CPR = rank / 8: 16-byte pieces a row of the up matrix.
+// the block's rows of the up matrix, one 16-byte piece a thread and slot: constant data, requested before the dependency wait
+// (threads 256 and up of a wider block hold none)
+__device__ __forceinline__ void sz_hc_up_fetch(const u8* __restrict__ up, int H, int C, int rank, uint4* w) {
+    const int t = threadIdx.x, cpr = rank >> 3, h0 = blockIdx.x * 16, chunks = 16 * C * cpr;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int ch = t + 256 * i;
+        w[i] = make_uint4(0, 0, 0, 0);
+        if (t < 256 && ch < chunks && h0 < H) {
+            const int lr = ch / cpr, c = ch - lr * cpr;       // local row s * 16 + hl
+            const int row = (lr >> 4) * H + h0 + (lr & 15);
+            w[i] = sz_ldg16_here((const uint4*)(up + (size_t)row * rank * 2) + c);
+        }
+    }
+}
+
+// everything after the wait, for the first 256 threads of the block (all of them reach every barrier inside)
+template <int M>
+__device__ __forceinline__ void
+sz_hc_up_body(const long long* __restrict__ acc, const float* __restrict__ rn, int H, int C, int rank, float* __restrict__ u, const uint4* w) {
     __shared__ __align__(16) float hd[SZ_MAX_VERIFY][256];
     __shared__ float mixs[64][SZ_MAX_VERIFY];
     const int t = threadIdx.x;
@@ -223,90 +256,136 @@ sz_hc_up_kernel(const long long* __restrict__ acc, const u8* __restrict__ up, co
     const int h0 = blockIdx.x * 16;
     const int chunks = 16 * C * cpr;  // <= 2048
     SZ_PH_DECL;
-    SZ_PH();  // 0
-    uint4 w[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int ch = t + 256 * i;
-        w[i] = make_uint4(0, 0, 0, 0);
-        if (ch < chunks) {
-            const int lr = ch / cpr, c = ch - lr * cpr;       // local row s * 16 + hl
-            const int row = (lr >> 4) * H + h0 + (lr & 15);
-            w[i] = sz_ldg16_here((const uint4*)(up + (size_t)row * rank * 2) + c);
-        }
-    }
-    sz_pdl_wait();
-    sz_pdl_trigger();
     SZ_PH();  // 1
-#ifdef SZ_PHASES
-    { u32 touch = 0;
-      for (int i = 0; i < 8; i++) touch ^= w[i].x ^ w[i].w;
-      if (touch == 0x12345679u) mixs[0][0] = 1.f;
-      SZ_PH(); }  // 1b weights arrived
-#endif
-    for (int idx = t; idx < M * rank; idx += 256) {
-        const int j = idx / rank, q = idx - j * rank;
-        const float v = (float)((double)__ldcg(acc + j * SZ_HC_ACC_ROWS + q) * SZ_HC_FIX_INV);
-        hd[j][q] = sz_silu(v / (float)C);
-    }
+    const bool on = t < 256;   // a wider block's extra warps only keep the barriers company
+    if (on)
+        for (int idx = t; idx < M * rank; idx += 256) {
+            const int j = idx / rank, q = idx - j * rank;
+            const float v = (float)((double)__ldcg(acc + j * SZ_HC_ACC_ROWS + q) * SZ_HC_FIX_INV);
+            hd[j][q] = sz_silu(v / (float)C);
+        }
     __syncthreads();
     SZ_PH();  // 2 hd
     // all partial dot products first, then the butterflies over the cpr lanes of a row interleaved (independent chains).  A thread's
     // pieces all sit at the same place c of their rows (256 is a multiple of cpr), so its 8 inputs per row are read once.
-    float p[8][M];
-    {
-        const int c = t % cpr;
-        float4 x0[M], x1[M];
+    if (on) {
+        float p[8][M];
+        {
+            const int c = t % cpr;
+            float4 x0[M], x1[M];
 #pragma unroll
-        for (int j = 0; j < M; j++) { x0[j] = *(const float4*)&hd[j][8 * c]; x1[j] = *(const float4*)&hd[j][8 * c + 4]; }
+            for (int j = 0; j < M; j++) { x0[j] = *(const float4*)&hd[j][8 * c]; x1[j] = *(const float4*)&hd[j][8 * c + 4]; }
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const u32 ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
-            float wf[8];
+            for (int i = 0; i < 8; i++) {
+                const u32 ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+                float wf[8];
 #pragma unroll
-            for (int q = 0; q < 4; q++) { wf[2 * q] = __uint_as_float(ww[q] << 16); wf[2 * q + 1] = __uint_as_float(ww[q] & 0xffff0000u); }
+                for (int q = 0; q < 4; q++) { wf[2 * q] = __uint_as_float(ww[q] << 16); wf[2 * q + 1] = __uint_as_float(ww[q] & 0xffff0000u); }
 #pragma unroll
-            for (int j = 0; j < M; j++) {
-                float v = wf[0] * x0[j].x;
-                v = fmaf(wf[1], x0[j].y, v); v = fmaf(wf[2], x0[j].z, v); v = fmaf(wf[3], x0[j].w, v);
-                v = fmaf(wf[4], x1[j].x, v); v = fmaf(wf[5], x1[j].y, v); v = fmaf(wf[6], x1[j].z, v); v = fmaf(wf[7], x1[j].w, v);
-                p[i][j] = v;
+                for (int j = 0; j < M; j++) {
+                    float v = wf[0] * x0[j].x;
+                    v = fmaf(wf[1], x0[j].y, v); v = fmaf(wf[2], x0[j].z, v); v = fmaf(wf[3], x0[j].w, v);
+                    v = fmaf(wf[4], x1[j].x, v); v = fmaf(wf[5], x1[j].y, v); v = fmaf(wf[6], x1[j].z, v); v = fmaf(wf[7], x1[j].w, v);
+                    p[i][j] = v;
+                }
             }
         }
-    }
-    for (int o = cpr >> 1; o > 0; o >>= 1) {
+        for (int o = cpr >> 1; o > 0; o >>= 1) {
 #pragma unroll
-        for (int i = 0; i < 8; i++)
+            for (int i = 0; i < 8; i++)
 #pragma unroll
-            for (int j = 0; j < M; j++)
-                if (j < M) p[i][j] += __shfl_xor_sync(0xffffffffu, p[i][j], o);
-    }
+                for (int j = 0; j < M; j++)
+                    if (j < M) p[i][j] += __shfl_xor_sync(0xffffffffu, p[i][j], o);
+        }
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        const int ch = t + 256 * i;
-        if (ch < chunks && ch % cpr == 0) {
-            const int lr = ch / cpr;
+        for (int i = 0; i < 8; i++) {
+            const int ch = t + 256 * i;
+            if (ch < chunks && ch % cpr == 0) {
+                const int lr = ch / cpr;
 #pragma unroll
-            for (int j = 0; j < M; j++)
-                if (j < M) mixs[lr][j] = p[i][j];
+                for (int j = 0; j < M; j++)
+                    if (j < M) mixs[lr][j] = p[i][j];
+            }
         }
     }
     __syncthreads();
     SZ_PH();  // 3 dots
     // mix * rn for each (stream, position, row), one a thread; then the mean over the streams
-    for (int idx = t; idx < 16 * C * M; idx += 256) {
-        const int lr = idx / M, j = idx - lr * M;
-        mixs[lr][j] = sz_sigmoid(mixs[lr][j]) * __ldcg(rn + ((size_t)j * C + (lr >> 4)) * H + h0 + (lr & 15));
-    }
+    if (on)
+        for (int idx = t; idx < 16 * C * M; idx += 256) {
+            const int lr = idx / M, j = idx - lr * M;
+            mixs[lr][j] = sz_sigmoid(mixs[lr][j]) * __ldcg(rn + ((size_t)j * C + (lr >> 4)) * H + h0 + (lr & 15));
+        }
     __syncthreads();
-    for (int idx = t; idx < M * 16; idx += 256) {
-        const int j = idx >> 4, hl = idx & 15;
-        float a = 0.f;
-        for (int s = 0; s < C; s++) a += mixs[s * 16 + hl][j];
-        u[(size_t)j * H + h0 + hl] = a / (float)C;
-    }
+    if (on)
+        for (int idx = t; idx < M * 16; idx += 256) {
+            const int j = idx >> 4, hl = idx & 15;
+            float a = 0.f;
+            for (int s = 0; s < C; s++) a += mixs[s * 16 + hl][j];
+            u[(size_t)j * H + h0 + hl] = a / (float)C;
+        }
     SZ_PH();  // 4 u
     SZ_PH_FLUSH(2, blockIdx.x == 5);
+}
+
+template <int M>
+__global__ void __launch_bounds__(256)
+sz_hc_up_kernel(const long long* __restrict__ acc, const u8* __restrict__ up, const float* __restrict__ rn, int H, int C, int rank,
+                float* __restrict__ u) {
+    uint4 w[8];
+    sz_hc_up_fetch(up, H, C, rank, w);
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    sz_hc_up_body<M>(acc, rn, H, C, rank, u, w);
+}
+
+// A barrier over all blocks of a grid whose blocks are all resident (no more blocks than the GPU holds at once: the caller sizes
+// the grid so).  sync[0] counts arrivals, sync[1] is the generation: the last block to arrive clears the count and bumps the
+// generation, the others poll it - a bounded number of times, after which the block raises *err and goes on (its results are then
+// wrong and flagged; nothing ever spins for good).  Writes before the barrier are visible to every block after it.
+__device__ __forceinline__ void sz_grid_barrier(u32* sync, u32 blocks, u32* err) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        u32 gen;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(gen) : "l"(sync + 1));
+        __threadfence();
+        const u32 arrived = atomicAdd(sync, 1u);
+        if (arrived == blocks - 1) {
+            atomicExch(sync, 0u);
+            __threadfence();
+            asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(sync + 1), "r"(gen + 1) : "memory");
+        } else {
+            u32 now = gen;
+            int polls = 0;
+            while (now == gen && polls < 2000000) {
+                asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(now) : "l"(sync + 1));
+                polls++;
+                if (polls > 64) __nanosleep(40);
+            }
+            if (now == gen && err) atomicExch(err, 1u);
+        }
+        __threadfence();
+    }
+    __syncthreads();
+}
+
+// The whole read in one launch: the down half, a grid-wide barrier, the up half.  grid = max(C H / 64, H / 16) blocks (one a
+// multiprocessor at most: the barrier needs them all resident), block = the down half's.  Both halves' weights are requested ahead
+// of the dependency wait, so the up matrix arrives while the down half runs.
+template <int M>
+__global__ void __launch_bounds__(320)
+sz_hc_read_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, const long long* __restrict__ g_acc, const float* __restrict__ y,
+                  const float* __restrict__ normw, const u8* __restrict__ down, const u8* __restrict__ inject, const u8* __restrict__ up, int H,
+                  int C, int rank, float eps, float* __restrict__ rn, long long* __restrict__ acc, long long* __restrict__ acc_next,
+                  float* __restrict__ u, u32* __restrict__ sync, u32* __restrict__ err) {
+    uint4 wd[8], wu[8];
+    const u8* wrow = sz_hc_down_fetch(down, inject, H, C, rank, wd);
+    sz_hc_up_fetch(up, H, C, rank, wu);
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    if ((int)blockIdx.x * 64 < C * H) sz_hc_down_body<M>(r_in, r_out, g_acc, y, normw, H, C, rank, eps, rn, acc, acc_next, wrow, wd);
+    sz_grid_barrier(sync, gridDim.x, err);
+    if ((int)blockIdx.x * 16 < H) sz_hc_up_body<M>(acc, rn, H, C, rank, u, wu);
 }
 
 // ---- DeltaNet front end (forward.rs:829-861): causal conv (k taps) + SiLU over the rows of the pass, L2 norm of q and k heads,

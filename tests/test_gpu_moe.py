@@ -142,3 +142,30 @@ def test_microbench_shapes_iq3_s_and_exl3():
     # CPU oracle finishes in seconds: the router only sees the first 64 experts' rows.
     for ety in (szlib.TYPE_IQ3_S, szlib.TYPE_EXL3(3)):
         run_case(2048, 64, 10, 512, 512, ety, ety, 4, seed=12)
+
+
+@pytest.mark.parametrize("bits,H,ne,k,FF,SF,m", [(3, 2048, 64, 10, 512, 512, 4), (3, 512, 32, 6, 256, 256, 8), (2, 1024, 32, 4, 128, 128, 1),
+                                                  (4, 512, 16, 4, 512, 512, 3), (3, 1024, 64, 8, 256, 0, 5)])
+def test_warp_specialised_exl3_kernels_give_the_bits_of_the_block_synchronous_ones(bits, H, ne, k, FF, SF, m):
+    # two implementations of the streaming EXL3 expert kernels (SZ_X3_CLASSIC=1 selects the block-synchronous one): the same units,
+    # the same decode, partial sums added as integers - the outputs must agree bit for bit, run after run
+    import os
+    ety = szlib.TYPE_EXL3(bits)
+    L = synth.make_moe_layer(H, ne, k, FF, SF, ety, ety, seed=21)
+    layer = moe.MoeLayer(L, "cuda:0")
+    x = torch.randn(m, H, generator=torch.Generator().manual_seed(4)).cuda()
+    outs = {}
+    for classic in ("1", "0", "0"):
+        os.environ["SZ_X3_CLASSIC"] = classic
+        try:
+            y = layer.moe_batch(x)
+            torch.cuda.synchronize()
+        finally:
+            del os.environ["SZ_X3_CLASSIC"]
+        outs.setdefault(classic, []).append(y.cpu().numpy().copy())
+    assert np.array_equal(outs["1"][0].view(np.uint32), outs["0"][0].view(np.uint32))
+    assert np.array_equal(outs["0"][0].view(np.uint32), outs["0"][1].view(np.uint32))
+    Ln = synth.to_numpy_layer(L)
+    for j in range(m):
+        want = ob.moe(Ln, x[j].cpu().numpy(), threads=4)[0]
+        assert np.abs(outs["0"][0][j] - want).max() / max(np.abs(want).max(), 1e-9) < REL_TOL
