@@ -162,6 +162,33 @@ typedef struct sz_model {
     const sz_layer* layers;     /* host array of n_layer entries */
 } sz_model;
 
+/* ---- model files ------------------------------------------------------------------------------------------------------------------
+ * A GGUF file into struct sz_model.  Replaces Gguf::open (crates/shadowzero-model/src/gguf.rs:468; header, key-values and tensor table
+ * :330-420, type table :99-150 with the EXL3 blob types 1021..1028 sized by the span to the next tensor), Config::from_gguf
+ * (crates/shadowzero-model/src/forward.rs:72-142: the `<architecture>.<key>` values behind every field of sz_model_config; vocab from
+ * output.weight, :106) and the tensor lookup by name (names and ggml dimension order as crates/shadowzero-model/src/exl3_model.rs:223-243
+ * lists them; expert e of a three-dimensional expert tensor at byte e * bytes / n_expert, forward.rs:477-485).
+ * placement SZ_PLACE_HOST: the file stays mapped and tensor addresses point into the mapping (for a CPU consumer of the struct).
+ * SZ_PLACE_DEVICE: one device allocation made here (loading is not a hot call), every tensor copied to an aligned place of its own -
+ * EXL3 blobs so that their trellis starts on a 16-byte boundary, EXL3 expert slices re-strided to a multiple of 16 bytes.
+ * The per-layer-embedding branch and the sparse indexer are not part of this build: a file that switches one on (a layer below
+ * block_count in ple.layers, a non-zero entry of attention.compress_ratios) is refused with SZ_E_TYPE; their tensors are ignored.
+ * sz_weights_model: the description, valid until sz_weights_free.  sz_weights_tensor_info: type, dimensions (ggml order, padded with
+ * 1) and byte size of a tensor by name (Gguf::tensor, gguf.rs:512).
+ * sz_gguf_open reads the header alone (any GGUF, not only a model of this architecture): the tensor table through
+ * sz_weights_tensor_info, integer key-values (an array gives its length) through sz_weights_key_u64; sz_weights_model is null then. */
+#define SZ_PLACE_HOST 0
+#define SZ_PLACE_DEVICE 1
+typedef struct sz_weights sz_weights;
+int sz_model_load_gguf(const char* path, int placement, uint64_t stream, sz_weights** out);
+int sz_gguf_open(const char* path, sz_weights** out);
+int sz_weights_key_u64(const sz_weights* w, const char* key, uint64_t* out);
+const sz_model* sz_weights_model(const sz_weights* w);
+int64_t sz_weights_bytes(const sz_weights* w);
+int sz_weights_tensor_count(const sz_weights* w);
+int sz_weights_tensor_info(const sz_weights* w, const char* name, int32_t* type, int64_t dims[4], int64_t* bytes);
+void sz_weights_free(sz_weights* w);
+
 /* ---- the session: the verify surface ------------------------------------------------------------------------------------
  * Replaces the verify subset of GpuSession (crates/shadowzero-cuda/src/session.rs): step_batch_verify_top (6061-6072), rollback
  * (6217-6276), note_verify, capacity, tokens, and prefill by passes.  One engine thread owns a session (engine.rs:340-420).
@@ -221,6 +248,27 @@ int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, uint64_t st
 int sz_session_export(sz_session* s, int what, int layer, void* dst, int64_t bytes, uint64_t stream);
 int sz_session_trace_routes(sz_session* s, int on);
 int sz_session_routes(sz_session* s, int32_t* idx, double* w, uint64_t stream);
+
+/* ---- launching a kernel by name -------------------------------------------------------------------------------------------------------
+ * The lowest seam of the reference: Program::launch(name, grid, block, shared, stream, args) (crates/shadowzero-cuda/src/kernels.rs:
+ * 546-572) over a static registry that spells out every entry point's parameter types (:9-57, 163-477).  Arguments are typed
+ * (pointer, const pointer, u32, i32, u64, f32) and travel in 8-byte slots; a device pointer satisfies both pointer kinds, scalars must
+ * match exactly; a launch whose count or types do not fit the registry is refused with SZ_E_ARG before anything reaches the driver
+ * ("takes 4 arguments", "does not fit": crates/shadowzero-cuda/tests/gpu.rs).  What remains the caller's promise is that every
+ * pointer is large enough for what the kernel reads and writes at that grid.  The registry holds the session's kernels with plain
+ * parameters; sz_kernel_count / sz_kernel_name / sz_kernel_params enumerate it (the drift test compares it with the sources). */
+#define SZ_P_PTR 0
+#define SZ_P_CONST_PTR 1
+#define SZ_P_U32 2
+#define SZ_P_I32 3
+#define SZ_P_U64 4
+#define SZ_P_F32 5
+typedef struct sz_karg { int32_t type; int32_t reserved; uint64_t bits; } sz_karg;   /* bits: the value, zero-extended (f32: its bit pattern) */
+int sz_kernel_count(void);
+const char* sz_kernel_name(int i);
+int sz_kernel_params(const char* name, int32_t* types, int cap);   /* the number of parameters (-1: unknown name); types[0 .. min(n, cap)) */
+int sz_kernel_launch(const char* name, const uint32_t grid[3], const uint32_t block[3], uint32_t shared, uint64_t stream, const sz_karg* args,
+                     int nargs);
 
 /* ---- the host side of speculation: drafting, the draft policy, sampling, the loop ------------------------------------------------
  * Pure host code (no CUDA): C++ where the reference is Rust.  Token ids are uint32_t, as there. */

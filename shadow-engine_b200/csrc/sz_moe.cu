@@ -2,6 +2,9 @@
 // Arithmetic follows Session::moe of the CPU reference (crates/shadowzero-model/src/forward.rs:1009-1034): router logits and
 // the softmax in f64, expert dot products accumulated in f32, the weighted sum over experts in f64 in rank order.
 #include "sz_moe.cuh"
+#define SZ_XW_DEFAULT_OCC 2
+#define SZ_XW_DEFAULT_TW 4
+#define SZ_XW_DEFAULT_TWD 4
 #include "sz_moe_exl3w.cuh"
 #include "sz_moe_blk.cuh"
 
@@ -759,26 +762,57 @@ static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const S
     if (!set) {
         SZ_CUDA(cudaFuncSetAttribute(sz_x3_gateup_kernel<K, NTC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzX3<K, NTC>::SMEM_BYTES));
         SZ_CUDA(cudaFuncSetAttribute(sz_x3_down_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzX3<K, 4>::SMEM_BYTES));
-        SZ_CUDA(cudaFuncSetAttribute(sz_xw_gateup_kernel<K, NTC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzXW<K, NTC>::SMEM_BYTES));
-        SZ_CUDA(cudaFuncSetAttribute(sz_xw_down_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzXW<K, 4>::SMEM_BYTES));
         set = true;
     }
     // SZ_X3_CLASSIC=1: the block-synchronous kernels of sz_moe_exl3.cuh (the second implementation; same bits) instead of the
     // warp-specialised ones
     const char* cl = getenv("SZ_X3_CLASSIC");   // (read at every call: a test switches it inside one process)
     const bool classic = cl && atoi(cl) != 0;
-    const dim3 grid(2 * sz_sm_count());
     if (!classic) {
+        // Shape of the launch: OCC blocks a multiprocessor (2 or 3), a unit 8 TW tile columns a consumer warp wide (TW = 4, 2 or 1: 24, 12
+        // or 6 KB of trellis at 3 bits).  Narrower units and a third block spread the units evenly: gate / up of 40 experts of the
+        // benchmark's shape are 1,280 units 4 wide - 4.3 a block at 296 blocks, so some take 5 - and the down matrices only 640.
+        // SZ_XW_OCC / SZ_XW_TW / SZ_XW_TWD override the choice (experiments).
         const dim3 block(SZ_XW_THREADS);
-        SZ_CUDA(sz_launch("gateup_exl3s", sz_xw_gateup_kernel<K, NTC>, grid, block, SzXW<K, NTC>::SMEM_BYTES, st, true, plan, (const u8*)L->gate,
-                          (u64)L->gate_stride, (const u8*)L->up, (u64)L->up_stride, (const u8*)(sh ? L->sh_gate : 0), (const u8*)(sh ? L->sh_up : 0), x, m,
-                          (int)L->hidden, (int)L->top_k, acc_gu, ctrl));
-        SZ_CUDA(sz_launch("down_exl3s", sz_xw_down_kernel<K>, grid, block, SzXW<K, 4>::SMEM_BYTES, st, true, plan, (const u8*)L->gate, (u64)L->gate_stride,
-                          (const u8*)L->up, (u64)L->up_stride, (const u8*)L->down, (u64)L->down_stride, (const u8*)(sh ? L->sh_gate : 0),
-                          (const u8*)(sh ? L->sh_up : 0), (const u8*)(sh ? L->sh_down : 0), m, (int)L->hidden, (int)L->expert_ff, (int)L->top_k,
-                          (const long long*)acc_gu, acc_d, ctrl));
-        return SZ_OK;
+        const char *eo = getenv("SZ_XW_OCC"), *et = getenv("SZ_XW_TW"), *ed = getenv("SZ_XW_TWD");
+        const int occ = eo && atoi(eo) == 2 ? 2 : (eo && atoi(eo) == 3 ? 3 : SZ_XW_DEFAULT_OCC);
+        int tw = et ? atoi(et) : SZ_XW_DEFAULT_TW, twd = ed ? atoi(ed) : SZ_XW_DEFAULT_TWD;
+        if (!(tw == 1 || tw == 2 || tw == 4) || tw > NTC || NTC % tw) tw = NTC < 4 ? NTC : 4;
+        if (tw == 3) tw = 1;
+        if (!(twd == 1 || twd == 2 || twd == 4)) twd = 4;
+        const dim3 grid(occ * sz_sm_count());
+        int rc = SZ_E_TYPE;
+#define SZ_XW_GU(TT, OO)                                                                                                                    \
+    if (tw == TT && occ == OO) {                                                                                                            \
+        static bool setv = false;                                                                                                           \
+        if (!setv) { SZ_CUDA(cudaFuncSetAttribute(sz_xw_gateup_kernel<K, NTC, TT, OO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzXW<K, TT, OO>::SMEM_BYTES)); setv = true; } \
+        SZ_CUDA(sz_launch("gateup_exl3s", sz_xw_gateup_kernel<K, NTC, TT, OO>, grid, block, SzXW<K, TT, OO>::SMEM_BYTES, st, true, plan, (const u8*)L->gate, \
+                          (u64)L->gate_stride, (const u8*)L->up, (u64)L->up_stride, (const u8*)(sh ? L->sh_gate : 0), (const u8*)(sh ? L->sh_up : 0), x, m, \
+                          (int)L->hidden, (int)L->top_k, acc_gu, ctrl));                                                                    \
+        rc = SZ_OK;                                                                                                                         \
     }
+#define SZ_XW_DN(TT, OO)                                                                                                                    \
+    if (twd == TT && occ == OO) {                                                                                                           \
+        static bool setv = false;                                                                                                           \
+        if (!setv) { SZ_CUDA(cudaFuncSetAttribute(sz_xw_down_kernel<K, TT, OO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzXW<K, TT, OO>::SMEM_BYTES)); setv = true; } \
+        SZ_CUDA(sz_launch("down_exl3s", sz_xw_down_kernel<K, TT, OO>, grid, block, SzXW<K, TT, OO>::SMEM_BYTES, st, true, plan, (const u8*)L->gate, (u64)L->gate_stride, \
+                          (const u8*)L->up, (u64)L->up_stride, (const u8*)L->down, (u64)L->down_stride, (const u8*)(sh ? L->sh_gate : 0),   \
+                          (const u8*)(sh ? L->sh_up : 0), (const u8*)(sh ? L->sh_down : 0), m, (int)L->hidden, (int)L->expert_ff, (int)L->top_k, \
+                          (const long long*)acc_gu, acc_d, ctrl));                                                                          \
+        rc = SZ_OK;                                                                                                                         \
+    }
+        if constexpr (NTC % 4 == 0) { SZ_XW_GU(4, 2) SZ_XW_GU(4, 3) }
+        if constexpr (NTC % 2 == 0) { SZ_XW_GU(2, 2) SZ_XW_GU(2, 3) }
+        SZ_XW_GU(1, 2) SZ_XW_GU(1, 3)
+        if (rc) return sz_fail(SZ_E_TYPE, "no gate/up kernel for this unit shape");
+        rc = SZ_E_TYPE;
+        SZ_XW_DN(4, 2) SZ_XW_DN(4, 3) SZ_XW_DN(2, 2) SZ_XW_DN(2, 3) SZ_XW_DN(1, 2) SZ_XW_DN(1, 3)
+        if (rc) return sz_fail(SZ_E_TYPE, "no down kernel for this unit shape");
+        return SZ_OK;
+#undef SZ_XW_GU
+#undef SZ_XW_DN
+    }
+    const dim3 grid(2 * sz_sm_count());
     const dim3 block(SZ_X3_THREADS);
     SZ_CUDA(sz_launch("gateup_exl3s", sz_x3_gateup_kernel<K, NTC>, grid, block, SzX3<K, NTC>::SMEM_BYTES, st, true, plan, (const u8*)L->gate,
                       (u64)L->gate_stride, (const u8*)L->up, (u64)L->up_stride, (const u8*)(sh ? L->sh_gate : 0), (const u8*)(sh ? L->sh_up : 0), x, m,

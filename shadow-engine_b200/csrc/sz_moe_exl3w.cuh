@@ -14,15 +14,20 @@
 
 #define SZ_XW_CONSUMERS 8
 #define SZ_XW_THREADS (32 * (SZ_XW_CONSUMERS + 1))
-#define SZ_XW_STAGES 3
 
-template <int K, int NTC>
+// A unit: 8 tile rows (one 128-input block) x 8 TW tile columns (TW a consumer warp).  OCC: blocks a multiprocessor the kernel is
+// built for (2 or 3); the ring takes as many stages as fit that share of shared memory, at most 6.
+template <int K, int TW, int OCC>
 struct SzXW {
     static constexpr int TILE_BYTES = 32 * K;
-    static constexpr int ROW_BYTES = 8 * NTC * TILE_BYTES;   // one tile row of the unit
+    static constexpr int ROW_BYTES = 8 * TW * TILE_BYTES;    // one tile row of the unit
     static constexpr int STAGE_BYTES = 8 * ROW_BYTES;        // the unit's trellis bytes
     static constexpr int FRAG_BYTES = 8 * 32 * 16;           // the unit's activation fragments: [8 tile rows][32 lanes] uint4
-    static constexpr int SMEM_BYTES = SZ_XW_STAGES * (STAGE_BYTES + FRAG_BYTES) + 2 * SZ_XW_STAGES * 8 + 16;
+    static constexpr int BUDGET = (OCC == 3 ? 72 : 108) * 1024;
+    static constexpr int FIT = BUDGET / (STAGE_BYTES + FRAG_BYTES);
+    static constexpr int STAGES = FIT > 6 ? 6 : FIT;
+    static_assert(STAGES >= 2, "the ring needs two stages");
+    static constexpr int SMEM_BYTES = STAGES * (STAGE_BYTES + FRAG_BYTES) + 2 * STAGES * 8 + 16;
 };
 
 // Two-word form of SzExl3Tile<K>::states_pre: valid when the lane's span (16 + 7 K bits) starting at its bit offset inside the
@@ -108,18 +113,20 @@ __device__ __forceinline__ void sz_xw_afrag(const u32* tile, const SzXWLane<K>& 
 
 // Decodes and multiplies one staged unit (8 tile rows x 8 NTC tile columns): warp w takes tile columns w NTC .. w NTC + NTC - 1.
 // c[tc] = outputs (w NTC + tc) 16 + {g, g + 8} for rows 2 q, 2 q + 1.
-template <int K, int NTC>
+// The decode loop is fully unrolled: rolled over the tile rows it ran 6% slower, and moving the byte-sum packing or the
+// word-crossing windows from the ALU pipe to multiply-adds on the FMA pipe another 2 - 4% slower (measured on the benchmark's shape).
+template <int K, int TW>
 __device__ __forceinline__ void sz_xw_compute(const u8* stage, const uint4* frag, int warp, int lane, const SzXWLane<K>& S, float (*c)[4]) {
 #pragma unroll
-    for (int tc = 0; tc < NTC; tc++) { c[tc][0] = 0.f; c[tc][1] = 0.f; c[tc][2] = 0.f; c[tc][3] = 0.f; }
-    const u8* wbase = stage + (size_t)(warp * NTC) * (32 * K);
+    for (int tc = 0; tc < TW; tc++) { c[tc][0] = 0.f; c[tc][1] = 0.f; c[tc][2] = 0.f; c[tc][3] = 0.f; }
+    const u8* wbase = stage + (size_t)(warp * TW) * (32 * K);
     const uint4* fl = frag + lane;
 #pragma unroll
     for (int kr = 0; kr < 8; kr++) {
         const uint4 b = fl[kr * 32];
 #pragma unroll
-        for (int tc = 0; tc < NTC; tc++) {
-            const u32* tile = (const u32*)(wbase + (size_t)(kr * 8 * NTC + tc) * (32 * K));
+        for (int tc = 0; tc < TW; tc++) {
+            const u32* tile = (const u32*)(wbase + (size_t)(kr * 8 * TW + tc) * (32 * K));
             u32 a[4];
             sz_xw_afrag<K>(tile, S, a);
             sz_mma16816(c[tc], a, b.x, b.y);
@@ -152,28 +159,77 @@ __device__ __forceinline__ void sz_xw_zero_row(uint4* frag, int t, int lane) {
     frag[(lane >> 2) * 32 + 4 * t + (lane & 3)] = make_uint4(0, 0, 0, 0);
 }
 
+// What the producer and the consumers of both kernels share: the stage ring and its barriers.
+template <int K, int TW, int OCC>
+struct SzXWRing {
+    using X = SzXW<K, TW, OCC>;
+    u8* stages;
+    uint4* frags;
+    u64 *full, *empty;
+    __device__ __forceinline__ void init(u8* smem) {
+        stages = smem;
+        frags = (uint4*)(smem + X::STAGES * X::STAGE_BYTES);
+        full = (u64*)(smem + X::STAGES * (X::STAGE_BYTES + X::FRAG_BYTES));
+        empty = full + X::STAGES;
+        if (threadIdx.x == 0) {
+            for (int i = 0; i < X::STAGES; i++) { sz_mbar_init(&full[i], 2); sz_mbar_init(&empty[i], SZ_XW_CONSUMERS); }
+            sz_mbar_fence_init();
+        }
+    }
+    // lane 0 of the producer: the unit's 8 tile rows, `row_stride` bytes apart in the matrix, into stage st
+    __device__ __forceinline__ void issue(int st, const u8* src, u64 row_stride) {
+        u8* dst = stages + (size_t)st * X::STAGE_BYTES;
+        sz_mbar_expect_tx(&full[st], X::STAGE_BYTES);
+        if (row_stride == (u64)X::ROW_BYTES) {
+            sz_bulk_g2s(dst, src, X::STAGE_BYTES, &full[st]);
+        } else {
+#pragma unroll
+            for (int kr = 0; kr < 8; kr++) sz_bulk_g2s(dst + kr * X::ROW_BYTES, src + kr * row_stride, X::ROW_BYTES, &full[st]);
+        }
+    }
+};
+
+// The consumers' epilogue: the unit's partial sums into the fixed-point accumulators of the group's pairs.
+template <int TW>
+__device__ __forceinline__ void sz_xw_flush(const SzPlan* plan, int g, int D, int m, int top_k, long long* base, size_t pair_stride, int col0,
+                                            int lane, const float (*c)[4]) {
+    const int q = lane & 3, g8 = lane >> 2;
+    int n, pair0;
+    const u8* pairs;
+    if (g < D) { n = plan->count[g]; pairs = plan->pairs[g]; pair0 = 0; }
+    else { n = m; pairs = nullptr; pair0 = m * top_k; }
+#pragma unroll
+    for (int tt = 0; tt < 2; tt++) {
+        const int t = 2 * q + tt;
+        if (t < n) {
+            const int pair = pairs ? pairs[t] : pair0 + t;
+            long long* dst = base + (size_t)pair * pair_stride + col0 + g8;
+#pragma unroll
+            for (int tc = 0; tc < TW; tc++) {
+                sz_fix_add(dst + tc * 16, c[tc][tt]);
+                sz_fix_add(dst + tc * 16 + 8, c[tc][2 + tt]);
+            }
+        }
+    }
+}
+
 // ---- gate / up --------------------------------------------------------------------------------------------------------------------
-// Units: group x {gate, up} x input block; a unit is contiguous in memory (every tile column of 8 tile rows).  A block takes a
-// contiguous share of the units.  acc: i64 [pairs][2][FF], zero on entry.
-template <int K, int NTC>
-__global__ void __launch_bounds__(SZ_XW_THREADS, 2)
+// Units: group x {gate, up} x input block x column chunk (8 TW tile columns of the FF / 16), the chunk fastest: the chunks of one
+// input block share their activation fragments (made for the first, copied for the others).  A block takes a contiguous share of
+// the units.  acc: i64 [pairs][2][FF], zero on entry.
+template <int K, int NTC, int TW, int OCC>
+__global__ void __launch_bounds__(SZ_XW_THREADS, OCC)
 sz_xw_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, u64 gstride, const u8* __restrict__ up, u64 ustride,
                     const u8* __restrict__ sh_gate, const u8* __restrict__ sh_up, const float* __restrict__ x, int m, int H, int top_k,
                     long long* __restrict__ acc, u32* __restrict__ ctrl) {
-    using X = SzXW<K, NTC>;
-    constexpr int FF = 128 * NTC;
-    constexpr int S = SZ_XW_STAGES;
+    using X = SzXW<K, TW, OCC>;
+    constexpr int FF = 128 * NTC, S = X::STAGES, NCH = NTC / TW;
+    static_assert(NTC % TW == 0, "column chunks tile the matrix");
     extern __shared__ __align__(128) u8 smem[];
-    u8* stages = smem;
-    uint4* frags = (uint4*)(smem + S * X::STAGE_BYTES);
-    u64* full = (u64*)(smem + S * (X::STAGE_BYTES + X::FRAG_BYTES));
-    u64* empty = full + S;
+    SzXWRing<K, TW, OCC> R;
+    R.init(smem);
     __shared__ __align__(16) SzPlan splan;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < S; i++) { sz_mbar_init(&full[i], 2); sz_mbar_init(&empty[i], SZ_XW_CONSUMERS); }
-        sz_mbar_fence_init();
-    }
     sz_pdl_wait();
     sz_pdl_trigger();
     plan = sz_plan_stage(plan, &splan);
@@ -181,19 +237,21 @@ sz_xw_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     const int D = plan ? plan->n_groups : 0;
     const int NG = D + (sh_gate ? 1 : 0);
     const int NS = H / 128;
-    const long long U = (long long)NG * NS * 2;
+    const long long U = (long long)NG * 2 * NS * NCH;
     const int u0 = (int)(U * blockIdx.x / gridDim.x), u1 = (int)(U * (blockIdx.x + 1) / gridDim.x);
     const int count = u1 - u0;
     if (count <= 0) return;
     const size_t hdr = 2 * (size_t)H + 2 * (size_t)FF + 4;
-    // unit u = (group g, matrix mat, input block s), s fastest: consecutive units walk one matrix
+    const u64 mrow = (u64)(8 * NTC) * X::TILE_BYTES;    // bytes of one tile row of the matrix
     int failed = 0;
     if (warp == SZ_XW_CONSUMERS) {
         // ---- producer: copies and fragments of unit i into stage i % S
+        int prev_key = -1, prev_st = 0;
         for (int i = 0; i < count; i++) {
             const int u = u0 + i, st = i % S;
-            if (i >= S && !sz_mbar_wait(&empty[st], ((i / S) - 1) & 1)) { failed = 1; break; }
-            const int g = u / (2 * NS), rem = u - g * 2 * NS, mat = rem / NS, s = rem - mat * NS;
+            if (i >= S && !sz_mbar_wait(&R.empty[st], ((i / S) - 1) & 1)) { failed = 1; break; }
+            const int key = u / NCH, ch = u - key * NCH;          // key = (g, mat, s)
+            const int g = key / (2 * NS), rem = key - g * 2 * NS, mat = rem / NS, s = rem - mat * NS;
             const u8* blob;
             int n;
             const u8* rows;
@@ -205,103 +263,85 @@ sz_xw_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
                 blob = mat ? sh_up : sh_gate;
                 n = m; rows = nullptr;
             }
-            if (lane == 0) {
-                sz_mbar_expect_tx(&full[st], X::STAGE_BYTES);
-                sz_bulk_g2s(stages + (size_t)st * X::STAGE_BYTES, blob + hdr + (size_t)s * X::STAGE_BYTES, X::STAGE_BYTES, &full[st]);
-            }
-            uint4* frag = frags + st * 256;
-            const u16* suh = (const u16*)blob + s * 128;
-            float sc[4];
+            if (lane == 0) R.issue(st, blob + hdr + (size_t)s * 8 * mrow + (size_t)ch * X::ROW_BYTES, mrow);
+            uint4* frag = R.frags + st * 256;
+            if (key == prev_key) {
+                const uint4* from = R.frags + prev_st * 256;   // that stage is still intact: its `empty` wait lies ahead of this warp
 #pragma unroll
-            for (int e = 0; e < 4; e++) sc[e] = sz_f16_to_f32(__ldg(suh + lane + 32 * e));
-            // every row's loads are in flight before the first is used (a row at a time would pay the L2 latency once a row)
-            float v[8][4];
+                for (int e = 0; e < 8; e++) frag[lane + 32 * e] = from[lane + 32 * e];
+            } else {
+                const u16* suh = (const u16*)blob + s * 128;
+                float sc[4];
 #pragma unroll
-            for (int t = 0; t < 8; t++) {
-                if (t < n) {
-                    const int row = rows ? rows[t] : t;
+                for (int e = 0; e < 4; e++) sc[e] = sz_f16_to_f32(__ldg(suh + lane + 32 * e));
+                // every row's loads are in flight before the first is used (a row at a time would pay the L2 latency once a row)
+                float v[8][4];
 #pragma unroll
-                    for (int e = 0; e < 4; e++) v[t][e] = __ldg(x + (size_t)row * H + s * 128 + lane + 32 * e);
+                for (int t = 0; t < 8; t++) {
+                    if (t < n) {
+                        const int row = rows ? rows[t] : t;
+#pragma unroll
+                        for (int e = 0; e < 4; e++) v[t][e] = __ldg(x + (size_t)row * H + s * 128 + lane + 32 * e);
+                    }
+                }
+#pragma unroll
+                for (int t = 0; t < 8; t++) {
+                    if (t < n) {
+#pragma unroll
+                        for (int e = 0; e < 4; e++) v[t][e] *= sc[e];
+                        sz_xw_store_row(frag, t, v[t], lane);
+                    } else {
+                        sz_xw_zero_row(frag, t, lane);
+                    }
                 }
             }
-#pragma unroll
-            for (int t = 0; t < 8; t++) {
-                if (t < n) {
-#pragma unroll
-                    for (int e = 0; e < 4; e++) v[t][e] *= sc[e];
-                    sz_xw_store_row(frag, t, v[t], lane);
-                } else {
-                    sz_xw_zero_row(frag, t, lane);
-                }
-            }
+            prev_key = key; prev_st = st;
             __syncwarp();
-            if (lane == 0) sz_mbar_arrive(&full[st]);   // (release: the warp's fragment stores are ordered before it by the __syncwarp)
+            if (lane == 0) sz_mbar_arrive(&R.full[st]);   // (release: the warp's fragment stores are ordered before it by the __syncwarp)
         }
     } else {
         // ---- consumers
         const SzXWLane<K> LS = sz_xw_lane<K>(lane);
-        const int q = lane & 3, g8 = lane >> 2;
         for (int i = 0; i < count; i++) {
             const int u = u0 + i, st = i % S;
-            const int g = u / (2 * NS), rem = u - g * 2 * NS, mat = rem / NS;
-            if (!sz_mbar_wait(&full[st], (i / S) & 1)) { failed = 1; break; }
-            float c[NTC][4];
-            sz_xw_compute<K, NTC>(stages + (size_t)st * X::STAGE_BYTES, frags + st * 256, warp, lane, LS, c);
+            const int key = u / NCH, ch = u - key * NCH;
+            const int g = key / (2 * NS), rem = key - g * 2 * NS, mat = rem / NS;
+            if (!sz_mbar_wait(&R.full[st], (i / S) & 1)) { failed = 1; break; }
+            float c[TW][4];
+            sz_xw_compute<K, TW>(R.stages + (size_t)st * X::STAGE_BYTES, R.frags + st * 256, warp, lane, LS, c);
             __syncwarp();
-            if (lane == 0) sz_mbar_arrive(&empty[st]);
-            int n, pair0;
-            const u8* pairs;
-            if (g < D) { n = plan->count[g]; pairs = plan->pairs[g]; pair0 = 0; }
-            else { n = m; pairs = nullptr; pair0 = m * top_k; }
-#pragma unroll
-            for (int tt = 0; tt < 2; tt++) {
-                const int t = 2 * q + tt;
-                if (t < n) {
-                    const int pair = pairs ? pairs[t] : pair0 + t;
-                    long long* dst = acc + ((size_t)pair * 2 + mat) * FF + (warp * NTC) * 16 + g8;
-#pragma unroll
-                    for (int tc = 0; tc < NTC; tc++) {
-                        sz_fix_add(dst + tc * 16, c[tc][tt]);
-                        sz_fix_add(dst + tc * 16 + 8, c[tc][2 + tt]);
-                    }
-                }
-            }
+            if (lane == 0) sz_mbar_arrive(&R.empty[st]);
+            sz_xw_flush<TW>(plan, g, D, m, top_k, acc + (size_t)mat * FF, (size_t)2 * FF, (ch * 8 * TW + warp * TW) * 16, lane, c);
         }
     }
     if (failed && lane == 0) atomicExch(&ctrl[1], 1u);
 }
 
 // ---- down ---------------------------------------------------------------------------------------------------------------------------
-// Units: group x input block (128 of FF) x output chunk (512 outputs = 32 tile columns), the chunk fastest; 8 tile rows of 32 tiles
-// each, strided.  The input of a unit is the SwiGLU product of its pairs, finished by the producer warp from the gate / up sums:
-// rotate back (H), scale by svh, silu(g) * u, then into the down trellis' basis (suh, H); the chunks of one (group, input block)
-// follow one another and share it, so it is computed for the first and copied for the others.  out: i64 [pairs][H], zero on entry.
-template <int K>
-__global__ void __launch_bounds__(SZ_XW_THREADS, 2)
+// Units: group x input block (128 of FF) x output chunk (8 TW tile columns of the H / 16), the chunk fastest; 8 tile rows, strided.
+// The input of a unit is the SwiGLU product of its pairs, finished by the producer warp from the gate / up sums: rotate back (H),
+// scale by svh, silu(g) * u, then into the down trellis' basis (suh, H); the chunks of one (group, input block) follow one another
+// and share it, so it is computed for the first and copied for the others.  out: i64 [pairs][H], zero on entry.
+template <int K, int TW, int OCC>
+__global__ void __launch_bounds__(SZ_XW_THREADS, OCC)
 sz_xw_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, u64 gstride, const u8* __restrict__ up, u64 ustride,
                   const u8* __restrict__ down, u64 dstride, const u8* __restrict__ sh_gate, const u8* __restrict__ sh_up,
                   const u8* __restrict__ sh_down, int m, int H, int FF, int top_k, const long long* __restrict__ acc,
                   long long* __restrict__ out, u32* __restrict__ ctrl) {
-    using X = SzXW<K, 4>;
-    constexpr int S = SZ_XW_STAGES;
+    using X = SzXW<K, TW, OCC>;
+    constexpr int S = X::STAGES;
     extern __shared__ __align__(128) u8 smem[];
-    u8* stages = smem;
-    uint4* frags = (uint4*)(smem + S * X::STAGE_BYTES);
-    u64* full = (u64*)(smem + S * (X::STAGE_BYTES + X::FRAG_BYTES));
-    u64* empty = full + S;
+    SzXWRing<K, TW, OCC> R;
+    R.init(smem);
     __shared__ __align__(16) SzPlan splan;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < S; i++) { sz_mbar_init(&full[i], 2); sz_mbar_init(&empty[i], SZ_XW_CONSUMERS); }
-        sz_mbar_fence_init();
-    }
     // the plan was finished two kernels ago (the kernel before this one waited for it before it let this one start): it can be read,
     // and the first copies issued, ahead of the wait; only the gate / up sums need the wait
     plan = sz_plan_stage(plan, &splan);
     __syncthreads();
     const int D = plan ? plan->n_groups : 0;
     const int NG = D + (sh_down ? 1 : 0);
-    const int KB = FF / 128, NC = H / 512;
+    const int KB = FF / 128, NC = H / (128 * TW);
     const long long U = (long long)NG * KB * NC;
     const int u0 = (int)(U * blockIdx.x / gridDim.x), u1 = (int)(U * (blockIdx.x + 1) / gridDim.x);
     const int count = u1 - u0;
@@ -317,16 +357,12 @@ sz_xw_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
                 *bg = sh_gate; *bu = sh_up; *bd = sh_down;
             }
         };
-        auto issue = [&](int i) {   // lane 0: the 8 row copies of the block's i-th unit
-            const int u = u0 + i, st = i % S;
+        auto issue = [&](int i) {   // lane 0: the row copies of the block's i-th unit
+            const int u = u0 + i;
             const int g = u / (KB * NC), rem = u - g * KB * NC, kb = rem / NC, c = rem - kb * NC;
             const u8 *bg, *bu, *bd;
             blobs(g, &bg, &bu, &bd);
-            const u8* src = bd + hdr_d + (size_t)kb * 8 * drow + (size_t)c * X::ROW_BYTES;
-            u8* dst = stages + (size_t)st * X::STAGE_BYTES;
-            sz_mbar_expect_tx(&full[st], X::STAGE_BYTES);
-#pragma unroll
-            for (int kr = 0; kr < 8; kr++) sz_bulk_g2s(dst + kr * X::ROW_BYTES, src + kr * drow, X::ROW_BYTES, &full[st]);
+            R.issue(i % S, bd + hdr_d + (size_t)kb * 8 * drow + (size_t)c * X::ROW_BYTES, drow);
         };
         const int pre = count < S ? count : S;
         if (lane == 0)
@@ -337,14 +373,14 @@ sz_xw_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
         for (int i = 0; i < count; i++) {
             const int u = u0 + i, st = i % S;
             if (i >= S) {
-                if (!sz_mbar_wait(&empty[st], ((i / S) - 1) & 1)) { failed = 1; break; }
+                if (!sz_mbar_wait(&R.empty[st], ((i / S) - 1) & 1)) { failed = 1; break; }
                 if (lane == 0) issue(i);
             }
             const int g = u / (KB * NC), rem = u - g * KB * NC, kb = rem / NC;
-            uint4* frag = frags + st * 256;
+            uint4* frag = R.frags + st * 256;
             if (g == prev_g && kb == prev_kb) {
-                const uint4* from = frags + prev_st * 256;   // the same input as the unit before: a copy (that stage is still intact: its
-                                                              // `empty` wait lies ahead of this warp)
+                const uint4* from = R.frags + prev_st * 256;   // the same input as the unit before: a copy (that stage is still intact: its
+                                                                // `empty` wait lies ahead of this warp)
 #pragma unroll
                 for (int e = 0; e < 8; e++) frag[lane + 32 * e] = from[lane + 32 * e];
             } else {
@@ -390,38 +426,21 @@ sz_xw_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
             }
             prev_g = g; prev_kb = kb; prev_st = st;
             __syncwarp();
-            if (lane == 0) sz_mbar_arrive(&full[st]);
+            if (lane == 0) sz_mbar_arrive(&R.full[st]);
         }
     } else {
         sz_pdl_wait();
         sz_pdl_trigger();
         const SzXWLane<K> LS = sz_xw_lane<K>(lane);
-        const int q = lane & 3, g8 = lane >> 2;
         for (int i = 0; i < count; i++) {
             const int u = u0 + i, st = i % S;
             const int g = u / (KB * NC), rem = u - g * KB * NC, kb = rem / NC, cc = rem - kb * NC;
-            if (!sz_mbar_wait(&full[st], (i / S) & 1)) { failed = 1; break; }
-            float c[4][4];
-            sz_xw_compute<K, 4>(stages + (size_t)st * X::STAGE_BYTES, frags + st * 256, warp, lane, LS, c);
+            if (!sz_mbar_wait(&R.full[st], (i / S) & 1)) { failed = 1; break; }
+            float c[TW][4];
+            sz_xw_compute<K, TW>(R.stages + (size_t)st * X::STAGE_BYTES, R.frags + st * 256, warp, lane, LS, c);
             __syncwarp();
-            if (lane == 0) sz_mbar_arrive(&empty[st]);
-            int n, pair0;
-            const u8* pairs;
-            if (g < D) { n = plan->count[g]; pairs = plan->pairs[g]; pair0 = 0; }
-            else { n = m; pairs = nullptr; pair0 = m * top_k; }
-#pragma unroll
-            for (int tt = 0; tt < 2; tt++) {
-                const int t = 2 * q + tt;
-                if (t < n) {
-                    const int pair = pairs ? pairs[t] : pair0 + t;
-                    long long* dst = out + (size_t)pair * H + cc * 512 + (warp * 4) * 16 + g8;
-#pragma unroll
-                    for (int tc = 0; tc < 4; tc++) {
-                        sz_fix_add(dst + tc * 16, c[tc][tt]);
-                        sz_fix_add(dst + tc * 16 + 8, c[tc][2 + tt]);
-                    }
-                }
-            }
+            if (lane == 0) sz_mbar_arrive(&R.empty[st]);
+            sz_xw_flush<TW>(plan, g, D, m, top_k, out, (size_t)H, (cc * 8 * TW + warp * TW) * 16, lane, c);
         }
     }
     if (failed && lane == 0) atomicExch(&ctrl[1], 1u);

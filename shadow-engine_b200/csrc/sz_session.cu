@@ -524,9 +524,12 @@ static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bo
         int nt = ((int)c.hc_rank + C + 31) / 32 * 32;
         if (nt < 256) nt = 256;
         cudaError_t e1 = cudaErrorInvalidValue, e2 = cudaSuccess;
-        // one launch (down half, grid-wide barrier, up half) when all its blocks fit the GPU at once - the barrier needs every block
-        // resident; SZ_HC_SPLIT=1 keeps the two halves as launches of their own (the second implementation of the same arithmetic)
-        static const bool split = getenv("SZ_HC_SPLIT") && atoi(getenv("SZ_HC_SPLIT")) != 0;
+        // SZ_HC_FUSED=1: one launch (down half, grid-wide barrier, up half) when all its blocks fit the GPU at once - the barrier
+        // needs every block resident.  Measured slower than the two launches (a 4-row pass of the 48-layer model: 6.48 ms against
+        // 6.16 ms): a launch boundary with programmatic dependent launch costs less than a barrier whose every step is a round
+        // trip to L2, so the two halves stay launches of their own and the fused form is the second implementation.
+        const char* fe = getenv("SZ_HC_FUSED");   // (read when a pass is built: a test switches it between two sessions of one process)
+        const bool split = !(fe && atoi(fe) != 0);
         const int blocks = CH / 64 > H / 16 ? CH / 64 : H / 16;
         if (!split && blocks <= sz_sm_count_session()) {
 #define SZ_HC_CASE(MM)                                                                                                                   \
@@ -1033,6 +1036,72 @@ extern "C" int sz_session_export(sz_session* s, int what, int layer, void* dst, 
     }
     SZ_CUDA(cudaStreamSynchronize(st));
     s->inflight = 0;
+    return SZ_OK;
+}
+
+// ---- launching a kernel by name --------------------------------------------------------------------------------------------------
+// The kernel-launch seam of the reference (Program::launch, crates/shadowzero-cuda/src/kernels.rs:546-572; the registry :39-57,
+// 163-477): an entry point is looked up by name in a static table that spells out its parameter types, every argument travels in an
+// 8-byte slot of its own, and a launch whose arguments do not fit the table is refused before the driver sees it.  The table covers
+// this translation unit's kernels with plain parameters (no templates, no structs by value); tests/test_kernel_registry.py parses
+// the sources and checks the table against them in both directions, as the reference's tests/drift.rs does.
+namespace {
+struct SzKernelEntry {
+    const char* name;
+    const void* fn;
+    int n;
+    int32_t types[20];
+};
+const SzKernelEntry kKernels[] = {
+    {"sz_embed_kernel", (const void*)sz_embed_kernel, 7, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
+    {"sz_hc_norm_kernel", (const void*)sz_hc_norm_kernel, 8, {SZ_P_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_F32, SZ_P_PTR}},
+    {"sz_hc_mix_kernel", (const void*)sz_hc_mix_kernel, 5, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
+    {"sz_delta_prep_kernel", (const void*)sz_delta_prep_kernel, 16, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_PTR, SZ_P_PTR}},
+    {"sz_conv_commit_kernel", (const void*)sz_conv_commit_kernel, 9, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_PTR}},
+    {"sz_state_update_kernel", (const void*)sz_state_update_kernel, 2, {SZ_P_PTR, SZ_P_CONST_PTR}},
+    {"sz_attn_prep_kernel", (const void*)sz_attn_prep_kernel, 18, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_F32, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_PTR, SZ_P_PTR, SZ_P_PTR, SZ_P_PTR}},
+    {"sz_attn_merge_kernel", (const void*)sz_attn_merge_kernel, 6, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
+    {"sz_accept_greedy_kernel", (const void*)sz_accept_greedy_kernel, 7, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
+    {"sz_accept_sampled_kernel", (const void*)sz_accept_sampled_kernel, 6, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_CONST_PTR, SZ_P_PTR}},
+    {"sz_topk_slices_kernel", (const void*)sz_topk_slices_kernel, 6, {SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_CONST_PTR}},
+    {"sz_topk_merge_kernel", (const void*)sz_topk_merge_kernel, 3, {SZ_P_CONST_PTR, SZ_P_I32, SZ_P_PTR}},
+    {"sz_fill_kv_kernel", (const void*)sz_fill_kv_kernel, 8, {SZ_P_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_U64, SZ_P_I32, SZ_P_I32, SZ_P_U32}},
+};
+const int kKernelCount = (int)(sizeof(kKernels) / sizeof(kKernels[0]));
+const SzKernelEntry* sz_find_kernel(const char* name) {
+    for (int i = 0; i < kKernelCount; i++)
+        if (strcmp(kKernels[i].name, name) == 0) return &kKernels[i];
+    return nullptr;
+}
+}  // namespace
+
+extern "C" int sz_kernel_count(void) { return kKernelCount; }
+extern "C" const char* sz_kernel_name(int i) { return i >= 0 && i < kKernelCount ? kKernels[i].name : nullptr; }
+extern "C" int sz_kernel_params(const char* name, int32_t* types, int cap) {
+    const SzKernelEntry* e = name ? sz_find_kernel(name) : nullptr;
+    if (!e) return -1;
+    for (int i = 0; i < e->n && i < cap && types; i++) types[i] = e->types[i];
+    return e->n;
+}
+
+extern "C" int sz_kernel_launch(const char* name, const uint32_t grid[3], const uint32_t block[3], uint32_t shared, uint64_t stream, const sz_karg* args,
+                                int nargs) {
+    if (!name || !grid || !block || (nargs > 0 && !args)) return sz_fail(SZ_E_ARG, "sz_kernel_launch: null argument");
+    const SzKernelEntry* e = sz_find_kernel(name);
+    if (!e) return sz_fail(SZ_E_ARG, "the registry has no entry point %s", name);
+    if (e->n != nargs) return sz_fail(SZ_E_ARG, "%s takes %d arguments, %d given", name, e->n, nargs);
+    static const char* tn[] = {"Ptr", "ConstPtr", "U32", "I32", "U64", "F32"};
+    for (int i = 0; i < nargs; i++) {
+        const int a = args[i].type, p = e->types[i];
+        const bool fits = a == p || (a == SZ_P_PTR && p == SZ_P_CONST_PTR);   // a device pointer satisfies both pointer kinds; scalars match exactly
+        if (a < 0 || a > SZ_P_F32 || !fits) return sz_fail(SZ_E_ARG, "%s argument %d: a %s does not fit a %s parameter", name, i, a >= 0 && a <= SZ_P_F32 ? tn[a] : "?", tn[p]);
+    }
+    if (!grid[0] || !grid[1] || !grid[2] || !block[0] || !block[1] || !block[2] || (uint64_t)block[0] * block[1] * block[2] > 1024)
+        return sz_fail(SZ_E_ARG, "%s: a grid of %u x %u x %u blocks of %u x %u x %u threads does not fit", name, grid[0], grid[1], grid[2], block[0], block[1], block[2]);
+    uint64_t slots[20];
+    void* ptrs[20];
+    for (int i = 0; i < nargs; i++) { slots[i] = args[i].bits; ptrs[i] = &slots[i]; }   // little-endian: a 4-byte parameter reads the low half of its slot
+    SZ_CUDA(cudaLaunchKernel(e->fn, dim3(grid[0], grid[1], grid[2]), dim3(block[0], block[1], block[2]), ptrs, shared, (cudaStream_t)stream));
     return SZ_OK;
 }
 

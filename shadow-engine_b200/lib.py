@@ -31,12 +31,21 @@ class MoeLayerC(C.Structure):
                 ("ep_first", C.c_int32), ("ep_count", C.c_int32), ("ep_shared", C.c_int32), ("ep_reserved", C.c_int32)]
 
 
+class KArg(C.Structure):
+    """struct sz_karg"""
+    _fields_ = [("type", C.c_int32), ("reserved", C.c_int32), ("bits", C.c_uint64)]
+
+
+P_PTR, P_CONST_PTR, P_U32, P_I32, P_U64, P_F32 = range(6)
+
+
 class HeadC(C.Structure):
     """struct sz_head"""
     _fields_ = [("rows", C.c_int32), ("cols", C.c_int32), ("bits", C.c_int32), ("k_blk", C.c_int32),
                 ("weight", C.c_uint64), ("w_q2", C.c_uint64), ("w_sc", C.c_uint64), ("work", C.c_uint64), ("work_bytes", C.c_int64)]
 
 
+PLACE_HOST, PLACE_DEVICE = 0, 1
 STATE_DELTA_S, STATE_DELTA_CONV, STATE_KV_K, STATE_KV_V = range(4)
 HEAD_XR, HEAD_XQ, HEAD_XSC, HEAD_XCORR, HEAD_BMAX, HEAD_SEL, HEAD_ERR = range(7)
 
@@ -57,6 +66,14 @@ SYMBOLS = {
     "sz_moe_verify_host": (C.c_int, [C.POINTER(MoeLayerC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_uint64, C.c_uint64, C.c_uint64, C.c_int64, C.c_uint64]),
     "sz_moe_launches": (C.c_int, [C.POINTER(MoeLayerC)]),
+    "sz_model_load_gguf": (C.c_int, [C.c_char_p, C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]),
+    "sz_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "sz_weights_key_u64": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "sz_weights_model": (C.c_void_p, [C.c_void_p]),
+    "sz_weights_bytes": (C.c_int64, [C.c_void_p]),
+    "sz_weights_tensor_count": (C.c_int, [C.c_void_p]),
+    "sz_weights_tensor_info": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int32), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
+    "sz_weights_free": (None, [C.c_void_p]),
     # the session (struct pointers are passed with ctypes.byref, so they are declared as void pointers here)
     "sz_session_bytes": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int64)]),
     "sz_session_create": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_uint64, C.c_int64, C.c_uint64, C.POINTER(C.c_void_p)]),
@@ -75,6 +92,10 @@ SYMBOLS = {
     "sz_session_export": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_uint64]),
     "sz_session_trace_routes": (C.c_int, [C.c_void_p, C.c_int]),
     "sz_session_routes": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint64]),
+    "sz_kernel_count": (C.c_int, []),
+    "sz_kernel_name": (C.c_char_p, [C.c_int]),
+    "sz_kernel_params": (C.c_int, [C.c_char_p, C.POINTER(C.c_int32), C.c_int]),
+    "sz_kernel_launch": (C.c_int, [C.c_char_p, C.POINTER(C.c_uint32), C.POINTER(C.c_uint32), C.c_uint32, C.c_uint64, C.c_void_p, C.c_int]),
     # host side of speculation
     "sz_lookup": (C.c_int, [C.POINTER(C.c_uint32), C.c_int, C.c_int, C.POINTER(C.c_int), C.c_int, C.POINTER(C.c_uint32)]),
     "sz_drafter_new": (C.c_void_p, [C.c_int, C.c_int, C.c_int]),

@@ -37,14 +37,33 @@ def cpu_steps(cpu, tokens):
     rows, routes = [], []
     for t in tokens:
         rows.append(cpu.step(t))
-        routes.append(cpu.routes()[0])
-    return np.stack(rows), np.stack(routes)
+        routes.append(cpu.routes())
+    return np.stack(rows), routes
+
+
+def same_routing(got, want_idx, want_w):
+    """Routing indices equal - except where the reference itself cannot tell two experts apart: their routing weights agree to
+    within 1e-5 relative, i.e. their logits differ by less than the last bits of the f32 activations they were computed from, and
+    the two sides (f64 dot products over f32 activations that differ in those bits) may rank such a pair either way.  The chosen
+    SET must still be the same, and any rank that differs must belong to such a near-tie."""
+    if np.array_equal(got, want_idx):
+        return True
+    for l in range(want_idx.shape[0]):
+        if np.array_equal(got[l], want_idx[l]):
+            continue
+        if sorted(got[l]) != sorted(want_idx[l]):
+            return False
+        for r in np.nonzero(got[l] != want_idx[l])[0]:
+            other = int(np.nonzero(want_idx[l] == got[l][r])[0][0])       # where the oracle ranks the expert the device put at rank r
+            if abs(want_w[l][r] - want_w[l][other]) > 1e-5 * want_w[l][r] or abs(other - r) != 1:
+                return False
+    return True
 
 
 def check_rows(got, routes, want, want_routes, what):
     worst = 0.0
     for j in range(len(want)):
-        assert np.array_equal(routes[:, j, :], want_routes[j]), "%s: routing differs at row %d" % (what, j)
+        assert same_routing(routes[:, j, :], want_routes[j][0], want_routes[j][1]), "%s: routing differs at row %d" % (what, j)
         e = rel_err(got[j], want[j])
         worst = max(worst, e)
         assert e < LOGIT_REL, "%s: row %d logits off by %g" % (what, j, e)

@@ -202,6 +202,26 @@ def test_graph_replay_equals_eager_launches(small):
     assert max(rel_err(outs[0][j], want[j]) for j in range(16)) < 1e-3
 
 
+def test_fused_hyper_connection_read_gives_the_bits_of_the_two_launches(small):
+    # SZ_HC_FUSED=1: down half, grid-wide barrier (bounded), up half in one launch - the second implementation of the same arithmetic
+    import os
+    M, hm, dm = small
+    toks = [int(t) for t in np.random.default_rng(6).integers(0, SMALL["vocab"], 12)]
+    outs = []
+    for fused in ("0", "1"):
+        os.environ["SZ_HC_FUSED"] = fused
+        try:
+            s = md.Session(dm, 64, kv_q8=True)
+            got = []
+            for lo in (0, 4, 8):            # the first pass is eager, the others replay its graph
+                s.verify(toks[lo:lo + 4]); got.append(s.result(logits=True)[2]); s.commit(4)
+            outs.append(np.concatenate(got))
+            del s
+        finally:
+            del os.environ["SZ_HC_FUSED"]
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+
+
 def test_synthetic_history_gives_a_long_context(small):
     M, hm, dm = small
     s = md.Session(dm, 4096, kv_q8=True)
