@@ -225,6 +225,21 @@ int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode,
 struct sz_sampler;
 int sz_session_set_sampler(sz_session* s, const struct sz_sampler* sp);
 int sz_session_verify_sampled(sz_session* s, const int32_t* ids, int m, uint64_t pos, int eog_token, uint64_t stream);
+/* Tree verification (no counterpart in the reference, whose verify pass is a chain: session.rs:7698-7723, kernels/forward.cu:1481-1487).
+ * One pass over a draft TREE of up to SZ_MAX_VERIFY rows: row 0 is the root (the pass's own token, parents[0] = -1), row j > 0 a drafted
+ * token whose parent is row parents[j] < j.  Row j attends to the committed positions, to its ancestors and to itself (a tree mask over
+ * the pass's own cache slots), sits at sequence position committed + depth(j), and continues the DeltaNet state and the conv window of
+ * its parent (the state after a row that a later row branches off is kept aside during the scan).  Row j's output is what follows the
+ * path root .. j.  accept_mode SZ_ACCEPT_GREEDY walks down from the root on the device: the target's best token after the current row
+ * must be the token of one of its children (the lowest row among equals), never a drafted end-of-generation token; SZ_ACCEPT_NONE
+ * leaves the decision to the caller (sampled acceptance: sz_tree_accept_sampled below, then sz_session_commit_path).
+ * Committing keeps a PATH: the recurrent state is replayed along it from the pass's saved inputs, and the kept rows' keys and values
+ * move from their rows' cache slots to their depths' positions.  sz_session_result gives {rows kept, next token} and every row's
+ * top-64 as for a chain; sz_session_tree_path the kept rows (root first) of a pass the device accepted, which is then closed with
+ * sz_session_commit(s, rows kept). */
+int sz_session_verify_tree(sz_session* s, const int32_t* ids, const int32_t* parents, int m, int accept_mode, int eog_token, uint64_t stream);
+int sz_session_tree_path(sz_session* s, int32_t* path, int* n, uint64_t stream);
+int sz_session_commit_path(sz_session* s, const int32_t* path, int n, uint64_t stream);
 /* Copies the pending pass's results to the host and synchronises: keep_next[2] = {rows kept by the device's acceptance, the
  * token that follows them}; top = [m][128] u32, 64 logit bit patterns (largest first, ties to the lower id) then 64 token ids
  * (session.rs:6034-6039); logits = [m][vocab] f32.  Any pointer may be null. */
@@ -301,6 +316,18 @@ void sz_policy_observe_chain(sz_draft_policy* p, int t_neural, int k_chain, int 
 typedef struct sz_sampler { float temperature; int32_t top_k; float top_p; float min_p; uint64_t seed; } sz_sampler;
 double sz_uniform(uint64_t seed, uint64_t pos);
 uint32_t sz_sample_top(const sz_sampler* sp, const uint32_t* top128, uint64_t pos);
+/* Sampled acceptance down a draft tree (no counterpart in the reference): rejection sampling against the drafter's probabilities, level
+ * by level.  At the current row the target distribution p is the sampler's over the row's top-64 (the candidates and weights
+ * sz_sample_top draws from); its children are tried in row order: child c with token x and draft probability draft_prob[c] = q is kept
+ * with probability min(1, p(x) / q); after a refusal p loses q at x (not below zero) and is renormalised; when no child is kept the next
+ * token is drawn from what is left of p.  With a drafter that proposes fixed tokens (q = 1: a lookup or suffix drafter) the emitted
+ * tokens are distributed exactly as the target's; for a drafter with a spread-out distribution exactness would need its whole
+ * distribution in the residual, and the call only knows the drafted tokens' probabilities: an approximation then.  Decisions use
+ * sz_uniform(seed, stream): stream 256 P for the draw of the token at output position P, 256 P + 1 + i for the i-th child tried there;
+ * `pos` is the output position of the token after the root.  top: [m][128] as sz_session_result gives it.  Returns the rows kept (-1: a
+ * bad argument); path: the kept rows, root first (for sz_session_commit_path); *next: the token after them. */
+int sz_tree_accept_sampled(const sz_sampler* sp, const uint32_t* top, const uint32_t* ids, const int32_t* parents, int m, const float* draft_prob,
+                           uint64_t pos, int eog_token, int32_t* path, uint32_t* next);
 /* The draft / verify / accept / commit loop of engine.rs:2149-2454 for `--spec spec_k` with the suffix drafter (no neural
  * drafter, draft policy not consulted): generates up to max_new tokens after the prompt into `out`; pass_log receives
  * (drafted, accepted) per verify pass.  device_accept = 1 lets the device decide acceptance, greedy or sampled (checked against the host's own decision). */

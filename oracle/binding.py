@@ -72,6 +72,10 @@ def lib():
         L.szo_session_clone.argtypes = [C.c_void_p]
         L.szo_session_step.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
         L.szo_session_fill_synthetic.argtypes = [C.c_void_p, C.c_int, C.c_uint32]
+        L.szo_session_tree.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int]
+        L.szo_tree_accept_sampled.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_uint64, C.c_int,
+                                              C.c_void_p, C.POINTER(C.c_uint32)]
+        L.szo_tree_accept_greedy.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_uint32)]
         L.szo_session_state.restype = C.c_void_p
         L.szo_session_state.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
         L.szo_lookup.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
@@ -247,6 +251,16 @@ class Session:
         lib().szo_session_step(self.h, int(token), _p(lg) if want_logits else None, _p(u) if want_u else None)
         return (lg, u) if want_u else lg
 
+    def tree(self, ids, parents, keep_path=None):
+        """Logits [m, vocab] of a pass over a draft tree (row j = the sequence root .. j); with keep_path the session then becomes
+        the one that read those rows."""
+        m = len(ids)
+        a, p = np.array(ids, dtype=np.uint32), np.array(parents, dtype=np.int32)
+        lg = np.empty((m, self.vocab), dtype=np.float32)
+        kp = np.array(keep_path if keep_path is not None else [], dtype=np.int32)
+        lib().szo_session_tree(self.h, _p(a), _p(p), m, _p(lg), _p(kp) if kp.size else None, int(kp.size))
+        return lg
+
     def fill_synthetic(self, length, seed=1):
         lib().szo_session_fill_synthetic(self.h, length, seed)
 
@@ -302,6 +316,28 @@ class Drafter:
         ml = C.c_int()
         n = lib().szo_drafter_propose_after(self.h, _p(ex), len(extra), k, _p(out), C.byref(ml))
         return [int(t) for t in out[:n]], ml.value
+
+
+def tree_accept_greedy(logits, ids, parents, eog=-1):
+    """(kept path, next token) of greedy acceptance down a draft tree."""
+    m, vocab = logits.shape
+    a, p = np.array(ids, dtype=np.uint32), np.array(parents, dtype=np.int32)
+    path = np.zeros(m, dtype=np.int32)
+    nxt = C.c_uint32()
+    n = lib().szo_tree_accept_greedy(_p(np.ascontiguousarray(logits, dtype=np.float32)), vocab, _p(a), _p(p), m, eog, _p(path), C.byref(nxt))
+    return [int(t) for t in path[:n]], int(nxt.value)
+
+
+def tree_accept_sampled(sampler, tv, ti, ids, parents, draft_prob, pos, eog=-1):
+    """(kept path, next token) of rejection-sampling acceptance down a draft tree; tv / ti: [m, 64] values and ids of the rows' top-64."""
+    m = len(ids)
+    tv = np.ascontiguousarray(tv, dtype=np.float32)
+    ti = np.ascontiguousarray(ti, dtype=np.uint32)
+    a, p, q = np.array(ids, dtype=np.uint32), np.array(parents, dtype=np.int32), np.array(draft_prob, dtype=np.float32)
+    path = np.zeros(m, dtype=np.int32)
+    nxt = C.c_uint32()
+    n = lib().szo_tree_accept_sampled(C.byref(sampler), _p(tv), _p(ti), _p(a), _p(p), m, _p(q), pos, eog, _p(path), C.byref(nxt))
+    return [int(t) for t in path[:n]], int(nxt.value)
 
 
 def lookup(hist, k, lens=(3, 2)):

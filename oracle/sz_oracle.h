@@ -101,6 +101,9 @@ const double* szo_session_route_weights(const szo_session* s);
 void szo_session_assign(szo_session* dst, const szo_session* src); /* snapshot / restore */
 szo_session* szo_session_clone(const szo_session* src);
 void szo_session_step(szo_session* s, uint32_t token, float* logits, float* final_u); /* forward.rs:751-794 */
+/* a pass over a draft tree, row by row on copies of the session (no counterpart in the reference); greedy acceptance down the tree */
+void szo_session_tree(szo_session* s, const uint32_t* ids, const int32_t* parents, int m, float* logits, const int32_t* keep_path, int n_keep);
+int szo_tree_accept_greedy(const float* logits, int vocab, const uint32_t* ids, const int32_t* parents, int m, int eog, int32_t* path, uint32_t* next);
 /* the library's synthetic history (sz_session_fill_synthetic), value for value: no counterpart in the reference */
 void szo_session_fill_synthetic(szo_session* s, int len, uint32_t seed);
 /* one piece of the state: 0 recurrent state [v heads][d][d], 1 carried conv rows, 2 / 3 K / V cache [position][kv head][head] */
@@ -124,6 +127,8 @@ uint32_t szo_sample_top(const szo_sampler* sp, const float* tv, const uint32_t* 
 
 typedef struct { int32_t spec_k, max_new, lookup_min, greedy, eog_token, reserved; szo_sampler sampler; } szo_gen_params;
 typedef struct { int32_t n_tokens, passes, drafted, accepted, lookup_passes; int32_t pos_tried[8], pos_right[8]; } szo_gen_stats;
+int szo_tree_accept_sampled(const szo_sampler* sp, const float* tv, const uint32_t* ti, const uint32_t* ids, const int32_t* parents, int m,
+                            const float* draft_prob, uint64_t pos, int eog, int32_t* path, uint32_t* next);
 /* Generates up to max_new tokens after the prompt with the engine's loop; pass_log gets (drafted, accepted) per verify pass. */
 int szo_generate(szo_session* s, const uint32_t* prompt, int n_prompt, const szo_gen_params* p, uint32_t* out, int32_t* pass_log,
                  int pass_cap, szo_gen_stats* stats);

@@ -458,6 +458,117 @@ void szo_session_step(szo_session* s, uint32_t token, float* logits, float* fina
     free(emb); free(r); free(u); free(y); free(g);
 }
 
+/* A pass over a draft tree, the slow and obvious way: every row steps its token on a COPY of the session as its parent left it, so
+ * row j's logits are those of the sequence root .. j by construction.  No counterpart in the reference (its verify pass is a chain);
+ * this is what the library's tree pass - tree mask, per-branch state forks, position by depth - must reproduce.  logits: [m][vocab].
+ * keep_path / n_keep (n_keep > 0): afterwards the session becomes the one that read the kept path (row indices, root first); with
+ * n_keep = 0 the session is left as it was. */
+void szo_session_tree(szo_session* s, const uint32_t* ids, const int32_t* parents, int m, float* logits, const int32_t* keep_path, int n_keep) {
+    size_t vocab = (size_t)s->m->cfg.vocab;
+    szo_session** after = (szo_session**)calloc((size_t)m, sizeof(szo_session*));
+    for (int j = 0; j < m; j++) {
+        after[j] = szo_session_clone(parents[j] < 0 ? s : after[parents[j]]);
+        szo_session_step(after[j], ids[j], logits + (size_t)j * vocab, NULL);
+    }
+    if (n_keep > 0) szo_session_assign(s, after[keep_path[n_keep - 1]]);
+    for (int j = 0; j < m; j++) szo_session_free(after[j]);
+    free(after);
+}
+
+/* Greedy acceptance down a tree: from the root, the best token (lowest id among equals, as the device's top-64 orders them) after
+ * the current row must be the token of one of its children - the lowest row among equals -, never a drafted end-of-generation token.
+ * Returns the rows kept; path[0 .. kept) the kept rows, *next the token after them. */
+int szo_tree_accept_greedy(const float* logits, int vocab, const uint32_t* ids, const int32_t* parents, int m, int eog, int32_t* path, uint32_t* next) {
+    int cur = 0, keep = 1;
+    path[0] = 0;
+    for (;;) {
+        const float* row = logits + (size_t)cur * (size_t)vocab;
+        int best = 0;
+        for (int v = 1; v < vocab; v++) if (row[v] > row[best]) best = v;
+        *next = (uint32_t)best;
+        int nxt = -1;
+        for (int c = cur + 1; c < m; c++)
+            if (parents[c] == cur && (int)ids[c] == best && best != eog) { nxt = c; break; }
+        if (nxt < 0) break;
+        cur = nxt;
+        path[keep++] = cur;
+    }
+    return keep;
+}
+
+/* Sampled acceptance down a draft tree by rejection sampling against the drafter's probabilities (no counterpart in the reference;
+ * the library's sz_tree_accept_sampled states the rule).  tv / ti: [m][64] values and ids of every row's top-64. */
+static int tree_candidates(const szo_sampler* sp, const float* tv, int ntop, double* p) {
+    float max = tv[0];
+    if (!isfinite(max)) { p[0] = 1.0; return 1; }
+    float cut = max - 18.0f * sp->temperature;
+    int n = 0;
+    while (n < ntop && tv[n] >= cut) n++;
+    int tk = sp->top_k < 1 ? 1 : sp->top_k;
+    if (n > tk) n = tk;
+    float inv_t = 1.0f / sp->temperature;
+    double z = 0.0;
+    for (int i = 0; i < n; i++) { p[i] = exp((double)((tv[i] - max) * inv_t)); z += p[i]; }
+    for (int i = 0; i < n; i++) p[i] /= z;
+    double floor_p = (double)sp->min_p * p[0];
+    int keep = 0;
+    while (keep < n && p[keep] >= floor_p) keep++;
+    if (keep < 1) keep = 1;
+    if (sp->top_p < 1.0f) {
+        double acc = 0.0;
+        int cnt = 0;
+        for (int i = 0; i < keep; i++) { acc += p[i]; cnt++; if (acc >= (double)sp->top_p) break; }
+        keep = cnt < 1 ? 1 : cnt;
+    }
+    double mass = 0.0;
+    for (int i = 0; i < keep; i++) mass += p[i];
+    for (int i = 0; i < keep; i++) p[i] /= mass;
+    return keep;
+}
+
+int szo_tree_accept_sampled(const szo_sampler* sp, const float* tv, const uint32_t* ti, const uint32_t* ids, const int32_t* parents, int m,
+                            const float* draft_prob, uint64_t pos, int eog, int32_t* path, uint32_t* next) {
+    int cur = 0, keep = 1;
+    path[0] = 0;
+    for (;;) {
+        double p[64];
+        const float* v = tv + (size_t)cur * 64;
+        const uint32_t* id = ti + (size_t)cur * 64;
+        int n = tree_candidates(sp, v, 64, p);
+        uint64_t P = pos + (uint64_t)(keep - 1);
+        int tried = 0, taken = -1;
+        for (int c = cur + 1; c < m; c++) {
+            if (parents[c] != cur) continue;
+            uint32_t x = ids[c];
+            int at = -1;
+            for (int i = 0; i < n; i++) if (id[i] == x) { at = i; break; }
+            double px = at >= 0 ? p[at] : 0.0, q = (double)draft_prob[c];
+            if (!(q > 1e-12)) q = 1e-12;
+            if (q > 1.0) q = 1.0;
+            double u = szo_uniform(sp->seed, 256 * P + 1 + (uint64_t)tried);
+            tried++;
+            if (eog >= 0 && x == (uint32_t)eog) continue;
+            if (u * q < px) { taken = c; break; }
+            if (at >= 0) {
+                p[at] = px > q ? px - q : 0.0;
+                double z = 0.0;
+                for (int i = 0; i < n; i++) z += p[i];
+                if (z > 0.0) { for (int i = 0; i < n; i++) p[i] /= z; }
+                else { p[at] = 0.0; n = tree_candidates(sp, v, 64, p); }
+            }
+        }
+        if (taken >= 0) { cur = taken; path[keep++] = cur; continue; }
+        double u = szo_uniform(sp->seed, 256 * P);
+        uint32_t tok = id[n - 1];
+        for (int i = 0; i < n; i++) {
+            if (u < p[i]) { tok = id[i]; break; }
+            u -= p[i];
+        }
+        *next = tok;
+        return keep;
+    }
+}
+
 /* ---------------------------------------------------------------------------------------------------------------- */
 /* prompt lookup and the suffix drafter (engine.rs:823-1011)                                                         */
 

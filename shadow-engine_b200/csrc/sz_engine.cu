@@ -343,6 +343,92 @@ extern "C" uint32_t sz_sample_top(const sz_sampler* sp, const uint32_t* top, uin
     return id[keep - 1];
 }
 
+// ---- sampled acceptance down a draft tree (no counterpart in the reference: its sampled acceptance is the chain's "the token the
+// target would have drawn", crates/shadowzero-serve/src/sampler.rs:3-9).  Rejection sampling against the drafter's probabilities,
+// one level at a time: at the current row the target distribution p is the sampler's (temperature, top-k, min-p, top-p over the row's
+// top-64, exactly the candidates and weights sz_sample_top draws from); its children are tried in row order - child c with token x
+// and draft probability q is kept with probability min(1, p(x) / q); on a refusal p loses q at x (never below zero) and is
+// renormalised.  When no child is kept the next token is drawn from what is left of p.  Under a drafter that proposes fixed tokens
+// (q = 1: lookup, suffix drafter) what is emitted is distributed exactly as p; a spread-out drafter's residual would need its whole
+// distribution, which the call does not have (only the drafted tokens' probabilities): an approximation then.  Every decision uses the counter-based uniform number of (seed, stream): the stream of the
+// token at output position P is 256 P for the final draw and 256 P + 1 + i for the i-th child tried there.
+// top: [m][128] as sz_session_result gives it; draft_prob[j]: the drafter's probability of ids[j] under its parent (row 0 unused).
+// Returns the rows kept; path[0 .. kept) the kept rows (root first), *next the token after them.
+static int sz_candidates(const sz_sampler* sp, const uint32_t* top, double* probs, const uint32_t** ids) {
+    float v[64];
+    std::memcpy(v, top, sizeof(v));
+    *ids = top + 64;
+    const float max = v[0];
+    if (!std::isfinite(max)) { probs[0] = 1.0; return 1; }
+    const float cut = max - 18.0f * sp->temperature;
+    int n = 0;
+    while (n < 64 && v[n] >= cut) n++;
+    const int tk = sp->top_k < 1 ? 1 : sp->top_k;
+    if (n > tk) n = tk;
+    const float inv_t = 1.0f / sp->temperature;
+    double total = 0.0;
+    for (int i = 0; i < n; i++) { probs[i] = std::exp((double)((v[i] - max) * inv_t)); total += probs[i]; }
+    for (int i = 0; i < n; i++) probs[i] /= total;
+    const double floor_p = (double)sp->min_p * probs[0];
+    int keep = 0;
+    while (keep < n && probs[keep] >= floor_p) keep++;
+    if (keep < 1) keep = 1;
+    if (sp->top_p < 1.0f) {
+        double acc = 0.0;
+        int cnt = 0;
+        for (int i = 0; i < keep; i++) { acc += probs[i]; cnt++; if (acc >= (double)sp->top_p) break; }
+        keep = cnt < 1 ? 1 : cnt;
+    }
+    double mass = 0.0;
+    for (int i = 0; i < keep; i++) mass += probs[i];
+    for (int i = 0; i < keep; i++) probs[i] /= mass;
+    return keep;
+}
+
+extern "C" int sz_tree_accept_sampled(const sz_sampler* sp, const uint32_t* top, const uint32_t* ids, const int32_t* parents, int m, const float* draft_prob,
+                                      uint64_t pos, int eog_token, int32_t* path, uint32_t* next) {
+    if (!sp || !top || !ids || !parents || !draft_prob || !path || !next || m < 1 || m > SZ_MAX_VERIFY) return -1;
+    int cur = 0, keep = 1;
+    path[0] = 0;
+    for (;;) {
+        double p[64];
+        const uint32_t* cid = nullptr;
+        int n = sz_candidates(sp, top + (size_t)cur * 128, p, &cid);
+        const uint64_t P = pos + (uint64_t)(keep - 1);       // output position of the token after the current row
+        int tried = 0, taken = -1;
+        for (int c = cur + 1; c < m && taken < 0; c++) {
+            if (parents[c] != cur) continue;
+            const uint32_t x = ids[c];
+            int at = -1;
+            for (int i = 0; i < n; i++) if (cid[i] == x) { at = i; break; }
+            const double px = at >= 0 ? p[at] : 0.0;
+            double q = (double)draft_prob[c];
+            if (!(q > 1e-12)) q = 1e-12;
+            if (q > 1.0) q = 1.0;
+            const double u = sz_uniform(sp->seed, 256 * P + 1 + (uint64_t)tried);
+            tried++;
+            if (eog_token >= 0 && x == (uint32_t)eog_token) continue;   // a drafted end-of-generation token is left for the loop's top
+            if (u * q < px) { taken = c; break; }
+            if (at >= 0) {                                               // refused: the residual distribution
+                p[at] = px > q ? px - q : 0.0;
+                double total = 0.0;
+                for (int i = 0; i < n; i++) total += p[i];
+                if (total > 0.0) for (int i = 0; i < n; i++) p[i] /= total;
+                else { p[at] = 0.0; n = sz_candidates(sp, top + (size_t)cur * 128, p, &cid); }   // (only when p was all on x and q >= p: start over)
+            }
+        }
+        if (taken >= 0) { cur = taken; path[keep++] = cur; continue; }
+        double u = sz_uniform(sp->seed, 256 * P);
+        uint32_t tok = cid[n - 1];
+        for (int i = 0; i < n; i++) {
+            if (u < p[i]) { tok = cid[i]; break; }
+            u -= p[i];
+        }
+        *next = tok;
+        return keep;
+    }
+}
+
 // ---- the loop (engine.rs:2149-2454 with the suffix drafter alone: no neural drafter, so the policy is not consulted and a window
 // is 1 + at most spec_k rows) ---------------------------------------------------------------------------------------------------------
 static double now_ms() {

@@ -60,6 +60,8 @@ struct sz_session {
     int32_t* h_pin;   // [0..8): ids of the pass, [8]: keep of a host-decided commit, [10..12]: error words read back, [13..14]: {kept, next}, [16..24): SzSampleArgs
     sz_sampler samp = {};   // sz_session_set_sampler
     int has_samp = 0;
+    int tree_pass = 0;      // the pass being built / pending is a tree pass (sz_session_verify_tree)
+    float* fork = nullptr;  // [v heads][8][d * d]: recurrent states a tree pass branches off
     int pending_committed;  // the pending pass was already committed on the device (acceptance modes GREEDY / ALL / SAMPLED)
     int device_keep;        // rows the device kept in that pass: known at launch for ALL, read by sz_session_result otherwise (-1: not read yet)
     int inflight;           // a pass was launched and the stream not synchronised since: the id staging buffer may still be read
@@ -86,7 +88,7 @@ static int sz_is_attn(const sz_model_config& c, int l) { return l % c.attn_inter
 
 struct SzSessLayout {
     int64_t r, r2, hc_acc, rope, rn, hdown, mix, u, g, y, d_xin, d_z, d_b, d_a, d_xc, d_beta, d_decay, d_og, S0, S1, conv0, conv1, a_qg, a_k, a_v, a_q, a_gate,
-        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, head_q2, head_sc, head_work, total;
+        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, head_q2, head_sc, head_work, fork, total;
     int64_t moe_bytes, S_bytes, conv_bytes, kv_bytes, head_work_bytes;
     int splits, splits2;
 };
@@ -152,7 +154,8 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
     L->logits = take(4 * M * (int64_t)c.vocab);
     const int64_t nb = ((int64_t)c.vocab + SZ_TK_N - 1) / SZ_TK_N;
     L->tk_tmp = take(8 * M * nb * 64); L->top = take(4 * M * 128);
-    L->ids = take(128);  // the rows' tokens, then (word 16) the sampler block of a sampled pass
+    L->ids = take(512);  // the rows' tokens, then (word 16) the sampler block of a sampled pass, then (word 32) the tables of a tree pass
+    L->fork = take(4 * (int64_t)vh * M * c.ssm_head_dim * c.ssm_head_dim);
     L->res = take(64); L->state = take(64);
     L->routes = take(4 * (int64_t)c.n_layer * M * SZ_MAX_TOPK); L->route_w = take(8 * (int64_t)c.n_layer * M * SZ_MAX_TOPK);
     int64_t moe_bytes = 0;
@@ -312,7 +315,7 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->model.layers = s->layers.data();
     s->ctx = ctx; s->flags = flags; s->want_routes = 0;
     s->h_pin = nullptr;
-    if (cudaHostAlloc((void**)&s->h_pin, 128, cudaHostAllocDefault) != cudaSuccess) { delete s; return sz_fail(SZ_E_CUDA, "cudaHostAlloc of the id staging buffer failed"); }
+    if (cudaHostAlloc((void**)&s->h_pin, 512, cudaHostAllocDefault) != cudaSuccess) { delete s; return sz_fail(SZ_E_CUDA, "cudaHostAlloc of the id staging buffer failed"); }
     {
         const char* e = getenv("SZ_SESSION_GRAPHS");  // A/B switch: 0 = launch every kernel eagerly
         s->use_graphs = !(e && atoi(e) == 0);
@@ -344,6 +347,7 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->logits = (float*)(b + L.logits); s->tk_tmp = (u64*)(b + L.tk_tmp); s->top = (u32*)(b + L.top);
     s->ids = (int32_t*)(b + L.ids); s->res = (int32_t*)(b + L.res); s->state = (int32_t*)(b + L.state); s->routes = (int32_t*)(b + L.routes); s->route_w = (double*)(b + L.route_w);
     s->moe_scratch = b + L.moe; s->moe_scratch_bytes = L.moe_bytes;
+    s->fork = (float*)(b + L.fork);
     s->attn_splits = L.splits; s->attn_splits2 = L.splits2;
     if ((rc = sz_head_describe(m, flags, &s->head))) { delete s; return rc; }
     if (s->head.rows > 0) {
@@ -599,7 +603,8 @@ static int sz_scan_launch(sz_session* s, cudaStream_t st, int l, int m, const Sz
     SZ_CUDA(sz_launch(l >= 0 ? "delta_scan" : "delta_replay", sz_delta_scan_kernel<D, PARTS>, dim3(c.ssm_v_heads, l >= 0 ? 1 : s->n_delta),
                       dim3(D * PARTS), 0, st, true, xc, beta, decay, (const float*)s->d_z, nw, (const float*)(s->S[0] + di * Sl),
                       (const float*)(s->S[1] + di * Sl), s->S[0] + di * Sl, s->S[1] + di * Sl, (const int32_t*)s->state, (const int32_t*)s->res,
-                      (int)c.ssm_k_heads, (int)c.ssm_v_heads, m, c.eps, l >= 0 ? s->d_og : (float*)nullptr, pp));
+                      (int)c.ssm_k_heads, (int)c.ssm_v_heads, m, c.eps, l >= 0 ? s->d_og : (float*)nullptr, pp,
+                      (const SzTree*)(s->tree_pass ? s->ids + 32 : nullptr), s->fork));
     return SZ_OK;
 }
 
@@ -651,7 +656,8 @@ template <int EPL>
 static int sz_attn_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m) {
     const sz_model_config& c = s->model.cfg;
     SZ_CUDA(sz_launch("attention", sz_attn_kernel<EPL>, dim3(c.n_head, m, s->attn_splits), dim3(256), 0, st, true, (const float*)s->a_q, kc, vc,
-                      (int)c.n_head, (int)c.n_kv_head, s->ctx, (const int32_t*)s->state, (s->flags & SZ_KV_Q8) ? 1 : 0, s->attn_splits, s->a_part));
+                      (int)c.n_head, (int)c.n_kv_head, s->ctx, (const int32_t*)s->state, (s->flags & SZ_KV_Q8) ? 1 : 0, s->attn_splits, s->a_part,
+                      (const SzTree*)(s->tree_pass ? s->ids + 32 : nullptr)));
     return SZ_OK;
 }
 
@@ -667,7 +673,8 @@ static int sz_attn2_go(sz_session* s, cudaStream_t st, const u8* kc, const u8* v
     if (smem + 2048 <= 113 * 1024 && 2 * splits <= (s->ctx + 255) / 256) splits *= 2;
     *splits_used = splits;
     SZ_CUDA(sz_launch("attention_grouped", sz_attn2_kernel<HD, NQT>, dim3(c.n_kv_head, splits), dim3(256), smem, st, true, (const float*)s->a_q,
-                      kc, vc, (int)c.n_head, (int)c.n_kv_head, m, s->ctx, (const int32_t*)s->state, splits, s->a_part, (u32*)(s->state + 2)));
+                      kc, vc, (int)c.n_head, (int)c.n_kv_head, m, s->ctx, (const int32_t*)s->state, splits, s->a_part, (u32*)(s->state + 2),
+                      (const SzTree*)(s->tree_pass ? s->ids + 32 : nullptr)));
     return SZ_OK;
 }
 
@@ -699,7 +706,8 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     if (rc) return rc;
     SZ_CUDA(sz_launch("attn_prep", sz_attn_prep_kernel, dim3(nh + 2 * nkv, m), dim3(128), 0, st, true, (const float*)s->a_qg, (const float*)s->a_k,
                       (const float*)s->a_v, (const float*)L.attn_q_norm.data, (const float*)L.attn_k_norm.data, nh, nkv, hd, s->ctx, c.eps,
-                      (const int32_t*)s->state, (int)c.rope_dims, (const double*)s->rope_den, q8, kc, vc, s->a_q, s->a_gate));
+                      (const int32_t*)s->state, (int)c.rope_dims, (const double*)s->rope_den, q8, kc, vc, s->a_q, s->a_gate,
+                      (const SzTree*)(s->tree_pass ? s->ids + 32 : nullptr)));
     // the grouped tensor-core kernel serves the packed int8 cache with up to 64 queries a KV head; the simple kernel everything else
     static const bool generic_only = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;
     const bool grouped = q8 && !generic_only && (nh / nkv) * m <= 64;
@@ -770,7 +778,12 @@ static int sz_commit_device(sz_session* s, cudaStream_t st, int m) {
         const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd;
         SZ_CUDA(sz_launch("conv_commit", sz_conv_commit_kernel, dim3(c.conv_k - 1, s->n_delta), dim3(256), 0, st, true, (const float*)s->conv[0],
                           (const float*)s->conv[1], (const int32_t*)s->state, (const int32_t*)s->res, (const float*)s->d_xin, (int)ch, (int)c.conv_k,
-                          s->conv[0], s->conv[1]));
+                          s->conv[0], s->conv[1], s->tree_pass));
+    }
+    if (s->tree_pass && s->n_attn > 0) {   // the kept rows' keys and values from their rows' slots to their depths' slots
+        const int hb = (s->flags & SZ_KV_Q8) ? (c.head_dim + (((c.head_dim >> 5) * 2 + 15) & ~15)) : 4 * c.head_dim;
+        SZ_CUDA(sz_launch("kv_compact", sz_kv_compact_kernel, dim3(c.n_kv_head, s->n_attn, 2), dim3(128), 0, st, true, s->kc, s->vc, (const int32_t*)s->state,
+                          (const int32_t*)s->res, s->ctx, (int)c.n_kv_head, hb));
     }
     SZ_CUDA(sz_launch("state_update", sz_state_update_kernel, dim3(1), dim3(32), 0, st, true, s->state, (const int32_t*)s->res));
     return SZ_OK;
@@ -784,6 +797,10 @@ static int sz_pass(sz_session* s, cudaStream_t st, int m, int accept_mode, int e
         SZ_CUDA(sz_launch("accept_sampled", sz_accept_sampled_kernel, dim3(1), dim3(32 * SZ_MAX_VERIFY), 0, st, true, (const u32*)s->top,
                           (const int32_t*)s->ids, m, eog_token, (const SzSampleArgs*)(s->ids + 16), s->res));
         if ((rc = sz_commit_device(s, st, m))) return rc;
+    } else if (accept_mode != SZ_ACCEPT_NONE && s->tree_pass) {
+        SZ_CUDA(sz_launch("accept_tree", sz_accept_tree_kernel, dim3(1), dim3(32), 0, st, true, (const u32*)s->top, (const int32_t*)s->ids,
+                          (const SzTree*)(s->ids + 32), m, eog_token, s->res));
+        if ((rc = sz_commit_device(s, st, m))) return rc;
     } else if (accept_mode != SZ_ACCEPT_NONE) {
         SZ_CUDA(sz_launch("accept", sz_accept_greedy_kernel, dim3(1), dim3(32), 0, st, true, (const u32*)s->top, (const int32_t*)s->ids, m, eog_token,
                           accept_mode == SZ_ACCEPT_ALL ? 1 : 0, head ? 1 : 0, s->res));
@@ -796,7 +813,51 @@ static int sz_verify_impl(sz_session* s, const int32_t* ids, int m, int accept_m
 
 extern "C" int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode, int eog_token, int want_head, uint64_t stream) {
     if (accept_mode < SZ_ACCEPT_NONE || accept_mode > SZ_ACCEPT_ALL) return sz_fail(SZ_E_ARG, "accept_mode %d (sampled acceptance: sz_session_verify_sampled)", accept_mode);
+    if (s && !s->last_m) s->tree_pass = 0;
     return sz_verify_impl(s, ids, m, accept_mode, eog_token, want_head, stream);
+}
+
+// A pass over a draft tree: row 0 is the root (the pass's own token), row j > 0 a drafted token whose parent is row parents[j] < j.
+// Row j attends to the committed positions, its ancestors and itself, sits at position committed + depth, and continues the
+// recurrent state of its parent.
+extern "C" int sz_session_verify_tree(sz_session* s, const int32_t* ids, const int32_t* parents, int m, int accept_mode, int eog_token, uint64_t stream) {
+    if (!s || !ids || !parents) return sz_fail(SZ_E_ARG, "sz_session_verify_tree: null argument");
+    if (accept_mode != SZ_ACCEPT_NONE && accept_mode != SZ_ACCEPT_GREEDY) return sz_fail(SZ_E_ARG, "a tree pass is accepted greedily on the device or by the caller (accept_mode %d)", accept_mode);
+    if (m < 1 || m > SZ_MAX_VERIFY) return sz_fail(SZ_E_ARG, "a pass has 1..%d rows, got %d", SZ_MAX_VERIFY, m);
+    if (s->last_m) return sz_fail(SZ_E_ARG, "the previous pass was not committed");
+    if (parents[0] != -1) return sz_fail(SZ_E_ARG, "row 0 of a tree pass is the root: parents[0] must be -1");
+    if (getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0) return sz_fail(SZ_E_ARG, "tree passes run on the fused DeltaNet front end only (SZ_GENERIC_KERNELS is set)");
+    SzTree t = {};
+    t.mask[0] = 1u;
+    for (int j = 1; j < m; j++) {
+        const int p = parents[j];
+        if (p < 0 || p >= j) return sz_fail(SZ_E_ARG, "parents[%d] = %d: a row's parent comes before it", j, p);
+        t.parents[j] = p;
+        t.depth[j] = t.depth[p] + 1;
+        t.mask[j] = t.mask[p] | (1u << j);
+        if (p != j - 1) t.save |= 1u << p;
+    }
+    t.parents[0] = -1;
+    if (s->inflight) { SZ_CUDA(cudaStreamSynchronize((cudaStream_t)stream)); s->inflight = 0; }
+    memcpy(s->h_pin + 32, &t, sizeof(t));
+    s->tree_pass = 1;
+    const int rc = sz_verify_impl(s, ids, m, accept_mode, eog_token, 1, stream);
+    if (rc) s->tree_pass = 0;
+    return rc;
+}
+
+// After sz_session_result of a tree pass that the device accepted: the kept rows, root first.
+extern "C" int sz_session_tree_path(sz_session* s, int32_t* path, int* n, uint64_t stream) {
+    if (!s || !path || !n) return sz_fail(SZ_E_ARG, "sz_session_tree_path: null argument");
+    if (!s->last_m || !s->tree_pass || !s->pending_committed) return sz_fail(SZ_E_ARG, "sz_session_tree_path: no tree pass accepted on the device is pending");
+    cudaStream_t st = (cudaStream_t)stream;
+    SZ_CUDA(cudaMemcpyAsync(s->h_pin + 96, s->res, 64, cudaMemcpyDeviceToHost, st));
+    SZ_CUDA(cudaStreamSynchronize(st));
+    s->inflight = 0;
+    *n = s->h_pin[96];
+    if (*n < 1 || *n > s->last_m) return sz_fail(SZ_E_DEVICE, "the device reports a path of %d rows", *n);
+    for (int i = 0; i < *n; i++) path[i] = s->h_pin[98 + i];
+    return SZ_OK;
 }
 
 extern "C" int sz_session_set_sampler(sz_session* s, const sz_sampler* sp) {
@@ -809,6 +870,7 @@ extern "C" int sz_session_set_sampler(sz_session* s, const sz_sampler* sp) {
 
 extern "C" int sz_session_verify_sampled(sz_session* s, const int32_t* ids, int m, uint64_t pos, int eog_token, uint64_t stream) {
     if (!s) return sz_fail(SZ_E_ARG, "null session or ids");
+    if (!s->last_m) s->tree_pass = 0;
     if (!s->has_samp) return sz_fail(SZ_E_ARG, "sz_session_verify_sampled: no sampler set (sz_session_set_sampler)");
     if (s->inflight) { SZ_CUDA(cudaStreamSynchronize((cudaStream_t)stream)); s->inflight = 0; }  // the staging block is free again
     SzSampleArgs a = {s->samp.temperature, s->samp.top_k, s->samp.top_p, s->samp.min_p, s->samp.seed, pos};
@@ -826,10 +888,11 @@ static int sz_verify_impl(sz_session* s, const int32_t* ids, int m, int accept_m
     cudaStream_t st = (cudaStream_t)stream;
     if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
     memcpy(s->h_pin, ids, (size_t)m * 4);
-    const size_t staged = accept_mode == SZ_ACCEPT_SAMPLED ? 96 : (size_t)m * 4;  // a sampled pass carries its sampler block along
+    // a sampled pass carries its sampler block along, a tree pass its tables
+    const size_t staged = s->tree_pass ? 128 + sizeof(SzTree) : (accept_mode == SZ_ACCEPT_SAMPLED ? 96 : (size_t)m * 4);
     int rc = SZ_OK;
     // one graph per (rows, head, acceptance, eog): every launch-time value a kernel needs lives in device memory
-    const int key = m | (want_head ? 16 : 0) | (accept_mode << 5) | ((eog_token & 0xfffff) << 8);
+    const int key = m | (want_head ? 16 : 0) | (accept_mode << 5) | (s->tree_pass ? 128 : 0) | ((eog_token & 0xfffff) << 8);
     bool traced = sz_trace_active();
     const bool capturable = st != (cudaStream_t)0 && st != cudaStreamLegacy && st != cudaStreamPerThread;  // the default stream cannot record
     if (s->use_graphs && capturable && !traced && !s->want_routes) {
@@ -922,6 +985,7 @@ extern "C" int sz_session_commit(sz_session* s, int keep, uint64_t stream) {
     const int m = s->last_m;
     if (keep < 0 || keep > m) return sz_fail(SZ_E_ARG, "keep = %d of a pass of %d rows", keep, m);
     cudaStream_t st = (cudaStream_t)stream;
+    if (s->tree_pass && !s->pending_committed) return sz_fail(SZ_E_ARG, "a tree pass is committed by its kept path: sz_session_commit_path");
     if (s->pending_committed) {
         // the device already advanced its state by the rows IT kept: the host's bookkeeping must follow that number, not the caller's
         if (s->device_keep < 0) return sz_fail(SZ_E_ARG, "the device decided this pass: read sz_session_result before sz_session_commit");
@@ -935,7 +999,29 @@ extern "C" int sz_session_commit(sz_session* s, int keep, uint64_t stream) {
     }
     s->last_m = 0;
     s->pending_committed = 0;
+    s->tree_pass = 0;
     if (keep > 0) { s->cur ^= 1; s->len += keep; }
+    return SZ_OK;
+}
+
+// The caller's decision for a tree pass: the kept rows are `path` (root first, each the child of the one before).
+extern "C" int sz_session_commit_path(sz_session* s, const int32_t* path, int n, uint64_t stream) {
+    if (!s || !s->last_m || !s->tree_pass) return sz_fail(SZ_E_ARG, "no tree pass to commit");
+    if (s->pending_committed) return sz_fail(SZ_E_ARG, "the device accepted this pass: sz_session_commit with the row count it kept");
+    if (!path || n < 1 || n > s->last_m || path[0] != 0) return sz_fail(SZ_E_ARG, "a kept path starts at the root and has 1..%d rows", s->last_m);
+    const SzTree* t = (const SzTree*)(s->h_pin + 32);
+    for (int i = 1; i < n; i++)
+        if (path[i] <= 0 || path[i] >= s->last_m || t->parents[path[i]] != path[i - 1]) return sz_fail(SZ_E_ARG, "path[%d] = %d is not a child of row %d", i, path[i], path[i - 1]);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
+    s->h_pin[96] = n; s->h_pin[97] = 0;
+    for (int i = 0; i < n; i++) s->h_pin[98 + i] = path[i];
+    SZ_CUDA(cudaMemcpyAsync(s->res, s->h_pin + 96, (size_t)(2 + n) * 4, cudaMemcpyHostToDevice, st));
+    const int rc = sz_commit_device(s, st, s->last_m);
+    if (rc) return rc;
+    s->last_m = 0;
+    s->tree_pass = 0;
+    s->cur ^= 1; s->len += n;
     return SZ_OK;
 }
 
@@ -1057,11 +1143,13 @@ const SzKernelEntry kKernels[] = {
     {"sz_hc_norm_kernel", (const void*)sz_hc_norm_kernel, 8, {SZ_P_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_F32, SZ_P_PTR}},
     {"sz_hc_mix_kernel", (const void*)sz_hc_mix_kernel, 5, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
     {"sz_delta_prep_kernel", (const void*)sz_delta_prep_kernel, 16, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_PTR, SZ_P_PTR}},
-    {"sz_conv_commit_kernel", (const void*)sz_conv_commit_kernel, 9, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_PTR}},
+    {"sz_conv_commit_kernel", (const void*)sz_conv_commit_kernel, 10, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_PTR, SZ_P_I32}},
     {"sz_state_update_kernel", (const void*)sz_state_update_kernel, 2, {SZ_P_PTR, SZ_P_CONST_PTR}},
-    {"sz_attn_prep_kernel", (const void*)sz_attn_prep_kernel, 18, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_F32, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_PTR, SZ_P_PTR, SZ_P_PTR, SZ_P_PTR}},
+    {"sz_attn_prep_kernel", (const void*)sz_attn_prep_kernel, 19, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_F32, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_PTR, SZ_P_PTR, SZ_P_PTR, SZ_P_PTR, SZ_P_CONST_PTR}},
     {"sz_attn_merge_kernel", (const void*)sz_attn_merge_kernel, 6, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
     {"sz_accept_greedy_kernel", (const void*)sz_accept_greedy_kernel, 7, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
+    {"sz_accept_tree_kernel", (const void*)sz_accept_tree_kernel, 6, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
+    {"sz_kv_compact_kernel", (const void*)sz_kv_compact_kernel, 7, {SZ_P_PTR, SZ_P_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32}},
     {"sz_accept_sampled_kernel", (const void*)sz_accept_sampled_kernel, 6, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_CONST_PTR, SZ_P_PTR}},
     {"sz_topk_slices_kernel", (const void*)sz_topk_slices_kernel, 6, {SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_CONST_PTR}},
     {"sz_topk_merge_kernel", (const void*)sz_topk_merge_kernel, 3, {SZ_P_CONST_PTR, SZ_P_I32, SZ_P_PTR}},

@@ -7,7 +7,27 @@
 #include "sz_dense.cuh"
 #include "sz_topk.cuh"
 
+// A draft tree's tables, as the kernels read them (device memory, written from the pass's staging block).  Row 0 is the root (the
+// pass's own token); parents[j] < j.  No counterpart in the reference, whose verify pass is a chain
+// (crates/shadowzero-cuda/src/session.rs:7698-7723).
+struct SzTree {
+    int32_t parents[SZ_MAX_VERIFY];   // parent row, -1 for the root
+    int32_t depth[SZ_MAX_VERIFY];     // distance from the root: the row's position is committed + depth
+    u32 mask[SZ_MAX_VERIFY];          // bit a: row a is the row itself or one of its ancestors (what it may attend to among the pass's rows)
+    u32 save;                         // bit j: a later row branches off row j, so the recurrent state after it is kept
+    u32 pad[7];
+};
+static_assert(sizeof(SzTree) == 128, "the tree tables are 32 words of the staging block");
+
 #ifdef __CUDACC__
+
+// the row `dist` steps up the tree from row j; -1, -2, .. are the committed rows before the pass (most recent first)
+__device__ __forceinline__ int sz_tree_up(const SzTree* tr, int j, int dist) {
+    if (!tr) return j - dist;
+    int a = j;
+    for (int s = 0; s < dist; s++) a = a >= 0 ? tr->parents[a] : a - 1;
+    return a;
+}
 
 __device__ __forceinline__ double sz_block_sum(double v, double* red) {
     v = sz_warp_sum(v);
@@ -451,7 +471,7 @@ sz_delta_prep_kernel(const float* __restrict__ xin, const float* __restrict__ co
 __global__ void __launch_bounds__(256)
 sz_conv_commit_kernel(const float* __restrict__ conv0, const float* __restrict__ conv1, const int32_t* __restrict__ state,
                       const int32_t* __restrict__ res, const float* __restrict__ xin_all, int ch, int k, float* __restrict__ out0,
-                      float* __restrict__ out1) {
+                      float* __restrict__ out1, int tree) {
     sz_pdl_wait();
     sz_pdl_trigger();
     const int keep = res[0];
@@ -462,8 +482,9 @@ sz_conv_commit_kernel(const float* __restrict__ conv0, const float* __restrict__
     const float* conv = (cur ? conv1 : conv0) + di * cl;
     float* dst = (cur ? out0 : out1) + di * cl;   // the other buffer
     const float* xin = xin_all + (size_t)di * SZ_MAX_VERIFY * ch;
-    const int tau = keep - (k - 1) + t;    // index into the pass rows, negative: into the old state
-    const float* src = tau >= 0 ? xin + (size_t)tau * ch : conv + (size_t)((k - 1) + tau) * ch;
+    const int tau = keep - (k - 1) + t;    // index into the kept rows, negative: into the old state
+    // (the kept rows of a tree pass are the path res[2 ..]; of a chain, rows 0 .. keep - 1)
+    const float* src = tau >= 0 ? xin + (size_t)(tree ? res[2 + tau] : tau) * ch : conv + (size_t)((k - 1) + tau) * ch;
     for (int i = threadIdx.x; i < ch; i += 256) dst[(size_t)t * ch + i] = src[i];
 }
 
@@ -506,7 +527,8 @@ __global__ void __launch_bounds__(D * PARTS)
 sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__ beta_all, const float* __restrict__ decay_all,
                      const float* __restrict__ z, const float* __restrict__ norm_w, const float* __restrict__ S0, const float* __restrict__ S1,
                      float* __restrict__ O0, float* __restrict__ O1, const int32_t* __restrict__ state, const int32_t* __restrict__ res, int kh,
-                     int vh, int m, float eps, float* __restrict__ og, const SzDeltaPrep pp) {
+                     int vh, int m, float eps, float* __restrict__ og, const SzDeltaPrep pp, const SzTree* __restrict__ tr,
+                     float* __restrict__ fork) {
     constexpr int NI = D / PARTS;
     constexpr int RUN = NI < 16 ? NI : 16;  // sums run in f32 over 16 terms and the runs are added in f64, as the reference's exact
                                             // GPU scan does (kernels/forward.cu:991-1013): a conversion to f64 per term would
@@ -532,10 +554,14 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
     }
     sz_pdl_wait();
     sz_pdl_trigger();
+    // A tree pass (tr != null): a row continues from the state after its PARENT.  Rows come parents first, so the state after a row
+    // that a later row branches off (tr->save) is kept in `fork` ([value head][row][D * D]) and fetched when a row's parent is not the
+    // row just before it.  The state the pass leaves in the other buffer is then that of no one path: the commit of a tree pass
+    // always replays, along the kept path res[2 ..] (row indices), where a chain's kept rows are simply 0 .. res[0] - 1.
     int rows = m;
     if (!og) {
         rows = res[0];
-        if (rows <= 0 || rows >= m) return;
+        if (rows <= 0 || (!tr && rows >= m)) return;
     }
     const int cur = state[1];
     const float* S_in = (cur ? S1 : S0) + di * Sl;
@@ -558,7 +584,7 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
             const int chn = part3 == 0 ? kx * D + i : (part3 == 1 ? kd + kx * D + i : 2 * kd + hd * D + i);
             double acc = (double)pp.cw[chn * k + (k - 1)] * (double)pp.xin[(size_t)j * ch + chn];
             for (int t = 0; t < k - 1; t++) {
-                const int tau = j - (k - 1) + t;  // row of this pass, or (negative) a row of the carried state
+                const int tau = sz_tree_up(tr, j, (k - 1) - t);  // the row (k - 1) - t steps back: of this pass, or (negative) of the carried state
                 const float prev = tau >= 0 ? pp.xin[(size_t)tau * ch + chn] : conv[(size_t)((k - 1) + tau) * ch + chn];
                 acc += (double)pp.cw[chn * k + t] * (double)prev;
             }
@@ -598,7 +624,18 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
             else if (hd < kh) pp.xc[(size_t)j * ch + part3 * kd + kx * D + i] = pbuf[j][part3][i];
         }
     }
-    for (int j = 0; j < rows; j++) {
+    float* fk = fork ? fork + ((size_t)di * vh + hd) * SZ_MAX_VERIFY * D * D : nullptr;
+    int prev_row = -1;
+    for (int jj = 0; jj < rows; jj++) {
+        const int j = (!og && tr) ? res[2 + jj] : jj;   // replay of a tree pass: the kept path
+        if (tr && og) {
+            const int par = tr->parents[j];
+            if (par != prev_row && par >= 0) {          // another branch: back to the state after the parent
+#pragma unroll
+                for (int i = 0; i < NI; i++) S[i] = fk[((size_t)par * D + pt * NI + i) * D + col];
+            }
+        }
+        prev_row = j;
         const float* x = xc + (size_t)j * ch;
         __syncthreads();
         float vj, dc, bt;
@@ -648,6 +685,10 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
 #pragma unroll
                 for (int p = 0; p < PARTS; p++) ot += part[p][col];
                 ofs[j][col] = (float)ot;
+            }
+            if (tr && ((tr->save >> j) & 1u)) {
+#pragma unroll
+                for (int i = 0; i < NI; i++) fk[((size_t)j * D + pt * NI + i) * D + col] = S[i];
             }
         }
     }
@@ -707,13 +748,15 @@ __device__ __forceinline__ void sz_kv_store(const float* src, int hd, int q8, u8
 __global__ void __launch_bounds__(128)
 sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, const float* __restrict__ vv, const float* __restrict__ wq,
                     const float* __restrict__ wk, int nh, int nkv, int hd, int ctx, float eps, const int32_t* __restrict__ state, int rope_dims,
-                    const double* __restrict__ rope_den, int q8, u8* __restrict__ kc, u8* __restrict__ vc, float* __restrict__ q, float* __restrict__ gate) {
+                    const double* __restrict__ rope_den, int q8, u8* __restrict__ kc, u8* __restrict__ vc, float* __restrict__ q, float* __restrict__ gate,
+                    const SzTree* __restrict__ tr) {
     __shared__ float tmp[512];
     __shared__ double red[8];
     sz_pdl_wait();
     sz_pdl_trigger();
     const int b = blockIdx.x, j = blockIdx.y;
-    const int pos = state[0] + j;
+    const int pos = state[0] + j;                              // the row's cache slot
+    const int rpos = state[0] + (tr ? tr->depth[j] : j);      // its position in the sequence (a tree: rows of one depth share it)
     const size_t hbytes = q8 ? (size_t)sz_kv_head_bytes(hd) : (size_t)hd * 4;  // the cache is [kv head][position][head bytes]
     if (b >= nh + nkv) {  // V head: raw into the cache
         const int h = b - nh - nkv;
@@ -734,7 +777,7 @@ sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, 
     for (int i = threadIdx.x; i < half; i += 128) {  // forward.rs:290-299
         // angle = pos / theta^(2i / rope_dims) in f64 (the table holds the denominators), reduced to [-pi, pi] in f64; sine and cosine
         // of the reduced angle in f32
-        const double f = (double)pos / __ldg(rope_den + i);
+        const double f = (double)rpos / __ldg(rope_den + i);
         const double kq = rint(f * 0.15915494309189535);
         double rd = fma(-kq, 6.283185307179586, f);
         rd = fma(-kq, 2.4492935982947064e-16, rd);
@@ -763,7 +806,7 @@ sz_attn_prep_kernel(const float* __restrict__ qg, const float* __restrict__ kk, 
 template <int EPL>  // elements per lane = hd / 32
 __global__ void __launch_bounds__(256)
 sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8* __restrict__ vc, int nh, int nkv, int ctx,
-               const int32_t* __restrict__ state, int q8, int splits, float* __restrict__ part) {
+               const int32_t* __restrict__ state, int q8, int splits, float* __restrict__ part, const SzTree* __restrict__ tr) {
     constexpr int HD = EPL * 32;
     __shared__ float sm_m[8], sm_s[8];
     __shared__ float sm_acc[8][HD];
@@ -772,7 +815,9 @@ sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8*
     const int h = blockIdx.x, j = blockIdx.y, sp = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = h / (nh / nkv);
-    const int n = state[0] + j + 1;
+    const int pos0 = state[0];
+    const u32 mk = tr ? tr->mask[j] : (2u << j) - 1u;          // which of the pass's rows this row sees (a chain: rows 0 .. j)
+    const int n = pos0 + 32 - __clz(mk);                        // one past the last slot it may see
     const int per = (n + splits - 1) / splits;
     const int t0 = sp * per, t1 = min(n, t0 + per);
     const int hb = sz_kv_head_bytes(HD);
@@ -785,6 +830,7 @@ sz_attn_kernel(const float* __restrict__ q, const u8* __restrict__ kc, const u8*
 #pragma unroll
     for (int e = 0; e < EPL; e++) acc[e] = 0.f;
     for (int t = t0 + warp; t < t1; t += 8) {
+        if (t >= pos0 && !((mk >> (t - pos0)) & 1u)) continue;  // a row of another branch
         const u8* kb = kc + (size_t)t * rowb + headb;
         const u8* vb = vc + (size_t)t * rowb + headb;
         float kvv[EPL], vvv[EPL];
@@ -853,7 +899,7 @@ struct SzAttn2 {
 template <int HD, int NQT>
 __global__ void __launch_bounds__(256)
 sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const u8* __restrict__ vc, int nh, int nkv, int m, int ctx,
-                const int32_t* __restrict__ state, int splits, float* __restrict__ part, u32* __restrict__ err) {
+                const int32_t* __restrict__ state, int splits, float* __restrict__ part, u32* __restrict__ err, const SzTree* __restrict__ tr) {
     using A = SzAttn2<HD>;
     extern __shared__ __align__(128) u8 smem[];
     u64* bars = (u64*)smem;
@@ -984,11 +1030,25 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
         {
             const int qv = threadIdx.x >> 2, sub = threadIdx.x & 3;
             if (qv < NQT * 16) {
-                const int lim = qv < QV ? min(pos0 + qv / G + 1, t1) - tbase : 0;  // positions of the chunk this query may see
+                // positions of the chunk this query may see: every committed one, and among the pass's own rows those of its mask
+                // (a chain: rows 0 .. j; a tree: its ancestors and itself).  vis: bit i = position sub * 16 + i of the chunk.
+                u32 vis = 0;
+                if (qv < QV) {
+                    const int jr = qv / G;
+                    const u32 mk = tr ? tr->mask[jr] : (2u << jr) - 1u;
+                    const int c0 = tbase + sub * 16;                  // first position of this thread's 16
+                    const int ncom = min(max(min(pos0, t1) - c0, 0), 16);   // committed positions among them
+                    vis = ncom >= 16 ? 0xffffu : ((1u << ncom) - 1u);
+                    const int sh = c0 - pos0;                         // the pass's row that position c0 is, when >= 0
+                    const u32 own = sh >= 0 ? (sh < 32 ? mk >> sh : 0u) : (sh > -32 ? mk << (-sh) : 0u);
+                    vis |= own & 0xffffu;
+                    const int room = t1 - c0;                          // positions past the block's range are not there
+                    vis &= room >= 16 ? 0xffffu : (room > 0 ? (1u << room) - 1u : 0u);
+                }
                 float* row = S + (size_t)qv * A::SST + sub * 16;
                 float mx = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < 16; i++) if (sub * 16 + i < lim) mx = fmaxf(mx, row[i]);
+                for (int i = 0; i < 16; i++) if ((vis >> i) & 1u) mx = fmaxf(mx, row[i]);
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
                 const float mo = rmax[qv];
@@ -996,7 +1056,7 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
                 float sum = 0.f;
 #pragma unroll
                 for (int i = 0; i < 16; i++) {
-                    const float p = (sub * 16 + i < lim) ? __expf(row[i] - mn) : 0.f;
+                    const float p = ((vis >> i) & 1u) ? __expf(row[i] - mn) : 0.f;
                     row[i] = p;
                     sum += p;
                 }
@@ -1163,6 +1223,53 @@ __global__ void sz_accept_greedy_kernel(const u32* __restrict__ top, const int32
         }
     res[0] = keep;
     res[1] = has_head ? (int)top[(size_t)(keep - 1) * 128 + 64] : -1;
+}
+
+// ---- greedy acceptance over a draft tree (the chain's rule, engine.rs:2377-2408, applied down the tree; no counterpart in the
+// reference).  From the root: the target's best token after the current row must be the token of one of its children; that child is
+// kept and becomes the current row (lowest row index among equal children); a drafted end-of-generation token is never accepted.
+// res[0] = rows kept (the path's length, root included), res[1] = the token after the path, res[2 ..] = the path's row indices.
+__global__ void sz_accept_tree_kernel(const u32* __restrict__ top, const int32_t* __restrict__ ids, const SzTree* __restrict__ tr, int m, int eog,
+                                      int32_t* __restrict__ res) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    int cur = 0, keep = 1;
+    res[2] = 0;
+    for (;;) {
+        const int want = (int)top[(size_t)cur * 128 + 64];
+        int next = -1;
+        for (int c = cur + 1; c < m; c++)
+            if (tr->parents[c] == cur && ids[c] == want && want != eog) { next = c; break; }
+        if (next < 0) break;
+        cur = next;
+        res[2 + keep] = cur;
+        keep++;
+    }
+    res[0] = keep;
+    res[1] = (int)top[(size_t)cur * 128 + 64];
+}
+
+// The kept rows of a tree pass wrote their keys and values at slot committed + row; the sequence wants them at committed + depth.
+// Path entry d (depth d) moves from slot committed + path[d] to committed + d; path[d] >= d and the path ascends, so moving in
+// order of d never overwrites a slot that is still to be read.  grid (kv heads, attention layers, 2: keys / values), block 128.
+__global__ void __launch_bounds__(128)
+sz_kv_compact_kernel(u8* __restrict__ kc, u8* __restrict__ vc, const int32_t* __restrict__ state, const int32_t* __restrict__ res, int ctx, int nkv,
+                     int head_bytes) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int keep = res[0];
+    u8* base = (blockIdx.z ? vc : kc) + ((size_t)blockIdx.y * nkv + blockIdx.x) * (size_t)ctx * head_bytes;
+    const int pos0 = state[0];
+    for (int d = 1; d < keep; d++) {
+        const int from = res[2 + d];
+        if (from != d) {
+            const u32* src = (const u32*)(base + (size_t)(pos0 + from) * head_bytes);
+            u32* dst = (u32*)(base + (size_t)(pos0 + d) * head_bytes);
+            for (int i = threadIdx.x; i < head_bytes / 4; i += 128) dst[i] = src[i];
+        }
+        __syncthreads();
+    }
 }
 
 // ---- sampled acceptance on the device: Sampler::sample_top (crates/shadowzero-serve/src/sampler.rs:159-210) for every row of the

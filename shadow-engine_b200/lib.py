@@ -86,6 +86,9 @@ SYMBOLS = {
     "sz_session_verify": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64]),
     "sz_session_set_sampler": (C.c_int, [C.c_void_p, C.c_void_p]),
     "sz_session_verify_sampled": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64, C.c_int, C.c_uint64]),
+    "sz_session_verify_tree": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_uint64]),
+    "sz_session_tree_path": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.c_uint64]),
+    "sz_session_commit_path": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64]),
     "sz_session_result": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_void_p, C.c_void_p, C.c_uint64]),
     "sz_session_commit": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
     "sz_session_fill_synthetic": (C.c_int, [C.c_void_p, C.c_int, C.c_uint32, C.c_uint64]),
@@ -116,6 +119,8 @@ SYMBOLS = {
     "sz_policy_observe_chain": (None, [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double]),
     "sz_uniform": (C.c_double, [C.c_uint64, C.c_uint64]),
     "sz_sample_top": (C.c_uint32, [C.c_void_p, C.POINTER(C.c_uint32), C.c_uint64]),
+    "sz_tree_accept_sampled": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_uint64, C.c_int, C.c_void_p,
+                                         C.POINTER(C.c_uint32)]),
     "sz_generate": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_void_p, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.c_int,
                               C.c_void_p, C.c_uint64]),
     "sz_gen_begin": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]),

@@ -336,6 +336,22 @@ class Session:
         szlib.check(self.lib.sz_session_verify(self.h, a, len(ids), accept, eog, 1 if head else 0, self.stream))
         self._m = len(ids)
 
+    def verify_tree(self, ids, parents, accept=0, eog=-1):
+        """A pass over a draft tree: ids[0] the root, ids[j] a drafted token under row parents[j] (parents[0] = -1)."""
+        a = (C.c_int32 * len(ids))(*[int(t) for t in ids])
+        p = (C.c_int32 * len(ids))(*[int(t) for t in parents])
+        szlib.check(self.lib.sz_session_verify_tree(self.h, a, p, len(ids), accept, eog, self.stream))
+        self._m = len(ids)
+
+    def tree_path(self):
+        path, n = (C.c_int32 * szlib.MAX_VERIFY)(), C.c_int()
+        szlib.check(self.lib.sz_session_tree_path(self.h, path, C.byref(n), self.stream))
+        return list(path[:n.value])
+
+    def commit_path(self, path):
+        a = (C.c_int32 * len(path))(*[int(t) for t in path])
+        szlib.check(self.lib.sz_session_commit_path(self.h, a, len(path), self.stream))
+
     def set_sampler(self, sampler):
         szlib.check(self.lib.sz_session_set_sampler(self.h, C.byref(sampler)))
 

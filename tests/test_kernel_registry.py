@@ -107,7 +107,7 @@ def test_a_launch_by_name_does_the_kernels_work():
     szlib.check(L.sz_kernel_launch(b"sz_hc_mix_kernel", g, b, 0, st, _args((szlib.P_PTR, mix.data_ptr()), (szlib.P_PTR, rn.data_ptr()), (szlib.P_I32, H),
                                                                           (szlib.P_I32, Cs), (szlib.P_PTR, u.data_ptr())), 5))
     torch.cuda.synchronize()
-    want = torch.zeros(m, H, device="cuda")
-    for s in range(Cs):                                   # f32, stream order, then the division (forward.rs:805-811)
-        want = want + mix[:, s] * rn[:, s]
-    assert torch.equal(u, want / Cs)
+    want = torch.zeros(m, H, device="cuda", dtype=torch.float64)
+    for s in range(Cs):                                   # stream order, then the division (forward.rs:805-811)
+        want = want + mix[:, s].double() * rn[:, s].double()
+    assert torch.allclose(u, (want / Cs).float(), rtol=1e-6, atol=1e-7)   # (the kernel's f32 multiply-adds round once a term)
