@@ -8,6 +8,8 @@ metric is accepted tokens per second (every emitted token: accepted drafts and t
 torchrun) the experts of every layer are sharded over the N ranks (expert parallelism); one sequence, so scaling is "strong".
 
 `--workload c2-moe`: benchmark config 2, the verify-step MoE microbench (one MoE sublayer pass over K+1 = 4 rows per step).
+`--workload c4-tree`: benchmark config 4's mechanism on the config-3 model: one verify pass over a draft tree (8 rows), greedy
+acceptance on the device and rejection sampling on the host; reports us per verify and the accepted length.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c3|c2-moe] [--impl reference]
 
@@ -150,7 +152,8 @@ def c3_config(args, cfg, ctx, bytes_all=None):
             "requests": "256-token prompts (a token cycle of the model repeated, 10%% random substitutions), %d tokens decoded each; "
                         "prompt passes and the cache fill are outside the timed region" % args.request_tokens,
             "acceptance_knobs": {"cycle_alpha": args.alpha, "cycle_beta": args.beta, "prompt_substitution": 0.1},
-            "parallelism": "ep%d" % world if world > 1 else "single", "exchange": args.exchange if world > 1 else None,
+            "parallelism": ("replicas%d" % world if args.parallelism == "replicas" else "ep%d" % world) if world > 1 else "single",
+            "exchange": args.exchange if world > 1 and args.parallelism != "replicas" else None,
             "l2": "inputs larger than L2: a pass streams about 5 GB of weights and cache"}
 
 
@@ -180,12 +183,15 @@ def run_c3(args):
     import __graft_entry__ as graft
     pkg = graft.load_package()
     md, szlib, ep = pkg.model, pkg.lib, pkg.ep
+    replicas = world > 1 and args.parallelism == "replicas"   # every GPU holds the whole model and decodes requests of its own: no exchange
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # stdout carries the one JSON line
         dist.init_process_group("nccl")
-        if args.exchange == "nccl":
+        if replicas:
+            pass
+        elif args.exchange == "nccl":
             ep.init_from_process_group()
         else:
             peer = ep.PeerExchange(C3["hidden"])
@@ -194,7 +200,7 @@ def run_c3(args):
     head_type = szlib.TYPE_Q8_0 if args.head == "q8" else szlib.TYPE_EXL3(4)
     M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha,
                       cycle_beta=args.beta, head_type=head_type)
-    dm = md.DeviceModel(M, device, ep=(rank, world) if world > 1 else None)
+    dm = md.DeviceModel(M, device, ep=(rank, world) if world > 1 and not replicas else None)
     # every tensor outside the experts is read once a pass, except the embedding table (m rows gathered)
     dense_bytes = sum(t[3].numel() * t[3].element_size() for n, t in M["tensors"].items() if n != "token_embd.weight")
     if args.head == "proxy":
@@ -216,7 +222,8 @@ def run_c3(args):
         (the long context), then a 256-token prompt of its own - one of the model's token cycles repeated, 10% of the tokens
         substituted at random - fed through the model.  Returns the generator, positioned after the prompt."""
         sess.fill_synthetic(ctx - n_prompt, seed=3)
-        return md.Generator(sess, md.make_prompt(n_prompt, cfg["vocab"], seed=1 + i, cycles=cyc), n_new, spec_k=3)
+        # (replicas: every rank takes requests of its own; expert parallelism: every rank the same ones)
+        return md.Generator(sess, md.make_prompt(n_prompt, cfg["vocab"], seed=1 + (i * world + rank if replicas else i), cycles=cyc), n_new, spec_k=3)
 
     if args.profile_passes > 0:
         # for a profiler: N verify passes of 4 rows and nothing else (run with SZ_SESSION_GRAPHS=0 to see every launch by name)
@@ -236,13 +243,16 @@ def run_c3(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    def agree_max(v):
+    def agree(v, op="max"):
         if world == 1:
             return v
         import torch.distributed as dist
         t = torch.tensor([v], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op={"max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN, "sum": dist.ReduceOp.SUM}[op])
         return float(t[0])
+
+    def agree_max(v):
+        return agree(v, "max")
 
     # --- the workload: a stream of requests.  Every request decodes n_new tokens after its prompt through the public loop (host
     # drafter, ids host -> device, result device -> host every round).  Only decode rounds are timed - the prompt passes and the
@@ -283,20 +293,28 @@ def run_c3(args):
     while True:
         run_request(req, tot)
         req += 1
-        if tot["rounds"] >= K and agree_max(tot["dev_ms"]) >= 1000.0:
-            break
-        if tot["requests"] >= 400:
+        # every rank runs the same number of requests: the run ends when the slowest-to-fill rank has its K rounds and its second
+        if agree(1.0 if tot["rounds"] >= K and tot["dev_ms"] >= 1000.0 else 0.0, "min") > 0.5 or tot["requests"] >= 400:
             break
     barrier()
     clocks = sampler.stop()
     dev_ms, wall_s = agree_max(tot["dev_ms"]), agree_max(tot["wall_s"])
     rounds, toks = tot["rounds"], tot["n"]
-    gen_stats = dict(tokens=toks, rounds=rounds, requests=tot["requests"], warmup_rounds=warm_rounds, drafting_rounds=tot["passes"],
-                     drafted=tot["drafted"], accepted=tot["accepted"], tokens_per_round=toks / max(rounds, 1),
+    if replicas:   # the job's tokens: every rank's
+        toks = int(agree(toks, "sum"))
+        for k_ in ("rounds", "passes", "drafted", "accepted", "requests"):
+            tot[k_] = int(agree(tot[k_], "sum"))
+        for j in range(8):
+            tot["tried"][j] = int(agree(tot["tried"][j], "sum")); tot["right"][j] = int(agree(tot["right"][j], "sum"))
+        rounds_all = tot["rounds"]
+    else:
+        rounds_all = rounds
+    gen_stats = dict(tokens=toks, rounds=rounds_all, requests=tot["requests"], warmup_rounds=warm_rounds, drafting_rounds=tot["passes"],
+                     drafted=tot["drafted"], accepted=tot["accepted"], tokens_per_round=toks / max(rounds_all, 1),
                      right_by_position=tot["right"][:3], tried_by_position=tot["tried"][:3],
                      accept_rate_by_position=[tot["right"][j] / max(tot["tried"][j], 1) for j in range(3)],
                      draft_ms=tot["draft_ms"], verify_ms=tot["verify_ms"], commit_ms=tot["commit_ms"])
-    rows_avg = 1 + gen_stats["drafted"] / max(rounds, 1)   # rows of a pass: its own token and the drafts
+    rows_avg = 1 + gen_stats["drafted"] / max(rounds_all, 1)   # rows of a pass: its own token and the drafts
     gen_stats["accept_rate"] = gen_stats["accepted"] / max(gen_stats["drafted"], 1)
     sess.fill_synthetic(ctx - n_prompt, seed=3)
     prompt = md.make_prompt(n_prompt, cfg["vocab"], seed=1, cycles=cyc)
@@ -356,7 +374,9 @@ def run_c3(args):
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
-        if args.exchange == "nccl":
+        if replicas:
+            pass
+        elif args.exchange == "nccl":
             szlib.check(L.sz_ep_destroy())
         else:
             assert peer.status() == 0, "a wait of the peer exchange ran out"
@@ -368,13 +388,13 @@ def run_c3(args):
     be = expert_bytes("exl3", cfg["hidden"], cfg["expert_ff"])
     # traffic: dram__bytes_read + write of one launch of this kernel on these shapes (39 + 1 experts), from an ncu --set full capture
     roof = {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind,
-            "traffic": gateup_traffic(sum(distinct) / len(distinct) / world + 1),
+            "traffic": gateup_traffic(sum(distinct) / len(distinct) / (1 if replicas else world) + 1),
             "traffic_source": "profiles/c2_moe_gateup_exl3_full.md: ncu capture of the same kernel and expert shapes on the c2-moe workload, "
                               "scaled by the experts a launch streams", "kernel": "gateup_exl3s"}
     ks = kern.get("gateup_exl3s")
     if ks:
         # gate + up of a layer's distinct routed experts and of the shared expert: 2/3 of their bytes, one launch a layer
-        per_launch = (sum(distinct) / len(distinct) / world + 1) * be * 2 / 3
+        per_launch = (sum(distinct) / len(distinct) / (1 if replicas else world) + 1) * be * 2 / 3
         roof.update(achieved=per_launch / (ks["avg_us"] * 1e-6) / 1e9, kernel_us=ks["avg_us"], bytes_per_launch=per_launch)
         roof["frac"] = roof["achieved"] / hbm
     roof.update(step_bytes=by["experts_kv"], step_bytes_all=by["all"], step_us=step_us[4],
@@ -387,7 +407,7 @@ def run_c3(args):
         cpu = cpu_c3(pkg, args.cpu_seconds, os.cpu_count() or 1, args.head, ctx)
     line = {
         "metric": C3_METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": W, "rounds_timed": rounds,
-        "ms_per_step": dev_ms / max(rounds, 1), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "ms_per_step": dev_ms / max(rounds, 1), "higher_is_better": True, "scaling": "weak" if replicas else "strong", "vs_baseline": None,
         "dtype": "f32 activations, f16 EXL3 codebook weights, int8 Q8_0 / Q8_KV, f32 accumulate (router, norms, combine in f64)",
         "data": "synthetic",
         "config": c3_config(args, cfg, ctx, by["all"]),
@@ -397,6 +417,140 @@ def run_c3(args):
                 "wall_ms_per_step": wall_s * 1e3 / max(rounds, 1)},
         "gpu_launches": (n_k - 1) * rounds, "launches_per_pass": n_k - 1, "clocks": clocks,
         "kernels": {k: v for k, v in sorted(kern.items(), key=lambda kv: -kv[1]["total_us"])},
+    }
+    out.emit(json.dumps(line))
+
+
+# ---- workload c4-tree: one verify pass over a draft tree on the config-3 model ------------------------------------------------------
+# Benchmark config 4 asks for a 16-node tree (depth 4, branching [4, 2, 1, 1]).  A pass of this library - like the reference's - has
+# at most 8 rows (MAX_VERIFY), the root included, so the tree here has 7 drafted nodes: depth 4, branching [3, 2, 1, 1].
+C4_PARENTS = [-1, 0, 0, 0, 1, 1, 4, 6]
+C4_METRIC = "verify-step us (draft tree, 8 rows, depth 4)"
+
+
+def run_c4(args):
+    out = QuietStdout()
+    import numpy as np
+    import torch
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        raise SystemExit("the c4-tree workload runs on one GPU")
+    torch.cuda.set_device(0)
+    device = "cuda:0"
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    md, szlib = pkg.model, pkg.lib
+    hbm, peak_kind = peaks()
+    cfg = dict(C3, n_layer=args.n_layer)
+    head_type = szlib.TYPE_Q8_0 if args.head == "q8" else szlib.TYPE_EXL3(4)
+    M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha,
+                      cycle_beta=args.beta, head_type=head_type)
+    dm = md.DeviceModel(M, device)
+    del M
+    torch.cuda.empty_cache()
+    ctx, n_prompt = args.ctx, 256
+    K, W = args.steps, max(args.warmup, 3)
+    sess = md.Session(dm, ctx + 8 * (K + W) * 3 + 64, kv_q8=True, head_proxy=args.head == "proxy")
+    stream = sess._stream
+    _, cyc = md.token_cycles(cfg["vocab"], 1)
+    sess.fill_synthetic(ctx - n_prompt, seed=3)
+    prompt = md.make_prompt(n_prompt, cfg["vocab"], seed=1, cycles=cyc)
+    sess.prefill(prompt)
+    _, top, _ = sess.result()
+    sess.commit((n_prompt - 1) % 8 + 1)
+    nxt = int(top[(n_prompt - 1) % 8][64])
+    rng = np.random.default_rng(4)
+    parents = C4_PARENTS
+    m = len(parents)
+    L = szlib.load()
+    sampler = md.Sampler(0.7, 64, 0.9, 0.0, 17)
+
+    def tree_ids(root):
+        return [int(root)] + [int(t) for t in rng.integers(0, cfg["vocab"], m - 1)]   # draft tokens uniform over the vocabulary
+
+    def greedy_pass(root):
+        """device acceptance: ids host -> device, {kept, next} and the path device -> host"""
+        ids = tree_ids(root)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(stream)
+        sess.verify_tree(ids, parents, accept=1)
+        e1.record(stream)
+        (keep, nx), _, _ = sess.result()
+        sess.commit(keep)
+        stream.synchronize()
+        return e0.elapsed_time(e1) * 1e3, (time.perf_counter() - t0) * 1e6, keep, nx
+
+    def sampled_pass(root, pos):
+        """host acceptance by rejection sampling against uniform-random draft probabilities, then the path commit"""
+        ids = tree_ids(root)
+        q = rng.random(m).astype(np.float32)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        e0.record(stream)
+        sess.verify_tree(ids, parents, accept=0)
+        _, top, _ = sess.result()
+        a, p = np.array(ids, dtype=np.uint32), np.array(parents, dtype=np.int32)
+        path = np.zeros(m, dtype=np.int32)
+        nx = C.c_uint32()
+        n = L.sz_tree_accept_sampled(C.byref(sampler), top.ctypes.data, a.ctypes.data, p.ctypes.data, m, q.ctypes.data, pos, -1, path.ctypes.data, C.byref(nx))
+        sess.commit_path([int(t) for t in path[:n]])
+        e1.record(stream)
+        stream.synchronize()
+        return e0.elapsed_time(e1) * 1e3, (time.perf_counter() - t0) * 1e6, n, int(nx.value)
+
+    for _ in range(W):
+        _, _, _, nxt = greedy_pass(nxt)
+    clock = ClockSampler(torch.cuda.current_device())
+    clock.start()
+    dev, wall, kept = [], [], []
+    for _ in range(K):
+        d, w_, k_, nxt = greedy_pass(nxt)
+        dev.append(d); wall.append(w_); kept.append(k_)
+    sdev, swall, skept = [], [], []
+    for i in range(K):
+        d, w_, k_, nxt = sampled_pass(nxt, 1000 + 8 * i)
+        sdev.append(d); swall.append(w_); skept.append(k_)
+    clocks = clock.stop()
+    # routing of one tree pass: distinct experts per layer (the bytes the pass must read)
+    sess.trace_routes(True)
+    sess.verify_tree(tree_ids(nxt), parents)
+    sess.result()
+    ridx, _ = sess.routes()
+    sess.commit_path([0])
+    sess.trace_routes(False)
+    distinct = [int(np.unique(ridx[l]).size) for l in range(cfg["n_layer"])]
+    # launches of one tree pass (eager, counted by the library's trace)
+    nev = 4096
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(nev)]
+    for e in evs:
+        e.record(stream)
+    stream.synchronize()
+    arr = (C.c_uint64 * nev)(*[e.cuda_event for e in evs])
+    szlib.check(L.sz_trace_begin(arr, nev, sess.stream))
+    sess.verify_tree(tree_ids(nxt), parents, accept=1)
+    n_k = L.sz_trace_end()
+    (kept1, _), _, _ = sess.result()
+    sess.commit(kept1)
+    by = c3_bytes(cfg, ctx, distinct, 0)
+    med = sorted(dev)[len(dev) // 2]
+    line = {
+        "metric": C4_METRIC, "value": med, "unit": "us", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": med / 1e3, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, f16 EXL3 codebook weights, int8 Q8_0 / Q8_KV, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "c4-tree", "n_layer": cfg["n_layer"], "context": ctx, "tree_rows": m, "parents": parents, "depth": 4, "branching": [3, 2, 1, 1],
+                   "note": "benchmark config 4 names 16 nodes with branching [4, 2, 1, 1]; a pass holds at most 8 rows (the root included), so the tree has 7 "
+                           "drafted nodes; draft tokens uniform over the vocabulary, draft probabilities uniform random; parity of tree passes is against "
+                           "this repository's own CPU restatement (the reference has no tree verification)",
+                   "l2": "inputs larger than L2: a pass streams several GB of weights and cache"},
+        "tree": {"greedy": {"us_per_verify": med, "accepted_len_mean": sum(kept) / len(kept)},
+                 "sampled_T0.7_top_p0.9": {"us_per_verify": sorted(sdev)[len(sdev) // 2], "accepted_len_mean": sum(skept) / len(skept),
+                                            "note": "pass without device acceptance, top-64 rows to the host, rejection sampling there, commit of the kept path"}},
+        "roofline": {"bound": "hbm", "peak": hbm, "unit": "GB/s", "peak_kind": peak_kind, "step_bytes": by["experts_kv"], "achieved": by["experts_kv"] / (med * 1e-6) / 1e9,
+                     "frac": by["experts_kv"] / (med * 1e-6) / 1e9 / hbm, "traffic": None, "distinct_experts_per_layer": sum(distinct) / len(distinct)},
+        "cpu_baseline": None,
+        "e2e": {"value": sorted(wall)[len(wall) // 2], "unit": "us", "h2d_bytes_per_step": 4 * m + 128, "d2h_bytes_per_step": 8 + 64 + 512 * m},
+        "gpu_launches": (n_k - 1) * 2 * K, "launches_per_pass": n_k - 1, "clocks": clocks,
     }
     out.emit(json.dumps(line))
 
@@ -626,11 +780,14 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe", "c4-tree"])
     ap.add_argument("--alpha", type=float, default=None,
                     help="c3: how strongly the synthetic model continues its token cycles (default: by kind of head, see C3_ALPHA_BY_HEAD)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="c3, N > 1: the expert-parallel exchange - stores into the peers' memory from the combine kernel (default) or an NCCL all-reduce")
+    ap.add_argument("--parallelism", default="ep", choices=["ep", "replicas"],
+                    help="c3, N > 1: experts sharded over the GPUs, one sequence (default, strong scaling), or every GPU with the whole model "
+                         "and requests of its own, no exchange (weak scaling)")
     ap.add_argument("--profile-passes", type=int, default=0, help="c3: only run this many 4-row verify passes (for ncu), no timing")
     ap.add_argument("--head", default="proxy", choices=["q8", "exl3", "proxy"],
                     help="c3: output.weight as Q8_0 read in full, as 4-bit EXL3 read in full, or EXL3 screened by its 2-bit proxy (Q2_P)")
@@ -649,6 +806,11 @@ def main():
         args.alpha = C3_ALPHA_BY_HEAD[args.head]
     if args.beta is None:
         args.beta = C3_BETA_BY_HEAD[args.head]
+    if args.workload == "c4-tree":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no tree verification (its verify pass is a chain); the CPU restatement of a tree pass is a test oracle only"}))
+            return
+        return run_c4(args)
     if args.workload == "c3":
         return run_reference_c3(args) if args.impl == "reference" else run_c3(args)
     if args.impl == "reference":

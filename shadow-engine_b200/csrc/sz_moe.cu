@@ -2,9 +2,6 @@
 // Arithmetic follows Session::moe of the CPU reference (crates/shadowzero-model/src/forward.rs:1009-1034): router logits and
 // the softmax in f64, expert dot products accumulated in f32, the weighted sum over experts in f64 in rank order.
 #include "sz_moe.cuh"
-#define SZ_XW_DEFAULT_OCC 2
-#define SZ_XW_DEFAULT_TW 4
-#define SZ_XW_DEFAULT_TWD 4
 #include "sz_moe_exl3w.cuh"
 #include "sz_moe_blk.cuh"
 
@@ -775,8 +772,12 @@ static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const S
         // SZ_XW_OCC / SZ_XW_TW / SZ_XW_TWD override the choice (experiments).
         const dim3 block(SZ_XW_THREADS);
         const char *eo = getenv("SZ_XW_OCC"), *et = getenv("SZ_XW_TW"), *ed = getenv("SZ_XW_TWD");
-        const int occ = eo && atoi(eo) == 2 ? 2 : (eo && atoi(eo) == 3 ? 3 : SZ_XW_DEFAULT_OCC);
-        int tw = et ? atoi(et) : SZ_XW_DEFAULT_TW, twd = ed ? atoi(ed) : SZ_XW_DEFAULT_TWD;
+        // few rows mean few units (a 1-row pass of the benchmark's shape: 11 groups, 352 units 4 wide for 296 blocks): narrower units
+        // and a third block a multiprocessor spread them better (4.30 -> 4.19 ms a 1-row pass of the 48-layer model); with 4 rows the
+        // wide units win (6.18 against 6.35 ms)
+        const bool few = m * (int)L->top_k <= 24;
+        const int occ = eo && atoi(eo) == 2 ? 2 : (eo && atoi(eo) == 3 ? 3 : (few ? 3 : 2));
+        int tw = et ? atoi(et) : (few ? 2 : 4), twd = ed ? atoi(ed) : (few ? 2 : 4);
         if (!(tw == 1 || tw == 2 || tw == 4) || tw > NTC || NTC % tw) tw = NTC < 4 ? NTC : 4;
         if (tw == 3) tw = 1;
         if (!(twd == 1 || twd == 2 || twd == 4)) twd = 4;
