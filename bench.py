@@ -413,7 +413,7 @@ def run_c3(args):
         "config": c3_config(args, cfg, ctx, by["all"]),
         "speculation": gen_stats, "verify_step_us": {"rows_1": step_us[1], "rows_4": step_us[4]},
         "roofline": roof, "cpu_baseline": cpu,
-        "e2e": {"value": toks / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * rows_avg, "d2h_bytes_per_step": 8 + 512 * rows_avg,
+        "e2e": {"value": toks / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 128, "d2h_bytes_per_step": 8 + 512 * rows_avg,
                 "wall_ms_per_step": wall_s * 1e3 / max(rounds, 1)},
         "gpu_launches": (n_k - 1) * rounds, "launches_per_pass": n_k - 1, "clocks": clocks,
         "kernels": {k: v for k, v in sorted(kern.items(), key=lambda kv: -kv[1]["total_us"])},

@@ -224,6 +224,11 @@ int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode,
  * cumulative distribution (the device's double-precision exp is not the host library's). */
 struct sz_sampler;
 int sz_session_set_sampler(sz_session* s, const struct sz_sampler* sp);
+/* Up to 7 further ids that end generation (the tokenizer's other end-of-generation ids, the request's stop tokens: engine.rs:2386
+ * `tok.is_eog(d) || stops.contains(&d)`): device acceptance - greedy, sampled, down a tree - never keeps a drafted one, exactly as
+ * it never keeps the pass's eog_token.  n = 0 clears the list.  Takes effect with the next pass. */
+int sz_session_set_stops(sz_session* s, const int32_t* ids, int n, uint64_t stream);
+int sz_session_stops(const sz_session* s, int32_t* out /* room for 7 */);   /* returns how many are set */
 int sz_session_verify_sampled(sz_session* s, const int32_t* ids, int m, uint64_t pos, int eog_token, uint64_t stream);
 /* Tree verification (no counterpart in the reference, whose verify pass is a chain: session.rs:7698-7723, kernels/forward.cu:1481-1487).
  * One pass over a draft TREE of up to SZ_MAX_VERIFY rows: row 0 is the root (the pass's own token, parents[0] = -1), row j > 0 a drafted
@@ -350,6 +355,8 @@ int sz_generate(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_ge
 typedef struct sz_gen sz_gen;
 int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint64_t stream, sz_gen** out);
 int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_log, int pass_cap, sz_gen_stats* stats, uint64_t stream);
+/* the request's stop ids for the loop: it ends at one as at eog_token, and never accepts a drafted one (host and device alike) */
+int sz_gen_set_stops(sz_gen* g, const uint32_t* ids, int n, uint64_t stream);
 void sz_gen_free(sz_gen* g);
 
 /* ---- expert parallelism over NCCL ------------------------------------------------------------------------------------------

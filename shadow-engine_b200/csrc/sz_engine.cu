@@ -13,6 +13,8 @@ int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint64_t stream
 int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode, int eog_token, int want_head, uint64_t stream);
 int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* top, float* logits, uint64_t stream);
 int sz_session_commit(sz_session* s, int keep, uint64_t stream);
+int sz_session_set_stops(sz_session* s, const int32_t* ids, int n, uint64_t stream);
+int sz_session_stops(const sz_session* s, int32_t* out);
 int sz_session_len(const sz_session* s);
 int sz_session_capacity(const sz_session* s);
 int sz_session_pending(const sz_session* s);
@@ -442,6 +444,7 @@ struct sz_gen {
     std::vector<uint32_t> hist, top, last;
     int n = 0;            // tokens emitted so far
     bool done = false;    // an end-of-generation token was drawn
+    std::vector<uint32_t> stops;   // the request's stop ids (sz_gen_set_stops): end generation like the end-of-generation id
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;  // bracket a pass on its stream: the device's share of a round
     ~sz_gen() {
         sz_drafter_free(sd);
@@ -457,6 +460,7 @@ extern "C" int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt,
         return sz_fail(SZ_E_ARG, "sz_gen_begin: prompt %d + %d new tokens do not fit the session", n_prompt, p->max_new);
     sz_gen* g = new sz_gen();
     g->s = s; g->p = *p;
+    { int32_t st[7]; const int ns = sz_session_stops(s, st); g->stops.assign(st, st + ns); }   // the session's stop ids hold for the loop too
     g->top.resize(SZ_MAX_VERIFY * 128); g->last.resize(128);
     if (cudaEventCreate(&g->ev0) != cudaSuccess || cudaEventCreate(&g->ev1) != cudaSuccess) { delete g; return sz_fail(SZ_E_CUDA, "sz_gen_begin: no events"); }
     int rc = !p->greedy && p->device_accept ? sz_session_set_sampler(s, &p->sampler) : SZ_OK;
@@ -473,6 +477,16 @@ extern "C" int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt,
     return SZ_OK;
 }
 
+// The request's stop tokens (engine.rs:2386 `stops.contains(&d)`; the tokenizer's further end-of-generation ids go here too): the
+// loop ends at one as at the end-of-generation id, and a drafted one is never accepted - on the host and on the device alike.
+extern "C" int sz_gen_set_stops(sz_gen* g, const uint32_t* ids, int n, uint64_t stream) {
+    if (!g || n < 0 || n > 7 || (n > 0 && !ids)) return sz_fail(SZ_E_ARG, "sz_gen_set_stops: 0..7 stop ids");
+    g->stops.assign(ids, ids + n);
+    int32_t tmp[7];
+    for (int i = 0; i < n; i++) tmp[i] = (int32_t)ids[i];
+    return sz_session_set_stops(g->s, tmp, n, stream);
+}
+
 extern "C" void sz_gen_free(sz_gen* g) { delete g; }
 
 // Runs up to `rounds` rounds of the loop (0: until max_new tokens or an end-of-generation token).  A round emits one token plus the
@@ -482,7 +496,11 @@ extern "C" int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_lo
     sz_session* s = g->s;
     const sz_gen_params* p = &g->p;
     auto pick = [&](const uint32_t* row, uint64_t pos) -> uint32_t { return p->greedy ? row[64] : sz_sample_top(&p->sampler, row, pos); };
-    auto is_eog = [&](uint32_t t) { return p->eog_token >= 0 && t == (uint32_t)p->eog_token; };
+    auto is_eog = [&](uint32_t t) {
+        if (p->eog_token >= 0 && t == (uint32_t)p->eog_token) return true;
+        for (uint32_t st : g->stops) if (st == t) return true;
+        return false;
+    };
     int& n = g->n;
     int rc = SZ_OK, done_rounds = 0;
     while (!g->done && n < p->max_new && (rounds <= 0 || done_rounds < rounds)) {

@@ -316,6 +316,7 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->ctx = ctx; s->flags = flags; s->want_routes = 0;
     s->h_pin = nullptr;
     if (cudaHostAlloc((void**)&s->h_pin, 512, cudaHostAllocDefault) != cudaSuccess) { delete s; return sz_fail(SZ_E_CUDA, "cudaHostAlloc of the id staging buffer failed"); }
+    memset(s->h_pin, 0, 512);
     {
         const char* e = getenv("SZ_SESSION_GRAPHS");  // A/B switch: 0 = launch every kernel eagerly
         s->use_graphs = !(e && atoi(e) == 0);
@@ -860,6 +861,22 @@ extern "C" int sz_session_tree_path(sz_session* s, int32_t* path, int* n, uint64
     return SZ_OK;
 }
 
+// Stop ids of the request: device acceptance never keeps a drafted one (as it never keeps the pass's end-of-generation id).
+extern "C" int sz_session_set_stops(sz_session* s, const int32_t* ids, int n, uint64_t stream) {
+    if (!s || n < 0 || n > 7 || (n > 0 && !ids)) return sz_fail(SZ_E_ARG, "sz_session_set_stops: 0..7 stop ids");
+    if (s->inflight) { SZ_CUDA(cudaStreamSynchronize((cudaStream_t)stream)); s->inflight = 0; }   // the staging block is free again
+    s->h_pin[24] = n;
+    for (int i = 0; i < 7; i++) s->h_pin[25 + i] = i < n ? ids[i] : -1;
+    return SZ_OK;
+}
+
+extern "C" int sz_session_stops(const sz_session* s, int32_t* out) {   // the list as set (out: room for 7); returns how many
+    if (!s || !out) return 0;
+    const int n = s->h_pin[24];
+    for (int i = 0; i < n; i++) out[i] = s->h_pin[25 + i];
+    return n;
+}
+
 extern "C" int sz_session_set_sampler(sz_session* s, const sz_sampler* sp) {
     if (!s || !sp) return sz_fail(SZ_E_ARG, "sz_session_set_sampler: null argument");
     if (!(sp->temperature > 0.0f)) return sz_fail(SZ_E_ARG, "sz_session_set_sampler: temperature %g (greedy decoding is SZ_ACCEPT_GREEDY)", (double)sp->temperature);
@@ -888,8 +905,8 @@ static int sz_verify_impl(sz_session* s, const int32_t* ids, int m, int accept_m
     cudaStream_t st = (cudaStream_t)stream;
     if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
     memcpy(s->h_pin, ids, (size_t)m * 4);
-    // a sampled pass carries its sampler block along, a tree pass its tables
-    const size_t staged = s->tree_pass ? 128 + sizeof(SzTree) : (accept_mode == SZ_ACCEPT_SAMPLED ? 96 : (size_t)m * 4);
+    // the staging block: ids, (word 16) the sampler of a sampled pass, (word 24) the stop ids, (word 32) a tree pass's tables
+    const size_t staged = s->tree_pass ? 128 + sizeof(SzTree) : 128;
     int rc = SZ_OK;
     // one graph per (rows, head, acceptance, eog): every launch-time value a kernel needs lives in device memory
     const int key = m | (want_head ? 16 : 0) | (accept_mode << 5) | (s->tree_pass ? 128 : 0) | ((eog_token & 0xfffff) << 8);

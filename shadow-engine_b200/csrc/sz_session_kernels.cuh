@@ -1204,6 +1204,17 @@ sz_attn_merge_kernel(const float* __restrict__ part, const float* __restrict__ g
     }
 }
 
+// A drafted token that ends generation is never accepted: the one end-of-generation id of the launch, or one of the session's stop
+// ids (the reference's loop leaves `tok.is_eog(d)` and `stops.contains(&d)` drafts for the loop's top: engine.rs:2381-2390).  The
+// stop list rides in the pass's staging block: word 24 = how many (at most 7), words 25.. the ids.
+__device__ __forceinline__ bool sz_is_stop(const int32_t* __restrict__ ids, int d, int eog) {
+    if (d == eog) return true;
+    const int n = ids[24];
+    for (int i = 0; i < n && i < 7; i++)
+        if (ids[25 + i] == d) return true;
+    return false;
+}
+
 // ---- greedy acceptance on the device (the host loop of crates/shadowzero-serve/src/engine.rs:2377-2408 for the greedy case):
 // row i's best token must equal the next drafted token ids[i + 1]; a drafted end-of-generation token is never accepted.
 // res[0] = rows kept (1 .. m), res[1] = the token after the kept rows (best of row keep - 1).
@@ -1218,7 +1229,7 @@ __global__ void sz_accept_greedy_kernel(const u32* __restrict__ top, const int32
         for (int i = 0; i + 1 < m; i++) {
             const int want = (int)top[(size_t)i * 128 + 64];
             const int d = ids[i + 1];
-            if (want != d || d == eog) break;
+            if (want != d || sz_is_stop(ids, d, eog)) break;
             keep++;
         }
     res[0] = keep;
@@ -1240,7 +1251,7 @@ __global__ void sz_accept_tree_kernel(const u32* __restrict__ top, const int32_t
         const int want = (int)top[(size_t)cur * 128 + 64];
         int next = -1;
         for (int c = cur + 1; c < m; c++)
-            if (tr->parents[c] == cur && ids[c] == want && want != eog) { next = c; break; }
+            if (tr->parents[c] == cur && ids[c] == want && !sz_is_stop(ids, want, eog)) { next = c; break; }
         if (next < 0) break;
         cur = next;
         res[2 + keep] = cur;
@@ -1340,7 +1351,7 @@ sz_accept_sampled_kernel(const u32* __restrict__ top, const int32_t* __restrict_
         int keep = 1;
         for (int i = 0; i + 1 < m; i++) {
             const int d = ids[i + 1];
-            if ((int)picks[i] != d || d == eog) break;
+            if ((int)picks[i] != d || sz_is_stop(ids, d, eog)) break;
             keep++;
         }
         res[0] = keep;

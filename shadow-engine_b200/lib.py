@@ -85,6 +85,8 @@ SYMBOLS = {
     "sz_session_prefill": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64]),
     "sz_session_verify": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64]),
     "sz_session_set_sampler": (C.c_int, [C.c_void_p, C.c_void_p]),
+    "sz_session_set_stops": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64]),
+    "sz_session_stops": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     "sz_session_verify_sampled": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64, C.c_int, C.c_uint64]),
     "sz_session_verify_tree": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_uint64]),
     "sz_session_tree_path": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int), C.c_uint64]),
@@ -125,6 +127,7 @@ SYMBOLS = {
                               C.c_void_p, C.c_uint64]),
     "sz_gen_begin": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_void_p, C.c_uint64, C.POINTER(C.c_void_p)]),
     "sz_gen_run": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.c_int, C.c_void_p, C.c_uint64]),
+    "sz_gen_set_stops": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_uint64]),
     "sz_gen_free": (None, [C.c_void_p]),
     "sz_ep_unique_id": (C.c_int, [C.c_void_p]),
     "sz_ep_init": (C.c_int, [C.c_int, C.c_int, C.c_void_p]),

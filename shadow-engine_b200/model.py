@@ -352,6 +352,11 @@ class Session:
         a = (C.c_int32 * len(path))(*[int(t) for t in path])
         szlib.check(self.lib.sz_session_commit_path(self.h, a, len(path), self.stream))
 
+    def set_stops(self, ids):
+        """Up to 7 more ids that end generation: device acceptance never keeps a drafted one, and the loop ends at one."""
+        a = (C.c_int32 * max(len(ids), 1))(*[int(t) for t in ids])
+        szlib.check(self.lib.sz_session_set_stops(self.h, a, len(ids), self.stream))
+
     def set_sampler(self, sampler):
         szlib.check(self.lib.sz_session_set_sampler(self.h, C.byref(sampler)))
 

@@ -136,6 +136,37 @@ def test_config1_greedy_spec3_tokens_and_accepted_counts(tiny_cycle):
     assert plain == toks and st2.passes == 0
 
 
+def test_stop_ids_end_the_loop_and_are_never_accepted_as_drafts(tiny_cycle):
+    # engine.rs:2381-2390: a pick that is a stop token ends the request, a drafted one is left for the loop's top to see.  The stop
+    # list rides to the device with the pass, so deciding on the device and on the host give the same tokens and counts.
+    M, hm, dm, prompt = tiny_cycle
+    plain, plain_log, _ = md.Session(dm, 512, kv_q8=True).generate(prompt, 64, spec_k=3)
+    accepted_at = [sum(1 + a for _, a in plain_log[:i]) for i in range(len(plain_log))]   # tokens emitted before round i
+    i = next(i for i, (d, a) in enumerate(plain_log) if a >= 2 and i > 2)                 # a round that accepted two drafts or more
+    stop = plain[accepted_at[i] + 2]                                                      # ... whose second draft becomes a stop id
+    cut = plain.index(stop)
+    outs = []
+    for device_accept in (True, False):
+        sess = md.Session(dm, 512, kv_q8=True)
+        sess.set_stops([M["cfg"]["vocab"] - 1, stop])
+        toks, log, st = sess.generate(prompt, 64, spec_k=3, device_accept=device_accept)
+        assert toks == plain[:cut]
+        outs.append((toks, log, (st.passes, st.drafted, st.accepted)))
+    assert outs[0] == outs[1]
+    # the same through the pass itself: the kept count stops before the stop id
+    tail = (len(prompt) - 1) % szlib.MAX_VERIFY + 1
+    free, sess = md.Session(dm, 512, kv_q8=True), md.Session(dm, 512, kv_q8=True)
+    for x in (free, sess):
+        x.prefill(prompt); x.result(); x.commit(tail)
+    assert plain[2] not in plain[:2]
+    free.verify(plain[:4], accept=1); (k0, _), _, _ = free.result()
+    sess.set_stops([plain[2]])
+    sess.verify(plain[:4], accept=1); (k1, _), _, _ = sess.result()
+    assert k0 == 4 and k1 == 2
+    with pytest.raises(szlib.SzError):
+        sess.set_stops(list(range(8)))                 # seven at most
+
+
 def test_config1_sampled_spec3(tiny_cycle):
     # sampled acceptance: the token the target would have drawn at that position (sampler.rs:3-9); T = 0.7, top-p 0.9
     M, hm, dm, prompt = tiny_cycle

@@ -141,6 +141,13 @@ def test_greedy_acceptance_down_the_tree_on_the_device(setup):
     (keep, nxt), _, _ = s3.result()
     assert s3.tree_path() == [0, 2] and keep == 2
     s3.commit(keep)
+    # nor one of the session's stop ids
+    s5 = md.Session(dm, 64, kv_q8=True)
+    s5.set_stops([bad[0], good[2]])
+    s5.verify(prefix); s5.result(); s5.commit(len(prefix))
+    s5.verify_tree(ids, parents, accept=1)
+    (keep, nxt), _, _ = s5.result()
+    assert s5.tree_path() == [0, 2] and keep == 2
     # misuse
     s4 = md.Session(dm, 64, kv_q8=True)
     with pytest.raises(szlib.SzError):
