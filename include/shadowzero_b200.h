@@ -189,6 +189,20 @@ int sz_weights_tensor_count(const sz_weights* w);
 int sz_weights_tensor_info(const sz_weights* w, const char* name, int32_t* type, int64_t dims[4], int64_t* bytes);
 void sz_weights_free(sz_weights* w);
 
+/* ---- many-row dense projections on the tensor pipe (tcgen05 + tensor memory) ----------------------------------------------------------
+ * y[t * ys + r] = sum_k w[r][k] * x[t * xs + k] for t < m token rows and every row r of w (strides in floats).  The prompt / batched
+ * form of a projection: replaces the reference's tensor-core family for a long prompt, kernels/matvec.cu:758-1260 (mma_core,
+ * mma_cols_<type>, mma_cols64_<type>; same argument meaning: w, x, xs, y, ys, rows, cols, m) as crates/shadowzero-cuda/src/session.rs:7276
+ * launches it, with that family's arithmetic: weights decoded as the reference decodes them (d * q in f32) and rounded to f16,
+ * inputs rounded to f16, f32 accumulation, the order of the sum left to the tensor core.  The reference calls the mode inexact and
+ * keeps it for prompts; results agree with the exact kernels to about 1e-3 relative, not bit for bit.
+ * w: Q8_0, cols a multiple of 256, data 16-byte aligned.  x rows 16-byte aligned.  scratch: sz_mma_cols_scratch_bytes, 256-byte
+ * aligned, cleared once by sz_mma_cols_status(scratch, 1, NULL, stream); sz_mma_cols_status(scratch, 0, &code, stream) synchronises
+ * and reports whether a bounded wait of the kernel ever ran out (code != 0: results of that call are not valid). */
+int sz_mma_cols_scratch_bytes(int cols, int m, int64_t* bytes);
+int sz_mma_cols(const sz_tensor* w, uint64_t x, int64_t xs, uint64_t y, int64_t ys, int m, uint64_t scratch, int64_t scratch_bytes, uint64_t stream);
+int sz_mma_cols_status(uint64_t scratch, int init, int* code, uint64_t stream);
+
 /* ---- the session: the verify surface ------------------------------------------------------------------------------------
  * Replaces the verify subset of GpuSession (crates/shadowzero-cuda/src/session.rs): step_batch_verify_top (6061-6072), rollback
  * (6217-6276), note_verify, capacity, tokens, and prefill by passes.  One engine thread owns a session (engine.rs:340-420).

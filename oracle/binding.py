@@ -400,3 +400,14 @@ def proxy_pick(bmax, k_use, max_sel):
     sel = np.empty(max(max_sel, 1), dtype=np.uint32)
     n = lib().szo_proxy_pick(_p(bmax), m, n_ob, k_use, max_sel, _p(sel))
     return sel[:n].copy()
+
+
+def mma_cols_q8(w_bytes, rows, cols, x):
+    """The arithmetic of the reference's tensor-core projections for a long prompt (kernels/matvec.cu:758-775 and `mma_core`, :1100-1180):
+    a weight is decoded as the scalar path decodes it (the f32 product d * q), rounded to f16; the input is rounded to f16; products are
+    summed in f32 by the tensor core in an order of its own.  Returned in f64 from the rounded operands, so a test can bound the
+    distance by what f32 accumulation of `cols` terms may add.  x: [m][cols] f32 -> ([m][rows] f64, [m][rows] f64 sum of |products|)."""
+    w = dequant(Q8_0, w_bytes).reshape(rows, cols)                 # d * q in f32, exactly (quant.rs:174-179)
+    w16 = w.astype(np.float16).astype(np.float64)
+    x16 = np.asarray(x, dtype=np.float32).astype(np.float16).astype(np.float64)
+    return x16 @ w16.T, np.abs(x16) @ np.abs(w16).T

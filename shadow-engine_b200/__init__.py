@@ -8,4 +8,4 @@ library raises.
 The directory name has a hyphen, so load it with `__graft_entry__.load_package()`, which registers it as
 `shadow_engine_b200`.
 """
-from . import lib, moe, synth, model, ep, head, gguf_io  # noqa: F401
+from . import lib, moe, synth, model, ep, head, gguf_io, mma_cols  # noqa: F401
