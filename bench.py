@@ -8,6 +8,8 @@ metric is accepted tokens per second (every emitted token: accepted drafts and t
 torchrun) the experts of every layer are sharded over the N ranks (expert parallelism); one sequence, so scaling is "strong".
 
 `--workload c2-moe`: benchmark config 2, the verify-step MoE microbench (one MoE sublayer pass over K+1 = 4 rows per step).
+`--workload prefill-dense`: the batched / prompt form of a DeltaNet layer's input projection (12,288 x 2,048 Q8_0) over 256 or more token
+rows on tcgen05 (`sz_mma_cols`); TFLOP/s against the measured dense bf16 rate.
 `--workload c4-tree`: benchmark config 4's mechanism on the config-3 model: one verify pass over a draft tree (8 rows), greedy
 acceptance on the device and rejection sampling on the host; reports us per verify and the accepted length.
 
@@ -610,6 +612,103 @@ def run_reference_c3(args):
         "cpu_baseline": cpu_line, "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+# ---- workload prefill-dense: many token rows through one dense projection on tcgen05 ------------------------------------------------
+PD = dict(rows=12288, cols=2048)     # attn_qkv (8,192) + attn_gate (4,096) of a config-3 DeltaNet layer, one Q8_0 matrix
+PD_METRIC = "dense projection TFLOP/s (Q8_0 weights, many token rows, tcgen05)"
+
+
+def cpu_prefill_dense(tokens, seconds, wb):
+    """The restated arithmetic of the reference's tensor-core projection on the host cores (numpy, f32 matmul of the f16-rounded
+    operands), on a bounded sample: as many token rows as fit the time box."""
+    import numpy as np
+    from oracle import binding as ob
+    w = ob.dequant(ob.Q8_0, wb).reshape(PD["rows"], PD["cols"]).astype(np.float16).astype(np.float32)
+    n = min(tokens, 64)
+    x = np.random.default_rng(1).standard_normal((n, PD["cols"])).astype(np.float16).astype(np.float32)
+    x @ w.T
+    t0, reps = time.perf_counter(), 0
+    while time.perf_counter() - t0 < max(seconds, 0.5):
+        x @ w.T
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": 2.0 * n * PD["rows"] * PD["cols"] / dt / 1e12, "unit": "TFLOP/s", "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": "%d token rows of the same matrix, numpy f32 matmul of the f16-rounded operands (the arithmetic of kernels/matvec.cu mma_core)" % n}
+
+
+def run_prefill_dense(args):
+    if args.impl == "reference":
+        import numpy as np
+        sys.path.insert(0, ROOT)
+        import __graft_entry__ as graft
+        pkg = graft.load_package()
+        wb = pkg.synth.quantize_q8_0(pkg.synth.normal((PD["rows"], PD["cols"]), 0.02, 1, "pd.w0")).numpy()
+        c = cpu_prefill_dense(args.tokens, 10.0, wb)
+        print(json.dumps({"impl": "reference", "metric": PD_METRIC, "value": c["value"], "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+                          "warmup": args.warmup, "higher_is_better": True, "config": {"workload": "prefill-dense", **PD, "tokens": args.tokens},
+                          "cpu_baseline": c, "e2e": {"value": c["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+    if args.gpus != 1:
+        raise SystemExit("the prefill-dense workload runs on one GPU")
+    out = QuietStdout()
+    import torch
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    torch.cuda.set_device(0)
+    T, K, W = args.tokens, args.steps, max(args.warmup, 3)
+    n_mat = 6                                                    # 6 x 26.7 MB of weights cycled: more than the 126 MB of L2
+    mats = [pkg.synth.quantize_q8_0(pkg.synth.normal((PD["rows"], PD["cols"]), 0.02, 1, "pd.w%d" % i, device="cuda")) for i in range(n_mat)]
+    ops = [pkg.mma_cols.MmaCols(wb, PD["rows"], PD["cols"], T) for wb in mats]
+    x = pkg.synth.normal((T, PD["cols"]), 1.0, 2, "pd.x", device="cuda")
+    y = torch.empty((T, PD["rows"]), dtype=torch.float32, device="cuda")
+    xh = x.cpu().pin_memory()
+    yh = torch.empty((T, PD["rows"]), dtype=torch.float32).pin_memory()
+    for i in range(W):
+        ops[i % n_mat](x, out=y)
+    torch.cuda.synchronize()
+    flops = 2.0 * T * PD["rows"] * PD["cols"]
+    sampler = ClockSampler(0)
+    sampler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+    torch.cuda.synchronize()
+    ev[0].record()
+    for i in range(K):
+        ops[i % n_mat](x, out=y)
+    ev[1].record()
+    torch.cuda.synchronize()
+    dev_ms = ev[0].elapsed_time(ev[1])
+    # the same through host buffers: the rows go up, the result comes back, every step
+    t0 = time.perf_counter()
+    for i in range(K):
+        x.copy_(xh, non_blocking=True)
+        ops[i % n_mat](x, out=y)
+        yh.copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+    wall_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    for o in ops:
+        assert o.status() == 0
+    tf = flops * K / (dev_ms * 1e-3) / 1e12
+    try:
+        pk = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        peak, kind = float(pk["bf16_tflops"]), "measured"
+    except Exception:
+        peak, kind = 1590.0, "fallback"
+    cpu = cpu_prefill_dense(T, args.cpu_seconds, mats[0].cpu().numpy()) if args.cpu_seconds > 0 else None
+    line = {"metric": PD_METRIC, "value": tf, "unit": "TFLOP/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands (Q8_0 weights decoded d * q then rounded, inputs rounded), f32 accumulate in tensor memory",
+            "data": "synthetic",
+            "config": {"workload": "prefill-dense", **PD, "tokens": T, "weight_bytes": PD["rows"] * PD["cols"] // 32 * 34,
+                       "l2": "inputs larger than L2: %d matrices of 26.7 MB cycled" % n_mat},
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak, "peak_kind": kind, "traffic": None,
+                         "kernel": "sz_mma_cols_q8_kernel (+ sz_x16_pack_kernel, in the same timed step)",
+                         "hbm_side": {"bytes_per_step": PD["rows"] * PD["cols"] // 32 * 34 + T * PD["cols"] * 4 + T * PD["rows"] * 4,
+                                      "gbs": (PD["rows"] * PD["cols"] // 32 * 34 + T * PD["cols"] * 4 + T * PD["rows"] * 4) * K / (dev_ms * 1e-3) / 1e9}},
+            "cpu_baseline": cpu,
+            "e2e": {"value": flops * K / wall_s / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": T * PD["cols"] * 4, "d2h_bytes_per_step": T * PD["rows"] * 4},
+            "gpu_launches": 2 * K, "clocks": clocks}
+    out.emit(json.dumps(line))
+
+
 # ---- workload c2-moe: the MoE sublayer microbench ---------------------------------------------------------------------------------
 def build_layers(fmt, n_layers, device, seed=1):
     import __graft_entry__ as graft
@@ -780,7 +879,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe", "c4-tree"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe", "c4-tree", "prefill-dense"])
+    ap.add_argument("--tokens", type=int, default=256, help="prefill-dense: token rows a step (256 = 64 sequences x K+1 = 4 rows)")
     ap.add_argument("--alpha", type=float, default=None,
                     help="c3: how strongly the synthetic model continues its token cycles (default: by kind of head, see C3_ALPHA_BY_HEAD)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
@@ -813,6 +913,8 @@ def main():
         return run_c4(args)
     if args.workload == "c3":
         return run_reference_c3(args) if args.impl == "reference" else run_c3(args)
+    if args.workload == "prefill-dense":
+        return run_prefill_dense(args)
     if args.impl == "reference":
         return run_reference_c2(args)
 

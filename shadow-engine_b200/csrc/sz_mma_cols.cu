@@ -11,9 +11,11 @@
 // Shape of the kernel.  A block owns 128 weight rows (the M side of the instruction) and one tile of up to 256 tokens (the N side);
 // the accumulator D[128 rows][NT tokens] lives in tensor memory (NT columns of 128 lanes), so no register holds a partial sum until
 // the end.  K advances in steps of 64:
-//   warp 0      the copy warp.  Raw Q8_0 bytes of the block's rows arrive 256 columns (272 bytes a row: a multiple of 16, which 68
-//               bytes of one 64-column step is not) at a time by cp.async.bulk, double-buffered; the token tile of a step, already in
-//               f16 and in the instruction's own shared-memory order (written once by sz_x16_pack_kernel), is one bulk copy.
+//   warp 0      the copy warp.  Raw Q8_0 bytes of the block's 128 rows arrive 256 columns at a time (272 bytes a row: a multiple of
+//               16, which the 68 bytes of one 64-column step are not) as ONE tiled TMA copy (cp.async.bulk.tensor.2d over the
+//               matrix seen as [rows][row bytes / 2] 16-bit words, box 136 x 128; 128 separate 272-byte bulk copies a piece kept
+//               the copy engine, not the tensor core, as the bound), double-buffered; the token tile of a step, already in f16 and
+//               in the instruction's own shared-memory order (written once by sz_x16_pack_kernel), is one bulk copy.
 //   warps 1..8  decode: two threads a weight row turn a step's 2 blocks a row into f16 and store them in the canonical K-major
 //               no-swizzle order (8 rows x 16 bytes core matrices), then fence.proxy.async and arrive.
 //   warp 9      one thread issues the step's 4 tcgen05.mma (K = 16 each) from shared-memory descriptors and commits them to the
@@ -21,6 +23,7 @@
 // After the last step warps 1..8 read the accumulator with tcgen05.ld (lane = weight row, column = token) and write Y: for one
 // token, the 32 lanes of a warp write 32 consecutive rows.
 // Every wait is bounded; a wait that runs out records where in the error word, and the block still frees its tensor memory.
+#include <cuda.h>   // CUtensorMap and its enums; the encoder's entry point is asked of the runtime, nothing links against the driver
 #include "sz_common.cuh"
 #include "sz_formats.cuh"
 
@@ -67,6 +70,37 @@ __device__ __forceinline__ void mc_commit(u64* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(sz_smem_addr(bar)) : "memory");
 }
 
+// Block KB (0..7) of a row's 272 raw bytes -> 32 f16 weights, stored as the 4 chunks of 8 the block covers (chunk stride 16 * 128
+// bytes).  The block starts 34 * KB bytes into the row: not a multiple of 16, so three aligned 16-byte loads cover it and the
+// bytes are brought into place by funnel shifts whose amounts are known at compile time.  A weight is d * q rounded once to f16;
+// d is f16 and q an integer below 128, so the f16 product (one rounding of the exact product) is that same value.  q as f16: the
+// byte with its sign bit flipped is q + 128, placed under exponent 0x64 it reads 1024 + q + 128, and 1152 is subtracted.
+template <int KB>
+__device__ __forceinline__ void mc_decode_block(const u8* __restrict__ rowp, u8* __restrict__ dst) {
+    constexpr int OFF = KB * 34, BASE = OFF & ~15, SH = OFF & 15;
+    const uint4 v0 = *(const uint4*)(rowp + BASE), v1 = *(const uint4*)(rowp + BASE + 16), v2 = *(const uint4*)(rowp + BASE + 32);
+    const u32 W[12] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w, v2.x, v2.y, v2.z, v2.w};
+    constexpr int DW = SH / 4, DS = (SH % 4) * 8;
+    const u32 dbits = (W[DW] >> DS) & 0xffffu;
+    const u32 d2 = dbits | (dbits << 16);
+    const __half2 dh = *(const __half2*)&d2;
+    const u32 bias = 0x64806480u;   // 1152, twice
+    const __half2 bh = *(const __half2*)&bias;
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        u32 o[4];
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int b = SH + 2 + 4 * (2 * c + i);                       // first byte of this word of four q
+            const u32 q4 = (b % 4 ? __funnelshift_r(W[b / 4], W[b / 4 + 1], (b % 4) * 8) : W[b / 4]) ^ 0x80808080u;
+            const u32 lo = __byte_perm(q4, 0x64646464u, 0x4140), hi = __byte_perm(q4, 0x64646464u, 0x4342);   // {q0, q1}, {q2, q3} as 1024 + q + 128
+            const __half2 w0 = __hmul2(dh, __hsub2(*(const __half2*)&lo, bh)), w1 = __hmul2(dh, __hsub2(*(const __half2*)&hi, bh));
+            o[2 * i] = *(const u32*)&w0; o[2 * i + 1] = *(const u32*)&w1;
+        }
+        *(uint4*)(dst + c * 16 * 128) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
 // The token rows as f16 in the order the instruction reads them from shared memory, so that a step's tile is one contiguous copy:
 // out[tile][step][chunk c of 8 columns][token t][8 halves]; tokens past m are zero.  One thread a 16-byte unit.
 __global__ void __launch_bounds__(256) sz_x16_pack_kernel(const float* __restrict__ x, long long xs, int m, int cols, int nt, uint4* __restrict__ out) {
@@ -91,8 +125,8 @@ __global__ void __launch_bounds__(256) sz_x16_pack_kernel(const float* __restric
 }
 
 __global__ void __launch_bounds__(MC_THREADS, 1)
-sz_mma_cols_q8_kernel(const u8* __restrict__ w, const uint4* __restrict__ x16, float* __restrict__ y, long long ys, int rows, int cols, int m,
-                      int nt, u32* __restrict__ err) {
+sz_mma_cols_q8_kernel(const __grid_constant__ CUtensorMap wmap, const uint4* __restrict__ x16, float* __restrict__ y, long long ys, int rows, int cols,
+                      int m, int nt, u32* __restrict__ err) {
     extern __shared__ __align__(128) u8 smem[];
     u8* raw = smem;                                   // [2][128 rows][272]
     u8* sa = raw + 2 * MC_RAW_BYTES;                  // [stages][16 chunks][16 row groups][128]
@@ -103,7 +137,6 @@ sz_mma_cols_q8_kernel(const u8* __restrict__ w, const uint4* __restrict__ x16, f
     const int row0 = blockIdx.x * MC_BM, tile = blockIdx.y;
     const int valid = rows - row0 < MC_BM ? rows - row0 : MC_BM;
     const int steps = cols / MC_KT;
-    const size_t row_bytes = (size_t)(cols / 32) * 34;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < MC_STAGES; i++) { sz_mbar_init(&S->full[i], 256 + 1); sz_mbar_init(&S->empty[i], 1); }
@@ -125,12 +158,15 @@ sz_mma_cols_q8_kernel(const u8* __restrict__ w, const uint4* __restrict__ x16, f
     if (warp == 0) {
         // ---- copies: raw weight bytes one 256-column piece ahead of the decoders, token tiles as stages come free
         const int pieces = steps / 4;
-        auto issue_raw = [&](int ss) {
+        auto issue_raw = [&](int ss) {   // x = 136 * ss words = 272 * ss bytes: a multiple of 16; rows past the matrix arrive as zeros
             const int rb = ss & 1;
-            if (lane == 0) sz_mbar_expect_tx(&S->raw_full[rb], (u32)valid * MC_RAW_ROW);
-            __syncwarp();
-            for (int r = lane; r < valid; r += 32)
-                sz_bulk_g2s(raw + rb * MC_RAW_BYTES + r * MC_RAW_ROW, w + (size_t)(row0 + r) * row_bytes + (size_t)ss * MC_RAW_ROW, MC_RAW_ROW, &S->raw_full[rb]);
+            if (lane == 0) {
+                sz_mbar_expect_tx(&S->raw_full[rb], (u32)MC_RAW_BYTES);
+                asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                                 sz_smem_addr(raw + rb * MC_RAW_BYTES)),
+                             "l"(&wmap), "r"(ss * (MC_RAW_ROW / 2)), "r"(row0), "r"(sz_smem_addr(&S->raw_full[rb]))
+                             : "memory");
+            }
         };
         issue_raw(0);
         for (int ks = 0; ks < steps && !failed; ks++) {
@@ -147,35 +183,38 @@ sz_mma_cols_q8_kernel(const u8* __restrict__ w, const uint4* __restrict__ x16, f
             }
         }
     } else if (warp <= 8) {
-        // ---- decode: thread d takes weight row d / 2, block d % 2 of the step
-        const int d = threadIdx.x - 32, r = d >> 1, half = d & 1;
-        for (int ks = 0; ks < steps && !failed; ks++) {
-            const int st = ks % MC_STAGES, ss = ks / 4, rb = ss & 1, j = ks & 3;
-            if (ks >= MC_STAGES && !sz_mbar_wait(&S->empty[st], ((ks / MC_STAGES) - 1) & 1, MC_WAIT)) { failed = 3; break; }
-            if (j == 0 && !sz_mbar_wait(&S->raw_full[rb], (ss / 2) & 1, MC_WAIT)) { failed = 4; break; }
-            u8* dst = sa + st * MC_A_BYTES + ((half * 4) * 16 + (r >> 3)) * 128 + (r & 7) * 16;
-            if (r < valid) {
-                const u16* blk = (const u16*)(raw + rb * MC_RAW_BYTES + r * MC_RAW_ROW + (j * 2 + half) * 34);
-                const float dd = sz_f16_to_f32(blk[0]);
+        // ---- decode: thread d takes weight row d % 128 and block d / 128 of the step (a warp: 32 consecutive rows of one block
+        // index, so its 16-byte stores fill 512 consecutive bytes and its block index is known when the code is compiled)
+        const int d = threadIdx.x - 32, r = d & 127, half = d >> 7;
+        for (int ks0 = 0; ks0 < steps && !failed; ks0 += 4) {
+            const int ss = ks0 / 4, rb = ss & 1;
+            if (!sz_mbar_wait(&S->raw_full[rb], (ss / 2) & 1, MC_WAIT)) { failed = 4; break; }
+            const u8* rowp = raw + rb * MC_RAW_BYTES + r * MC_RAW_ROW;
 #pragma unroll
-                for (int c = 0; c < 4; c++) {
-                    u32 o[4];
-#pragma unroll
-                    for (int p = 0; p < 4; p++) {
-                        const u16 q2 = blk[1 + c * 4 + p];
-                        const float w0 = __fmul_rn(dd, (float)(signed char)(q2 & 0xff)), w1 = __fmul_rn(dd, (float)(signed char)(q2 >> 8));
-                        const __half2 h = __floats2half2_rn(w0, w1);
-                        o[p] = *(const u32*)&h;
+            for (int j = 0; j < 4; j++) {
+                const int ks = ks0 + j, st = ks % MC_STAGES;
+                if (ks >= MC_STAGES && !sz_mbar_wait(&S->empty[st], ((ks / MC_STAGES) - 1) & 1, MC_WAIT)) { failed = 3; break; }
+                u8* dst = sa + st * MC_A_BYTES + ((half * 4) * 16 + (r >> 3)) * 128 + (r & 7) * 16;
+                if (r < valid) {
+                    switch (2 * j + half) {   // j is an unrolled loop's counter and half is the same for a whole warp
+                        case 0: mc_decode_block<0>(rowp, dst); break;
+                        case 1: mc_decode_block<1>(rowp, dst); break;
+                        case 2: mc_decode_block<2>(rowp, dst); break;
+                        case 3: mc_decode_block<3>(rowp, dst); break;
+                        case 4: mc_decode_block<4>(rowp, dst); break;
+                        case 5: mc_decode_block<5>(rowp, dst); break;
+                        case 6: mc_decode_block<6>(rowp, dst); break;
+                        default: mc_decode_block<7>(rowp, dst); break;
                     }
-                    *(uint4*)(dst + c * 16 * 128) = make_uint4(o[0], o[1], o[2], o[3]);
-                }
-            } else {
+                } else {
 #pragma unroll
-                for (int c = 0; c < 4; c++) *(uint4*)(dst + c * 16 * 128) = make_uint4(0, 0, 0, 0);
+                    for (int c = 0; c < 4; c++) *(uint4*)(dst + c * 16 * 128) = make_uint4(0, 0, 0, 0);
+                }
+                mc_fence_async();                 // the tensor core reads shared memory through the async proxy
+                mc_arrive(&S->full[st]);
             }
-            mc_fence_async();                 // the tensor core reads shared memory through the async proxy
-            mc_arrive(&S->full[st]);
-            if (j == 3 || ks == steps - 1) mc_arrive(&S->raw_empty[rb]);
+            if (failed) break;
+            mc_arrive(&S->raw_empty[rb]);
         }
     } else {
         // ---- issue
@@ -230,6 +269,18 @@ sz_mma_cols_q8_kernel(const u8* __restrict__ w, const uint4* __restrict__ x16, f
     if (threadIdx.x == 0 && S->failed) atomicMax(err, S->failed);
 }
 
+typedef CUresult (*McEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+McEncodeTiled mc_encoder() {
+    static McEncodeTiled fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess) fn = (McEncodeTiled)p;
+    }
+    return fn;
+}
+
 int mc_nt(int m) {
     const int r = (m + 15) & ~15;
     return r < MC_NT_MAX ? r : MC_NT_MAX;
@@ -266,10 +317,21 @@ extern "C" int sz_mma_cols(const sz_tensor* w, uint64_t x, int64_t xs, uint64_t 
         SZ_CUDA(cudaFuncSetAttribute(sz_mma_cols_q8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * MC_RAW_BYTES + MC_STAGES * (MC_A_BYTES + MC_NT_MAX * MC_KT * 2) + (int)sizeof(McSmem)));
         set = true;
     }
+    McEncodeTiled enc = mc_encoder();
+    if (!enc) return sz_fail(SZ_E_CUDA, "sz_mma_cols: the driver has no cuTensorMapEncodeTiled");
+    CUtensorMap wmap;
+    {   // the matrix as [rows][row bytes / 2] 16-bit words; a box is 272 bytes of 128 rows
+        const cuuint64_t row_bytes = (cuuint64_t)(cols / 32) * 34;
+        const cuuint64_t gdim[2] = {row_bytes / 2, (cuuint64_t)rows}, gstride[1] = {row_bytes};
+        const cuuint32_t box[2] = {MC_RAW_ROW / 2, MC_BM}, es[2] = {1, 1};
+        const CUresult r = enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (void*)w->data, gdim, gstride, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return sz_fail(SZ_E_CUDA, "sz_mma_cols: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    }
     const long long units = (long long)tiles * (cols / MC_KT) * 8 * nt;
     SZ_CUDA(sz_launch("x16_pack", sz_x16_pack_kernel, dim3((unsigned)((units + 255) / 256 < 1184 ? (units + 255) / 256 : 1184)), dim3(256), 0, st, false,
                       (const float*)x, (long long)xs, m, cols, nt, x16));
-    SZ_CUDA(sz_launch("mma_cols_q8", sz_mma_cols_q8_kernel, dim3((rows + MC_BM - 1) / MC_BM, tiles), dim3(MC_THREADS), smem, st, false, (const u8*)w->data,
+    SZ_CUDA(sz_launch("mma_cols_q8", sz_mma_cols_q8_kernel, dim3((rows + MC_BM - 1) / MC_BM, tiles), dim3(MC_THREADS), smem, st, false, wmap,
                       (const uint4*)x16, (float*)y, (long long)ys, rows, cols, m, nt, err));
     return SZ_OK;
 }
