@@ -117,8 +117,8 @@ int sz_moe_launches(const sz_moe_layer* layer);
  * Shapes and tensors as Config::from_gguf and Model read them (crates/shadowzero-model/src/forward.rs:25-142, tensor names in
  * crates/shadowzero-model/src/exl3_model.rs:223-243).  Every tensor is stored as the reference stores it: ggml [cols = in,
  * rows = out] with whole rows contiguous, or one EXL3 blob.  `data` is a device address for the library (a host address for
- * the CPU oracle, which reads the same structs).  The per-layer-embedding (PLE) branch and the sparse indexer are not part of
- * this build: a model described here has neither (the indexer would only select below its budget anyway). */
+ * the CPU oracle, which reads the same structs).  The per-layer-embedding (PLE) branch is not part of this build: a model
+ * described here has none.  The sparse indexer is optional (cfg.idx_heads). */
 typedef struct sz_tensor {
     int32_t type;      /* ggml type id; 0 rows = absent */
     int32_t reserved;
@@ -136,6 +136,10 @@ typedef struct sz_model_config {
     float eps;
     float reserved;
     double rope_theta;
+    /* The sparse indexer of the attention layers (forward.rs:63-68, 137-140: attention.indexer.head_count, .key_length, .top_k):
+     * heads, head width, and the budget of positions a query attends to.  idx_heads = 0: the model has no indexer and every
+     * query attends to every position (what the reference computes while no more than idx_budget positions are complete). */
+    int32_t idx_heads, idx_dim, idx_budget, idx_reserved;
 } sz_model_config;
 
 typedef struct sz_hc {          /* a hyper-connection read: forward.rs:797-817 */
@@ -151,6 +155,11 @@ typedef struct sz_layer {
     sz_tensor attn_qkv, attn_gate, ssm_beta, ssm_alpha, ssm_conv1d, ssm_a, ssm_dt_bias, ssm_norm, ssm_out;
     /* gated attention (forward.rs:898-1007) */
     sz_tensor attn_q, attn_k, attn_v, attn_q_norm, attn_k_norm, attn_output;
+    /* the sparse indexer of a gated-attention layer (forward.rs:906-976): indexer.q_proj [hidden -> idx_heads * idx_dim],
+     * indexer.k_proj [hidden -> idx_dim], indexer.q_norm / k_norm F32 [idx_dim]; idx_ratio = positions a pooled block
+     * (attention.compress_ratios; 0 is read as 1, as the reference reads it).  Absent (rows 0) when cfg.idx_heads = 0. */
+    sz_tensor idx_q, idx_k, idx_q_norm, idx_k_norm;
+    int32_t idx_ratio, idx_reserved;
     sz_moe_layer moe;
 } sz_layer;
 

@@ -76,6 +76,10 @@ def lib():
         L.szo_tree_accept_sampled.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_uint64, C.c_int,
                                               C.c_void_p, C.POINTER(C.c_uint32)]
         L.szo_tree_accept_greedy.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.POINTER(C.c_uint32)]
+        L.szo_session_selected.restype = C.c_int
+        L.szo_session_selected.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
+        L.szo_session_idx_scores.restype = C.c_int
+        L.szo_session_idx_scores.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int]
         L.szo_session_state.restype = C.c_void_p
         L.szo_session_state.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
         L.szo_lookup.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p]
@@ -245,6 +249,17 @@ class Session:
     def __len__(self):
         return lib().szo_session_len(self.h)
 
+    def clone(self):
+        """A copy of the whole state: the snapshot the CPU side of the speculation loop takes before a pass."""
+        c = Session.__new__(Session)
+        c.hm, c.vocab = self.hm, self.vocab
+        c.h = lib().szo_session_clone(self.h)
+        return c
+
+    def assign(self, other):
+        """Become a copy of `other` (restore a snapshot)."""
+        lib().szo_session_assign(self.h, other.h)
+
     def step(self, token, want_logits=True, want_u=False):
         lg = np.empty(self.vocab, dtype=np.float32) if want_logits else None
         u = np.empty(self.hm.cfg["hidden"], dtype=np.float32) if want_u else None
@@ -270,6 +285,17 @@ class Session:
         p = lib().szo_session_state(self.h, what, layer, C.byref(n))
         raw = np.frombuffer(C.string_at(p, n.value), dtype=np.uint8).copy()
         return raw.view(np.float32) if what < 2 else raw
+
+    def selected(self, layer):
+        """Positions attention layer `layer` attended to in the last step, ascending (the trace stream `layerL.selected`)."""
+        out = np.empty(len(self) + 8, dtype=np.int32)
+        n = lib().szo_session_selected(self.h, layer, _p(out), out.size)
+        return out[:n].copy()
+
+    def idx_scores(self, layer):
+        out = np.empty(len(self) + 8, dtype=np.float32)
+        n = lib().szo_session_idx_scores(self.h, layer, _p(out), out.size)
+        return out[:n].copy()
 
     def routes(self):
         n, k = self.hm.cfg["n_layer"], self.hm.cfg["n_expert_used"]

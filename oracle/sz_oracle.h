@@ -108,6 +108,10 @@ int szo_tree_accept_greedy(const float* logits, int vocab, const uint32_t* ids, 
 void szo_session_fill_synthetic(szo_session* s, int len, uint32_t seed);
 /* one piece of the state: 0 recurrent state [v heads][d][d], 1 carried conv rows, 2 / 3 K / V cache [position][kv head][head] */
 const void* szo_session_state(const szo_session* s, int what, int l, size_t* bytes);
+/* the sparse indexer of attention layer l in the last step: the positions attended to (ascending; returns how many), and the
+ * block scores the selection was made by (0 when everything was attended to) */
+int szo_session_selected(const szo_session* s, int l, int32_t* out, int cap);
+int szo_session_idx_scores(const szo_session* s, int l, float* out, int cap);
 
 int szo_lookup(const uint32_t* hist, int n_hist, int k, const int* lens, int n_lens, uint32_t* out); /* engine.rs:829-839 */
 typedef struct szo_drafter szo_drafter;

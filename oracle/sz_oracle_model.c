@@ -111,6 +111,14 @@ typedef struct {
     uint8_t* kq; /* attention: positions x kv_heads x head_bytes (Q8 mode) */
     uint8_t* vq;
     size_t cap;  /* positions allocated */
+    /* the sparse indexer (forward.rs:282-286): raw keys, one per position, and the pooled key of every complete block */
+    float* idx_raw;   /* positions x idx_dim */
+    float* blocks;    /* complete blocks x idx_dim */
+    size_t n_blocks;  /* blocks whose pooled key is valid */
+    int32_t* sel;     /* positions the last step attended to, ascending */
+    size_t n_sel;
+    float* scores;    /* block scores of the last step that selected (n_scores of them) */
+    size_t n_scores;
 } layer_state;
 
 struct szo_session {
@@ -146,6 +154,7 @@ void szo_session_free(szo_session* s) {
     if (!s) return;
     for (int l = 0; l < s->m->cfg.n_layer; l++) {
         free(s->st[l].s); free(s->st[l].conv); free(s->st[l].k); free(s->st[l].v); free(s->st[l].kq); free(s->st[l].vq);
+        free(s->st[l].idx_raw); free(s->st[l].blocks); free(s->st[l].sel); free(s->st[l].scores);
     }
     free(s->st); free(s->routes); free(s->route_w); free(s);
 }
@@ -163,6 +172,12 @@ static void kv_reserve(szo_session* s, layer_state* L, size_t positions) {
     size_t rowq = (size_t)c->n_kv_head * szo_kv_q8_head_bytes(c->head_dim);
     if (s->kv_q8) { L->kq = (uint8_t*)realloc(L->kq, cap * rowq); L->vq = (uint8_t*)realloc(L->vq, cap * rowq); }
     else { L->k = (float*)realloc(L->k, cap * row * sizeof(float)); L->v = (float*)realloc(L->v, cap * row * sizeof(float)); }
+    if (c->idx_heads > 0) {
+        L->idx_raw = (float*)realloc(L->idx_raw, cap * (size_t)c->idx_dim * sizeof(float));
+        L->blocks = (float*)realloc(L->blocks, cap * (size_t)c->idx_dim * sizeof(float));
+        L->sel = (int32_t*)realloc(L->sel, cap * sizeof(int32_t));
+        L->scores = (float*)realloc(L->scores, cap * sizeof(float));
+    }
     L->cap = cap;
 }
 
@@ -179,6 +194,11 @@ void szo_session_assign(szo_session* dst, const szo_session* src) {
             kv_reserve(dst, &dst->st[l], src->len);
             if (src->kv_q8) { memcpy(dst->st[l].kq, src->st[l].kq, src->len * rowq); memcpy(dst->st[l].vq, src->st[l].vq, src->len * rowq); }
             else { memcpy(dst->st[l].k, src->st[l].k, src->len * row * sizeof(float)); memcpy(dst->st[l].v, src->st[l].v, src->len * row * sizeof(float)); }
+            if (c->idx_heads > 0 && src->st[l].idx_raw) {
+                memcpy(dst->st[l].idx_raw, src->st[l].idx_raw, src->len * (size_t)c->idx_dim * sizeof(float));
+                memcpy(dst->st[l].blocks, src->st[l].blocks, src->st[l].n_blocks * (size_t)c->idx_dim * sizeof(float));
+                dst->st[l].n_blocks = src->st[l].n_blocks;
+            }
         }
     }
 }
@@ -226,6 +246,13 @@ void szo_session_fill_synthetic(szo_session* s, int len, uint32_t seed) {
                     }
                 }
         }
+        if (c->idx_heads > 0) {   /* the indexer's raw keys of the history; the pooled block keys follow from them at the next step */
+            size_t id = (size_t)c->idx_dim;
+            for (size_t pos = 0; pos < (size_t)len; pos++)
+                for (size_t i = 0; i < id; i++)
+                    L->idx_raw[pos * id + i] = ((float)(fill_hash((uint64_t)pos, (uint32_t)i, seed ^ 0x51ed270bu, ai) % 2001u) - 1000.0f) * 1e-3f;
+            L->n_blocks = 0;
+        }
         ai++;
     }
     s->len = (size_t)len;
@@ -244,6 +271,20 @@ const void* szo_session_state(const szo_session* s, int what, int l, size_t* byt
     }
     *bytes = 0;
     return NULL;
+}
+
+/* The positions layer l attended to in the last step (ascending), and the block scores it selected by (n_scores = 0: it did not
+ * select).  The reference records the former as the trace stream `layerL.selected` (forward.rs:997-1004). */
+int szo_session_selected(const szo_session* s, int l, int32_t* out, int cap) {
+    const layer_state* L = &s->st[l];
+    if (!L->sel) return -1;
+    for (size_t i = 0; i < L->n_sel && (int)i < cap; i++) out[i] = L->sel[i];
+    return (int)L->n_sel;
+}
+int szo_session_idx_scores(const szo_session* s, int l, float* out, int cap) {
+    const layer_state* L = &s->st[l];
+    for (size_t i = 0; i < L->n_scores && (int)i < cap; i++) out[i] = L->scores[i];
+    return (int)L->n_scores;
 }
 
 /* forward.rs:797-817 */
@@ -379,6 +420,75 @@ static void attention(szo_session* s, int l, const float* u, float* y) {
         }
     }
     free(kh);
+    /* ---- the sparse indexer (forward.rs:930-976): positions in blocks of `ratio`; every COMPLETE block is scored against the query by
+     * its pooled key; the best budget / ratio blocks and the incomplete tail are attended to.  With no more complete blocks than
+     * that, everything is. */
+    size_t nt = n;           /* positions attended to */
+    int32_t* toks = NULL;    /* NULL: all of them */
+    if (c->idx_heads > 0 && L->idx_q.data) {
+        size_t ratio = L->idx_ratio > 0 ? (size_t)L->idx_ratio : 1, id = (size_t)c->idx_dim, ih = (size_t)c->idx_heads;
+        float* iq = (float*)malloc(ih * id * sizeof(float));
+        float* ik = (float*)malloc(id * sizeof(float));
+        mv(&L->idx_q, u, iq, s->threads);
+        mv(&L->idx_k, u, ik, s->threads);
+        const float *iqn = f32p(&L->idx_q_norm), *ikn = f32p(&L->idx_k_norm);
+        memcpy(st->idx_raw + (n - 1) * id, ik, id * sizeof(float));
+        size_t nb = n / ratio;
+        if (st->n_blocks > nb) st->n_blocks = nb;
+        float* pooled = (float*)malloc(id * sizeof(float));
+        while (st->n_blocks < nb) {
+            size_t b = st->n_blocks;
+            for (size_t d = 0; d < id; d++) pooled[d] = 0.0f;
+            for (size_t r = 0; r < ratio; r++)
+                for (size_t d = 0; d < id; d++) pooled[d] += st->idx_raw[(b * ratio + r) * id + d];
+            for (size_t d = 0; d < id; d++) pooled[d] /= (float)ratio;
+            szo_rmsnorm(pooled, ikn, id, c->eps, st->blocks + b * id);
+            rope_apply(st->blocks + b * id, (double)(b * ratio), c->rope_dims, c->rope_theta);
+            st->n_blocks++;
+        }
+        free(pooled);
+        size_t keep = (size_t)c->idx_budget / ratio;
+        st->n_scores = 0;
+        if (nb > keep) {
+            float* qs = (float*)malloc(ih * id * sizeof(float));
+            for (size_t h = 0; h < ih; h++) {
+                szo_rmsnorm(iq + h * id, iqn, id, c->eps, qs + h * id);
+                rope_apply(qs + h * id, pos, c->rope_dims, c->rope_theta);
+            }
+            float norm = sqrtf((float)id);
+            for (size_t b = 0; b < nb; b++) {
+                const float* kb = st->blocks + b * id;
+                float sc = 0.0f;
+                for (size_t h = 0; h < ih; h++) {
+                    double dot = 0.0;
+                    for (size_t d = 0; d < id; d++) dot += (double)qs[h * id + d] * (double)kb[d];
+                    float f = (float)dot;
+                    sc += f > 0.0f ? f : 0.0f;   /* f32::max(0.0): a NaN gives 0 */
+                }
+                st->scores[b] = sc / norm;
+            }
+            st->n_scores = nb;
+            free(qs);
+            /* the `keep` best, score descending, block ascending among equals (a stable descending sort) */
+            uint8_t* taken = (uint8_t*)calloc(nb, 1);
+            for (size_t k = 0; k < keep; k++) {
+                size_t best = nb;
+                for (size_t b = 0; b < nb; b++)
+                    if (!taken[b] && (best == nb || st->scores[b] > st->scores[best])) best = b;
+                taken[best] = 1;
+            }
+            toks = st->sel;
+            nt = 0;
+            for (size_t b = 0; b < nb; b++)
+                if (taken[b])
+                    for (size_t r = 0; r < ratio; r++) toks[nt++] = (int32_t)(b * ratio + r);
+            for (size_t t = nb * ratio; t < n; t++) toks[nt++] = (int32_t)t;
+            free(taken);
+        }
+        if (!toks) { for (size_t t = 0; t < n; t++) st->sel[t] = (int32_t)t; }
+        st->n_sel = nt;
+        free(iq); free(ik);
+    }
     /* dequantised views for the Q8 cache (one group at a time) */
     float *kview = NULL, *vview = NULL;
     if (s->kv_q8) { kview = (float*)malloc(n * hd * sizeof(float)); vview = (float*)malloc(n * hd * sizeof(float)); }
@@ -397,21 +507,23 @@ static void attention(szo_session* s, int l, const float* u, float* y) {
         }
         const float* qh = q + h * hd;
         double mx = -1.7976931348623157e308; /* f64::MIN */
-        for (size_t t = 0; t < n; t++) {
+        for (size_t ti = 0; ti < nt; ti++) {
+            size_t t = toks ? (size_t)toks[ti] : ti;
             const float* kt = s->kv_q8 ? kview + t * hd : st->k + (t * nkv + g) * hd;
             double sc = 0.0;
             for (size_t i = 0; i < hd; i++) sc += (double)qh[i] * (double)kt[i];
             sc *= scale;
-            ex[t] = sc;
+            ex[ti] = sc;
             mx = sc > mx ? sc : mx;
         }
         double zs = 0.0;
-        for (size_t t = 0; t < n; t++) { ex[t] = exp(ex[t] - mx); zs += ex[t]; }
+        for (size_t ti = 0; ti < nt; ti++) { ex[ti] = exp(ex[ti] - mx); zs += ex[ti]; }
         for (size_t j = 0; j < hd; j++) {
             double acc = 0.0;
-            for (size_t t = 0; t < n; t++) {
+            for (size_t ti = 0; ti < nt; ti++) {
+                size_t t = toks ? (size_t)toks[ti] : ti;
                 float vv = s->kv_q8 ? vview[t * hd + j] : st->v[(t * nkv + g) * hd + j];
-                acc += ex[t] * (double)vv;
+                acc += ex[ti] * (double)vv;
             }
             o[h * hd + j] = (float)(acc / zs) * szo_sigmoid(gate[h * hd + j]);
         }

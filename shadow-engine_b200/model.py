@@ -19,7 +19,8 @@ class Tensor(C.Structure):
 class ModelConfig(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("n_layer", "hidden", "streams", "hc_rank", "vocab", "n_head", "n_kv_head", "head_dim", "rope_dims",
                                          "n_expert", "n_expert_used", "expert_ff", "shared_ff", "ssm_k_heads", "ssm_v_heads", "ssm_head_dim",
-                                         "conv_k", "attn_interval")] + [("eps", C.c_float), ("reserved", C.c_float), ("rope_theta", C.c_double)]
+                                         "conv_k", "attn_interval")] + [("eps", C.c_float), ("reserved", C.c_float), ("rope_theta", C.c_double)] + \
+               [(n, C.c_int32) for n in ("idx_heads", "idx_dim", "idx_budget", "idx_reserved")]
 
 
 class Hc(C.Structure):
@@ -29,7 +30,9 @@ class Hc(C.Structure):
 class Layer(C.Structure):
     _fields_ = [("hc_attn", Hc), ("hc_ffn", Hc)] + \
                [(n, Tensor) for n in ("attn_qkv", "attn_gate", "ssm_beta", "ssm_alpha", "ssm_conv1d", "ssm_a", "ssm_dt_bias", "ssm_norm", "ssm_out",
-                                      "attn_q", "attn_k", "attn_v", "attn_q_norm", "attn_k_norm", "attn_output")] + [("moe", szlib.MoeLayerC)]
+                                      "attn_q", "attn_k", "attn_v", "attn_q_norm", "attn_k_norm", "attn_output",
+                                      "idx_q", "idx_k", "idx_q_norm", "idx_k_norm")] + \
+               [("idx_ratio", C.c_int32), ("idx_reserved", C.c_int32), ("moe", szlib.MoeLayerC)]
 
 
 class Model(C.Structure):
@@ -181,6 +184,12 @@ def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, sha
             mat(p + "attn_output.weight", H, qd, dense_type)
             vec(p + "attn_q_norm.weight", torch.ones(cfg["head_dim"], device=device))
             vec(p + "attn_k_norm.weight", torch.ones(cfg["head_dim"], device=device))
+            if cfg.get("idx_heads", 0) > 0:
+                mat(p + "indexer.q_proj.weight", cfg["idx_heads"] * cfg["idx_dim"], H, dense_type)
+                mat(p + "indexer.k_proj.weight", cfg["idx_dim"], H, dense_type)
+                # (norm weights away from 1, so that a test notices a forgotten weight)
+                vec(p + "indexer.q_norm.weight", 1.0 + synth.normal((cfg["idx_dim"],), 0.1, seed, p + "indexer.q_norm", device))
+                vec(p + "indexer.k_norm.weight", 1.0 + synth.normal((cfg["idx_dim"],), 0.1, seed, p + "indexer.k_norm", device))
         else:
             mat(p + "attn_qkv.weight", ch, H, dense_type)
             mat(p + "attn_gate.weight", vd, H, dense_type)
@@ -198,8 +207,10 @@ def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, sha
 
 
 def _fill_config(c, cfg):
+    names = {n for n, _ in ModelConfig._fields_}
     for k, v in cfg.items():
-        setattr(c, k, v)
+        if k in names:
+            setattr(c, k, v)
 
 
 class _Placed:
@@ -234,6 +245,10 @@ class _Placed:
             if is_attention(cfg, l):
                 for n in ("attn_q", "attn_k", "attn_v", "attn_output", "attn_q_norm", "attn_k_norm"):
                     setattr(L, n, tens(p + n + ".weight"))
+                if cfg.get("idx_heads", 0) > 0:
+                    L.idx_q, L.idx_k = tens(p + "indexer.q_proj.weight"), tens(p + "indexer.k_proj.weight")
+                    L.idx_q_norm, L.idx_k_norm = tens(p + "indexer.q_norm.weight"), tens(p + "indexer.k_norm.weight")
+                    L.idx_ratio = int(cfg.get("idx_ratio", 4))
             else:
                 for n in ("attn_qkv", "attn_gate", "ssm_beta", "ssm_alpha", "ssm_out", "ssm_conv1d", "ssm_norm"):
                     setattr(L, n, tens(p + n + ".weight"))
