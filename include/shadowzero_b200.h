@@ -283,7 +283,14 @@ int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, uint64_t st
  * for tests and checkpoints.  DELTA_S: f32 [v heads][d][d] (key index, then value index) and DELTA_CONV: f32 [conv_k - 1][channels],
  * oldest row first, of DeltaNet layer `layer`; KV_K / KV_V: the first sz_session_len positions of attention layer `layer` in the
  * reference's order [position][kv head][head bytes] (head bytes: 4 head_dim, or the packed Q8_KV head).  `bytes` must be the exact
- * size of the piece; no pass may be pending. */
+ * size of the piece; no pass may be pending.
+ * IDX_SELECTED: what the sparse indexer of attention layer `layer` chose in the last pass (the reference's trace stream
+ * `layerL.selected`, forward.rs:997-1004, as block sets): u32 [SZ_MAX_VERIFY][words], words = sz_session_idx_words, bit b of row j
+ * = row j attended to complete block b (every complete block, while there are no more than budget / ratio of them).
+ * IDX_SCORES: f32 [SZ_MAX_VERIFY][32 * words]: the block scores of the last attention layer the last pass ran (rows that selected). */
+#define SZ_STATE_IDX_SELECTED 4
+#define SZ_STATE_IDX_SCORES 5
+int sz_session_idx_words(const sz_session* s);
 #define SZ_STATE_DELTA_S 0
 #define SZ_STATE_DELTA_CONV 1
 #define SZ_STATE_KV_K 2

@@ -6,7 +6,7 @@
 
 #include "sz_formats.cuh"
 
-#define SZ_DENSE_MAX_JOBS 4
+#define SZ_DENSE_MAX_JOBS 6
 #define SZ_EPI_NONE 0
 #define SZ_EPI_SILU_DIV 1      // silu(v / div)            (hyper-connection down, forward.rs:803)
 #define SZ_EPI_SIGMOID 2       // sigmoid(v)

@@ -9,9 +9,9 @@
 // Two placements.  HOST: the file is mapped and every tensor address points into the mapping (what a CPU consumer of struct
 // sz_model reads).  DEVICE: one device allocation, every tensor copied to a 256-byte aligned place of its own; EXL3 blobs are placed
 // so that their trellis starts on a 16-byte boundary, and EXL3 expert slices are re-strided to a multiple of 16 bytes, as the
-// kernels need (the file cannot give that: its alignment applies to the blob's first byte).  The per-layer-embedding branch and the
-// sparse indexer of the reference's checkpoints are not part of this build: their keys are read and must describe "none" (no
-// layer in ple.layers below block_count, every compress ratio 0), their tensors are ignored.
+// kernels need (the file cannot give that: its alignment applies to the blob's first byte).  The per-layer-embedding branch of the
+// reference's checkpoints is not part of this build: its keys are read and must describe "none" (no layer in ple.layers below
+// block_count), its tensors are ignored.  The sparse indexer is read when attention.indexer.head_count is not 0.
 #include "sz_common.cuh"
 
 #include <fcntl.h>
@@ -132,6 +132,7 @@ struct sz_weights {
     int64_t placed_bytes = 0;
     sz_model model = {};
     std::vector<sz_layer> layers;
+    std::vector<int64_t> ratios;   // attention.compress_ratios, when the file has a sparse indexer
     ~sz_weights() {
         if (dev) cudaFree(dev);
         if (map) munmap((void*)map, map_len);
@@ -339,6 +340,13 @@ int build(Placer& P) {
             if ((rc = tens(P, p + "attn_output.weight", qd, H, &L.attn_output))) return rc;
             if ((rc = vec(P, p + "attn_q_norm.weight", c.head_dim, &L.attn_q_norm))) return rc;
             if ((rc = vec(P, p + "attn_k_norm.weight", c.head_dim, &L.attn_k_norm))) return rc;
+            if (c.idx_heads > 0) {   // the sparse indexer (names: exl3_model.rs:227)
+                if ((rc = tens(P, p + "indexer.q_proj.weight", H, (int64_t)c.idx_heads * c.idx_dim, &L.idx_q))) return rc;
+                if ((rc = tens(P, p + "indexer.k_proj.weight", H, c.idx_dim, &L.idx_k))) return rc;
+                if ((rc = vec(P, p + "indexer.q_norm.weight", c.idx_dim, &L.idx_q_norm))) return rc;
+                if ((rc = vec(P, p + "indexer.k_norm.weight", c.idx_dim, &L.idx_k_norm))) return rc;
+                L.idx_ratio = l < (int)w->ratios.size() && w->ratios[l] > 0 ? (int32_t)w->ratios[l] : 1;
+            }
         } else {
             if ((rc = tens(P, p + "attn_qkv.weight", H, ch, &L.attn_qkv))) return rc;
             if ((rc = tens(P, p + "attn_gate.weight", H, vd, &L.attn_gate))) return rc;
@@ -421,10 +429,17 @@ extern "C" int sz_model_load_gguf(const char* path, int placement, uint64_t stre
     if (pl)
         for (int64_t l : pl->ints)
             if (l >= 0 && l < c.n_layer) { delete w; return sz_fail(SZ_E_TYPE, "%s: layer %lld has per-layer embeddings (ple.layers); that branch is not part of this build", path, (long long)l); }
-    const GVal* cr = w->key("attention.compress_ratios");
-    if (cr)
-        for (int64_t v : cr->ints)
-            if (v != 0) { delete w; return sz_fail(SZ_E_TYPE, "%s: a layer has a sparse indexer (attention.compress_ratios); that branch is not part of this build", path); }
+    // the sparse indexer (forward.rs:137-140): heads 0 = the file has none (its budget is then never reached)
+    {
+        int32_t ih = 0, id = 0, ib = 0;
+        const GVal* kh = w->key("attention.indexer.head_count");
+        if (kh && !get_u(w, "attention.indexer.head_count", &ih) && ih > 0) {
+            if ((rc = get_u(w, "attention.indexer.key_length", &id)) || (rc = get_u(w, "attention.indexer.top_k", &ib))) { delete w; return rc; }
+            c.idx_heads = ih; c.idx_dim = id; c.idx_budget = ib;
+            const GVal* cr = w->key("attention.compress_ratios");
+            if (cr) w->ratios = cr->ints;
+        }
+    }
     w->layers.assign((size_t)c.n_layer, sz_layer());
     w->model.layers = w->layers.data();
     Placer P{w};

@@ -7,6 +7,7 @@
 // recurrences for the kept rows from the pass's saved inputs - the reference's replay (session.rs:6245-6268) - into `cur ^ 1`,
 // then the buffers swap.  The KV cache is append-only: rejected positions are overwritten by the next pass.
 #include "sz_session_kernels.cuh"
+#include "sz_indexer.cuh"
 
 #include <cmath>
 #include <map>
@@ -62,6 +63,12 @@ struct sz_session {
     int has_samp = 0;
     int tree_pass = 0;      // the pass being built / pending is a tree pass (sz_session_verify_tree)
     float* fork = nullptr;  // [v heads][8][d * d]: recurrent states a tree pass branches off
+    // the sparse indexer (model.cfg.idx_heads > 0): see sz_indexer.cuh
+    float *i_q = nullptr, *i_k = nullptr, *i_qn = nullptr, *i_raw = nullptr, *i_blocks = nullptr, *i_scores = nullptr;
+    u32 *i_sel = nullptr, *i_trace = nullptr;
+    int32_t *i_list = nullptr, *i_count = nullptr;   // [8][ctx blocks]: each row's ascending list of position groups; [8]: how many
+    int64_t i_raw_layer = 0, i_blocks_layer = 0;
+    int i_ctx_blocks = 0, i_words = 0;
     int pending_committed;  // the pending pass was already committed on the device (acceptance modes GREEDY / ALL / SAMPLED)
     int device_keep;        // rows the device kept in that pass: known at launch for ALL, read by sz_session_result otherwise (-1: not read yet)
     int inflight;           // a pass was launched and the stream not synchronised since: the id staging buffer may still be read
@@ -88,7 +95,9 @@ static int sz_is_attn(const sz_model_config& c, int l) { return l % c.attn_inter
 
 struct SzSessLayout {
     int64_t r, r2, hc_acc, rope, rn, hdown, mix, u, g, y, d_xin, d_z, d_b, d_a, d_xc, d_beta, d_decay, d_og, S0, S1, conv0, conv1, a_qg, a_k, a_v, a_q, a_gate,
-        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, head_q2, head_sc, head_work, fork, total;
+        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, head_q2, head_sc, head_work, fork, i_q, i_k, i_qn, i_raw, i_blocks, i_scores, i_sel, i_list, i_count, i_trace, total;
+    int64_t i_raw_layer, i_blocks_layer;   // bytes of one attention layer's raw-key and pooled-key caches
+    int i_ctx_blocks, i_words;
     int64_t moe_bytes, S_bytes, conv_bytes, kv_bytes, head_work_bytes;
     int splits, splits2;
 };
@@ -156,6 +165,25 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
     L->tk_tmp = take(8 * M * nb * 64); L->top = take(4 * M * 128);
     L->ids = take(512);  // the rows' tokens, then (word 16) the sampler block of a sampled pass, then (word 32) the tables of a tree pass
     L->fork = take(4 * (int64_t)vh * M * c.ssm_head_dim * c.ssm_head_dim);
+    // the sparse indexer: projections of the pass, raw and pooled key caches of every attention layer, scores, per-row block sets,
+    // the merged list.  Sized by the smallest block (the most blocks) any layer uses.
+    L->i_ctx_blocks = 0; L->i_words = 0; L->i_raw_layer = 0; L->i_blocks_layer = 0;
+    if (c.idx_heads > 0) {
+        int rmin = 1 << 30;
+        for (int l = 0; l < c.n_layer; l++)
+            if (sz_is_attn(c, l)) { const int r = m->layers[l].idx_ratio > 0 ? m->layers[l].idx_ratio : 1; rmin = r < rmin ? r : rmin; }
+        if (rmin == 1 << 30) rmin = 1;
+        const int64_t id = c.idx_dim, ih = c.idx_heads, na = n_attn > 0 ? n_attn : 1;
+        L->i_ctx_blocks = ctx / rmin + 1;
+        L->i_words = (L->i_ctx_blocks + 31) / 32;
+        L->i_raw_layer = up256(4 * (int64_t)ctx * id);
+        L->i_blocks_layer = up256(4 * (int64_t)L->i_ctx_blocks * id);
+        L->i_q = take(4 * M * ih * id); L->i_k = take(4 * M * id); L->i_qn = take(4 * M * ih * id);
+        L->i_raw = take(na * L->i_raw_layer); L->i_blocks = take(na * L->i_blocks_layer);
+        L->i_scores = take(4 * M * (int64_t)L->i_ctx_blocks); L->i_sel = take(4 * M * (int64_t)L->i_words);
+        L->i_list = take(4 * M * (int64_t)L->i_ctx_blocks); L->i_count = take(64);
+        L->i_trace = take(4 * na * M * (int64_t)L->i_words);
+    }
     L->res = take(64); L->state = take(64);
     L->routes = take(4 * (int64_t)c.n_layer * M * SZ_MAX_TOPK); L->route_w = take(8 * (int64_t)c.n_layer * M * SZ_MAX_TOPK);
     int64_t moe_bytes = 0;
@@ -221,6 +249,8 @@ static int sz_model_check(const sz_model* m) {
     const int64_t H = c.hidden, CH = (int64_t)c.streams * H;
     const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim, ch = 2 * kd + vd;
     const int64_t qd = (int64_t)c.n_head * c.head_dim, kvd = (int64_t)c.n_kv_head * c.head_dim;
+    if (c.idx_heads < 0 || c.idx_heads > 8 || (c.idx_heads > 0 && (c.idx_dim < 16 || c.idx_dim > SZ_IDX_MAX_DIM || c.idx_dim % 4 || c.idx_dim < c.rope_dims || c.idx_budget < 1)))
+        return sz_fail(SZ_E_ARG, "indexer shape (heads %d, width %d, budget %d): up to 8 heads of 16..%d, at least the rotated dimensions", c.idx_heads, c.idx_dim, c.idx_budget, SZ_IDX_MAX_DIM);
     int rc;
     auto hc = [&](const sz_hc& h, const char* what, bool inject) -> int {
         int r2;
@@ -246,6 +276,14 @@ static int sz_model_check(const sz_model* m) {
             if ((rc = sz_dense_check(&L.attn_output, "attn_output", H, qd))) return rc;
             if ((rc = sz_f32_check(&L.attn_q_norm, "attn_q_norm", c.head_dim))) return rc;
             if ((rc = sz_f32_check(&L.attn_k_norm, "attn_k_norm", c.head_dim))) return rc;
+            if (c.idx_heads > 0) {
+                if ((rc = sz_dense_check(&L.idx_q, "indexer.q_proj", (int64_t)c.idx_heads * c.idx_dim, H))) return rc;
+                if ((rc = sz_dense_check(&L.idx_k, "indexer.k_proj", c.idx_dim, H))) return rc;
+                if ((rc = sz_f32_check(&L.idx_q_norm, "indexer.q_norm", c.idx_dim))) return rc;
+                if ((rc = sz_f32_check(&L.idx_k_norm, "indexer.k_norm", c.idx_dim))) return rc;
+                const int ratio = L.idx_ratio > 0 ? L.idx_ratio : 1;
+                if (ratio > SZ_AT_T || SZ_AT_T % ratio) return sz_fail(SZ_E_ARG, "layer %d: %d positions a block of the indexer (a power of two up to %d)", l, ratio, SZ_AT_T);
+            }
         } else {
             if ((rc = sz_dense_check(&L.attn_qkv, "attn_qkv", ch, H))) return rc;
             if ((rc = sz_dense_check(&L.attn_gate, "attn_gate", vd, H))) return rc;
@@ -285,6 +323,7 @@ extern "C" int sz_session_reset(sz_session* s, uint64_t stream) {
     SZ_CUDA(cudaMemsetAsync(s->conv[1], 0, L.conv_bytes, st));
     SZ_CUDA(cudaMemsetAsync(s->state, 0, 64, st));
     SZ_CUDA(cudaMemsetAsync(s->res, 0, 64, st));
+    if (s->i_count) SZ_CUDA(cudaMemsetAsync(s->i_count, 0, 64, st));
     if ((rc = sz_moe_scratch_init((uint64_t)s->moe_scratch, s->moe_scratch_bytes, stream))) return rc;
     s->len = 0; s->cur = 0; s->last_m = 0; s->pending_committed = 0; s->inflight = 0;
     return SZ_OK;
@@ -305,6 +344,8 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     int rc = sz_model_check(m);
     if (rc) return rc;
     if (!out || !mem || (mem & 255)) return sz_fail(SZ_E_ARG, "sz_session_create: memory must be 256-byte aligned");
+    if (m->cfg.idx_heads > 0 && (!(flags & SZ_KV_Q8) || m->cfg.n_head / m->cfg.n_kv_head * SZ_MAX_VERIFY > 64))
+        return sz_fail(SZ_E_ARG, "sz_session_create: the sparse indexer runs on the packed cache (SZ_KV_Q8) with at most 8 query heads a KV head");
     SzSessLayout L;
     if ((rc = sz_sess_layout(m, ctx, flags, &L))) return rc;
     if (bytes < L.total) return sz_fail(SZ_E_SCRATCH, "sz_session_create: %lld bytes given, %lld needed", (long long)bytes, (long long)L.total);
@@ -349,6 +390,12 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->ids = (int32_t*)(b + L.ids); s->res = (int32_t*)(b + L.res); s->state = (int32_t*)(b + L.state); s->routes = (int32_t*)(b + L.routes); s->route_w = (double*)(b + L.route_w);
     s->moe_scratch = b + L.moe; s->moe_scratch_bytes = L.moe_bytes;
     s->fork = (float*)(b + L.fork);
+    if (m->cfg.idx_heads > 0) {
+        s->i_q = (float*)(b + L.i_q); s->i_k = (float*)(b + L.i_k); s->i_qn = (float*)(b + L.i_qn); s->i_raw = (float*)(b + L.i_raw);
+        s->i_blocks = (float*)(b + L.i_blocks); s->i_scores = (float*)(b + L.i_scores); s->i_sel = (u32*)(b + L.i_sel);
+        s->i_list = (int32_t*)(b + L.i_list); s->i_count = (int32_t*)(b + L.i_count); s->i_trace = (u32*)(b + L.i_trace);
+        s->i_raw_layer = L.i_raw_layer; s->i_blocks_layer = L.i_blocks_layer; s->i_ctx_blocks = L.i_ctx_blocks; s->i_words = L.i_words;
+    }
     s->attn_splits = L.splits; s->attn_splits2 = L.splits2;
     if ((rc = sz_head_describe(m, flags, &s->head))) { delete s; return rc; }
     if (s->head.rows > 0) {
@@ -663,7 +710,7 @@ static int sz_attn_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8
 }
 
 template <int HD, int NQT>
-static int sz_attn2_go(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m, int* splits_used) {
+static int sz_attn2_go(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m, int* splits_used, int ratio) {
     const sz_model_config& c = s->model.cfg;
     static bool set = false;
     const size_t smem = (size_t)SzAttn2<HD>::smem_bytes(NQT);
@@ -672,20 +719,25 @@ static int sz_attn2_go(sz_session* s, cudaStream_t st, const u8* kc, const u8* v
     // chunks is half as long and the two blocks hide each other's barriers
     int splits = s->attn_splits2;
     if (smem + 2048 <= 113 * 1024 && 2 * splits <= (s->ctx + 255) / 256) splits *= 2;
+    if (ratio) {   // the sparse form: a block a (kv head, split, row); a row's list holds about the budget's positions, 128 or more a split
+        const int by_budget = (c.idx_budget + 127) / 128;
+        if (splits > by_budget) splits = by_budget < 1 ? 1 : by_budget;
+    }
     *splits_used = splits;
-    SZ_CUDA(sz_launch("attention_grouped", sz_attn2_kernel<HD, NQT>, dim3(c.n_kv_head, splits), dim3(256), smem, st, true, (const float*)s->a_q,
+    SZ_CUDA(sz_launch("attention_grouped", sz_attn2_kernel<HD, NQT>, dim3(c.n_kv_head, splits, ratio ? m : 1), dim3(256), smem, st, true, (const float*)s->a_q,
                       kc, vc, (int)c.n_head, (int)c.n_kv_head, m, s->ctx, (const int32_t*)s->state, splits, s->a_part, (u32*)(s->state + 2),
-                      (const SzTree*)(s->tree_pass ? s->ids + 32 : nullptr)));
+                      (const SzTree*)(s->tree_pass ? s->ids + 32 : nullptr), (const int32_t*)(ratio ? s->i_list : nullptr), (const int32_t*)s->i_count,
+                      s->i_ctx_blocks, ratio));
     return SZ_OK;
 }
 
 template <int HD>
-static int sz_attn2_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m, int* splits_used) {
+static int sz_attn2_launch(sz_session* s, cudaStream_t st, const u8* kc, const u8* vc, int m, int* splits_used, int ratio) {
     const sz_model_config& c = s->model.cfg;
-    const int qv = c.n_head / c.n_kv_head * m;
-    if (qv <= 16) return sz_attn2_go<HD, 1>(s, st, kc, vc, m, splits_used);
-    if (qv <= 32) return sz_attn2_go<HD, 2>(s, st, kc, vc, m, splits_used);
-    return sz_attn2_go<HD, 4>(s, st, kc, vc, m, splits_used);
+    const int qv = c.n_head / c.n_kv_head * (ratio ? 1 : m);   // the sparse form serves one row a block
+    if (qv <= 16) return sz_attn2_go<HD, 1>(s, st, kc, vc, m, splits_used, ratio);
+    if (qv <= 32) return sz_attn2_go<HD, 2>(s, st, kc, vc, m, splits_used, ratio);
+    return sz_attn2_go<HD, 4>(s, st, kc, vc, m, splits_used, ratio);
 }
 
 static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
@@ -703,20 +755,42 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     a.job[0] = sz_job(L.attn_q, s->a_qg, 2 * nh * hd);
     a.job[1] = sz_job(L.attn_k, s->a_k, nkv * hd);
     a.job[2] = sz_job(L.attn_v, s->a_v, nkv * hd);
+    const bool idx = c.idx_heads > 0;
+    const int ratio = idx ? (L.idx_ratio > 0 ? L.idx_ratio : 1) : 0;
+    if (idx) {
+        if (s->tree_pass) return sz_fail(SZ_E_ARG, "a tree pass on a model with the sparse indexer is not supported");
+        a.n_jobs = 5;
+        a.job[3] = sz_job(L.idx_q, s->i_q, c.idx_heads * c.idx_dim);
+        a.job[4] = sz_job(L.idx_k, s->i_k, c.idx_dim);
+    }
     int rc = sz_dense_launch(a, st, "attn_proj");
     if (rc) return rc;
+    if (idx) {
+        SzIdxGeom g;
+        g.heads = c.idx_heads; g.dim = c.idx_dim; g.ratio = ratio; g.keep = c.idx_budget / ratio; g.ctx_blocks = s->i_ctx_blocks; g.words = s->i_words;
+        float* raw = (float*)((u8*)s->i_raw + ai * s->i_raw_layer);
+        float* blocks = (float*)((u8*)s->i_blocks + ai * s->i_blocks_layer);
+        SZ_CUDA(sz_launch("idx_prep", sz_idx_prep_kernel, dim3(c.idx_heads + 2, m), dim3(128), 0, st, true, (const float*)s->i_q, (const float*)s->i_k,
+                          (const float*)L.idx_q_norm.data, (const float*)L.idx_k_norm.data, g, c.eps, (const int32_t*)s->state, (int)c.rope_dims,
+                          (const double*)s->rope_den, raw, blocks, s->i_qn));
+        const int nb_cap = s->ctx / ratio + 1;
+        SZ_CUDA(sz_launch("idx_score", sz_idx_score_kernel, dim3((nb_cap + 127) / 128), dim3(128), (size_t)m * c.idx_heads * c.idx_dim * 4, st, true,
+                          (const float*)s->i_qn, (const float*)blocks, g, m, (const int32_t*)s->state, s->i_scores));
+        SZ_CUDA(sz_launch("idx_select", sz_idx_select_kernel, dim3(m), dim3(1024), (size_t)s->i_words * 4, st, true, (const float*)s->i_scores, g, m,
+                          (const int32_t*)s->state, s->i_sel, s->i_list, s->i_count, s->i_trace + (size_t)ai * SZ_MAX_VERIFY * s->i_words));
+    }
     SZ_CUDA(sz_launch("attn_prep", sz_attn_prep_kernel, dim3(nh + 2 * nkv, m), dim3(128), 0, st, true, (const float*)s->a_qg, (const float*)s->a_k,
                       (const float*)s->a_v, (const float*)L.attn_q_norm.data, (const float*)L.attn_k_norm.data, nh, nkv, hd, s->ctx, c.eps,
                       (const int32_t*)s->state, (int)c.rope_dims, (const double*)s->rope_den, q8, kc, vc, s->a_q, s->a_gate,
                       (const SzTree*)(s->tree_pass ? s->ids + 32 : nullptr)));
     // the grouped tensor-core kernel serves the packed int8 cache with up to 64 queries a KV head; the simple kernel everything else
     static const bool generic_only = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;
-    const bool grouped = q8 && !generic_only && (nh / nkv) * m <= 64;
+    const bool grouped = q8 && (!generic_only || idx) && (nh / nkv) * m <= 64;
     int splits = grouped ? s->attn_splits2 : s->attn_splits;
     if (grouped) {
-        if (hd == 64) rc = sz_attn2_launch<64>(s, st, kc, vc, m, &splits);
-        else if (hd == 128) rc = sz_attn2_launch<128>(s, st, kc, vc, m, &splits);
-        else rc = sz_attn2_launch<256>(s, st, kc, vc, m, &splits);
+        if (hd == 64) rc = sz_attn2_launch<64>(s, st, kc, vc, m, &splits, ratio);
+        else if (hd == 128) rc = sz_attn2_launch<128>(s, st, kc, vc, m, &splits, ratio);
+        else rc = sz_attn2_launch<256>(s, st, kc, vc, m, &splits, ratio);
     } else {
         if (hd == 64) rc = sz_attn_launch<2>(s, st, kc, vc, m);
         else if (hd == 128) rc = sz_attn_launch<4>(s, st, kc, vc, m);
@@ -1097,6 +1171,18 @@ extern "C" int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, 
         sz_fill_kv_kernel<<<dim3(1024, s->n_attn), 128, 0, st>>>(s->kc, len, s->ctx, (int)c.n_kv_head, stride, (int)c.head_dim, q8, seed);
         sz_fill_kv_kernel<<<dim3(1024, s->n_attn), 128, 0, st>>>(s->vc, len, s->ctx, (int)c.n_kv_head, stride, (int)c.head_dim, q8, seed ^ 0x9e3779b9u);
         SZ_CUDA(cudaGetLastError());
+        if (s->i_raw) {   // the indexer's raw keys of the history and the pooled key of every complete block
+            sz_idx_fill_kernel<<<dim3(1024, s->n_attn), 128, 0, st>>>(s->i_raw, (long long)(s->i_raw_layer / 4), len, (int)c.idx_dim, seed ^ 0x51ed270bu);
+            for (int l = 0; l < c.n_layer; l++) {
+                if (!sz_is_attn(c, l)) continue;
+                const int ai = s->lb[l].attn_index, ratio = s->layers[l].idx_ratio > 0 ? s->layers[l].idx_ratio : 1;
+                if (len / ratio > 0)
+                    sz_idx_rebuild_kernel<<<len / ratio, 128, 0, st>>>((const float*)((u8*)s->i_raw + ai * s->i_raw_layer), (const float*)s->layers[l].idx_k_norm.data,
+                                                                       (int)c.idx_dim, ratio, c.eps, (int)c.rope_dims, (const double*)s->rope_den,
+                                                                       (float*)((u8*)s->i_blocks + ai * s->i_blocks_layer));
+            }
+            SZ_CUDA(cudaGetLastError());
+        }
     }
     s->h_pin[8] = len;
     SZ_CUDA(cudaMemcpyAsync(s->state, s->h_pin + 8, 4, cudaMemcpyHostToDevice, st));
@@ -1109,6 +1195,8 @@ extern "C" int sz_session_fill_synthetic(sz_session* s, int len, uint32_t seed, 
 // What GpuSession::snapshot (crates/shadowzero-cuda/src/session.rs:3407-3459) copies, one piece at a time: the recurrent state and the
 // carried conv rows of a DeltaNet layer (the current buffer), or the cache rows of an attention layer in the reference's order
 // [position][kv head][head bytes] (the library keeps them per KV head).  No pass may be pending.
+extern "C" int sz_session_idx_words(const sz_session* s) { return s ? s->i_words : -1; }
+
 extern "C" int sz_session_export(sz_session* s, int what, int layer, void* dst, int64_t bytes, uint64_t stream) {
     if (!s || !dst) return sz_fail(SZ_E_ARG, "sz_session_export: null argument");
     if (s->last_m) return sz_fail(SZ_E_ARG, "sz_session_export: a pass is pending; commit it first");
@@ -1134,6 +1222,20 @@ extern "C" int sz_session_export(sz_session* s, int what, int layer, void* dst, 
         for (int h = 0; h < c.n_kv_head && s->len > 0; h++)
             SZ_CUDA(cudaMemcpy2DAsync((u8*)dst + h * hb, (size_t)(c.n_kv_head * hb), base + (int64_t)h * s->ctx * hb, (size_t)hb, (size_t)hb, (size_t)s->len,
                                       cudaMemcpyDeviceToHost, st));
+    } else if (what == SZ_STATE_IDX_SELECTED || what == SZ_STATE_IDX_SCORES) {
+        if (!attn || !s->i_trace) return sz_fail(SZ_E_ARG, "sz_session_export: layer %d has no sparse indexer", layer);
+        const int ai = s->lb[layer].attn_index;
+        if (what == SZ_STATE_IDX_SELECTED) {
+            const int64_t n = 4 * (int64_t)SZ_MAX_VERIFY * s->i_words;
+            if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_export: %lld bytes given, the piece has %lld", (long long)bytes, (long long)n);
+            SZ_CUDA(cudaMemcpyAsync(dst, s->i_trace + (size_t)ai * SZ_MAX_VERIFY * s->i_words, (size_t)n, cudaMemcpyDeviceToHost, st));
+        } else {
+            const int64_t n = 4 * (int64_t)SZ_MAX_VERIFY * 32 * s->i_words;
+            if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_export: %lld bytes given, the piece has %lld", (long long)bytes, (long long)n);
+            for (int j = 0; j < SZ_MAX_VERIFY; j++)   // rows of i_ctx_blocks scores, of which 32 * words >= that many are asked for
+                SZ_CUDA(cudaMemcpyAsync((u8*)dst + (size_t)j * 32 * s->i_words * 4, s->i_scores + (size_t)j * s->i_ctx_blocks, (size_t)s->i_ctx_blocks * 4,
+                                        cudaMemcpyDeviceToHost, st));
+        }
     } else {
         return sz_fail(SZ_E_ARG, "sz_session_export: unknown piece %d", what);
     }

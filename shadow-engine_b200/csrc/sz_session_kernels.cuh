@@ -899,7 +899,11 @@ struct SzAttn2 {
 template <int HD, int NQT>
 __global__ void __launch_bounds__(256)
 sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const u8* __restrict__ vc, int nh, int nkv, int m, int ctx,
-                const int32_t* __restrict__ state, int splits, float* __restrict__ part, u32* __restrict__ err, const SzTree* __restrict__ tr) {
+                const int32_t* __restrict__ state, int splits, float* __restrict__ part, u32* __restrict__ err, const SzTree* __restrict__ tr,
+                const int32_t* __restrict__ glist, const int32_t* __restrict__ gcount, int gstride, int ratio) {
+    // glist != null: the sparse form, grid (kv heads, splits, rows).  The block serves ONE row (blockIdx.z) and walks that row's list
+    // of position groups (`ratio` positions each; row j's list at glist + j * gstride, gcount[j] long) instead of the positions
+    // themselves.  A chunk of 64 list positions is then 64 / ratio copies of a group each for K and for V.
     using A = SzAttn2<HD>;
     extern __shared__ __align__(128) u8 smem[];
     u64* bars = (u64*)smem;
@@ -910,20 +914,26 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
     float* rmax = S + 64 * A::SST;                           // running max, sum, and this chunk's rescale factor per query
     float* rsum = rmax + 64;
     float* ralpha = rsum + 64;
+    __shared__ int32_t cgrp[2][SZ_AT_T];     // sparse form: the groups of the chunk in each stage
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g8 = lane >> 2, q4 = lane & 3;
     const int kvh = blockIdx.x, sp = blockIdx.y;
+    const bool sparse = glist != nullptr;
+    const int jz = sparse ? (int)blockIdx.z : 0;   // sparse: the one row of this block
+    if (sparse) { glist += (size_t)jz * gstride; m = 1; }
     const int G = nh / nkv, QV = G * m;
     // The committed length belongs to the previous pass, and so does every cache position below it: the block's first chunk is
     // requested ahead of the dependency wait when it lies wholly there (the rows of this pass are written by the kernel before).
     int pos0;
     asm volatile("ld.global.s32 %0, [%1];" : "=r"(pos0) : "l"(state));
-    const int nmax = pos0 + m;
+    // (sparse: the list is written by the kernel before, so its length is read after the dependency wait, below)
+    int nmax = pos0 + m;
+    if (sparse) { sz_pdl_wait(); nmax = __ldcg(gcount + jz) * ratio; }
     const int per = ((nmax + splits - 1) / splits + SZ_AT_T - 1) / SZ_AT_T * SZ_AT_T;
     const int t0 = sp * per, t1 = min(nmax, t0 + per);
     const int nchunk = t1 > t0 ? (t1 - t0 + SZ_AT_T - 1) / SZ_AT_T : 0;
     const u8* kbase = kc + (size_t)kvh * ctx * A::HB;
     const u8* vbase = vc + (size_t)kvh * ctx * A::HB;
-    const bool early = nchunk > 0 && t0 + SZ_AT_T <= pos0;
+    const bool early = !sparse && nchunk > 0 && t0 + SZ_AT_T <= pos0;
     if (threadIdx.x == 0) {
         sz_mbar_init(&bars[0], 1);
         sz_mbar_init(&bars[1], 1);
@@ -949,7 +959,7 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
             const int dim = ks * 16 + 2 * qq + 8 * (r >> 1);
             float v0 = 0.f, v1 = 0.f;
             if (qv < QV) {
-                const int j = qv / G, h = kvh * G + qv % G;
+                const int j = jz + qv / G, h = kvh * G + qv % G;
                 const float* src = qin + ((size_t)j * nh + h) * HD + dim;
                 v0 = src[0] * scale; v1 = src[1] * scale;
             }
@@ -971,7 +981,23 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
         sz_bulk_g2s(dst, kbase + (size_t)t * A::HB, bytes, bar);
         sz_bulk_g2s(dst + SZ_AT_T * A::HB, vbase + (size_t)t * A::HB, bytes, bar);
     };
-    if (threadIdx.x == 0 && nchunk > 0 && !early) issue(0);
+    auto issue_sparse = [&](int ci) {  // warp 0: lane i copies group i of chunk ci (K and V) and notes the group for the masks
+        const int t = t0 + ci * SZ_AT_T;
+        const int np = min(SZ_AT_T, t1 - t), ng = np / ratio;        // list positions come in whole groups
+        u64* bar = &bars[ci & 1];
+        u8* dst = stage + (size_t)(ci & 1) * A::STAGE;
+        if (lane == 0) sz_mbar_expect_tx(bar, 2u * (u32)np * A::HB);
+        __syncwarp();
+        for (int i = lane; i < ng; i += 32) {
+            const int gi = __ldcg(glist + t / ratio + i);
+            cgrp[ci & 1][i] = gi;
+            const u32 bytes = (u32)ratio * A::HB;
+            sz_bulk_g2s(dst + (size_t)i * bytes, kbase + (size_t)gi * bytes, bytes, bar);
+            sz_bulk_g2s(dst + SZ_AT_T * A::HB + (size_t)i * bytes, vbase + (size_t)gi * bytes, bytes, bar);
+        }
+    };
+    if (sparse) { if (warp == 0 && nchunk > 0) issue_sparse(0); }
+    else if (threadIdx.x == 0 && nchunk > 0 && !early) issue(0);
     __syncthreads();
     float o[NQT][A::NT][4];
 #pragma unroll
@@ -980,7 +1006,8 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
         for (int b = 0; b < A::NT; b++) { o[a][b][0] = 0.f; o[a][b][1] = 0.f; o[a][b][2] = 0.f; o[a][b][3] = 0.f; }
     int failed = 0;
     for (int ci = 0; ci < nchunk; ci++) {
-        if (threadIdx.x == 0 && ci + 1 < nchunk) issue(ci + 1);
+        if (sparse) { if (warp == 0 && ci + 1 < nchunk) issue_sparse(ci + 1); }
+        else if (threadIdx.x == 0 && ci + 1 < nchunk) issue(ci + 1);
         if (!sz_mbar_wait(&bars[ci & 1], (ci >> 1) & 1)) failed = 1;
         if (__syncthreads_or(failed)) { failed = 1; break; }
         const u8* kch = stage + (size_t)(ci & 1) * A::STAGE;
@@ -1033,7 +1060,17 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
                 // positions of the chunk this query may see: every committed one, and among the pass's own rows those of its mask
                 // (a chain: rows 0 .. j; a tree: its ancestors and itself).  vis: bit i = position sub * 16 + i of the chunk.
                 u32 vis = 0;
-                if (qv < QV) {
+                if (qv < QV && sparse) {
+                    // position i of this thread's 16: list position c0 + i, in group cgrp[(c0 - tbase + i) / ratio]; the row sees it
+                    // up to its own position (the last group of a list may reach past it)
+                    const int c0 = tbase + sub * 16;
+                    for (int i = 0; i < 16; i++) {
+                        const int cl = sub * 16 + i;
+                        if (c0 + i >= t1) break;
+                        const int ap = cgrp[ci & 1][cl / ratio] * ratio + cl % ratio;
+                        vis |= ap <= pos0 + jz ? 1u << i : 0u;
+                    }
+                } else if (qv < QV) {
                     const int jr = qv / G;
                     const u32 mk = tr ? tr->mask[jr] : (2u << jr) - 1u;
                     const int c0 = tbase + sub * 16;                  // first position of this thread's 16
@@ -1121,7 +1158,7 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
         for (int r = 0; r < 2; r++) {
             const int qv = a * 16 + g8 + 8 * r;
             if (qv < QV) {
-                const int j = qv / G, h = kvh * G + qv % G;
+                const int j = jz + qv / G, h = kvh * G + qv % G;
                 float* out = part + (((size_t)j * nh + h) * splits + sp) * (HD + 2);
 #pragma unroll
                 for (int b = 0; b < A::NT; b++) {
@@ -1132,7 +1169,7 @@ sz_attn2_kernel(const float* __restrict__ qin, const u8* __restrict__ kc, const 
             }
         }
     if (threadIdx.x < QV) {
-        const int qv = threadIdx.x, j = qv / G, h = kvh * G + qv % G;
+        const int qv = threadIdx.x, j = jz + qv / G, h = kvh * G + qv % G;
         float* out = part + (((size_t)j * nh + h) * splits + sp) * (HD + 2);
         out[HD] = rmax[qv];
         out[HD + 1] = rsum[qv];

@@ -61,13 +61,18 @@ def write_gguf(path, M, arch="qwen4exp"):
         _kv(arch + ".ssm.time_step_rank", T_U32, cfg["ssm_v_heads"]), _kv(arch + ".ssm.inner_size", T_U32, cfg["ssm_v_heads"] * cfg["ssm_head_dim"]),
         _kv(arch + ".ssm.conv_kernel", T_U32, cfg["conv_k"]), _kv(arch + ".full_attention_interval", T_U32, cfg["attn_interval"]),
         _kv(arch + ".hyper_connection.count", T_U32, cfg["streams"]), _kv(arch + ".hyper_connection.low_rank", T_U32, cfg["hc_rank"]),
-        # the per-layer-embedding branch and the sparse indexer: present for the reference's Config::from_gguf, describing none
+        # the per-layer-embedding branch: present for the reference's Config::from_gguf, describing none
         _kv(arch + ".ple.layers", T_ARR, [n_layer]), _kv(arch + ".ple.ngram_size", T_U32, 1), _kv(arch + ".ple.heads_per_ngram", T_U32, 1),
         _kv(arch + ".embedding_length_per_layer_input", T_U32, 0), _kv(arch + ".ple.conv_kernel", T_U32, 1), _kv(arch + ".ple.eos_token_id", T_U32, 0),
         _kv(arch + ".ple.layer_multipliers", T_ARR, []), _kv(arch + ".ple.head_vocab_sizes", T_ARR, []), _kv(arch + ".ple.head_offsets", T_ARR, []),
-        _kv(arch + ".attention.indexer.head_count", T_U32, 0), _kv(arch + ".attention.indexer.key_length", T_U32, 0),
-        _kv(arch + ".attention.indexer.top_k", T_U32, 1 << 30), _kv(arch + ".attention.compress_ratios", T_ARR, [0] * n_layer),
     ]
+    if cfg.get("idx_heads", 0) > 0:   # the sparse indexer of the attention layers (forward.rs:137-140)
+        ratios = [int(cfg.get("idx_ratio", 4)) if (l % cfg["attn_interval"] == cfg["attn_interval"] - 1) else 0 for l in range(n_layer)]
+        kvs += [_kv(arch + ".attention.indexer.head_count", T_U32, cfg["idx_heads"]), _kv(arch + ".attention.indexer.key_length", T_U32, cfg["idx_dim"]),
+                _kv(arch + ".attention.indexer.top_k", T_U32, cfg["idx_budget"]), _kv(arch + ".attention.compress_ratios", T_ARR, ratios)]
+    else:                             # none: no heads, a budget no context reaches
+        kvs += [_kv(arch + ".attention.indexer.head_count", T_U32, 0), _kv(arch + ".attention.indexer.key_length", T_U32, 0),
+                _kv(arch + ".attention.indexer.top_k", T_U32, 1 << 30), _kv(arch + ".attention.compress_ratios", T_ARR, [0] * n_layer)]
     tensors = []   # (name, dims in ggml order, type id, uint8 array)
 
     def add(name, dims, ty, data):

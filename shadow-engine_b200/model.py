@@ -415,6 +415,10 @@ class Session:
             a = np.empty((c["ssm_v_heads"], c["ssm_head_dim"], c["ssm_head_dim"]), dtype=np.float32)
         elif what == szlib.STATE_DELTA_CONV:
             a = np.empty((c["conv_k"] - 1, (2 * c["ssm_k_heads"] + c["ssm_v_heads"]) * c["ssm_head_dim"]), dtype=np.float32)
+        elif what == szlib.STATE_IDX_SELECTED:
+            a = np.empty((szlib.MAX_VERIFY, self.lib.sz_session_idx_words(self.h)), dtype=np.uint32)
+        elif what == szlib.STATE_IDX_SCORES:
+            a = np.empty((szlib.MAX_VERIFY, 32 * self.lib.sz_session_idx_words(self.h)), dtype=np.float32)
         else:
             hb = c["head_dim"] + ((c["head_dim"] // 32 * 2 + 15) & ~15) if self.flags & 1 else 4 * c["head_dim"]
             a = np.empty((len(self), c["n_kv_head"], hb), dtype=np.uint8)

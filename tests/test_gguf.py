@@ -105,6 +105,25 @@ def test_a_model_read_back_from_its_file_steps_to_the_same_bits(small_file):
     lm.close()
 
 
+def test_a_file_with_a_sparse_indexer_reads_back_to_the_same_bits(tmp_path):
+    cfg = dict(SMALL, idx_heads=2, idx_dim=32, idx_budget=8, idx_ratio=2)
+    M = md.make_model(cfg, seed=4)
+    path = str(tmp_path / "idx.gguf")
+    gio.write_gguf(path, M)
+    lm = gio.LoadedModel(path)
+    assert (lm.cfg["idx_heads"], lm.cfg["idx_dim"], lm.cfg["idx_budget"]) == (2, 32, 8)
+    assert lm.tensor_info("blk.3.indexer.q_proj.weight")[1][:2] == [SMALL["hidden"], 64]
+    a = ob.Session(md.HostModel(M), kv_q8=True, threads=2)
+    b = ob.Session(lm, kv_q8=True, threads=2)
+    for t in (3, 500, 17, 17, 256, 9, 9, 41, 77, 5, 6, 7, 8, 1):    # past the budget of 8 positions: the indexer selects
+        la, lb = a.step(t), b.step(t)
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+        assert np.array_equal(a.selected(3), b.selected(3))
+    assert len(a.selected(3)) == 8 + len(a) % 2
+    del b
+    lm.close()
+
+
 def test_files_that_switch_on_a_branch_this_build_lacks_are_refused(small_file, tmp_path):
     M, path = small_file
     L = szlib.load()

@@ -185,3 +185,41 @@ def test_long_context_pass_matches_the_cpu_steps(c3, length):
         worst = max(worst, check_rows(lg, idx, want, want_routes, "context %d" % length))
     assert len(sess) == length + 5
     print("largest relative logit error at context %d: %.3g" % (length, worst))
+
+
+def test_the_sparse_indexer_at_the_benchmark_shapes_and_a_long_context():
+    """The reference's indexer shape (4 heads of 128, blocks of 4 positions, a budget of 2,048 positions: docs/ARCH.md:142-157) on the
+    4-layer slice, past its threshold: 5,000 cached positions = 1,250 complete blocks of which every row keeps 512 and the tail.
+    Both sides start from the same seeded caches (attention K / V and the indexer's raw keys)."""
+    cfg = dict(C3_SLICE, idx_heads=4, idx_dim=128, idx_budget=2048, idx_ratio=4)
+    M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=5)
+    hm, dm = md.HostModel(M), md.DeviceModel(M)
+    length, l = 5000, cfg["n_layer"] - 1
+    cpu = ob.Session(hm, kv_q8=True, threads=THREADS)
+    cpu.fill_synthetic(length, seed=7)
+    sess = md.Session(dm, 8192, kv_q8=True)
+    sess.fill_synthetic(length, seed=7)
+    toks = [int(t) for t in np.random.default_rng(17).integers(0, cfg["vocab"], 5)]
+    worst, at = 0.0, length
+    for ids in (toks[:4], toks[4:]):
+        sess.verify(ids)
+        _, top, lg = sess.result(logits=True)
+        sess.commit(len(ids))
+        sel = sess.export(szlib.STATE_IDX_SELECTED, l)
+        for j, t in enumerate(ids):
+            want = cpu.step(t)
+            n = at + j + 1
+            nb = n // 4
+            got = {b for b in range(nb) if (int(sel[j][b >> 5]) >> (b & 31)) & 1}
+            ref = {int(p) // 4 for p in cpu.selected(l) if int(p) // 4 < nb}
+            assert len(got) == 512 and len(cpu.selected(l)) == 2048 + n % 4
+            sc = cpu.idx_scores(l)
+            thr = sorted(sc, reverse=True)[511]
+            for b in got ^ ref:                        # only blocks tied with the last one kept (to rounding) may differ
+                assert abs(sc[b] - thr) <= 1e-5 * max(1.0, abs(thr)), "row %d: block %d (score %g, threshold %g)" % (j, b, sc[b], thr)
+            if got == ref:
+                e = rel_err(lg[j], want)
+                worst = max(worst, e)
+                assert e < LOGIT_REL and int(np.argmax(lg[j])) == int(np.argmax(want))
+        at += len(ids)
+    print("largest relative logit error with the indexer selecting 2,048 of %d positions: %.3g" % (length, worst))
