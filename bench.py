@@ -39,6 +39,14 @@ C3 = dict(n_layer=48, hidden=2048, streams=4, hc_rank=256, vocab=151936, n_head=
           n_expert=512, n_expert_used=10, expert_ff=512, shared_ff=512, ssm_k_heads=16, ssm_v_heads=32, ssm_head_dim=128, conv_k=4,
           attn_interval=4, eps=1e-6, rope_theta=1e7)
 C3_CTX = 24576
+C3_INDEXER = dict(idx_heads=4, idx_dim=128, idx_budget=2048, idx_ratio=4)   # docs/ARCH.md:142-157 of the reference
+
+
+def c3_model_cfg(args, n_layer):
+    cfg = dict(C3, n_layer=n_layer)
+    if getattr(args, "indexer", False):
+        cfg.update(C3_INDEXER)
+    return cfg
 GATEUP_PROFILE = os.path.join(ROOT, "profiles", "c2_moe_gateup_exl3_full.md")
 
 
@@ -151,6 +159,7 @@ def c3_config(args, cfg, ctx, bytes_all=None):
             "expert_ff": cfg["expert_ff"], "vocab": cfg["vocab"], "experts": "exl3-3bit", "dense": "q8_0", "kv": "q8_kv",
             "head": {"q8": "q8_0, read in full", "exl3": "exl3-4bit, read in full", "proxy": "exl3-4bit screened by its 2-bit proxy (128 blocks a row)"}[args.head],
             "context": ctx, "spec_k": 3, "batch": 1, "greedy": True,
+            "indexer": ({k: cfg[k] for k in C3_INDEXER} if cfg.get("idx_heads", 0) else None),
             "requests": "256-token prompts (a token cycle of the model repeated, 10%% random substitutions), %d tokens decoded each; "
                         "prompt passes and the cache fill are outside the timed region" % args.request_tokens,
             "acceptance_knobs": {"cycle_alpha": args.alpha, "cycle_beta": args.beta, "prompt_substitution": 0.1},
@@ -169,6 +178,9 @@ def c3_bytes(cfg, ctx, distinct_per_layer, dense_bytes):
     hb = cfg["head_dim"] + ((cfg["head_dim"] // 32 * 2 + 15) & ~15)
     experts = sum(distinct_per_layer) * be + cfg["n_layer"] * expert_bytes("exl3", H, cfg["shared_ff"])
     kv = n_attn * ctx * cfg["n_kv_head"] * hb * 2
+    if cfg.get("idx_heads", 0) and ctx > cfg["idx_budget"]:
+        # the sparse indexer: a row attends to the budget's positions; the pooled keys (one per block of positions) are read instead
+        kv = n_attn * (cfg["idx_budget"] * cfg["n_kv_head"] * hb * 2 + ctx // cfg["idx_ratio"] * cfg["idx_dim"] * 4)
     return {"experts": experts, "kv": kv, "experts_kv": experts + kv, "dense_and_head": dense_bytes, "all": experts + kv + dense_bytes}
 
 
@@ -198,7 +210,7 @@ def run_c3(args):
         else:
             peer = ep.PeerExchange(C3["hidden"])
     hbm, peak_kind = peaks()
-    cfg = dict(C3, n_layer=args.n_layer)
+    cfg = c3_model_cfg(args, args.n_layer)
     head_type = szlib.TYPE_Q8_0 if args.head == "q8" else szlib.TYPE_EXL3(4)
     M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha,
                       cycle_beta=args.beta, head_type=head_type)
@@ -406,7 +418,7 @@ def run_c3(args):
     value = toks / (dev_ms * 1e-3)
     cpu = None
     if world == 1 and args.cpu_seconds > 0:
-        cpu = cpu_c3(pkg, args.cpu_seconds, os.cpu_count() or 1, args.head, ctx)
+        cpu = cpu_c3(pkg, args.cpu_seconds, os.cpu_count() or 1, args.head, ctx, C3_INDEXER if args.indexer else None)
     line = {
         "metric": C3_METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": W, "rounds_timed": rounds,
         "ms_per_step": dev_ms / max(rounds, 1), "higher_is_better": True, "scaling": "weak" if replicas else "strong", "vs_baseline": None,
@@ -557,7 +569,7 @@ def run_c4(args):
     out.emit(json.dumps(line))
 
 
-def cpu_c3(pkg, budget_s, threads, head="q8", ctx=C3_CTX):
+def cpu_c3(pkg, budget_s, threads, head="q8", ctx=C3_CTX, extra=None):
     """Accepted tok/s of the CPU restatement of the reference's scalar path on the config-3 shapes, at the benchmark's context.
     The CPU path verifies one token at a time (a batched pass is bitwise the one-at-a-time pass there), so its accepted tok/s is
     1 / (seconds a token).  Sample: models of 4 and of 8 layers (one and two periods of the 3:1 pattern) with the full-size layers,
@@ -569,7 +581,7 @@ def cpu_c3(pkg, budget_s, threads, head="q8", ctx=C3_CTX):
     per = {}
     ntok = 0
     for nl in (4, 8):
-        cfg = dict(C3, n_layer=nl)
+        cfg = dict(C3, n_layer=nl, **(extra or {}))
         # (the time of a token does not depend on which tokens come out: with an EXL3 head, whose token cycles need a GPU to build,
         # the sample's model has none; the CPU path always evaluates the head in full, as the reference's --exact does)
         M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device="cpu",
@@ -602,13 +614,13 @@ def run_reference_c3(args):
     import __graft_entry__ as graft
     pkg = graft.load_package()
     threads = os.cpu_count() or 1
-    cpu = cpu_c3(pkg, max(10.0, min(60.0, 2.0 * args.steps)), threads, args.head, args.ctx)
+    cpu = cpu_c3(pkg, max(10.0, min(60.0, 2.0 * args.steps)), threads, args.head, args.ctx, C3_INDEXER if args.indexer else None)
     v = cpu["value"]
     cpu_line = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps({
         "impl": "reference", "metric": C3_METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (f64 accumulate)",
-        "data": "synthetic", "config": c3_config(args, dict(C3, n_layer=args.n_layer), args.ctx),
+        "data": "synthetic", "config": c3_config(args, c3_model_cfg(args, args.n_layer), args.ctx),
         "cpu_baseline": cpu_line, "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
@@ -894,6 +906,9 @@ def main():
     ap.add_argument("--ctx", type=int, default=C3_CTX, help="c3: context length the decode runs at")
     ap.add_argument("--request-tokens", type=int, default=96, help="c3: tokens decoded after each request's 256-token prompt")
     ap.add_argument("--beta", type=float, default=None, help="c3: how strongly the synthetic model leans towards skipping a token of its cycle")
+    ap.add_argument("--indexer", action="store_true",
+                    help="c3: the model has the reference's sparse indexer (4 heads of 128, blocks of 4 positions, a budget of 2,048 positions); "
+                         "BASELINE's configs describe a model without one, so this is off by default")
     ap.add_argument("--n-layer", type=int, default=C3["n_layer"], help="c3: layers (a smaller model for a quick check; not the benchmark)")
     ap.add_argument("--format", default="exl3", choices=["exl3", "iq3_s", "q8_0"])
     ap.add_argument("--also", default="iq3_s", help="comma list of further formats to time and report under 'also' ('' for none)")

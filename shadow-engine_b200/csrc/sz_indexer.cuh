@@ -8,7 +8,7 @@
 // attention kernel takes one row a block in this form): what a row computes then depends on nothing but the row, which is what
 // makes a pass of several rows equal, bit for bit, to the same rows read one at a time (tests/reference.rs:258-290 asks for that).
 //   sz_idx_prep_kernel    indexer queries (norm, rotation), raw keys into their cache slots, pooled keys of the blocks this pass completes
-//   sz_idx_score_kernel   block scores of every row: one thread a block, the dot products in f64 in the reference's order
+//   sz_idx_score_kernel   block scores of every row: a warp a block, the dot products in f64 (one fixed order, a butterfly over the lanes)
 //   sz_idx_select_kernel  per row the `keep` best blocks (score descending, block ascending among equals) by a radix select, then the
 //                         row's ascending list of position groups
 // Caches: raw keys [position][width] f32; pooled keys [block][width] f32.  Nothing is rolled back on a rejection: a slot is
@@ -92,34 +92,47 @@ sz_idx_prep_kernel(const float* __restrict__ iq, const float* __restrict__ ik, c
     sz_idx_finish(tmp, red, id, w, eps, rpos, rope_dims, rope_den, dst);
 }
 
-// ---- grid (ceil(blocks / 128)), block 128: scores[j][b] for every row j whose complete blocks include b --------------------------
-__global__ void __launch_bounds__(128)
+// ---- grid (any), block 256: scores[j][b] for every row j whose complete blocks include b ------------------------------------------
+// A warp takes a block: its lanes hold the pooled key (dimension lane, lane + 32, ...), and for every (row, head) the lanes' f64
+// partial products meet in a butterfly, so the sum has one fixed order whatever the pass looks like.  (One thread a block with the
+// dot product as one serial f64 chain was 184 us a launch at 6,144 blocks x 4 rows; the f64 pipe wants parallel chains.)  The f64
+// sum differs from the reference's serial one far below the f32 it is rounded to.
+__global__ void __launch_bounds__(256)
 sz_idx_score_kernel(const float* __restrict__ qn, const float* __restrict__ blocks, SzIdxGeom g, int m, const int32_t* __restrict__ state,
                     float* __restrict__ scores) {
     extern __shared__ float sq[];   // [m][heads][dim]
     sz_pdl_wait();
     sz_pdl_trigger();
     const int id = g.dim, nq = m * g.heads * id;
-    for (int i = threadIdx.x; i < nq; i += 128) sq[i] = qn[i];
+    for (int i = threadIdx.x; i < nq; i += 256) sq[i] = qn[i];
     __syncthreads();
     const int pos0 = state[0];
-    const int b = blockIdx.x * 128 + threadIdx.x;
+    const int lane = threadIdx.x & 31;
     const int nb_last = (pos0 + m) / g.ratio;
-    if (b >= nb_last) return;
-    const float* kb = blocks + (size_t)b * id;
     const float norm = sqrtf((float)id);
-    for (int j = 0; j < m; j++) {
-        const int nb = (pos0 + j + 1) / g.ratio;
-        if (b >= nb || nb <= g.keep) continue;     // not complete for this row yet, or the row attends to everything
-        float sc = 0.0f;
-        for (int h = 0; h < g.heads; h++) {
-            const float* q = sq + ((size_t)j * g.heads + h) * id;
-            double dot = 0.0;
-            for (int d = 0; d < id; d++) dot = fma((double)q[d], (double)__ldg(kb + d), dot);   // f32 x f32 is exact in f64: the reference's sum
-            const float f = (float)dot;
-            sc += f > 0.0f ? f : 0.0f;
+    constexpr int MAXT = SZ_IDX_MAX_DIM / 32;
+    const int nt = (id + 31) / 32;
+    for (int b = blockIdx.x * 8 + (threadIdx.x >> 5); b < nb_last; b += gridDim.x * 8) {
+        float kb[MAXT];
+#pragma unroll
+        for (int t = 0; t < MAXT; t++) kb[t] = t < nt && lane + 32 * t < id ? __ldg(blocks + (size_t)b * id + lane + 32 * t) : 0.0f;
+        for (int j = 0; j < m; j++) {
+            const int nb = (pos0 + j + 1) / g.ratio;
+            if (b >= nb || nb <= g.keep) continue;     // not complete for this row yet, or the row attends to everything
+            float sc = 0.0f;
+            for (int h = 0; h < g.heads; h++) {
+                const float* q = sq + ((size_t)j * g.heads + h) * id;
+                double dot = 0.0;
+#pragma unroll
+                for (int t = 0; t < MAXT; t++)
+                    if (t < nt && lane + 32 * t < id) dot = fma((double)q[lane + 32 * t], (double)kb[t], dot);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                const float f = (float)dot;
+                sc += f > 0.0f ? f : 0.0f;
+            }
+            if (lane == 0) scores[(size_t)j * g.ctx_blocks + b] = sc / norm;
         }
-        scores[(size_t)j * g.ctx_blocks + b] = sc / norm;
     }
 }
 
@@ -160,15 +173,25 @@ sz_idx_select_kernel(const float* __restrict__ scores, SzIdxGeom g, int m, const
                 if ((k & kmask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1u);
             }
             __syncthreads();
-            if (tid == 0) {   // the digit where the count from the top reaches what is still wanted
-                u32 need = s_remaining, cum = 0;
-                int d = 255;
-                for (; d > 0; d--) {
-                    if (cum + hist[d] >= need) break;
-                    cum += hist[d];
+            if (warp == 0) {   // the digit where the count from the top reaches what is still wanted: lane l owns digits 255 - 8 l .. 248 - 8 l
+                const u32 need = s_remaining;
+                u32 own = 0;
+#pragma unroll
+                for (int i = 0; i < 8; i++) own += hist[255 - 8 * lane - i];
+                u32 incl = own;
+                for (int o = 1; o < 32; o <<= 1) { const u32 v = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += v; }
+                const u32 hit = __ballot_sync(0xffffffffu, incl >= need);
+                const int owner = hit ? __ffs((int)hit) - 1 : 31;   // (need <= the count of matching keys, so some lane reaches it)
+                if (lane == owner) {
+                    u32 cum = incl - own;
+                    int d = 255 - 8 * lane;
+                    for (int i = 0; i < 7; i++, d--) {
+                        if (cum + hist[d] >= need) break;
+                        cum += hist[d];
+                    }
+                    s_remaining = need - cum;
+                    s_prefix = prefix | ((u32)d << shift);
                 }
-                s_remaining = need - cum;
-                s_prefix = prefix | ((u32)d << shift);
             }
             kmask |= 255u << shift;
             __syncthreads();

@@ -773,8 +773,9 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
         SZ_CUDA(sz_launch("idx_prep", sz_idx_prep_kernel, dim3(c.idx_heads + 2, m), dim3(128), 0, st, true, (const float*)s->i_q, (const float*)s->i_k,
                           (const float*)L.idx_q_norm.data, (const float*)L.idx_k_norm.data, g, c.eps, (const int32_t*)s->state, (int)c.rope_dims,
                           (const double*)s->rope_den, raw, blocks, s->i_qn));
-        const int nb_cap = s->ctx / ratio + 1;
-        SZ_CUDA(sz_launch("idx_score", sz_idx_score_kernel, dim3((nb_cap + 127) / 128), dim3(128), (size_t)m * c.idx_heads * c.idx_dim * 4, st, true,
+        const int nb_cap = s->ctx / ratio + 1;   // a warp a block, eight blocks a thread block, up to four thread blocks a multiprocessor
+        const int sblocks = (nb_cap + 7) / 8 < 4 * sz_sm_count_session() ? (nb_cap + 7) / 8 : 4 * sz_sm_count_session();
+        SZ_CUDA(sz_launch("idx_score", sz_idx_score_kernel, dim3(sblocks), dim3(256), (size_t)m * c.idx_heads * c.idx_dim * 4, st, true,
                           (const float*)s->i_qn, (const float*)blocks, g, m, (const int32_t*)s->state, s->i_scores));
         SZ_CUDA(sz_launch("idx_select", sz_idx_select_kernel, dim3(m), dim3(1024), (size_t)s->i_words * 4, st, true, (const float*)s->i_scores, g, m,
                           (const int32_t*)s->state, s->i_sel, s->i_list, s->i_count, s->i_trace + (size_t)ai * SZ_MAX_VERIFY * s->i_words));
