@@ -897,9 +897,10 @@ def main():
                     help="c3: how strongly the synthetic model continues its token cycles (default: by kind of head, see C3_ALPHA_BY_HEAD)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
                     help="c3, N > 1: the expert-parallel exchange - stores into the peers' memory from the combine kernel (default) or an NCCL all-reduce")
-    ap.add_argument("--parallelism", default="ep", choices=["ep", "replicas"],
-                    help="c3, N > 1: experts sharded over the GPUs, one sequence (default, strong scaling), or every GPU with the whole model "
-                         "and requests of its own, no exchange (weak scaling)")
+    ap.add_argument("--parallelism", default="replicas", choices=["ep", "replicas"],
+                    help="c3, N > 1: every GPU with the whole 33 GB model and requests of its own, no exchange on the data path (default: "
+                         "weak scaling, the throughput form), or experts sharded over the GPUs and ONE sequence (strong scaling: batch-1 "
+                         "expert parallelism, which pays an exchange a layer and cannot scale)")
     ap.add_argument("--profile-passes", type=int, default=0, help="c3: only run this many 4-row verify passes (for ncu), no timing")
     ap.add_argument("--head", default="proxy", choices=["q8", "exl3", "proxy"],
                     help="c3: output.weight as Q8_0 read in full, as 4-bit EXL3 read in full, or EXL3 screened by its 2-bit proxy (Q2_P)")
