@@ -10,6 +10,8 @@ torchrun) the experts of every layer are sharded over the N ranks (expert parall
 `--workload c2-moe`: benchmark config 2, the verify-step MoE microbench (one MoE sublayer pass over K+1 = 4 rows per step).
 `--workload prefill-dense`: the batched / prompt form of a DeltaNet layer's input projection (12,288 x 2,048 Q8_0) over 256 or more token
 rows on tcgen05 (`sz_mma_cols`); TFLOP/s against the measured dense bf16 rate.
+`--workload c5-concurrent`: B sequences decoded at once on every GPU (config 5's batched serving, without batching the kernels): each
+sequence has a verify session, stream and CUDA graphs of its own over the one resident model, and the GPU overlaps their passes.
 `--workload c4-tree`: benchmark config 4's mechanism on the config-3 model: one verify pass over a draft tree (8 rows), greedy
 acceptance on the device and rejection sampling on the host; reports us per verify and the accepted length.
 
@@ -624,6 +626,133 @@ def run_reference_c3(args):
         "cpu_baseline": cpu_line, "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
 
+# ---- workload c5-concurrent: B sequences at once on every GPU ----------------------------------------------------------------------
+def run_c5(args):
+    """Config 5's shape of load - many sequences decoding at once, spec K=3 each - served by B independent verify sessions a GPU over
+    one resident model: a session, a stream, CUDA graphs and a host thread (drafter + loop) per sequence.  A single pass leaves most
+    of the GPU idle (it is a chain of short dependent kernels), so the passes of different sequences overlap.  Kernels are NOT
+    batched across sequences: every sequence streams its own experts.  N > 1: every GPU holds the whole model and B sequences of its
+    own (no exchange on the data path).  Waves: every sequence takes a request (cache filled to the context, 256-token prompt fed:
+    untimed), then all decode their tokens at once (timed, device time between events around the wave)."""
+    import threading
+    out = QuietStdout()
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d (launch with torch.distributed.run for N > 1)" % (args.gpus, world))
+    torch.cuda.set_device(local)
+    device = "cuda:%d" % local
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    md, szlib = pkg.model, pkg.lib
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl")
+    cfg = c3_model_cfg(args, args.n_layer)
+    head_type = szlib.TYPE_Q8_0 if args.head == "q8" else szlib.TYPE_EXL3(4)
+    M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha,
+                      cycle_beta=args.beta, head_type=head_type)
+    dm = md.DeviceModel(M, device)
+    del M
+    torch.cuda.empty_cache()
+    B, ctx, n_prompt, n_new = args.sequences, args.ctx, 256, args.request_tokens
+    _, cyc = md.token_cycles(cfg["vocab"], 1)
+    sessions = [md.Session(dm, ctx + n_new + 64, kv_q8=True, head_proxy=args.head == "proxy") for _ in range(B)]
+    gens = [None] * B
+    stats = [None] * B
+    errors = []
+
+    def prepare(b, wave):
+        try:
+            sessions[b].fill_synthetic(ctx - n_prompt, seed=3)
+            gens[b] = md.Generator(sessions[b], md.make_prompt(n_prompt, cfg["vocab"], seed=1 + (wave * B + b) * world + rank, cycles=cyc), n_new, spec_k=3)
+        except Exception as e:   # noqa: BLE001
+            errors.append(repr(e))
+
+    def decode(b):
+        try:
+            stats[b] = gens[b].run(0)
+            sessions[b]._stream.synchronize()
+        except Exception as e:   # noqa: BLE001
+            errors.append(repr(e))
+
+    def in_threads(fn, *a):
+        ts = [threading.Thread(target=fn, args=(b,) + a) for b in range(B)]
+        for t in ts:
+            t.start()
+        for t in ts:
+            t.join()
+        if errors:
+            raise SystemExit("c5-concurrent: " + errors[0])
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    tot = dict(n=0, rounds=0, drafted=0, accepted=0, dev_ms=0.0, wall_s=0.0, pass_ms=0.0)
+    clocks = None
+    for wave in range(-1, args.waves):     # wave -1: warm-up (records every session's graphs)
+        in_threads(prepare, wave + 1)
+        barrier()
+        if wave == 0:
+            sampler = ClockSampler(torch.cuda.current_device())
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        t0 = time.perf_counter()
+        in_threads(decode)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        e1.record()
+        torch.cuda.synchronize()
+        if wave >= 0:
+            tot["dev_ms"] += e0.elapsed_time(e1); tot["wall_s"] += wall
+            for st in stats:
+                tot["n"] += st.n_tokens; tot["rounds"] += st.rounds; tot["drafted"] += st.drafted; tot["accepted"] += st.accepted
+                tot["pass_ms"] += st.device_ms
+        for b in range(B):
+            gens[b] = None
+    barrier()
+    clocks = sampler.stop()
+
+    def agree(v, op):
+        if world == 1:
+            return v
+        import torch.distributed as dist
+        t = torch.tensor([v], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op={"max": dist.ReduceOp.MAX, "sum": dist.ReduceOp.SUM}[op])
+        return float(t[0])
+
+    dev_ms, wall_s = agree(tot["dev_ms"], "max"), agree(tot["wall_s"], "max")
+    toks, rounds = int(agree(tot["n"], "sum")), int(agree(tot["rounds"], "sum"))
+    drafted, accepted = int(agree(tot["drafted"], "sum")), int(agree(tot["accepted"], "sum"))
+    if rank != 0:
+        return
+    hbm, peak_kind = peaks()
+    line = {
+        "metric": "accepted tok/s at spec K=3, %d sequences at once a GPU" % B, "value": toks / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": rounds, "warmup": B, "ms_per_step": dev_ms / max(rounds, 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 activations, f16 EXL3 codebook weights, int8 Q8_0 / Q8_KV, f32 accumulate (router, norms, combine in f64)", "data": "synthetic",
+        "config": dict(c3_config(args, cfg, ctx), workload="c5-concurrent", sequences_per_gpu=B, batch=B * world, waves=args.waves,
+                       parallelism="replicas%d x %d sequences" % (world, B) if world > 1 else "%d sequences, one GPU" % B,
+                       batching="none across sequences: a session, stream and CUDA graphs per sequence; passes of different sequences overlap on the GPU"),
+        "speculation": {"tokens": toks, "rounds": rounds, "drafted": drafted, "accepted": accepted, "tokens_per_round": toks / max(rounds, 1)},
+        "sequence_pass_ms": tot["pass_ms"] / max(tot["rounds"], 1),
+        "roofline": {"bound": "hbm", "achieved": None, "peak": hbm, "unit": "GB/s", "frac": None, "traffic": None, "peak_kind": peak_kind,
+                     "note": "the kernels are those of the c3 workload (see its line for the per-kernel roofline); this line measures how many of their chains one GPU overlaps"},
+        "cpu_baseline": None,
+        "e2e": {"value": toks / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 128, "d2h_bytes_per_step": 8 + 512 * (1 + drafted / max(rounds, 1))},
+        "gpu_launches": None, "clocks": clocks,
+    }
+    out.emit(json.dumps(line))
+
+
 # ---- workload prefill-dense: many token rows through one dense projection on tcgen05 ------------------------------------------------
 PD = dict(rows=12288, cols=2048)     # attn_qkv (8,192) + attn_gate (4,096) of a config-3 DeltaNet layer, one Q8_0 matrix
 PD_METRIC = "dense projection TFLOP/s (Q8_0 weights, many token rows, tcgen05)"
@@ -891,7 +1020,9 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe", "c4-tree", "prefill-dense"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe", "c4-tree", "prefill-dense", "c5-concurrent"])
+    ap.add_argument("--sequences", type=int, default=8, help="c5-concurrent: sequences decoded at once on every GPU")
+    ap.add_argument("--waves", type=int, default=2, help="c5-concurrent: timed waves of requests (one request a sequence a wave)")
     ap.add_argument("--tokens", type=int, default=256, help="prefill-dense: token rows a step (256 = 64 sequences x K+1 = 4 rows)")
     ap.add_argument("--alpha", type=float, default=None,
                     help="c3: how strongly the synthetic model continues its token cycles (default: by kind of head, see C3_ALPHA_BY_HEAD)")
@@ -931,6 +1062,11 @@ def main():
         return run_reference_c3(args) if args.impl == "reference" else run_c3(args)
     if args.workload == "prefill-dense":
         return run_prefill_dense(args)
+    if args.workload == "c5-concurrent":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's CPU path serves one sequence at a time; see the c3 workload's reference arm for its tok/s"}))
+            return
+        return run_c5(args)
     if args.impl == "reference":
         return run_reference_c2(args)
 

@@ -296,6 +296,14 @@ int sz_session_idx_words(const sz_session* s);
 #define SZ_STATE_KV_K 2
 #define SZ_STATE_KV_V 3
 int sz_session_export(sz_session* s, int what, int layer, void* dst, int64_t bytes, uint64_t stream);
+/* The way back (GpuSession::restore, session.rs:3463-3541): sz_session_reset, then every piece a checkpoint holds through
+ * sz_session_import - DELTA_S and DELTA_CONV of every DeltaNet layer, KV_K and KV_V of every attention layer with the `positions`
+ * they cover (in sz_session_export's layout), and for a model with the sparse indexer IDX_RAW: the raw indexer keys, f32
+ * [positions][idx_dim] (the pooled block keys are rebuilt from them) - and last sz_session_set_len(positions).  The session then
+ * continues, bit for bit, as the one the pieces were taken from.  No pass may be pending; each call synchronises the stream. */
+#define SZ_STATE_IDX_RAW 6
+int sz_session_import(sz_session* s, int what, int layer, const void* src, int64_t bytes, int positions, uint64_t stream);
+int sz_session_set_len(sz_session* s, int positions, uint64_t stream);
 int sz_session_trace_routes(sz_session* s, int on);
 int sz_session_routes(sz_session* s, int32_t* idx, double* w, uint64_t stream);
 

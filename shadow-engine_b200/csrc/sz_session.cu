@@ -1223,6 +1223,11 @@ extern "C" int sz_session_export(sz_session* s, int what, int layer, void* dst, 
         for (int h = 0; h < c.n_kv_head && s->len > 0; h++)
             SZ_CUDA(cudaMemcpy2DAsync((u8*)dst + h * hb, (size_t)(c.n_kv_head * hb), base + (int64_t)h * s->ctx * hb, (size_t)hb, (size_t)hb, (size_t)s->len,
                                       cudaMemcpyDeviceToHost, st));
+    } else if (what == SZ_STATE_IDX_RAW) {
+        if (!attn || !s->i_raw) return sz_fail(SZ_E_ARG, "sz_session_export: layer %d has no sparse indexer", layer);
+        const int64_t n = 4 * (int64_t)s->len * c.idx_dim;
+        if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_export: %lld bytes given, %d positions take %lld", (long long)bytes, s->len, (long long)n);
+        if (n) SZ_CUDA(cudaMemcpyAsync(dst, (const u8*)s->i_raw + s->lb[layer].attn_index * s->i_raw_layer, (size_t)n, cudaMemcpyDeviceToHost, st));
     } else if (what == SZ_STATE_IDX_SELECTED || what == SZ_STATE_IDX_SCORES) {
         if (!attn || !s->i_trace) return sz_fail(SZ_E_ARG, "sz_session_export: layer %d has no sparse indexer", layer);
         const int ai = s->lb[layer].attn_index;
@@ -1242,6 +1247,65 @@ extern "C" int sz_session_export(sz_session* s, int what, int layer, void* dst, 
     }
     SZ_CUDA(cudaStreamSynchronize(st));
     s->inflight = 0;
+    return SZ_OK;
+}
+
+// ---- the way back: a checkpoint's pieces into a fresh session (GpuSession::restore, session.rs:3463-3541) ---------------------------
+extern "C" int sz_session_import(sz_session* s, int what, int layer, const void* src, int64_t bytes, int positions, uint64_t stream) {
+    if (!s || !src) return sz_fail(SZ_E_ARG, "sz_session_import: null argument");
+    if (s->last_m) return sz_fail(SZ_E_ARG, "sz_session_import: a pass is pending; commit it first");
+    const sz_model_config& c = s->model.cfg;
+    if (layer < 0 || layer >= c.n_layer) return sz_fail(SZ_E_ARG, "sz_session_import: layer %d of %d", layer, c.n_layer);
+    if (positions < 0 || positions + SZ_MAX_VERIFY > s->ctx) return sz_fail(SZ_E_ARG, "sz_session_import: %d positions in a session of %d", positions, s->ctx);
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool attn = sz_is_attn(c, layer);
+    if (what == SZ_STATE_DELTA_S || what == SZ_STATE_DELTA_CONV) {
+        if (attn) return sz_fail(SZ_E_ARG, "sz_session_import: layer %d is an attention layer", layer);
+        const int di = s->lb[layer].delta_index;
+        const int64_t d = c.ssm_head_dim, ch = (2 * (int64_t)c.ssm_k_heads + c.ssm_v_heads) * d;
+        const int64_t n = what == SZ_STATE_DELTA_S ? 4 * (int64_t)c.ssm_v_heads * d * d : 4 * (int64_t)(c.conv_k - 1) * ch;
+        if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_import: %lld bytes given, the piece has %lld", (long long)bytes, (long long)n);
+        u8* dst = what == SZ_STATE_DELTA_S ? (u8*)s->S[s->cur] : (u8*)s->conv[s->cur];
+        SZ_CUDA(cudaMemcpyAsync(dst + (int64_t)di * n, src, (size_t)n, cudaMemcpyHostToDevice, st));
+    } else if (what == SZ_STATE_KV_K || what == SZ_STATE_KV_V) {
+        if (!attn) return sz_fail(SZ_E_ARG, "sz_session_import: layer %d is a DeltaNet layer", layer);
+        const int ai = s->lb[layer].attn_index;
+        const int64_t hb = (s->flags & SZ_KV_Q8) ? (c.head_dim + (((c.head_dim >> 5) * 2 + 15) & ~15)) : 4 * (int64_t)c.head_dim;
+        const int64_t n = (int64_t)positions * c.n_kv_head * hb;
+        if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_import: %lld bytes given, %d positions take %lld", (long long)bytes, positions, (long long)n);
+        u8* base = (what == SZ_STATE_KV_K ? s->kc : s->vc) + (int64_t)ai * s->ctx * c.n_kv_head * hb;
+        for (int h = 0; h < c.n_kv_head && positions > 0; h++)   // [position][kv head][head] of the checkpoint into the cache's [kv head][position][head]
+            SZ_CUDA(cudaMemcpy2DAsync(base + (int64_t)h * s->ctx * hb, (size_t)hb, (const u8*)src + h * hb, (size_t)(c.n_kv_head * hb), (size_t)hb, (size_t)positions,
+                                      cudaMemcpyHostToDevice, st));
+    } else if (what == SZ_STATE_IDX_RAW) {
+        if (!attn || !s->i_raw) return sz_fail(SZ_E_ARG, "sz_session_import: layer %d has no sparse indexer", layer);
+        const int ai = s->lb[layer].attn_index, ratio = s->layers[layer].idx_ratio > 0 ? s->layers[layer].idx_ratio : 1;
+        const int64_t n = 4 * (int64_t)positions * c.idx_dim;
+        if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_import: %lld bytes given, %d positions take %lld", (long long)bytes, positions, (long long)n);
+        float* raw = (float*)((u8*)s->i_raw + ai * s->i_raw_layer);
+        if (n) SZ_CUDA(cudaMemcpyAsync(raw, src, (size_t)n, cudaMemcpyHostToDevice, st));
+        if (positions / ratio > 0) {   // the pooled key of every complete block
+            sz_idx_rebuild_kernel<<<positions / ratio, 128, 0, st>>>((const float*)raw, (const float*)s->layers[layer].idx_k_norm.data, (int)c.idx_dim, ratio, c.eps,
+                                                                     (int)c.rope_dims, (const double*)s->rope_den, (float*)((u8*)s->i_blocks + ai * s->i_blocks_layer));
+            SZ_CUDA(cudaGetLastError());
+        }
+    } else {
+        return sz_fail(SZ_E_ARG, "sz_session_import: piece %d cannot be imported", what);
+    }
+    SZ_CUDA(cudaStreamSynchronize(st));
+    s->inflight = 0;
+    return SZ_OK;
+}
+
+extern "C" int sz_session_set_len(sz_session* s, int positions, uint64_t stream) {
+    if (!s || s->last_m) return sz_fail(SZ_E_ARG, "sz_session_set_len: null session or a pass is pending");
+    if (positions < 0 || positions + SZ_MAX_VERIFY > s->ctx) return sz_fail(SZ_E_ARG, "sz_session_set_len: %d positions in a session of %d", positions, s->ctx);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
+    s->h_pin[8] = positions;
+    SZ_CUDA(cudaMemcpyAsync(s->state, s->h_pin + 8, 4, cudaMemcpyHostToDevice, st));   // word 0 of the device state: the committed positions
+    SZ_CUDA(cudaStreamSynchronize(st));
+    s->len = positions;
     return SZ_OK;
 }
 

@@ -46,7 +46,7 @@ class HeadC(C.Structure):
 
 
 PLACE_HOST, PLACE_DEVICE = 0, 1
-STATE_DELTA_S, STATE_DELTA_CONV, STATE_KV_K, STATE_KV_V, STATE_IDX_SELECTED, STATE_IDX_SCORES = range(6)
+STATE_DELTA_S, STATE_DELTA_CONV, STATE_KV_K, STATE_KV_V, STATE_IDX_SELECTED, STATE_IDX_SCORES, STATE_IDX_RAW = range(7)
 HEAD_XR, HEAD_XQ, HEAD_XSC, HEAD_XCORR, HEAD_BMAX, HEAD_SEL, HEAD_ERR = range(7)
 
 # name -> (restype, argtypes); every symbol include/shadowzero_b200.h declares
@@ -86,6 +86,8 @@ SYMBOLS = {
     "sz_session_verify": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64]),
     "sz_session_set_sampler": (C.c_int, [C.c_void_p, C.c_void_p]),
     "sz_session_idx_words": (C.c_int, [C.c_void_p]),
+    "sz_session_import": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int64, C.c_int, C.c_uint64]),
+    "sz_session_set_len": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64]),
     "sz_session_set_stops": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64]),
     "sz_session_stops": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
     "sz_session_verify_sampled": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32), C.c_int, C.c_uint64, C.c_int, C.c_uint64]),

@@ -415,6 +415,8 @@ class Session:
             a = np.empty((c["ssm_v_heads"], c["ssm_head_dim"], c["ssm_head_dim"]), dtype=np.float32)
         elif what == szlib.STATE_DELTA_CONV:
             a = np.empty((c["conv_k"] - 1, (2 * c["ssm_k_heads"] + c["ssm_v_heads"]) * c["ssm_head_dim"]), dtype=np.float32)
+        elif what == szlib.STATE_IDX_RAW:
+            a = np.empty((len(self), c["idx_dim"]), dtype=np.float32)
         elif what == szlib.STATE_IDX_SELECTED:
             a = np.empty((szlib.MAX_VERIFY, self.lib.sz_session_idx_words(self.h)), dtype=np.uint32)
         elif what == szlib.STATE_IDX_SCORES:
@@ -424,6 +426,26 @@ class Session:
             a = np.empty((len(self), c["n_kv_head"], hb), dtype=np.uint8)
         szlib.check(self.lib.sz_session_export(self.h, what, layer, a.ctypes.data_as(C.c_void_p), a.nbytes, self.stream))
         return a
+
+    def checkpoint(self):
+        """Every piece of the committed state, in host memory (GpuSession::snapshot with the cache): what `restore` takes."""
+        c = self.dm.cfg
+        pieces = []
+        for l in range(c["n_layer"]):
+            if is_attention(c, l):
+                kinds = [szlib.STATE_KV_K, szlib.STATE_KV_V] + ([szlib.STATE_IDX_RAW] if c.get("idx_heads", 0) else [])
+            else:
+                kinds = [szlib.STATE_DELTA_S, szlib.STATE_DELTA_CONV]
+            pieces += [(k, l, self.export(k, l)) for k in kinds]
+        return dict(positions=len(self), pieces=pieces)
+
+    def restore(self, ck):
+        """Become the session the checkpoint was taken from (GpuSession::restore): reset, every piece back, the length."""
+        szlib.check(self.lib.sz_session_reset(self.h, self.stream))
+        for what, layer, a in ck["pieces"]:
+            a = np.ascontiguousarray(a)
+            szlib.check(self.lib.sz_session_import(self.h, what, layer, a.ctypes.data_as(C.c_void_p), a.nbytes, ck["positions"], self.stream))
+        szlib.check(self.lib.sz_session_set_len(self.h, ck["positions"], self.stream))
 
     def generate(self, prompt, max_new, spec_k=3, greedy=True, sampler=None, lookup_min=4, eog=-1, device_accept=True, max_rounds=0):
         p = GenParams(spec_k, max_new, lookup_min, 1 if greedy else 0, eog, 1 if device_accept else 0,

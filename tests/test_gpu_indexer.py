@@ -111,3 +111,34 @@ def test_what_the_indexer_does_not_run_on_is_refused(model):
     s = md.Session(dm, 128, kv_q8=True)
     with pytest.raises(szlib.SzError):
         s.verify_tree([1, 2, 3], [-1, 0, 0])
+
+
+@pytest.mark.parametrize("with_indexer", [True, False])
+def test_a_checkpoint_restored_into_another_session_continues_exactly(model, with_indexer):
+    """GpuSession::snapshot / restore (session.rs:3339-3541): every piece of the committed state out to the host and back into a
+    fresh session - recurrent states, carried conv rows, K and V rows, the indexer's raw keys (pooled keys are rebuilt) - after
+    which both sessions give the same bits, pass after pass, and select the same blocks."""
+    if with_indexer:
+        M, hm, dm = model
+    else:
+        cfg = {k: v for k, v in IDX.items() if not k.startswith("idx_")}
+        dm = md.DeviceModel(md.make_model(cfg, seed=5))
+    rng = np.random.default_rng(21)
+    toks = [int(t) for t in rng.integers(0, IDX["vocab"], 70)]
+    a = md.Session(dm, 128, kv_q8=True)
+    a.prefill(toks[:53]); a.result(); a.commit((53 - 1) % 8 + 1)
+    a.verify([toks[53], 3, 4]); a.result(); a.commit(1)            # the state to save follows a rejected pass
+    ck = a.checkpoint()
+    assert ck["positions"] == 54
+    b = md.Session(dm, 128, kv_q8=True)
+    b.verify([1, 2, 3]); b.result(); b.commit(3)                   # something of its own first: the restore must clear it
+    b.restore(ck)
+    assert len(b) == 54
+    for ids in (toks[54:58], toks[58:59], toks[59:67]):
+        a.verify(ids); _, _, la = a.result(logits=True); a.commit(len(ids))
+        b.verify(ids); _, _, lb = b.result(logits=True); b.commit(len(ids))
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+        if with_indexer:
+            assert np.array_equal(a.export(szlib.STATE_IDX_SELECTED, LAYER)[:len(ids)], b.export(szlib.STATE_IDX_SELECTED, LAYER)[:len(ids)])
+    with pytest.raises(szlib.SzError):
+        b.lib.sz_session_import and szlib.check(b.lib.sz_session_import(b.h, szlib.STATE_IDX_SELECTED, LAYER, ck["pieces"][0][2].ctypes.data, 4, 0, b.stream))
