@@ -117,8 +117,8 @@ int sz_moe_launches(const sz_moe_layer* layer);
  * Shapes and tensors as Config::from_gguf and Model read them (crates/shadowzero-model/src/forward.rs:25-142, tensor names in
  * crates/shadowzero-model/src/exl3_model.rs:223-243).  Every tensor is stored as the reference stores it: ggml [cols = in,
  * rows = out] with whole rows contiguous, or one EXL3 blob.  `data` is a device address for the library (a host address for
- * the CPU oracle, which reads the same structs).  The per-layer-embedding (PLE) branch is not part of this build: a model
- * described here has none.  The sparse indexer is optional (cfg.idx_heads). */
+ * the CPU oracle, which reads the same structs).  The per-layer embedding (sz_ple) and the sparse indexer (cfg.idx_heads) are
+ * optional. */
 typedef struct sz_tensor {
     int32_t type;      /* ggml type id; 0 rows = absent */
     int32_t reserved;
@@ -163,12 +163,35 @@ typedef struct sz_layer {
     sz_moe_layer moe;
 } sz_layer;
 
+/* The per-layer embedding of ONE layer: a hashed n-gram memory added to the whole residual stream before that layer's first read
+ * (forward.rs:1036-1074 `ple`, :1177-1198 `ple_rows`, configuration :54-62 and :93-136; the reference implements one such layer).
+ * For every n-gram order 2 .. ngram the last `order` tokens (tokens before the last `eos` count as `eos`) are mixed -
+ * XOR of token * multipliers[distance], 64-bit wrapping - and each of heads_per_ngram heads takes row
+ * (mixed mod vocab[i]) + offsets[i] (the non-negative remainder) of `table`; the (ngram - 1) * heads_per_ngram rows of head_dim
+ * weights, side by side, are the embedding e [hidden].  key = norm_key(key . e) per stream, val = value . e, qry = norm_query(r) per
+ * stream; a stream's gate is sigmoid(sign(d) sqrt(max(|d|, 1e-6))) with d = key . qry / sqrt(hidden); gv = gate * val;
+ * out = gv + silu(depthwise causal conv over norm_conv(gv), kernel conv_k, dilation ngram); r += out.
+ * ngram < 2: the model has none (a zeroed struct). */
+#define SZ_PLE_MAX_NGRAM 8
+#define SZ_PLE_MAX_HEADS 32
+typedef struct sz_ple {
+    int32_t layer, ngram, heads_per_ngram, head_dim, conv_k, eos;
+    int64_t multipliers[SZ_PLE_MAX_NGRAM];
+    int64_t vocab[SZ_PLE_MAX_HEADS], offsets[SZ_PLE_MAX_HEADS];
+    sz_tensor table;        /* per_layer_token_embd [head_dim -> rows] */
+    sz_tensor key;          /* ple_key [hidden -> streams * hidden] */
+    sz_tensor value;        /* ple_value [hidden -> hidden] */
+    sz_tensor norm_key, norm_query, norm_conv;   /* F32 [streams * hidden] */
+    sz_tensor conv1d;       /* F32 [streams * hidden][conv_k]: tap t of a channel multiplies the input (conv_k - 1 - t) * ngram steps back */
+} sz_ple;
+
 typedef struct sz_model {
     sz_model_config cfg;
     sz_tensor token_embd;       /* [hidden -> vocab]: row t is token t's embedding */
     sz_tensor output;           /* [hidden -> vocab] */
     sz_hc output_hc;
     const sz_layer* layers;     /* host array of n_layer entries */
+    sz_ple ple;                 /* ple.ngram < 2: none */
 } sz_model;
 
 /* ---- model files ------------------------------------------------------------------------------------------------------------------
@@ -298,10 +321,15 @@ int sz_session_idx_words(const sz_session* s);
 int sz_session_export(sz_session* s, int what, int layer, void* dst, int64_t bytes, uint64_t stream);
 /* The way back (GpuSession::restore, session.rs:3463-3541): sz_session_reset, then every piece a checkpoint holds through
  * sz_session_import - DELTA_S and DELTA_CONV of every DeltaNet layer, KV_K and KV_V of every attention layer with the `positions`
- * they cover (in sz_session_export's layout), and for a model with the sparse indexer IDX_RAW: the raw indexer keys, f32
- * [positions][idx_dim] (the pooled block keys are rebuilt from them) - and last sz_session_set_len(positions).  The session then
+ * they cover (in sz_session_export's layout), for a model with the sparse indexer IDX_RAW: the raw indexer keys, f32
+ * [positions][idx_dim] (the pooled block keys are rebuilt from them), for a model with per-layer embeddings PLE_HIST and PLE_TAIL -
+ * and last sz_session_set_len(positions).  The session then
  * continues, bit for bit, as the one the pieces were taken from.  No pass may be pending; each call synchronises the stream. */
 #define SZ_STATE_IDX_RAW 6
+/* the per-layer embedding's carried state (any `layer`): PLE_HIST f32 [(conv_k - 1) * ngram][streams * hidden], oldest row first;
+ * PLE_TAIL int32 [8]: the last committed tokens, most recent first (the end-of-text id where the sequence has none) */
+#define SZ_STATE_PLE_HIST 7
+#define SZ_STATE_PLE_TAIL 8
 int sz_session_import(sz_session* s, int what, int layer, const void* src, int64_t bytes, int positions, uint64_t stream);
 int sz_session_set_len(sz_session* s, int positions, uint64_t stream);
 int sz_session_trace_routes(sz_session* s, int on);

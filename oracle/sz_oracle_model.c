@@ -125,11 +125,17 @@ struct szo_session {
     const sz_model* m;
     int kv_q8, threads;
     size_t len;
+    uint32_t* tokens;   /* every token read so far (the PLE hashes the last few) */
+    size_t tok_cap;
+    float* ple_conv;    /* the PLE's conv history: (conv_k - 1) * ngram rows of streams * hidden, oldest first (forward.rs:701) */
     layer_state* st;
     int32_t* routes; /* [n_layer][top_k] of the last step */
     double* route_w;
 };
 
+static size_t ple_hist_floats(const sz_model* m) {
+    return (size_t)(m->ple.conv_k - 1) * (size_t)m->ple.ngram * (size_t)m->cfg.streams * (size_t)m->cfg.hidden;
+}
 static int is_attention(const sz_model_config* c, int l) { return l % c->attn_interval == c->attn_interval - 1; }
 static size_t delta_channels(const sz_model_config* c) { return (size_t)(2 * c->ssm_k_heads + c->ssm_v_heads) * (size_t)c->ssm_head_dim; }
 static size_t delta_s_floats(const sz_model_config* c) { return (size_t)c->ssm_v_heads * (size_t)c->ssm_head_dim * (size_t)c->ssm_head_dim; }
@@ -147,6 +153,7 @@ szo_session* szo_session_new(const sz_model* m, int kv_q8, int threads) {
     }
     s->routes = (int32_t*)calloc((size_t)c->n_layer * (size_t)c->n_expert_used, sizeof(int32_t));
     s->route_w = (double*)calloc((size_t)c->n_layer * (size_t)c->n_expert_used, sizeof(double));
+    if (m->ple.ngram >= 2) s->ple_conv = (float*)calloc(ple_hist_floats(m), sizeof(float));
     return s;
 }
 
@@ -156,7 +163,7 @@ void szo_session_free(szo_session* s) {
         free(s->st[l].s); free(s->st[l].conv); free(s->st[l].k); free(s->st[l].v); free(s->st[l].kq); free(s->st[l].vq);
         free(s->st[l].idx_raw); free(s->st[l].blocks); free(s->st[l].sel); free(s->st[l].scores);
     }
-    free(s->st); free(s->routes); free(s->route_w); free(s);
+    free(s->st); free(s->routes); free(s->route_w); free(s->tokens); free(s->ple_conv); free(s);
 }
 
 int szo_session_len(const szo_session* s) { return (int)s->len; }
@@ -185,6 +192,9 @@ static void kv_reserve(szo_session* s, layer_state* L, size_t positions) {
 void szo_session_assign(szo_session* dst, const szo_session* src) {
     const sz_model_config* c = &src->m->cfg;
     dst->len = src->len;
+    if (src->len > dst->tok_cap) { dst->tok_cap = src->tok_cap; dst->tokens = (uint32_t*)realloc(dst->tokens, dst->tok_cap * sizeof(uint32_t)); }
+    if (src->len && src->tokens) memcpy(dst->tokens, src->tokens, src->len * sizeof(uint32_t));
+    if (src->ple_conv) memcpy(dst->ple_conv, src->ple_conv, ple_hist_floats(src->m) * sizeof(float));
     size_t row = (size_t)c->n_kv_head * (size_t)c->head_dim, rowq = (size_t)c->n_kv_head * szo_kv_q8_head_bytes(c->head_dim);
     for (int l = 0; l < c->n_layer; l++) {
         if (!is_attention(c, l)) {
@@ -256,6 +266,10 @@ void szo_session_fill_synthetic(szo_session* s, int len, uint32_t seed) {
         ai++;
     }
     s->len = (size_t)len;
+    /* the tokens of that history are not known: they read as the end-of-text token to the per-layer embedding, whose conv history is zero */
+    if ((size_t)len > s->tok_cap) { s->tok_cap = (size_t)len * 2; s->tokens = (uint32_t*)realloc(s->tokens, s->tok_cap * sizeof(uint32_t)); }
+    for (int i = 0; i < len; i++) s->tokens[i] = (uint32_t)s->m->ple.eos;
+    if (s->ple_conv) memset(s->ple_conv, 0, ple_hist_floats(s->m) * sizeof(float));
 }
 
 /* Where one piece of the session's state lives (what: 0 recurrent state, 1 carried conv rows, 2 K cache, 3 V cache) and its size. */
@@ -532,6 +546,79 @@ static void attention(szo_session* s, int l, const float* u, float* y) {
     free(qg); free(k); free(v); free(q); free(gate); free(o); free(ex); free(kview); free(vview);
 }
 
+/* forward.rs:1177-1198: the rows of the n-gram table the last tokens select */
+int szo_ple_rows(const sz_ple* p, const uint32_t* tokens, size_t n, int64_t* rows) {
+    long long last_eos = -1;
+    for (size_t i = n; i-- > 0;) if (tokens[i] == (uint32_t)p->eos) { last_eos = (long long)i; break; }
+    int nr = 0;
+    for (int order = 2; order <= p->ngram; order++) {
+        uint64_t mixed = 0;
+        for (int sft = 0; sft < order; sft++) {
+            int64_t tk = (int64_t)(uint32_t)p->eos;
+            if ((size_t)(1 + sft) <= n) {
+                size_t i = n - 1 - (size_t)sft;
+                if (last_eos < 0 || (long long)i >= last_eos) tk = (int64_t)tokens[i];
+            }
+            uint64_t term = (uint64_t)tk * (uint64_t)p->multipliers[sft];   /* wrapping_mul */
+            mixed = sft == 0 ? term : (mixed ^ term);
+        }
+        for (int j = 0; j < p->heads_per_ngram; j++) {
+            int i = (order - 2) * p->heads_per_ngram + j;
+            int64_t v = p->vocab[i], rmd = (int64_t)mixed % v;
+            if (rmd < 0) rmd += v < 0 ? -v : v;                              /* rem_euclid */
+            rows[nr++] = rmd + p->offsets[i];
+        }
+    }
+    return nr;
+}
+
+/* forward.rs:1036-1074: the hashed n-gram memory, added to the whole residual stream */
+static void ple(szo_session* s, float* r) {
+    const sz_model* m = s->m;
+    const sz_model_config* c = &m->cfg;
+    const sz_ple* p = &m->ple;
+    size_t h = (size_t)c->hidden, cs = (size_t)c->streams, ch = cs * h, hd = (size_t)p->head_dim;
+    int64_t rows[SZ_PLE_MAX_HEADS];
+    int nr = szo_ple_rows(p, s->tokens, s->len, rows);
+    float* e = (float*)malloc(h * sizeof(float));
+    size_t rb = row_bytes(&p->table);
+    for (int i = 0; i < nr; i++)
+        szo_dequant(p->table.type, (const uint8_t*)(uintptr_t)p->table.data + (size_t)rows[i] * rb, rb, e + (size_t)i * hd, hd);
+    float* key = (float*)malloc(ch * sizeof(float));
+    float* keyn = (float*)malloc(ch * sizeof(float));
+    float* val = (float*)malloc(h * sizeof(float));
+    float* qry = (float*)malloc(ch * sizeof(float));
+    float* gv = (float*)malloc(ch * sizeof(float));
+    float* gvn = (float*)malloc(ch * sizeof(float));
+    mv(&p->key, e, key, s->threads);
+    rmsnorm_groups(key, f32p(&p->norm_key), ch, h, c->eps, keyn);
+    mv(&p->value, e, val, s->threads);
+    rmsnorm_groups(r, f32p(&p->norm_query), ch, h, c->eps, qry);
+    for (size_t st = 0; st < cs; st++) {
+        double dot = 0.0;
+        for (size_t i = 0; i < h; i++) dot += (double)keyn[st * h + i] * (double)qry[st * h + i];
+        dot /= sqrt((double)h);
+        double ad = fabs(dot) > 1e-6 ? fabs(dot) : 1e-6;
+        double gg = sqrt(ad) * (dot > 0.0 ? 1.0 : (dot < 0.0 ? -1.0 : (signbit(dot) ? -1.0 : 1.0)));   /* f64::signum: +-1, also for +-0 */
+        float sg = szo_sigmoid((float)gg);
+        for (size_t i = 0; i < h; i++) gv[st * h + i] = sg * val[i];
+    }
+    rmsnorm_groups(gv, f32p(&p->norm_conv), ch, h, c->eps, gvn);
+    size_t k = (size_t)p->conv_k, dil = (size_t)p->ngram, hist_len = (k - 1) * dil;
+    const float* w = f32p(&p->conv1d);
+    for (size_t i = 0; i < ch; i++) {
+        double acc = (double)w[i * k + (k - 1)] * (double)gvn[i];
+        for (size_t t = 0; t + 1 < k; t++) {
+            size_t back = (k - 1 - t) * dil;
+            acc += (double)w[i * k + t] * (double)s->ple_conv[(hist_len - back) * ch + i];
+        }
+        r[i] += gv[i] + szo_silu((float)acc);
+    }
+    memmove(s->ple_conv, s->ple_conv + ch, (hist_len - 1) * ch * sizeof(float));
+    memcpy(s->ple_conv + (hist_len - 1) * ch, gvn, ch * sizeof(float));
+    free(e); free(key); free(keyn); free(val); free(qry); free(gv); free(gvn);
+}
+
 /* Session::step (forward.rs:751-794).  logits may be NULL (prefill rows whose logits nobody reads); hidden_out, when not NULL,
  * receives the head's input u (the trace stream `final_u`). */
 void szo_session_step(szo_session* s, uint32_t token, float* logits, float* final_u) {
@@ -539,6 +626,8 @@ void szo_session_step(szo_session* s, uint32_t token, float* logits, float* fina
     const sz_model_config* c = &m->cfg;
     size_t h = (size_t)c->hidden, cs = (size_t)c->streams;
     s->len += 1;
+    if (s->len > s->tok_cap) { s->tok_cap = s->tok_cap ? s->tok_cap * 2 : 256; while (s->tok_cap < s->len) s->tok_cap *= 2; s->tokens = (uint32_t*)realloc(s->tokens, s->tok_cap * sizeof(uint32_t)); }
+    s->tokens[s->len - 1] = token;
     float* emb = (float*)malloc(h * sizeof(float));
     size_t rb = row_bytes(&m->token_embd);
     szo_dequant(m->token_embd.type, (const uint8_t*)(uintptr_t)m->token_embd.data + (size_t)token * rb, rb, emb, h);
@@ -549,6 +638,7 @@ void szo_session_step(szo_session* s, uint32_t token, float* logits, float* fina
     float* g = (float*)malloc(cs * sizeof(float));
     for (int l = 0; l < c->n_layer; l++) {
         const sz_layer* L = &m->layers[l];
+        if (m->ple.ngram >= 2 && l == m->ple.layer) ple(s, r);
         hc_read(s, r, &L->hc_attn, 1, u, g);
         if (is_attention(c, l)) attention(s, l, u, y); else delta_net(s, l, u, y);
         hc_write(r, g, y, h, cs);

@@ -8,6 +8,7 @@
 // then the buffers swap.  The KV cache is append-only: rejected positions are overwritten by the next pass.
 #include "sz_session_kernels.cuh"
 #include "sz_indexer.cuh"
+#include "sz_ple.cuh"
 
 #include <cmath>
 #include <map>
@@ -63,6 +64,10 @@ struct sz_session {
     int has_samp = 0;
     int tree_pass = 0;      // the pass being built / pending is a tree pass (sz_session_verify_tree)
     float* fork = nullptr;  // [v heads][8][d * d]: recurrent states a tree pass branches off
+    // the per-layer embedding (model.ple.ngram >= 2): see sz_ple.cuh
+    float *p_e = nullptr, *p_key = nullptr, *p_val = nullptr, *p_gv = nullptr, *p_gvn = nullptr, *p_hist = nullptr;
+    int32_t* p_tail = nullptr;
+    int64_t p_hist_bytes = 0;
     // the sparse indexer (model.cfg.idx_heads > 0): see sz_indexer.cuh
     float *i_q = nullptr, *i_k = nullptr, *i_qn = nullptr, *i_raw = nullptr, *i_blocks = nullptr, *i_scores = nullptr;
     u32 *i_sel = nullptr, *i_trace = nullptr;
@@ -95,7 +100,8 @@ static int sz_is_attn(const sz_model_config& c, int l) { return l % c.attn_inter
 
 struct SzSessLayout {
     int64_t r, r2, hc_acc, rope, rn, hdown, mix, u, g, y, d_xin, d_z, d_b, d_a, d_xc, d_beta, d_decay, d_og, S0, S1, conv0, conv1, a_qg, a_k, a_v, a_q, a_gate,
-        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, head_q2, head_sc, head_work, fork, i_q, i_k, i_qn, i_raw, i_blocks, i_scores, i_sel, i_list, i_count, i_trace, total;
+        a_o, a_part, kc, vc, logits, tk_tmp, top, ids, res, state, routes, route_w, moe, head_q2, head_sc, head_work, fork, i_q, i_k, i_qn, i_raw, i_blocks, i_scores, i_sel, i_list, i_count, i_trace, p_e, p_key, p_val, p_gv, p_gvn, p_hist, p_tail, total;
+    int64_t p_hist_bytes;
     int64_t i_raw_layer, i_blocks_layer;   // bytes of one attention layer's raw-key and pooled-key caches
     int i_ctx_blocks, i_words;
     int64_t moe_bytes, S_bytes, conv_bytes, kv_bytes, head_work_bytes;
@@ -184,6 +190,12 @@ static int sz_sess_layout(const sz_model* m, int ctx, int flags, SzSessLayout* L
         L->i_list = take(4 * M * (int64_t)L->i_ctx_blocks); L->i_count = take(64);
         L->i_trace = take(4 * na * M * (int64_t)L->i_words);
     }
+    L->p_hist_bytes = 0;
+    if (m->ple.ngram >= 2) {   // the per-layer embedding: the pass's rows and the carried history (two copies, as the DeltaNet's conv rows)
+        L->p_hist_bytes = up256(4 * (int64_t)(m->ple.conv_k - 1) * m->ple.ngram * CH);
+        L->p_e = take(4 * M * H); L->p_key = take(4 * M * CH); L->p_val = take(4 * M * H); L->p_gv = take(4 * M * CH); L->p_gvn = take(4 * M * CH);
+        L->p_hist = take(2 * L->p_hist_bytes); L->p_tail = take(64);
+    }
     L->res = take(64); L->state = take(64);
     L->routes = take(4 * (int64_t)c.n_layer * M * SZ_MAX_TOPK); L->route_w = take(8 * (int64_t)c.n_layer * M * SZ_MAX_TOPK);
     int64_t moe_bytes = 0;
@@ -252,6 +264,21 @@ static int sz_model_check(const sz_model* m) {
     if (c.idx_heads < 0 || c.idx_heads > 8 || (c.idx_heads > 0 && (c.idx_dim < 16 || c.idx_dim > SZ_IDX_MAX_DIM || c.idx_dim % 4 || c.idx_dim < c.rope_dims || c.idx_budget < 1)))
         return sz_fail(SZ_E_ARG, "indexer shape (heads %d, width %d, budget %d): up to 8 heads of 16..%d, at least the rotated dimensions", c.idx_heads, c.idx_dim, c.idx_budget, SZ_IDX_MAX_DIM);
     int rc;
+    if (m->ple.ngram >= 2) {
+        const sz_ple& p = m->ple;
+        const int heads = (p.ngram - 1) * p.heads_per_ngram;
+        if (p.ngram > SZ_PLE_MAX_NGRAM || heads < 1 || heads > SZ_PLE_MAX_HEADS || p.head_dim < 4 || p.head_dim % 4 || (int64_t)heads * p.head_dim != H ||
+            p.layer < 0 || p.layer >= c.n_layer || p.conv_k < 2 || p.conv_k > 8)
+            return sz_fail(SZ_E_ARG, "per-layer embedding shape (layer %d, n-grams to %d, %d heads each of %d, conv %d): the heads' rows side by side are one embedding of %d",
+                           p.layer, p.ngram, p.heads_per_ngram, p.head_dim, p.conv_k, (int)H);
+        for (int i = 0; i < heads; i++)
+            if (p.vocab[i] < 1 || p.offsets[i] < 0 || p.offsets[i] + p.vocab[i] > p.table.rows) return sz_fail(SZ_E_ARG, "per-layer embedding: head %d reaches past the table", i);
+        if ((rc = sz_dense_check(&p.table, "per_layer_token_embd", p.table.rows, p.head_dim))) return rc;
+        if ((rc = sz_dense_check(&p.key, "ple_key", CH, H)) || (rc = sz_dense_check(&p.value, "ple_value", H, H))) return rc;
+        if ((rc = sz_f32_check(&p.norm_key, "ple_norm_key", CH)) || (rc = sz_f32_check(&p.norm_query, "ple_norm_query", CH)) ||
+            (rc = sz_f32_check(&p.norm_conv, "ple_norm_conv", CH)) || (rc = sz_f32_check(&p.conv1d, "ple_conv1d", CH * p.conv_k)))
+            return rc;
+    }
     auto hc = [&](const sz_hc& h, const char* what, bool inject) -> int {
         int r2;
         if ((r2 = sz_f32_check(&h.norm, what, CH))) return r2;
@@ -324,6 +351,13 @@ extern "C" int sz_session_reset(sz_session* s, uint64_t stream) {
     SZ_CUDA(cudaMemsetAsync(s->state, 0, 64, st));
     SZ_CUDA(cudaMemsetAsync(s->res, 0, 64, st));
     if (s->i_count) SZ_CUDA(cudaMemsetAsync(s->i_count, 0, 64, st));
+    if (s->p_hist) {   // no history; every position before the sequence reads as the end-of-text token (forward.rs:1181-1184)
+        SZ_CUDA(cudaMemsetAsync(s->p_hist, 0, (size_t)(2 * s->p_hist_bytes), st));
+        if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
+        for (int i = 0; i < 16; i++) s->h_pin[64 + i] = s->model.ple.eos;
+        SZ_CUDA(cudaMemcpyAsync(s->p_tail, s->h_pin + 64, 64, cudaMemcpyHostToDevice, st));
+        SZ_CUDA(cudaStreamSynchronize(st));
+    }
     if ((rc = sz_moe_scratch_init((uint64_t)s->moe_scratch, s->moe_scratch_bytes, stream))) return rc;
     s->len = 0; s->cur = 0; s->last_m = 0; s->pending_committed = 0; s->inflight = 0;
     return SZ_OK;
@@ -390,6 +424,10 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     s->ids = (int32_t*)(b + L.ids); s->res = (int32_t*)(b + L.res); s->state = (int32_t*)(b + L.state); s->routes = (int32_t*)(b + L.routes); s->route_w = (double*)(b + L.route_w);
     s->moe_scratch = b + L.moe; s->moe_scratch_bytes = L.moe_bytes;
     s->fork = (float*)(b + L.fork);
+    if (m->ple.ngram >= 2) {
+        s->p_e = (float*)(b + L.p_e); s->p_key = (float*)(b + L.p_key); s->p_val = (float*)(b + L.p_val); s->p_gv = (float*)(b + L.p_gv);
+        s->p_gvn = (float*)(b + L.p_gvn); s->p_hist = (float*)(b + L.p_hist); s->p_tail = (int32_t*)(b + L.p_tail); s->p_hist_bytes = L.p_hist_bytes;
+    }
     if (m->cfg.idx_heads > 0) {
         s->i_q = (float*)(b + L.i_q); s->i_k = (float*)(b + L.i_k); s->i_qn = (float*)(b + L.i_qn); s->i_raw = (float*)(b + L.i_raw);
         s->i_blocks = (float*)(b + L.i_blocks); s->i_scores = (float*)(b + L.i_scores); s->i_sel = (u32*)(b + L.i_sel);
@@ -807,6 +845,45 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     return sz_dense_launch(b, st, "attn_output");
 }
 
+// The per-layer embedding before layer model.ple.layer's first read (sz_ple.cuh).  The residual of the moment: with the fused
+// hyper-connection read, the buffer the next read takes as its input, and the pending write's gates in the previous read's accumulator.
+static int sz_ple_layer(sz_session* s, cudaStream_t st, int m, bool pending) {
+    const sz_model_config& c = s->model.cfg;
+    const sz_ple& p = s->model.ple;
+    const int H = c.hidden, C = c.streams, CH = C * H, heads = (p.ngram - 1) * p.heads_per_ngram;
+    if (s->tree_pass) return sz_fail(SZ_E_ARG, "a tree pass on a model with per-layer embeddings is not supported");
+    SzPleGeom g = {};
+    g.ngram = p.ngram; g.heads_per_ngram = p.heads_per_ngram; g.head_dim = p.head_dim; g.conv_k = p.conv_k; g.eos = p.eos; g.table_type = p.table.type;
+    for (int i = 0; i < SZ_PLE_MAX_NGRAM; i++) g.multipliers[i] = p.multipliers[i];
+    for (int i = 0; i < SZ_PLE_MAX_HEADS; i++) { g.vocab[i] = p.vocab[i]; g.offsets[i] = p.offsets[i]; }
+    SZ_CUDA(sz_launch("ple_embed", sz_ple_embed_kernel, dim3(heads, m), dim3(64), 0, st, true, (const int32_t*)s->ids, (const int32_t*)s->p_tail,
+                      (const int32_t*)s->state, g, (const u8*)p.table.data, (long long)p.table.rows, H, s->p_e));
+    SzDenseArgs a = {};
+    a.err = (u32*)(s->state + 2);
+    a.x = s->p_e; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 2;
+    a.job[0] = sz_job(p.key, s->p_key, CH);
+    a.job[1] = sz_job(p.value, s->p_val, H);
+    int rc = sz_dense_launch(a, st, "ple_proj");
+    if (rc) return rc;
+    float* r = s->r;
+    const long long* g_acc = nullptr;
+    const float* g_f = nullptr;
+    if (s->hc_fast) {
+        const int n = s->hc_n;                       // the read that follows
+        r = (n & 1) ? s->r2 : s->r;
+        if (pending) g_acc = s->hc_acc + ((n + 2) % 3) * (int64_t)SZ_MAX_VERIFY * SZ_HC_ACC_ROWS;
+    } else if (pending) {
+        g_f = s->g;
+    }
+    SZ_CUDA(sz_launch("ple_gate", sz_ple_gate_kernel, dim3(C, m), dim3(256), (size_t)2 * H * 4, st, true, r, g_acc, (int)SZ_HC_ACC_ROWS, (int)c.hc_rank, g_f,
+                      (const float*)s->y, (const float*)s->p_key, (const float*)s->p_val, (const float*)p.norm_key.data, (const float*)p.norm_query.data,
+                      (const float*)p.norm_conv.data, H, C, c.eps, s->p_gv, s->p_gvn));
+    SZ_CUDA(sz_launch("ple_conv", sz_ple_conv_kernel, dim3((CH + 255) / 256, m), dim3(256), 0, st, true, r, (const float*)s->p_gv, (const float*)s->p_gvn,
+                      (const float*)s->p_hist, (const float*)((const u8*)s->p_hist + s->p_hist_bytes), (const int32_t*)s->state, (const float*)p.conv1d.data, CH,
+                      (int)p.conv_k, (int)p.ngram));
+    return SZ_OK;
+}
+
 // Runs the m rows through every layer and, with `head`, through the output projection and the top-64.
 static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
     const sz_model_config& c = s->model.cfg;
@@ -819,6 +896,10 @@ static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
     bool pending = false;
     for (int l = 0; l < c.n_layer; l++) {
         const sz_layer& L = s->layers[l];
+        if (s->p_hist && l == s->model.ple.layer) {   // the per-layer embedding joins the residual stream; it applies the pending write itself
+            if ((rc = sz_ple_layer(s, st, m, pending))) return rc;
+            pending = false;
+        }
         if ((rc = sz_hc_read(s, st, L.hc_attn, m, pending, true))) return rc;
         rc = sz_is_attn(c, l) ? sz_attn_layer(s, st, l, m) : sz_delta_layer(s, st, l, m);
         if (rc) return rc;
@@ -856,6 +937,10 @@ static int sz_commit_device(sz_session* s, cudaStream_t st, int m) {
                           (const float*)s->conv[1], (const int32_t*)s->state, (const int32_t*)s->res, (const float*)s->d_xin, (int)ch, (int)c.conv_k,
                           s->conv[0], s->conv[1], s->tree_pass));
     }
+    if (s->p_hist)   // the per-layer embedding's history and token tail as the kept rows leave them
+        SZ_CUDA(sz_launch("ple_commit", sz_ple_commit_kernel, dim3((s->model.ple.conv_k - 1) * s->model.ple.ngram), dim3(256), 0, st, true, (const float*)s->p_gvn,
+                          s->p_hist, (float*)((u8*)s->p_hist + s->p_hist_bytes), s->p_tail, (const int32_t*)s->ids, (const int32_t*)s->state, (const int32_t*)s->res,
+                          (int)(c.streams * c.hidden), (int)((s->model.ple.conv_k - 1) * s->model.ple.ngram)));
     if (s->tree_pass && s->n_attn > 0) {   // the kept rows' keys and values from their rows' slots to their depths' slots
         const int hb = (s->flags & SZ_KV_Q8) ? (c.head_dim + (((c.head_dim >> 5) * 2 + 15) & ~15)) : 4 * c.head_dim;
         SZ_CUDA(sz_launch("kv_compact", sz_kv_compact_kernel, dim3(c.n_kv_head, s->n_attn, 2), dim3(128), 0, st, true, s->kc, s->vc, (const int32_t*)s->state,
@@ -1223,6 +1308,12 @@ extern "C" int sz_session_export(sz_session* s, int what, int layer, void* dst, 
         for (int h = 0; h < c.n_kv_head && s->len > 0; h++)
             SZ_CUDA(cudaMemcpy2DAsync((u8*)dst + h * hb, (size_t)(c.n_kv_head * hb), base + (int64_t)h * s->ctx * hb, (size_t)hb, (size_t)hb, (size_t)s->len,
                                       cudaMemcpyDeviceToHost, st));
+    } else if (what == SZ_STATE_PLE_HIST || what == SZ_STATE_PLE_TAIL) {
+        if (!s->p_hist) return sz_fail(SZ_E_ARG, "sz_session_export: the model has no per-layer embedding");
+        const int64_t n = what == SZ_STATE_PLE_TAIL ? 32 : 4 * (int64_t)(s->model.ple.conv_k - 1) * s->model.ple.ngram * c.streams * c.hidden;
+        if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_export: %lld bytes given, the piece has %lld", (long long)bytes, (long long)n);
+        const u8* src = what == SZ_STATE_PLE_TAIL ? (const u8*)(s->p_tail + (s->cur ? 8 : 0)) : (const u8*)s->p_hist + (s->cur ? s->p_hist_bytes : 0);
+        SZ_CUDA(cudaMemcpyAsync(dst, src, (size_t)n, cudaMemcpyDeviceToHost, st));
     } else if (what == SZ_STATE_IDX_RAW) {
         if (!attn || !s->i_raw) return sz_fail(SZ_E_ARG, "sz_session_export: layer %d has no sparse indexer", layer);
         const int64_t n = 4 * (int64_t)s->len * c.idx_dim;
@@ -1277,6 +1368,12 @@ extern "C" int sz_session_import(sz_session* s, int what, int layer, const void*
         for (int h = 0; h < c.n_kv_head && positions > 0; h++)   // [position][kv head][head] of the checkpoint into the cache's [kv head][position][head]
             SZ_CUDA(cudaMemcpy2DAsync(base + (int64_t)h * s->ctx * hb, (size_t)hb, (const u8*)src + h * hb, (size_t)(c.n_kv_head * hb), (size_t)hb, (size_t)positions,
                                       cudaMemcpyHostToDevice, st));
+    } else if (what == SZ_STATE_PLE_HIST || what == SZ_STATE_PLE_TAIL) {
+        if (!s->p_hist) return sz_fail(SZ_E_ARG, "sz_session_import: the model has no per-layer embedding");
+        const int64_t n = what == SZ_STATE_PLE_TAIL ? 32 : 4 * (int64_t)(s->model.ple.conv_k - 1) * s->model.ple.ngram * c.streams * c.hidden;
+        if (bytes != n) return sz_fail(SZ_E_ARG, "sz_session_import: %lld bytes given, the piece has %lld", (long long)bytes, (long long)n);
+        u8* dst = what == SZ_STATE_PLE_TAIL ? (u8*)(s->p_tail + (s->cur ? 8 : 0)) : (u8*)s->p_hist + (s->cur ? s->p_hist_bytes : 0);
+        SZ_CUDA(cudaMemcpyAsync(dst, src, (size_t)n, cudaMemcpyHostToDevice, st));
     } else if (what == SZ_STATE_IDX_RAW) {
         if (!attn || !s->i_raw) return sz_fail(SZ_E_ARG, "sz_session_import: layer %d has no sparse indexer", layer);
         const int ai = s->lb[layer].attn_index, ratio = s->layers[layer].idx_ratio > 0 ? s->layers[layer].idx_ratio : 1;

@@ -46,7 +46,7 @@ class HeadC(C.Structure):
 
 
 PLACE_HOST, PLACE_DEVICE = 0, 1
-STATE_DELTA_S, STATE_DELTA_CONV, STATE_KV_K, STATE_KV_V, STATE_IDX_SELECTED, STATE_IDX_SCORES, STATE_IDX_RAW = range(7)
+STATE_DELTA_S, STATE_DELTA_CONV, STATE_KV_K, STATE_KV_V, STATE_IDX_SELECTED, STATE_IDX_SCORES, STATE_IDX_RAW, STATE_PLE_HIST, STATE_PLE_TAIL = range(9)
 HEAD_XR, HEAD_XQ, HEAD_XSC, HEAD_XCORR, HEAD_BMAX, HEAD_SEL, HEAD_ERR = range(7)
 
 # name -> (restype, argtypes); every symbol include/shadowzero_b200.h declares

@@ -35,8 +35,15 @@ class Layer(C.Structure):
                [("idx_ratio", C.c_int32), ("idx_reserved", C.c_int32), ("moe", szlib.MoeLayerC)]
 
 
+class Ple(C.Structure):
+    """struct sz_ple"""
+    _fields_ = [(n, C.c_int32) for n in ("layer", "ngram", "heads_per_ngram", "head_dim", "conv_k", "eos")] + \
+               [("multipliers", C.c_int64 * 8), ("vocab", C.c_int64 * 32), ("offsets", C.c_int64 * 32)] + \
+               [(n, Tensor) for n in ("table", "key", "value", "norm_key", "norm_query", "norm_conv", "conv1d")]
+
+
 class Model(C.Structure):
-    _fields_ = [("cfg", ModelConfig), ("token_embd", Tensor), ("output", Tensor), ("output_hc", Hc), ("layers", C.POINTER(Layer))]
+    _fields_ = [("cfg", ModelConfig), ("token_embd", Tensor), ("output", Tensor), ("output_hc", Hc), ("layers", C.POINTER(Layer)), ("ple", Ple)]
 
 
 class Sampler(C.Structure):
@@ -172,6 +179,17 @@ def make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_Q8_0, sha
         mat("token_embd.weight", cfg["vocab"], H, dense_type)
         mat("output.weight", cfg["vocab"], H, dense_type)
     hc("output_hc", False)
+    if cfg.get("ple_ngram", 0) >= 2:
+        # the hashed n-gram memory of one layer: (ngram - 1) * heads_per_ngram table rows of ple_head_dim weights make up one embedding
+        pl, nh_ = cfg["ple_layer"], (cfg["ple_ngram"] - 1) * cfg["ple_heads_per_ngram"]
+        assert nh_ * cfg["ple_head_dim"] == H and len(cfg["ple_vocab"]) == nh_ and len(cfg["ple_offsets"]) == nh_
+        pp = "blk.%d." % pl
+        mat("per_layer_token_embd.weight", cfg["ple_offsets"][-1] + cfg["ple_vocab"][-1], cfg["ple_head_dim"], cfg.get("ple_table_type", szlib.TYPE_Q8_0))
+        mat(pp + "ple_key.weight", CH, H, hc_type)
+        mat(pp + "ple_value.weight", H, H, hc_type)
+        for n_ in ("ple_norm_key", "ple_norm_query", "ple_norm_conv"):
+            vec(pp + n_ + ".weight", 1.0 + synth.normal((CH,), 0.1, seed, pp + n_, device))
+        vec(pp + "ple_conv1d.weight", synth.normal((CH, cfg["ple_conv_k"]), 0.3, seed, pp + "ple_conv1d", device).reshape(-1))
     moe_layers = []
     for l in range(cfg["n_layer"]):
         p = "blk.%d." % l
@@ -237,6 +255,17 @@ class _Placed:
             return h
 
         self.model.token_embd, self.model.output, self.model.output_hc = tens("token_embd.weight"), tens("output.weight"), hc("output_hc", False)
+        if cfg.get("ple_ngram", 0) >= 2:
+            P, pp = self.model.ple, "blk.%d." % cfg["ple_layer"]
+            for k in ("layer", "ngram", "heads_per_ngram", "head_dim", "conv_k", "eos"):
+                setattr(P, k, int(cfg["ple_" + k]))
+            for i, v in enumerate(cfg["ple_multipliers"]):
+                P.multipliers[i] = int(v)
+            for i, (v, o) in enumerate(zip(cfg["ple_vocab"], cfg["ple_offsets"])):
+                P.vocab[i], P.offsets[i] = int(v), int(o)
+            P.table, P.key, P.value = tens("per_layer_token_embd.weight"), tens(pp + "ple_key.weight"), tens(pp + "ple_value.weight")
+            P.norm_key, P.norm_query, P.norm_conv = tens(pp + "ple_norm_key.weight"), tens(pp + "ple_norm_query.weight"), tens(pp + "ple_norm_conv.weight")
+            P.conv1d = tens(pp + "ple_conv1d.weight")
         self.layers = (Layer * cfg["n_layer"])()
         for l in range(cfg["n_layer"]):
             p = "blk.%d." % l
@@ -415,6 +444,10 @@ class Session:
             a = np.empty((c["ssm_v_heads"], c["ssm_head_dim"], c["ssm_head_dim"]), dtype=np.float32)
         elif what == szlib.STATE_DELTA_CONV:
             a = np.empty((c["conv_k"] - 1, (2 * c["ssm_k_heads"] + c["ssm_v_heads"]) * c["ssm_head_dim"]), dtype=np.float32)
+        elif what == szlib.STATE_PLE_HIST:
+            a = np.empty(((c["ple_conv_k"] - 1) * c["ple_ngram"], c["streams"] * c["hidden"]), dtype=np.float32)
+        elif what == szlib.STATE_PLE_TAIL:
+            a = np.empty(8, dtype=np.int32)
         elif what == szlib.STATE_IDX_RAW:
             a = np.empty((len(self), c["idx_dim"]), dtype=np.float32)
         elif what == szlib.STATE_IDX_SELECTED:
@@ -437,6 +470,8 @@ class Session:
             else:
                 kinds = [szlib.STATE_DELTA_S, szlib.STATE_DELTA_CONV]
             pieces += [(k, l, self.export(k, l)) for k in kinds]
+        if c.get("ple_ngram", 0) >= 2:
+            pieces += [(k, 0, self.export(k, 0)) for k in (szlib.STATE_PLE_HIST, szlib.STATE_PLE_TAIL)]
         return dict(positions=len(self), pieces=pieces)
 
     def restore(self, ck):
