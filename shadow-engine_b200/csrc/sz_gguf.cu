@@ -9,9 +9,9 @@
 // Two placements.  HOST: the file is mapped and every tensor address points into the mapping (what a CPU consumer of struct
 // sz_model reads).  DEVICE: one device allocation, every tensor copied to a 256-byte aligned place of its own; EXL3 blobs are placed
 // so that their trellis starts on a 16-byte boundary, and EXL3 expert slices are re-strided to a multiple of 16 bytes, as the
-// kernels need (the file cannot give that: its alignment applies to the blob's first byte).  The per-layer-embedding branch of the
-// reference's checkpoints is not part of this build: its keys are read and must describe "none" (no layer in ple.layers below
-// block_count), its tensors are ignored.  The sparse indexer is read when attention.indexer.head_count is not 0.
+// kernels need (the file cannot give that: its alignment applies to the blob's first byte).  The per-layer embedding is read when
+// ple.layers names a layer of the model (one at most, as in the reference), the sparse indexer when
+// attention.indexer.head_count is not 0.
 #include "sz_common.cuh"
 
 #include <fcntl.h>
@@ -328,6 +328,18 @@ int build(Placer& P) {
     if ((rc = tens(P, "token_embd.weight", H, c.vocab, &w->model.token_embd))) return rc;
     if ((rc = tens(P, "output.weight", H, c.vocab, &w->model.output))) return rc;
     if ((rc = hc(P, c, "output_hc", false, &w->model.output_hc))) return rc;
+    if (w->model.ple.ngram >= 2) {   // the per-layer embedding of one layer (forward.rs:93-136; tensor names docs/ARCH.md:171-172)
+        sz_ple& p = w->model.ple;
+        const std::string pp = "blk." + std::to_string(p.layer) + ".";
+        const int64_t CH = (int64_t)c.streams * H;
+        const GTensor* tt = w->find("per_layer_token_embd.weight");
+        if (!tt || tt->dims.size() < 2 || (int64_t)tt->dims[0] != p.head_dim) return sz_fail(SZ_E_ARG, "per_layer_token_embd.weight: a table of rows of %d weights is expected", p.head_dim);
+        if ((rc = tens(P, "per_layer_token_embd.weight", p.head_dim, (int64_t)tt->dims[1], &p.table))) return rc;
+        if ((rc = tens(P, pp + "ple_key.weight", H, CH, &p.key)) || (rc = tens(P, pp + "ple_value.weight", H, H, &p.value))) return rc;
+        if ((rc = vec(P, pp + "ple_norm_key.weight", CH, &p.norm_key)) || (rc = vec(P, pp + "ple_norm_query.weight", CH, &p.norm_query)) ||
+            (rc = vec(P, pp + "ple_norm_conv.weight", CH, &p.norm_conv)) || (rc = vec(P, pp + "ple_conv1d.weight", CH * p.conv_k, &p.conv1d)))
+            return rc;
+    }
     for (int l = 0; l < c.n_layer; l++) {
         sz_layer& L = w->layers[l];
         const std::string p = "blk." + std::to_string(l) + ".";
@@ -424,11 +436,33 @@ extern "C" int sz_model_load_gguf(const char* path, int placement, uint64_t stre
     const GTensor* ow = w->find("output.weight");
     if (!ow || ow->dims.size() < 2) { delete w; return sz_fail(SZ_E_ARG, "%s: no output.weight", path); }
     c.vocab = (int32_t)ow->dims[1];                                                               // forward.rs:106
-    // the branches this build does not have must be switched off in the file
-    const GVal* pl = w->key("ple.layers");
-    if (pl)
-        for (int64_t l : pl->ints)
-            if (l >= 0 && l < c.n_layer) { delete w; return sz_fail(SZ_E_TYPE, "%s: layer %lld has per-layer embeddings (ple.layers); that branch is not part of this build", path, (long long)l); }
+    // the per-layer embedding (forward.rs:93-136): one layer at most, as in the reference; a layer index past the last = none
+    {
+        const GVal* pl = w->key("ple.layers");
+        int n_ple = 0;
+        int64_t which = -1;
+        if (pl)
+            for (int64_t l : pl->ints)
+                if (l >= 0 && l < c.n_layer) { n_ple++; which = l; }
+        if (n_ple > 1) { delete w; return sz_fail(SZ_E_TYPE, "%s: ple.layers names %d layers; one per-layer embedding is implemented (as in the reference)", path, n_ple); }
+        if (n_ple == 1) {
+            sz_ple& p = w->model.ple;
+            p = sz_ple();
+            p.layer = (int32_t)which;
+            if ((rc = get_u(w, "ple.ngram_size", &p.ngram)) || (rc = get_u(w, "ple.heads_per_ngram", &p.heads_per_ngram)) ||
+                (rc = get_u(w, "embedding_length_per_layer_input", &p.head_dim)) || (rc = get_u(w, "ple.conv_kernel", &p.conv_k)) ||
+                (rc = get_u(w, "ple.eos_token_id", &p.eos))) { delete w; return rc; }
+            const GVal *km = w->key("ple.layer_multipliers"), *kv = w->key("ple.head_vocab_sizes"), *ko = w->key("ple.head_offsets");
+            const int heads = (p.ngram - 1) * p.heads_per_ngram;
+            if (p.ngram < 2 || p.ngram > SZ_PLE_MAX_NGRAM || heads < 1 || heads > SZ_PLE_MAX_HEADS || !km || !kv || !ko || (int)km->ints.size() < p.ngram ||
+                (int)kv->ints.size() < heads || (int)ko->ints.size() < heads) {
+                delete w;
+                return sz_fail(SZ_E_ARG, "%s: the per-layer embedding's keys (ple.ngram_size, ple.heads_per_ngram, ple.layer_multipliers, ple.head_vocab_sizes, ple.head_offsets) do not fit together", path);
+            }
+            for (int i = 0; i < p.ngram; i++) p.multipliers[i] = km->ints[i];
+            for (int i = 0; i < heads; i++) { p.vocab[i] = kv->ints[i]; p.offsets[i] = ko->ints[i]; }
+        }
+    }
     // the sparse indexer (forward.rs:137-140): heads 0 = the file has none (its budget is then never reached)
     {
         int32_t ih = 0, id = 0, ib = 0;

@@ -61,11 +61,17 @@ def write_gguf(path, M, arch="qwen4exp"):
         _kv(arch + ".ssm.time_step_rank", T_U32, cfg["ssm_v_heads"]), _kv(arch + ".ssm.inner_size", T_U32, cfg["ssm_v_heads"] * cfg["ssm_head_dim"]),
         _kv(arch + ".ssm.conv_kernel", T_U32, cfg["conv_k"]), _kv(arch + ".full_attention_interval", T_U32, cfg["attn_interval"]),
         _kv(arch + ".hyper_connection.count", T_U32, cfg["streams"]), _kv(arch + ".hyper_connection.low_rank", T_U32, cfg["hc_rank"]),
-        # the per-layer-embedding branch: present for the reference's Config::from_gguf, describing none
-        _kv(arch + ".ple.layers", T_ARR, [n_layer]), _kv(arch + ".ple.ngram_size", T_U32, 1), _kv(arch + ".ple.heads_per_ngram", T_U32, 1),
-        _kv(arch + ".embedding_length_per_layer_input", T_U32, 0), _kv(arch + ".ple.conv_kernel", T_U32, 1), _kv(arch + ".ple.eos_token_id", T_U32, 0),
-        _kv(arch + ".ple.layer_multipliers", T_ARR, []), _kv(arch + ".ple.head_vocab_sizes", T_ARR, []), _kv(arch + ".ple.head_offsets", T_ARR, []),
     ]
+    if cfg.get("ple_ngram", 0) >= 2:  # the per-layer embedding of one layer (forward.rs:93-136)
+        kvs += [_kv(arch + ".ple.layers", T_ARR, [cfg["ple_layer"]]), _kv(arch + ".ple.ngram_size", T_U32, cfg["ple_ngram"]),
+                _kv(arch + ".ple.heads_per_ngram", T_U32, cfg["ple_heads_per_ngram"]), _kv(arch + ".embedding_length_per_layer_input", T_U32, cfg["ple_head_dim"]),
+                _kv(arch + ".ple.conv_kernel", T_U32, cfg["ple_conv_k"]), _kv(arch + ".ple.eos_token_id", T_U32, cfg["ple_eos"]),
+                _kv(arch + ".ple.layer_multipliers", T_ARR, list(cfg["ple_multipliers"])), _kv(arch + ".ple.head_vocab_sizes", T_ARR, list(cfg["ple_vocab"])),
+                _kv(arch + ".ple.head_offsets", T_ARR, list(cfg["ple_offsets"]))]
+    else:                             # none: the keys are there for the reference's Config::from_gguf, naming a layer past the last
+        kvs += [_kv(arch + ".ple.layers", T_ARR, [n_layer]), _kv(arch + ".ple.ngram_size", T_U32, 1), _kv(arch + ".ple.heads_per_ngram", T_U32, 1),
+                _kv(arch + ".embedding_length_per_layer_input", T_U32, 0), _kv(arch + ".ple.conv_kernel", T_U32, 1), _kv(arch + ".ple.eos_token_id", T_U32, 0),
+                _kv(arch + ".ple.layer_multipliers", T_ARR, []), _kv(arch + ".ple.head_vocab_sizes", T_ARR, []), _kv(arch + ".ple.head_offsets", T_ARR, [])]
     if cfg.get("idx_heads", 0) > 0:   # the sparse indexer of the attention layers (forward.rs:137-140)
         ratios = [int(cfg.get("idx_ratio", 4)) if (l % cfg["attn_interval"] == cfg["attn_interval"] - 1) else 0 for l in range(n_layer)]
         kvs += [_kv(arch + ".attention.indexer.head_count", T_U32, cfg["idx_heads"]), _kv(arch + ".attention.indexer.key_length", T_U32, cfg["idx_dim"]),
@@ -125,6 +131,11 @@ class LoadedModel:
         self.model = md.Model.from_address(self.lib.sz_weights_model(self.h))
         c = self.model.cfg
         self.cfg = {n: getattr(c, n) for n, _ in md.ModelConfig._fields_ if n != "reserved"}
+        P = self.model.ple
+        if P.ngram >= 2:
+            heads = (P.ngram - 1) * P.heads_per_ngram
+            self.cfg.update(ple_layer=P.layer, ple_ngram=P.ngram, ple_heads_per_ngram=P.heads_per_ngram, ple_head_dim=P.head_dim, ple_conv_k=P.conv_k,
+                            ple_eos=P.eos, ple_multipliers=list(P.multipliers[:P.ngram]), ple_vocab=list(P.vocab[:heads]), ple_offsets=list(P.offsets[:heads]))
 
     def tensor_info(self, name):
         ty, dims, n = C.c_int32(), (C.c_int64 * 4)(), C.c_int64()

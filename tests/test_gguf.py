@@ -124,7 +124,24 @@ def test_a_file_with_a_sparse_indexer_reads_back_to_the_same_bits(tmp_path):
     lm.close()
 
 
-def test_files_that_switch_on_a_branch_this_build_lacks_are_refused(small_file, tmp_path):
+def test_a_file_with_a_per_layer_embedding_reads_back_to_the_same_bits(tmp_path):
+    from tests.test_oracle_ple import PLE
+    M = md.make_model(PLE, seed=2)
+    path = str(tmp_path / "ple.gguf")
+    gio.write_gguf(path, M)
+    lm = gio.LoadedModel(path)
+    for k in ("ple_layer", "ple_ngram", "ple_heads_per_ngram", "ple_head_dim", "ple_conv_k", "ple_eos", "ple_multipliers", "ple_vocab", "ple_offsets"):
+        assert lm.cfg[k] == PLE[k], k
+    a = ob.Session(md.HostModel(M), kv_q8=True, threads=2)
+    b = ob.Session(lm, kv_q8=True, threads=2)
+    for t in (3, 500, 17, 7, 256, 9, 9, 41):
+        la, lb = a.step(t), b.step(t)
+        assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    del b
+    lm.close()
+
+
+def test_files_whose_keys_do_not_fit_are_refused(small_file, tmp_path):
     M, path = small_file
     L = szlib.load()
     raw = open(path, "rb").read()
@@ -134,8 +151,8 @@ def test_files_that_switch_on_a_branch_this_build_lacks_are_refused(small_file, 
     bad = str(tmp_path / "ple.gguf")
     open(bad, "wb").write(raw[:at + 16] + struct.pack("<q", 1) + raw[at + 24:])
     h = C.c_void_p()
-    assert L.sz_model_load_gguf(bad.encode(), szlib.PLACE_HOST, 0, C.byref(h)) == szlib.E_TYPE
-    assert b"per-layer embeddings" in L.sz_last_error()
+    assert L.sz_model_load_gguf(bad.encode(), szlib.PLACE_HOST, 0, C.byref(h)) == szlib.E_ARG   # a layer is named, the rest of its keys say "none"
+    assert b"per-layer embedding" in L.sz_last_error()
     # a missing shape key: the reader says which (forward.rs:78)
     key = b"qwen4exp.ssm.conv_kernel"
     at = raw.index(key)
