@@ -99,3 +99,19 @@ def test_tree_passes_are_refused(model):
     s = md.Session(dm, 64, kv_q8=True)
     with pytest.raises(szlib.SzError):
         s.verify_tree([1, 2, 3], [-1, 0, 0])
+
+
+def test_a_model_with_every_optional_branch_from_its_file_on_the_device(tmp_path):
+    """Per-layer embedding and sparse indexer together, written as a GGUF, loaded onto the device by the library: speculative
+    generation equals the CPU loop on the same file (tokens and the accepted count of every pass), past the indexer's threshold."""
+    gio = pkg.gguf_io
+    cfg = dict(PLE, idx_heads=2, idx_dim=32, idx_budget=16, idx_ratio=4)
+    M = md.make_model(cfg, seed=6, cycle_alpha=0.9)
+    path = str(tmp_path / "all.gguf")
+    gio.write_gguf(path, M)
+    host, dev = gio.LoadedModel(path), gio.LoadedModel(path, device="cuda:0")
+    prompt = md.make_prompt(64, cfg["vocab"], seed=8)
+    want_toks, want_log, want_st = ob.Session(host, kv_q8=True, threads=4).generate(prompt, 48, spec_k=3)
+    toks, log, st = md.Session(dev, 256, kv_q8=True).generate(prompt, 48, spec_k=3)
+    assert toks == want_toks and log == want_log
+    assert st.accepted == want_st.accepted and st.passes > 0
