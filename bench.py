@@ -378,7 +378,7 @@ def run_c3(args):
     n_k = 0
     for rep in range(2):
         szlib.check(L.sz_trace_begin(arr, nev, sess.stream))
-        sess.verify([int(prompt[0])] + [int(t) for t in other[:3]], accept=1)
+        sess.verify([int(prompt[0])] + [int(t) for t in other[:args.trace_rows - 1]], accept=1)
         n_k = L.sz_trace_end()
         (kept, _), _, _ = sess.result()
         sess.commit(kept)
@@ -621,7 +621,8 @@ def run_reference_c3(args):
     cpu_line = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
     print(json.dumps({
         "impl": "reference", "metric": C3_METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32 (f64 accumulate)",
+        "ms_per_step": 1e3 / v, "higher_is_better": True, "scaling": "weak" if args.gpus > 1 and args.parallelism == "replicas" else "strong",
+        "vs_baseline": None, "dtype": "f32 (f64 accumulate)",
         "data": "synthetic", "config": c3_config(args, c3_model_cfg(args, args.n_layer), args.ctx),
         "cpu_baseline": cpu_line, "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
 
@@ -1032,6 +1033,7 @@ def main():
                     help="c3, N > 1: every GPU with the whole 33 GB model and requests of its own, no exchange on the data path (default: "
                          "weak scaling, the throughput form), or experts sharded over the GPUs and ONE sequence (strong scaling: batch-1 "
                          "expert parallelism, which pays an exchange a layer and cannot scale)")
+    ap.add_argument("--trace-rows", type=int, default=4, help="c3: rows of the pass whose launches are timed one by one (the line's `kernels`)")
     ap.add_argument("--profile-passes", type=int, default=0, help="c3: only run this many 4-row verify passes (for ncu), no timing")
     ap.add_argument("--head", default="proxy", choices=["q8", "exl3", "proxy"],
                     help="c3: output.weight as Q8_0 read in full, as 4-bit EXL3 read in full, or EXL3 screened by its 2-bit proxy (Q2_P)")
