@@ -110,6 +110,17 @@ int sz_moe_verify(const sz_moe_layer* layer, uint64_t x, int m, uint64_t y, uint
 int sz_moe_verify_host(const sz_moe_layer* layer, const float* x_host, int m, float* y_host, int32_t* route_idx_host,
                        double* route_w_host, uint64_t x_dev, uint64_t y_dev, uint64_t scratch, int64_t scratch_bytes,
                        uint64_t stream);
+/* The same sublayer over MANY rows at once (a prompt chunk; the verify rows of many sequences): y[j] = moe(x[j]) for j < rows, rows a
+ * multiple of 8 up to 256, every distinct expert decoded once for all the rows that chose it.  The role of the reference's grouped
+ * experts of a long prompt (plan_scan_w / plan_fill_w, kernels/forward.cu:3234-3319; mma_grouped*, kernels/matvec.cu:1190-1260;
+ * exl3_mma, kernels/exl3.cu:500-590), with the verify pass's exact kernels: a row's output is bit for bit sz_moe_verify's.  EXL3
+ * experts, no expert sharding.  sz_moe_rows_status(layer, rows, scratch, NULL, stream) once after the scratch is allocated (and
+ * after a failed call); with a code pointer it synchronises and reports (bit 0: a bounded wait ran out, bit 1: the routing needed
+ * more windows than the scratch has). */
+int sz_moe_rows_scratch_bytes(const sz_moe_layer* layer, int rows, int64_t* bytes);
+int sz_moe_rows(const sz_moe_layer* layer, uint64_t x, int rows, uint64_t y, uint64_t route_idx, uint64_t route_w, uint64_t scratch,
+                int64_t scratch_bytes, uint64_t stream);
+int sz_moe_rows_status(const sz_moe_layer* layer, int rows, uint64_t scratch, int* code, uint64_t stream);
 /* Number of kernel launches one sz_moe_verify call makes for this layer (for launch accounting). */
 int sz_moe_launches(const sz_moe_layer* layer);
 

@@ -4,6 +4,7 @@
 #include "sz_moe.cuh"
 #include "sz_moe_exl3w.cuh"
 #include "sz_moe_blk.cuh"
+#include "sz_moe_rows.cuh"
 
 #include <float.h>
 #include <stdlib.h>
@@ -75,6 +76,13 @@ sz_route_kernel(const float* __restrict__ x, int H, const float* __restrict__ ro
     const int ld = ne + 1;
     const int nrows = ne + (shared_router != nullptr ? 1 : 0);
     const int row0 = blockIdx.x * RB;
+    // grid.y > 1 (sz_moe_rows): block row y routes rows y * M .. of a longer batch, with tables and a ticket of its own
+    if (gridDim.y > 1) {
+        const size_t cy = blockIdx.y;
+        x += cy * M * H; logits += cy * M * ld; ridx += cy * M * k; rw += cy * M * k; plan += cy; plan_sh += cy; ctrl += cy * 16;
+        if (out_idx) out_idx += cy * M * k;
+        if (out_w) out_w += cy * M * k;
+    }
     SZ_PH_DECL;
     SZ_PH();  // 0 start
     // the router rows do not depend on the previous kernel: fetched before waiting for it
@@ -754,7 +762,7 @@ static int sz_ffn(cudaStream_t st, int type, const SzPlan* plan, int groups, u64
 
 template <int K, int NTC>
 static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const SzPlan* plan, const float* x, long long* acc_gu, long long* acc_d,
-                          u32* ctrl, bool sh) {
+                          u32* ctrl, bool sh, bool only_xw = false) {
     static bool set = false;
     if (!set) {
         SZ_CUDA(cudaFuncSetAttribute(sz_x3_gateup_kernel<K, NTC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzX3<K, NTC>::SMEM_BYTES));
@@ -764,7 +772,7 @@ static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const S
     // SZ_X3_CLASSIC=1: the block-synchronous kernels of sz_moe_exl3.cuh (the second implementation; same bits) instead of the
     // warp-specialised ones
     const char* cl = getenv("SZ_X3_CLASSIC");   // (read at every call: a test switches it inside one process)
-    const bool classic = cl && atoi(cl) != 0;
+    const bool classic = !only_xw && cl && atoi(cl) != 0;
     if (!classic) {
         // Shape of the launch: OCC blocks a multiprocessor (2 or 3), a unit 8 TW tile columns a consumer warp wide (TW = 4, 2 or 1: 24, 12
         // or 6 KB of trellis at 3 bits).  Narrower units and a third block spread the units evenly: gate / up of 40 experts of the
@@ -826,9 +834,9 @@ static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const S
 }
 
 static int sz_x3_launch(cudaStream_t st, const sz_moe_layer* L, int m, const SzPlan* plan, const float* x, long long* acc_gu, long long* acc_d,
-                        u32* ctrl, bool sh) {
+                        u32* ctrl, bool sh, bool only_xw = false) {
     const int K = L->expert_type - 1020, NTC = L->expert_ff / 128;
-#define SZ_X3_CASE(KK, NN) if (K == KK && NTC == NN) return sz_x3_launch_k<KK, NN>(st, L, m, plan, x, acc_gu, acc_d, ctrl, sh);
+#define SZ_X3_CASE(KK, NN) if (K == KK && NTC == NN) return sz_x3_launch_k<KK, NN>(st, L, m, plan, x, acc_gu, acc_d, ctrl, sh, only_xw);
     SZ_X3_CASE(2, 1) SZ_X3_CASE(2, 2) SZ_X3_CASE(2, 4) SZ_X3_CASE(3, 1) SZ_X3_CASE(3, 2) SZ_X3_CASE(3, 4) SZ_X3_CASE(4, 1) SZ_X3_CASE(4, 2) SZ_X3_CASE(4, 4)
 #undef SZ_X3_CASE
     return sz_fail(SZ_E_TYPE, "no streaming EXL3 kernel for K = %d, FF = %d", K, L->expert_ff);
@@ -984,6 +992,137 @@ extern "C" int sz_moe_verify(const sz_moe_layer* L, uint64_t x, int m, uint64_t 
     const bool exchange = sz_ep_world() > 1;
     if (exchange && (rc = sz_ep_allreduce_i64(y_fix, (size_t)m * L->hidden, (cudaStream_t)stream))) return rc;
     return sz_moe_finish_launch((uint64_t)y_fix, m, L->hidden, y, stream, !exchange);
+}
+
+// ---- many rows at once (sz_moe_rows.cuh) ---------------------------------------------------------------------------------------------
+struct SzRowsScratch {
+    int64_t ctrl, logits, ridx, rw, cplan, cplan_sh, plan, xg, acc_gu, acc_d, total;
+    int64_t gu_row, d_row;   // i64 elements a slot
+};
+static SzRowsScratch sz_rows_layout(const sz_moe_layer* L, int R) {
+    SzRowsScratch s;
+    int64_t o = 0;
+    const int chunks = R / 8, W = SZ_ROWS_WIN + SZ_ROWS_SHWIN;
+    const int64_t ffm = L->expert_ff > L->shared_ff ? L->expert_ff : L->shared_ff;
+    s.ctrl = o; o = sz_up256(o + 64 * (int64_t)(chunks + 1));            // one block of 16 words a chunk (the router's ticket), then the expert kernels'
+    s.logits = o; o = sz_up256(o + 4 * (int64_t)R * (L->n_expert + 1));
+    s.ridx = o; o = sz_up256(o + 4 * (int64_t)R * L->top_k);
+    s.rw = o; o = sz_up256(o + 8 * (int64_t)R * L->top_k);
+    s.cplan = o; o = sz_up256(o + (int64_t)sizeof(SzPlan) * chunks);
+    s.cplan_sh = o; o = sz_up256(o + (int64_t)sizeof(SzPlan) * chunks);
+    s.plan = o; o = sz_up256(o + (int64_t)sizeof(SzRowsPlan));
+    s.xg = o; o = sz_up256(o + 4 * (int64_t)W * SZ_ROWS_SLOTS * L->hidden);
+    s.gu_row = 2 * ffm; s.d_row = L->hidden;
+    s.acc_gu = o; o = sz_up256(o + 8 * (int64_t)W * SZ_ROWS_SLOTS * s.gu_row);
+    s.acc_d = o; o = sz_up256(o + 8 * (int64_t)W * SZ_ROWS_SLOTS * s.d_row);
+    s.total = o;
+    return s;
+}
+
+// zeroes the accumulators of the slots a window uses (grid (slots, windows), block 256)
+static __global__ void __launch_bounds__(256)
+sz_rows_zero_kernel(const SzRowsPlan* __restrict__ P, long long* __restrict__ acc_gu, long long gu_row, long long* __restrict__ acc_d, long long d_row) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int s = blockIdx.x, w = blockIdx.y;
+    if (P->src[w][s] < 0) return;
+    uint4* a = (uint4*)(acc_gu + ((size_t)w * SZ_ROWS_SLOTS + s) * gu_row);
+    uint4* b = (uint4*)(acc_d + ((size_t)w * SZ_ROWS_SLOTS + s) * d_row);
+    for (long long i = threadIdx.x; i < gu_row / 2; i += 256) a[i] = make_uint4(0, 0, 0, 0);
+    for (long long i = threadIdx.x; i < d_row / 2; i += 256) b[i] = make_uint4(0, 0, 0, 0);
+}
+
+extern "C" int sz_moe_rows_scratch_bytes(const sz_moe_layer* L, int rows, int64_t* bytes) {
+    if (!L || !bytes) return sz_fail(SZ_E_ARG, "sz_moe_rows_scratch_bytes: null argument");
+    if (rows < 8 || rows > SZ_ROWS_MAX || rows % 8) return sz_fail(SZ_E_ARG, "sz_moe_rows: rows = %d (a multiple of 8 up to %d)", rows, SZ_ROWS_MAX);
+    *bytes = sz_rows_layout(L, rows).total;
+    return SZ_OK;
+}
+
+// y[j] = moe(x[j]) for j < rows; x, y: f32 [rows][hidden].  EXL3 experts (routed and shared); every distinct expert is decoded once.
+// route_idx / route_w: as sz_moe_verify's, [rows][top_k], or 0.
+extern "C" int sz_moe_rows(const sz_moe_layer* L, uint64_t x, int rows, uint64_t y, uint64_t route_idx, uint64_t route_w, uint64_t scratch,
+                           int64_t scratch_bytes, uint64_t stream) {
+    int rc = sz_moe_check(L, 8);
+    if (rc) return rc;
+    if (rows < 8 || rows > SZ_ROWS_MAX || rows % 8) return sz_fail(SZ_E_ARG, "sz_moe_rows: rows = %d (a multiple of 8 up to %d)", rows, SZ_ROWS_MAX);
+    const SzFast fast = sz_fast_path(L);
+    if (!fast.exl3 || L->ep_count > 0) return sz_fail(SZ_E_TYPE, "sz_moe_rows: EXL3 experts and shared expert of the streaming kernels' shapes, no expert sharding");
+    if (!x || !y || !sz_aligned16(x) || !sz_aligned16(y)) return sz_fail(SZ_E_ARG, "sz_moe_rows: x and y must be non-null and 16-byte aligned");
+    const SzRowsScratch S = sz_rows_layout(L, rows);
+    if (!scratch || (scratch & 255)) return sz_fail(SZ_E_ARG, "scratch must be 256-byte aligned");
+    if (scratch_bytes < S.total) return sz_fail(SZ_E_SCRATCH, "scratch of %lld bytes, %lld needed", (long long)scratch_bytes, (long long)S.total);
+    cudaStream_t st = (cudaStream_t)stream;
+    u8* base = (u8*)scratch;
+    const int H = L->hidden, chunks = rows / 8, W = SZ_ROWS_WIN + SZ_ROWS_SHWIN;
+    const bool shared = L->shared_ff > 0;
+    u32* ctrl = (u32*)(base + S.ctrl);
+    u32* ctrl_x = ctrl + 16 * chunks;              // the expert kernels' error word lives in word 1 of the block after the chunks'
+    float* logits = (float*)(base + S.logits);
+    int32_t* ridx = (int32_t*)(base + S.ridx);
+    double* rw = (double*)(base + S.rw);
+    SzRowsPlan* P = (SzRowsPlan*)(base + S.plan);
+    float* xg = (float*)(base + S.xg);
+    long long *acc_gu = (long long*)(base + S.acc_gu), *acc_d = (long long*)(base + S.acc_d);
+    {   // routing: 8 rows a block row of the verify pass's router kernel (the chunks' own plans are written and not used)
+        const int route_rows = L->n_expert + (shared ? 1 : 0);
+        const dim3 grid((route_rows + SZ_ROUTE_RB - 1) / SZ_ROUTE_RB, chunks), block(SZ_ROUTE_THREADS);
+        const int nch = (H / 4 + SZ_ROUTE_THREADS - 1) / SZ_ROUTE_THREADS;
+        cudaError_t e = cudaErrorInvalidValue;
+#define SZ_ROWS_ROUTE(NC)                                                                                                                  \
+    e = sz_launch("route_rows", sz_route_kernel<8, 8, NC>, grid, block, 0, st, true, (const float*)x, H, (const float*)L->router,           \
+                  (const float*)(shared ? L->shared_router : 0), (int)L->n_expert, (int)L->top_k, logits, ridx, rw, (SzPlan*)(base + S.cplan), \
+                  (SzPlan*)(base + S.cplan_sh), ctrl, (int32_t*)route_idx, (double*)route_w, (uint4*)nullptr, 0, 0, 0)
+        if (nch <= 1) SZ_ROWS_ROUTE(1); else if (nch == 2) SZ_ROWS_ROUTE(2); else SZ_ROWS_ROUTE(4);
+#undef SZ_ROWS_ROUTE
+        SZ_CUDA(e);
+    }
+    SZ_CUDA(sz_launch("rows_plan", sz_rows_plan_kernel, dim3(1), dim3(1024), 0, st, true, (const int32_t*)ridx, rows, (int)L->top_k, (int)L->n_expert,
+                      shared ? 1 : 0, P));
+    SZ_CUDA(sz_launch("rows_zero", sz_rows_zero_kernel, dim3(SZ_ROWS_SLOTS, W), dim3(256), 0, st, true, (const SzRowsPlan*)P, acc_gu, (long long)S.gu_row, acc_d,
+                      (long long)S.d_row));
+    SZ_CUDA(sz_launch("rows_gather", sz_rows_gather_kernel, dim3(SZ_ROWS_SLOTS, W), dim3(256), 0, st, true, (const float*)x, H, (const SzRowsPlan*)P, xg));
+    // the experts, window by window (a window without groups costs a launch that returns at once); how many windows the routing
+    // needs is known on the device only, so all are launched
+    const size_t win_plan = offsetof(SzRowsPlan, win);
+    for (int w = 0; w < SZ_ROWS_WIN; w++) {
+        const SzPlan* pw = (const SzPlan*)((u8*)P + win_plan + (size_t)w * sizeof(SzPlan));
+        if ((rc = sz_x3_launch(st, L, 8, pw, xg + (size_t)w * SZ_ROWS_SLOTS * H, acc_gu + (size_t)w * SZ_ROWS_SLOTS * S.gu_row,
+                               acc_d + (size_t)w * SZ_ROWS_SLOTS * S.d_row, ctrl_x, false, true)))
+            return rc;
+    }
+    if (shared) {   // the shared expert as expert 0 of a layer of one
+        sz_moe_layer Ls = *L;
+        Ls.gate = L->sh_gate; Ls.up = L->sh_up; Ls.down = L->sh_down;
+        Ls.gate_stride = Ls.up_stride = Ls.down_stride = 0;
+        Ls.expert_ff = L->shared_ff; Ls.expert_type = L->shared_type;
+        const int w = SZ_ROWS_WIN;
+        const SzPlan* pw = (const SzPlan*)((u8*)P + win_plan + (size_t)w * sizeof(SzPlan));
+        if ((rc = sz_x3_launch(st, &Ls, 8, pw, xg + (size_t)w * SZ_ROWS_SLOTS * H, acc_gu + (size_t)w * SZ_ROWS_SLOTS * S.gu_row,
+                               acc_d + (size_t)w * SZ_ROWS_SLOTS * S.d_row, ctrl_x, false, true)))
+            return rc;
+    }
+    SZ_CUDA(sz_launch("rows_combine", sz_rows_combine_kernel, dim3(rows * (H / 128)), dim3((L->top_k + 1) * 32), 0, st, true, (const long long*)acc_d,
+                      (const SzRowsPlan*)P, (const int32_t*)ridx, (const double*)rw, (const u8*)L->down, (u64)L->down_stride, (const u8*)L->sh_down,
+                      (const float*)logits, (int)L->n_expert, (int)L->top_k, H, (int)L->expert_ff, (int)L->shared_ff, shared ? 1 : 0, (float*)y));
+    return SZ_OK;
+}
+
+// Clears the scratch's counters (once after allocation, and after a failed call); code != null: reads the expert kernels' error
+// word and the plan's overflow flag instead (synchronises).
+extern "C" int sz_moe_rows_status(const sz_moe_layer* L, int rows, uint64_t scratch, int* code, uint64_t stream) {
+    if (!L || !scratch || rows < 8 || rows > SZ_ROWS_MAX || rows % 8) return sz_fail(SZ_E_ARG, "sz_moe_rows_status: bad argument");
+    const SzRowsScratch S = sz_rows_layout(L, rows);
+    cudaStream_t st = (cudaStream_t)stream;
+    u8* base = (u8*)scratch;
+    if (!code) { SZ_CUDA(cudaMemsetAsync(base + S.ctrl, 0, (size_t)(S.logits - S.ctrl), st)); return SZ_OK; }
+    u32 err = 0;
+    int32_t over = 0;
+    SZ_CUDA(cudaMemcpyAsync(&err, base + S.ctrl + 64 * (rows / 8) + 4, 4, cudaMemcpyDeviceToHost, st));
+    SZ_CUDA(cudaMemcpyAsync(&over, base + S.plan + offsetof(SzRowsPlan, overflow), 4, cudaMemcpyDeviceToHost, st));
+    SZ_CUDA(cudaStreamSynchronize(st));
+    *code = (int)err | (over ? 2 : 0);
+    return SZ_OK;
 }
 
 extern "C" int sz_moe_verify_host(const sz_moe_layer* L, const float* x_host, int m, float* y_host, int32_t* route_idx_host,

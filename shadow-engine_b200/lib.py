@@ -66,6 +66,9 @@ SYMBOLS = {
     "sz_moe_verify_host": (C.c_int, [C.POINTER(MoeLayerC), C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
                                      C.c_uint64, C.c_uint64, C.c_uint64, C.c_int64, C.c_uint64]),
     "sz_moe_launches": (C.c_int, [C.POINTER(MoeLayerC)]),
+    "sz_moe_rows_scratch_bytes": (C.c_int, [C.POINTER(MoeLayerC), C.c_int, C.POINTER(C.c_int64)]),
+    "sz_moe_rows": (C.c_int, [C.POINTER(MoeLayerC), C.c_uint64, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64, C.c_int64, C.c_uint64]),
+    "sz_moe_rows_status": (C.c_int, [C.POINTER(MoeLayerC), C.c_int, C.c_uint64, C.POINTER(C.c_int), C.c_uint64]),
     "sz_model_load_gguf": (C.c_int, [C.c_char_p, C.c_int, C.c_uint64, C.POINTER(C.c_void_p)]),
     "sz_gguf_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
     "sz_weights_key_u64": (C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)]),

@@ -97,6 +97,45 @@ class MoeLayer:
                                            self.scratch_bytes, st))
         return (y, ridx, rw) if want_routing else y
 
+    def moe_rows(self, x, y=None, want_routing=False, stream=None):
+        """The sublayer over many rows at once (`sz_moe_rows`): x float32 [rows, hidden], rows a multiple of 8 up to 256; every
+        distinct expert is decoded once for all the rows that chose it.  The scratch of this form is made at the first call."""
+        rows = x.shape[0]
+        assert x.is_cuda and x.dtype == torch.float32 and x.is_contiguous() and x.shape[1] == self.shape["hidden"]
+        st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        have = getattr(self, "_rows_scratch", None)
+        if have is None or have[0] < rows:
+            n = C.c_int64()
+            szlib.check(self.lib.sz_moe_rows_scratch_bytes(C.byref(self.c), rows, C.byref(n)))
+            buf = torch.empty(n.value + 256, dtype=torch.uint8, device=self.device)
+            addr = buf.data_ptr() + (-buf.data_ptr()) % 256
+            szlib.check(self.lib.sz_moe_rows_status(C.byref(self.c), rows, addr, None, st))
+            self._rows_scratch = have = (rows, buf, addr, n.value)
+        if y is None:
+            y = torch.empty_like(x)
+        if want_routing:
+            ridx = torch.empty((rows, self.shape["top_k"]), dtype=torch.int32, device=self.device)
+            rw = torch.empty((rows, self.shape["top_k"]), dtype=torch.float64, device=self.device)
+            a, b = ridx.data_ptr(), rw.data_ptr()
+        else:
+            a = b = 0
+        if have[0] != rows:   # the layout depends on the row count: a smaller batch gets a scratch of its own size class
+            n = C.c_int64()
+            szlib.check(self.lib.sz_moe_rows_scratch_bytes(C.byref(self.c), rows, C.byref(n)))
+            szlib.check(self.lib.sz_moe_rows_status(C.byref(self.c), rows, have[2], None, st))
+            nbytes = n.value
+        else:
+            nbytes = have[3]
+        szlib.check(self.lib.sz_moe_rows(C.byref(self.c), x.data_ptr(), rows, y.data_ptr(), a, b, have[2], nbytes, st))
+        return (y, ridx, rw) if want_routing else y
+
+    def moe_rows_status(self, rows, stream=None):
+        """Synchronises; 0 unless a bounded wait ran out (1) or the routing needed more windows than the scratch has (2)."""
+        st = (stream or torch.cuda.current_stream(self.device)).cuda_stream
+        code = C.c_int()
+        szlib.check(self.lib.sz_moe_rows_status(C.byref(self.c), rows, self._rows_scratch[2], C.byref(code), st))
+        return code.value
+
     def moe_partial(self, x, y_fix=None, stream=None):
         """This rank's share of moe(x[j]) as 64-bit fixed point (int64 [m, hidden]); the shares of all ranks sum, as integers,
         to the layer's output, which `finish` converts to float32."""
