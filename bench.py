@@ -12,6 +12,8 @@ torchrun) the experts of every layer are sharded over the N ranks (expert parall
 rows on tcgen05 (`sz_mma_cols`); TFLOP/s against the measured dense bf16 rate.
 `--workload c5-concurrent`: B sequences decoded at once on every GPU (config 5's batched serving, without batching the kernels): each
 sequence has a verify session, stream and CUDA graphs of its own over the one resident model, and the GPU overlaps their passes.
+`--workload c5-moe`: the MoE sublayer over the verify rows of many sequences at once (64 sequences x K+1 = 4 rows = 256 rows), every
+distinct expert decoded once (`sz_moe_rows`), next to the same rows as 64 passes of 4.
 `--workload c4-tree`: benchmark config 4's mechanism on the config-3 model: one verify pass over a draft tree (8 rows), greedy
 acceptance on the device and rejection sampling on the host; reports us per verify and the accepted length.
 
@@ -754,6 +756,97 @@ def run_c5(args):
     out.emit(json.dumps(line))
 
 
+# ---- workload c5-moe: the MoE sublayer over the rows of many sequences -----------------------------------------------------------------
+def run_c5_moe(args):
+    """Config 2's layer shape (hidden 2048, 512 experts top-10 of FFN 512 + a shared expert, EXL3 3-bit) with config 5's batch:
+    `rows` = 256 rows a step.  Timed: sz_moe_rows, a graph of K steps over `layers` distinct layers (weights larger than L2), and
+    for comparison the same rows as rows / 4 verify-pass calls of 4 rows."""
+    if args.gpus != 1:
+        raise SystemExit("the c5-moe workload runs on one GPU")
+    out = QuietStdout()
+    import torch
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    szlib = pkg.lib
+    torch.cuda.set_device(0)
+    R, nl, K, W = args.rows, max(2, min(args.layers, 4)), max(4, min(args.steps, 32)), max(args.warmup, 3)
+    ty = szlib.TYPE_EXL3(3)
+    layers = [pkg.moe.MoeLayer(pkg.synth.make_moe_layer(C2["hidden"], C2["n_expert"], C2["top_k"], C2["expert_ff"], C2["shared_ff"], ty, ty, seed=1 + i,
+                                                        device="cuda"), "cuda:0") for i in range(nl)]
+    x = pkg.synth.normal((R, C2["hidden"]), 1.0, 5, "c5moe.x", device="cuda").to(torch.bfloat16).to(torch.float32).contiguous()
+    y = torch.empty_like(x)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for i in range(W):
+            _, ridx, _ = layers[i % nl].moe_rows(x, y, want_routing=True, stream=stream)
+        stream.synchronize()
+        distinct = int(torch.unique(ridx).numel())
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ev[0].record(stream)
+        for i in range(K):
+            layers[i % nl].moe_rows(x, y, stream=stream)
+        ev[1].record(stream)
+        stream.synchronize()
+        rows_ms = ev[0].elapsed_time(ev[1]) / K
+        # the same rows as verify passes of 4 rows (what a server without the batched form would run)
+        for i in range(2):
+            layers[i % nl].moe_batch(x[:4].contiguous(), stream=stream)
+        xs = [x[c:c + 4].contiguous() for c in range(0, R, 4)]
+        ys = torch.empty((4, C2["hidden"]), device="cuda")
+        ev[2].record(stream)
+        for i in range(2):
+            for xc in xs:
+                layers[i % nl].moe_batch(xc, ys, stream=stream)
+        ev[3].record(stream)
+        stream.synchronize()
+        pass_ms = ev[2].elapsed_time(ev[3]) / 2
+        # end to end: host rows up, result back, every step
+        xh, yh = x.cpu().pin_memory(), torch.empty(x.shape, dtype=torch.float32).pin_memory()
+        t0 = time.perf_counter()
+        for i in range(K):
+            x.copy_(xh, non_blocking=True)
+            layers[i % nl].moe_rows(x, y, stream=stream)
+            yh.copy_(y, non_blocking=True)
+            stream.synchronize()
+        e2e_us = (time.perf_counter() - t0) / K * 1e6
+        # per-kernel attribution of one step (eager, an event between launches: durations include the launch gap)
+        nev = 256
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(nev)]
+        for e in evs:
+            e.record(stream)
+        stream.synchronize()
+        arr = (C.c_uint64 * nev)(*[e.cuda_event for e in evs])
+        Lb = szlib.load()
+        szlib.check(Lb.sz_trace_begin(arr, nev, stream.cuda_stream))
+        layers[0].moe_rows(x, y, stream=stream)
+        n_k = Lb.sz_trace_end()
+        stream.synchronize()
+        per = {}
+        for i in range(1, n_k):
+            per.setdefault(Lb.sz_trace_name(i).decode(), []).append(evs[i - 1].elapsed_time(evs[i]) * 1e3)
+        kern = {nm: {"launches": len(v), "total_us": sum(v), "max_us": max(v)} for nm, v in per.items()}
+    for l in layers:
+        assert l.moe_rows_status(R) == 0
+    hbm, peak_kind = peaks()
+    be = expert_bytes("exl3", C2["hidden"], C2["expert_ff"])
+    step_bytes = (distinct + 1) * be + C2["n_expert"] * C2["hidden"] * 4
+    us = rows_ms * 1e3
+    line = {"metric": "verify-step us (MoE sublayer, %d rows = %d sequences x K+1 = 4)" % (R, R // 4), "value": us, "unit": "us", "n_gpus": 1, "steps": K, "warmup": W,
+            "ms_per_step": rows_ms, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 activations, f16 codebook weights, f32 accumulate (router and combine in f64)", "data": "synthetic",
+            "config": {"workload": "c5-moe", "format": "exl3", **{k: v for k, v in C2.items() if k != "rows"}, "rows": R, "layers_cycled": nl,
+                       "distinct_experts_per_step": distinct, "l2": "inputs larger than L2: %d layers of %d MB of expert weights cycled" % (nl, C2["n_expert"] * be >> 20)},
+            "us_per_row": us / R, "as_passes_of_4_rows_us": pass_ms * 1e3, "speedup_over_passes_of_4": pass_ms / rows_ms,
+            "roofline": {"bound": "hbm", "achieved": step_bytes / (us * 1e-6) / 1e9, "peak": hbm, "unit": "GB/s", "frac": step_bytes / (us * 1e-6) / 1e9 / hbm,
+                         "peak_kind": peak_kind, "traffic": None, "step_bytes": step_bytes,
+                         "note": "bytes = every distinct expert once + the router; the expert kernels are the verify pass's (decode-bound, see the c2-moe line)"},
+            "cpu_baseline": None,
+            "e2e": {"value": e2e_us, "unit": "us", "h2d_bytes_per_step": R * C2["hidden"] * 4, "d2h_bytes_per_step": R * C2["hidden"] * 4},
+            "gpu_launches": K * (n_k - 1), "launches_per_step": n_k - 1, "kernels": kern,
+            "clocks": {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}}
+    out.emit(json.dumps(line))
+
+
 # ---- workload prefill-dense: many token rows through one dense projection on tcgen05 ------------------------------------------------
 PD = dict(rows=12288, cols=2048)     # attn_qkv (8,192) + attn_gate (4,096) of a config-3 DeltaNet layer, one Q8_0 matrix
 PD_METRIC = "dense projection TFLOP/s (Q8_0 weights, many token rows, tcgen05)"
@@ -1021,7 +1114,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe", "c4-tree", "prefill-dense", "c5-concurrent"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe", "c4-tree", "prefill-dense", "c5-concurrent", "c5-moe"])
+    ap.add_argument("--rows", type=int, default=256, help="c5-moe: rows a step (64 sequences x 4 rows)")
     ap.add_argument("--sequences", type=int, default=8, help="c5-concurrent: sequences decoded at once on every GPU")
     ap.add_argument("--waves", type=int, default=2, help="c5-concurrent: timed waves of requests (one request a sequence a wave)")
     ap.add_argument("--tokens", type=int, default=256, help="prefill-dense: token rows a step (256 = 64 sequences x K+1 = 4 rows)")
@@ -1064,6 +1158,10 @@ def main():
         return run_reference_c3(args) if args.impl == "reference" else run_c3(args)
     if args.workload == "prefill-dense":
         return run_prefill_dense(args)
+    if args.workload == "c5-moe":
+        if args.impl == "reference":
+            return run_reference_c2(args)
+        return run_c5_moe(args)
     if args.workload == "c5-concurrent":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference's CPU path serves one sequence at a time; see the c3 workload's reference arm for its tok/s"}))

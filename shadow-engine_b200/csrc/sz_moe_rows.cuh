@@ -26,34 +26,46 @@ struct SzRowsPlan {
     SzPlan win[SZ_ROWS_WIN + SZ_ROWS_SHWIN];                     // routed windows, then the shared expert's
     int32_t src[SZ_ROWS_WIN + SZ_ROWS_SHWIN][SZ_ROWS_SLOTS];     // slot -> input row (-1: unused)
     int32_t pair_loc[SZ_ROWS_MAX * SZ_MAX_TOPK];                 // pair (row * top_k + rank) -> window * 256 + slot
-    int32_t win_of[SZ_MAX_EXPERTS], grp_of[SZ_MAX_EXPERTS], slot_of[SZ_MAX_EXPERTS];
 };
 
 // ---- one block of 1024 threads -------------------------------------------------------------------------------------------------------
+// Every (row, rank) pair marks its row in its expert's row mask (256 bits); an expert's pairs in ascending row order are then the
+// set bits of its mask, and a pair's place among them the number of set bits below its row: no sorting, no order of arrival.
 __global__ void __launch_bounds__(1024)
 sz_rows_plan_kernel(const int32_t* __restrict__ ridx, int R, int k, int ne, int has_shared, SzRowsPlan* __restrict__ P) {
-    __shared__ int cnt[SZ_MAX_EXPERTS];
+    __shared__ u32 mask[SZ_MAX_EXPERTS][SZ_ROWS_MAX / 32];
+    __shared__ short win_of[SZ_MAX_EXPERTS], grp_of[SZ_MAX_EXPERTS], slot_of[SZ_MAX_EXPERTS], cnt[SZ_MAX_EXPERTS];
     sz_pdl_wait();
     sz_pdl_trigger();
     const int t = threadIdx.x, pairs = R * k;
-    for (int e = t; e < ne; e += 1024) cnt[e] = 0;
+    for (int i = t; i < ne * (SZ_ROWS_MAX / 32); i += 1024) (&mask[0][0])[i] = 0u;
     for (int i = t; i < (SZ_ROWS_WIN + SZ_ROWS_SHWIN) * SZ_ROWS_SLOTS; i += 1024) P->src[i / SZ_ROWS_SLOTS][i % SZ_ROWS_SLOTS] = -1;
     __syncthreads();
-    for (int p = t; p < pairs; p += 1024) atomicAdd(&cnt[__ldcg(ridx + p)], 1);
+    for (int p = t; p < pairs; p += 1024) {
+        const int e = __ldcg(ridx + p), row = p / k;
+        atomicOr(&mask[e][row >> 5], 1u << (row & 31));
+    }
+    __syncthreads();
+    for (int e = t; e < ne; e += 1024) {
+        int c = 0;
+#pragma unroll
+        for (int q = 0; q < SZ_ROWS_MAX / 32; q++) c += __popc(mask[e][q]);
+        cnt[e] = (short)c;
+    }
     __syncthreads();
     if (t == 0) {
         // experts in ascending order into windows: an expert's rows (at most R <= 256) stay in one window, as groups of up to 8
         int w = 0, g = 0, s = 0, over = 0;
         for (int e = 0; e < ne; e++) {
             const int c = cnt[e];
-            if (c == 0) continue;
+            if (c == 0) { win_of[e] = -1; continue; }
             const int ng = (c + 7) / 8;
             if (g + ng > SZ_MAXG || s + c > SZ_ROWS_SLOTS) {
                 if (w < SZ_ROWS_WIN) P->win[w].n_groups = g;
                 w++; g = 0; s = 0;
             }
-            if (w >= SZ_ROWS_WIN) { over = 1; P->win_of[e] = -1; continue; }
-            P->win_of[e] = w; P->grp_of[e] = g; P->slot_of[e] = s;
+            if (w >= SZ_ROWS_WIN) { over = 1; win_of[e] = -1; continue; }
+            win_of[e] = (short)w; grp_of[e] = (short)g; slot_of[e] = (short)s;
             g += ng; s += c;
         }
         if (w < SZ_ROWS_WIN) { P->win[w].n_groups = g; w++; }
@@ -64,24 +76,20 @@ sz_rows_plan_kernel(const int32_t* __restrict__ ridx, int R, int k, int ne, int 
         P->overflow = over;
     }
     __syncthreads();
-    // expert e's thread walks all pairs in ascending order (pair = row * k + rank: ascending pairs are ascending rows)
-    for (int e = t; e < ne; e += 1024) {
+    for (int p = t; p < pairs; p += 1024) {
+        const int e = __ldcg(ridx + p), row = p / k;
+        const int w = win_of[e];
+        if (w < 0) { P->pair_loc[p] = 0; continue; }
+        int n = __popc(mask[e][row >> 5] & ((1u << (row & 31)) - 1u));
+        for (int q = 0; q < (row >> 5); q++) n += __popc(mask[e][q]);
         const int c = cnt[e];
-        const int w = c > 0 ? P->win_of[e] : -1;
-        if (w < 0) continue;
+        const int slot = slot_of[e] + n, grp = grp_of[e] + n / 8, in = n % 8;
         SzPlan& W = P->win[w];
-        const int g0 = P->grp_of[e], s0 = P->slot_of[e];
-        int n = 0;
-        for (int p = 0; p < pairs && n < c; p++) {
-            if (__ldcg(ridx + p) != e) continue;
-            const int slot = s0 + n, grp = g0 + n / 8, in = n % 8;
-            W.rows[grp][in] = (uint8_t)slot;
-            W.pairs[grp][in] = (uint8_t)slot;
-            if (in == 0) { W.expert[grp] = (int16_t)e; W.count[grp] = (uint8_t)(c - n < 8 ? c - n : 8); }
-            P->src[w][slot] = p / k;
-            P->pair_loc[p] = w * SZ_ROWS_SLOTS + slot;
-            n++;
-        }
+        W.rows[grp][in] = (uint8_t)slot;
+        W.pairs[grp][in] = (uint8_t)slot;
+        if (in == 0) { W.expert[grp] = (int16_t)e; W.count[grp] = (uint8_t)(c - n < 8 ? c - n : 8); }
+        P->src[w][slot] = row;
+        P->pair_loc[p] = w * SZ_ROWS_SLOTS + slot;
     }
     if (has_shared)   // the shared expert: the rows in order, 8 a group; its pair of row r is slot r of the last window
         for (int r = t; r < R; r += 1024) {
