@@ -308,6 +308,17 @@ int sz_session_commit_path(sz_session* s, const int32_t* path, int n, uint64_t s
 int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* top, float* logits, uint64_t stream);
 /* Keeps the first `keep` rows of the pending pass and drops the rest (rollback(&snap, &batch[..keep])). */
 int sz_session_commit(sz_session* s, int keep, uint64_t stream);
+/* Several sequences in one step (the batch of config 5, from the pieces above): every sequence keeps its session and runs its own
+ * reads, mixers and head in lockstep with the others; the MoE sublayer of every layer takes the rows of ALL sequences as one batch
+ * (sz_moe_rows), so an expert several sequences chose is streamed and decoded once.  n <= 64 sessions of one model (EXL3 experts,
+ * no expert sharding) on one stream; ms[b] rows of sequence b, ids = the rows of all sequences one after the other; the rows of
+ * a step, padded to a multiple of 8, must fit rows_max (<= 256), the size the scratch was made for.  Afterwards every session
+ * holds a pending pass: sz_session_result / sz_session_commit per session.  A sequence's results are bit for bit those of a pass
+ * of its own.  sz_batch_scratch_init once after the scratch is allocated. */
+int sz_batch_scratch_bytes(const sz_model* model, int rows_max, int64_t* bytes);
+int sz_batch_scratch_init(const sz_model* model, int rows_max, uint64_t scratch, uint64_t stream);
+int sz_batch_verify(sz_session* const* sessions, int n, const int32_t* ids, const int32_t* ms, int accept_mode, int eog_token, int rows_max,
+                    uint64_t scratch, int64_t scratch_bytes, uint64_t stream);
 /* Routing trace (the `layerL.route_idx` / `route_w` streams, forward.rs:1015-1018): switch it on, run a pass, read
  * idx [n_layer][SZ_MAX_VERIFY][SZ_MAX_TOPK] and w (same shape, f64). */
 /* Benchmarks: pretend `len` tokens were fed - seeded pseudo-random keys and values in the first `len` cache positions of every
@@ -432,6 +443,11 @@ int sz_generate(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_ge
 typedef struct sz_gen sz_gen;
 int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint64_t stream, sz_gen** out);
 int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_log, int pass_cap, sz_gen_stats* stats, uint64_t stream);
+/* The loop of n sequences in lockstep (generators made by sz_gen_begin on sessions of one model): every round each live sequence
+ * proposes its rows, one sz_batch_verify step verifies them all, each sequence settles its own.  Greedy acceptance on the device.
+ * outs[b] / stats[b] as sz_gen_run's; *device_ms accumulates the steps' device time.  A sequence's tokens are those of its own loop. */
+int sz_batch_gen_run(sz_gen* const* gens, int n, int rounds, uint32_t* const* outs, sz_gen_stats* const* stats, int rows_max, uint64_t scratch,
+                     int64_t scratch_bytes, double* device_ms, uint64_t stream);
 /* the request's stop ids for the loop: it ends at one as at eog_token, and never accepts a drafted one (host and device alike) */
 int sz_gen_set_stops(sz_gen* g, const uint32_t* ids, int n, uint64_t stream);
 void sz_gen_free(sz_gen* g);

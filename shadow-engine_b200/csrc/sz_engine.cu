@@ -14,6 +14,8 @@ int sz_session_verify(sz_session* s, const int32_t* ids, int m, int accept_mode,
 int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* top, float* logits, uint64_t stream);
 int sz_session_commit(sz_session* s, int keep, uint64_t stream);
 int sz_session_set_stops(sz_session* s, const int32_t* ids, int n, uint64_t stream);
+int sz_batch_verify(sz_session* const* sessions, int n, const int32_t* ids, const int32_t* ms, int accept_mode, int eog_token, int rows_max, uint64_t scratch,
+                    int64_t scratch_bytes, uint64_t stream);
 int sz_session_stops(const sz_session* s, int32_t* out);
 int sz_session_len(const sz_session* s);
 int sz_session_capacity(const sz_session* s);
@@ -489,83 +491,150 @@ extern "C" int sz_gen_set_stops(sz_gen* g, const uint32_t* ids, int n, uint64_t 
 
 extern "C" void sz_gen_free(sz_gen* g) { delete g; }
 
+// One round of the loop in two halves, so that the pass between them can be one sequence's own (sz_gen_run) or a step shared
+// with other sequences (sz_batch_gen_run).
+struct SzRound {
+    int32_t batch[SZ_MAX_VERIFY];
+    uint32_t draft[SZ_MAX_VERIFY];
+    int nd = 0, m = 0;
+    double t1 = 0.0;
+};
+static uint32_t gen_pick(const sz_gen* g, const uint32_t* row, uint64_t pos) { return g->p.greedy ? row[64] : sz_sample_top(&g->p.sampler, row, pos); }
+static bool gen_is_eog(const sz_gen* g, uint32_t t) {
+    if (g->p.eog_token >= 0 && t == (uint32_t)g->p.eog_token) return true;
+    for (uint32_t st : g->stops) if (st == t) return true;
+    return false;
+}
+// The round's own token and its drafts.  false: the sequence has ended (nothing to verify).
+static bool gen_propose(sz_gen* g, uint32_t* out, sz_gen_stats* stats, SzRound* r) {
+    const sz_gen_params* p = &g->p;
+    int& n = g->n;
+    if (g->done || n >= p->max_new) return false;
+    const uint32_t next = gen_pick(g, g->last.data(), (uint64_t)n);
+    if (gen_is_eog(g, next)) { g->done = true; return false; }
+    out[n++] = next;
+    g->hist.push_back(next);
+    sz_drafter_push(g->sd, next);
+    r->batch[0] = (int32_t)next;
+    int nd = 0, match_len = 0;
+    const double t0 = now_ms();
+    if (p->spec_k > 0) {
+        const int rem = p->max_new - n;
+        const int k = p->spec_k < rem ? p->spec_k : rem;
+        if (p->lookup_min > 0) nd = sz_drafter_propose(g->sd, k, r->draft, &match_len);
+        if (nd >= 2) stats->lookup_passes++;
+        else {
+            nd = sz_drafter_propose_with_min(g->sd, k, 3, r->draft, &match_len);
+            if (nd == 0) { const int lens[2] = {3, 2}; nd = sz_lookup(g->hist.data(), (int)g->hist.size(), k, lens, 2, r->draft); }
+        }
+    }
+    r->t1 = now_ms();
+    stats->draft_ms += r->t1 - t0;
+    for (int i = 0; i < nd; i++) r->batch[1 + i] = (int32_t)r->draft[i];
+    r->nd = nd;
+    r->m = 1 + nd;
+    return true;
+}
+// After the pass: the result, acceptance as the host sees it (checked against the device's), the commit, the books.
+static int gen_settle(sz_gen* g, uint32_t* out, int32_t* pass_log, int pass_cap, sz_gen_stats* stats, const SzRound* r, uint64_t stream) {
+    sz_session* s = g->s;
+    const bool dev_accept = g->p.device_accept != 0;
+    int& n = g->n;
+    int32_t kn[2] = {1, 0};
+    int rc = sz_session_result(s, dev_accept ? kn : nullptr, g->top.data(), nullptr, stream);
+    if (rc) return rc;
+    const double t2 = now_ms();
+    stats->verify_ms += t2 - r->t1;
+    int keep = 1;
+    for (int i = 0; i < r->nd; i++) {
+        stats->pos_tried[i < 7 ? i : 7]++;
+        const uint32_t want = gen_pick(g, g->top.data() + (size_t)i * 128, (uint64_t)n);
+        if (want != r->draft[i] || gen_is_eog(g, r->draft[i])) break;
+        out[n++] = r->draft[i];
+        keep++;
+        stats->pos_right[i < 7 ? i : 7]++;
+        g->hist.push_back(r->draft[i]);
+        sz_drafter_push(g->sd, r->draft[i]);
+    }
+    if (dev_accept && kn[0] != keep) return sz_fail(SZ_E_DEVICE, "device acceptance kept %d rows, the host loop %d", kn[0], keep);
+    if ((rc = sz_session_commit(s, keep, stream))) return rc;
+    stats->commit_ms += now_ms() - t2;
+    stats->rounds++;
+    if (r->nd > 0) {
+        stats->passes++;
+        stats->drafted += r->nd;
+        stats->accepted += keep - 1;
+        if (pass_log && stats->passes <= pass_cap) { pass_log[2 * (stats->passes - 1)] = r->nd; pass_log[2 * (stats->passes - 1) + 1] = keep - 1; }
+    }
+    std::memcpy(g->last.data(), g->top.data() + (size_t)(keep - 1) * 128, 128 * 4);
+    stats->n_tokens = n;
+    return SZ_OK;
+}
+
 // Runs up to `rounds` rounds of the loop (0: until max_new tokens or an end-of-generation token).  A round emits one token plus the
 // drafts it accepts.  `out` receives every token emitted so far at its position; stats accumulate over calls that pass the same struct.
 extern "C" int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_log, int pass_cap, sz_gen_stats* stats, uint64_t stream) {
     if (!g || !out || !stats) return sz_fail(SZ_E_ARG, "sz_gen_run: null argument");
     sz_session* s = g->s;
     const sz_gen_params* p = &g->p;
-    auto pick = [&](const uint32_t* row, uint64_t pos) -> uint32_t { return p->greedy ? row[64] : sz_sample_top(&p->sampler, row, pos); };
-    auto is_eog = [&](uint32_t t) {
-        if (p->eog_token >= 0 && t == (uint32_t)p->eog_token) return true;
-        for (uint32_t st : g->stops) if (st == t) return true;
-        return false;
-    };
-    int& n = g->n;
     int rc = SZ_OK, done_rounds = 0;
-    while (!g->done && n < p->max_new && (rounds <= 0 || done_rounds < rounds)) {
-        const uint32_t next = pick(g->last.data(), (uint64_t)n);
-        if (is_eog(next)) { g->done = true; break; }
-        out[n++] = next;
-        g->hist.push_back(next);
-        sz_drafter_push(g->sd, next);
-        int32_t batch[SZ_MAX_VERIFY];
-        batch[0] = (int32_t)next;
-        uint32_t draft[SZ_MAX_VERIFY];
-        int nd = 0, match_len = 0;
-        const double t0 = now_ms();
-        if (p->spec_k > 0) {
-            const int rem = p->max_new - n;
-            const int k = p->spec_k < rem ? p->spec_k : rem;
-            if (p->lookup_min > 0) nd = sz_drafter_propose(g->sd, k, draft, &match_len);
-            if (nd >= 2) stats->lookup_passes++;
-            else {
-                nd = sz_drafter_propose_with_min(g->sd, k, 3, draft, &match_len);
-                if (nd == 0) { const int lens[2] = {3, 2}; nd = sz_lookup(g->hist.data(), (int)g->hist.size(), k, lens, 2, draft); }
-            }
-        }
-        const double t1 = now_ms();
-        stats->draft_ms += t1 - t0;
-        for (int i = 0; i < nd; i++) batch[1 + i] = (int32_t)draft[i];
-        const int m = 1 + nd;
+    while (rounds <= 0 || done_rounds < rounds) {
+        SzRound r;
+        if (!gen_propose(g, out, stats, &r)) break;
         const bool dev_accept = p->device_accept != 0;
         cudaEventRecord(g->ev0, (cudaStream_t)stream);
         // sampled: row i is the draw at output position n + i (n already counts this round's first token)
-        rc = dev_accept && !p->greedy ? sz_session_verify_sampled(s, batch, m, (uint64_t)n, p->eog_token, stream)
-                                      : sz_session_verify(s, batch, m, dev_accept ? SZ_ACCEPT_GREEDY : SZ_ACCEPT_NONE, p->eog_token, 1, stream);
+        rc = dev_accept && !p->greedy ? sz_session_verify_sampled(s, r.batch, r.m, (uint64_t)g->n, p->eog_token, stream)
+                                      : sz_session_verify(s, r.batch, r.m, dev_accept ? SZ_ACCEPT_GREEDY : SZ_ACCEPT_NONE, p->eog_token, 1, stream);
         if (rc) break;
         cudaEventRecord(g->ev1, (cudaStream_t)stream);
-        int32_t kn[2] = {1, 0};
-        if ((rc = sz_session_result(s, dev_accept ? kn : nullptr, g->top.data(), nullptr, stream))) break;
+        if ((rc = gen_settle(g, out, pass_log, pass_cap, stats, &r, stream))) break;
         float dev = 0.f;
         if (cudaEventElapsedTime(&dev, g->ev0, g->ev1) == cudaSuccess) stats->device_ms += dev;
-        const double t2 = now_ms();
-        stats->verify_ms += t2 - t1;
-        int keep = 1;
-        for (int i = 0; i < nd; i++) {
-            stats->pos_tried[i < 7 ? i : 7]++;
-            const uint32_t want = pick(g->top.data() + (size_t)i * 128, (uint64_t)n);
-            if (want != draft[i] || is_eog(draft[i])) break;
-            out[n++] = draft[i];
-            keep++;
-            stats->pos_right[i < 7 ? i : 7]++;
-            g->hist.push_back(draft[i]);
-            sz_drafter_push(g->sd, draft[i]);
-        }
-        if (dev_accept && kn[0] != keep) { rc = sz_fail(SZ_E_DEVICE, "device acceptance kept %d rows, the host loop %d", kn[0], keep); break; }
-        if ((rc = sz_session_commit(s, keep, stream))) break;
-        stats->commit_ms += now_ms() - t2;
-        stats->rounds++;
         done_rounds++;
-        if (nd > 0) {
-            stats->passes++;
-            stats->drafted += nd;
-            stats->accepted += keep - 1;
-            if (pass_log && stats->passes <= pass_cap) { pass_log[2 * (stats->passes - 1)] = nd; pass_log[2 * (stats->passes - 1) + 1] = keep - 1; }
-        }
-        std::memcpy(g->last.data(), g->top.data() + (size_t)(keep - 1) * 128, 128 * 4);
     }
-    stats->n_tokens = n;
+    stats->n_tokens = g->n;
+    return rc;
+}
+
+// The loop of n sequences in lockstep: every round, each live sequence proposes its rows, ONE step verifies them all
+// (sz_batch_verify: the sequences' sessions, the MoE sublayers shared), and each settles its own.  Greedy acceptance on the device.
+// outs[b], stats[b]: as sz_gen_run's for sequence b.  device_ms (when not null) accumulates the steps' time on the device.
+extern "C" int sz_batch_gen_run(sz_gen* const* gs, int n, int rounds, uint32_t* const* outs, sz_gen_stats* const* stats, int rows_max, uint64_t scratch,
+                                int64_t scratch_bytes, double* device_ms, uint64_t stream) {
+    if (!gs || !outs || !stats || n < 1 || n > 64) return sz_fail(SZ_E_ARG, "sz_batch_gen_run: 1..64 sequences");
+    for (int b = 0; b < n; b++) {
+        if (!gs[b] || !outs[b] || !stats[b]) return sz_fail(SZ_E_ARG, "sz_batch_gen_run: null argument");
+        if (!gs[b]->p.greedy || !gs[b]->p.device_accept) return sz_fail(SZ_E_ARG, "sz_batch_gen_run: greedy acceptance on the device (sequence %d asks otherwise)", b);
+        if (gs[b]->p.eog_token != gs[0]->p.eog_token) return sz_fail(SZ_E_ARG, "sz_batch_gen_run: one end-of-generation id for the batch");
+    }
+    cudaEvent_t e0 = gs[0]->ev0, e1 = gs[0]->ev1;
+    int rc = SZ_OK, done_rounds = 0;
+    std::vector<SzRound> rs((size_t)n);
+    std::vector<sz_session*> ss;
+    std::vector<int32_t> ids, ms;
+    std::vector<int> who;
+    while (rounds <= 0 || done_rounds < rounds) {
+        ss.clear(); ids.clear(); ms.clear(); who.clear();
+        for (int b = 0; b < n; b++) {
+            if (!gen_propose(gs[b], outs[b], stats[b], &rs[b])) continue;
+            who.push_back(b);
+            ss.push_back(gs[b]->s);
+            ms.push_back(rs[b].m);
+            ids.insert(ids.end(), rs[b].batch, rs[b].batch + rs[b].m);
+        }
+        if (who.empty()) break;
+        cudaEventRecord(e0, (cudaStream_t)stream);
+        if ((rc = sz_batch_verify(ss.data(), (int)ss.size(), ids.data(), ms.data(), SZ_ACCEPT_GREEDY, gs[0]->p.eog_token, rows_max, scratch, scratch_bytes, stream))) break;
+        cudaEventRecord(e1, (cudaStream_t)stream);
+        for (int b : who)
+            if ((rc = gen_settle(gs[b], outs[b], nullptr, 0, stats[b], &rs[b], stream))) break;
+        if (rc) break;
+        float dev = 0.f;
+        if (device_ms && cudaEventElapsedTime(&dev, e0, e1) == cudaSuccess) *device_ms += dev;
+        done_rounds++;
+    }
+    for (int b = 0; b < n; b++) stats[b]->n_tokens = gs[b]->n;
     return rc;
 }
 

@@ -1047,7 +1047,8 @@ extern "C" int sz_moe_rows(const sz_moe_layer* L, uint64_t x, int rows, uint64_t
     if (rc) return rc;
     if (rows < 8 || rows > SZ_ROWS_MAX || rows % 8) return sz_fail(SZ_E_ARG, "sz_moe_rows: rows = %d (a multiple of 8 up to %d)", rows, SZ_ROWS_MAX);
     const SzFast fast = sz_fast_path(L);
-    if (!fast.exl3 || L->ep_count > 0) return sz_fail(SZ_E_TYPE, "sz_moe_rows: EXL3 experts and shared expert of the streaming kernels' shapes, no expert sharding");
+    if (!fast.exl3 || L->ep_count > 0 || (L->shared_ff > 0 && !fast.shared_fused))
+        return sz_fail(SZ_E_TYPE, "sz_moe_rows: EXL3 experts of the streaming kernels' shapes, a shared expert of the same width and type, no expert sharding");
     if (!x || !y || !sz_aligned16(x) || !sz_aligned16(y)) return sz_fail(SZ_E_ARG, "sz_moe_rows: x and y must be non-null and 16-byte aligned");
     const SzRowsScratch S = sz_rows_layout(L, rows);
     if (!scratch || (scratch & 255)) return sz_fail(SZ_E_ARG, "scratch must be 256-byte aligned");

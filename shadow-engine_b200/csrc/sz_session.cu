@@ -885,33 +885,33 @@ static int sz_ple_layer(sz_session* s, cudaStream_t st, int m, bool pending) {
 }
 
 // Runs the m rows through every layer and, with `head`, through the output projection and the top-64.
-static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
+static int sz_forward_begin(sz_session* s, cudaStream_t st, int m) {
     const sz_model_config& c = s->model.cfg;
-    const int H = c.hidden, C = c.streams;
     s->hc_n = 0;
     if (s->hc_fast) SZ_CUDA(cudaMemsetAsync(s->hc_acc, 0, sizeof(long long) * SZ_MAX_VERIFY * SZ_HC_ACC_ROWS, st));  // read 0 adds into buffer 0
     SZ_CUDA(sz_launch("embed", sz_embed_kernel, dim3(m), dim3(256), 0, st, false, (const int32_t*)s->ids, (const u8*)s->model.token_embd.data,
-                      (int)s->model.token_embd.type, H, C, (int)c.vocab, s->r));
+                      (int)s->model.token_embd.type, (int)c.hidden, (int)c.streams, (int)c.vocab, s->r));
+    return SZ_OK;
+}
+// Layer l up to the input of its MoE sublayer (s->u): the per-layer embedding where it is, the read, the mixer, the second read.
+static int sz_layer_to_moe(sz_session* s, cudaStream_t st, int l, int m, bool pending) {
+    const sz_model_config& c = s->model.cfg;
+    const sz_layer& L = s->layers[l];
     int rc;
-    bool pending = false;
-    for (int l = 0; l < c.n_layer; l++) {
-        const sz_layer& L = s->layers[l];
-        if (s->p_hist && l == s->model.ple.layer) {   // the per-layer embedding joins the residual stream; it applies the pending write itself
-            if ((rc = sz_ple_layer(s, st, m, pending))) return rc;
-            pending = false;
-        }
-        if ((rc = sz_hc_read(s, st, L.hc_attn, m, pending, true))) return rc;
-        rc = sz_is_attn(c, l) ? sz_attn_layer(s, st, l, m) : sz_delta_layer(s, st, l, m);
-        if (rc) return rc;
-        if ((rc = sz_hc_read(s, st, L.hc_ffn, m, true, true))) return rc;   // applies the mixer's write first
-        int32_t* ri = s->want_routes ? s->routes + (int64_t)l * SZ_MAX_VERIFY * SZ_MAX_TOPK : nullptr;
-        double* rw = s->want_routes ? s->route_w + (int64_t)l * SZ_MAX_VERIFY * SZ_MAX_TOPK : nullptr;
-        if ((rc = sz_moe_verify(&L.moe, (uint64_t)s->u, m, (uint64_t)s->y, (uint64_t)ri, (uint64_t)rw, (uint64_t)s->moe_scratch, s->moe_scratch_bytes,
-                                (uint64_t)st)))
-            return rc;
-        pending = true;
+    if (s->p_hist && l == s->model.ple.layer) {   // the per-layer embedding joins the residual stream; it applies the pending write itself
+        if ((rc = sz_ple_layer(s, st, m, pending))) return rc;
+        pending = false;
     }
-    if (!head) return SZ_OK;  // the last write only matters to the output read; the next pass starts from the embedding
+    if ((rc = sz_hc_read(s, st, L.hc_attn, m, pending, true))) return rc;
+    rc = sz_is_attn(c, l) ? sz_attn_layer(s, st, l, m) : sz_delta_layer(s, st, l, m);
+    if (rc) return rc;
+    return sz_hc_read(s, st, L.hc_ffn, m, true, true);   // applies the mixer's write first
+}
+// After the last layer: the output read, the head, the top-64 of every row.
+static int sz_forward_head(sz_session* s, cudaStream_t st, int m, bool pending) {
+    const sz_model_config& c = s->model.cfg;
+    const int H = c.hidden;
+    int rc;
     if ((rc = sz_hc_read(s, st, s->model.output_hc, m, pending, false))) return rc;
     if (s->head.rows > 0) return sz_head_top(&s->head, (uint64_t)s->u, H, m, 64, (uint64_t)s->logits, (uint64_t)s->top, (uint64_t)st);
     SzDenseArgs a = {};
@@ -923,6 +923,24 @@ static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
     SZ_CUDA(sz_launch("topk_slices", sz_topk_slices_kernel, dim3(nb, m), dim3(256), 0, st, true, (const float*)s->logits, (int)c.vocab, (int)c.vocab, nb, s->tk_tmp, (const u32*)nullptr));
     SZ_CUDA(sz_launch("topk_merge", sz_topk_merge_kernel, dim3(m), dim3(256), 0, st, true, (const u64*)s->tk_tmp, nb, s->top));
     return SZ_OK;
+}
+static int sz_forward(sz_session* s, cudaStream_t st, int m, bool head) {
+    const sz_model_config& c = s->model.cfg;
+    int rc = sz_forward_begin(s, st, m);
+    if (rc) return rc;
+    bool pending = false;
+    for (int l = 0; l < c.n_layer; l++) {
+        const sz_layer& L = s->layers[l];
+        if ((rc = sz_layer_to_moe(s, st, l, m, pending))) return rc;
+        int32_t* ri = s->want_routes ? s->routes + (int64_t)l * SZ_MAX_VERIFY * SZ_MAX_TOPK : nullptr;
+        double* rw = s->want_routes ? s->route_w + (int64_t)l * SZ_MAX_VERIFY * SZ_MAX_TOPK : nullptr;
+        if ((rc = sz_moe_verify(&L.moe, (uint64_t)s->u, m, (uint64_t)s->y, (uint64_t)ri, (uint64_t)rw, (uint64_t)s->moe_scratch, s->moe_scratch_bytes,
+                                (uint64_t)st)))
+            return rc;
+        pending = true;
+    }
+    if (!head) return SZ_OK;  // the last write only matters to the output read; the next pass starts from the embedding
+    return sz_forward_head(s, st, m, pending);
 }
 
 // The commit as the device does it: replay of the kept rows where some were dropped, conv rows, position count and buffer swap.
@@ -951,9 +969,15 @@ static int sz_commit_device(sz_session* s, cudaStream_t st, int m) {
 }
 
 // Everything a pass launches after the ids are on the device.
+static int sz_pass_tail(sz_session* s, cudaStream_t st, int m, int accept_mode, int eog_token, bool head);
 static int sz_pass(sz_session* s, cudaStream_t st, int m, int accept_mode, int eog_token, bool head) {
     int rc = sz_forward(s, st, m, head);
     if (rc) return rc;
+    return sz_pass_tail(s, st, m, accept_mode, eog_token, head);
+}
+// Acceptance and commit on the device, after the rows' top-64 are there.
+static int sz_pass_tail(sz_session* s, cudaStream_t st, int m, int accept_mode, int eog_token, bool head) {
+    int rc = SZ_OK;
     if (accept_mode == SZ_ACCEPT_SAMPLED) {
         SZ_CUDA(sz_launch("accept_sampled", sz_accept_sampled_kernel, dim3(1), dim3(32 * SZ_MAX_VERIFY), 0, st, true, (const u32*)s->top,
                           (const int32_t*)s->ids, m, eog_token, (const SzSampleArgs*)(s->ids + 16), s->res));
@@ -1219,6 +1243,141 @@ extern "C" int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint
     return SZ_OK;
 }
 
+// ---- several sequences in one step ---------------------------------------------------------------------------------------------------
+// Config 5's batch, built from what is there: every sequence keeps its session (cache, recurrent states, buffers) and runs its own
+// reads, mixers and head, layer by layer in lockstep with the others; where the layers meet - the MoE sublayer - the rows of ALL
+// sequences go through sz_moe_rows as one batch, so an expert that several sequences chose is streamed and decoded once.  A
+// sequence's numbers are those of a pass of its own (the MoE rows are bit for bit sz_moe_verify's), so acceptance, commit and the
+// result are read session by session as after sz_session_verify.  Launched eagerly on one stream (no graph: the rows a step holds
+// change from step to step).
+#define SZ_BATCH_MAX 64
+struct SzBatchTab {
+    const float* u[SZ_BATCH_MAX];
+    float* y[SZ_BATCH_MAX];
+    int32_t m[SZ_BATCH_MAX], off[SZ_BATCH_MAX];
+    int32_t n, pad[3];
+};
+// grid (rows), block 256: dir 0: X[off_b + j] = u_b[j]; dir 1: y_b[j] = Y[off_b + j]
+static __global__ void __launch_bounds__(256)
+sz_batch_rows_kernel(const SzBatchTab* __restrict__ T, float* __restrict__ X, int H, int dir) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int r = blockIdx.x;
+    int b = 0;
+    while (b + 1 < T->n && T->off[b + 1] <= r) b++;
+    const int j = r - T->off[b];
+    if (j >= T->m[b]) return;
+    float4* x = (float4*)(X + (size_t)r * H);
+    if (dir == 0) { const float4* src = (const float4*)(T->u[b] + (size_t)j * H); for (int i = threadIdx.x; i < H / 4; i += 256) x[i] = __ldcg(src + i); }
+    else { float4* dst = (float4*)(T->y[b] + (size_t)j * H); for (int i = threadIdx.x; i < H / 4; i += 256) dst[i] = __ldcg(x + i); }
+}
+
+struct SzBatchScratch { int64_t tab, x, y, moe, moe_bytes, total; };
+static int sz_batch_layout(const sz_model* m, int rows_max, SzBatchScratch* S) {
+    if (!m || !m->layers) return sz_fail(SZ_E_ARG, "null model");
+    if (rows_max < 8 || rows_max % 8) return sz_fail(SZ_E_ARG, "sz_batch: rows_max = %d (a multiple of 8)", rows_max);
+    int64_t o = 0, mb = 0;
+    S->tab = o; o = up256(o + (int64_t)sizeof(SzBatchTab));
+    S->x = o; o = up256(o + 4 * (int64_t)rows_max * m->cfg.hidden);
+    S->y = o; o = up256(o + 4 * (int64_t)rows_max * m->cfg.hidden);
+    for (int l = 0; l < m->cfg.n_layer; l++) {
+        int64_t b = 0;
+        const int rc = sz_moe_rows_scratch_bytes(&m->layers[l].moe, rows_max, &b);
+        if (rc) return rc;
+        mb = b > mb ? b : mb;
+    }
+    S->moe = o; S->moe_bytes = mb; o = up256(o + mb);
+    S->total = o;
+    return SZ_OK;
+}
+extern "C" int sz_batch_scratch_bytes(const sz_model* m, int rows_max, int64_t* bytes) {
+    SzBatchScratch S;
+    const int rc = sz_batch_layout(m, rows_max, &S);
+    if (rc) return rc;
+    if (!bytes) return sz_fail(SZ_E_ARG, "null bytes");
+    *bytes = S.total;
+    return SZ_OK;
+}
+// Once after the scratch is allocated (and after a failed step).
+extern "C" int sz_batch_scratch_init(const sz_model* m, int rows_max, uint64_t scratch, uint64_t stream) {
+    SzBatchScratch S;
+    int rc = sz_batch_layout(m, rows_max, &S);
+    if (rc) return rc;
+    if (!scratch || (scratch & 255)) return sz_fail(SZ_E_ARG, "scratch must be 256-byte aligned");
+    SZ_CUDA(cudaMemsetAsync((void*)(scratch + S.x), 0, (size_t)(S.moe - S.x), (cudaStream_t)stream));
+    return sz_moe_rows_status(&m->layers[0].moe, rows_max, scratch + S.moe, nullptr, stream);
+}
+
+// One step of n sequences: sequence b reads ms[b] rows (ids: the rows of all sequences, one after the other).  accept_mode:
+// SZ_ACCEPT_NONE, _GREEDY or _ALL, as sz_session_verify.  Afterwards every session holds a pending pass: sz_session_result and
+// sz_session_commit per session, as after a pass of its own.
+extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids, const int32_t* ms, int accept_mode, int eog_token, int rows_max,
+                               uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
+    if (!ss || !ids || !ms || n < 1 || n > SZ_BATCH_MAX) return sz_fail(SZ_E_ARG, "sz_batch_verify: 1..%d sequences", SZ_BATCH_MAX);
+    if (accept_mode < SZ_ACCEPT_NONE || accept_mode > SZ_ACCEPT_ALL) return sz_fail(SZ_E_ARG, "sz_batch_verify: accept_mode %d", accept_mode);
+    sz_session* s0 = ss[0];
+    if (!s0) return sz_fail(SZ_E_ARG, "sz_batch_verify: null session");
+    SzBatchScratch S;
+    int rc = sz_batch_layout(&s0->model, rows_max, &S);
+    if (rc) return rc;
+    if (!scratch || (scratch & 255) || scratch_bytes < S.total) return sz_fail(SZ_E_SCRATCH, "sz_batch_verify: scratch of %lld bytes, %lld needed", (long long)scratch_bytes, (long long)S.total);
+    cudaStream_t st = (cudaStream_t)stream;
+    const sz_model_config& c = s0->model.cfg;
+    SzBatchTab tab = {};
+    int R = 0;
+    for (int b = 0; b < n; b++) {
+        sz_session* s = ss[b];
+        if (!s || s->model.layers[0].moe.gate != s0->model.layers[0].moe.gate || s->model.cfg.n_layer != c.n_layer)
+            return sz_fail(SZ_E_ARG, "sz_batch_verify: sequence %d is not a session of the same model", b);
+        for (int q = 0; q < b; q++) if (ss[q] == s) return sz_fail(SZ_E_ARG, "sz_batch_verify: a session appears twice");
+        const int m = ms[b];
+        if (m < 1 || m > SZ_MAX_VERIFY) return sz_fail(SZ_E_ARG, "a pass has 1..%d rows, got %d", SZ_MAX_VERIFY, m);
+        if (s->last_m) return sz_fail(SZ_E_ARG, "sequence %d: the previous pass was not committed", b);
+        if (s->len + m > s->ctx) return sz_fail(SZ_E_ARG, "sequence %d: %d positions + %d rows exceed the session's capacity %d", b, s->len, m, s->ctx);
+        if (s->want_routes) return sz_fail(SZ_E_ARG, "sz_batch_verify: no routing trace in a batched step");
+        tab.u[b] = s->u; tab.y[b] = s->y; tab.m[b] = m; tab.off[b] = R;
+        R += m;
+    }
+    tab.n = n;
+    const int Rp = (R + 7) & ~7;
+    if (Rp > rows_max) return sz_fail(SZ_E_ARG, "sz_batch_verify: %d rows in a scratch for %d", R, rows_max);
+    // the ids of every sequence into its session's staging block (pinned: the copy is asynchronous)
+    int at = 0;
+    for (int b = 0; b < n; b++) {
+        sz_session* s = ss[b];
+        if (s->inflight) { SZ_CUDA(cudaStreamSynchronize(st)); s->inflight = 0; }
+        s->tree_pass = 0;
+        memcpy(s->h_pin, ids + at, (size_t)ms[b] * 4);
+        at += ms[b];
+        SZ_CUDA(cudaMemcpyAsync(s->ids, s->h_pin, 128, cudaMemcpyHostToDevice, st));
+    }
+    u8* base = (u8*)scratch;
+    SZ_CUDA(cudaMemcpyAsync(base + S.tab, &tab, sizeof(tab), cudaMemcpyHostToDevice, st));   // (pageable: staged before the call returns)
+    float *X = (float*)(base + S.x), *Y = (float*)(base + S.y);
+    if (Rp > R) SZ_CUDA(cudaMemsetAsync(X + (size_t)R * c.hidden, 0, (size_t)(Rp - R) * c.hidden * 4, st));   // the rows that pad the batch to a multiple of 8
+    for (int b = 0; b < n; b++)
+        if ((rc = sz_forward_begin(ss[b], st, ms[b]))) return rc;
+    bool pending = false;
+    for (int l = 0; l < c.n_layer; l++) {
+        for (int b = 0; b < n; b++)
+            if ((rc = sz_layer_to_moe(ss[b], st, l, ms[b], pending))) return rc;
+        SZ_CUDA(sz_launch("batch_gather", sz_batch_rows_kernel, dim3(R), dim3(256), 0, st, true, (const SzBatchTab*)(base + S.tab), X, (int)c.hidden, 0));
+        if ((rc = sz_moe_rows(&s0->layers[l].moe, (uint64_t)X, Rp, (uint64_t)Y, 0, 0, scratch + S.moe, S.moe_bytes, stream))) return rc;
+        SZ_CUDA(sz_launch("batch_scatter", sz_batch_rows_kernel, dim3(R), dim3(256), 0, st, true, (const SzBatchTab*)(base + S.tab), Y, (int)c.hidden, 1));
+        pending = true;
+    }
+    for (int b = 0; b < n; b++) {
+        sz_session* s = ss[b];
+        if ((rc = sz_forward_head(s, st, ms[b], pending))) return rc;
+        if ((rc = sz_pass_tail(s, st, ms[b], accept_mode, eog_token, true))) return rc;
+        s->last_m = ms[b];
+        s->pending_committed = accept_mode != SZ_ACCEPT_NONE;
+        s->device_keep = accept_mode == SZ_ACCEPT_ALL ? ms[b] : -1;
+        s->inflight = 1;
+    }
+    return SZ_OK;
+}
+
 // ---- synthetic history (benchmarks) -------------------------------------------------------------------------------------------------
 // Fills the first `len` positions of every attention layer's cache with seeded pseudo-random keys and values (and small random
 // DeltaNet states), as if `len` tokens had been fed: a long context without running a long prefill.
@@ -1434,6 +1593,7 @@ const SzKernelEntry kKernels[] = {
     {"sz_accept_sampled_kernel", (const void*)sz_accept_sampled_kernel, 6, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_CONST_PTR, SZ_P_PTR}},
     {"sz_topk_slices_kernel", (const void*)sz_topk_slices_kernel, 6, {SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_CONST_PTR}},
     {"sz_topk_merge_kernel", (const void*)sz_topk_merge_kernel, 3, {SZ_P_CONST_PTR, SZ_P_I32, SZ_P_PTR}},
+    {"sz_batch_rows_kernel", (const void*)sz_batch_rows_kernel, 4, {SZ_P_CONST_PTR, SZ_P_PTR, SZ_P_I32, SZ_P_I32}},
     {"sz_fill_kv_kernel", (const void*)sz_fill_kv_kernel, 8, {SZ_P_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_U64, SZ_P_I32, SZ_P_I32, SZ_P_U32}},
 };
 const int kKernelCount = (int)(sizeof(kKernels) / sizeof(kKernels[0]));

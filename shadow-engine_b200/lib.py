@@ -135,6 +135,12 @@ SYMBOLS = {
     "sz_gen_run": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int32), C.c_int, C.c_void_p, C.c_uint64]),
     "sz_gen_set_stops": (C.c_int, [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_uint64]),
     "sz_gen_free": (None, [C.c_void_p]),
+    "sz_batch_scratch_bytes": (C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_int64)]),
+    "sz_batch_scratch_init": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64, C.c_uint64]),
+    "sz_batch_verify": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_uint64,
+                                  C.c_int64, C.c_uint64]),
+    "sz_batch_gen_run": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.c_uint64, C.c_int64,
+                                   C.POINTER(C.c_double), C.c_uint64]),
     "sz_mma_cols_scratch_bytes": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int64)]),
     "sz_mma_cols": (C.c_int, [C.c_void_p, C.c_uint64, C.c_int64, C.c_uint64, C.c_int64, C.c_int, C.c_uint64, C.c_int64, C.c_uint64]),
     "sz_mma_cols_status": (C.c_int, [C.c_uint64, C.c_int, C.POINTER(C.c_int), C.c_uint64]),

@@ -522,6 +522,50 @@ class Generator:
             self.h = None
 
 
+class Batch:
+    """Several sequences stepped together (`sz_batch_verify`, `sz_batch_gen_run`): sessions of one model on one stream; the MoE
+    sublayers take the rows of all of them at once."""
+
+    def __init__(self, dm, n, ctx, rows_max=None, kv_q8=True, head_proxy=False):
+        self.lib = szlib.load()
+        self.dm = dm
+        self._stream = torch.cuda.Stream(dm.device)
+        self.stream = self._stream.cuda_stream
+        self.sessions = [Session(dm, ctx, kv_q8=kv_q8, stream=self._stream, head_proxy=head_proxy) for _ in range(n)]
+        self.rows_max = rows_max or min(256, (n * szlib.MAX_VERIFY + 7) // 8 * 8)
+        nb = C.c_int64()
+        szlib.check(self.lib.sz_batch_scratch_bytes(C.byref(dm.model), self.rows_max, C.byref(nb)))
+        self.mem = torch.empty(nb.value + 256, dtype=torch.uint8, device=dm.device)
+        self.scratch = self.mem.data_ptr() + (-self.mem.data_ptr()) % 256
+        self.scratch_bytes = nb.value
+        szlib.check(self.lib.sz_batch_scratch_init(C.byref(dm.model), self.rows_max, self.scratch, self.stream))
+
+    def verify(self, rows, accept=0, eog=-1, which=None):
+        """rows: one list of token ids per sequence (`which`: the sessions that take part, default all).  Afterwards every one of
+        them holds a pending pass: `result()` and `commit()` on the session."""
+        ss = [self.sessions[i] for i in (which if which is not None else range(len(self.sessions)))]
+        assert len(ss) == len(rows)
+        hs = (C.c_void_p * len(ss))(*[s.h for s in ss])
+        flat = [int(t) for r in rows for t in r]
+        ids = (C.c_int32 * len(flat))(*flat)
+        ms = (C.c_int32 * len(rows))(*[len(r) for r in rows])
+        szlib.check(self.lib.sz_batch_verify(hs, len(ss), ids, ms, accept, eog, self.rows_max, self.scratch, self.scratch_bytes, self.stream))
+        for s, r in zip(ss, rows):
+            s._m = len(r)
+
+    def generate(self, prompts, max_new, spec_k=3, eog=-1, rounds=0):
+        """Every prompt through its session (one at a time), then the sequences decode in lockstep.  Returns the tokens of every
+        sequence, their statistics and the device time of the steps in ms."""
+        gens = [Generator(s, p, max_new, spec_k=spec_k, eog=eog) for s, p in zip(self.sessions, prompts)]
+        n = len(gens)
+        gh = (C.c_void_p * n)(*[g.h for g in gens])
+        outs = (C.c_void_p * n)(*[C.cast(g.out, C.c_void_p) for g in gens])
+        sts = (C.c_void_p * n)(*[C.cast(C.pointer(g.stats), C.c_void_p) for g in gens])
+        dev = C.c_double(0.0)
+        szlib.check(self.lib.sz_batch_gen_run(gh, n, rounds, outs, sts, self.rows_max, self.scratch, self.scratch_bytes, C.byref(dev), self.stream))
+        return [g.tokens() for g in gens], [g.stats for g in gens], dev.value
+
+
 def make_prompt(n_tokens, vocab, seed=1, block=16, substitute=0.1, cycles=None):
     """benchmark config 1's prompt: a block of `block` tokens repeated, with a fraction of random substitutions, so a suffix drafter
     finds repeats.  With `cycles` (token_cycles(...)[1]) the block is one of the model's own token cycles."""

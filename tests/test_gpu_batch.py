@@ -1,0 +1,66 @@
+"""Several sequences in one step (`sz_batch_verify`, `sz_batch_gen_run`): every sequence's logits, acceptance and tokens are bit for
+bit those of a session stepping alone - the sequences share the MoE sublayers' work, not their numbers."""
+import numpy as np
+import pytest
+
+from tests.util import pkg
+
+szlib, md = pkg.lib, pkg.model
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(md.TINY, vocab=2048, n_expert=16, n_expert_used=4, shared_ff=256)   # a shared expert as wide as the routed ones: the streaming kernels take it
+
+
+@pytest.fixture(scope="module")
+def dm():
+    M = md.make_model(CFG, expert_type=szlib.TYPE_EXL3(3), seed=4, cycle_alpha=0.9, cycle_beta=0.5)
+    return md.DeviceModel(M)
+
+
+def test_a_step_of_several_sequences_equals_their_own_passes(dm):
+    rng = np.random.default_rng(2)
+    seqs = [[int(t) for t in rng.integers(0, CFG["vocab"], 30)] for _ in range(5)]
+    batch = md.Batch(dm, 5, 64)
+    alone = [md.Session(dm, 64, kv_q8=True) for _ in range(5)]
+    at = [0] * 5
+    for step, ms in enumerate([(8, 1, 4, 3, 8), (1, 1, 1, 1, 1), (4, 8, 2, 1, 5), (3, 3, 3, 3, 3)]):
+        rows = [seqs[b][at[b]:at[b] + ms[b]] for b in range(5)]
+        batch.verify(rows)
+        for b in range(5):
+            _, top, lg = batch.sessions[b].result(logits=True)
+            batch.sessions[b].commit(ms[b])
+            alone[b].verify(rows[b]); _, top2, lg2 = alone[b].result(logits=True); alone[b].commit(ms[b])
+            assert np.array_equal(lg.view(np.uint32), lg2.view(np.uint32)), "step %d sequence %d" % (step, b)
+            assert np.array_equal(top, top2)
+            at[b] += ms[b]
+    # a step of some of the sequences only, with acceptance on the device and a rejected draft
+    rows = [seqs[0][at[0]:at[0] + 1] + [5, 6], seqs[3][at[3]:at[3] + 2]]
+    batch.verify(rows, accept=1, which=[0, 3])
+    for b, r in zip((0, 3), rows):
+        (keep, nxt), _, _ = batch.sessions[b].result()
+        alone[b].verify(r, accept=1); (keep2, nxt2), _, _ = alone[b].result()
+        assert (keep, nxt) == (keep2, nxt2)
+        batch.sessions[b].commit(keep); alone[b].commit(keep2)
+    with pytest.raises(szlib.SzError):
+        batch.verify([[1], [2]], which=[1, 1])         # a session twice
+
+
+def test_sequences_decoding_in_lockstep_emit_their_own_tokens(dm):
+    prompts = [md.make_prompt(40 + 8 * b, CFG["vocab"], seed=10 + b) for b in range(4)]
+    want = []
+    for p in prompts:
+        toks, _, st = md.Session(dm, 256, kv_q8=True).generate(p, 32 + len(want), spec_k=3)
+        want.append((toks, st.passes, st.drafted, st.accepted))
+    batch = md.Batch(dm, 4, 256)
+    gens = [md.Generator(s, p, 32 + b, spec_k=3) for b, (s, p) in enumerate(zip(batch.sessions, prompts))]
+    import ctypes as C
+    n = 4
+    gh = (C.c_void_p * n)(*[g.h for g in gens])
+    outs = (C.c_void_p * n)(*[C.cast(g.out, C.c_void_p) for g in gens])
+    sts = (C.c_void_p * n)(*[C.cast(C.pointer(g.stats), C.c_void_p) for g in gens])
+    dev = C.c_double(0.0)
+    szlib.check(batch.lib.sz_batch_gen_run(gh, n, 0, outs, sts, batch.rows_max, batch.scratch, batch.scratch_bytes, C.byref(dev), batch.stream))
+    for b, g in enumerate(gens):
+        assert (g.tokens(), g.stats.passes, g.stats.drafted, g.stats.accepted) == want[b], "sequence %d" % b
+    assert dev.value > 0.0
