@@ -12,6 +12,8 @@ torchrun) the experts of every layer are sharded over the N ranks (expert parall
 rows on tcgen05 (`sz_mma_cols`); TFLOP/s against the measured dense bf16 rate.
 `--workload c5-concurrent`: B sequences decoded at once on every GPU (config 5's batched serving, without batching the kernels): each
 sequence has a verify session, stream and CUDA graphs of its own over the one resident model, and the GPU overlaps their passes.
+`--workload c5-batch`: B sequences decoding in lockstep on every GPU (`sz_batch_gen_run`): sessions of their own, the MoE sublayers of
+every layer shared by the rows of all sequences.
 `--workload c5-moe`: the MoE sublayer over the verify rows of many sequences at once (64 sequences x K+1 = 4 rows = 256 rows), every
 distinct expert decoded once (`sz_moe_rows`), next to the same rows as 64 passes of 4.
 `--workload c4-tree`: benchmark config 4's mechanism on the config-3 model: one verify pass over a draft tree (8 rows), greedy
@@ -847,6 +849,110 @@ def run_c5_moe(args):
     out.emit(json.dumps(line))
 
 
+# ---- workload c5-batch: B sequences in lockstep, the MoE sublayers shared -----------------------------------------------------------
+def run_c5_batch(args):
+    """Config 5's batch on the config-3 model: B sequences a GPU, every one with a session of its own (cache filled to the context,
+    a 256-token prompt fed through it: untimed), then all decode `request_tokens` tokens in lockstep, spec K=3 each, through
+    sz_batch_gen_run: a step runs every sequence's reads, mixers and head and ONE MoE sublayer a layer over the rows of all of them.
+    N > 1: every GPU holds the whole model and B sequences of its own.  Timed: the steps' device time (events around each step) and
+    the wall clock of the loop."""
+    out = QuietStdout()
+    import torch
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE=%d (launch with torch.distributed.run for N > 1)" % (args.gpus, world))
+    torch.cuda.set_device(local)
+    device = "cuda:%d" % local
+    import __graft_entry__ as graft
+    pkg = graft.load_package()
+    md, szlib = pkg.model, pkg.lib
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl")
+    cfg = c3_model_cfg(args, args.n_layer)
+    head_type = szlib.TYPE_Q8_0 if args.head == "q8" else szlib.TYPE_EXL3(4)
+    M = md.make_model(cfg, dense_type=szlib.TYPE_Q8_0, expert_type=szlib.TYPE_EXL3(3), seed=1, device=device, cycle_alpha=args.alpha,
+                      cycle_beta=args.beta, head_type=head_type)
+    dm = md.DeviceModel(M, device)
+    del M
+    torch.cuda.empty_cache()
+    B, ctx, n_prompt, n_new = args.sequences, args.ctx, 256, args.request_tokens
+    _, cyc = md.token_cycles(cfg["vocab"], 1)
+    batch = md.Batch(dm, B, ctx + n_new + 64, head_proxy=args.head == "proxy")
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    tot = dict(n=0, rounds=0, steps=0, drafted=0, accepted=0, dev_ms=0.0, wall_s=0.0)
+    sampler = None
+    for wave in range(-1, args.waves):     # wave -1: warm-up
+        for s in batch.sessions:
+            s.fill_synthetic(ctx - n_prompt, seed=3)
+        prompts = [md.make_prompt(n_prompt, cfg["vocab"], seed=1 + ((wave + 1) * B + b) * world + rank, cycles=cyc) for b in range(B)]
+        gens = [md.Generator(s, p, n_new, spec_k=3) for s, p in zip(batch.sessions, prompts)]   # the prompts, one session at a time
+        barrier()
+        if wave == 0:
+            sampler = ClockSampler(torch.cuda.current_device())
+            sampler.start()
+        n = len(gens)
+        gh = (C.c_void_p * n)(*[g.h for g in gens])
+        outs = (C.c_void_p * n)(*[C.cast(g.out, C.c_void_p) for g in gens])
+        sts = (C.c_void_p * n)(*[C.cast(C.pointer(g.stats), C.c_void_p) for g in gens])
+        dev = C.c_double(0.0)
+        t0 = time.perf_counter()
+        szlib.check(batch.lib.sz_batch_gen_run(gh, n, 0, outs, sts, batch.rows_max, batch.scratch, batch.scratch_bytes, C.byref(dev), batch.stream))
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        if wave >= 0:
+            tot["dev_ms"] += dev.value; tot["wall_s"] += wall
+            tot["steps"] += max(g.stats.rounds for g in gens)
+            for g in gens:
+                tot["n"] += g.stats.n_tokens; tot["rounds"] += g.stats.rounds; tot["drafted"] += g.stats.drafted; tot["accepted"] += g.stats.accepted
+        del gens
+    barrier()
+    clocks = sampler.stop()
+
+    def agree(v, op):
+        if world == 1:
+            return v
+        import torch.distributed as dist
+        t = torch.tensor([v], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op={"max": dist.ReduceOp.MAX, "sum": dist.ReduceOp.SUM}[op])
+        return float(t[0])
+
+    dev_ms, wall_s = agree(tot["dev_ms"], "max"), agree(tot["wall_s"], "max")
+    toks, rounds = int(agree(tot["n"], "sum")), int(agree(tot["rounds"], "sum"))
+    drafted, accepted = int(agree(tot["drafted"], "sum")), int(agree(tot["accepted"], "sum"))
+    if rank != 0:
+        return
+    hbm, peak_kind = peaks()
+    steps = tot["steps"]
+    line = {
+        "metric": "accepted tok/s at spec K=3, %d sequences in lockstep a GPU" % B, "value": toks / (dev_ms * 1e-3), "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": B, "ms_per_step": dev_ms / max(steps, 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 activations, f16 EXL3 codebook weights, int8 Q8_0 / Q8_KV, f32 accumulate (router, norms, combine in f64)", "data": "synthetic",
+        "config": dict(c3_config(args, cfg, ctx), workload="c5-batch", sequences_per_gpu=B, batch=B * world, waves=args.waves,
+                       parallelism="replicas%d x %d sequences" % (world, B) if world > 1 else "%d sequences, one GPU" % B,
+                       batching="a step = every sequence's own reads, mixers and head (its session's kernels) + one MoE sublayer a layer over the rows of all "
+                                "sequences (sz_moe_rows); launched eagerly on one stream"),
+        "speculation": {"tokens": toks, "rounds": rounds, "drafted": drafted, "accepted": accepted, "tokens_per_round": toks / max(rounds, 1),
+                        "rows_per_step": (rounds + drafted) / max(steps, 1)},
+        "roofline": {"bound": "hbm", "achieved": None, "peak": hbm, "unit": "GB/s", "frac": None, "traffic": None, "peak_kind": peak_kind,
+                     "note": "see the c3 line for the per-kernel roofline of the sessions' kernels and the c5-moe line for the shared MoE sublayer"},
+        "cpu_baseline": None,
+        "e2e": {"value": toks / wall_s, "unit": "tok/s", "h2d_bytes_per_step": 128 * B + 1600, "d2h_bytes_per_step": B * (8 + 512 * (1 + drafted / max(rounds, 1)))},
+        "gpu_launches": None, "clocks": clocks,
+    }
+    out.emit(json.dumps(line))
+
+
 # ---- workload prefill-dense: many token rows through one dense projection on tcgen05 ------------------------------------------------
 PD = dict(rows=12288, cols=2048)     # attn_qkv (8,192) + attn_gate (4,096) of a config-3 DeltaNet layer, one Q8_0 matrix
 PD_METRIC = "dense projection TFLOP/s (Q8_0 weights, many token rows, tcgen05)"
@@ -1114,7 +1220,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe", "c4-tree", "prefill-dense", "c5-concurrent", "c5-moe"])
+    ap.add_argument("--workload", default="c3", choices=["c3", "c2-moe", "c4-tree", "prefill-dense", "c5-concurrent", "c5-moe", "c5-batch"])
     ap.add_argument("--rows", type=int, default=256, help="c5-moe: rows a step (64 sequences x 4 rows)")
     ap.add_argument("--sequences", type=int, default=8, help="c5-concurrent: sequences decoded at once on every GPU")
     ap.add_argument("--waves", type=int, default=2, help="c5-concurrent: timed waves of requests (one request a sequence a wave)")
@@ -1162,6 +1268,11 @@ def main():
         if args.impl == "reference":
             return run_reference_c2(args)
         return run_c5_moe(args)
+    if args.workload == "c5-batch":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's CPU path serves one sequence at a time; see the c3 workload's reference arm for its tok/s"}))
+            return
+        return run_c5_batch(args)
     if args.workload == "c5-concurrent":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference's CPU path serves one sequence at a time; see the c3 workload's reference arm for its tok/s"}))

@@ -116,7 +116,8 @@ int sz_moe_verify_host(const sz_moe_layer* layer, const float* x_host, int m, fl
  * exl3_mma, kernels/exl3.cu:500-590), with the verify pass's exact kernels: a row's output is bit for bit sz_moe_verify's.  EXL3
  * experts, no expert sharding.  sz_moe_rows_status(layer, rows, scratch, NULL, stream) once after the scratch is allocated (and
  * after a failed call); with a code pointer it synchronises and reports (bit 0: a bounded wait ran out, bit 1: the routing needed
- * more windows than the scratch has). */
+ * more windows than the scratch has, bit 2: an expert id out of range reached the plan).  The scratch has one size and one layout
+ * whatever the rows of a call. */
 int sz_moe_rows_scratch_bytes(const sz_moe_layer* layer, int rows, int64_t* bytes);
 int sz_moe_rows(const sz_moe_layer* layer, uint64_t x, int rows, uint64_t y, uint64_t route_idx, uint64_t route_w, uint64_t scratch,
                 int64_t scratch_bytes, uint64_t stream);

@@ -999,9 +999,12 @@ struct SzRowsScratch {
     int64_t ctrl, logits, ridx, rw, cplan, cplan_sh, plan, xg, acc_gu, acc_d, total;
     int64_t gu_row, d_row;   // i64 elements a slot
 };
-static SzRowsScratch sz_rows_layout(const sz_moe_layer* L, int R) {
+// One layout whatever the rows of a call (sized for SZ_ROWS_MAX): a scratch serves calls of any row count, and the tickets and the
+// error word stay where they were cleared - a layout that moved with the row count would put one call's tickets on another's data.
+static SzRowsScratch sz_rows_layout(const sz_moe_layer* L) {
     SzRowsScratch s;
     int64_t o = 0;
+    const int R = SZ_ROWS_MAX;
     const int chunks = R / 8, W = SZ_ROWS_WIN + SZ_ROWS_SHWIN;
     const int64_t ffm = L->expert_ff > L->shared_ff ? L->expert_ff : L->shared_ff;
     s.ctrl = o; o = sz_up256(o + 64 * (int64_t)(chunks + 1));            // one block of 16 words a chunk (the router's ticket), then the expert kernels'
@@ -1035,7 +1038,7 @@ sz_rows_zero_kernel(const SzRowsPlan* __restrict__ P, long long* __restrict__ ac
 extern "C" int sz_moe_rows_scratch_bytes(const sz_moe_layer* L, int rows, int64_t* bytes) {
     if (!L || !bytes) return sz_fail(SZ_E_ARG, "sz_moe_rows_scratch_bytes: null argument");
     if (rows < 8 || rows > SZ_ROWS_MAX || rows % 8) return sz_fail(SZ_E_ARG, "sz_moe_rows: rows = %d (a multiple of 8 up to %d)", rows, SZ_ROWS_MAX);
-    *bytes = sz_rows_layout(L, rows).total;
+    *bytes = sz_rows_layout(L).total;
     return SZ_OK;
 }
 
@@ -1050,7 +1053,7 @@ extern "C" int sz_moe_rows(const sz_moe_layer* L, uint64_t x, int rows, uint64_t
     if (!fast.exl3 || L->ep_count > 0 || (L->shared_ff > 0 && !fast.shared_fused))
         return sz_fail(SZ_E_TYPE, "sz_moe_rows: EXL3 experts of the streaming kernels' shapes, a shared expert of the same width and type, no expert sharding");
     if (!x || !y || !sz_aligned16(x) || !sz_aligned16(y)) return sz_fail(SZ_E_ARG, "sz_moe_rows: x and y must be non-null and 16-byte aligned");
-    const SzRowsScratch S = sz_rows_layout(L, rows);
+    const SzRowsScratch S = sz_rows_layout(L);
     if (!scratch || (scratch & 255)) return sz_fail(SZ_E_ARG, "scratch must be 256-byte aligned");
     if (scratch_bytes < S.total) return sz_fail(SZ_E_SCRATCH, "scratch of %lld bytes, %lld needed", (long long)scratch_bytes, (long long)S.total);
     cudaStream_t st = (cudaStream_t)stream;
@@ -1058,7 +1061,7 @@ extern "C" int sz_moe_rows(const sz_moe_layer* L, uint64_t x, int rows, uint64_t
     const int H = L->hidden, chunks = rows / 8, W = SZ_ROWS_WIN + SZ_ROWS_SHWIN;
     const bool shared = L->shared_ff > 0;
     u32* ctrl = (u32*)(base + S.ctrl);
-    u32* ctrl_x = ctrl + 16 * chunks;              // the expert kernels' error word lives in word 1 of the block after the chunks'
+    u32* ctrl_x = ctrl + 16 * (SZ_ROWS_MAX / 8);   // the expert kernels' error word lives in word 1 of the block after the chunks'
     float* logits = (float*)(base + S.logits);
     int32_t* ridx = (int32_t*)(base + S.ridx);
     double* rw = (double*)(base + S.rw);
@@ -1113,16 +1116,16 @@ extern "C" int sz_moe_rows(const sz_moe_layer* L, uint64_t x, int rows, uint64_t
 // word and the plan's overflow flag instead (synchronises).
 extern "C" int sz_moe_rows_status(const sz_moe_layer* L, int rows, uint64_t scratch, int* code, uint64_t stream) {
     if (!L || !scratch || rows < 8 || rows > SZ_ROWS_MAX || rows % 8) return sz_fail(SZ_E_ARG, "sz_moe_rows_status: bad argument");
-    const SzRowsScratch S = sz_rows_layout(L, rows);
+    const SzRowsScratch S = sz_rows_layout(L);
     cudaStream_t st = (cudaStream_t)stream;
     u8* base = (u8*)scratch;
     if (!code) { SZ_CUDA(cudaMemsetAsync(base + S.ctrl, 0, (size_t)(S.logits - S.ctrl), st)); return SZ_OK; }
     u32 err = 0;
     int32_t over = 0;
-    SZ_CUDA(cudaMemcpyAsync(&err, base + S.ctrl + 64 * (rows / 8) + 4, 4, cudaMemcpyDeviceToHost, st));
+    SZ_CUDA(cudaMemcpyAsync(&err, base + S.ctrl + 64 * (SZ_ROWS_MAX / 8) + 4, 4, cudaMemcpyDeviceToHost, st));
     SZ_CUDA(cudaMemcpyAsync(&over, base + S.plan + offsetof(SzRowsPlan, overflow), 4, cudaMemcpyDeviceToHost, st));
     SZ_CUDA(cudaStreamSynchronize(st));
-    *code = (int)err | (over ? 2 : 0);
+    *code = (int)(err ? 1 : 0) | (over & 1 ? 2 : 0) | (over & 4);
     return SZ_OK;
 }
 

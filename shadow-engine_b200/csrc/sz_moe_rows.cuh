@@ -43,6 +43,7 @@ sz_rows_plan_kernel(const int32_t* __restrict__ ridx, int R, int k, int ne, int 
     __syncthreads();
     for (int p = t; p < pairs; p += 1024) {
         const int e = __ldcg(ridx + p), row = p / k;
+        if ((unsigned)e >= (unsigned)ne) continue;     // (a routing that was never written: caught below, nothing is touched)
         atomicOr(&mask[e][row >> 5], 1u << (row & 31));
     }
     __syncthreads();
@@ -78,6 +79,7 @@ sz_rows_plan_kernel(const int32_t* __restrict__ ridx, int R, int k, int ne, int 
     __syncthreads();
     for (int p = t; p < pairs; p += 1024) {
         const int e = __ldcg(ridx + p), row = p / k;
+        if ((unsigned)e >= (unsigned)ne) { P->pair_loc[p] = 0; P->overflow = 4; continue; }   // an expert id out of range: the call is reported as failed
         const int w = win_of[e];
         if (w < 0) { P->pair_loc[p] = 0; continue; }
         int n = __popc(mask[e][row >> 5] & ((1u << (row & 31)) - 1u));
@@ -131,7 +133,8 @@ sz_rows_combine_kernel(const long long* __restrict__ out, const SzRowsPlan* __re
     const int j = blockIdx.x / nb, b = blockIdx.x % nb;
     if (warp < top_k) {
         const int pair = j * top_k + warp;
-        const int e = __ldcg(ridx + pair);
+        int e = __ldcg(ridx + pair);
+        e = (unsigned)e < (unsigned)ne ? e : 0;
         const u16* svh = (const u16*)(down + (u64)e * dstride + 2 * (size_t)FF) + b * 128;
         const int loc = P->pair_loc[pair];
         float v[4];

@@ -16,6 +16,11 @@
 #include <stdlib.h>
 #include <string.h>
 #include <vector>
+#include <atomic>
+#include <condition_variable>
+#include <functional>
+#include <mutex>
+#include <thread>
 
 struct SzLayerBuf {
     int delta_index;   // index among DeltaNet layers, or -1
@@ -1251,6 +1256,69 @@ extern "C" int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint
 // result are read session by session as after sz_session_verify.  Launched eagerly on one stream (no graph: the rows a step holds
 // change from step to step).
 #define SZ_BATCH_MAX 64
+// A step of B sequences is some 400 launches a sequence: issued by one host thread they take longer than the GPU needs to run
+// them.  A few worker threads (SZ_BATCH_THREADS, default 6; 0 = none) issue the sequences' own launches side by side, each on the
+// sequences' own streams; what is shared is issued by the calling thread.  The workers live as long as the process.
+namespace {
+struct SzIssuePool {
+    std::vector<std::thread> th;
+    std::mutex mu;
+    std::condition_variable cv, cv_done;
+    std::function<void(int)> job;
+    int n = 0, dev = 0;
+    std::atomic<int> next{0};
+    int done = 0;
+    unsigned long long gen = 0;
+    bool stop = false;
+    explicit SzIssuePool(int workers) {
+        for (int i = 0; i < workers; i++) th.emplace_back([this] { run(); });
+    }
+    ~SzIssuePool() {
+        { std::lock_guard<std::mutex> lk(mu); stop = true; }
+        cv.notify_all();
+        for (auto& t : th) t.join();
+    }
+    void work() {
+        for (;;) {
+            const int i = next.fetch_add(1);
+            if (i >= n) break;
+            job(i);
+            std::lock_guard<std::mutex> lk(mu);
+            if (++done == n) cv_done.notify_all();
+        }
+    }
+    void run() {
+        unsigned long long seen = 0;
+        for (;;) {
+            {
+                std::unique_lock<std::mutex> lk(mu);
+                cv.wait(lk, [&] { return stop || gen != seen; });
+                if (stop) return;
+                seen = gen;
+            }
+            cudaSetDevice(dev);
+            work();
+        }
+    }
+    // runs fn(0) .. fn(count - 1), the caller taking its share; returns when all are done
+    void each(int count, int device, std::function<void(int)> fn) {
+        if (th.empty() || count < 2) { for (int i = 0; i < count; i++) fn(i); return; }
+        {
+            std::lock_guard<std::mutex> lk(mu);
+            job = std::move(fn); n = count; dev = device; done = 0; next.store(0); gen++;
+        }
+        cv.notify_all();
+        work();
+        std::unique_lock<std::mutex> lk(mu);
+        cv_done.wait(lk, [&] { return done == n; });
+    }
+};
+SzIssuePool& sz_issue_pool() {
+    static SzIssuePool pool([] { const char* e = getenv("SZ_BATCH_THREADS"); const int w = e ? atoi(e) : 6; return w < 0 ? 0 : (w > 32 ? 32 : w); }());
+    return pool;
+}
+}  // namespace
+
 struct SzBatchTab {
     const float* u[SZ_BATCH_MAX];
     float* y[SZ_BATCH_MAX];
@@ -1355,27 +1423,78 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
     SZ_CUDA(cudaMemcpyAsync(base + S.tab, &tab, sizeof(tab), cudaMemcpyHostToDevice, st));   // (pageable: staged before the call returns)
     float *X = (float*)(base + S.x), *Y = (float*)(base + S.y);
     if (Rp > R) SZ_CUDA(cudaMemsetAsync(X + (size_t)R * c.hidden, 0, (size_t)(Rp - R) * c.hidden * 4, st));   // the rows that pad the batch to a multiple of 8
-    for (int b = 0; b < n; b++)
-        if ((rc = sz_forward_begin(ss[b], st, ms[b]))) return rc;
+    // The sequences' own kernels are chains of short dependent launches: on one stream they would run one sequence after the other
+    // and leave the GPU as idle as a lone pass does.  So every sequence gets a stream of its own for them (a pool owned by the
+    // calling thread, made at the first call), and the caller's stream carries what is shared: per layer it waits for the
+    // sequences' inputs, runs the MoE sublayer over all rows, and lets the sequences go on.  SZ_BATCH_STREAMS=0: everything on the
+    // caller's stream.
+    static thread_local cudaStream_t pool[SZ_BATCH_MAX] = {};
+    static thread_local cudaEvent_t pool_ev[SZ_BATCH_MAX] = {};
+    static thread_local cudaEvent_t main_ev = nullptr;
+    static const bool streams_off = getenv("SZ_BATCH_STREAMS") && atoi(getenv("SZ_BATCH_STREAMS")) == 0;
+    const bool multi = !streams_off && n > 1;
+    if (multi) {
+        if (!main_ev) SZ_CUDA(cudaEventCreateWithFlags(&main_ev, cudaEventDisableTiming));
+        for (int b = 0; b < n; b++)
+            if (!pool[b]) {
+                SZ_CUDA(cudaStreamCreateWithFlags(&pool[b], cudaStreamNonBlocking));
+                SZ_CUDA(cudaEventCreateWithFlags(&pool_ev[b], cudaEventDisableTiming));
+            }
+    }
+    cudaStream_t* const pl = pool;          // (a worker thread that named `pool` would get its own, empty, thread-local array)
+    cudaEvent_t* const pe = pool_ev;
+    const cudaEvent_t mev = main_ev;
+    auto sq = [&, pl](int b) { return multi ? pl[b] : st; };
+    auto fork = [&]() -> int {      // the sequences' streams continue after what the caller's stream has done so far
+        if (!multi) return SZ_OK;
+        SZ_CUDA(cudaEventRecord(mev, st));
+        for (int b = 0; b < n; b++) SZ_CUDA(cudaStreamWaitEvent(pl[b], mev, 0));
+        return SZ_OK;
+    };
+    auto join = [&]() -> int {      // the caller's stream continues after every sequence's stream
+        if (!multi) return SZ_OK;
+        for (int b = 0; b < n; b++) {
+            SZ_CUDA(cudaEventRecord(pe[b], pl[b]));
+            SZ_CUDA(cudaStreamWaitEvent(st, pe[b], 0));
+        }
+        return SZ_OK;
+    };
+    int dev = 0;
+    SZ_CUDA(cudaGetDevice(&dev));
+    SzIssuePool& workers = sz_issue_pool();
+    std::atomic<int> worst{SZ_OK};   // (a failing launch: the first code is kept; its message is the last one written)
+    auto each = [&](const std::function<int(int)>& fn) -> int {
+        if (!multi) { for (int b = 0; b < n; b++) { const int r = fn(b); if (r) return r; } return SZ_OK; }
+        workers.each(n, dev, [&](int b) { const int r = fn(b); if (r) { int z = SZ_OK; worst.compare_exchange_strong(z, r); } });
+        return worst.load();
+    };
+    if ((rc = fork())) return rc;
+    if ((rc = each([&](int b) { return sz_forward_begin(ss[b], sq(b), ms[b]); }))) return rc;
     bool pending = false;
     for (int l = 0; l < c.n_layer; l++) {
-        for (int b = 0; b < n; b++)
-            if ((rc = sz_layer_to_moe(ss[b], st, l, ms[b], pending))) return rc;
-        SZ_CUDA(sz_launch("batch_gather", sz_batch_rows_kernel, dim3(R), dim3(256), 0, st, true, (const SzBatchTab*)(base + S.tab), X, (int)c.hidden, 0));
+        if ((rc = each([&](int b) { return sz_layer_to_moe(ss[b], sq(b), l, ms[b], pending); }))) return rc;
+        if ((rc = join())) return rc;
+        SZ_CUDA(sz_launch("batch_gather", sz_batch_rows_kernel, dim3(R), dim3(256), 0, st, !multi, (const SzBatchTab*)(base + S.tab), X, (int)c.hidden, 0));
         if ((rc = sz_moe_rows(&s0->layers[l].moe, (uint64_t)X, Rp, (uint64_t)Y, 0, 0, scratch + S.moe, S.moe_bytes, stream))) return rc;
         SZ_CUDA(sz_launch("batch_scatter", sz_batch_rows_kernel, dim3(R), dim3(256), 0, st, true, (const SzBatchTab*)(base + S.tab), Y, (int)c.hidden, 1));
+        if ((rc = fork())) return rc;
         pending = true;
     }
+    if ((rc = each([&](int b) {
+            sz_session* s = ss[b];
+            int r = sz_forward_head(s, sq(b), ms[b], pending);
+            if (!r) r = sz_pass_tail(s, sq(b), ms[b], accept_mode, eog_token, true);
+            return r;
+        })))
+        return rc;
     for (int b = 0; b < n; b++) {
         sz_session* s = ss[b];
-        if ((rc = sz_forward_head(s, st, ms[b], pending))) return rc;
-        if ((rc = sz_pass_tail(s, st, ms[b], accept_mode, eog_token, true))) return rc;
         s->last_m = ms[b];
         s->pending_committed = accept_mode != SZ_ACCEPT_NONE;
         s->device_keep = accept_mode == SZ_ACCEPT_ALL ? ms[b] : -1;
         s->inflight = 1;
     }
-    return SZ_OK;
+    return join();
 }
 
 // ---- synthetic history (benchmarks) -------------------------------------------------------------------------------------------------
