@@ -48,6 +48,7 @@ struct sz_session {
     float *r, *rn, *hdown, *mix, *u, *g, *y;
     float* r2;            // the second residual buffer of the fused hyper-connection read (reads ping-pong between r and r2)
     long long* hc_acc;    // [3][8][SZ_HC_ACC_ROWS] fixed-point accumulators of the fused read
+    int64_t hc_acc_stride;   // entries from one of the three to the next (a batched step points the session into buffers of the batch)
     double* rope_den;     // [rope_dims / 2]: theta^(2 i / rope_dims), computed on the host as the CPU reference computes it
     int hc_fast;          // every hyper-connection of the model fits the fused kernels
     int hc_n;             // reads launched so far in the pass being built (buffer parities are static per launch)
@@ -417,7 +418,7 @@ extern "C" int sz_session_create(const sz_model* m, int ctx, int flags, uint64_t
     }
     u8* b = (u8*)mem;
     s->base = b; s->bytes = bytes;
-    s->r = (float*)(b + L.r); s->r2 = (float*)(b + L.r2); s->hc_acc = (long long*)(b + L.hc_acc); s->rope_den = (double*)(b + L.rope); s->rn = (float*)(b + L.rn); s->hdown = (float*)(b + L.hdown); s->mix = (float*)(b + L.mix);
+    s->r = (float*)(b + L.r); s->r2 = (float*)(b + L.r2); s->hc_acc = (long long*)(b + L.hc_acc); s->hc_acc_stride = (int64_t)SZ_MAX_VERIFY * SZ_HC_ACC_ROWS; s->rope_den = (double*)(b + L.rope); s->rn = (float*)(b + L.rn); s->hdown = (float*)(b + L.hdown); s->mix = (float*)(b + L.mix);
     s->u = (float*)(b + L.u); s->g = (float*)(b + L.g); s->y = (float*)(b + L.y);
     s->d_xin = (float*)(b + L.d_xin); s->d_z = (float*)(b + L.d_z); s->d_b = (float*)(b + L.d_b); s->d_a = (float*)(b + L.d_a);
     s->d_xc = (float*)(b + L.d_xc); s->d_beta = (float*)(b + L.d_beta); s->d_decay = (float*)(b + L.d_decay); s->d_og = (float*)(b + L.d_og);
@@ -612,7 +613,7 @@ static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bo
         const int n = s->hc_n++;
         float* rin = (n & 1) ? s->r2 : s->r;
         float* rout = (n & 1) ? s->r : s->r2;
-        const int64_t as = (int64_t)SZ_MAX_VERIFY * SZ_HC_ACC_ROWS;
+        const int64_t as = s->hc_acc_stride;
         long long* acc = s->hc_acc + (n % 3) * as;
         long long* acc_prev = s->hc_acc + ((n + 2) % 3) * as;
         long long* acc_next = s->hc_acc + ((n + 1) % 3) * as;
@@ -679,6 +680,27 @@ static int sz_hc_read(sz_session* s, cudaStream_t st, const sz_hc& hc, int m, bo
     return SZ_OK;
 }
 
+// The fused read over the rows of a batch: buffers that hold the rows of all sequences one after the other (a multiple of 8 rows,
+// the sequences' own buffers pointing into them), eight rows a block row of the two kernels.  n: the read's number in the pass.
+struct SzBatchBufs { float *r, *r2, *y, *u, *rn; long long* acc; int64_t acc_stride; };
+static int sz_hc_read_rows(const sz_session* s, cudaStream_t st, const sz_hc& hc, int rows, int n, bool pending, bool inject, const SzBatchBufs& B, bool pdl) {
+    const sz_model_config& c = s->model.cfg;
+    const int H = c.hidden, C = c.streams, CH = C * H;
+    float* rin = (n & 1) ? B.r2 : B.r;
+    float* rout = (n & 1) ? B.r : B.r2;
+    long long* acc = B.acc + (n % 3) * B.acc_stride;
+    long long* acc_prev = B.acc + ((n + 2) % 3) * B.acc_stride;
+    long long* acc_next = B.acc + ((n + 1) % 3) * B.acc_stride;
+    int nt = ((int)c.hc_rank + C + 31) / 32 * 32;
+    if (nt < 256) nt = 256;
+    SZ_CUDA(sz_launch("hc_down", sz_hc_down_kernel<8>, dim3(CH / 64, rows / 8), dim3(nt), 0, st, pdl, (const float*)rin, rout,
+                      (const long long*)(pending ? acc_prev : nullptr), (const float*)B.y, (const float*)hc.norm.data, (const u8*)hc.down.data,
+                      (const u8*)(inject ? hc.inject.data : 0), H, C, (int)c.hc_rank, c.eps, B.rn, acc, acc_next));
+    SZ_CUDA(sz_launch("hc_up", sz_hc_up_kernel<8>, dim3(H / 16, rows / 8), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data,
+                      (const float*)B.rn, H, C, (int)c.hc_rank, B.u));
+    return SZ_OK;
+}
+
 // The DeltaNet scan: the pass of one layer (l >= 0: all m rows, with outputs) or the replay of a commit (l < 0: every layer in one
 // launch, the kept rows only, decided on the device).
 template <int D, int PARTS>
@@ -704,25 +726,63 @@ static int sz_scan(sz_session* s, cudaStream_t st, int l, int m, const SzDeltaPr
     return sz_scan_launch<64, 1>(s, st, l, m, pp);
 }
 
-static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
+// Which parts of a mixer a call runs: its input projections, what lies between them and the output projection, the output
+// projection.  A batched step runs the projections of all sequences together and only the middle per sequence.
+enum { SZ_MIX_IN = 1, SZ_MIX_CORE = 2, SZ_MIX_OUT = 4, SZ_MIX_ALL = 7 };
+
+// The input projections of layer l's mixer as jobs of the dense launcher that write the session's buffers (a: x = s->u), and the
+// output projection (b: x = the mixer's result before it, into s->y).
+static void sz_mixer_args(sz_session* s, int l, int m, SzDenseArgs* a, SzDenseArgs* b) {
+    const sz_model_config& c = s->model.cfg;
+    const sz_layer& L = s->layers[l];
+    const int H = c.hidden;
+    *a = SzDenseArgs{};
+    *b = SzDenseArgs{};
+    a->err = b->err = (u32*)(s->state + 2);
+    a->x = s->u; a->xstride = H; a->cols = H; a->m = m;
+    b->m = m; b->n_jobs = 1;
+    if (sz_is_attn(c, l)) {
+        const int nh = c.n_head, nkv = c.n_kv_head, hd = c.head_dim;
+        a->n_jobs = 3;
+        a->job[0] = sz_job(L.attn_q, s->a_qg, 2 * nh * hd);
+        a->job[1] = sz_job(L.attn_k, s->a_k, nkv * hd);
+        a->job[2] = sz_job(L.attn_v, s->a_v, nkv * hd);
+        if (c.idx_heads > 0) {
+            a->n_jobs = 5;
+            a->job[3] = sz_job(L.idx_q, s->i_q, c.idx_heads * c.idx_dim);
+            a->job[4] = sz_job(L.idx_k, s->i_k, c.idx_dim);
+        }
+        b->x = s->a_o; b->xstride = nh * hd; b->cols = nh * hd;
+        b->job[0] = sz_job(L.attn_output, s->y, H);
+    } else {
+        const int di = s->lb[l].delta_index;
+        const int vh = c.ssm_v_heads, kh = c.ssm_k_heads, d = c.ssm_head_dim;
+        const int64_t kd = (int64_t)kh * d, vd = (int64_t)vh * d, ch = 2 * kd + vd;
+        a->n_jobs = 4;
+        a->job[0] = sz_job(L.attn_qkv, s->d_xin + (int64_t)di * SZ_MAX_VERIFY * ch, (int)ch);
+        a->job[1] = sz_job(L.attn_gate, s->d_z, (int)vd);
+        a->job[2] = sz_job(L.ssm_beta, s->d_b, vh);
+        a->job[3] = sz_job(L.ssm_alpha, s->d_a, vh);
+        b->x = s->d_og; b->xstride = (int)vd; b->cols = (int)vd;
+        b->job[0] = sz_job(L.ssm_out, s->y, H);
+    }
+}
+
+static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m, int parts = SZ_MIX_ALL) {
     const sz_model_config& c = s->model.cfg;
     const sz_layer& L = s->layers[l];
     const int di = s->lb[l].delta_index;
-    const int H = c.hidden, vh = c.ssm_v_heads, kh = c.ssm_k_heads, d = c.ssm_head_dim;
+    const int vh = c.ssm_v_heads, kh = c.ssm_k_heads, d = c.ssm_head_dim;
     const int64_t kd = (int64_t)kh * d, vd = (int64_t)vh * d, ch = 2 * kd + vd;
     float* xin = s->d_xin + (int64_t)di * SZ_MAX_VERIFY * ch;
     float* xc = s->d_xc + (int64_t)di * SZ_MAX_VERIFY * ch;
     float* beta = s->d_beta + (int64_t)di * SZ_MAX_VERIFY * vh;
     float* decay = s->d_decay + (int64_t)di * SZ_MAX_VERIFY * vh;
-    SzDenseArgs a = {};
-    a.err = (u32*)(s->state + 2);
-    a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 4;
-    a.job[0] = sz_job(L.attn_qkv, xin, (int)ch);
-    a.job[1] = sz_job(L.attn_gate, s->d_z, (int)vd);
-    a.job[2] = sz_job(L.ssm_beta, s->d_b, vh);
-    a.job[3] = sz_job(L.ssm_alpha, s->d_a, vh);
-    int rc = sz_dense_launch(a, st, "delta_proj");
-    if (rc) return rc;
+    SzDenseArgs a, b;
+    sz_mixer_args(s, l, m, &a, &b);
+    int rc = SZ_OK;
+    if ((parts & SZ_MIX_IN) && (rc = sz_dense_launch(a, st, "delta_proj"))) return rc;
+    if (!(parts & SZ_MIX_CORE)) return (parts & SZ_MIX_OUT) ? sz_dense_launch(b, st, "ssm_out") : SZ_OK;
     const int64_t cl = (int64_t)(c.conv_k - 1) * ch;
     static const bool split_prep = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;
     SzDeltaPrep pp = {};
@@ -736,11 +796,7 @@ static int sz_delta_layer(sz_session* s, cudaStream_t st, int l, int m) {
         pp.xc = xc; pp.beta = beta; pp.decay = decay; pp.k = (int)c.conv_k;
     }
     if ((rc = sz_scan(s, st, l, m, pp))) return rc;
-    SzDenseArgs b = {};
-    b.err = (u32*)(s->state + 2);
-    b.x = s->d_og; b.xstride = (int)vd; b.cols = (int)vd; b.m = m; b.n_jobs = 1;
-    b.job[0] = sz_job(L.ssm_out, s->y, H);
-    return sz_dense_launch(b, st, "ssm_out");
+    return (parts & SZ_MIX_OUT) ? sz_dense_launch(b, st, "ssm_out") : SZ_OK;
 }
 
 template <int EPL>
@@ -783,31 +839,23 @@ static int sz_attn2_launch(sz_session* s, cudaStream_t st, const u8* kc, const u
     return sz_attn2_go<HD, 4>(s, st, kc, vc, m, splits_used, ratio);
 }
 
-static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
+static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m, int parts = SZ_MIX_ALL) {
     const sz_model_config& c = s->model.cfg;
     const sz_layer& L = s->layers[l];
     const int ai = s->lb[l].attn_index;
-    const int H = c.hidden, nh = c.n_head, nkv = c.n_kv_head, hd = c.head_dim;
+    const int nh = c.n_head, nkv = c.n_kv_head, hd = c.head_dim;
     const int q8 = (s->flags & SZ_KV_Q8) ? 1 : 0;
     const int64_t hb = q8 ? (hd + (((hd >> 5) * 2 + 15) & ~15)) : 4 * (int64_t)hd;
     const int64_t layer_bytes = (int64_t)s->ctx * nkv * hb;
     u8 *kc = s->kc + ai * layer_bytes, *vc = s->vc + ai * layer_bytes;
-    SzDenseArgs a = {};
-    a.err = (u32*)(s->state + 2);
-    a.x = s->u; a.xstride = H; a.cols = H; a.m = m; a.n_jobs = 3;
-    a.job[0] = sz_job(L.attn_q, s->a_qg, 2 * nh * hd);
-    a.job[1] = sz_job(L.attn_k, s->a_k, nkv * hd);
-    a.job[2] = sz_job(L.attn_v, s->a_v, nkv * hd);
+    SzDenseArgs a, b;
+    sz_mixer_args(s, l, m, &a, &b);
     const bool idx = c.idx_heads > 0;
     const int ratio = idx ? (L.idx_ratio > 0 ? L.idx_ratio : 1) : 0;
-    if (idx) {
-        if (s->tree_pass) return sz_fail(SZ_E_ARG, "a tree pass on a model with the sparse indexer is not supported");
-        a.n_jobs = 5;
-        a.job[3] = sz_job(L.idx_q, s->i_q, c.idx_heads * c.idx_dim);
-        a.job[4] = sz_job(L.idx_k, s->i_k, c.idx_dim);
-    }
-    int rc = sz_dense_launch(a, st, "attn_proj");
-    if (rc) return rc;
+    if (idx && s->tree_pass) return sz_fail(SZ_E_ARG, "a tree pass on a model with the sparse indexer is not supported");
+    int rc = SZ_OK;
+    if ((parts & SZ_MIX_IN) && (rc = sz_dense_launch(a, st, "attn_proj"))) return rc;
+    if (!(parts & SZ_MIX_CORE)) return (parts & SZ_MIX_OUT) ? sz_dense_launch(b, st, "attn_output") : SZ_OK;
     if (idx) {
         SzIdxGeom g;
         g.heads = c.idx_heads; g.dim = c.idx_dim; g.ratio = ratio; g.keep = c.idx_budget / ratio; g.ctx_blocks = s->i_ctx_blocks; g.words = s->i_words;
@@ -843,11 +891,7 @@ static int sz_attn_layer(sz_session* s, cudaStream_t st, int l, int m) {
     if (rc) return rc;
     SZ_CUDA(sz_launch("attn_merge", sz_attn_merge_kernel, dim3(nh, m), dim3(256), 0, st, true, (const float*)s->a_part, (const float*)s->a_gate, nh, hd,
                       splits, s->a_o));
-    SzDenseArgs b = {};
-    b.err = (u32*)(s->state + 2);
-    b.x = s->a_o; b.xstride = nh * hd; b.cols = nh * hd; b.m = m; b.n_jobs = 1;
-    b.job[0] = sz_job(L.attn_output, s->y, H);
-    return sz_dense_launch(b, st, "attn_output");
+    return (parts & SZ_MIX_OUT) ? sz_dense_launch(b, st, "attn_output") : SZ_OK;
 }
 
 // The per-layer embedding before layer model.ple.layer's first read (sz_ple.cuh).  The residual of the moment: with the fused
@@ -876,7 +920,7 @@ static int sz_ple_layer(sz_session* s, cudaStream_t st, int m, bool pending) {
     if (s->hc_fast) {
         const int n = s->hc_n;                       // the read that follows
         r = (n & 1) ? s->r2 : s->r;
-        if (pending) g_acc = s->hc_acc + ((n + 2) % 3) * (int64_t)SZ_MAX_VERIFY * SZ_HC_ACC_ROWS;
+        if (pending) g_acc = s->hc_acc + ((n + 2) % 3) * s->hc_acc_stride;
     } else if (pending) {
         g_f = s->g;
     }
@@ -890,10 +934,10 @@ static int sz_ple_layer(sz_session* s, cudaStream_t st, int m, bool pending) {
 }
 
 // Runs the m rows through every layer and, with `head`, through the output projection and the top-64.
-static int sz_forward_begin(sz_session* s, cudaStream_t st, int m) {
+static int sz_forward_begin(sz_session* s, cudaStream_t st, int m, bool clear = true) {
     const sz_model_config& c = s->model.cfg;
     s->hc_n = 0;
-    if (s->hc_fast) SZ_CUDA(cudaMemsetAsync(s->hc_acc, 0, sizeof(long long) * SZ_MAX_VERIFY * SZ_HC_ACC_ROWS, st));  // read 0 adds into buffer 0
+    if (s->hc_fast && clear) SZ_CUDA(cudaMemsetAsync(s->hc_acc, 0, sizeof(long long) * SZ_MAX_VERIFY * SZ_HC_ACC_ROWS, st));  // read 0 adds into buffer 0
     SZ_CUDA(sz_launch("embed", sz_embed_kernel, dim3(m), dim3(256), 0, st, false, (const int32_t*)s->ids, (const u8*)s->model.token_embd.data,
                       (int)s->model.token_embd.type, (int)c.hidden, (int)c.streams, (int)c.vocab, s->r));
     return SZ_OK;
@@ -913,11 +957,11 @@ static int sz_layer_to_moe(sz_session* s, cudaStream_t st, int l, int m, bool pe
     return sz_hc_read(s, st, L.hc_ffn, m, true, true);   // applies the mixer's write first
 }
 // After the last layer: the output read, the head, the top-64 of every row.
-static int sz_forward_head(sz_session* s, cudaStream_t st, int m, bool pending) {
+static int sz_forward_head(sz_session* s, cudaStream_t st, int m, bool pending, bool read = true) {
     const sz_model_config& c = s->model.cfg;
     const int H = c.hidden;
     int rc;
-    if ((rc = sz_hc_read(s, st, s->model.output_hc, m, pending, false))) return rc;
+    if (read && (rc = sz_hc_read(s, st, s->model.output_hc, m, pending, false))) return rc;
     if (s->head.rows > 0) return sz_head_top(&s->head, (uint64_t)s->u, H, m, 64, (uint64_t)s->logits, (uint64_t)s->top, (uint64_t)st);
     SzDenseArgs a = {};
     a.err = (u32*)(s->state + 2);
@@ -1340,15 +1384,58 @@ sz_batch_rows_kernel(const SzBatchTab* __restrict__ T, float* __restrict__ X, in
     else { float4* dst = (float4*)(T->y[b] + (size_t)j * H); for (int i = threadIdx.x; i < H / 4; i += 256) dst[i] = __ldcg(x + i); }
 }
 
-struct SzBatchScratch { int64_t tab, x, y, moe, moe_bytes, total; };
+// The rows of a batch to and from buffers of the sequences' own: what[k] says where piece k of a row lives in the batch buffer
+// (offset of the piece's block in floats, floats a row) and ptrs[(slot + k) * SZ_BATCH_MAX + b] where sequence b keeps it.
+// grid (rows, pieces), block 256.  dir 0: batch <- sequences; dir 1: sequences <- batch.
+struct SzBatchMove { long long off[SZ_DENSE_MAX_JOBS]; int32_t width[SZ_DENSE_MAX_JOBS]; };
+static __global__ void __launch_bounds__(256)
+sz_batch_move_kernel(const SzBatchTab* __restrict__ T, float* const* __restrict__ ptrs, SzBatchMove mv, float* __restrict__ X, int dir) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int r = blockIdx.x, k = blockIdx.y;
+    int b = 0;
+    while (b + 1 < T->n && T->off[b + 1] <= r) b++;
+    const int j = r - T->off[b];
+    if (j >= T->m[b]) return;
+    const int w = mv.width[k];
+    float* x = X + mv.off[k] + (size_t)r * w;
+    float* p = ptrs[(size_t)k * SZ_BATCH_MAX + b] + (size_t)j * w;
+    if (!(w & 3)) {
+        if (dir == 0) for (int i = threadIdx.x; i < w / 4; i += 256) ((float4*)x)[i] = __ldcg((const float4*)p + i);
+        else for (int i = threadIdx.x; i < w / 4; i += 256) ((float4*)p)[i] = __ldcg((const float4*)x + i);
+    } else {
+        if (dir == 0) for (int i = threadIdx.x; i < w; i += 256) x[i] = __ldcg(p + i);
+        else for (int i = threadIdx.x; i < w; i += 256) p[i] = __ldcg(x + i);
+    }
+}
+
+enum { SZ_BATCH_SLOTS = SZ_DENSE_MAX_JOBS + 1 };   // per layer: the outputs of the input projections, then the input of the output projection
+struct SzBatchScratch { int64_t tab, ptrs, ptrs_bytes, x, y, r, r2, rn, acc, in, in_row, core, core_row, moe, moe_bytes, total; };
 static int sz_batch_layout(const sz_model* m, int rows_max, SzBatchScratch* S) {
     if (!m || !m->layers) return sz_fail(SZ_E_ARG, "null model");
     if (rows_max < 8 || rows_max % 8) return sz_fail(SZ_E_ARG, "sz_batch: rows_max = %d (a multiple of 8)", rows_max);
+    const sz_model_config& c = m->cfg;
     int64_t o = 0, mb = 0;
     S->tab = o; o = up256(o + (int64_t)sizeof(SzBatchTab));
-    S->x = o; o = up256(o + 4 * (int64_t)rows_max * m->cfg.hidden);
-    S->y = o; o = up256(o + 4 * (int64_t)rows_max * m->cfg.hidden);
-    for (int l = 0; l < m->cfg.n_layer; l++) {
+    S->ptrs_bytes = (int64_t)c.n_layer * SZ_BATCH_SLOTS * SZ_BATCH_MAX * (int64_t)sizeof(float*);
+    S->ptrs = o; o = up256(o + S->ptrs_bytes);
+    S->x = o; o = up256(o + 4 * (int64_t)rows_max * c.hidden);
+    S->y = o; o = up256(o + 4 * (int64_t)rows_max * c.hidden);
+    // the residual streams, their normed copy and the accumulators of the fused reads, for the rows of all sequences
+    const int64_t CH = (int64_t)c.streams * c.hidden;
+    S->r = o; o = up256(o + 4 * rows_max * CH);
+    S->r2 = o; o = up256(o + 4 * rows_max * CH);
+    S->rn = o; o = up256(o + 4 * rows_max * CH);
+    S->acc = o; o = up256(o + 8 * 3 * (int64_t)rows_max * SZ_HC_ACC_ROWS);
+    // a row of the mixers' projections: the wider of the two kinds of layer
+    const int64_t kd = (int64_t)c.ssm_k_heads * c.ssm_head_dim, vd = (int64_t)c.ssm_v_heads * c.ssm_head_dim;
+    const int64_t in_d = 2 * kd + vd + vd + 2 * c.ssm_v_heads;
+    const int64_t in_a = 2 * (int64_t)c.n_head * c.head_dim + 2 * (int64_t)c.n_kv_head * c.head_dim + (int64_t)c.idx_heads * c.idx_dim + c.idx_dim;
+    S->in_row = (in_d > in_a ? in_d : in_a);
+    S->core_row = vd > (int64_t)c.n_head * c.head_dim ? vd : (int64_t)c.n_head * c.head_dim;
+    S->in = o; o = up256(o + 4 * rows_max * S->in_row);
+    S->core = o; o = up256(o + 4 * rows_max * S->core_row);
+    for (int l = 0; l < c.n_layer; l++) {
         int64_t b = 0;
         const int rc = sz_moe_rows_scratch_bytes(&m->layers[l].moe, rows_max, &b);
         if (rc) return rc;
@@ -1421,8 +1508,54 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
     }
     u8* base = (u8*)scratch;
     SZ_CUDA(cudaMemcpyAsync(base + S.tab, &tab, sizeof(tab), cudaMemcpyHostToDevice, st));   // (pageable: staged before the call returns)
-    float *X = (float*)(base + S.x), *Y = (float*)(base + S.y);
-    if (Rp > R) SZ_CUDA(cudaMemsetAsync(X + (size_t)R * c.hidden, 0, (size_t)(Rp - R) * c.hidden * 4, st));   // the rows that pad the batch to a multiple of 8
+    float *X = (float*)(base + S.x), *Y = (float*)(base + S.y), *IN = (float*)(base + S.in), *CORE = (float*)(base + S.core);
+    // What reads the same weights for every sequence runs once over the rows of all of them (`shared`): the hyper-connection reads
+    // and the mixers' projections, besides the MoE sublayers.  The sequences' residual streams, mixer outputs and sublayer inputs
+    // then live side by side in buffers of the batch - for the length of the step every session points into them, so that its own
+    // kernels (embedding, per-layer embedding, scan, attention, head) find their rows where they always do - and the shared kernels
+    // take eight rows a block row or a launch, the very kernels of a lone pass: a row's result does not depend on the rows beside
+    // it.  Only what carries a sequence's own state stays a launch per sequence.  SZ_BATCH_SHARED=0: only the MoE is shared.
+    const char* se = getenv("SZ_BATCH_SHARED");   // (read at every step: a test switches it inside one process)
+    const bool shared_off = se && atoi(se) == 0;
+    const bool shared = !shared_off && n > 1 && s0->hc_fast;
+    const int64_t CH = (int64_t)c.streams * c.hidden;
+    SzBatchBufs BB = {(float*)(base + S.r), (float*)(base + S.r2), Y, X, (float*)(base + S.rn), (long long*)(base + S.acc), (int64_t)rows_max * SZ_HC_ACC_ROWS};
+    struct Repoint {   // the sessions' buffers while they point into the batch's: put back however the step ends
+        sz_session* const* ss = nullptr;
+        int n = 0;
+        struct { float *r, *r2, *y, *u, *rn; long long* acc; int64_t stride; } was[SZ_BATCH_MAX];
+        ~Repoint() {
+            for (int b = 0; b < n; b++) {
+                sz_session* s = ss[b];
+                s->r = was[b].r; s->r2 = was[b].r2; s->y = was[b].y; s->u = was[b].u; s->rn = was[b].rn; s->hc_acc = was[b].acc; s->hc_acc_stride = was[b].stride;
+            }
+        }
+    } repoint;
+    float* const* ptrs = (float* const*)(base + S.ptrs);
+    if (shared) {
+        repoint.ss = ss;
+        for (int b = 0; b < n; b++) {
+            sz_session* s = ss[b];
+            repoint.was[b] = {s->r, s->r2, s->y, s->u, s->rn, s->hc_acc, s->hc_acc_stride};
+            repoint.n = b + 1;
+            const int64_t o = tab.off[b];
+            s->r = BB.r + o * CH; s->r2 = BB.r2 + o * CH; s->y = BB.y + o * c.hidden; s->u = BB.u + o * c.hidden; s->rn = BB.rn + o * CH;
+            s->hc_acc = BB.acc + o * SZ_HC_ACC_ROWS; s->hc_acc_stride = BB.acc_stride;
+        }
+        static thread_local std::vector<float*> host;   // where every sequence keeps the projections' outputs and the output projection's input
+        host.assign((size_t)c.n_layer * SZ_BATCH_SLOTS * SZ_BATCH_MAX, nullptr);
+        for (int l = 0; l < c.n_layer; l++)
+            for (int b = 0; b < n; b++) {
+                SzDenseArgs a, o;
+                sz_mixer_args(ss[b], l, ms[b], &a, &o);
+                float** row = host.data() + (size_t)l * SZ_BATCH_SLOTS * SZ_BATCH_MAX;
+                for (int k = 0; k < a.n_jobs; k++) row[(size_t)k * SZ_BATCH_MAX + b] = a.job[k].out;
+                row[(size_t)SZ_DENSE_MAX_JOBS * SZ_BATCH_MAX + b] = const_cast<float*>(o.x);
+            }
+        SZ_CUDA(cudaMemcpyAsync(base + S.ptrs, host.data(), (size_t)S.ptrs_bytes, cudaMemcpyHostToDevice, st));   // (pageable, as the table)
+        SZ_CUDA(cudaMemsetAsync(BB.acc, 0, sizeof(long long) * (size_t)Rp * SZ_HC_ACC_ROWS, st));   // read 0 adds into accumulator 0
+    }
+    if (Rp > R && !shared) SZ_CUDA(cudaMemsetAsync(X + (size_t)R * c.hidden, 0, (size_t)(Rp - R) * c.hidden * 4, st));   // the rows that pad the batch to a multiple of 8
     // The sequences' own kernels are chains of short dependent launches: on one stream they would run one sequence after the other
     // and leave the GPU as idle as a lone pass does.  So every sequence gets a stream of its own for them (a pool owned by the
     // calling thread, made at the first call), and the caller's stream carries what is shared: per layer it waits for the
@@ -1469,20 +1602,75 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
         return worst.load();
     };
     if ((rc = fork())) return rc;
-    if ((rc = each([&](int b) { return sz_forward_begin(ss[b], sq(b), ms[b]); }))) return rc;
+    if ((rc = each([&](int b) { return sz_forward_begin(ss[b], sq(b), ms[b], !shared); }))) return rc;
     bool pending = false;
-    for (int l = 0; l < c.n_layer; l++) {
-        if ((rc = each([&](int b) { return sz_layer_to_moe(ss[b], sq(b), l, ms[b], pending); }))) return rc;
-        if ((rc = join())) return rc;
-        SZ_CUDA(sz_launch("batch_gather", sz_batch_rows_kernel, dim3(R), dim3(256), 0, st, !multi, (const SzBatchTab*)(base + S.tab), X, (int)c.hidden, 0));
-        if ((rc = sz_moe_rows(&s0->layers[l].moe, (uint64_t)X, Rp, (uint64_t)Y, 0, 0, scratch + S.moe, S.moe_bytes, stream))) return rc;
-        SZ_CUDA(sz_launch("batch_scatter", sz_batch_rows_kernel, dim3(R), dim3(256), 0, st, true, (const SzBatchTab*)(base + S.tab), Y, (int)c.hidden, 1));
+    const SzBatchTab* T = (const SzBatchTab*)(base + S.tab);
+    if (shared) {
+        int hn = 0;   // hyper-connection reads so far (every session's count follows: the per-layer embedding looks at it)
+        auto read_rows = [&](const sz_hc& hc, bool pend, bool inject, bool pdl) -> int {
+            const int r = sz_hc_read_rows(s0, st, hc, Rp, hn++, pend, inject, BB, pdl);
+            for (int b = 0; b < n; b++) ss[b]->hc_n = hn;
+            return r;
+        };
+        for (int l = 0; l < c.n_layer; l++) {
+            const sz_layer& L = s0->layers[l];
+            const bool ple_here = s0->p_hist && l == s0->model.ple.layer;
+            bool pend = pending;
+            if (ple_here) {   // (it applies the pending write itself, on the sequence's rows of the shared buffers)
+                if (l > 0 && (rc = fork())) return rc;
+                if ((rc = each([&](int b) { return sz_ple_layer(ss[b], sq(b), ms[b], pending); }))) return rc;
+                pend = false;
+            }
+            const bool joined = l == 0 || ple_here;
+            if (joined && (rc = join())) return rc;
+            if ((rc = read_rows(L.hc_attn, pend, true, !(joined && multi)))) return rc;
+            float* const* lp = ptrs + (size_t)l * SZ_BATCH_SLOTS * SZ_BATCH_MAX;
+            SzDenseArgs a, o;
+            sz_mixer_args(s0, l, 8, &a, &o);
+            SzBatchMove mi = {}, mo = {};
+            long long at_in = 0;
+            for (int k = 0; k < a.n_jobs; k++) { mi.off[k] = at_in; mi.width[k] = a.job[k].ostride; at_in += (long long)Rp * a.job[k].ostride; }
+            mo.off[0] = 0; mo.width[0] = o.cols;
+            for (int g = 0; g < Rp / 8; g++) {
+                SzDenseArgs ag = a;
+                ag.x = X + (size_t)g * 8 * c.hidden;
+                for (int k = 0; k < a.n_jobs; k++) ag.job[k].out = IN + mi.off[k] + (size_t)g * 8 * mi.width[k];
+                if ((rc = sz_dense_launch(ag, st, "batch_proj"))) return rc;
+            }
+            SZ_CUDA(sz_launch("batch_move", sz_batch_move_kernel, dim3(R, a.n_jobs), dim3(256), 0, st, true, T, lp, mi, IN, 1));
+            if ((rc = fork())) return rc;
+            if ((rc = each([&](int b) {
+                    return sz_is_attn(c, l) ? sz_attn_layer(ss[b], sq(b), l, ms[b], SZ_MIX_CORE) : sz_delta_layer(ss[b], sq(b), l, ms[b], SZ_MIX_CORE);
+                })))
+                return rc;
+            if ((rc = join())) return rc;
+            SZ_CUDA(sz_launch("batch_move", sz_batch_move_kernel, dim3(R, 1), dim3(256), 0, st, !multi, T, lp + (size_t)SZ_DENSE_MAX_JOBS * SZ_BATCH_MAX, mo, CORE, 0));
+            for (int g = 0; g < Rp / 8; g++) {
+                SzDenseArgs og = o;
+                og.x = CORE + (size_t)g * 8 * o.cols;
+                og.job[0].out = Y + (size_t)g * 8 * c.hidden;
+                if ((rc = sz_dense_launch(og, st, "batch_out"))) return rc;
+            }
+            if ((rc = read_rows(L.hc_ffn, true, true, true))) return rc;
+            if ((rc = sz_moe_rows(&L.moe, (uint64_t)X, Rp, (uint64_t)Y, 0, 0, scratch + S.moe, S.moe_bytes, stream))) return rc;
+            pending = true;
+        }
+        if ((rc = read_rows(s0->model.output_hc, pending, false, true))) return rc;
         if ((rc = fork())) return rc;
-        pending = true;
+    } else {
+        for (int l = 0; l < c.n_layer; l++) {
+            if ((rc = each([&](int b) { return sz_layer_to_moe(ss[b], sq(b), l, ms[b], pending); }))) return rc;
+            if ((rc = join())) return rc;
+            SZ_CUDA(sz_launch("batch_gather", sz_batch_rows_kernel, dim3(R), dim3(256), 0, st, !multi, T, X, (int)c.hidden, 0));
+            if ((rc = sz_moe_rows(&s0->layers[l].moe, (uint64_t)X, Rp, (uint64_t)Y, 0, 0, scratch + S.moe, S.moe_bytes, stream))) return rc;
+            SZ_CUDA(sz_launch("batch_scatter", sz_batch_rows_kernel, dim3(R), dim3(256), 0, st, true, T, Y, (int)c.hidden, 1));
+            if ((rc = fork())) return rc;
+            pending = true;
+        }
     }
     if ((rc = each([&](int b) {
             sz_session* s = ss[b];
-            int r = sz_forward_head(s, sq(b), ms[b], pending);
+            int r = sz_forward_head(s, sq(b), ms[b], pending, !shared);
             if (!r) r = sz_pass_tail(s, sq(b), ms[b], accept_mode, eog_token, true);
             return r;
         })))

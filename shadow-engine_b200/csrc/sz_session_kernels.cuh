@@ -245,7 +245,10 @@ sz_hc_down_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, con
     const u8* wrow = sz_hc_down_fetch(down, inject, H, C, rank, w);
     sz_pdl_wait();
     sz_pdl_trigger();
-    sz_hc_down_body<M>(r_in, r_out, g_acc, y, normw, H, C, rank, eps, rn, acc, acc_next, wrow, w);
+    // grid.y > 1: block row g serves rows [g M, g M + M) of buffers that hold the rows of several sequences one after the other
+    const size_t g = (size_t)blockIdx.y * M;
+    sz_hc_down_body<M>(r_in + g * C * H, r_out + g * C * H, g_acc ? g_acc + g * SZ_HC_ACC_ROWS : nullptr, y + g * H, normw, H, C, rank, eps,
+                       rn + g * C * H, acc + g * SZ_HC_ACC_ROWS, acc_next + g * SZ_HC_ACC_ROWS, wrow, w);
 }
 
 // grid H / 16, block 256.  CPR = rank / 8: 16-byte pieces a row of the up matrix.
@@ -356,7 +359,8 @@ sz_hc_up_kernel(const long long* __restrict__ acc, const u8* __restrict__ up, co
     sz_hc_up_fetch(up, H, C, rank, w);
     sz_pdl_wait();
     sz_pdl_trigger();
-    sz_hc_up_body<M>(acc, rn, H, C, rank, u, w);
+    const size_t g = (size_t)blockIdx.y * M;   // (as the down kernel)
+    sz_hc_up_body<M>(acc + g * SZ_HC_ACC_ROWS, rn + g * C * H, H, C, rank, u + g * H, w);
 }
 
 // A barrier over all blocks of a grid whose blocks are all resident (no more blocks than the GPU holds at once: the caller sizes

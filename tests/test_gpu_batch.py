@@ -44,18 +44,25 @@ def test_a_step_of_several_sequences_equals_their_own_passes(dm):
         batch.sessions[b].commit(keep); alone[b].commit(keep2)
     with pytest.raises(szlib.SzError):
         batch.verify([[1], [2]], which=[1, 1])         # a session twice
+    # after the steps the sessions are their own again: a pass alone on one of them is the pass of the session that always was
+    for b in (1, 4):
+        r = seqs[b][at[b]:at[b] + 3]
+        batch.sessions[b].verify(r); _, top, lg = batch.sessions[b].result(logits=True)
+        alone[b].verify(r); _, top2, lg2 = alone[b].result(logits=True)
+        assert np.array_equal(lg.view(np.uint32), lg2.view(np.uint32)) and np.array_equal(top, top2)
 
 
-def test_sequences_decoding_in_lockstep_emit_their_own_tokens(dm):
-    prompts = [md.make_prompt(40 + 8 * b, CFG["vocab"], seed=10 + b) for b in range(4)]
+def lockstep(dm, vocab, n_seq, n_new, ctx=256):
+    """n_seq sequences alone and then in lockstep: tokens and the books of every sequence."""
+    import ctypes as C
+    prompts = [md.make_prompt(40 + 8 * b, vocab, seed=10 + b) for b in range(n_seq)]
     want = []
     for p in prompts:
-        toks, _, st = md.Session(dm, 256, kv_q8=True).generate(p, 32 + len(want), spec_k=3)
+        toks, _, st = md.Session(dm, ctx, kv_q8=True).generate(p, n_new + len(want), spec_k=3)
         want.append((toks, st.passes, st.drafted, st.accepted))
-    batch = md.Batch(dm, 4, 256)
-    gens = [md.Generator(s, p, 32 + b, spec_k=3) for b, (s, p) in enumerate(zip(batch.sessions, prompts))]
-    import ctypes as C
-    n = 4
+    batch = md.Batch(dm, n_seq, ctx)
+    gens = [md.Generator(s, p, n_new + b, spec_k=3) for b, (s, p) in enumerate(zip(batch.sessions, prompts))]
+    n = n_seq
     gh = (C.c_void_p * n)(*[g.h for g in gens])
     outs = (C.c_void_p * n)(*[C.cast(g.out, C.c_void_p) for g in gens])
     sts = (C.c_void_p * n)(*[C.cast(C.pointer(g.stats), C.c_void_p) for g in gens])
@@ -64,3 +71,31 @@ def test_sequences_decoding_in_lockstep_emit_their_own_tokens(dm):
     for b, g in enumerate(gens):
         assert (g.tokens(), g.stats.passes, g.stats.drafted, g.stats.accepted) == want[b], "sequence %d" % b
     assert dev.value > 0.0
+
+
+def test_sequences_decoding_in_lockstep_emit_their_own_tokens(dm):
+    lockstep(dm, CFG["vocab"], 4, 32)
+
+
+@pytest.mark.parametrize("ple_layer", [0, 1])
+def test_lockstep_on_a_model_with_the_per_layer_embedding_and_the_indexer(ple_layer):
+    """The per-layer embedding (first layer: before anything shared has run; a later one: after a shared MoE) and the sparse indexer
+    keep their state per sequence while the reads and projections around them run over all rows."""
+    from tests.test_oracle_ple import PLE
+    cfg = dict(PLE, hidden=512, hc_rank=64, ple_head_dim=128, ple_layer=ple_layer, idx_heads=2, idx_dim=32, idx_budget=16, idx_ratio=4)   # (the streaming expert kernels take a hidden size that is a multiple of 512)
+    M = md.make_model(cfg, expert_type=szlib.TYPE_EXL3(3), seed=6, cycle_alpha=0.9)
+    lockstep(md.DeviceModel(M), cfg["vocab"], 3, 40)
+
+
+def test_the_shared_reads_and_projections_change_no_bit(dm, monkeypatch):
+    """SZ_BATCH_SHARED=0 shares only the MoE sublayers (every sequence reads and projects its own rows): the same logits."""
+    rng = np.random.default_rng(5)
+    rows = [[int(t) for t in rng.integers(0, CFG["vocab"], m)] for m in (3, 8, 1, 4, 2, 7)]
+    got = []
+    for flag in ("1", "0"):
+        monkeypatch.setenv("SZ_BATCH_SHARED", flag)
+        batch = md.Batch(dm, 6, 64)
+        batch.verify(rows)
+        got.append([batch.sessions[b].result(logits=True)[2].view(np.uint32).copy() for b in range(6)])
+    for a, b in zip(*got):
+        assert np.array_equal(a, b)
