@@ -12,8 +12,8 @@ torchrun) the experts of every layer are sharded over the N ranks (expert parall
 rows on tcgen05 (`sz_mma_cols`); TFLOP/s against the measured dense bf16 rate.
 `--workload c5-concurrent`: B sequences decoded at once on every GPU (config 5's batched serving, without batching the kernels): each
 sequence has a verify session, stream and CUDA graphs of its own over the one resident model, and the GPU overlaps their passes.
-`--workload c5-batch`: B sequences decoding in lockstep on every GPU (`sz_batch_gen_run`): sessions of their own, the MoE sublayers of
-every layer shared by the rows of all sequences.
+`--workload c5-batch`: B sequences decoding in lockstep on every GPU (`sz_batch_gen_run`): sessions of their own, the reads, projections
+and MoE sublayers of every layer run once over the rows of all sequences.
 `--workload c5-moe`: the MoE sublayer over the verify rows of many sequences at once (64 sequences x K+1 = 4 rows = 256 rows), every
 distinct expert decoded once (`sz_moe_rows`), next to the same rows as 64 passes of 4.
 `--workload c4-tree`: benchmark config 4's mechanism on the config-3 model: one verify pass over a draft tree (8 rows), greedy
@@ -849,11 +849,12 @@ def run_c5_moe(args):
     out.emit(json.dumps(line))
 
 
-# ---- workload c5-batch: B sequences in lockstep, the MoE sublayers shared -----------------------------------------------------------
+# ---- workload c5-batch: B sequences in lockstep, what reads weights shared -----------------------------------------------------------
 def run_c5_batch(args):
     """Config 5's batch on the config-3 model: B sequences a GPU, every one with a session of its own (cache filled to the context,
     a 256-token prompt fed through it: untimed), then all decode `request_tokens` tokens in lockstep, spec K=3 each, through
-    sz_batch_gen_run: a step runs every sequence's reads, mixers and head and ONE MoE sublayer a layer over the rows of all of them.
+    sz_batch_gen_run: a step runs every sequence's scan, attention and head, and the reads, projections and MoE sublayer of a layer
+    ONCE over the rows of all of them.
     N > 1: every GPU holds the whole model and B sequences of its own.  Timed: the steps' device time (events around each step) and
     the wall clock of the loop."""
     out = QuietStdout()
