@@ -760,9 +760,10 @@ static int sz_ffn(cudaStream_t st, int type, const SzPlan* plan, int groups, u64
 }
 
 
+struct SzXWindows { int n = 1; long long x = 0, gu = 0, d = 0; };   // plans in a row, one block row each: elements between the windows' inputs and sums
 template <int K, int NTC>
 static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const SzPlan* plan, const float* x, long long* acc_gu, long long* acc_d,
-                          u32* ctrl, bool sh, bool only_xw = false) {
+                          u32* ctrl, bool sh, bool only_xw = false, SzXWindows win = SzXWindows()) {
     static bool set = false;
     if (!set) {
         SZ_CUDA(cudaFuncSetAttribute(sz_x3_gateup_kernel<K, NTC>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzX3<K, NTC>::SMEM_BYTES));
@@ -789,7 +790,7 @@ static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const S
         if (!(tw == 1 || tw == 2 || tw == 4) || tw > NTC || NTC % tw) tw = NTC < 4 ? NTC : 4;
         if (tw == 3) tw = 1;
         if (!(twd == 1 || twd == 2 || twd == 4)) twd = 4;
-        const dim3 grid(occ * sz_sm_count());
+        const dim3 grid(occ * sz_sm_count(), win.n);
         int rc = SZ_E_TYPE;
 #define SZ_XW_GU(TT, OO)                                                                                                                    \
     if (tw == TT && occ == OO) {                                                                                                            \
@@ -797,7 +798,7 @@ static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const S
         if (!setv) { SZ_CUDA(cudaFuncSetAttribute(sz_xw_gateup_kernel<K, NTC, TT, OO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SzXW<K, TT, OO>::SMEM_BYTES)); setv = true; } \
         SZ_CUDA(sz_launch("gateup_exl3s", sz_xw_gateup_kernel<K, NTC, TT, OO>, grid, block, SzXW<K, TT, OO>::SMEM_BYTES, st, true, plan, (const u8*)L->gate, \
                           (u64)L->gate_stride, (const u8*)L->up, (u64)L->up_stride, (const u8*)(sh ? L->sh_gate : 0), (const u8*)(sh ? L->sh_up : 0), x, m, \
-                          (int)L->hidden, (int)L->top_k, acc_gu, ctrl));                                                                    \
+                          (int)L->hidden, (int)L->top_k, acc_gu, ctrl, win.x, win.gu));                                                     \
         rc = SZ_OK;                                                                                                                         \
     }
 #define SZ_XW_DN(TT, OO)                                                                                                                    \
@@ -807,7 +808,7 @@ static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const S
         SZ_CUDA(sz_launch("down_exl3s", sz_xw_down_kernel<K, TT, OO>, grid, block, SzXW<K, TT, OO>::SMEM_BYTES, st, true, plan, (const u8*)L->gate, (u64)L->gate_stride, \
                           (const u8*)L->up, (u64)L->up_stride, (const u8*)L->down, (u64)L->down_stride, (const u8*)(sh ? L->sh_gate : 0),   \
                           (const u8*)(sh ? L->sh_up : 0), (const u8*)(sh ? L->sh_down : 0), m, (int)L->hidden, (int)L->expert_ff, (int)L->top_k, \
-                          (const long long*)acc_gu, acc_d, ctrl));                                                                          \
+                          (const long long*)acc_gu, acc_d, ctrl, win.gu, win.d));                                                           \
         rc = SZ_OK;                                                                                                                         \
     }
         if constexpr (NTC % 4 == 0) { SZ_XW_GU(4, 2) SZ_XW_GU(4, 3) }
@@ -834,9 +835,9 @@ static int sz_x3_launch_k(cudaStream_t st, const sz_moe_layer* L, int m, const S
 }
 
 static int sz_x3_launch(cudaStream_t st, const sz_moe_layer* L, int m, const SzPlan* plan, const float* x, long long* acc_gu, long long* acc_d,
-                        u32* ctrl, bool sh, bool only_xw = false) {
+                        u32* ctrl, bool sh, bool only_xw = false, SzXWindows win = SzXWindows()) {
     const int K = L->expert_type - 1020, NTC = L->expert_ff / 128;
-#define SZ_X3_CASE(KK, NN) if (K == KK && NTC == NN) return sz_x3_launch_k<KK, NN>(st, L, m, plan, x, acc_gu, acc_d, ctrl, sh, only_xw);
+#define SZ_X3_CASE(KK, NN) if (K == KK && NTC == NN) return sz_x3_launch_k<KK, NN>(st, L, m, plan, x, acc_gu, acc_d, ctrl, sh, only_xw, win);
     SZ_X3_CASE(2, 1) SZ_X3_CASE(2, 2) SZ_X3_CASE(2, 4) SZ_X3_CASE(3, 1) SZ_X3_CASE(3, 2) SZ_X3_CASE(3, 4) SZ_X3_CASE(4, 1) SZ_X3_CASE(4, 2) SZ_X3_CASE(4, 4)
 #undef SZ_X3_CASE
     return sz_fail(SZ_E_TYPE, "no streaming EXL3 kernel for K = %d, FF = %d", K, L->expert_ff);
@@ -1086,14 +1087,22 @@ extern "C" int sz_moe_rows(const sz_moe_layer* L, uint64_t x, int rows, uint64_t
     SZ_CUDA(sz_launch("rows_zero", sz_rows_zero_kernel, dim3(SZ_ROWS_SLOTS, W), dim3(256), 0, st, true, (const SzRowsPlan*)P, acc_gu, (long long)S.gu_row, acc_d,
                       (long long)S.d_row));
     SZ_CUDA(sz_launch("rows_gather", sz_rows_gather_kernel, dim3(SZ_ROWS_SLOTS, W), dim3(256), 0, st, true, (const float*)x, H, (const SzRowsPlan*)P, xg));
-    // the experts, window by window (a window without groups costs a launch that returns at once); how many windows the routing
-    // needs is known on the device only, so all are launched
+    // the experts: every window a block row of one gate/up and one down launch (how many windows the routing needs is known on the
+    // device only: the blocks of a window without groups return at once).  SZ_ROWS_SERIAL=1: a launch pair a window, one after the
+    // other (the second form; same bits).
     const size_t win_plan = offsetof(SzRowsPlan, win);
-    for (int w = 0; w < SZ_ROWS_WIN; w++) {
-        const SzPlan* pw = (const SzPlan*)((u8*)P + win_plan + (size_t)w * sizeof(SzPlan));
-        if ((rc = sz_x3_launch(st, L, 8, pw, xg + (size_t)w * SZ_ROWS_SLOTS * H, acc_gu + (size_t)w * SZ_ROWS_SLOTS * S.gu_row,
-                               acc_d + (size_t)w * SZ_ROWS_SLOTS * S.d_row, ctrl_x, false, true)))
-            return rc;
+    const char* ser = getenv("SZ_ROWS_SERIAL");   // (read at every call: a test switches it inside one process)
+    if (ser && atoi(ser) != 0) {
+        for (int w = 0; w < SZ_ROWS_WIN; w++) {
+            const SzPlan* pw = (const SzPlan*)((u8*)P + win_plan + (size_t)w * sizeof(SzPlan));
+            if ((rc = sz_x3_launch(st, L, 8, pw, xg + (size_t)w * SZ_ROWS_SLOTS * H, acc_gu + (size_t)w * SZ_ROWS_SLOTS * S.gu_row,
+                                   acc_d + (size_t)w * SZ_ROWS_SLOTS * S.d_row, ctrl_x, false, true)))
+                return rc;
+        }
+    } else {
+        SzXWindows win;
+        win.n = SZ_ROWS_WIN; win.x = (long long)SZ_ROWS_SLOTS * H; win.gu = (long long)SZ_ROWS_SLOTS * S.gu_row; win.d = (long long)SZ_ROWS_SLOTS * S.d_row;
+        if ((rc = sz_x3_launch(st, L, 8, (const SzPlan*)((u8*)P + win_plan), xg, acc_gu, acc_d, ctrl_x, false, true, win))) return rc;
     }
     if (shared) {   // the shared expert as expert 0 of a layer of one
         sz_moe_layer Ls = *L;

@@ -221,9 +221,15 @@ template <int K, int NTC, int TW, int OCC>
 __global__ void __launch_bounds__(SZ_XW_THREADS, OCC)
 sz_xw_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, u64 gstride, const u8* __restrict__ up, u64 ustride,
                     const u8* __restrict__ sh_gate, const u8* __restrict__ sh_up, const float* __restrict__ x, int m, int H, int top_k,
-                    long long* __restrict__ acc, u32* __restrict__ ctrl) {
+                    long long* __restrict__ acc, u32* __restrict__ ctrl, long long win_x, long long win_acc) {
     using X = SzXW<K, TW, OCC>;
     constexpr int FF = 128 * NTC, S = X::STAGES, NCH = NTC / TW;
+    // grid.y > 1: block row w works on plan w of an array of plans, with its own inputs and sums (win_x, win_acc: elements from one
+    // window's to the next's); a window without groups is left at once
+    if (gridDim.y > 1) {
+        plan += blockIdx.y; x += blockIdx.y * win_x; acc += blockIdx.y * win_acc;
+        if (plan->n_groups == 0 && !sh_gate) return;
+    }
     static_assert(NTC % TW == 0, "column chunks tile the matrix");
     extern __shared__ __align__(128) u8 smem[];
     SzXWRing<K, TW, OCC> R;
@@ -327,9 +333,13 @@ __global__ void __launch_bounds__(SZ_XW_THREADS, OCC)
 sz_xw_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, u64 gstride, const u8* __restrict__ up, u64 ustride,
                   const u8* __restrict__ down, u64 dstride, const u8* __restrict__ sh_gate, const u8* __restrict__ sh_up,
                   const u8* __restrict__ sh_down, int m, int H, int FF, int top_k, const long long* __restrict__ acc,
-                  long long* __restrict__ out, u32* __restrict__ ctrl) {
+                  long long* __restrict__ out, u32* __restrict__ ctrl, long long win_acc, long long win_out) {
     using X = SzXW<K, TW, OCC>;
     constexpr int S = X::STAGES;
+    if (gridDim.y > 1) {   // (as the gate / up kernel)
+        plan += blockIdx.y; acc += blockIdx.y * win_acc; out += blockIdx.y * win_out;
+        if (plan->n_groups == 0 && !sh_down) return;
+    }
     extern __shared__ __align__(128) u8 smem[];
     SzXWRing<K, TW, OCC> R;
     R.init(smem);

@@ -2,13 +2,13 @@
 // rows, for up to SZ_ROWS_MAX, with every expert's matrices decoded ONCE for all the rows that chose it.  The role of the reference's
 // grouped experts of a long prompt (device planner plan_scan_w / plan_fill_w, kernels/forward.cu:3234-3319; mma_grouped*,
 // kernels/matvec.cu:1190-1260; EXL3 exl3_mma, kernels/exl3.cu:500-590) with this library's exact kernels: the expert kernels are
-// the verify pass's own (sz_xw_gateup_kernel, sz_xw_down_kernel), fed window by window.
+// the verify pass's own (sz_xw_gateup_kernel, sz_xw_down_kernel), a window a block row of their grids.
 //
 //   route     sz_route_kernel with a second grid dimension: 8 rows a block row, same arithmetic as a verify pass
 //   plan      sz_rows_plan_kernel: every expert's rows (ascending), cut into groups of up to 8 rows, groups packed into WINDOWS of at
 //             most 80 groups and 256 (row, rank) pairs - the sizes one SzPlan holds.  A pair's place is (window, slot).
 //   gather    sz_rows_gather_kernel: xg[window][slot] = the pair's input row (a window's rows are then indexed by a byte)
-//   experts   per window one gate/up and one down launch over the window's plan, input and accumulators
+//   experts   one gate/up and one down launch, block row w over window w's plan, input and accumulators
 //   shared    the shared expert as windows of their own: groups of 8 consecutive rows, expert 0 of a one-matrix "layer"
 //   combine   sz_rows_combine_kernel: per (row, 128 outputs) the ranks' terms in rank order, as sz_x3_combine_kernel adds them
 // A pair's numbers do not depend on which rows share its group (every row of a group is a column of its own in the tensor-core

@@ -34,6 +34,20 @@ def test_rows_at_once_equal_rows_of_verify_passes(hidden, n_expert, top_k, ff, r
     assert torch.equal(y.view(torch.int32), y2.view(torch.int32))
 
 
+def test_windows_as_block_rows_of_one_launch_equal_a_launch_pair_a_window(monkeypatch):
+    """The expert kernels take all windows of a call as block rows of one launch; SZ_ROWS_SERIAL=1 launches them one after the
+    other: the same bits, the same status."""
+    L = layer(2048, 512, 10, 512, 17)
+    ml = moe.MoeLayer(L, "cuda:0")
+    x = synth.normal((96, 2048), 1.0, 19, "rows.x3").cuda()
+    got = []
+    for flag in ("0", "1"):
+        monkeypatch.setenv("SZ_ROWS_SERIAL", flag)
+        got.append(ml.moe_rows(x).clone())
+        assert ml.moe_rows_status(96) == 0
+    assert torch.equal(got[0].view(torch.int32), got[1].view(torch.int32))
+
+
 def test_rows_at_once_against_the_cpu_restatement():
     hidden, n_expert, top_k, ff, rows = 512, 32, 4, 256, 24
     L = layer(hidden, n_expert, top_k, ff, 11)
