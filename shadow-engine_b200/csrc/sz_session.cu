@@ -693,11 +693,22 @@ static int sz_hc_read_rows(const sz_session* s, cudaStream_t st, const sz_hc& hc
     long long* acc_next = B.acc + ((n + 1) % 3) * B.acc_stride;
     int nt = ((int)c.hc_rank + C + 31) / 32 * 32;
     if (nt < 256) nt = 256;
-    SZ_CUDA(sz_launch("hc_down", sz_hc_down_kernel<8>, dim3(CH / 64, rows / 8), dim3(nt), 0, st, pdl, (const float*)rin, rout,
-                      (const long long*)(pending ? acc_prev : nullptr), (const float*)B.y, (const float*)hc.norm.data, (const u8*)hc.down.data,
-                      (const u8*)(inject ? hc.inject.data : 0), H, C, (int)c.hc_rank, c.eps, B.rn, acc, acc_next));
-    SZ_CUDA(sz_launch("hc_up", sz_hc_up_kernel<8>, dim3(H / 16, rows / 8), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data,
-                      (const float*)B.rn, H, C, (int)c.hc_rank, B.u));
+    // rows a block row: the kernels keep a row's data in registers, so fewer rows a block mean more blocks a multiprocessor (8 rows:
+    // 168 / 187 registers a thread, one block; 4: two; 2: two and four) and the number of waves stays what it is while a wave gets shorter
+    static const int per = [] { const char* e = getenv("SZ_BATCH_HC_ROWS"); const int v = e ? atoi(e) : 4; return v == 8 || v == 2 ? v : 4; }();
+    cudaError_t e1 = cudaErrorInvalidValue, e2 = cudaErrorInvalidValue;
+#define SZ_HC_ROWS(MM)                                                                                                                          \
+    if (per == MM) {                                                                                                                            \
+        e1 = sz_launch("hc_down", sz_hc_down_kernel<MM>, dim3(CH / 64, rows / MM), dim3(nt), 0, st, pdl, (const float*)rin, rout,               \
+                       (const long long*)(pending ? acc_prev : nullptr), (const float*)B.y, (const float*)hc.norm.data, (const u8*)hc.down.data, \
+                       (const u8*)(inject ? hc.inject.data : 0), H, C, (int)c.hc_rank, c.eps, B.rn, acc, acc_next);                             \
+        e2 = sz_launch("hc_up", sz_hc_up_kernel<MM>, dim3(H / 16, rows / MM), dim3(256), 0, st, true, (const long long*)acc,                    \
+                       (const u8*)hc.up.data, (const float*)B.rn, H, C, (int)c.hc_rank, B.u);                                                   \
+    }
+    SZ_HC_ROWS(8) SZ_HC_ROWS(4) SZ_HC_ROWS(2)
+#undef SZ_HC_ROWS
+    SZ_CUDA(e1);
+    SZ_CUDA(e2);
     return SZ_OK;
 }
 

@@ -159,8 +159,10 @@ sz_hc_down_body(const float* __restrict__ r_in, float* __restrict__ r_out, const
             yv[j][q] = on && g_acc ? __ldcg((const float4*)(y + (size_t)j * H) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
     }
-    if (blockIdx.x == 0)
-        for (int i = t; i < SZ_MAX_VERIFY * SZ_HC_ACC_ROWS; i += nt) acc_next[i] = 0;
+    if (blockIdx.x == 0) {   // (a block row of a grid over many rows clears its own rows only: its neighbours clear theirs)
+        const int clr = (gridDim.y > 1 ? M : SZ_MAX_VERIFY) * SZ_HC_ACC_ROWS;
+        for (int i = t; i < clr; i += nt) acc_next[i] = 0;
+    }
     if (t < M) gs[t] = g_acc ? 2.0f * sz_sigmoid((float)((double)graw * SZ_HC_FIX_INV) / (float)C) : 0.f;
     __syncthreads();
     SZ_PH();  // 2 gates
