@@ -891,6 +891,33 @@ def run_c5_batch(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    if args.profile_steps > 0:
+        # for a profiler: N steps of the B sequences with 1..4 rows each (no prompts, no timing); the last step sits between
+        # cudaProfilerStart and cudaProfilerStop, so `ncu --profile-from-start off` lists exactly its launches
+        for s in batch.sessions:
+            s.fill_synthetic(ctx - n_prompt, seed=3)
+        prompts = [md.make_prompt(n_prompt, cfg["vocab"], seed=1 + b, cycles=cyc) for b in range(B)]
+        at = [0] * B
+        rows_of = 0
+        for step in range(args.profile_steps):
+            ms = [1 + (b + step) % 4 for b in range(B)]
+            rows = [[int(t) for t in prompts[b][at[b]:at[b] + ms[b]]] for b in range(B)]
+            last = step == args.profile_steps - 1
+            torch.cuda.synchronize()
+            if last:
+                torch.cuda.profiler.start()
+            batch.verify(rows, accept=1)
+            torch.cuda.synchronize()
+            if last:
+                torch.cuda.profiler.stop()
+                rows_of = sum(ms)
+            for b, sess in enumerate(batch.sessions):
+                (keep, _), _, _ = sess.result()
+                sess.commit(keep)
+                at[b] += keep
+        out.emit(json.dumps({"profile_steps": args.profile_steps, "sequences": B, "rows_of_last_step": rows_of, "context": ctx, "n_layer": cfg["n_layer"]}))
+        return
+
     tot = dict(n=0, rounds=0, steps=0, drafted=0, accepted=0, dev_ms=0.0, wall_s=0.0)
     sampler = None
     for wave in range(-1, args.waves):     # wave -1: warm-up
@@ -1235,6 +1262,7 @@ def main():
                          "weak scaling, the throughput form), or experts sharded over the GPUs and ONE sequence (strong scaling: batch-1 "
                          "expert parallelism, which pays an exchange a layer and cannot scale)")
     ap.add_argument("--trace-rows", type=int, default=4, help="c3: rows of the pass whose launches are timed one by one (the line's `kernels`)")
+    ap.add_argument("--profile-steps", type=int, default=0, help="c5-batch: only run this many batched steps (the last one between cudaProfilerStart/Stop), no timing")
     ap.add_argument("--profile-passes", type=int, default=0, help="c3: only run this many 4-row verify passes (for ncu), no timing")
     ap.add_argument("--head", default="proxy", choices=["q8", "exl3", "proxy"],
                     help="c3: output.weight as Q8_0 read in full, as 4-bit EXL3 read in full, or EXL3 screened by its 2-bit proxy (Q2_P)")
