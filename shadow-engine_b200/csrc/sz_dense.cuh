@@ -418,8 +418,169 @@ static __global__ void __launch_bounds__(256, 2) sz_dense_q8_kernel(const SzDens
     if (failed && threadIdx.x == 0 && a.err) atomicExch(a.err, 1u);
 }
 
+// ---- Q8_0 projections over MANY rows (the rows of a batch of sequences), the arithmetic of sz_dense_q8_kernel --------------------------
+// What the kernel above computes for the (up to) 8 rows of a pass, for any multiple of 8 rows, with the matrices read once for all
+// of them instead of once per 8 rows.  A row's result is bit for bit the kernel above's: there a warp owns one eighth of the columns
+// (a "part") and runs, per 32-column block of its part in order, four MMAs into a fresh accumulator and one fused multiply-add with
+// the block's scale into the part's running sum; the eight parts' sums are then added in order.  Here the same chains run in
+// another place: a thread block owns ONE part, a range of row groups (8 rows each, as many as fit shared memory) and a range of
+// 16-row units of the matrices; it stages its part of the rows once (f16 high + low, as above) and streams the units' slices of
+// that part through a ring of shared-memory stages (cp.async, 8 units a stage, one a warp); a warp decodes a block's A fragments
+// once and uses them for every row group (the chains of the groups are independent accumulators).  The parts' sums go to
+// `partial` [8][rows][outputs] and sz_dense_rows_reduce_kernel adds them in order and applies the epilogue.
+// A slice of a matrix row starts at a multiple of 34 bytes, not of 16: the copy starts at the 16-byte boundary below it and the
+// reads skip the difference (the same for every row of a block, matrix rows being whole 16-byte chunks).
+struct SzDenseRowsCfg {
+    int units[SZ_DENSE_MAX_JOBS + 1];   // 16-row units before each job
+    int upc;          // units a block takes (a multiple of 8)
+    int G, nz, gb;    // row groups in all, blocks along the rows, row groups a block at most
+    int sb;           // bytes of a matrix row's slice of one part
+    int rs;           // bytes between the staged slices
+    int xs;           // halves between the staged rows
+    int rows;         // rows in all (8 G)
+    float* partial;
+};
+
+__device__ __forceinline__ void sz_cp_async16(void* smem_dst, const void* src) {
+    const u32 d = (u32)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void sz_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void sz_cp_async_wait1() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+// grid (8 parts, unit chunks, row blocks); block 256; dynamic shared memory gb * 8 * xs * 4 + 2 * 128 * rs
+template <int GB>
+static __global__ void __launch_bounds__(256) sz_dense_rows_q8_kernel(const SzDenseArgs a, const SzDenseRowsCfg c) {
+    extern __shared__ __align__(128) u8 smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, q = lane & 3;
+    const int p = blockIdx.x;
+    const int part = a.cols / 8, nblk = part / 32;
+    const int g0 = (int)((long long)c.G * blockIdx.z / c.nz), g1 = (int)((long long)c.G * (blockIdx.z + 1) / c.nz);
+    const int ng = g1 - g0;                       // <= GB
+    const int total = c.units[a.n_jobs];
+    const int u0 = blockIdx.y * c.upc, u1 = min(total, u0 + c.upc);
+    if (ng <= 0 || u0 >= u1) return;
+    __half* xhi = (__half*)smem;                  // [GB * 8][xs]
+    __half* xlo = xhi + (size_t)GB * 8 * c.xs;
+    u8* stages = smem + (size_t)GB * 8 * c.xs * 4;
+    const size_t stage_bytes = (size_t)128 * c.rs;
+    const size_t rb = (size_t)(a.cols / 32) * 34;
+    const int s_off = (p * c.sb) & 15;
+    const int chunks = (s_off + c.sb + 15) >> 4;
+    const int nstage = (u1 - u0 + 7) >> 3;
+    auto locate = [&](int u, int& ji, int& row0, int& nrows) {
+        ji = 0;
+#pragma unroll
+        for (int t = 1; t < SZ_DENSE_MAX_JOBS; t++)
+            if (t < a.n_jobs && u >= c.units[t]) ji = t;
+        row0 = (u - c.units[ji]) * 16;
+        nrows = min(16, a.job[ji].rows - row0);
+    };
+    // two threads a staged row: thread t copies the chunks t & 1, (t & 1) + 2, ... of row t >> 1 of the stage
+    auto issue = [&](int si) {
+        const int r = threadIdx.x >> 1;
+        const int u = u0 + 8 * si + (r >> 4);
+        if (u < u1) {
+            int ji, row0, nrows;
+            locate(u, ji, row0, nrows);
+            const int rr = (r & 15) < nrows ? (r & 15) : 0;   // (a unit's missing rows: its first row again; nothing of them is kept)
+            const u8* src = a.job[ji].w + (size_t)(row0 + rr) * rb + (size_t)p * c.sb - s_off;
+            u8* dst = stages + (size_t)(si & 1) * stage_bytes + (size_t)r * c.rs;
+            for (int ch = threadIdx.x & 1; ch < chunks; ch += 2) sz_cp_async16(dst + ch * 16, src + ch * 16);
+        }
+        sz_cp_async_commit();
+    };
+    issue(0);   // (the matrices are constants: their first stage is on its way before the kernel waits for its inputs)
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    for (int i = threadIdx.x; i < ng * 8 * (part / 4); i += 256) {
+        const int j = i / (part / 4), c4 = i - j * (part / 4);
+        const float4 v = __ldcg((const float4*)(a.x + (size_t)(g0 * 8 + j) * a.xstride + (size_t)p * part) + c4);
+        const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+        const __half2 l0 = __floats2half2_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2half2_rn(v.z - f1.x, v.w - f1.y);
+        *(uint2*)(xhi + (size_t)j * c.xs + 4 * c4) = make_uint2(*(const u32*)&h0, *(const u32*)&h1);
+        *(uint2*)(xlo + (size_t)j * c.xs + 4 * c4) = make_uint2(*(const u32*)&l0, *(const u32*)&l1);
+    }
+    for (int si = 0; si < nstage; si++) {
+        if (si + 1 < nstage) issue(si + 1); else sz_cp_async_commit();
+        sz_cp_async_wait1();          // this thread's copies of stage si have landed ...
+        __syncthreads();              // ... and everybody's (and, the first time, the rows)
+        const int u = u0 + 8 * si + warp;
+        if (u < u1) {
+            int ji, row0, nrows;
+            locate(u, ji, row0, nrows);
+            const SzDenseJob& jb = a.job[ji];
+            const u8* st = stages + (size_t)(si & 1) * stage_bytes + (size_t)(warp * 16) * c.rs + s_off;
+            const u8* r0 = st + (size_t)(g < nrows ? g : 0) * c.rs;
+            const u8* r1 = st + (size_t)(g + 8 < nrows ? g + 8 : 0) * c.rs;
+            float acc[GB][4];
+#pragma unroll
+            for (int gi = 0; gi < GB; gi++) { acc[gi][0] = 0.f; acc[gi][1] = 0.f; acc[gi][2] = 0.f; acc[gi][3] = 0.f; }
+            for (int b = 0; b < nblk; b++) {
+                const int col = b * 32 + 8 * q;
+                const u8* p0 = r0 + (size_t)b * 34;
+                const u8* p1 = r1 + (size_t)b * 34;
+                const float d0 = sz_f16_to_f32(*(const u16*)p0), d1 = sz_f16_to_f32(*(const u16*)p1);
+                const u16* c0 = (const u16*)(p0 + 2 + 8 * q);
+                const u16* c1 = (const u16*)(p1 + 2 + 8 * q);
+                u32 a1[4], a2[4];
+                a1[0] = sz_q8_pair(c0[0]); a1[2] = sz_q8_pair(c0[1]); a2[0] = sz_q8_pair(c0[2]); a2[2] = sz_q8_pair(c0[3]);
+                a1[1] = sz_q8_pair(c1[0]); a1[3] = sz_q8_pair(c1[1]); a2[1] = sz_q8_pair(c1[2]); a2[3] = sz_q8_pair(c1[3]);
+#pragma unroll
+                for (int gi = 0; gi < GB; gi++) {
+                    if (gi < ng) {
+                        const uint4 bh = *(const uint4*)(xhi + (size_t)(gi * 8 + g) * c.xs + col);
+                        const uint4 bl = *(const uint4*)(xlo + (size_t)(gi * 8 + g) * c.xs + col);
+                        float t[4] = {0.f, 0.f, 0.f, 0.f};
+                        sz_mma16816_z(t, a1, bh.x, bh.y);
+                        sz_mma16816_z(t, a2, bh.z, bh.w);
+                        sz_mma16816_z(t, a1, bl.x, bl.y);
+                        sz_mma16816_z(t, a2, bl.z, bl.w);
+                        acc[gi][0] = fmaf(d0, t[0], acc[gi][0]); acc[gi][1] = fmaf(d0, t[1], acc[gi][1]);
+                        acc[gi][2] = fmaf(d1, t[2], acc[gi][2]); acc[gi][3] = fmaf(d1, t[3], acc[gi][3]);
+                    }
+                }
+            }
+            const size_t T = (size_t)a.total_rows;
+            const size_t o = (size_t)jb.row0 + row0 + g;
+#pragma unroll
+            for (int gi = 0; gi < GB; gi++) {
+                if (gi < ng) {
+                    float* P = c.partial + ((size_t)p * c.rows + (size_t)(g0 + gi) * 8 + 2 * q) * T + o;
+                    if (g < nrows) { P[0] = acc[gi][0]; P[T] = acc[gi][1]; }
+                    if (g + 8 < nrows) { P[8] = acc[gi][2]; P[T + 8] = acc[gi][3]; }
+                }
+            }
+        }
+        __syncthreads();              // the stage is free for the copies of stage si + 2
+    }
+}
+
+// grid (ceil(outputs / 256), rows); block 256: the eight parts' sums in order, the epilogue, the job's output
+static __global__ void __launch_bounds__(256) sz_dense_rows_reduce_kernel(const SzDenseArgs a, const float* __restrict__ partial, int rows) {
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int o = blockIdx.x * 256 + threadIdx.x, row = blockIdx.y;
+    if (o >= a.total_rows) return;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) v += __ldcg(partial + ((size_t)w * rows + row) * a.total_rows + o);
+    int ji = 0;
+#pragma unroll
+    for (int t = 1; t < SZ_DENSE_MAX_JOBS; t++)
+        if (t < a.n_jobs && o >= a.job[t].row0) ji = t;
+    const SzDenseJob& jb = a.job[ji];
+    jb.out[(size_t)row * jb.ostride + (o - jb.row0)] = sz_epilogue(jb.epi, v, jb.div);
+}
+
 #endif  // __CUDACC__
 
 // host: launches the jobs of `a` (row0 / total_rows are filled here)
 int sz_dense_launch(SzDenseArgs& a, cudaStream_t st, const char* name);
+// a.m rows, a multiple of 8 (any number of them), through the many-row form of the Q8_0 tensor-pipe kernel when sz_dense_launch would
+// take that kernel for 8 rows of these jobs: *taken = 1 and the rows are computed (bit for bit as 8 at a time); otherwise *taken = 0
+// and nothing is launched.  partial: a.m * total rows * 8 floats of scratch.
+int sz_dense_rows_launch(SzDenseArgs& a, float* partial, int64_t partial_floats, cudaStream_t st, const char* name, int* taken);
 int sz_dense_check(const sz_tensor* t, const char* what, int64_t rows, int64_t cols);

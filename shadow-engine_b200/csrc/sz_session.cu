@@ -588,6 +588,78 @@ int sz_dense_launch(SzDenseArgs& a, cudaStream_t st, const char* name) {
     return SZ_OK;
 }
 
+// Would sz_dense_launch take the Q8_0 tensor-pipe kernel for 8 rows of these jobs (whole, or as two launches of 4)?  Then it takes
+// it for every row count up to 8, and the many-row form computes the same bits.
+static bool sz_dense_q8_takes(const SzDenseArgs& a) {
+    static const bool generic_only = getenv("SZ_GENERIC_KERNELS") && atoi(getenv("SZ_GENERIC_KERNELS")) != 0;
+    if (generic_only || a.n_jobs < 1) return false;
+    for (int i = 0; i < a.n_jobs; i++) if (a.job[i].type != SZ_TYPE_Q8_0) return false;
+    const size_t rb = sz_row_bytes_host(SZ_TYPE_Q8_0, a.cols);
+    if (a.cols % 256 || rb % 16 || rb > 96 * 1024) return false;
+    int rbp = (int)rb;
+    while (((rbp / 4) % 32) % 8 != 4) rbp += 16;
+    int xsp = a.cols;
+    while (((xsp / 2) % 32) != 16) xsp += 8;
+    const size_t two = 2 * (size_t)16 * rbp;
+    for (int m : {8, 4}) {
+        const size_t fixed = 64 + 4096 + (size_t)m * xsp * 4;
+        if (fixed + two <= 110 * 1024 || fixed + two <= 216 * 1024) return true;
+    }
+    return false;
+}
+
+int sz_dense_rows_launch(SzDenseArgs& a, float* partial, int64_t partial_floats, cudaStream_t st, const char* name, int* taken) {
+    *taken = 0;
+    if (a.m < 8 || a.m % 8 || !sz_dense_q8_takes(a)) return SZ_OK;
+    int total = 0;
+    for (int i = 0; i < a.n_jobs; i++) { a.job[i].row0 = total; total += a.job[i].rows; }
+    a.total_rows = total;
+    if ((int64_t)8 * a.m * total > partial_floats) return SZ_OK;
+    SzDenseRowsCfg c = {};
+    int units = 0;
+    for (int i = 0; i < a.n_jobs; i++) { c.units[i] = units; units += (a.job[i].rows + 15) / 16; }
+    c.units[a.n_jobs] = units;
+    const int part = a.cols / 8;
+    c.sb = part / 32 * 34;
+    int rs = 0;
+    for (int p = 0; p < 8; p++) { const int need = ((((p * c.sb) & 15) + c.sb + 15) >> 4) << 4; rs = need > rs ? need : rs; }
+    while (((rs / 4) % 32) % 8 != 4) rs += 16;     // staged slices 4 (mod 8) words apart, rows of the pass 16 words, as the 8-row kernel
+    int xs = part;
+    while (((xs / 2) % 32) != 16) xs += 8;
+    c.rs = rs; c.xs = xs; c.rows = a.m; c.G = a.m / 8; c.partial = partial;
+    // row groups a block: what fits beside the two stages, two blocks a multiprocessor where four groups do
+    const size_t stages = 2 * (size_t)128 * rs, group = (size_t)8 * xs * 4;
+    int gb = 0;
+    if (stages + 4 * group <= 110 * 1024) gb = 4;
+    else if (c.G >= 8 && stages + 8 * group <= 216 * 1024) gb = 8;
+    else if (stages + 4 * group <= 216 * 1024) gb = 4;
+    else if (stages + 2 * group <= 216 * 1024) gb = 2;
+    else return SZ_OK;
+    if (c.G <= 2) gb = 2;
+    c.gb = gb;
+    c.nz = (c.G + gb - 1) / gb;
+    const size_t smem = stages + (size_t)gb * group;
+    const int target = sz_sm_count_session() * (smem <= 110 * 1024 ? 2 : 1);
+    int nc = target / (8 * c.nz);
+    if (nc < 1) nc = 1;
+    c.upc = ((units + nc - 1) / nc + 7) / 8 * 8;
+    nc = (units + c.upc - 1) / c.upc;
+    const dim3 grid(8, nc, c.nz);
+    cudaError_t e = cudaErrorInvalidValue;
+#define SZ_DR(GG)                                                                                                                            \
+    if (gb == GG) {                                                                                                                          \
+        static bool set = false;                                                                                                             \
+        if (!set) { SZ_CUDA(cudaFuncSetAttribute(sz_dense_rows_q8_kernel<GG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024)); set = true; } \
+        e = sz_launch(name, sz_dense_rows_q8_kernel<GG>, grid, dim3(256), smem, st, true, a, c);                                             \
+    }
+    SZ_DR(2) SZ_DR(4) SZ_DR(8)
+#undef SZ_DR
+    SZ_CUDA(e);
+    SZ_CUDA(sz_launch("dense_rows_reduce", sz_dense_rows_reduce_kernel, dim3((total + 255) / 256, a.m), dim3(256), 0, st, true, a, (const float*)partial, a.m));
+    *taken = 1;
+    return SZ_OK;
+}
+
 static SzDenseJob sz_job(const sz_tensor& t, float* out, int ostride, int epi = SZ_EPI_NONE, float div = 1.f) {
     SzDenseJob j;
     j.w = (const u8*)t.data; j.out = out; j.rows = (int)t.rows; j.type = t.type; j.ostride = ostride; j.epi = epi; j.div = div; j.row0 = 0;
@@ -1421,7 +1493,7 @@ sz_batch_move_kernel(const SzBatchTab* __restrict__ T, float* const* __restrict_
 }
 
 enum { SZ_BATCH_SLOTS = SZ_DENSE_MAX_JOBS + 1 };   // per layer: the outputs of the input projections, then the input of the output projection
-struct SzBatchScratch { int64_t tab, ptrs, ptrs_bytes, x, y, r, r2, rn, acc, in, in_row, core, core_row, moe, moe_bytes, total; };
+struct SzBatchScratch { int64_t tab, ptrs, ptrs_bytes, x, y, r, r2, rn, acc, in, in_row, core, core_row, partial, partial_floats, moe, moe_bytes, total; };
 static int sz_batch_layout(const sz_model* m, int rows_max, SzBatchScratch* S) {
     if (!m || !m->layers) return sz_fail(SZ_E_ARG, "null model");
     if (rows_max < 8 || rows_max % 8) return sz_fail(SZ_E_ARG, "sz_batch: rows_max = %d (a multiple of 8)", rows_max);
@@ -1446,6 +1518,9 @@ static int sz_batch_layout(const sz_model* m, int rows_max, SzBatchScratch* S) {
     S->core_row = vd > (int64_t)c.n_head * c.head_dim ? vd : (int64_t)c.n_head * c.head_dim;
     S->in = o; o = up256(o + 4 * rows_max * S->in_row);
     S->core = o; o = up256(o + 4 * rows_max * S->core_row);
+    // the many-row projection kernel's sums of the eight column parts, for the widest set of projections
+    S->partial_floats = 8 * (int64_t)rows_max * (S->in_row > c.hidden ? S->in_row : c.hidden);
+    S->partial = o; o = up256(o + 4 * S->partial_floats);
     for (int l = 0; l < c.n_layer; l++) {
         int64_t b = 0;
         const int rc = sz_moe_rows_scratch_bytes(&m->layers[l].moe, rows_max, &b);
@@ -1543,6 +1618,9 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
         }
     } repoint;
     float* const* ptrs = (float* const*)(base + S.ptrs);
+    float* PART = (float*)(base + S.partial);
+    const char* re = getenv("SZ_BATCH_DENSE_ROWS");   // 0: the projections 8 rows a launch (the second form; same bits)
+    const bool rows_form = !(re && atoi(re) == 0);
     if (shared) {
         repoint.ss = ss;
         for (int b = 0; b < n; b++) {
@@ -1642,11 +1720,18 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
             long long at_in = 0;
             for (int k = 0; k < a.n_jobs; k++) { mi.off[k] = at_in; mi.width[k] = a.job[k].ostride; at_in += (long long)Rp * a.job[k].ostride; }
             mo.off[0] = 0; mo.width[0] = o.cols;
-            for (int g = 0; g < Rp / 8; g++) {
-                SzDenseArgs ag = a;
-                ag.x = X + (size_t)g * 8 * c.hidden;
-                for (int k = 0; k < a.n_jobs; k++) ag.job[k].out = IN + mi.off[k] + (size_t)g * 8 * mi.width[k];
-                if ((rc = sz_dense_launch(ag, st, "batch_proj"))) return rc;
+            {   // all rows through one launch where the many-row form of the kernel exists, else 8 rows a launch
+                SzDenseArgs ar = a;
+                ar.m = Rp; ar.x = X;
+                for (int k = 0; k < a.n_jobs; k++) ar.job[k].out = IN + mi.off[k];
+                int taken = 0;
+                if (rows_form && (rc = sz_dense_rows_launch(ar, PART, S.partial_floats, st, "batch_proj", &taken))) return rc;
+                for (int g = 0; g < Rp / 8 && !taken; g++) {
+                    SzDenseArgs ag = a;
+                    ag.x = X + (size_t)g * 8 * c.hidden;
+                    for (int k = 0; k < a.n_jobs; k++) ag.job[k].out = IN + mi.off[k] + (size_t)g * 8 * mi.width[k];
+                    if ((rc = sz_dense_launch(ag, st, "batch_proj"))) return rc;
+                }
             }
             SZ_CUDA(sz_launch("batch_move", sz_batch_move_kernel, dim3(R, a.n_jobs), dim3(256), 0, st, true, T, lp, mi, IN, 1));
             if ((rc = fork())) return rc;
@@ -1656,11 +1741,17 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
                 return rc;
             if ((rc = join())) return rc;
             SZ_CUDA(sz_launch("batch_move", sz_batch_move_kernel, dim3(R, 1), dim3(256), 0, st, !multi, T, lp + (size_t)SZ_DENSE_MAX_JOBS * SZ_BATCH_MAX, mo, CORE, 0));
-            for (int g = 0; g < Rp / 8; g++) {
-                SzDenseArgs og = o;
-                og.x = CORE + (size_t)g * 8 * o.cols;
-                og.job[0].out = Y + (size_t)g * 8 * c.hidden;
-                if ((rc = sz_dense_launch(og, st, "batch_out"))) return rc;
+            {
+                SzDenseArgs orr = o;
+                orr.m = Rp; orr.x = CORE; orr.job[0].out = Y;
+                int taken = 0;
+                if (rows_form && (rc = sz_dense_rows_launch(orr, PART, S.partial_floats, st, "batch_out", &taken))) return rc;
+                for (int g = 0; g < Rp / 8 && !taken; g++) {
+                    SzDenseArgs og = o;
+                    og.x = CORE + (size_t)g * 8 * o.cols;
+                    og.job[0].out = Y + (size_t)g * 8 * c.hidden;
+                    if ((rc = sz_dense_launch(og, st, "batch_out"))) return rc;
+                }
             }
             if ((rc = read_rows(L.hc_ffn, true, true, true))) return rc;
             if ((rc = sz_moe_rows(&L.moe, (uint64_t)X, Rp, (uint64_t)Y, 0, 0, scratch + S.moe, S.moe_bytes, stream))) return rc;

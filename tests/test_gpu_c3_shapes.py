@@ -160,6 +160,36 @@ def test_batched_rows_equal_one_at_a_time(c3):
     assert np.array_equal(rest.view(np.uint32), rest_c.view(np.uint32))
 
 
+def test_a_batched_step_at_the_benchmark_shapes_equals_the_sequences_own_passes(c3, monkeypatch):
+    """Five sequences of ragged row counts through sz_batch_verify at config 3's layer shapes (projections of 2,048 and 4,096
+    columns through the many-row form of the Q8_0 kernel, reads and MoE over all rows): bit for bit each sequence's own pass;
+    and the same with the projections 8 rows a launch."""
+    M, hm, dm = c3
+    rng = np.random.default_rng(21)
+    seqs = [[int(t) for t in rng.integers(0, C3_SLICE["vocab"], 16)] for _ in range(5)]
+    alone = [md.Session(dm, 32, kv_q8=True) for _ in range(5)]
+    want = []
+    plan = [(4, 1, 8, 3, 2), (1, 4, 2, 8, 4)]
+    at = [0] * 5
+    for ms in plan:
+        for b in range(5):
+            alone[b].verify(seqs[b][at[b]:at[b] + ms[b]]); want.append(alone[b].result(logits=True)[2].view(np.uint32).copy()); alone[b].commit(ms[b])
+            at[b] += ms[b]
+    for flag in ("1", "0"):
+        monkeypatch.setenv("SZ_BATCH_DENSE_ROWS", flag)
+        batch = md.Batch(dm, 5, 32)
+        at = [0] * 5
+        k = 0
+        for ms in plan:
+            batch.verify([seqs[b][at[b]:at[b] + ms[b]] for b in range(5)])
+            for b in range(5):
+                got = batch.sessions[b].result(logits=True)[2].view(np.uint32)
+                batch.sessions[b].commit(ms[b])
+                assert np.array_equal(got, want[k]), "rows form %s, sequence %d" % (flag, b)
+                k += 1
+                at[b] += ms[b]
+
+
 @pytest.mark.parametrize("length", [700, 5000])
 def test_long_context_pass_matches_the_cpu_steps(c3, length):
     """Attention over thousands of cached positions: both sides start from the same seeded cache (the library's synthetic history,
