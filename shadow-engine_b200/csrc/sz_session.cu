@@ -769,6 +769,21 @@ static int sz_hc_read_rows(const sz_session* s, cudaStream_t st, const sz_hc& hc
     // 168 / 187 registers a thread, one block; 4: two; 2: two and four) and the number of waves stays what it is while a wave gets shorter
     static const int per = [] { const char* e = getenv("SZ_BATCH_HC_ROWS"); const int v = e ? atoi(e) : 4; return v == 8 || v == 2 ? v : 4; }();
     cudaError_t e1 = cudaErrorInvalidValue, e2 = cudaErrorInvalidValue;
+    // The first half in its many-row form: the norm once a (row, stream), then the products (SZ_BATCH_HC_SPLIT=0: the pass's own
+    // kernel with a block row per `per` rows, where every block of a stream redoes the stream's norm; same bits).
+    const char* sp = getenv("SZ_BATCH_HC_SPLIT");   // (read at every call: a test switches it inside one process)
+    if (!(sp && atoi(sp) == 0)) {
+        SZ_CUDA(sz_launch("hc_rows_norm", sz_hc_rows_norm_kernel, dim3(C, rows), dim3(nt), 0, st, pdl, (const float*)rin, rout,
+                          (const long long*)(pending ? acc_prev : nullptr), (const float*)B.y, (const float*)hc.norm.data, H, C, (int)c.hc_rank, c.eps,
+                          B.rn, acc_next));
+        SZ_CUDA(sz_launch("hc_rows_down", sz_hc_rows_down_kernel<8>, dim3(CH / 64, rows / 8), dim3(nt), 0, st, true, (const float*)B.rn,
+                          (const u8*)hc.down.data, (const u8*)(inject ? hc.inject.data : 0), H, C, (int)c.hc_rank, acc));
+        if (per == 8) e2 = sz_launch("hc_up", sz_hc_up_kernel<8>, dim3(H / 16, rows / 8), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data, (const float*)B.rn, H, C, (int)c.hc_rank, B.u);
+        else if (per == 2) e2 = sz_launch("hc_up", sz_hc_up_kernel<2>, dim3(H / 16, rows / 2), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data, (const float*)B.rn, H, C, (int)c.hc_rank, B.u);
+        else e2 = sz_launch("hc_up", sz_hc_up_kernel<4>, dim3(H / 16, rows / 4), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data, (const float*)B.rn, H, C, (int)c.hc_rank, B.u);
+        SZ_CUDA(e2);
+        return SZ_OK;
+    }
 #define SZ_HC_ROWS(MM)                                                                                                                          \
     if (per == MM) {                                                                                                                            \
         e1 = sz_launch("hc_down", sz_hc_down_kernel<MM>, dim3(CH / 64, rows / MM), dim3(nt), 0, st, pdl, (const float*)rin, rout,               \
@@ -1990,6 +2005,7 @@ struct SzKernelEntry {
 const SzKernelEntry kKernels[] = {
     {"sz_embed_kernel", (const void*)sz_embed_kernel, 7, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
     {"sz_hc_norm_kernel", (const void*)sz_hc_norm_kernel, 8, {SZ_P_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_F32, SZ_P_PTR}},
+    {"sz_hc_rows_norm_kernel", (const void*)sz_hc_rows_norm_kernel, 11, {SZ_P_CONST_PTR, SZ_P_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_F32, SZ_P_PTR, SZ_P_PTR}},
     {"sz_hc_mix_kernel", (const void*)sz_hc_mix_kernel, 5, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_PTR}},
     {"sz_delta_prep_kernel", (const void*)sz_delta_prep_kernel, 16, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_PTR, SZ_P_PTR}},
     {"sz_conv_commit_kernel", (const void*)sz_conv_commit_kernel, 10, {SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_CONST_PTR, SZ_P_I32, SZ_P_I32, SZ_P_PTR, SZ_P_PTR, SZ_P_I32}},

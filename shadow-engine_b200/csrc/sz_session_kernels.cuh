@@ -253,6 +253,121 @@ sz_hc_down_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, con
                        rn + g * C * H, acc + g * SZ_HC_ACC_ROWS, acc_next + g * SZ_HC_ACC_ROWS, wrow, w);
 }
 
+// ---- the first half of the read over MANY rows (a batch of sequences) ------------------------------------------------------------------
+// sz_hc_down_kernel makes every one of a stream's H / 64 blocks load the whole stream of its rows and sum its squares - nothing
+// for the few rows of a pass, 32 times the work when a launch carries the rows of many sequences.  Here that part runs once a
+// (row, stream) - sz_hc_rows_norm_kernel: the pending write, the sum of squares in the very order of the kernel above (the same
+// block size, the same float4 a thread, warp sums, then the warps in order), the new residual and rn - and sz_hc_rows_down_kernel
+// only multiplies: a block's 64 columns of rn for 8 rows, the thread's 64 weights, the same chain of multiply-adds, the same
+// fixed-point sums.  Bit for bit the kernel above's results.
+// grid (streams, rows); block: as sz_hc_down_kernel's (the order of the sum of squares depends on it)
+__global__ void __launch_bounds__(320)
+sz_hc_rows_norm_kernel(const float* __restrict__ r_in, float* __restrict__ r_out, const long long* __restrict__ g_acc, const float* __restrict__ y,
+                       const float* __restrict__ normw, int H, int C, int rank, float eps, float* __restrict__ rn, long long* __restrict__ acc_next) {
+    __shared__ double red[10];
+    __shared__ float rinv_s, gs_s;
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int t = threadIdx.x, warp = t >> 5, lane = t & 31, nt = blockDim.x;
+    const int s = blockIdx.x, row = blockIdx.y;
+    constexpr int NV = 2;
+    float4 rv[NV], yv[NV];
+#pragma unroll
+    for (int q = 0; q < NV; q++) {
+        const int i = t + q * nt;
+        const bool on = i < H / 4;
+        rv[q] = on ? __ldcg((const float4*)(r_in + ((size_t)row * C + s) * H) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        yv[q] = on && g_acc ? __ldcg((const float4*)(y + (size_t)row * H) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (s == 0)
+        for (int i = t; i < SZ_HC_ACC_ROWS; i += nt) acc_next[(size_t)row * SZ_HC_ACC_ROWS + i] = 0;
+    if (t == 0) {
+        const long long graw = g_acc ? __ldcg(g_acc + (size_t)row * SZ_HC_ACC_ROWS + rank + s) : 0;
+        gs_s = g_acc ? 2.0f * sz_sigmoid((float)((double)graw * SZ_HC_FIX_INV) / (float)C) : 0.f;
+    }
+    __syncthreads();
+    const float g = gs_s;
+    double ss = 0.0;
+#pragma unroll
+    for (int q = 0; q < NV; q++) {
+        float4 v = rv[q];
+        const float4 w4 = yv[q];
+        v.x = v.x + g * w4.x; v.y = v.y + g * w4.y; v.z = v.z + g * w4.z; v.w = v.w + g * w4.w;
+        ss += (double)v.x * (double)v.x;
+        ss += (double)v.y * (double)v.y;
+        ss += (double)v.z * (double)v.z;
+        ss += (double)v.w * (double)v.w;
+        rv[q] = v;
+    }
+    ss = sz_warp_sum(ss);
+    if (lane == 0) red[warp] = ss;
+    __syncthreads();
+    if (t == 0) {
+        double v = 0.0;
+        for (int q = 0; q < (nt >> 5); q++) v += red[q];
+        rinv_s = (float)sz_rsqrt64(v / (double)H + (double)eps);
+    }
+    __syncthreads();
+    const float rinv = rinv_s;
+#pragma unroll
+    for (int q = 0; q < NV; q++) {
+        const int i = t + q * nt;
+        if (i < H / 4) {
+            const size_t at = ((size_t)row * C + s) * H + 4 * (size_t)i;
+            const float4 v = rv[q];
+            const float4 nw = __ldg((const float4*)(normw + (size_t)s * H) + i);
+            float4 x;
+            x.x = (float)((double)v.x * (double)rinv) * nw.x;
+            x.y = (float)((double)v.y * (double)rinv) * nw.y;
+            x.z = (float)((double)v.z * (double)rinv) * nw.z;
+            x.w = (float)((double)v.w * (double)rinv) * nw.w;
+            *(float4*)(r_out + at) = v;
+            *(float4*)(rn + at) = x;
+        }
+    }
+}
+
+// grid (C * H / 64, rows / M); block: as sz_hc_down_kernel's (one thread a row of the down / inject matrices)
+template <int M>
+__global__ void __launch_bounds__(320)
+sz_hc_rows_down_kernel(const float* __restrict__ rn, const u8* __restrict__ down, const u8* __restrict__ inject, int H, int C, int rank,
+                       long long* __restrict__ acc) {
+    __shared__ __align__(16) float xs[M][64];
+    uint4 w[8];
+    const u8* wrow = sz_hc_down_fetch(down, inject, H, C, rank, w);
+    sz_pdl_wait();
+    sz_pdl_trigger();
+    const int t = threadIdx.x, nt = blockDim.x, CH = C * H, c0 = blockIdx.x * 64;
+    const size_t g = (size_t)blockIdx.y * M;
+    for (int idx = t; idx < M * 64; idx += nt) {
+        const int j = idx >> 6, c = idx & 63;
+        xs[j][c] = __ldcg(rn + (g + j) * CH + c0 + c);
+    }
+    __syncthreads();
+    if (wrow != nullptr) {
+        float a[M];
+#pragma unroll
+        for (int j = 0; j < M; j++) a[j] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const u32 ww[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float w0 = __uint_as_float(ww[q] << 16), w1 = __uint_as_float(ww[q] & 0xffff0000u);
+#pragma unroll
+                for (int j = 0; j < M; j++) {
+                    const float2 xv = *(const float2*)&xs[j][8 * i + 2 * q];
+                    a[j] = fmaf(w0, xv.x, a[j]);
+                    a[j] = fmaf(w1, xv.y, a[j]);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < M; j++)
+            atomicAdd((unsigned long long*)(acc + (g + j) * SZ_HC_ACC_ROWS + t), (unsigned long long)__double2ll_rn((double)a[j] * SZ_HC_FIX));
+    }
+}
+
 // grid H / 16, block 256.  CPR = rank / 8: 16-byte pieces a row of the up matrix.
 // the block's rows of the up matrix, one 16-byte piece a thread and slot: constant data, requested before the dependency wait
 // (threads 256 and up of a wider block hold none)
