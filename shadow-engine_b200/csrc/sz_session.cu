@@ -824,6 +824,47 @@ static int sz_scan(sz_session* s, cudaStream_t st, int l, int m, const SzDeltaPr
     return sz_scan_launch<64, 1>(s, st, l, m, pp);
 }
 
+// One sequence's entry of the table the many-sequence scan reads: what sz_delta_layer hands the scan of layer l, fused front end.
+static void sz_scan_seq_entry(sz_session* s, int l, int m, SzScanSeq* e) {
+    const sz_model_config& c = s->model.cfg;
+    const sz_layer& L = s->layers[l];
+    const int di = s->lb[l].delta_index;
+    const int vh = c.ssm_v_heads, kh = c.ssm_k_heads, d = c.ssm_head_dim;
+    const int64_t kd = (int64_t)kh * d, vd = (int64_t)vh * d, ch = 2 * kd + vd;
+    const int64_t Sl = (int64_t)vh * d * d, cl = (int64_t)(c.conv_k - 1) * ch;
+    *e = SzScanSeq{};
+    e->xc = s->d_xc + (int64_t)di * SZ_MAX_VERIFY * ch;
+    e->beta = s->d_beta + (int64_t)di * SZ_MAX_VERIFY * vh;
+    e->decay = s->d_decay + (int64_t)di * SZ_MAX_VERIFY * vh;
+    e->z = s->d_z;
+    e->S0 = s->S[0] + di * Sl; e->S1 = s->S[1] + di * Sl;
+    e->O0 = s->S[0] + di * Sl; e->O1 = s->S[1] + di * Sl;
+    e->state = s->state; e->res = s->res;
+    e->og = s->d_og;
+    e->pp.xin = s->d_xin + (int64_t)di * SZ_MAX_VERIFY * ch;
+    e->pp.conv0 = s->conv[0] + di * cl; e->pp.conv1 = s->conv[1] + di * cl;
+    e->pp.cw = (const float*)L.ssm_conv1d.data;
+    e->pp.b = s->d_b; e->pp.a = s->d_a;
+    e->pp.a_log = (const float*)L.ssm_a.data; e->pp.dt = (const float*)L.ssm_dt_bias.data;
+    e->pp.xc = s->d_xc + (int64_t)di * SZ_MAX_VERIFY * ch;
+    e->pp.beta = s->d_beta + (int64_t)di * SZ_MAX_VERIFY * vh;
+    e->pp.decay = s->d_decay + (int64_t)di * SZ_MAX_VERIFY * vh;
+    e->pp.k = (int)c.conv_k;
+    e->m = m;
+}
+// The scans of layer l of n sequences in one launch (tab: their entries on the device).
+static int sz_scan_seqs(sz_session* s0, cudaStream_t st, int l, int n, const SzScanSeq* tab, bool pdl) {
+    const sz_model_config& c = s0->model.cfg;
+    const float* nw = (const float*)s0->layers[l].ssm_norm.data;
+    if (c.ssm_head_dim == 128)
+        SZ_CUDA(sz_launch("delta_scan_seqs", sz_delta_scan_seqs_kernel<128, 2>, dim3(c.ssm_v_heads, n), dim3(256), 0, st, pdl, tab, nw, (int)c.ssm_k_heads,
+                          (int)c.ssm_v_heads, c.eps));
+    else
+        SZ_CUDA(sz_launch("delta_scan_seqs", sz_delta_scan_seqs_kernel<64, 1>, dim3(c.ssm_v_heads, n), dim3(64), 0, st, pdl, tab, nw, (int)c.ssm_k_heads,
+                          (int)c.ssm_v_heads, c.eps));
+    return SZ_OK;
+}
+
 // Which parts of a mixer a call runs: its input projections, what lies between them and the output projection, the output
 // projection.  A batched step runs the projections of all sequences together and only the middle per sequence.
 enum { SZ_MIX_IN = 1, SZ_MIX_CORE = 2, SZ_MIX_OUT = 4, SZ_MIX_ALL = 7 };
@@ -1508,7 +1549,7 @@ sz_batch_move_kernel(const SzBatchTab* __restrict__ T, float* const* __restrict_
 }
 
 enum { SZ_BATCH_SLOTS = SZ_DENSE_MAX_JOBS + 1 };   // per layer: the outputs of the input projections, then the input of the output projection
-struct SzBatchScratch { int64_t tab, ptrs, ptrs_bytes, x, y, r, r2, rn, acc, in, in_row, core, core_row, partial, partial_floats, moe, moe_bytes, total; };
+struct SzBatchScratch { int64_t tab, ptrs, ptrs_bytes, scan, scan_bytes, x, y, r, r2, rn, acc, in, in_row, core, core_row, partial, partial_floats, moe, moe_bytes, total; };
 static int sz_batch_layout(const sz_model* m, int rows_max, SzBatchScratch* S) {
     if (!m || !m->layers) return sz_fail(SZ_E_ARG, "null model");
     if (rows_max < 8 || rows_max % 8) return sz_fail(SZ_E_ARG, "sz_batch: rows_max = %d (a multiple of 8)", rows_max);
@@ -1517,6 +1558,10 @@ static int sz_batch_layout(const sz_model* m, int rows_max, SzBatchScratch* S) {
     S->tab = o; o = up256(o + (int64_t)sizeof(SzBatchTab));
     S->ptrs_bytes = (int64_t)c.n_layer * SZ_BATCH_SLOTS * SZ_BATCH_MAX * (int64_t)sizeof(float*);
     S->ptrs = o; o = up256(o + S->ptrs_bytes);
+    int n_delta = 0;
+    for (int l = 0; l < c.n_layer; l++) n_delta += sz_is_attn(c, l) ? 0 : 1;
+    S->scan_bytes = (int64_t)n_delta * SZ_BATCH_MAX * (int64_t)sizeof(SzScanSeq);   // the many-sequence scan's table: [DeltaNet layer][sequence]
+    S->scan = o; o = up256(o + S->scan_bytes);
     S->x = o; o = up256(o + 4 * (int64_t)rows_max * c.hidden);
     S->y = o; o = up256(o + 4 * (int64_t)rows_max * c.hidden);
     // the residual streams, their normed copy and the accumulators of the fused reads, for the rows of all sequences
@@ -1636,6 +1681,11 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
     float* PART = (float*)(base + S.partial);
     const char* re = getenv("SZ_BATCH_DENSE_ROWS");   // 0: the projections 8 rows a launch (the second form; same bits)
     const bool rows_form = !(re && atoi(re) == 0);
+    // the DeltaNet scans of a layer, all sequences in one launch from a table of their pointers (0, or the generic kernels: a launch
+    // a sequence on its stream; same bits)
+    const char* sc = getenv("SZ_BATCH_SCAN_SEQS");
+    const char* ge = getenv("SZ_GENERIC_KERNELS");
+    const bool scan_seqs = !(sc && atoi(sc) == 0) && !(ge && atoi(ge) != 0);
     if (shared) {
         repoint.ss = ss;
         for (int b = 0; b < n; b++) {
@@ -1657,6 +1707,14 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
                 row[(size_t)SZ_DENSE_MAX_JOBS * SZ_BATCH_MAX + b] = const_cast<float*>(o.x);
             }
         SZ_CUDA(cudaMemcpyAsync(base + S.ptrs, host.data(), (size_t)S.ptrs_bytes, cudaMemcpyHostToDevice, st));   // (pageable, as the table)
+        if (scan_seqs) {
+            static thread_local std::vector<SzScanSeq> hs;
+            hs.assign((size_t)(S.scan_bytes / sizeof(SzScanSeq)), SzScanSeq{});
+            for (int l = 0; l < c.n_layer; l++)
+                if (!sz_is_attn(c, l))
+                    for (int b = 0; b < n; b++) sz_scan_seq_entry(ss[b], l, ms[b], &hs[(size_t)s0->lb[l].delta_index * SZ_BATCH_MAX + b]);
+            SZ_CUDA(cudaMemcpyAsync(base + S.scan, hs.data(), (size_t)S.scan_bytes, cudaMemcpyHostToDevice, st));
+        }
         SZ_CUDA(cudaMemsetAsync(BB.acc, 0, sizeof(long long) * (size_t)Rp * SZ_HC_ACC_ROWS, st));   // read 0 adds into accumulator 0
     }
     if (Rp > R && !shared) SZ_CUDA(cudaMemsetAsync(X + (size_t)R * c.hidden, 0, (size_t)(Rp - R) * c.hidden * 4, st));   // the rows that pad the batch to a multiple of 8
@@ -1749,13 +1807,18 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
                 }
             }
             SZ_CUDA(sz_launch("batch_move", sz_batch_move_kernel, dim3(R, a.n_jobs), dim3(256), 0, st, true, T, lp, mi, IN, 1));
-            if ((rc = fork())) return rc;
-            if ((rc = each([&](int b) {
-                    return sz_is_attn(c, l) ? sz_attn_layer(ss[b], sq(b), l, ms[b], SZ_MIX_CORE) : sz_delta_layer(ss[b], sq(b), l, ms[b], SZ_MIX_CORE);
-                })))
-                return rc;
-            if ((rc = join())) return rc;
-            SZ_CUDA(sz_launch("batch_move", sz_batch_move_kernel, dim3(R, 1), dim3(256), 0, st, !multi, T, lp + (size_t)SZ_DENSE_MAX_JOBS * SZ_BATCH_MAX, mo, CORE, 0));
+            const bool one_scan = scan_seqs && !sz_is_attn(c, l);
+            if (one_scan) {   // the whole layer stays on the caller's stream
+                if ((rc = sz_scan_seqs(s0, st, l, n, (const SzScanSeq*)(base + S.scan) + (size_t)s0->lb[l].delta_index * SZ_BATCH_MAX, true))) return rc;
+            } else {
+                if ((rc = fork())) return rc;
+                if ((rc = each([&](int b) {
+                        return sz_is_attn(c, l) ? sz_attn_layer(ss[b], sq(b), l, ms[b], SZ_MIX_CORE) : sz_delta_layer(ss[b], sq(b), l, ms[b], SZ_MIX_CORE);
+                    })))
+                    return rc;
+                if ((rc = join())) return rc;
+            }
+            SZ_CUDA(sz_launch("batch_move", sz_batch_move_kernel, dim3(R, 1), dim3(256), 0, st, one_scan || !multi, T, lp + (size_t)SZ_DENSE_MAX_JOBS * SZ_BATCH_MAX, mo, CORE, 0));
             {
                 SzDenseArgs orr = o;
                 orr.m = Rp; orr.x = CORE; orr.job[0].out = Y;

@@ -643,13 +643,14 @@ struct SzDeltaPrep {
     int k;
 };
 
+// (the kernel's body: block (hd, di) of the grid described above)
 template <int D, int PARTS>
-__global__ void __launch_bounds__(D * PARTS)
-sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__ beta_all, const float* __restrict__ decay_all,
-                     const float* __restrict__ z, const float* __restrict__ norm_w, const float* __restrict__ S0, const float* __restrict__ S1,
-                     float* __restrict__ O0, float* __restrict__ O1, const int32_t* __restrict__ state, const int32_t* __restrict__ res, int kh,
-                     int vh, int m, float eps, float* __restrict__ og, const SzDeltaPrep pp, const SzTree* __restrict__ tr,
-                     float* __restrict__ fork) {
+__device__ __forceinline__ void
+sz_delta_scan_body(const float* __restrict__ xc_all, const float* __restrict__ beta_all, const float* __restrict__ decay_all,
+                   const float* __restrict__ z, const float* __restrict__ norm_w, const float* __restrict__ S0, const float* __restrict__ S1,
+                   float* __restrict__ O0, float* __restrict__ O1, const int32_t* __restrict__ state, const int32_t* __restrict__ res, int kh,
+                   int vh, int m, float eps, float* __restrict__ og, const SzDeltaPrep& pp, const SzTree* __restrict__ tr,
+                   float* __restrict__ fork, const int hd, const int di) {
     constexpr int NI = D / PARTS;
     constexpr int RUN = NI < 16 ? NI : 16;  // sums run in f32 over 16 terms and the runs are added in f64, as the reference's exact
                                             // GPU scan does (kernels/forward.cu:991-1013): a conversion to f64 per term would
@@ -660,7 +661,6 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
     __shared__ double rrs[SZ_MAX_VERIFY];
     __shared__ float pbuf[SZ_MAX_VERIFY][3][D];   // the rows' q, k, v after the front end
     __shared__ float sbeta[SZ_MAX_VERIFY], sdecay[SZ_MAX_VERIFY];
-    const int hd = blockIdx.x, di = blockIdx.y;
     const int col = threadIdx.x % D, pt = threadIdx.x / D;
     const int kx = hd % kh;  // value heads are tiled over the key heads (forward.rs:862-864)
     const int kd = kh * D, ch = 2 * kd + vh * D;
@@ -834,6 +834,38 @@ sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__
     float* So = S_out + (size_t)hd * D * D;
 #pragma unroll
     for (int i = 0; i < NI; i++) So[(size_t)(pt * NI + i) * D + col] = S[i];
+}
+
+template <int D, int PARTS>
+__global__ void __launch_bounds__(D * PARTS)
+sz_delta_scan_kernel(const float* __restrict__ xc_all, const float* __restrict__ beta_all, const float* __restrict__ decay_all,
+                     const float* __restrict__ z, const float* __restrict__ norm_w, const float* __restrict__ S0, const float* __restrict__ S1,
+                     float* __restrict__ O0, float* __restrict__ O1, const int32_t* __restrict__ state, const int32_t* __restrict__ res, int kh,
+                     int vh, int m, float eps, float* __restrict__ og, const SzDeltaPrep pp, const SzTree* __restrict__ tr,
+                     float* __restrict__ fork) {
+    sz_delta_scan_body<D, PARTS>(xc_all, beta_all, decay_all, z, norm_w, S0, S1, O0, O1, state, res, kh, vh, m, eps, og, pp, tr, fork,
+                                 (int)blockIdx.x, (int)blockIdx.y);
+}
+
+// The pass of one layer for SEVERAL sequences in one launch (a batched step): block row b is sequence b's scan, its pointers and
+// row count from a table.  grid (vh, sequences); the arithmetic is the kernel above's.
+struct SzScanSeq {
+    const float *xc, *beta, *decay, *z, *S0, *S1;
+    float *O0, *O1;
+    const int32_t *state, *res;
+    float* og;
+    SzDeltaPrep pp;
+    int m, pad;
+};
+template <int D, int PARTS>
+__global__ void __launch_bounds__(D * PARTS, 512 / (D * PARTS))   // (128 registers a thread, as the kernel above happens to need)
+sz_delta_scan_seqs_kernel(const SzScanSeq* __restrict__ tab, const float* __restrict__ norm_w, int kh, int vh, float eps) {
+    __shared__ SzScanSeq q;   // (the entry in shared memory: two dozen pointers in registers would cost the kernel its second block)
+    static_assert(sizeof(SzScanSeq) % 8 == 0, "copied in 8-byte words");
+    if (threadIdx.x < sizeof(SzScanSeq) / 8) ((u64*)&q)[threadIdx.x] = ((const u64*)(tab + blockIdx.y))[threadIdx.x];
+    __syncthreads();
+    sz_delta_scan_body<D, PARTS>(q.xc, q.beta, q.decay, q.z, norm_w, q.S0, q.S1, q.O0, q.O1, q.state, q.res, kh, vh, q.m, eps, q.og, q.pp,
+                                 (const SzTree*)nullptr, (float*)nullptr, (int)blockIdx.x, 0);
 }
 
 // ---- attention front end (forward.rs:908-927): per head RMSNorm + NeoX RoPE of q and k, the gate halves, K and V into the cache.

@@ -93,10 +93,12 @@ def test_the_shared_reads_and_projections_change_no_bit(dm, monkeypatch):
     rows = [[int(t) for t in rng.integers(0, CFG["vocab"], m)] for m in (3, 8, 1, 4, 2, 7)]
     got = []
     # (SZ_BATCH_DENSE_ROWS=0: the projections 8 rows a launch; SZ_BATCH_HC_SPLIT=0: the reads' first half by the pass's own kernel)
-    for shared, rows_form, split in (("1", "1", "1"), ("0", "1", "1"), ("1", "0", "1"), ("1", "1", "0")):
+    # SZ_BATCH_SCAN_SEQS=0: a scan launch a sequence instead of one a layer
+    for shared, rows_form, split, scans in (("1", "1", "1", "1"), ("0", "1", "1", "1"), ("1", "0", "1", "1"), ("1", "1", "0", "1"), ("1", "1", "1", "0")):
         monkeypatch.setenv("SZ_BATCH_SHARED", shared)
         monkeypatch.setenv("SZ_BATCH_DENSE_ROWS", rows_form)
         monkeypatch.setenv("SZ_BATCH_HC_SPLIT", split)
+        monkeypatch.setenv("SZ_BATCH_SCAN_SEQS", scans)
         batch = md.Batch(dm, 6, 64)
         batch.verify(rows)
         got.append([batch.sessions[b].result(logits=True)[2].view(np.uint32).copy() for b in range(6)])
