@@ -853,8 +853,8 @@ def run_c5_moe(args):
 def run_c5_batch(args):
     """Config 5's batch on the config-3 model: B sequences a GPU, every one with a session of its own (cache filled to the context,
     a 256-token prompt fed through it: untimed), then all decode `request_tokens` tokens in lockstep, spec K=3 each, through
-    sz_batch_gen_run: a step runs every sequence's scan, attention and head, and the reads, projections and MoE sublayer of a layer
-    ONCE over the rows of all of them.
+    sz_batch_gen_run: a step runs every sequence's attention and head, and the reads, projections, scans and MoE sublayer of a
+    layer ONCE over the rows of all of them.
     N > 1: every GPU holds the whole model and B sequences of its own.  Timed: the steps' device time (events around each step) and
     the wall clock of the loop."""
     out = QuietStdout()

@@ -310,9 +310,9 @@ int sz_session_result(sz_session* s, int32_t* keep_next, uint32_t* top, float* l
 /* Keeps the first `keep` rows of the pending pass and drops the rest (rollback(&snap, &batch[..keep])). */
 int sz_session_commit(sz_session* s, int keep, uint64_t stream);
 /* Several sequences in one step (the batch of config 5, from the pieces above): every sequence keeps its session and runs what
- * carries its own state (embedding, scan, attention, head) in lockstep with the others; the hyper-connection reads, the mixers'
+ * carries its own state (embedding, attention, head) in lockstep with the others; the hyper-connection reads, the mixers'
  * projections and the MoE sublayer of every layer take the rows of ALL sequences as one batch, so their weights are streamed once
- * a step and an expert several sequences chose is decoded once (sz_moe_rows).  While the call runs, the sessions' per-pass buffers
+ * a step and an expert several sequences chose is decoded once (sz_moe_rows); the DeltaNet scans of a layer are one launch.  While the call runs, the sessions' per-pass buffers
  * point into the batch's scratch: no other thread may use those sessions.  n <= 64 sessions of one model (EXL3 experts,
  * no expert sharding) on one stream; ms[b] rows of sequence b, ids = the rows of all sequences one after the other; the rows of
  * a step, padded to a multiple of 8, must fit rows_max (<= 256), the size the scratch was made for.  Afterwards every session
