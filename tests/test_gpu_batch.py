@@ -52,6 +52,29 @@ def test_a_step_of_several_sequences_equals_their_own_passes(dm):
         assert np.array_equal(lg.view(np.uint32), lg2.view(np.uint32)) and np.array_equal(top, top2)
 
 
+def test_a_step_of_forty_sequences_and_two_hundred_rows(dm):
+    """Many sequences: the reads, projections and experts then run over several row blocks and windows; every sequence still gets
+    the bits of its own pass, step after step."""
+    n = 40
+    rng = np.random.default_rng(31)
+    seqs = [[int(t) for t in rng.integers(0, CFG["vocab"], 24)] for _ in range(n)]
+    batch = md.Batch(dm, n, 48)
+    alone = [md.Session(dm, 48, kv_q8=True) for _ in range(n)]
+    at = [0] * n
+    for step in range(3):
+        ms = [1 + (3 * b + 5 * step) % 8 for b in range(n)]          # 1..8 rows, about 180 a step
+        rows = [seqs[b][at[b]:at[b] + ms[b]] for b in range(n)]
+        batch.verify(rows, accept=2)                                  # every row accepted on the device
+        for b in range(n):
+            (keep, _), top, lg = batch.sessions[b].result(logits=True)
+            alone[b].verify(rows[b], accept=2); (keep2, _), top2, lg2 = alone[b].result(logits=True)
+            assert keep == keep2 == ms[b]
+            assert np.array_equal(lg.view(np.uint32), lg2.view(np.uint32)), "step %d sequence %d" % (step, b)
+            assert np.array_equal(top, top2)
+            batch.sessions[b].commit(keep); alone[b].commit(keep2)
+            at[b] += ms[b]
+
+
 def lockstep(dm, vocab, n_seq, n_new, ctx=256):
     """n_seq sequences alone and then in lockstep: tokens and the books of every sequence."""
     import ctypes as C

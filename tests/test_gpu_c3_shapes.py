@@ -190,6 +190,22 @@ def test_a_batched_step_at_the_benchmark_shapes_equals_the_sequences_own_passes(
                 at[b] += ms[b]
 
 
+def test_a_batched_step_of_a_hundred_rows_at_the_benchmark_shapes(c3):
+    """Twenty-four sequences of 3..6 rows: 512 experts over several windows, projections over three row blocks."""
+    M, hm, dm = c3
+    n = 24
+    rng = np.random.default_rng(23)
+    seqs = [[int(t) for t in rng.integers(0, C3_SLICE["vocab"], 6)] for _ in range(n)]
+    ms = [3 + b % 4 for b in range(n)]
+    batch = md.Batch(dm, n, 16)
+    batch.verify([seqs[b][:ms[b]] for b in range(n)])
+    for b in range(n):
+        got = batch.sessions[b].result(logits=True)[2].view(np.uint32)
+        s = md.Session(dm, 16, kv_q8=True)
+        s.verify(seqs[b][:ms[b]])
+        assert np.array_equal(got, s.result(logits=True)[2].view(np.uint32)), "sequence %d" % b
+
+
 @pytest.mark.parametrize("length", [700, 5000])
 def test_long_context_pass_matches_the_cpu_steps(c3, length):
     """Attention over thousands of cached positions: both sides start from the same seeded cache (the library's synthetic history,
