@@ -918,13 +918,22 @@ def run_c5_batch(args):
         out.emit(json.dumps({"profile_steps": args.profile_steps, "sequences": B, "rows_of_last_step": rows_of, "context": ctx, "n_layer": cfg["n_layer"]}))
         return
 
-    tot = dict(n=0, rounds=0, steps=0, drafted=0, accepted=0, dev_ms=0.0, wall_s=0.0)
+    tot = dict(n=0, rounds=0, steps=0, drafted=0, accepted=0, dev_ms=0.0, wall_s=0.0, prefill_s=0.0, prefill_tokens=0)
     sampler = None
     for wave in range(-1, args.waves):     # wave -1: warm-up
         for s in batch.sessions:
             s.fill_synthetic(ctx - n_prompt, seed=3)
         prompts = [md.make_prompt(n_prompt, cfg["vocab"], seed=1 + ((wave + 1) * B + b) * world + rank, cycles=cyc) for b in range(B)]
-        gens = [md.Generator(s, p, n_new, spec_k=3) for s, p in zip(batch.sessions, prompts)]   # the prompts, one session at a time
+        torch.cuda.synchronize()
+        tp = time.perf_counter()
+        if args.feed == "alone":
+            gens = [md.Generator(s, p, n_new, spec_k=3) for s, p in zip(batch.sessions, prompts)]   # the prompts, one session at a time
+        else:
+            gens = batch.begin(prompts, n_new, spec_k=3)                                            # ... or in lockstep (sz_batch_prefill)
+        torch.cuda.synchronize()
+        if wave >= 0:
+            tot["prefill_s"] += time.perf_counter() - tp
+            tot["prefill_tokens"] += B * n_prompt
         barrier()
         if wave == 0:
             sampler = ClockSampler(torch.cuda.current_device())
@@ -968,8 +977,10 @@ def run_c5_batch(args):
         "dtype": "f32 activations, f16 EXL3 codebook weights, int8 Q8_0 / Q8_KV, f32 accumulate (router, norms, combine in f64)", "data": "synthetic",
         "config": dict(c3_config(args, cfg, ctx), workload="c5-batch", sequences_per_gpu=B, batch=B * world, waves=args.waves,
                        parallelism="replicas%d x %d sequences" % (world, B) if world > 1 else "%d sequences, one GPU" % B,
-                       batching="a step = every sequence's own reads, mixers and head (its session's kernels) + one MoE sublayer a layer over the rows of all "
-                                "sequences (sz_moe_rows); launched eagerly on one stream"),
+                       batching="a step = every sequence's own attention and head (its session's kernels) + the reads, projections, scans and MoE "
+                                "sublayer of a layer once over the rows of all sequences; launched eagerly"),
+        "prefill": {"feed": args.feed, "tokens": tot["prefill_tokens"], "tok_s": tot["prefill_tokens"] / max(tot["prefill_s"], 1e-9),
+                    "note": "the 256-token prompts of the sequences (untimed in `value`), wall clock on rank 0"},
         "speculation": {"tokens": toks, "rounds": rounds, "drafted": drafted, "accepted": accepted, "tokens_per_round": toks / max(rounds, 1),
                         "rows_per_step": (rounds + drafted) / max(steps, 1)},
         "roofline": {"bound": "hbm", "achieved": None, "peak": hbm, "unit": "GB/s", "frac": None, "traffic": None, "peak_kind": peak_kind,
@@ -1262,6 +1273,7 @@ def main():
                          "weak scaling, the throughput form), or experts sharded over the GPUs and ONE sequence (strong scaling: batch-1 "
                          "expert parallelism, which pays an exchange a layer and cannot scale)")
     ap.add_argument("--trace-rows", type=int, default=4, help="c3: rows of the pass whose launches are timed one by one (the line's `kernels`)")
+    ap.add_argument("--feed", default="batch", choices=["batch", "alone"], help="c5-batch: the prompts in lockstep (sz_batch_prefill) or one session at a time")
     ap.add_argument("--profile-steps", type=int, default=0, help="c5-batch: only run this many batched steps (the last one between cudaProfilerStart/Stop), no timing")
     ap.add_argument("--profile-passes", type=int, default=0, help="c3: only run this many 4-row verify passes (for ncu), no timing")
     ap.add_argument("--head", default="proxy", choices=["q8", "exl3", "proxy"],

@@ -322,6 +322,12 @@ int sz_batch_scratch_bytes(const sz_model* model, int rows_max, int64_t* bytes);
 int sz_batch_scratch_init(const sz_model* model, int rows_max, uint64_t scratch, uint64_t stream);
 int sz_batch_verify(sz_session* const* sessions, int n, const int32_t* ids, const int32_t* ms, int accept_mode, int eog_token, int rows_max,
                     uint64_t scratch, int64_t scratch_bytes, uint64_t stream);
+/* sz_session_prefill for n sequences in lockstep: every step takes up to 8 rows of every sequence that still has prompt left (as
+ * many sequences a step as rows_max holds; the rest wait their turn), keeps them all, and runs the head only for a prompt's last
+ * pass - which is left pending, as sz_session_prefill leaves it: sz_session_result, then sz_session_commit of its
+ * (lens[b] - 1) % 8 + 1 rows.  Every sequence's state and results are bit for bit those of its own sz_session_prefill. */
+int sz_batch_prefill(sz_session* const* sessions, int n, const int32_t* const* ids, const int32_t* lens, int rows_max, uint64_t scratch,
+                     int64_t scratch_bytes, uint64_t stream);
 /* Routing trace (the `layerL.route_idx` / `route_w` streams, forward.rs:1015-1018): switch it on, run a pass, read
  * idx [n_layer][SZ_MAX_VERIFY][SZ_MAX_TOPK] and w (same shape, f64). */
 /* Benchmarks: pretend `len` tokens were fed - seeded pseudo-random keys and values in the first `len` cache positions of every
@@ -451,6 +457,10 @@ int sz_gen_run(sz_gen* g, int rounds, uint32_t* out, int32_t* pass_log, int pass
  * outs[b] / stats[b] as sz_gen_run's; *device_ms accumulates the steps' device time.  A sequence's tokens are those of its own loop. */
 int sz_batch_gen_run(sz_gen* const* gens, int n, int rounds, uint32_t* const* outs, sz_gen_stats* const* stats, int rows_max, uint64_t scratch,
                      int64_t scratch_bytes, double* device_ms, uint64_t stream);
+/* sz_gen_begin for n sequences at once: the prompts go through sz_batch_prefill; gens[b] is sequence b's generator, as sz_gen_begin
+ * on its own would have made it (one parameter block for all). */
+int sz_batch_gen_begin(sz_session* const* sessions, int n, const uint32_t* const* prompts, const int32_t* n_prompts, const sz_gen_params* p, int rows_max,
+                       uint64_t scratch, int64_t scratch_bytes, uint64_t stream, sz_gen** gens);
 /* the request's stop ids for the loop: it ends at one as at eog_token, and never accepts a drafted one (host and device alike) */
 int sz_gen_set_stops(sz_gen* g, const uint32_t* ids, int n, uint64_t stream);
 void sz_gen_free(sz_gen* g);

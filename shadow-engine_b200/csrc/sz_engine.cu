@@ -16,6 +16,8 @@ int sz_session_commit(sz_session* s, int keep, uint64_t stream);
 int sz_session_set_stops(sz_session* s, const int32_t* ids, int n, uint64_t stream);
 int sz_batch_verify(sz_session* const* sessions, int n, const int32_t* ids, const int32_t* ms, int accept_mode, int eog_token, int rows_max, uint64_t scratch,
                     int64_t scratch_bytes, uint64_t stream);
+int sz_batch_prefill(sz_session* const* sessions, int n, const int32_t* const* ids, const int32_t* lens, int rows_max, uint64_t scratch, int64_t scratch_bytes,
+                     uint64_t stream);
 int sz_session_stops(const sz_session* s, int32_t* out);
 int sz_session_len(const sz_session* s);
 int sz_session_capacity(const sz_session* s);
@@ -455,7 +457,8 @@ struct sz_gen {
     }
 };
 
-extern "C" int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint64_t stream, sz_gen** out) {
+// sz_gen_begin in its two halves, around the feeding of the prompt (one sequence's own passes, or steps shared with others)
+static int gen_create(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint64_t stream, sz_gen** out) {
     if (!s || !prompt || n_prompt < 1 || !p || !out) return sz_fail(SZ_E_ARG, "sz_gen_begin: null argument or empty prompt");
     if (p->spec_k < 0 || p->spec_k > SZ_MAX_VERIFY - 1) return sz_fail(SZ_E_ARG, "sz_gen_begin: spec_k = %d (0..%d)", p->spec_k, SZ_MAX_VERIFY - 1);
     if (sz_session_len(s) + n_prompt + p->max_new + SZ_MAX_VERIFY > sz_session_capacity(s))
@@ -465,18 +468,48 @@ extern "C" int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt,
     { int32_t st[7]; const int ns = sz_session_stops(s, st); g->stops.assign(st, st + ns); }   // the session's stop ids hold for the loop too
     g->top.resize(SZ_MAX_VERIFY * 128); g->last.resize(128);
     if (cudaEventCreate(&g->ev0) != cudaSuccess || cudaEventCreate(&g->ev1) != cudaSuccess) { delete g; return sz_fail(SZ_E_CUDA, "sz_gen_begin: no events"); }
-    int rc = !p->greedy && p->device_accept ? sz_session_set_sampler(s, &p->sampler) : SZ_OK;
-    if (!rc) rc = sz_session_prefill(s, (const int32_t*)prompt, n_prompt, stream);
-    const int tail = (n_prompt - 1) % SZ_MAX_VERIFY + 1;  // rows of the last prompt pass
-    if (!rc) rc = sz_session_result(s, nullptr, g->top.data(), nullptr, stream);
-    if (!rc) rc = sz_session_commit(s, tail, stream);
+    const int rc = !p->greedy && p->device_accept ? sz_session_set_sampler(s, &p->sampler) : SZ_OK;
     if (rc) { delete g; return rc; }
+    *out = g;
+    return SZ_OK;
+}
+// after the prompt's last pass (pending): its top-64, the commit, the drafter's index of the prompt
+static int gen_fed(sz_gen* g, const uint32_t* prompt, int n_prompt, uint64_t stream) {
+    const sz_gen_params* p = &g->p;
+    const int tail = (n_prompt - 1) % SZ_MAX_VERIFY + 1;  // rows of the last prompt pass
+    int rc = sz_session_result(g->s, nullptr, g->top.data(), nullptr, stream);
+    if (!rc) rc = sz_session_commit(g->s, tail, stream);
+    if (rc) return rc;
     std::memcpy(g->last.data(), g->top.data() + (size_t)(tail - 1) * 128, 128 * 4);
     g->sd = sz_drafter_new(p->lookup_min < 3 ? 3 : p->lookup_min, 32, n_prompt + p->max_new + 64);
     g->hist.assign(prompt, prompt + n_prompt);
     sz_drafter_extend(g->sd, prompt, n_prompt);
+    return SZ_OK;
+}
+
+extern "C" int sz_gen_begin(sz_session* s, const uint32_t* prompt, int n_prompt, const sz_gen_params* p, uint64_t stream, sz_gen** out) {
+    sz_gen* g = nullptr;
+    int rc = gen_create(s, prompt, n_prompt, p, stream, &g);
+    if (rc) return rc;
+    rc = sz_session_prefill(s, (const int32_t*)prompt, n_prompt, stream);
+    if (!rc) rc = gen_fed(g, prompt, n_prompt, stream);
+    if (rc) { delete g; return rc; }
     *out = g;
     return SZ_OK;
+}
+
+// sz_gen_begin for n sequences at once: the prompts are fed in lockstep (sz_batch_prefill: steps of up to 8 rows of every
+// sequence, what reads weights once over the rows of all of them).  gens[b] is sequence b's generator, as sz_gen_begin makes it.
+extern "C" int sz_batch_gen_begin(sz_session* const* ss, int n, const uint32_t* const* prompts, const int32_t* n_prompts, const sz_gen_params* p, int rows_max,
+                                  uint64_t scratch, int64_t scratch_bytes, uint64_t stream, sz_gen** gens) {
+    if (!ss || !prompts || !n_prompts || !p || !gens || n < 1 || n > 64) return sz_fail(SZ_E_ARG, "sz_batch_gen_begin: 1..64 sequences");
+    int rc = SZ_OK, made = 0;
+    for (; made < n && !rc; made++) rc = gen_create(ss[made], prompts[made], n_prompts[made], p, stream, &gens[made]);
+    if (rc) made--;   // (the one that failed made nothing)
+    if (!rc) rc = sz_batch_prefill(ss, n, (const int32_t* const*)prompts, n_prompts, rows_max, scratch, scratch_bytes, stream);
+    for (int b = 0; b < n && !rc; b++) rc = gen_fed(gens[b], prompts[b], n_prompts[b], stream);
+    if (rc) { for (int b = 0; b < made; b++) { delete gens[b]; gens[b] = nullptr; } }
+    return rc;
 }
 
 // The request's stop tokens (engine.rs:2386 `stops.contains(&d)`; the tokenizer's further end-of-generation ids go here too): the

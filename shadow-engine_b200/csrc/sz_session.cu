@@ -1432,15 +1432,15 @@ extern "C" int sz_session_prefill(sz_session* s, const int32_t* ids, int n, uint
 }
 
 // ---- several sequences in one step ---------------------------------------------------------------------------------------------------
-// Config 5's batch, built from what is there: every sequence keeps its session (cache, recurrent states, buffers) and runs its own
-// reads, mixers and head, layer by layer in lockstep with the others; where the layers meet - the MoE sublayer - the rows of ALL
-// sequences go through sz_moe_rows as one batch, so an expert that several sequences chose is streamed and decoded once.  A
-// sequence's numbers are those of a pass of its own (the MoE rows are bit for bit sz_moe_verify's), so acceptance, commit and the
-// result are read session by session as after sz_session_verify.  Launched eagerly on one stream (no graph: the rows a step holds
-// change from step to step).
+// Config 5's batch, built from what is there: every sequence keeps its session (cache, recurrent states, buffers) and the
+// sequences go through the layers in lockstep.  What reads the same weights for every sequence - the hyper-connection reads, the
+// mixers' projections, the MoE sublayer - runs once over the rows of ALL sequences (an expert that several sequences chose is
+// streamed and decoded once), and so do the DeltaNet scans of a layer; attention and the head stay launches of the sequence.  A
+// sequence's numbers are those of a pass of its own, so acceptance, commit and the result are read session by session as after
+// sz_session_verify.  Launched eagerly (no graph: the rows a step holds change from step to step).
 #define SZ_BATCH_MAX 64
-// A step of B sequences is some 400 launches a sequence: issued by one host thread they take longer than the GPU needs to run
-// them.  A few worker threads (SZ_BATCH_THREADS, default 6; 0 = none) issue the sequences' own launches side by side, each on the
+// A step of B sequences is up to some 400 launches a sequence (about 50 with the shared forms): issued by one host thread they
+// can take longer than the GPU needs to run them.  A few worker threads (SZ_BATCH_THREADS, default 6; 0 = none) issue the sequences' own launches side by side, each on the
 // sequences' own streams; what is shared is issued by the calling thread.  The workers live as long as the process.
 namespace {
 struct SzIssuePool {
@@ -1612,10 +1612,17 @@ extern "C" int sz_batch_scratch_init(const sz_model* m, int rows_max, uint64_t s
 // One step of n sequences: sequence b reads ms[b] rows (ids: the rows of all sequences, one after the other).  accept_mode:
 // SZ_ACCEPT_NONE, _GREEDY or _ALL, as sz_session_verify.  Afterwards every session holds a pending pass: sz_session_result and
 // sz_session_commit per session, as after a pass of its own.
-extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids, const int32_t* ms, int accept_mode, int eog_token, int rows_max,
-                               uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
+// (accept[b], heads[b]: sequence b's acceptance mode and whether its rows go through the head - a prompt's passes before its last
+// keep all rows and need no logits)
+static int sz_batch_step(sz_session* const* ss, int n, const int32_t* ids, const int32_t* ms, const int* accept, const int* heads, int eog_token,
+                         int rows_max, uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
     if (!ss || !ids || !ms || n < 1 || n > SZ_BATCH_MAX) return sz_fail(SZ_E_ARG, "sz_batch_verify: 1..%d sequences", SZ_BATCH_MAX);
-    if (accept_mode < SZ_ACCEPT_NONE || accept_mode > SZ_ACCEPT_ALL) return sz_fail(SZ_E_ARG, "sz_batch_verify: accept_mode %d", accept_mode);
+    bool any_head = false;
+    for (int b = 0; b < n; b++) {
+        if (accept[b] < SZ_ACCEPT_NONE || accept[b] > SZ_ACCEPT_ALL) return sz_fail(SZ_E_ARG, "sz_batch_verify: accept_mode %d", accept[b]);
+        if (!heads[b] && accept[b] != SZ_ACCEPT_ALL) return sz_fail(SZ_E_ARG, "sz_batch_verify: a pass without the head keeps all its rows");
+        any_head = any_head || heads[b];
+    }
     sz_session* s0 = ss[0];
     if (!s0) return sz_fail(SZ_E_ARG, "sz_batch_verify: null session");
     SzBatchScratch S;
@@ -1835,7 +1842,7 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
             if ((rc = sz_moe_rows(&L.moe, (uint64_t)X, Rp, (uint64_t)Y, 0, 0, scratch + S.moe, S.moe_bytes, stream))) return rc;
             pending = true;
         }
-        if ((rc = read_rows(s0->model.output_hc, pending, false, true))) return rc;
+        if (any_head && (rc = read_rows(s0->model.output_hc, pending, false, true))) return rc;
         if ((rc = fork())) return rc;
     } else {
         for (int l = 0; l < c.n_layer; l++) {
@@ -1850,19 +1857,65 @@ extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids,
     }
     if ((rc = each([&](int b) {
             sz_session* s = ss[b];
-            int r = sz_forward_head(s, sq(b), ms[b], pending, !shared);
-            if (!r) r = sz_pass_tail(s, sq(b), ms[b], accept_mode, eog_token, true);
+            int r = heads[b] ? sz_forward_head(s, sq(b), ms[b], pending, !shared) : SZ_OK;
+            if (!r) r = sz_pass_tail(s, sq(b), ms[b], accept[b], eog_token, heads[b] != 0);
             return r;
         })))
         return rc;
     for (int b = 0; b < n; b++) {
         sz_session* s = ss[b];
         s->last_m = ms[b];
-        s->pending_committed = accept_mode != SZ_ACCEPT_NONE;
-        s->device_keep = accept_mode == SZ_ACCEPT_ALL ? ms[b] : -1;
+        s->pending_committed = accept[b] != SZ_ACCEPT_NONE;
+        s->device_keep = accept[b] == SZ_ACCEPT_ALL ? ms[b] : -1;
         s->inflight = 1;
     }
     return join();
+}
+
+extern "C" int sz_batch_verify(sz_session* const* ss, int n, const int32_t* ids, const int32_t* ms, int accept_mode, int eog_token, int rows_max,
+                               uint64_t scratch, int64_t scratch_bytes, uint64_t stream) {
+    if (n < 1 || n > SZ_BATCH_MAX) return sz_fail(SZ_E_ARG, "sz_batch_verify: 1..%d sequences", SZ_BATCH_MAX);
+    int accept[SZ_BATCH_MAX], heads[SZ_BATCH_MAX];
+    for (int b = 0; b < n; b++) { accept[b] = accept_mode; heads[b] = 1; }
+    return sz_batch_step(ss, n, ids, ms, accept, heads, eog_token, rows_max, scratch, scratch_bytes, stream);
+}
+
+// The prompts of n sequences fed in lockstep: every step takes up to 8 rows of every sequence that still has some (as many
+// sequences a step as the scratch's rows hold), keeps them all, and skips the head except for a prompt's last pass - which is left
+// pending, as sz_session_prefill leaves it: sz_session_result, then sz_session_commit of its rows (lens[b] - 1) % 8 + 1.
+extern "C" int sz_batch_prefill(sz_session* const* ss, int n, const int32_t* const* ids, const int32_t* lens, int rows_max, uint64_t scratch,
+                                int64_t scratch_bytes, uint64_t stream) {
+    if (!ss || !ids || !lens || n < 1 || n > SZ_BATCH_MAX) return sz_fail(SZ_E_ARG, "sz_batch_prefill: 1..%d sequences", SZ_BATCH_MAX);
+    if (rows_max < SZ_MAX_VERIFY) return sz_fail(SZ_E_ARG, "sz_batch_prefill: a scratch for %d rows", rows_max);
+    std::vector<int> done((size_t)n, 0);
+    for (int b = 0; b < n; b++)
+        if (!ss[b] || !ids[b] || lens[b] < 1) return sz_fail(SZ_E_ARG, "sz_batch_prefill: sequence %d has nothing to feed", b);
+    for (;;) {
+        sz_session* step_s[SZ_BATCH_MAX];
+        int32_t step_m[SZ_BATCH_MAX];
+        int accept[SZ_BATCH_MAX], heads[SZ_BATCH_MAX], who[SZ_BATCH_MAX];
+        std::vector<int32_t> rows;
+        int k = 0;
+        for (int b = 0; b < n && (k + 1) * SZ_MAX_VERIFY <= rows_max; b++) {
+            if (done[b] >= lens[b]) continue;
+            const int left = lens[b] - done[b];
+            const int m = left < SZ_MAX_VERIFY ? left : SZ_MAX_VERIFY;
+            const bool last = m == left;
+            step_s[k] = ss[b]; step_m[k] = m; who[k] = b;
+            accept[k] = last ? SZ_ACCEPT_NONE : SZ_ACCEPT_ALL;
+            heads[k] = last ? 1 : 0;
+            rows.insert(rows.end(), ids[b] + done[b], ids[b] + done[b] + m);
+            k++;
+        }
+        if (k == 0) return SZ_OK;
+        int rc = sz_batch_step(step_s, k, rows.data(), step_m, accept, heads, -1, rows_max, scratch, scratch_bytes, stream);
+        if (rc) return rc;
+        for (int i = 0; i < k; i++) {
+            const int b = who[i];
+            done[b] += step_m[i];
+            if (done[b] < lens[b] && (rc = sz_session_commit(step_s[i], step_m[i], stream))) return rc;   // (a prompt's last pass stays pending)
+        }
+    }
 }
 
 // ---- synthetic history (benchmarks) -------------------------------------------------------------------------------------------------

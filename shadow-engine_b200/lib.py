@@ -139,6 +139,9 @@ SYMBOLS = {
     "sz_batch_scratch_init": (C.c_int, [C.c_void_p, C.c_int, C.c_uint64, C.c_uint64]),
     "sz_batch_verify": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_int32), C.POINTER(C.c_int32), C.c_int, C.c_int, C.c_int, C.c_uint64,
                                   C.c_int64, C.c_uint64]),
+    "sz_batch_prefill": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_int, C.c_uint64, C.c_int64, C.c_uint64]),
+    "sz_batch_gen_begin": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int32), C.c_void_p, C.c_int, C.c_uint64, C.c_int64,
+                                     C.c_uint64, C.POINTER(C.c_void_p)]),
     "sz_batch_gen_run": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.c_int, C.c_uint64, C.c_int64,
                                    C.POINTER(C.c_double), C.c_uint64]),
     "sz_mma_cols_scratch_bytes": (C.c_int, [C.c_int, C.c_int, C.POINTER(C.c_int64)]),

@@ -497,13 +497,17 @@ class Session:
 class Generator:
     """The loop in pieces (sz_gen_begin / sz_gen_run): feed the prompt, then run rounds and look at the statistics in between."""
 
-    def __init__(self, sess, prompt, max_new, spec_k=3, greedy=True, sampler=None, lookup_min=4, eog=-1, device_accept=True):
+    def __init__(self, sess, prompt, max_new, spec_k=3, greedy=True, sampler=None, lookup_min=4, eog=-1, device_accept=True, handle=None):
+        """handle: a generator that already exists (sz_batch_gen_begin made it with these parameters): the prompt is not fed again."""
         self.sess, self.lib = sess, sess.lib
         self.p = GenParams(spec_k, max_new, lookup_min, 1 if greedy else 0, eog, 1 if device_accept else 0,
                            sampler or Sampler(1.0, 20, 0.95, 0.0, 1), 0, 0)
-        pr = (C.c_uint32 * len(prompt))(*[int(t) for t in prompt])
-        self.h = C.c_void_p()
-        szlib.check(self.lib.sz_gen_begin(sess.h, pr, len(prompt), C.byref(self.p), sess.stream, C.byref(self.h)))
+        if handle is not None:
+            self.h = C.c_void_p(handle)
+        else:
+            pr = (C.c_uint32 * len(prompt))(*[int(t) for t in prompt])
+            self.h = C.c_void_p()
+            szlib.check(self.lib.sz_gen_begin(sess.h, pr, len(prompt), C.byref(self.p), sess.stream, C.byref(self.h)))
         self.out = (C.c_uint32 * max_new)()
         self.log = (C.c_int32 * (2 * max_new))()
         self.max_new = max_new
@@ -523,8 +527,8 @@ class Generator:
 
 
 class Batch:
-    """Several sequences stepped together (`sz_batch_verify`, `sz_batch_gen_run`): sessions of one model on one stream; the MoE
-    sublayers take the rows of all of them at once."""
+    """Several sequences stepped together (`sz_batch_verify`, `sz_batch_prefill`, `sz_batch_gen_begin`, `sz_batch_gen_run`): sessions
+    of one model on one stream; what reads weights takes the rows of all of them at once."""
 
     def __init__(self, dm, n, ctx, rows_max=None, kv_q8=True, head_proxy=False):
         self.lib = szlib.load()
@@ -553,10 +557,39 @@ class Batch:
         for s, r in zip(ss, rows):
             s._m = len(r)
 
-    def generate(self, prompts, max_new, spec_k=3, eog=-1, rounds=0):
-        """Every prompt through its session (one at a time), then the sequences decode in lockstep.  Returns the tokens of every
-        sequence, their statistics and the device time of the steps in ms."""
-        gens = [Generator(s, p, max_new, spec_k=spec_k, eog=eog) for s, p in zip(self.sessions, prompts)]
+    def prefill(self, prompts, which=None):
+        """The prompts of the sessions fed in lockstep (`sz_batch_prefill`); every session is left with its last pass pending."""
+        ss = [self.sessions[i] for i in (which if which is not None else range(len(self.sessions)))]
+        assert len(ss) == len(prompts)
+        n = len(ss)
+        keep = [(C.c_int32 * len(p))(*[int(t) for t in p]) for p in prompts]
+        hs = (C.c_void_p * n)(*[s.h for s in ss])
+        ids = (C.c_void_p * n)(*[C.cast(k, C.c_void_p) for k in keep])
+        lens = (C.c_int32 * n)(*[len(p) for p in prompts])
+        szlib.check(self.lib.sz_batch_prefill(hs, n, ids, lens, self.rows_max, self.scratch, self.scratch_bytes, self.stream))
+        for s, p in zip(ss, prompts):
+            s._m = (len(p) - 1) % szlib.MAX_VERIFY + 1
+
+    def begin(self, prompts, max_new, spec_k=3, eog=-1):
+        """A generator per session, the prompts fed in lockstep (`sz_batch_gen_begin`)."""
+        n = len(prompts)
+        assert n == len(self.sessions)
+        par = GenParams(spec_k, max_new, 4, 1, eog, 1, Sampler(1.0, 20, 0.95, 0.0, 1), 0, 0)
+        keep = [(C.c_uint32 * len(p))(*[int(t) for t in p]) for p in prompts]
+        hs = (C.c_void_p * n)(*[s.h for s in self.sessions])
+        pr = (C.c_void_p * n)(*[C.cast(k, C.c_void_p) for k in keep])
+        lens = (C.c_int32 * n)(*[len(p) for p in prompts])
+        out = (C.c_void_p * n)()
+        szlib.check(self.lib.sz_batch_gen_begin(hs, n, pr, lens, C.byref(par), self.rows_max, self.scratch, self.scratch_bytes, self.stream, out))
+        return [Generator(s, p, max_new, spec_k=spec_k, eog=eog, handle=out[b]) for b, (s, p) in enumerate(zip(self.sessions, prompts))]
+
+    def generate(self, prompts, max_new, spec_k=3, eog=-1, rounds=0, feed="batch"):
+        """The prompts through the sessions (feed="batch": in lockstep; "alone": one session at a time), then the sequences decode
+        in lockstep.  Returns the tokens of every sequence, their statistics and the device time of the steps in ms."""
+        if feed == "batch":
+            gens = self.begin(prompts, max_new, spec_k=spec_k, eog=eog)
+        else:
+            gens = [Generator(s, p, max_new, spec_k=spec_k, eog=eog) for s, p in zip(self.sessions, prompts)]
         n = len(gens)
         gh = (C.c_void_p * n)(*[g.h for g in gens])
         outs = (C.c_void_p * n)(*[C.cast(g.out, C.c_void_p) for g in gens])

@@ -75,6 +75,38 @@ def test_a_step_of_forty_sequences_and_two_hundred_rows(dm):
             at[b] += ms[b]
 
 
+@pytest.mark.parametrize("rows_max", [None, 16])
+def test_prompts_fed_in_lockstep_equal_prompts_fed_alone(dm, rows_max):
+    """sz_batch_prefill: prompts of ragged lengths (one token, whole passes, a tail), more sequences than a step holds when the
+    scratch is small: the last pass's logits, and a pass after the commit, are bit for bit those of sz_session_prefill."""
+    lens = [1, 8, 9, 30, 16, 23]
+    prompts = [md.make_prompt(n, CFG["vocab"], seed=40 + i) for i, n in enumerate(lens)]
+    batch = md.Batch(dm, len(lens), 64, rows_max=rows_max)
+    batch.prefill(prompts)
+    for b, p in enumerate(prompts):
+        tail = (len(p) - 1) % 8 + 1
+        a = md.Session(dm, 64, kv_q8=True)
+        a.prefill(p)
+        _, top2, lg2 = a.result(logits=True); a.commit(tail)
+        s = batch.sessions[b]
+        _, top, lg = s.result(logits=True); s.commit(tail)
+        assert np.array_equal(lg.view(np.uint32), lg2.view(np.uint32)) and np.array_equal(top, top2), "prompt %d" % b
+        s.verify([5, 6, 7]); a.verify([5, 6, 7])
+        assert np.array_equal(s.result(logits=True)[2].view(np.uint32), a.result(logits=True)[2].view(np.uint32)), "after prompt %d" % b
+        s.commit(3); a.commit(3)
+
+
+def test_generation_from_prompts_fed_in_lockstep(dm):
+    prompts = [md.make_prompt(40 + 8 * b, CFG["vocab"], seed=10 + b) for b in range(4)]
+    toks_b, st_b, _ = md.Batch(dm, 4, 256).generate(prompts, 32, feed="batch")
+    toks_a, st_a, _ = md.Batch(dm, 4, 256).generate(prompts, 32, feed="alone")
+    assert toks_b == toks_a
+    assert [(s.passes, s.drafted, s.accepted) for s in st_b] == [(s.passes, s.drafted, s.accepted) for s in st_a]
+    for b, p in enumerate(prompts):
+        want, _, _ = md.Session(dm, 256, kv_q8=True).generate(p, 32, spec_k=3)
+        assert toks_b[b] == want
+
+
 def lockstep(dm, vocab, n_seq, n_new, ctx=256):
     """n_seq sequences alone and then in lockstep: tokens and the books of every sequence."""
     import ctypes as C
