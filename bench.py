@@ -883,6 +883,15 @@ def run_c5_batch(args):
     torch.cuda.empty_cache()
     B, ctx, n_prompt, n_new = args.sequences, args.ctx, 256, args.request_tokens
     _, cyc = md.token_cycles(cfg["vocab"], 1)
+    # --contexts a,b,c: every sequence's context (history + prompt) is one of these, drawn with a fixed seed (benchmark config 5:
+    # 3k, 9.6k or 15k tokens before the decode); default: every sequence at --ctx
+    if args.contexts:
+        choices = [int(v) for v in args.contexts.split(",")]
+        rng_c = __import__("numpy").random.default_rng(5 + rank)
+        ctx_of = [int(choices[int(rng_c.integers(0, len(choices)))]) for _ in range(B)]
+        ctx = max(ctx_of)
+    else:
+        ctx_of = [ctx] * B
     batch = md.Batch(dm, B, ctx + n_new + 64, head_proxy=args.head == "proxy")
 
     def barrier():
@@ -921,8 +930,8 @@ def run_c5_batch(args):
     tot = dict(n=0, rounds=0, steps=0, drafted=0, accepted=0, dev_ms=0.0, wall_s=0.0, prefill_s=0.0, prefill_tokens=0)
     sampler = None
     for wave in range(-1, args.waves):     # wave -1: warm-up
-        for s in batch.sessions:
-            s.fill_synthetic(ctx - n_prompt, seed=3)
+        for s, cb in zip(batch.sessions, ctx_of):
+            s.fill_synthetic(cb - n_prompt, seed=3)
         prompts = [md.make_prompt(n_prompt, cfg["vocab"], seed=1 + ((wave + 1) * B + b) * world + rank, cycles=cyc) for b in range(B)]
         torch.cuda.synchronize()
         tp = time.perf_counter()
@@ -976,6 +985,7 @@ def run_c5_batch(args):
         "steps": steps, "warmup": B, "ms_per_step": dev_ms / max(steps, 1), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32 activations, f16 EXL3 codebook weights, int8 Q8_0 / Q8_KV, f32 accumulate (router, norms, combine in f64)", "data": "synthetic",
         "config": dict(c3_config(args, cfg, ctx), workload="c5-batch", sequences_per_gpu=B, batch=B * world, waves=args.waves,
+                       contexts=sorted(set(ctx_of)), request_tokens=n_new,
                        parallelism="replicas%d x %d sequences" % (world, B) if world > 1 else "%d sequences, one GPU" % B,
                        batching="a step = every sequence's own attention and head (its session's kernels) + the reads, projections, scans and MoE "
                                 "sublayer of a layer once over the rows of all sequences; launched eagerly"),
@@ -1273,6 +1283,7 @@ def main():
                          "weak scaling, the throughput form), or experts sharded over the GPUs and ONE sequence (strong scaling: batch-1 "
                          "expert parallelism, which pays an exchange a layer and cannot scale)")
     ap.add_argument("--trace-rows", type=int, default=4, help="c3: rows of the pass whose launches are timed one by one (the line's `kernels`)")
+    ap.add_argument("--contexts", default="", help="c5-batch: comma list of context lengths the sequences draw theirs from (config 5: 3000,9600,15000); default: all at --ctx")
     ap.add_argument("--feed", default="batch", choices=["batch", "alone"], help="c5-batch: the prompts in lockstep (sz_batch_prefill) or one session at a time")
     ap.add_argument("--profile-steps", type=int, default=0, help="c5-batch: only run this many batched steps (the last one between cudaProfilerStart/Stop), no timing")
     ap.add_argument("--profile-passes", type=int, default=0, help="c3: only run this many 4-row verify passes (for ncu), no timing")
