@@ -1727,9 +1727,9 @@ static int sz_batch_step(sz_session* const* ss, int n, const int32_t* ids, const
     if (Rp > R && !shared) SZ_CUDA(cudaMemsetAsync(X + (size_t)R * c.hidden, 0, (size_t)(Rp - R) * c.hidden * 4, st));   // the rows that pad the batch to a multiple of 8
     // The sequences' own kernels are chains of short dependent launches: on one stream they would run one sequence after the other
     // and leave the GPU as idle as a lone pass does.  So every sequence gets a stream of its own for them (a pool owned by the
-    // calling thread, made at the first call), and the caller's stream carries what is shared: per layer it waits for the
-    // sequences' inputs, runs the MoE sublayer over all rows, and lets the sequences go on.  SZ_BATCH_STREAMS=0: everything on the
-    // caller's stream.
+    // calling thread, made at the first call), and the caller's stream carries what is shared: it lets the sequences' streams go
+    // where a layer has work of their own (attention; everything but the MoE when nothing else is shared), waits for them, and
+    // goes on with the rows of all.  SZ_BATCH_STREAMS=0: everything on the caller's stream.
     static thread_local cudaStream_t pool[SZ_BATCH_MAX] = {};
     static thread_local cudaEvent_t pool_ev[SZ_BATCH_MAX] = {};
     static thread_local cudaEvent_t main_ev = nullptr;
