@@ -372,13 +372,15 @@ sz_hc_rows_down_kernel(const float* __restrict__ rn, const u8* __restrict__ down
 // the block's rows of the up matrix, one 16-byte piece a thread and slot: constant data, requested before the dependency wait
 // (threads 256 and up of a wider block hold none)
 __device__ __forceinline__ void sz_hc_up_fetch(const u8* __restrict__ up, int H, int C, int rank, uint4* w) {
-    const int t = threadIdx.x, cpr = rank >> 3, h0 = blockIdx.x * 16, chunks = 16 * C * cpr;
+    const int t = threadIdx.x, cpr = rank >> 3, h0 = blockIdx.x * 16;
+    // piece t + 256 i of the block's rows: cpr divides 256, so the thread's place c in a row is the same for every i and the row
+    // advances by 256 / cpr (one division here instead of one a slot)
+    const int lr0 = t / cpr, c = t - lr0 * cpr, step = 256 / cpr;
 #pragma unroll
     for (int i = 0; i < 8; i++) {
-        const int ch = t + 256 * i;
+        const int lr = lr0 + step * i;                        // local row s * 16 + hl
         w[i] = make_uint4(0, 0, 0, 0);
-        if (t < 256 && ch < chunks && h0 < H) {
-            const int lr = ch / cpr, c = ch - lr * cpr;       // local row s * 16 + hl
+        if (t < 256 && lr < 16 * C && h0 < H) {
             const int row = (lr >> 4) * H + h0 + (lr & 15);
             w[i] = sz_ldg16_here((const uint4*)(up + (size_t)row * rank * 2) + c);
         }
@@ -394,16 +396,18 @@ sz_hc_up_body(const long long* __restrict__ acc, const float* __restrict__ rn, i
     const int t = threadIdx.x;
     const int cpr = rank >> 3;
     const int h0 = blockIdx.x * 16;
-    const int chunks = 16 * C * cpr;  // <= 2048
+    const int lr0 = t / cpr, c = t - lr0 * cpr, step = 256 / cpr;   // (as sz_hc_up_fetch: the thread's place in a row, its first row)
     SZ_PH_DECL;
     SZ_PH();  // 1
     const bool on = t < 256;   // a wider block's extra warps only keep the barriers company
-    if (on)
-        for (int idx = t; idx < M * rank; idx += 256) {
-            const int j = idx / rank, q = idx - j * rank;
-            const float v = (float)((double)__ldcg(acc + j * SZ_HC_ACC_ROWS + q) * SZ_HC_FIX_INV);
-            hd[j][q] = sz_silu(v / (float)C);
-        }
+    if (on) {
+#pragma unroll
+        for (int j = 0; j < M; j++)
+            for (int q = t; q < rank; q += 256) {
+                const float v = (float)((double)__ldcg(acc + j * SZ_HC_ACC_ROWS + q) * SZ_HC_FIX_INV);
+                hd[j][q] = sz_silu(v / (float)C);
+            }
+    }
     __syncthreads();
     SZ_PH();  // 2 hd
     // all partial dot products first, then the butterflies over the cpr lanes of a row interleaved (independent chains).  A thread's
@@ -411,7 +415,6 @@ sz_hc_up_body(const long long* __restrict__ acc, const float* __restrict__ rn, i
     if (on) {
         float p[8][M];
         {
-            const int c = t % cpr;
             float4 x0[M], x1[M];
 #pragma unroll
             for (int j = 0; j < M; j++) { x0[j] = *(const float4*)&hd[j][8 * c]; x1[j] = *(const float4*)&hd[j][8 * c + 4]; }
@@ -439,9 +442,8 @@ sz_hc_up_body(const long long* __restrict__ acc, const float* __restrict__ rn, i
         }
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-            const int ch = t + 256 * i;
-            if (ch < chunks && ch % cpr == 0) {
-                const int lr = ch / cpr;
+            const int lr = lr0 + step * i;
+            if (c == 0 && lr < 16 * C) {
 #pragma unroll
                 for (int j = 0; j < M; j++)
                     if (j < M) mixs[lr][j] = p[i][j];
