@@ -349,8 +349,8 @@ static __global__ void __launch_bounds__(256, 2) sz_dense_q8_kernel(const SzDens
         for (int i = 0; i < c.NS - 1 && i < count; i++) issue(i);
     sz_pdl_wait();
     sz_pdl_trigger();
-    for (int i = threadIdx.x; i < a.m * (a.cols / 4); i += 256) {
-        const int j = i / (a.cols / 4), c4 = i - j * (a.cols / 4);
+    for (int j = 0; j < a.m; j++)
+      for (int c4 = threadIdx.x; c4 < a.cols / 4; c4 += 256) {
         const float4 v = __ldcg((const float4*)(a.x + (size_t)j * a.xstride) + c4);
         const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
         const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);

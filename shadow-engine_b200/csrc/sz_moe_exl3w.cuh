@@ -253,11 +253,16 @@ sz_xw_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     if (warp == SZ_XW_CONSUMERS) {
         // ---- producer: copies and fragments of unit i into stage i % S
         int prev_key = -1, prev_st = 0;
+        // the unit's (group, matrix, input block, column chunk): divided out once, then stepped (the units of a block follow one another)
+        int key = u0 / NCH, ch = u0 - key * NCH;                  // key = (g, mat, s)
+        int g = key / (2 * NS), mat, s;
+        { const int rem = key - g * 2 * NS; mat = rem / NS; s = rem - mat * NS; }
         for (int i = 0; i < count; i++) {
-            const int u = u0 + i, st = i % S;
+            const int st = i % S;
+            if (i > 0) {
+                if (++ch == NCH) { ch = 0; key++; if (++s == NS) { s = 0; if (++mat == 2) { mat = 0; g++; } } }
+            }
             if (i >= S && !sz_mbar_wait(&R.empty[st], ((i / S) - 1) & 1)) { failed = 1; break; }
-            const int key = u / NCH, ch = u - key * NCH;          // key = (g, mat, s)
-            const int g = key / (2 * NS), rem = key - g * 2 * NS, mat = rem / NS, s = rem - mat * NS;
             const u8* blob;
             int n;
             const u8* rows;
@@ -308,10 +313,14 @@ sz_xw_gateup_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate
     } else {
         // ---- consumers
         const SzXWLane<K> LS = sz_xw_lane<K>(lane);
+        int key = u0 / NCH, ch = u0 - key * NCH;
+        int g = key / (2 * NS), mat, s;
+        { const int rem = key - g * 2 * NS; mat = rem / NS; s = rem - mat * NS; }
         for (int i = 0; i < count; i++) {
-            const int u = u0 + i, st = i % S;
-            const int key = u / NCH, ch = u - key * NCH;
-            const int g = key / (2 * NS), rem = key - g * 2 * NS, mat = rem / NS;
+            const int st = i % S;
+            if (i > 0) {
+                if (++ch == NCH) { ch = 0; if (++s == NS) { s = 0; if (++mat == 2) { mat = 0; g++; } } }
+            }
             if (!sz_mbar_wait(&R.full[st], (i / S) & 1)) { failed = 1; break; }
             float c[TW][4];
             sz_xw_compute<K, TW>(R.stages + (size_t)st * X::STAGE_BYTES, R.frags + st * 256, warp, lane, LS, c);
@@ -442,9 +451,13 @@ sz_xw_down_kernel(const SzPlan* __restrict__ plan, const u8* __restrict__ gate, 
         sz_pdl_wait();
         sz_pdl_trigger();
         const SzXWLane<K> LS = sz_xw_lane<K>(lane);
+        int g = u0 / (KB * NC), kb, cc;   // (divided out once, then stepped, as in the gate / up kernel)
+        { const int rem = u0 - g * KB * NC; kb = rem / NC; cc = rem - kb * NC; }
         for (int i = 0; i < count; i++) {
-            const int u = u0 + i, st = i % S;
-            const int g = u / (KB * NC), rem = u - g * KB * NC, kb = rem / NC, cc = rem - kb * NC;
+            const int st = i % S;
+            if (i > 0) {
+                if (++cc == NC) { cc = 0; if (++kb == KB) { kb = 0; g++; } }
+            }
             if (!sz_mbar_wait(&R.full[st], (i / S) & 1)) { failed = 1; break; }
             float c[TW][4];
             sz_xw_compute<K, TW>(R.stages + (size_t)st * X::STAGE_BYTES, R.frags + st * 256, warp, lane, LS, c);
