@@ -387,6 +387,35 @@ __device__ __forceinline__ void sz_hc_up_fetch(const u8* __restrict__ up, int H,
     }
 }
 
+// One level of the reduce-scatter over the lanes of a row (see sz_hc_up_body).  Before level LVL a lane holds sz_hc_up_held(N, LVL)
+// values: an even count is halved - the lane keeps the half its bit `o` of the lane's place selects, adds the partner's partial of
+// those, and hands over the other half - an odd count (a pass of 3, 5, 6 or 7 rows gets there) stays whole and both sides add, as
+// a butterfly level does.  o == 0: the row has fewer lanes than that, nothing to do.
+__host__ __device__ constexpr int sz_hc_up_held(int n, int levels) {
+    for (int l = 0; l < levels; l++)
+        if (n % 2 == 0) n /= 2;
+    return n;
+}
+template <int N, int LVL>
+__device__ __forceinline__ void sz_hc_up_level(float* v, int o, int place, int& base) {
+    if (o <= 0) return;
+    constexpr int n = sz_hc_up_held(N, LVL);
+    if constexpr (n % 2 == 0) {
+        constexpr int h = n / 2;
+        const bool up = (place & o) != 0;
+#pragma unroll
+        for (int k = 0; k < h; k++) {
+            const float lo = v[k], hi = v[k + h];
+            const float send = up ? lo : hi, keep = up ? hi : lo;
+            v[k] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+        }
+        if (up) base += h;
+    } else {
+#pragma unroll
+        for (int k = 0; k < n; k++) v[k] += __shfl_xor_sync(0xffffffffu, v[k], o);
+    }
+}
+
 // everything after the wait, for the first 256 threads of the block (all of them reach every barrier inside)
 template <int M>
 __device__ __forceinline__ void
@@ -433,20 +462,26 @@ sz_hc_up_body(const long long* __restrict__ acc, const float* __restrict__ rn, i
                 }
             }
         }
-        for (int o = cpr >> 1; o > 0; o >>= 1) {
+        // The sums over the cpr lanes of a row: a butterfly's additions (lane with lane ^ 16, then ^ 8, .. ^ 1: every sum the same
+        // tree), but each level hands half of the lane's values to the partner instead of summing all of them on both sides - a
+        // reduce-scatter: about 8 M shuffles a thread instead of 8 M log2(cpr) - and every lane ends with its share of the finished
+        // sums (a + b on one side is b + a on the other: the bits are the butterfly's).
+        float* v = &p[0][0];          // value i * M + j
+        int base = 0;                 // the first of the values this lane still holds
+        sz_hc_up_level<8 * M, 0>(v, cpr >> 1, c, base);
+        sz_hc_up_level<8 * M, 1>(v, cpr >> 2, c, base);
+        sz_hc_up_level<8 * M, 2>(v, cpr >> 3, c, base);
+        sz_hc_up_level<8 * M, 3>(v, cpr >> 4, c, base);
+        sz_hc_up_level<8 * M, 4>(v, cpr >> 5, c, base);
+        int held = 8 * M;             // values a lane ends with
+        for (int o = cpr >> 1; o > 0; o >>= 1)
+            if (!(held & 1)) held >>= 1;
 #pragma unroll
-            for (int i = 0; i < 8; i++)
-#pragma unroll
-                for (int j = 0; j < M; j++)
-                    if (j < M) p[i][j] += __shfl_xor_sync(0xffffffffu, p[i][j], o);
-        }
-#pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const int lr = lr0 + step * i;
-            if (c == 0 && lr < 16 * C) {
-#pragma unroll
-                for (int j = 0; j < M; j++)
-                    if (j < M) mixs[lr][j] = p[i][j];
+        for (int k = 0; k < 8 * M; k++) {
+            if (k < held) {
+                const int idx = base + k, i = idx / M, j = idx - i * M;
+                const int lr = lr0 + step * i;
+                if (lr < 16 * C) mixs[lr][j] = v[k];
             }
         }
     }
