@@ -765,9 +765,9 @@ static int sz_hc_read_rows(const sz_session* s, cudaStream_t st, const sz_hc& hc
     long long* acc_next = B.acc + ((n + 1) % 3) * B.acc_stride;
     int nt = ((int)c.hc_rank + C + 31) / 32 * 32;
     if (nt < 256) nt = 256;
-    // rows a block row: the kernels keep a row's data in registers, so fewer rows a block mean more blocks a multiprocessor (8 rows:
-    // 168 / 187 registers a thread, one block; 4: two; 2: two and four) and the number of waves stays what it is while a wave gets shorter
-    static const int per = [] { const char* e = getenv("SZ_BATCH_HC_ROWS"); const int v = e ? atoi(e) : 4; return v == 8 || v == 2 ? v : 4; }();
+    // rows a block row: the kernels keep a row's data in registers, so fewer rows a block mean more blocks a multiprocessor (the
+    // second half: 8 or 4 rows two blocks, 2 rows four); measured on a step of 160 rows: 57.7 / 57.5 / 56.8 ms at 8 / 4 / 2
+    static const int per = [] { const char* e = getenv("SZ_BATCH_HC_ROWS"); const int v = e ? atoi(e) : 2; return v == 8 || v == 4 ? v : 2; }();
     cudaError_t e1 = cudaErrorInvalidValue, e2 = cudaErrorInvalidValue;
     // The first half in its many-row form: the norm once a (row, stream), then the products (SZ_BATCH_HC_SPLIT=0: the pass's own
     // kernel with a block row per `per` rows, where every block of a stream redoes the stream's norm; same bits).
@@ -779,8 +779,8 @@ static int sz_hc_read_rows(const sz_session* s, cudaStream_t st, const sz_hc& hc
         SZ_CUDA(sz_launch("hc_rows_down", sz_hc_rows_down_kernel<8>, dim3(CH / 64, rows / 8), dim3(nt), 0, st, true, (const float*)B.rn,
                           (const u8*)hc.down.data, (const u8*)(inject ? hc.inject.data : 0), H, C, (int)c.hc_rank, acc));
         if (per == 8) e2 = sz_launch("hc_up", sz_hc_up_kernel<8>, dim3(H / 16, rows / 8), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data, (const float*)B.rn, H, C, (int)c.hc_rank, B.u);
-        else if (per == 2) e2 = sz_launch("hc_up", sz_hc_up_kernel<2>, dim3(H / 16, rows / 2), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data, (const float*)B.rn, H, C, (int)c.hc_rank, B.u);
-        else e2 = sz_launch("hc_up", sz_hc_up_kernel<4>, dim3(H / 16, rows / 4), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data, (const float*)B.rn, H, C, (int)c.hc_rank, B.u);
+        else if (per == 4) e2 = sz_launch("hc_up", sz_hc_up_kernel<4>, dim3(H / 16, rows / 4), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data, (const float*)B.rn, H, C, (int)c.hc_rank, B.u);
+        else e2 = sz_launch("hc_up", sz_hc_up_kernel<2>, dim3(H / 16, rows / 2), dim3(256), 0, st, true, (const long long*)acc, (const u8*)hc.up.data, (const float*)B.rn, H, C, (int)c.hc_rank, B.u);
         SZ_CUDA(e2);
         return SZ_OK;
     }
